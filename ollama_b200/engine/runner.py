@@ -1,0 +1,477 @@
+"""The model runner: one loaded model, N slots, continuous batching.
+
+This is the in-process replacement of the engine subprocess the reference spawns per model
+(llm/server.go:59-78 lists the calls: Load, Ping, Completion, Embedding, Tokenize, Detokenize, Close,
+MemorySize ...).  Semantics kept from there:
+
+* ``num_parallel`` slots share a cache of ``num_ctx`` tokens each (llm/llama_server.go:375-376);
+* a request reuses the slot whose cached tokens share the longest prefix with its prompt and always
+  re-evaluates at least one token (``cache_prompt``, llm/llama_server.go:1562);
+* when the context fills up, either the oldest half after ``num_keep`` is dropped (context shift,
+  llm/llama_server.go:321-331) or generation ends with ``done_reason = "length"`` (:1713-1727);
+* open-ended generation is bounded at 10 x num_ctx tokens (:106-118) and a run of more than 30
+  identical tokens aborts the request (:1692-1703);
+* final chunk carries prompt/eval counts and durations (:1503-1513, :1719-1727).
+"""
+from __future__ import annotations
+
+import queue
+import threading
+import time
+from dataclasses import dataclass, field
+from typing import Iterator, Sequence
+
+import torch
+
+from ..text.tokenizer import Tokenizer, tokenizer_from_gguf
+from .backend import make_backend, open_model
+from .sampler import Sampler, SamplingParams, TokenLogprob
+
+
+@dataclass
+class RunnerOptions:
+    num_ctx: int = 4096
+    num_batch: int = 512
+    num_parallel: int = 1
+    kv_cache_type: str = "f16"
+    device: str = "auto"
+    flash_attention: bool = True
+    tp: int = 1
+
+
+@dataclass
+class CompletionRequest:
+    prompt: str | Sequence[int] = ""
+    sampling: SamplingParams = field(default_factory=SamplingParams)
+    num_predict: int = -1
+    num_keep: int = 4
+    stop: list[str] = field(default_factory=list)
+    grammar: str | None = None
+    truncate: bool = True
+    shift: bool = True
+    cache_prompt: bool = True
+    add_special: bool = True
+    embedding: bool = False
+    ignore_eos: bool = False
+    preserved_tokens: bool = True     # render special tokens into the text stream (harmony needs them)
+
+
+@dataclass
+class CompletionChunk:
+    content: str = ""
+    tokens: list[int] = field(default_factory=list)
+    done: bool = False
+    done_reason: str = ""
+    prompt_eval_count: int = 0
+    prompt_eval_duration: float = 0.0
+    eval_count: int = 0
+    eval_duration: float = 0.0
+    cached_tokens: int = 0
+    logprobs: list[TokenLogprob] = field(default_factory=list)
+    embedding: list[float] | None = None
+    error: str | None = None
+
+
+class RunnerError(RuntimeError):
+    def __init__(self, msg: str, status: int = 500):
+        super().__init__(msg)
+        self.status = status
+
+
+class _Seq:
+    def __init__(self, req: CompletionRequest, prompt: list[int]):
+        self.req = req
+        self.prompt = prompt
+        self.slot = -1
+        self.n_past = 0                 # tokens whose K/V are in the cache
+        self.cached = 0
+        self.generated: list[int] = []
+        self.out: "queue.Queue[CompletionChunk]" = queue.Queue()
+        self.state = "pending"          # pending -> prefill -> decode -> done
+        self.sampler: Sampler | None = None
+        self.grammar = None
+        self.next_token = -1
+        self.pending_bytes = b""
+        self.held_text = ""
+        self.text_len = 0
+        self.t_prefill = 0.0
+        self.t_decode = 0.0
+        self.n_decoded = 0
+        self.n_prompt_eval = 0
+        self.cancelled = False
+        self.repeat_run = 0
+        self.logprobs: list[TokenLogprob] = []
+        self.limit = 0
+
+
+class Runner:
+    def __init__(self, model_path: str, opts: RunnerOptions | None = None, backend=None):
+        self.opts = opts or RunnerOptions()
+        self.path = model_path
+        t0 = time.time()
+        self.gguf = open_model(model_path)
+        self.backend = backend if backend is not None else make_backend(self.gguf, self.opts.device, opts=self.opts)
+        self.cfg = self.backend.cfg
+        try:
+            self.tokenizer: Tokenizer | None = tokenizer_from_gguf(self.gguf.kv)
+        except (ValueError, NotImplementedError):
+            self.tokenizer = None
+        n_ctx = max(4, int(self.opts.num_ctx))
+        if self.cfg.ctx_train:
+            n_ctx = min(n_ctx, self.cfg.ctx_train)          # llm/server.go:111-116
+        self.n_ctx = n_ctx
+        self.n_slots = max(1, int(self.opts.num_parallel))
+        self.backend.alloc(self.n_slots, self.n_ctx)
+        self.slot_tokens: list[list[int]] = [[] for _ in range(self.n_slots)]
+        self.slot_seq: list[_Seq | None] = [None] * self.n_slots
+        self.slot_used_at = [0.0] * self.n_slots
+        self.pending: list[_Seq] = []
+        self.cv = threading.Condition()
+        self.closed = False
+        self.error: str | None = None
+        self.load_duration = time.time() - t0
+        self.thread = threading.Thread(target=self._loop, name="runner-loop", daemon=True)
+        self.thread.start()
+
+    # -- public calls -------------------------------------------------------------------------------
+    def ping(self) -> bool:
+        return not self.closed and self.thread.is_alive() and self.error is None
+
+    def tokenize(self, text: str, add_special: bool = False, parse_special: bool = True) -> list[int]:
+        if self.tokenizer is None:
+            raise RunnerError("model has no tokenizer", 400)
+        return self.tokenizer.encode(text, add_special=add_special, parse_special=parse_special)
+
+    def detokenize(self, tokens: Sequence[int]) -> str:
+        if self.tokenizer is None:
+            raise RunnerError("model has no tokenizer", 400)
+        return self.tokenizer.decode(tokens)
+
+    def memory(self) -> dict:
+        w, kv = self.backend.weight_bytes(), self.backend.kv_bytes()
+        on_gpu = getattr(self.backend, "name", "torch") != "torch" or str(getattr(self.backend, "device", "cpu")).startswith("cuda")
+        return {"weights": w, "kv": kv, "total": w + kv, "vram": (w + kv) if on_gpu else 0}
+
+    def completion(self, req: CompletionRequest) -> Iterator[CompletionChunk]:
+        seq = self.submit(req)
+        try:
+            while True:
+                ch = seq.out.get()
+                if ch.error:
+                    raise RunnerError(ch.error)
+                yield ch
+                if ch.done:
+                    return
+        finally:
+            seq.cancelled = True
+            with self.cv:
+                self.cv.notify_all()
+
+    def submit(self, req: CompletionRequest) -> _Seq:
+        if self.closed:
+            raise RunnerError("runner is closed")
+        if isinstance(req.prompt, str):
+            toks = self.tokenize(req.prompt, add_special=req.add_special)
+        else:
+            toks = [int(t) for t in req.prompt]
+        if req.embedding and self.tokenizer is not None and self.tokenizer.add_eos is False and self.cfg.pooling == "last":
+            if self.tokenizer.eos >= 0 and (not toks or toks[-1] != self.tokenizer.eos):
+                toks = toks + [self.tokenizer.eos]
+        if not toks:
+            toks = [self.tokenizer.bos if self.tokenizer and self.tokenizer.bos >= 0 else 0]
+        limit = self.n_ctx - 1
+        if len(toks) > limit:
+            if not req.truncate or req.embedding:
+                raise RunnerError("the prompt is longer than the context length currently available to the model; shorten the "
+                                  "prompt, adjust the context length in settings, or use a model with a longer context length", 400)
+            keep = min(max(req.num_keep, 0), limit // 2)
+            toks = toks[:keep] + toks[len(toks) - (limit - keep):]
+        seq = _Seq(req, toks)
+        with self.cv:
+            self.pending.append(seq)
+            self.cv.notify_all()
+        return seq
+
+    def embedding(self, text: str | Sequence[int]) -> tuple[list[float], int]:
+        seq = self.submit(CompletionRequest(prompt=text, embedding=True, truncate=False))
+        ch = seq.out.get()
+        if ch.error:
+            raise RunnerError(ch.error)
+        return ch.embedding or [], ch.prompt_eval_count
+
+    def close(self) -> None:
+        with self.cv:
+            self.closed = True
+            self.cv.notify_all()
+        self.thread.join(timeout=30)
+        self.backend.close()
+        self.gguf.close()
+
+    # -- batching loop -------------------------------------------------------------------------------
+    def _loop(self) -> None:
+        try:
+            while True:
+                with self.cv:
+                    while not self.closed and not self.pending and not any(self.slot_seq):
+                        self.cv.wait(timeout=0.5)
+                    if self.closed:
+                        break
+                    self._admit()
+                self._step()
+        except Exception as e:  # a failed step poisons the runner; the scheduler replaces it
+            import traceback
+            self.error = f"{type(e).__name__}: {e}"
+            traceback.print_exc()
+            for s in list(self.slot_seq) + list(self.pending):
+                if s is not None:
+                    s.out.put(CompletionChunk(done=True, error=self.error))
+            self.closed = True
+        finally:
+            for s in list(self.slot_seq) + list(self.pending):
+                if s is not None and s.state != "done":
+                    s.out.put(CompletionChunk(done=True, error=self.error or "runner closed"))
+
+    def _admit(self) -> None:
+        while self.pending:
+            free = [i for i in range(self.n_slots) if self.slot_seq[i] is None]
+            if not free:
+                return
+            seq = self.pending.pop(0)
+            if seq.cancelled:
+                continue
+            best, best_lcp = free[0], -1
+            for i in free:
+                lcp = _common_prefix(self.slot_tokens[i], seq.prompt) if seq.req.cache_prompt else 0
+                if lcp > best_lcp or (lcp == best_lcp and self.slot_used_at[i] < self.slot_used_at[best]):
+                    best, best_lcp = i, lcp
+            reuse = max(0, min(best_lcp, len(seq.prompt) - 1))   # always evaluate at least one token
+            if seq.req.embedding or not self.cfg.causal:
+                reuse = 0
+            seq.slot, seq.n_past, seq.cached = best, reuse, reuse
+            del self.slot_tokens[best][reuse:]
+            self.slot_seq[best] = seq
+            seq.state = "prefill"
+            r = seq.req
+            seq.sampler = Sampler(r.sampling, self.cfg.vocab_size, self.n_ctx, history=seq.prompt)
+            if r.grammar:
+                from .grammar import Grammar
+                seq.grammar = Grammar(r.grammar, self.tokenizer)
+            seq.limit = r.num_predict if r.num_predict >= 0 else 10 * self.n_ctx
+
+    def _step(self) -> None:
+        active = [s for s in self.slot_seq if s is not None]
+        for s in active:
+            if s.cancelled and s.state != "done":
+                self._finish(s, "cancelled")
+        # one prefill chunk per iteration keeps decode latency of the other slots bounded
+        for s in active:
+            if s.state == "prefill":
+                self._prefill_chunk(s)
+                break
+        dec = [s for s in self.slot_seq if s is not None and s.state == "decode"]
+        if dec:
+            self._decode(dec)
+
+    def _prefill_chunk(self, s: _Seq) -> None:
+        t0 = time.perf_counter()
+        remaining = len(s.prompt) - s.n_past
+        n = min(remaining, max(1, self.opts.num_batch))
+        chunk = s.prompt[s.n_past:s.n_past + n]
+        last = n == remaining
+        if s.req.embedding:
+            hid = self.backend.hidden(s.slot, s.prompt)
+            vec = _pool(hid.float(), self.cfg.pooling)
+            _sync(hid)
+            s.n_prompt_eval = len(s.prompt)
+            s.out.put(CompletionChunk(done=True, done_reason="stop", embedding=vec.tolist(), prompt_eval_count=len(s.prompt),
+                                      prompt_eval_duration=time.perf_counter() - t0))
+            self.slot_tokens[s.slot] = []
+            self._release(s)
+            return
+        logits = self.backend.prefill(s.slot, chunk, s.n_past, need_logits=last)
+        s.n_past += n
+        s.n_prompt_eval += n
+        self.slot_tokens[s.slot].extend(chunk)
+        if last:
+            tok, lp = s.sampler.sample(logits, s.grammar.allows if s.grammar else None)
+            s.t_prefill += time.perf_counter() - t0
+            s.state = "decode"
+            self._accept(s, tok, lp)
+        else:
+            _sync(None)
+            s.t_prefill += time.perf_counter() - t0
+
+    def _decode(self, seqs: list[_Seq]) -> None:
+        t0 = time.perf_counter()
+        ready: list[_Seq] = []
+        for s in seqs:
+            if s.n_past + 1 > self.n_ctx:
+                if not self._shift(s):
+                    continue
+            ready.append(s)
+        if not ready:
+            return
+        slots = [s.slot for s in ready]
+        toks = [s.next_token for s in ready]
+        poss = [s.n_past for s in ready]
+        fast = hasattr(self.backend, "decode_argmax") and all(
+            s.sampler.p.greedy and not s.sampler.p.has_penalties and s.grammar is None and not s.sampler.p.logprobs for s in ready)
+        if fast:
+            out = self.backend.decode_argmax(slots, toks, poss)
+            sampled = [(int(t), None) for t in out]
+            for s, (t, _) in zip(ready, sampled):
+                s.sampler.accept(t)
+        else:
+            logits = self.backend.decode(slots, toks, poss)
+            sampled = [s.sampler.sample(logits[i], s.grammar.allows if s.grammar else None) for i, s in enumerate(ready)]
+        dt = time.perf_counter() - t0
+        for s, (tok, lp) in zip(ready, sampled):
+            self.slot_tokens[s.slot].append(s.next_token)
+            s.n_past += 1
+            s.t_decode += dt
+            s.n_decoded += 1
+            self._accept(s, tok, lp)
+
+    def _shift(self, s: _Seq) -> bool:
+        """Context is full: drop half of the tokens after ``num_keep`` and rebuild the cache for the rest."""
+        if not s.req.shift:
+            self._finish(s, "length")
+            return False
+        keep = min(max(s.req.num_keep, 0), self.n_ctx // 2)
+        toks = self.slot_tokens[s.slot]
+        discard = max(1, (len(toks) - keep) // 2)
+        new = toks[:keep] + toks[keep + discard:]
+        self.slot_tokens[s.slot] = new[:keep]
+        tail = new[keep:]
+        pos = keep
+        while tail:
+            chunk, tail = tail[: self.opts.num_batch], tail[self.opts.num_batch:]
+            self.backend.prefill(s.slot, chunk, pos, need_logits=False)
+            pos += len(chunk)
+        self.slot_tokens[s.slot] = new
+        s.n_past = len(new)
+        return True
+
+    def _accept(self, s: _Seq, tok: int, lp: TokenLogprob | None) -> None:
+        """Handle a freshly sampled token: stop conditions, detokenise, stream."""
+        tk = self.tokenizer
+        s.generated.append(tok)
+        if s.grammar is not None:
+            s.grammar.accept(tok)
+        if s.next_token == tok:
+            s.repeat_run += 1
+        else:
+            s.repeat_run = 0
+        s.next_token = tok
+        if lp is not None:
+            s.logprobs.append(lp)
+        if tk is not None and tk.is_eog(tok) and not s.req.ignore_eos:
+            s.generated.pop()
+            self._flush(s, final=True)
+            self._finish(s, "stop")
+            return
+        piece = b""
+        if tk is not None:
+            if tok in tk.special and not s.req.preserved_tokens:
+                piece = b""
+            else:
+                piece = tk.token_bytes(tok) if 0 <= tok < tk.n_vocab else b""
+        s.pending_bytes += piece
+        text, s.pending_bytes = _valid_utf8_prefix(s.pending_bytes)
+        stopped = self._emit(s, text, [tok])
+        if stopped:
+            self._finish(s, "stop")
+        elif s.grammar is not None and s.grammar.done():
+            self._flush(s, final=True)
+            self._finish(s, "stop")
+        elif len(s.generated) >= s.limit:
+            self._flush(s, final=True)
+            self._finish(s, "length")
+        elif s.repeat_run > 30:
+            self._flush(s, final=True)
+            self._finish(s, "stop")
+
+    def _emit(self, s: _Seq, text: str, toks: list[int]) -> bool:
+        """Stream ``text`` while holding back anything that may still turn into a stop string."""
+        buf = s.held_text + text
+        for st in s.req.stop:
+            if st and st in buf:
+                buf = buf[: buf.index(st)]
+                s.held_text = ""
+                if buf:
+                    s.out.put(CompletionChunk(content=buf, tokens=toks, logprobs=self._take_lp(s)))
+                return True
+        hold = 0
+        for st in s.req.stop:
+            for k in range(min(len(st) - 1, len(buf)), 0, -1):
+                if buf.endswith(st[:k]):
+                    hold = max(hold, k)
+                    break
+        out, s.held_text = (buf[: len(buf) - hold], buf[len(buf) - hold:]) if hold else (buf, "")
+        if out or toks:
+            s.out.put(CompletionChunk(content=out, tokens=toks, logprobs=self._take_lp(s)))
+        return False
+
+    def _take_lp(self, s: _Seq) -> list[TokenLogprob]:
+        lps, s.logprobs = s.logprobs, []
+        return lps
+
+    def _flush(self, s: _Seq, final: bool = False) -> None:
+        text = s.held_text
+        if final and s.pending_bytes:
+            text += s.pending_bytes.decode("utf-8", errors="replace")
+            s.pending_bytes = b""
+        s.held_text = ""
+        if text:
+            s.out.put(CompletionChunk(content=text, logprobs=self._take_lp(s)))
+
+    def _finish(self, s: _Seq, reason: str) -> None:
+        if s.state == "done":
+            return
+        s.out.put(CompletionChunk(done=True, done_reason=reason, prompt_eval_count=len(s.prompt),
+                                  prompt_eval_duration=s.t_prefill, eval_count=len(s.generated), eval_duration=s.t_decode,
+                                  cached_tokens=s.cached, logprobs=self._take_lp(s)))
+        self._release(s)
+
+    def _release(self, s: _Seq) -> None:
+        s.state = "done"
+        if s.slot >= 0 and self.slot_seq[s.slot] is s:
+            self.slot_seq[s.slot] = None
+            self.slot_used_at[s.slot] = time.time()
+
+
+def _common_prefix(a: Sequence[int], b: Sequence[int]) -> int:
+    n = min(len(a), len(b))
+    i = 0
+    while i < n and a[i] == b[i]:
+        i += 1
+    return i
+
+
+def _valid_utf8_prefix(b: bytes) -> tuple[str, bytes]:
+    """Split ``b`` into the longest decodable prefix and the incomplete trailing sequence."""
+    if not b:
+        return "", b""
+    cut = len(b)
+    for back in range(1, min(4, len(b)) + 1):
+        c = b[-back]
+        if c & 0xC0 == 0x80:
+            continue
+        need = 1 if c < 0x80 else 2 if c >> 5 == 0b110 else 3 if c >> 4 == 0b1110 else 4 if c >> 3 == 0b11110 else 1
+        if need > back:
+            cut = len(b) - back
+        break
+    return b[:cut].decode("utf-8", errors="replace"), b[cut:]
+
+
+def _pool(hid: torch.Tensor, mode: str) -> torch.Tensor:
+    if mode == "cls":
+        return hid[0]
+    if mode == "last":
+        return hid[-1]
+    return hid.mean(0)
+
+
+def _sync(t) -> None:
+    if torch.cuda.is_available():
+        torch.cuda.synchronize()

@@ -1,0 +1,91 @@
+"""In-memory normalisation of legacy GGUF spellings to the current conventions.
+
+Older published blobs differ from today's key and tensor names; the reference fixes them while
+loading (llama/compat/llama-ollama-compat.cpp:3239-3286 dispatches per architecture; gpt-oss rules
+at :1510-1555, gemma3 at :237-275, llama3 tokenizer metadata at :1334-1355).  Here the same rules are
+a table applied to the opened :class:`GGUFFile` (nothing is written back to disk).  Set
+``OLLAMA_LLAMA_CPP_COMPAT=0`` to switch the normaliser off (llama/compat/README.md:64-66).
+"""
+from __future__ import annotations
+
+import os
+
+from .reader import GGUFFile
+
+_GEMMA3_TEMPLATE = (
+    "{{ bos_token }}{% for message in messages %}{% if message['role'] == 'assistant' %}{% set role = 'model' %}"
+    "{% else %}{% set role = message['role'] %}{% endif %}<start_of_turn>{{ role }}\n{{ message['content'] | trim }}"
+    "<end_of_turn>\n{% endfor %}{% if add_generation_prompt %}<start_of_turn>model\n{% endif %}"
+)
+
+# arch -> list of (needle, replacement) applied once per tensor name
+_TENSOR_RENAMES = {
+    "gpt-oss": [(".attn_out.", ".attn_output."), (".attn_sinks", ".attn_sinks.weight"), (".ffn_norm.", ".post_attention_norm.")],
+}
+
+
+def _rename_prefix(g: GGUFFile, old: str, new: str) -> None:
+    for k in [k for k in g.kv if k.startswith(old)]:
+        nk = new + k[len(old):]
+        g.kv.setdefault(nk, g.kv[k])
+        if k in g.kv_types:
+            g.kv_types.setdefault(nk, g.kv_types[k])
+
+
+def _rename_tensors(g: GGUFFile, rules) -> None:
+    out = {}
+    for name, ti in g.tensors.items():
+        new = name
+        for needle, repl in rules:
+            if needle in new and repl not in new:
+                new = new.replace(needle, repl, 1)
+        if new.endswith(".weight.weight"):
+            new = new[: -len(".weight")]
+        ti.name = new
+        out[new] = ti
+    g.tensors.clear()
+    g.tensors.update(out)
+
+
+def normalise(g: GGUFFile) -> GGUFFile:
+    if os.environ.get("OLLAMA_LLAMA_CPP_COMPAT", "1") == "0":
+        return g
+    arch = g.kv.get("general.architecture", "")
+    if arch == "gptoss":
+        g.kv["general.architecture"] = "gpt-oss"
+        _rename_prefix(g, "gptoss.", "gpt-oss.")
+        if "gpt-oss.expert_feed_forward_length" not in g.kv and "blk.0.ffn_gate_exps.weight" in g.tensors:
+            g.kv["gpt-oss.expert_feed_forward_length"] = int(g.tensors["blk.0.ffn_gate_exps.weight"].shape[1])
+        g.kv.setdefault("gpt-oss.rope.scaling.type", "yarn")
+        g.kv["tokenizer.ggml.pre"] = "gpt-4o"
+        _rename_tensors(g, _TENSOR_RENAMES["gpt-oss"])
+    elif arch == "gemma3":
+        if "gemma3.rope.global.freq_base" in g.kv:
+            g.kv.setdefault("gemma3.rope.freq_base", g.kv["gemma3.rope.global.freq_base"])
+        if "gemma3.rope.freq_base_swa" in g.kv:
+            g.kv.setdefault("gemma3.rope.local.freq_base", g.kv["gemma3.rope.freq_base_swa"])
+        g.kv.setdefault("gemma3.attention.layer_norm_rms_epsilon", 1e-6)
+        g.kv.setdefault("gemma3.rope.freq_base", 1000000.0)
+        g.kv.setdefault("gemma3.rope.local.freq_base", 10000.0)
+        g.kv.setdefault("tokenizer.chat_template", _GEMMA3_TEMPLATE)
+        if int(g.kv.get("gemma3.context_length", 0)) >= 131072:
+            g.kv.setdefault("gemma3.rope.scaling.type", "linear")
+            g.kv.setdefault("gemma3.rope.scaling.factor", 8.0)
+        # extra multimodal tokens beyond the embedding rows are dropped from the vocabulary arrays
+        if "token_embd.weight" in g.tensors:
+            rows = int(g.tensors["token_embd.weight"].shape[-1])
+            for k in ("tokenizer.ggml.tokens", "tokenizer.ggml.scores", "tokenizer.ggml.token_type"):
+                v = g.kv.get(k)
+                if v is not None and hasattr(v, "__len__") and len(v) > rows:
+                    g.kv[k] = v[:rows]
+    elif arch == "llama":
+        # Llama-3 blobs whose tokenizer block lacks the pre-tokenizer id / end-of-turn ids
+        toks = g.kv.get("tokenizer.ggml.tokens")
+        is_l3 = g.kv.get("tokenizer.ggml.model") == "gpt2" and toks is not None and len(toks) >= 128256
+        if is_l3:
+            if g.kv.get("tokenizer.ggml.pre", "default") in ("", "default"):
+                g.kv["tokenizer.ggml.pre"] = "llama-bpe"
+            if int(g.kv.get("tokenizer.ggml.eos_token_id", 128001)) == 128001:
+                g.kv["tokenizer.ggml.eos_token_id"] = 128009
+                g.kv["tokenizer.ggml.eos_token_ids"] = [128009]
+    return g
