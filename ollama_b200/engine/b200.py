@@ -1,0 +1,378 @@
+"""The sm_100a execution engine.
+
+One process drives one GPU.  Weights stay in their GGUF quantisation, re-laid out into aligned planes
+(``ops/cuda.py``); the KV cache is f16, partitioned by slot: ``[slot][kv_head][position][dim]`` per
+layer.  A decode step for up to eight sequences is a fixed sequence of hand-written kernels
+
+    embed -> L x [ rmsnorm+quant -> QKV GEMV -> qk-norm+RoPE+cache append -> split-K attention
+                   -> O GEMV (+residual) -> rmsnorm+quant -> gate/up GEMV + GLU + quant
+                   -> down GEMV (+residual) ] -> rmsnorm+quant -> LM-head GEMV -> arg-max
+
+captured once per batch size into a CUDA graph (kernels are launched with programmatic dependent
+launch so that the launch latency of kernel i+1 hides behind kernel i) and replayed with device-side
+token / position / slot arrays.  Prefill runs chunked through the tensor-core GEMM path.
+
+In the reference this layer is the external engine process (SURVEY of the runner protocol:
+llm/server.go:59-78); its kernels are ggml-cuda's mmvq / mmq / fattn / norm / rope families.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import math
+from typing import Sequence
+
+import torch
+
+from ..gguf.reader import GGUFFile
+from ..models.config import ModelConfig, config_from_gguf
+from ..models.weights import QWeight, load_tensor
+from ..ops import cuda as K
+from ..ops import reference as R
+
+MAX_DECODE_BATCH = 8
+
+
+def supports(cfg: ModelConfig) -> bool:
+    return cfg.arch in ("llama", "mistral", "qwen2", "qwen3", "gemma", "gemma2", "gemma3") and not cfg.is_moe \
+        and cfg.head_dim in (32, 64, 128, 256) and cfg.head_dim == cfg.v_head_dim and cfg.d_model % 256 == 0 \
+        and cfg.d_ff % 32 == 0
+
+
+class _Layer:
+    pass
+
+
+class B200Backend:
+    name = "b200"
+
+    def __init__(self, g: GGUFFile | None, device: str = "cuda", opts=None, cfg: ModelConfig | None = None,
+                 tensors: dict[str, QWeight] | None = None, keep_bf16: bool = True):
+        """Load from an opened GGUF, or from ``cfg`` + an iterable source of :class:`QWeight` (synthetic checkpoints)."""
+        self.device = torch.device(device if device != "cuda" else f"cuda:{torch.cuda.current_device()}")
+        self.cfg = cfg if cfg is not None else config_from_gguf(g)
+        if not supports(self.cfg):
+            raise NotImplementedError(f"{self.cfg.arch} is not supported by the sm_100a engine")
+        K.lib()
+        self.keep_bf16 = keep_bf16
+        self.n_slots = self.n_ctx = 0
+        self._graphs: dict[tuple[int, bool], torch.cuda.CUDAGraph] = {}
+        self.pdl = True
+        self.use_graphs = True
+        self.launches_per_step = 0
+        self.launches_by_key: dict = {}
+        self._warm: set = set()
+        self.kernel_launches = 0          # kernels of this library executed so far (graph nodes count individually)
+        self.h2d_bytes = self.d2h_bytes = 0
+        self._load(g, tensors)
+
+    # -- loading ------------------------------------------------------------------------------------
+    def _load(self, g: GGUFFile | None, tensors) -> None:
+        c, dev = self.cfg, self.device
+
+        def has(name):
+            return (name in tensors) if tensors is not None else g.has(name)
+
+        def get(name) -> QWeight:
+            return tensors[name] if tensors is not None else load_tensor(g, name)
+
+        def vec(name) -> torch.Tensor | None:
+            if not has(name):
+                return None
+            return get(name).dequant().to(dev).contiguous()
+
+        def mat(name) -> K.DevWeight:
+            w = K.repack(get(name + ".weight"), dev, bias=vec(name + ".bias"))
+            if self.keep_bf16:
+                w.bf16 = K.dequant_to_bf16(w)
+            return w
+
+        self.embd = K.repack(get("token_embd.weight"), dev)
+        self.out_norm = vec("output_norm.weight")
+        self.head = mat("output") if has("output.weight") else self.embd
+        if self.keep_bf16 and not hasattr(self.head, "bf16"):
+            self.head.bf16 = K.dequant_to_bf16(self.head)
+        self.layers: list[_Layer] = []
+        for i in range(c.n_layers):
+            p, L = f"blk.{i}.", _Layer()
+            L.attn_norm = vec(p + "attn_norm.weight")
+            L.wq, L.wk, L.wv, L.wo = mat(p + "attn_q"), mat(p + "attn_k"), mat(p + "attn_v"), mat(p + "attn_output")
+            L.q_norm, L.k_norm = vec(p + "attn_q_norm.weight"), vec(p + "attn_k_norm.weight")
+            L.post_attn_norm = vec(p + "post_attention_norm.weight") if c.sandwich_norm else None
+            L.ffn_norm = vec(p + "ffn_norm.weight")
+            if L.ffn_norm is None:
+                L.ffn_norm = vec(p + "post_attention_norm.weight")
+            L.post_ffw_norm = vec(p + "post_ffw_norm.weight") if c.sandwich_norm else None
+            L.gate, L.up, L.down = mat(p + "ffn_gate"), mat(p + "ffn_up"), mat(p + "ffn_down")
+            L.sinks = vec(p + "attn_sinks.weight")
+            L.swa = c.layer_is_swa(i)
+            self.layers.append(L)
+        ff = vec("rope_freqs.weight")
+        kw = dict(scaling=c.rope_scaling_type if c.rope_scaling_type != "llama3" else "none", factor=c.rope_scaling_factor,
+                  orig_ctx=c.rope_orig_ctx, beta_fast=c.yarn_beta_fast, beta_slow=c.yarn_beta_slow, device=dev)
+        self.inv_freq, self.mscale = R.rope_inv_freq(c.rope_dim, c.rope_base, freq_factors=ff, **kw)
+        self.inv_freq = self.inv_freq.contiguous()
+        self.inv_freq_local = self.inv_freq
+        if c.rope_base_local > 0:
+            self.inv_freq_local = R.rope_inv_freq(c.rope_dim, c.rope_base_local, device=dev)[0].contiguous()
+        self.attn_scale = c.scale
+        if c.arch in ("gemma2", "gemma3") and c.n_layers in (46, 62):
+            self.attn_scale = 1.0 / math.sqrt(c.d_model / c.n_heads)
+        torch.cuda.synchronize(dev)
+
+    def weight_bytes(self) -> int:
+        ws = [self.embd] + ([self.head] if self.head is not self.embd else [])
+        for L in self.layers:
+            ws += [L.wq, L.wk, L.wv, L.wo, L.gate, L.up, L.down]
+        return sum(w.nbytes for w in ws)
+
+    def kv_bytes(self) -> int:
+        return sum(t.numel() * 2 for t in getattr(self, "k_cache", [])) * 2
+
+    # -- buffers --------------------------------------------------------------------------------------
+    def alloc(self, n_slots: int, n_ctx: int) -> None:
+        c, dev = self.cfg, self.device
+        self.n_slots, self.n_ctx = n_slots, n_ctx
+        self.k_cache = [torch.zeros(n_slots, c.n_kv_heads, n_ctx, c.head_dim, device=dev, dtype=torch.float16) for _ in range(c.n_layers)]
+        self.v_cache = [torch.zeros(n_slots, c.n_kv_heads, n_ctx, c.head_dim, device=dev, dtype=torch.float16) for _ in range(c.n_layers)]
+        MB = MAX_DECODE_BATCH
+        f32, i8, i32 = torch.float32, torch.int8, torch.int32
+        qkv_dim = (c.n_heads + 2 * c.n_kv_heads) * c.head_dim
+        kmax = max(c.d_model, c.q_dim)
+        self.n_splits = max(1, min(32, n_ctx // 512))
+        b = self.buf = _Layer()
+        b.x = torch.zeros(MB, c.d_model, device=dev, dtype=f32)
+        b.tmp = torch.zeros(MB, c.d_model, device=dev, dtype=f32)
+        b.xq = torch.zeros(MB, kmax, device=dev, dtype=i8)
+        b.xds = torch.zeros(MB, kmax // 32, 2, device=dev, dtype=f32)
+        b.xf = torch.zeros(MB, kmax, device=dev, dtype=f32)
+        b.qkv = torch.zeros(MB, qkv_dim, device=dev, dtype=f32)
+        b.q = torch.zeros(MB, c.n_heads, c.head_dim, device=dev, dtype=f32)
+        b.ao = torch.zeros(MB, c.q_dim, device=dev, dtype=f32)
+        b.aq = torch.zeros(MB, c.q_dim, device=dev, dtype=i8)
+        b.ads = torch.zeros(MB, c.q_dim // 32, 2, device=dev, dtype=f32)
+        b.hq = torch.zeros(MB, c.d_ff, device=dev, dtype=i8)
+        b.hds = torch.zeros(MB, c.d_ff // 32, 2, device=dev, dtype=f32)
+        b.hf = torch.zeros(MB, c.d_ff, device=dev, dtype=f32)
+        b.logits = torch.zeros(MB, c.vocab_size, device=dev, dtype=f32)
+        b.part_acc = torch.zeros(MB * c.n_heads * self.n_splits * c.head_dim, device=dev, dtype=f32)
+        b.part_ml = torch.zeros(MB * c.n_heads * self.n_splits * 2, device=dev, dtype=f32)
+        b.meta = torch.zeros(3, MB, device=dev, dtype=i32)          # tokens | positions | slots of the decode batch
+        b.tokens, b.positions, b.slots = b.meta[0], b.meta[1], b.meta[2]
+        b.sampled = torch.zeros(MB, device=dev, dtype=i32)
+        b.host_in = torch.zeros(3, MB, dtype=i32).pin_memory()
+        b.host_out = torch.zeros(MB, dtype=i32).pin_memory()
+        b.host_np, b.host_out_np = b.host_in.numpy(), b.host_out.numpy()
+        self._graphs.clear()
+        self._warm.clear()
+
+    def close(self) -> None:
+        self._graphs.clear()
+        self.k_cache = self.v_cache = []
+        self.buf = None
+
+    # -- decode ---------------------------------------------------------------------------------------
+    def _norm_quant(self, x, w, nb, k, *, do_norm=True, residual=None, src=None):
+        b = self.buf
+        a = K.NormQuantArgs(K.ptr(x if src is None else src), K.ptr(w), self.cfg.norm_eps, k, int(do_norm), K.ptr(b.xq), K.ptr(b.xds),
+                            K.ptr(b.xf), K.ptr(residual))
+        K._check(K.lib().b2_rmsnorm_quant(C.byref(a), nb, int(self.pdl), K.stream()), "rmsnorm_quant")
+        self._n += 1
+
+    def _gemv(self, ws, nb, xq, xds, xf, out, ldo, accumulate=False):
+        a = K.GemvArgs()
+        off = 0
+        for i, w in enumerate(ws):
+            a.seg[i] = w.desc(out_off=off)
+            off += w.n
+        a.nseg, a.nb = len(ws), nb
+        a.xq, a.xds, a.xf, a.out, a.ldo, a.accumulate = K.ptr(xq), K.ptr(xds), K.ptr(xf), K.ptr(out), ldo, int(accumulate)
+        K._check(K.lib().b2_gemv(C.byref(a), int(self.pdl), K.stream()), "gemv")
+        self._n += 1
+
+    def _decode_kernels(self, nb: int, want_argmax: bool) -> None:
+        """Enqueue one decode step for ``nb`` sequences on the current stream (inputs: buf.tokens/positions/slots)."""
+        c, b, lib, st = self.cfg, self.buf, K.lib(), K.stream
+        self._n = 0
+        K.embed(self.embd, b.tokens[:nb], c.embed_scale, out=b.x)
+        self._n += 1
+        act = K._ACT[c.act]
+        for i, L in enumerate(self.layers):
+            self._norm_quant(b.x, L.attn_norm, nb, c.d_model)
+            self._gemv([L.wq, L.wk, L.wv], nb, b.xq, b.xds, b.xf, b.qkv, b.qkv.stride(0))
+            local = L.swa and c.rope_base_local > 0
+            ra = K.RopeKvArgs(K.ptr(b.qkv), K.ptr(b.positions), K.ptr(b.slots), K.ptr(self.inv_freq_local if local else self.inv_freq),
+                              K.ptr(L.q_norm), K.ptr(L.k_norm), c.norm_eps, 1.0 if local else self.mscale, c.n_heads, c.n_kv_heads,
+                              c.head_dim, c.rope_dim, int(c.rope_style == "neox"), self.n_ctx, K.ptr(b.q), K.ptr(self.k_cache[i]),
+                              K.ptr(self.v_cache[i]))
+            K._check(lib.b2_rope_kv(C.byref(ra), nb, int(self.pdl), st()), "rope_kv")
+            aa = K.AttnDecodeArgs(K.ptr(b.q), K.ptr(self.k_cache[i]), K.ptr(self.v_cache[i]), K.ptr(b.positions), K.ptr(b.slots),
+                                  c.n_heads, c.n_kv_heads, self.n_ctx, self.n_splits, self.attn_scale, c.attn_softcap,
+                                  c.sliding_window if L.swa else 0, K.ptr(b.part_acc), K.ptr(b.part_ml))
+            ca = K.AttnCombineArgs(K.ptr(b.part_acc), K.ptr(b.part_ml), K.ptr(L.sinks), c.n_heads, self.n_splits, c.head_dim,
+                                   K.ptr(b.ao), K.ptr(b.aq), K.ptr(b.ads))
+            K._check(lib.b2_attn_decode(C.byref(aa), C.byref(ca), nb, c.head_dim, int(self.pdl), st()), "attn_decode")
+            self._n += 3
+            if c.sandwich_norm:
+                self._gemv([L.wo], nb, b.aq, b.ads, b.ao, b.tmp, b.tmp.stride(0))
+                self._norm_quant(b.tmp, L.post_attn_norm, nb, c.d_model, residual=b.x)
+            else:
+                self._gemv([L.wo], nb, b.aq, b.ads, b.ao, b.x, b.x.stride(0), accumulate=True)
+            self._norm_quant(b.x, L.ffn_norm, nb, c.d_model)
+            ga = K.GluArgs()
+            ga.gate, ga.up = L.gate.desc(), L.up.desc()
+            ga.nb, ga.xq, ga.xds, ga.xf = nb, K.ptr(b.xq), K.ptr(b.xds), K.ptr(b.xf)
+            ga.act, ga.alpha, ga.limit = act, c.swiglu_alpha, c.swiglu_limit
+            ga.hq, ga.hds, ga.hf = K.ptr(b.hq), K.ptr(b.hds), K.ptr(b.hf) if not L.down.quant_input else None
+            K._check(lib.b2_gemv_glu_quant(C.byref(ga), int(self.pdl), st()), "gemv_glu_quant")
+            self._n += 1
+            if c.sandwich_norm:
+                self._gemv([L.down], nb, b.hq, b.hds, b.hf, b.tmp, b.tmp.stride(0))
+                self._norm_quant(b.tmp, L.post_ffw_norm, nb, c.d_model, residual=b.x)
+            else:
+                self._gemv([L.down], nb, b.hq, b.hds, b.hf, b.x, b.x.stride(0), accumulate=True)
+        self._norm_quant(b.x, self.out_norm, nb, c.d_model)
+        self._gemv([self.head], nb, b.xq, b.xds, b.xf, b.logits, b.logits.stride(0))
+        if want_argmax:
+            K.argmax(b.logits[:nb], out=b.sampled)
+            self._n += 1
+        if want_argmax == "loop":     # feed the sampled token back on the device: no host round trip between steps
+            lib.b2_advance.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_void_p]
+            K._check(lib.b2_advance(K.ptr(b.tokens), K.ptr(b.positions), K.ptr(b.sampled), nb, st()), "advance")
+            self._n += 1
+        self.launches_per_step = self._n
+
+    def _run_step(self, nb: int, mode) -> None:
+        """mode: False = logits only, True = + arg-max, "loop" = + arg-max and on-device token feedback."""
+        key = (nb, mode)
+        self.kernel_launches += self.launches_by_key.get(key, 0)
+        if not self.use_graphs:
+            self._decode_kernels(nb, mode)
+            self.launches_by_key[key] = self.launches_per_step
+            return
+        g = self._graphs.get(key)
+        if g is None:
+            # the first call runs eagerly (loads the kernels); the second call records the graph
+            if key not in self._warm:
+                self._warm.add(key)
+                self._decode_kernels(nb, mode)
+                self.launches_by_key[key] = self.launches_per_step
+                return
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g):
+                self._decode_kernels(nb, mode)
+            self._graphs[key] = g
+        g.replay()
+
+    def _stage(self, slots, tokens, positions) -> int:
+        nb = len(slots)
+        if nb > MAX_DECODE_BATCH:
+            raise ValueError(f"decode batch {nb} exceeds {MAX_DECODE_BATCH}")
+        b = self.buf
+        h = b.host_np
+        h[0, :nb] = tokens
+        h[1, :nb] = positions
+        h[2, :nb] = slots
+        b.meta.copy_(b.host_in, non_blocking=True)        # one pinned host -> device copy per step
+        self.h2d_bytes += b.host_in.numel() * 4
+        return nb
+
+    @torch.no_grad()
+    def decode_argmax(self, slots: Sequence[int], tokens: Sequence[int], positions: Sequence[int]) -> list[int]:
+        nb = self._stage(slots, tokens, positions)
+        self._run_step(nb, True)
+        self.buf.host_out.copy_(self.buf.sampled, non_blocking=True)
+        self.d2h_bytes += self.buf.host_out.numel() * 4
+        torch.cuda.current_stream().synchronize()
+        return self.buf.host_out_np[:nb].tolist()
+
+    @torch.no_grad()
+    def decode(self, slots, tokens, positions) -> torch.Tensor:
+        nb = self._stage(slots, tokens, positions)
+        self._run_step(nb, False)
+        return R.softcap(self.buf.logits[:nb].clone(), self.cfg.final_softcap)
+
+    @torch.no_grad()
+    def decode_loop(self, slots: Sequence[int], tokens: Sequence[int], positions: Sequence[int], n_steps: int,
+                    first_tokens: torch.Tensor | None = None) -> torch.Tensor:
+        """Greedy-decode ``n_steps`` tokens for every sequence without leaving the device.
+
+        Returns the sampled ids as an int32 tensor [n_steps, nb] (still on the device).  Used by the
+        benchmark's kernel-only measurement and by speculative prefixes where no stop condition can fire.
+        """
+        nb = self._stage(slots, tokens, positions)
+        if first_tokens is not None:          # ids that are already on the device (e.g. the arg-max of the prefill logits)
+            self.buf.tokens[:nb].copy_(first_tokens.to(torch.int32))
+        out = torch.empty(n_steps, nb, device=self.device, dtype=torch.int32)
+        for i in range(n_steps):
+            self._run_step(nb, "loop")
+            out[i].copy_(self.buf.sampled[:nb])
+        return out
+
+    # -- prefill --------------------------------------------------------------------------------------
+    def _mm(self, x_bf16: torch.Tensor, w: K.DevWeight) -> torch.Tensor:
+        wb = getattr(w, "bf16", None)
+        if wb is None:
+            wb = K.dequant_to_bf16(w)
+        y = (x_bf16 @ wb.t()).float()
+        if w.bias is not None:
+            y = y + w.bias
+        return y
+
+    @torch.no_grad()
+    def _forward_chunk(self, slot: int, tokens: Sequence[int], pos0: int) -> torch.Tensor:
+        """Chunked prefill: returns the final hidden states [T, d_model] (fp32, before the output norm)."""
+        c, dev = self.cfg, self.device
+        T = len(tokens)
+        ids = torch.tensor(list(tokens), device=dev, dtype=torch.int32)
+        pos = torch.arange(pos0, pos0 + T, device=dev, dtype=torch.int32)
+        slots = torch.full((T,), slot, device=dev, dtype=torch.int32)
+        x = K.embed(self.embd, ids, c.embed_scale)
+        p_end = pos0 + T
+        kpos = torch.arange(p_end, device=dev)
+        dp = pos.long()[:, None] - kpos[None, :]
+        base_mask = dp >= 0 if c.causal else torch.ones_like(dp, dtype=torch.bool)
+        swa_mask = base_mask & (dp < c.sliding_window) if c.sliding_window > 0 else base_mask
+        group = c.n_heads // c.n_kv_heads
+        for i, L in enumerate(self.layers):
+            h = R.rmsnorm(x, L.attn_norm, c.norm_eps).to(torch.bfloat16)
+            qkv = torch.cat([self._mm(h, L.wq), self._mm(h, L.wk), self._mm(h, L.wv)], 1).contiguous()
+            local = L.swa and c.rope_base_local > 0
+            q = K.rope_kv(qkv, pos, slots, self.inv_freq_local if local else self.inv_freq, n_heads=c.n_heads, n_kv_heads=c.n_kv_heads,
+                          hd=c.head_dim, n_rot=c.rope_dim, neox=c.rope_style == "neox", mscale=1.0 if local else self.mscale,
+                          k_cache=self.k_cache[i], v_cache=self.v_cache[i], q_norm=L.q_norm, k_norm=L.k_norm, eps=c.norm_eps)
+            kk = self.k_cache[i][slot, :, :p_end]                    # [Hkv, S, hd] f16
+            vv = self.v_cache[i][slot, :, :p_end]
+            qh = q.transpose(0, 1).to(torch.float16)[None]              # [1, H, T, hd]
+            mask = swa_mask if L.swa else base_mask
+            if c.attn_softcap > 0 or L.sinks is not None:
+                o = R.attention(q, kk.transpose(0, 1), vv.transpose(0, 1), pos.long(), kpos, scale=self.attn_scale, causal=c.causal,
+                                window=c.sliding_window if L.swa else 0, softcap=c.attn_softcap, sinks=L.sinks).reshape(T, -1)
+            else:
+                o = torch.nn.functional.scaled_dot_product_attention(qh, kk[None], vv[None], attn_mask=mask, scale=self.attn_scale,
+                                                                     enable_gqa=group > 1)
+                o = o[0].transpose(0, 1).reshape(T, -1).float()
+            o = self._mm(o.to(torch.bfloat16), L.wo)
+            if c.sandwich_norm:
+                o = R.rmsnorm(o, L.post_attn_norm, c.norm_eps)
+            x = x + o
+            h = R.rmsnorm(x, L.ffn_norm, c.norm_eps).to(torch.bfloat16)
+            f = R.glu(self._mm(h, L.gate), self._mm(h, L.up), c.act, c.swiglu_alpha, c.swiglu_limit)
+            f = self._mm(f.to(torch.bfloat16), L.down)
+            if c.sandwich_norm:
+                f = R.rmsnorm(f, L.post_ffw_norm, c.norm_eps)
+            x = x + f
+        return x
+
+    @torch.no_grad()
+    def prefill(self, slot: int, tokens: Sequence[int], pos0: int, need_logits: bool = True):
+        x = self._forward_chunk(slot, tokens, pos0)
+        if not need_logits:
+            return None
+        h = R.rmsnorm(x[-1:], self.out_norm, self.cfg.norm_eps).to(torch.bfloat16)
+        logits = self._mm(h, self.head)[0]
+        return R.softcap(logits, self.cfg.final_softcap)
+
+    @torch.no_grad()
+    def hidden(self, slot: int, tokens: Sequence[int]) -> torch.Tensor:
+        x = self._forward_chunk(slot, tokens, 0)
+        return R.rmsnorm(x, self.out_norm, self.cfg.norm_eps)

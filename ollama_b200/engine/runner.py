@@ -109,11 +109,11 @@ class Runner:
         self.opts = opts or RunnerOptions()
         self.path = model_path
         t0 = time.time()
-        self.gguf = open_model(model_path)
+        self.gguf = open_model(model_path) if model_path else None     # a ready backend may come without a file
         self.backend = backend if backend is not None else make_backend(self.gguf, self.opts.device, opts=self.opts)
         self.cfg = self.backend.cfg
         try:
-            self.tokenizer: Tokenizer | None = tokenizer_from_gguf(self.gguf.kv)
+            self.tokenizer: Tokenizer | None = tokenizer_from_gguf(self.gguf.kv) if self.gguf is not None else None
         except (ValueError, NotImplementedError):
             self.tokenizer = None
         n_ctx = max(4, int(self.opts.num_ctx))
@@ -205,7 +205,8 @@ class Runner:
             self.cv.notify_all()
         self.thread.join(timeout=30)
         self.backend.close()
-        self.gguf.close()
+        if self.gguf is not None:
+            self.gguf.close()
 
     # -- batching loop -------------------------------------------------------------------------------
     def _loop(self) -> None:

@@ -1,0 +1,230 @@
+// Split-K decode attention over the slot-partitioned f16 KV cache, sm_100a.
+//
+// One query token per sequence.  grid = (splits, kv_head * head_groups, sequences).  Every CTA owns
+// a contiguous range of cached positions of one (sequence, kv head) and G query heads that share
+// that kv head (grouped-query attention: K/V are read once for G heads).  Inside a warp, LP = HD/16
+// lanes cooperate on one cached position (each lane holds 16 dims = one 32-byte load of K and one of
+// V), so a warp walks 32/LP positions per step with fully coalesced loads and keeps the running
+// soft-max statistics and the output accumulator in registers.  Lane groups, warps and finally the
+// splits are merged with the usual (max, sum, acc) rescaling; the merge of the splits, the attention
+// sinks, the normalisation and the int8 re-quantisation for the output projection happen in the
+// combine kernel.  Masks: causal by construction (only positions <= the query position are stored),
+// optional sliding window, optional logit soft-cap.
+#include "common.cuh"
+
+struct AttnDecodeArgs {
+    const float* q;          // [nb][H][HD]
+    const __half* k_cache;   // [slots][Hkv][n_ctx][HD]
+    const __half* v_cache;
+    const int* positions;    // [nb] position of the query token (its K/V is already in the cache)
+    const int* slots;        // [nb]
+    int n_heads, n_kv_heads, n_ctx, n_splits;
+    float scale, softcap;
+    int window;              // 0 = full
+    float* part_acc;         // scratch [nb][H][splits][HD]
+    float2* part_ml;         // scratch [nb][H][splits] (max, sum)
+};
+
+template <int HD, int G>
+__global__ void __launch_bounds__(128) attn_decode_kernel(const __grid_constant__ AttnDecodeArgs a) {
+    constexpr int LP = HD / 16;          // lanes per position
+    constexpr int PPW = 32 / LP;         // positions per warp step
+    const int split = blockIdx.x, b = blockIdx.z;
+    const int group = a.n_heads / a.n_kv_heads;
+    const int hg_per_kv = group / G;
+    const int kvh = blockIdx.y / hg_per_kv, hg = blockIdx.y % hg_per_kv;
+    const int head0 = kvh * group + hg * G;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int sub = lane % LP, pg = lane / LP;
+
+    pdl_launch();
+    pdl_wait();
+    const int qpos = a.positions[b], slot = a.slots[b];
+    const int kv_len = qpos + 1;
+    const int start = (a.window > 0 && kv_len > a.window) ? kv_len - a.window : 0;
+    const int span = kv_len - start;
+    int chunk = (span + a.n_splits - 1) / a.n_splits;
+    chunk = ((chunk + PPW * 4 - 1) / (PPW * 4)) * (PPW * 4);
+    const int p0 = start + split * chunk, p1 = min(p0 + chunk, kv_len);
+
+    float q[G][16], acc[G][16], m[G], l[G];
+#pragma unroll
+    for (int g = 0; g < G; g++) {
+        const float* qp = a.q + ((size_t)b * a.n_heads + head0 + g) * HD + sub * 16;
+#pragma unroll
+        for (int i = 0; i < 16; i += 4) {
+            const float4 t = *(const float4*)(qp + i);
+            q[g][i] = t.x * a.scale; q[g][i + 1] = t.y * a.scale; q[g][i + 2] = t.z * a.scale; q[g][i + 3] = t.w * a.scale;
+        }
+#pragma unroll
+        for (int i = 0; i < 16; i++) acc[g][i] = 0.f;
+        m[g] = -1e30f;
+        l[g] = 0.f;
+    }
+    const size_t base = ((size_t)slot * a.n_kv_heads + kvh) * a.n_ctx;
+    // uniform trip count for the whole warp (the shuffles below need every lane); lanes whose position
+    // falls beyond the range load a clamped address and skip the soft-max update
+    for (int pb = p0 + warp * PPW; pb < p1; pb += 4 * PPW) {
+        const int p = pb + pg;
+        const bool valid = p < p1;
+        const int pc = valid ? p : p1 - 1;
+        const __half* kp = a.k_cache + (base + pc) * HD + sub * 16;
+        const __half* vp = a.v_cache + (base + pc) * HD + sub * 16;
+        const uint4 k0 = *(const uint4*)kp, k1 = *(const uint4*)(kp + 8);
+        const uint4 v0 = *(const uint4*)vp, v1 = *(const uint4*)(vp + 8);
+        float kf[16], vf[16];
+        {
+            const __half2* h = reinterpret_cast<const __half2*>(&k0);
+            const __half2* h2 = reinterpret_cast<const __half2*>(&k1);
+            const __half2* w = reinterpret_cast<const __half2*>(&v0);
+            const __half2* w2 = reinterpret_cast<const __half2*>(&v1);
+#pragma unroll
+            for (int i = 0; i < 4; i++) {
+                float2 t = __half22float2(h[i]); kf[2 * i] = t.x; kf[2 * i + 1] = t.y;
+                t = __half22float2(h2[i]); kf[8 + 2 * i] = t.x; kf[8 + 2 * i + 1] = t.y;
+                t = __half22float2(w[i]); vf[2 * i] = t.x; vf[2 * i + 1] = t.y;
+                t = __half22float2(w2[i]); vf[8 + 2 * i] = t.x; vf[8 + 2 * i + 1] = t.y;
+            }
+        }
+#pragma unroll
+        for (int g = 0; g < G; g++) {
+            float s = 0.f;
+#pragma unroll
+            for (int i = 0; i < 16; i++) s += q[g][i] * kf[i];
+#pragma unroll
+            for (int o = 1; o < LP; o <<= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+            if (a.softcap > 0.f) s = a.softcap * tanhf(s / a.softcap);
+            // no divergent control flow here: the next head's shuffles need the whole warp converged
+            const float mn = valid ? fmaxf(m[g], s) : m[g];
+            const float corr = __expf(m[g] - mn), pr = valid ? __expf(s - mn) : 0.f;
+            l[g] = l[g] * corr + pr;
+#pragma unroll
+            for (int i = 0; i < 16; i++) acc[g][i] = acc[g][i] * corr + pr * vf[i];
+            m[g] = mn;
+        }
+    }
+    __syncwarp();
+    // merge the PPW lane groups of the warp
+#pragma unroll
+    for (int o = LP; o < 32; o <<= 1) {
+#pragma unroll
+        for (int g = 0; g < G; g++) {
+            const float mo = __shfl_xor_sync(0xffffffffu, m[g], o), lo = __shfl_xor_sync(0xffffffffu, l[g], o);
+            const float mn = fmaxf(m[g], mo);
+            const float c0 = __expf(m[g] - mn), c1 = __expf(mo - mn);
+            l[g] = l[g] * c0 + lo * c1;
+#pragma unroll
+            for (int i = 0; i < 16; i++) {
+                const float ao = __shfl_xor_sync(0xffffffffu, acc[g][i], o);
+                acc[g][i] = acc[g][i] * c0 + ao * c1;
+            }
+            m[g] = mn;
+        }
+    }
+    // merge the four warps through shared memory
+    __shared__ float s_acc[4][G][HD];
+    __shared__ float s_m[4][G], s_l[4][G];
+    if (pg == 0) {
+#pragma unroll
+        for (int g = 0; g < G; g++) {
+#pragma unroll
+            for (int i = 0; i < 16; i++) s_acc[warp][g][sub * 16 + i] = acc[g][i];
+            if (sub == 0) { s_m[warp][g] = m[g]; s_l[warp][g] = l[g]; }
+        }
+    }
+    __syncthreads();
+    for (int idx = threadIdx.x; idx < G * HD; idx += 128) {
+        const int g = idx / HD, d = idx % HD;
+        float mn = fmaxf(fmaxf(s_m[0][g], s_m[1][g]), fmaxf(s_m[2][g], s_m[3][g]));
+        float o = 0.f, lt = 0.f;
+#pragma unroll
+        for (int w = 0; w < 4; w++) {
+            const float c = __expf(s_m[w][g] - mn);
+            o += s_acc[w][g][d] * c;
+            lt += s_l[w][g] * c;
+        }
+        const size_t pi = ((size_t)b * a.n_heads + head0 + g) * a.n_splits + split;
+        a.part_acc[pi * HD + d] = o;
+        if (d == 0) a.part_ml[pi] = make_float2(mn, lt);
+    }
+}
+
+struct AttnCombineArgs {
+    const float* part_acc;
+    const float2* part_ml;
+    const float* sinks;      // [H] or null
+    int n_heads, n_splits, hd;
+    float* out;              // [nb][H*hd] or null
+    int8_t* out_q;           // [nb][H*hd] or null
+    float2* out_ds;          // [nb][H*hd/32]
+};
+
+// grid = (H, nb), block = hd threads (multiple of 32)
+__global__ void attn_combine_kernel(const __grid_constant__ AttnCombineArgs a) {
+    const int h = blockIdx.x, b = blockIdx.y, d = threadIdx.x;
+    pdl_launch();
+    pdl_wait();
+    const size_t p0 = ((size_t)b * a.n_heads + h) * a.n_splits;
+    float mn = -1e30f;
+    for (int s = 0; s < a.n_splits; s++) mn = fmaxf(mn, a.part_ml[p0 + s].x);
+    if (a.sinks) mn = fmaxf(mn, a.sinks[h]);
+    float o = 0.f, l = 0.f;
+    for (int s = 0; s < a.n_splits; s++) {
+        const float2 ml = a.part_ml[p0 + s];
+        const float c = __expf(ml.x - mn);
+        o += a.part_acc[(p0 + s) * a.hd + d] * c;
+        l += ml.y * c;
+    }
+    if (a.sinks) l += __expf(a.sinks[h] - mn);
+    const float v = l > 0.f ? o / l : 0.f;
+    const size_t oi = ((size_t)b * a.n_heads + h) * a.hd + d;
+    if (a.out) a.out[oi] = v;
+    if (a.out_q) {
+        const float amax = warp_max(fabsf(v));
+        const float dq = amax / 127.f;
+        const int q = dq > 0.f ? __float2int_rn(v / dq) : 0;
+        const float s = dq * warp_sum((float)q);
+        a.out_q[oi] = (int8_t)q;
+        if ((d & 31) == 0) a.out_ds[oi >> 5] = make_float2(dq, s);
+    }
+}
+
+template <int HD>
+static const void* pick_decode(int g) {
+    if (g >= 4) return (const void*)attn_decode_kernel<HD, 4>;
+    if (g >= 2) return (const void*)attn_decode_kernel<HD, 2>;
+    return (const void*)attn_decode_kernel<HD, 1>;
+}
+
+static cudaError_t launch1(const void* fn, dim3 grid, dim3 block, void** args, cudaStream_t st, int pdl) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.stream = st;
+    cudaLaunchAttribute at[1];
+    at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    at[0].val.programmaticStreamSerializationAllowed = pdl ? 1 : 0;
+    cfg.attrs = at;
+    cfg.numAttrs = 1;
+    return cudaLaunchKernelExC(&cfg, fn, args);
+}
+
+// Scratch needed by b2_attn_decode: part_acc = nb*H*splits*hd floats, part_ml = nb*H*splits float2.
+B2_API int b2_attn_decode(const AttnDecodeArgs* a, const AttnCombineArgs* c, int nb, int hd, int pdl, cudaStream_t st) {
+    const int group = a->n_heads / a->n_kv_heads;
+    int G = group >= 4 && group % 4 == 0 ? 4 : (group % 2 == 0 ? 2 : 1);
+    const void* fn = nullptr;
+    if (hd == 64) fn = pick_decode<64>(G);
+    else if (hd == 128) fn = pick_decode<128>(G);
+    else if (hd == 256) fn = pick_decode<256>(G);
+    else if (hd == 32) fn = pick_decode<32>(G);
+    else return (int)cudaErrorInvalidValue;
+    dim3 grid(a->n_splits, a->n_kv_heads * (group / G), nb);
+    AttnDecodeArgs ca = *a;
+    void* args[] = {&ca};
+    cudaError_t e = launch1(fn, grid, dim3(128), args, st, pdl);
+    if (e != cudaSuccess) return (int)e;
+    AttnCombineArgs cc = *c;
+    void* args2[] = {&cc};
+    return (int)launch1((const void*)attn_combine_kernel, dim3(a->n_heads, nb), dim3(hd), args2, st, pdl);
+}

@@ -1,0 +1,345 @@
+// Normalisation, activation quantisation, rotary embedding + KV-cache append, embedding gather,
+// arg-max.  These are the memory-bound glue ops of a decode step; each one is fused with its
+// neighbours where the data flow allows (RMSNorm + int8 block quantisation of the GEMV input;
+// per-head QK-norm + RoPE + f16 conversion + scatter into the slot-partitioned cache).
+#include "common.cuh"
+
+// ---------------------------------------------------------------------------------------------
+// y = rmsnorm(x) * w  ->  fp32 copy (optional) + int8 blocks of 32 with (d, d*sum q)
+// one CTA per token
+// ---------------------------------------------------------------------------------------------
+struct NormQuantArgs {
+    const float* x;      // [nb][k]
+    const float* w;      // [k] or null (no scaling)
+    float eps;
+    int k;
+    int do_norm;         // 0: quantise x as is
+    int8_t* xq;          // [nb][k] or null
+    float2* xds;         // [nb][k/32]
+    float* xf;           // [nb][k] or null
+    float* residual;     // if set: residual[b][i] += y   (post-norm residual add of sandwich-norm models)
+};
+
+__global__ void __launch_bounds__(256) rmsnorm_quant_kernel(const __grid_constant__ NormQuantArgs a) {
+    __shared__ float red[8];
+    const int b = blockIdx.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    pdl_launch();
+    pdl_wait();
+    const float* x = a.x + (size_t)b * a.k;
+    float inv = 1.f;
+    if (a.do_norm) {
+        float ss = 0.f;
+        for (int i = tid * 4; i < a.k; i += 256 * 4) {
+            const float4 v = *(const float4*)(x + i);
+            ss += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
+        }
+        ss = warp_sum(ss);
+        if (lane == 0) red[warp] = ss;
+        __syncthreads();
+        float t = lane < 8 ? red[lane] : 0.f;
+        t = warp_sum(t);
+        inv = rsqrtf(t / (float)a.k + a.eps);
+    }
+    // each warp handles blocks of 32 consecutive elements
+    for (int blk = warp; blk < (a.k >> 5); blk += 8) {
+        const int i = blk * 32 + lane;
+        float v = x[i] * inv;
+        if (a.w) v *= a.w[i];
+        if (a.xf) a.xf[(size_t)b * a.k + i] = v;
+        if (a.residual) a.residual[(size_t)b * a.k + i] += v;
+        if (a.xq) {
+            const float amax = warp_max(fabsf(v));
+            const float d = amax / 127.f;
+            const int q = d > 0.f ? __float2int_rn(v / d) : 0;
+            const float s = d * warp_sum((float)q);
+            a.xq[(size_t)b * a.k + i] = (int8_t)q;
+            if (lane == 0) a.xds[(size_t)b * (a.k >> 5) + blk] = make_float2(d, s);
+        }
+    }
+}
+
+B2_API int b2_rmsnorm_quant(const NormQuantArgs* a, int nb, int pdl, cudaStream_t st) {
+    if (a->k & 31) return (int)cudaErrorInvalidValue;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(nb);
+    cfg.blockDim = dim3(256);
+    cfg.stream = st;
+    cudaLaunchAttribute at[1];
+    at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    at[0].val.programmaticStreamSerializationAllowed = pdl ? 1 : 0;
+    cfg.attrs = at;
+    cfg.numAttrs = 1;
+    NormQuantArgs copy = *a;
+    void* args[] = {&copy};
+    return (int)cudaLaunchKernelExC(&cfg, (const void*)rmsnorm_quant_kernel, args);
+}
+
+// ---------------------------------------------------------------------------------------------
+// QKV post-processing: optional per-head RMSNorm of q and k, RoPE, write q (fp32) and append K/V
+// (f16) to the cache at [slot][kv_head][position][dim].  grid = (tokens, n_heads + 2 n_kv_heads)
+// ---------------------------------------------------------------------------------------------
+struct RopeKvArgs {
+    const float* qkv;        // [nt][(H + 2 Hkv) * hd]  (q | k | v)
+    const int* positions;    // [nt]
+    const int* slots;        // [nt]
+    const float* inv_freq;   // [n_rot/2]
+    const float* q_norm;     // [hd] or null
+    const float* k_norm;     // [hd] or null
+    float eps, mscale;
+    int n_heads, n_kv_heads, hd, n_rot, neox, n_ctx;
+    float* q_out;            // [nt][H][hd]
+    __half* k_cache;         // [slots][Hkv][n_ctx][hd]
+    __half* v_cache;
+};
+
+__global__ void __launch_bounds__(128) rope_kv_kernel(const __grid_constant__ RopeKvArgs a) {
+    const int t = blockIdx.x, head = blockIdx.y, tid = threadIdx.x;
+    const int H = a.n_heads, Hkv = a.n_kv_heads, hd = a.hd;
+    pdl_launch();
+    pdl_wait();
+    const int pos = a.positions[t], slot = a.slots[t];
+    const float* src = a.qkv + (size_t)t * (H + 2 * Hkv) * hd + (size_t)head * hd;
+    const bool is_q = head < H, is_k = !is_q && head < H + Hkv;
+    __shared__ float sh[512];
+    __shared__ float red[4];
+    for (int i = tid; i < hd; i += 128) sh[i] = src[i];
+    __syncthreads();
+    const float* nw = is_q ? a.q_norm : (is_k ? a.k_norm : nullptr);
+    if (nw) {
+        float ss = 0.f;
+        for (int i = tid; i < hd; i += 128) ss += sh[i] * sh[i];
+        ss = warp_sum(ss);
+        if ((tid & 31) == 0) red[tid >> 5] = ss;
+        __syncthreads();
+        const float tot = red[0] + red[1] + red[2] + red[3];
+        const float inv = rsqrtf(tot / (float)hd + a.eps);
+        for (int i = tid; i < hd; i += 128) sh[i] = sh[i] * inv * nw[i];
+        __syncthreads();
+    }
+    if (is_q || is_k) {
+        const int half_rot = a.n_rot >> 1;
+        for (int p = tid; p < half_rot; p += 128) {
+            const int i0 = a.neox ? p : 2 * p, i1 = a.neox ? p + half_rot : 2 * p + 1;
+            float sn, cs;
+            sincosf((float)pos * a.inv_freq[p], &sn, &cs);
+            sn *= a.mscale; cs *= a.mscale;
+            const float x0 = sh[i0], x1 = sh[i1];
+            sh[i0] = x0 * cs - x1 * sn;
+            sh[i1] = x0 * sn + x1 * cs;
+        }
+        __syncthreads();
+    }
+    if (is_q) {
+        float* dst = a.q_out + ((size_t)t * H + head) * hd;
+        for (int i = tid; i < hd; i += 128) dst[i] = sh[i];
+    } else {
+        const int kvh = is_k ? head - H : head - H - Hkv;
+        __half* dst = (is_k ? a.k_cache : a.v_cache) + (((size_t)slot * Hkv + kvh) * a.n_ctx + pos) * hd;
+        for (int i = tid; i < hd; i += 128) dst[i] = __float2half_rn(sh[i]);
+    }
+}
+
+B2_API int b2_rope_kv(const RopeKvArgs* a, int nt, int pdl, cudaStream_t st) {
+    if (a->hd > 512) return (int)cudaErrorInvalidValue;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(nt, a->n_heads + 2 * a->n_kv_heads);
+    cfg.blockDim = dim3(128);
+    cfg.stream = st;
+    cudaLaunchAttribute at[1];
+    at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    at[0].val.programmaticStreamSerializationAllowed = pdl ? 1 : 0;
+    cfg.attrs = at;
+    cfg.numAttrs = 1;
+    RopeKvArgs copy = *a;
+    void* args[] = {&copy};
+    return (int)cudaLaunchKernelExC(&cfg, (const void*)rope_kv_kernel, args);
+}
+
+// ---------------------------------------------------------------------------------------------
+// Embedding gather from a (possibly quantised) table: out[t][:] = scale * dequant(table[ids[t]][:])
+// ---------------------------------------------------------------------------------------------
+__device__ __forceinline__ float deq_elem(const WDesc& w, int row, int i) {
+    const int K = w.k;
+    switch (w.type) {
+        case WT_F32: return ((const float*)w.p0)[(size_t)row * K + i];
+        case WT_F16: return __half2float(((const __half*)w.p0)[(size_t)row * K + i]);
+        case WT_BF16: return __bfloat162float(((const __nv_bfloat16*)w.p0)[(size_t)row * K + i]);
+        case WT_Q8_0: {
+            const int8_t q = ((const int8_t*)w.p0)[(size_t)row * K + i];
+            return (float)q * __half2float(((const __half*)w.p1)[(size_t)row * (K >> 5) + (i >> 5)]);
+        }
+        case WT_Q4_0: {
+            const int blk = i >> 5, l = i & 31;
+            const uint8_t q = ((const uint8_t*)w.p0)[(size_t)row * (K >> 1) + blk * 16 + (l & 15)];
+            const int v = (l < 16 ? (q & 15) : (q >> 4)) - 8;
+            return (float)v * __half2float(((const __half*)w.p1)[(size_t)row * (K >> 5) + blk]);
+        }
+        case WT_MXFP4: {
+            const int blk = i >> 5, l = i & 31;
+            const uint8_t q = ((const uint8_t*)w.p0)[(size_t)row * (K >> 1) + blk * 16 + (l & 15)];
+            const int code = l < 16 ? (q & 15) : (q >> 4);
+            const float mags[8] = {0.f, 0.5f, 1.f, 1.5f, 2.f, 3.f, 4.f, 6.f};
+            const float v = (code & 8) ? -mags[code & 7] : mags[code & 7];
+            return v * e8m0_to_float(((const uint8_t*)w.p1)[(size_t)row * (K >> 5) + blk]);
+        }
+        case WT_Q4_K:
+        case WT_Q5_K: {
+            const int sb = i >> 8, r = i & 255, j = r >> 6, hi = (r >> 5) & 1, l = r & 31;
+            const uint4 hd = ((const uint4*)w.p1)[(size_t)row * (K >> 8) + sb];
+            const __half2 dm = *reinterpret_cast<const __half2*>(&hd.x);
+            const uint8_t* sc = reinterpret_cast<const uint8_t*>(&hd.y);
+            const int is = 2 * j + hi;
+            int s, m;
+            if (is < 4) { s = sc[is] & 63; m = sc[is + 4] & 63; }
+            else { s = (sc[is + 4] & 0xF) | ((sc[is - 4] >> 6) << 4); m = (sc[is + 4] >> 4) | ((sc[is] >> 6) << 4); }
+            const uint8_t qb = ((const uint8_t*)w.p0)[(size_t)row * (K >> 1) + sb * 128 + j * 32 + l];
+            int q = hi ? (qb >> 4) : (qb & 15);
+            if (w.type == WT_Q5_K) {
+                const uint8_t h = ((const uint8_t*)w.p2)[(size_t)row * (K >> 3) + sb * 32 + l];
+                q |= ((h >> is) & 1) << 4;
+            }
+            return __low2float(dm) * (float)s * (float)q - __high2float(dm) * (float)m;
+        }
+        case WT_Q6_K: {
+            const int sb = i >> 8, r = i & 255, n = r >> 7, qd = (r >> 5) & 3, l = r & 31;
+            const uint8_t qlb = ((const uint8_t*)w.p0)[(size_t)row * (K >> 1) + sb * 128 + n * 64 + (qd & 1) * 32 + l];
+            const uint8_t qhb = ((const uint8_t*)w.p1)[(size_t)row * (K >> 2) + sb * 64 + n * 32 + l];
+            const int q = ((qd < 2 ? (qlb & 15) : (qlb >> 4)) | (((qhb >> (2 * qd)) & 3) << 4)) - 32;
+            const int8_t s = ((const int8_t*)w.p2)[(size_t)row * (K >> 4) + sb * 16 + n * 8 + (l >> 4) + 2 * qd];
+            return __half2float(((const __half*)w.p3)[(size_t)row * (K >> 8) + sb]) * (float)s * (float)q;
+        }
+    }
+    return 0.f;
+}
+
+struct EmbedArgs {
+    WDesc table;
+    const int* ids;      // [nt]
+    float scale;
+    float* out;          // [nt][k]
+};
+
+__global__ void __launch_bounds__(256) embed_kernel(const __grid_constant__ EmbedArgs a) {
+    pdl_launch();
+    pdl_wait();
+    const int t = blockIdx.x;
+    int row = a.ids[t];
+    row = min(max(row, 0), a.table.n - 1);
+    for (int i = threadIdx.x; i < a.table.k; i += 256) a.out[(size_t)t * a.table.k + i] = a.scale * deq_elem(a.table, row, i);
+}
+
+B2_API int b2_embed(const EmbedArgs* a, int nt, cudaStream_t st) {
+    EmbedArgs copy = *a;
+    embed_kernel<<<nt, 256, 0, st>>>(copy);
+    return (int)cudaGetLastError();
+}
+
+// Dequantise rows [row0, row0+nrows) of a weight into bf16 (used to stage operands for the
+// tensor-core GEMM and by the tests that check the plane layouts).
+struct DequantArgs {
+    WDesc w;
+    int row0, nrows;
+    __nv_bfloat16* out;   // [nrows][k]
+};
+
+__global__ void __launch_bounds__(256) dequant_rows_kernel(const __grid_constant__ DequantArgs a) {
+    const int r = blockIdx.x;
+    if (r >= a.nrows) return;
+    for (int i = threadIdx.x; i < a.w.k; i += 256)
+        a.out[(size_t)r * a.w.k + i] = __float2bfloat16(deq_elem(a.w, a.row0 + r, i));
+}
+
+B2_API int b2_dequant_rows(const DequantArgs* a, cudaStream_t st) {
+    DequantArgs copy = *a;
+    dequant_rows_kernel<<<a->nrows, 256, 0, st>>>(copy);
+    return (int)cudaGetLastError();
+}
+
+// ---------------------------------------------------------------------------------------------
+// arg-max over the vocabulary, one CTA per row; optional soft-cap is monotonic so it is skipped
+// ---------------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(1024) argmax_kernel(const float* logits, int n, int ld, int* out) {
+    pdl_launch();
+    pdl_wait();
+    const float* x = logits + (size_t)blockIdx.x * ld;
+    float best = -INFINITY;
+    int bi = 0x7fffffff;
+    for (int i = threadIdx.x; i < n; i += 1024) {
+        const float v = x[i];
+        if (v > best) { best = v; bi = i; }
+    }
+    __shared__ float sv[32];
+    __shared__ int si[32];
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+        const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+        if (ov > best || (ov == best && oi < bi)) { best = ov; bi = oi; }
+    }
+    if ((threadIdx.x & 31) == 0) { sv[threadIdx.x >> 5] = best; si[threadIdx.x >> 5] = bi; }
+    __syncthreads();
+    if (threadIdx.x < 32) {
+        best = sv[threadIdx.x]; bi = si[threadIdx.x];
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+            const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+            if (ov > best || (ov == best && oi < bi)) { best = ov; bi = oi; }
+        }
+        if (threadIdx.x == 0) out[blockIdx.x] = bi;
+    }
+}
+
+B2_API int b2_argmax(const float* logits, int rows, int n, int ld, int* out, cudaStream_t st) {
+    argmax_kernel<<<rows, 1024, 0, st>>>(logits, n, ld, out);
+    return (int)cudaGetLastError();
+}
+
+// Decode-step bookkeeping kept on the device so that a captured step can be replayed:
+// tokens[b] = sampled[b]; positions[b] += 1
+__global__ void advance_kernel(int* tokens, int* positions, const int* sampled, int nb) {
+    const int b = threadIdx.x;
+    if (b < nb) { tokens[b] = sampled[b]; positions[b] += 1; }
+}
+
+B2_API int b2_advance(int* tokens, int* positions, const int* sampled, int nb, cudaStream_t st) {
+    advance_kernel<<<1, 32, 0, st>>>(tokens, positions, sampled, nb);
+    return (int)cudaGetLastError();
+}
+
+// fp32 -> bf16 with optional row-wise RMSNorm (prefill activations feeding the tensor-core GEMM)
+struct NormCastArgs {
+    const float* x;
+    const float* w;
+    float eps;
+    int k, do_norm;
+    __nv_bfloat16* out;
+};
+
+__global__ void __launch_bounds__(256) rmsnorm_bf16_kernel(const __grid_constant__ NormCastArgs a) {
+    __shared__ float red[8];
+    const int b = blockIdx.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const float* x = a.x + (size_t)b * a.k;
+    float inv = 1.f;
+    if (a.do_norm) {
+        float ss = 0.f;
+        for (int i = tid; i < a.k; i += 256) ss += x[i] * x[i];
+        ss = warp_sum(ss);
+        if (lane == 0) red[warp] = ss;
+        __syncthreads();
+        float t = lane < 8 ? red[lane] : 0.f;
+        t = warp_sum(t);
+        inv = rsqrtf(t / (float)a.k + a.eps);
+    }
+    for (int i = tid; i < a.k; i += 256) {
+        float v = x[i] * inv;
+        if (a.w) v *= a.w[i];
+        a.out[(size_t)b * a.k + i] = __float2bfloat16(v);
+    }
+}
+
+B2_API int b2_rmsnorm_bf16(const NormCastArgs* a, int rows, cudaStream_t st) {
+    NormCastArgs copy = *a;
+    rmsnorm_bf16_kernel<<<rows, 256, 0, st>>>(copy);
+    return (int)cudaGetLastError();
+}

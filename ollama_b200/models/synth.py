@@ -224,3 +224,49 @@ def write_synthetic_gguf(path: str, spec_name: str, file_type: str | int = "F32"
     for name, shape, t, raw in iter_tensors(spec, ft, seed, device):
         tensors.append(WriteTensor(name, tuple(reversed(shape)), t, raw.cpu().numpy()))
     write_gguf(path, kv, tensors)
+
+
+class SyntheticTensors:
+    """Mapping-like source of :class:`QWeight` that draws and encodes each tensor when it is asked for.
+
+    ``rows`` optionally restricts a tensor to a row range (tensor-parallel shards are generated
+    directly, the full matrix is never materialised on one device).
+    """
+
+    def __init__(self, spec_name: str, file_type: str | int = "Q4_K_M", seed: int = 0, device="cpu"):
+        from .weights import QWeight
+        self._QWeight = QWeight
+        self.spec = SPECS[spec_name]
+        self.ft = file_type if isinstance(file_type, int) else int(getattr(FileType, file_type if file_type != "MXFP4" else "MXFP4_MOE"))
+        self.seed, self.device = seed, device
+        self.table = {n: (shape, layer) for n, shape, layer in tensor_table(self.spec)}
+
+    def __contains__(self, name: str) -> bool:
+        return name in self.table
+
+    def keys(self):
+        return self.table.keys()
+
+    def type_of(self, name: str) -> GGMLType:
+        shape, layer = self.table[name]
+        return tensor_type(name, shape, self.ft, max(layer, 0), self.spec.n_layers, self.spec)
+
+    def __getitem__(self, name: str):
+        shape, layer = self.table[name]
+        t = self.type_of(name)
+        x = random_tensor(name, shape, self.seed, self.device)
+        return self._QWeight(name, t, tuple(shape), quants.quantize(x, t))
+
+
+def synthetic_header(spec_name: str, file_type: str | int = "Q4_K_M", with_tokenizer: bool = False):
+    """A data-less :class:`GGUFFile` carrying the metadata of a synthetic checkpoint (for config parsing)."""
+    from ..gguf.reader import GGUFFile, TensorInfo
+    spec = SPECS[spec_name]
+    ft = file_type if isinstance(file_type, int) else int(getattr(FileType, file_type if file_type != "MXFP4" else "MXFP4_MOE"))
+    raw = metadata(spec, ft, spec_name, with_tokenizer=with_tokenizer)
+    kv = {}
+    for k, v in raw.items():
+        kv[k if k.startswith(("general.", "tokenizer.")) else f"{spec.arch}.{k}"] = v
+    tensors = {n: TensorInfo(n, tuple(reversed(shape)), tensor_type(n, shape, ft, max(layer, 0), spec.n_layers, spec), 0, 0)
+               for n, shape, layer in tensor_table(spec)}
+    return GGUFFile("", 3, "<", kv, {}, tensors, 0, 32)

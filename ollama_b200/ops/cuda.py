@@ -1,0 +1,316 @@
+"""ctypes bindings of the sm_100a kernel library and the load-time weight re-layout.
+
+The library (``ollama_b200/kernels/libb200ops.so``) exports plain C entry points that take raw
+device pointers and a stream; tensors stay owned by torch.  If a CUDA device is present and the
+library cannot be loaded this module raises: there is no silent fallback on a GPU box.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import os
+from dataclasses import dataclass, field
+
+import torch
+
+from ..gguf import quants
+from ..gguf.types import GGMLType
+from ..models.weights import QWeight
+
+_LIB_PATH = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "kernels", "libb200ops.so")
+_lib = None
+
+WT_F32, WT_F16, WT_BF16, WT_Q8_0, WT_Q4_K, WT_Q6_K, WT_Q5_K, WT_MXFP4, WT_Q4_0 = range(9)
+QUANT_INPUT_TYPES = {WT_Q8_0, WT_Q4_K, WT_Q6_K, WT_Q5_K, WT_MXFP4, WT_Q4_0}   # weights that consume int8 activations
+
+
+class CudaKernelError(RuntimeError):
+    pass
+
+
+def lib():
+    global _lib
+    if _lib is None:
+        if not os.path.exists(_LIB_PATH):
+            from ..kernels.build import build
+            build()
+        _lib = C.CDLL(_LIB_PATH)
+    return _lib
+
+
+def available() -> bool:
+    return torch.cuda.is_available()
+
+
+def _check(rc: int, what: str) -> None:
+    if rc != 0:
+        raise CudaKernelError(f"{what} failed with CUDA error {rc}")
+
+
+def stream() -> C.c_void_p:
+    return C.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+def ptr(t: torch.Tensor | None) -> int | None:
+    return None if t is None else t.data_ptr()
+
+
+class WDesc(C.Structure):
+    _fields_ = [("p0", C.c_void_p), ("p1", C.c_void_p), ("p2", C.c_void_p), ("p3", C.c_void_p), ("bias", C.c_void_p),
+                ("type", C.c_int), ("n", C.c_int), ("k", C.c_int), ("out_off", C.c_int)]
+
+
+class GemvArgs(C.Structure):
+    _fields_ = [("seg", WDesc * 4), ("nseg", C.c_int), ("nb", C.c_int), ("xq", C.c_void_p), ("xds", C.c_void_p),
+                ("xf", C.c_void_p), ("out", C.c_void_p), ("ldo", C.c_int), ("accumulate", C.c_int)]
+
+
+class GluArgs(C.Structure):
+    _fields_ = [("gate", WDesc), ("up", WDesc), ("nb", C.c_int), ("xq", C.c_void_p), ("xds", C.c_void_p), ("xf", C.c_void_p),
+                ("act", C.c_int), ("alpha", C.c_float), ("limit", C.c_float), ("hq", C.c_void_p), ("hds", C.c_void_p),
+                ("hf", C.c_void_p)]
+
+
+class NormQuantArgs(C.Structure):
+    _fields_ = [("x", C.c_void_p), ("w", C.c_void_p), ("eps", C.c_float), ("k", C.c_int), ("do_norm", C.c_int),
+                ("xq", C.c_void_p), ("xds", C.c_void_p), ("xf", C.c_void_p), ("residual", C.c_void_p)]
+
+
+class RopeKvArgs(C.Structure):
+    _fields_ = [("qkv", C.c_void_p), ("positions", C.c_void_p), ("slots", C.c_void_p), ("inv_freq", C.c_void_p),
+                ("q_norm", C.c_void_p), ("k_norm", C.c_void_p), ("eps", C.c_float), ("mscale", C.c_float),
+                ("n_heads", C.c_int), ("n_kv_heads", C.c_int), ("hd", C.c_int), ("n_rot", C.c_int), ("neox", C.c_int),
+                ("n_ctx", C.c_int), ("q_out", C.c_void_p), ("k_cache", C.c_void_p), ("v_cache", C.c_void_p)]
+
+
+class EmbedArgs(C.Structure):
+    _fields_ = [("table", WDesc), ("ids", C.c_void_p), ("scale", C.c_float), ("out", C.c_void_p)]
+
+
+class DequantArgs(C.Structure):
+    _fields_ = [("w", WDesc), ("row0", C.c_int), ("nrows", C.c_int), ("out", C.c_void_p)]
+
+
+class NormCastArgs(C.Structure):
+    _fields_ = [("x", C.c_void_p), ("w", C.c_void_p), ("eps", C.c_float), ("k", C.c_int), ("do_norm", C.c_int), ("out", C.c_void_p)]
+
+
+class AttnDecodeArgs(C.Structure):
+    _fields_ = [("q", C.c_void_p), ("k_cache", C.c_void_p), ("v_cache", C.c_void_p), ("positions", C.c_void_p),
+                ("slots", C.c_void_p), ("n_heads", C.c_int), ("n_kv_heads", C.c_int), ("n_ctx", C.c_int), ("n_splits", C.c_int),
+                ("scale", C.c_float), ("softcap", C.c_float), ("window", C.c_int), ("part_acc", C.c_void_p), ("part_ml", C.c_void_p)]
+
+
+class AttnCombineArgs(C.Structure):
+    _fields_ = [("part_acc", C.c_void_p), ("part_ml", C.c_void_p), ("sinks", C.c_void_p), ("n_heads", C.c_int),
+                ("n_splits", C.c_int), ("hd", C.c_int), ("out", C.c_void_p), ("out_q", C.c_void_p), ("out_ds", C.c_void_p)]
+
+
+# ---------------------------------------------------------------------------------------------------
+# device weights
+# ---------------------------------------------------------------------------------------------------
+@dataclass
+class DevWeight:
+    """A weight matrix [n, k] re-laid out into the planes the kernels read (see kernels/common.cuh)."""
+
+    wtype: int
+    n: int
+    k: int
+    planes: list[torch.Tensor]
+    bias: torch.Tensor | None = None
+    name: str = ""
+    experts: int = 0          # > 0: planes hold `experts` stacked [n, k] matrices
+
+    def desc(self, out_off: int = 0, row0: int = 0, rows: int | None = None) -> WDesc:
+        """Descriptor of rows [row0, row0+rows) (used for expert slices of stacked tensors)."""
+        d = WDesc()
+        ps = [0, 0, 0, 0]
+        for i, p in enumerate(self.planes):
+            ps[i] = p.data_ptr() + row0 * (p.numel() * p.element_size() // self.total_rows)
+        d.p0, d.p1, d.p2, d.p3 = ps
+        d.bias = (self.bias.data_ptr() + row0 * 4) if self.bias is not None else None
+        d.type, d.n, d.k, d.out_off = self.wtype, (rows if rows is not None else self.n), self.k, out_off
+        return d
+
+    @property
+    def total_rows(self) -> int:
+        return self.n * max(self.experts, 1)
+
+    @property
+    def nbytes(self) -> int:
+        return sum(p.numel() * p.element_size() for p in self.planes) + (self.bias.numel() * 4 if self.bias is not None else 0)
+
+    @property
+    def quant_input(self) -> bool:
+        return self.wtype in QUANT_INPUT_TYPES
+
+
+def repack(w: QWeight, device, bias: torch.Tensor | None = None) -> DevWeight:
+    """GGUF block layout -> dense planes on ``device``.  Encodings without a native kernel become f16."""
+    shape = w.shape
+    experts = 0
+    if len(shape) == 3:
+        experts, n, k = shape
+    elif len(shape) == 2:
+        n, k = shape
+    else:
+        raise ValueError(f"{w.name}: expected a matrix, got shape {shape}")
+    rows = n * max(experts, 1)
+    raw = w.raw.to(device)
+    t = w.dtype
+    b = bias.to(device=device, dtype=torch.float32).contiguous() if bias is not None else None
+
+    def mk(wt, planes):
+        return DevWeight(wt, n, k, [p.contiguous() for p in planes], b, w.name, experts)
+
+    if t == GGMLType.F32:
+        return mk(WT_F32, [raw.view(torch.float32).view(rows, k)])
+    if t == GGMLType.F16:
+        return mk(WT_F16, [raw.view(torch.float16).view(rows, k)])
+    if t == GGMLType.BF16:
+        return mk(WT_BF16, [raw.view(torch.bfloat16).view(rows, k)])
+    if t == GGMLType.Q8_0 and k % 32 == 0:
+        blk = raw.view(rows, k // 32, 34)
+        return mk(WT_Q8_0, [blk[:, :, 2:].reshape(rows, k).view(torch.int8), blk[:, :, :2].reshape(rows, k // 32 * 2).view(torch.float16)])
+    if t == GGMLType.Q4_0 and k % 32 == 0:
+        blk = raw.view(rows, k // 32, 18)
+        return mk(WT_Q4_0, [blk[:, :, 2:].reshape(rows, k // 2), blk[:, :, :2].reshape(rows, k // 32 * 2).view(torch.float16)])
+    if t == GGMLType.MXFP4 and k % 32 == 0:
+        blk = raw.view(rows, k // 32, 17)
+        return mk(WT_MXFP4, [blk[:, :, 1:].reshape(rows, k // 2), blk[:, :, 0].reshape(rows, k // 32)])
+    if t == GGMLType.Q4_K:
+        blk = raw.view(rows, k // 256, 144)
+        return mk(WT_Q4_K, [blk[:, :, 16:].reshape(rows, k // 2), blk[:, :, :16].reshape(rows, k // 256 * 16)])
+    if t == GGMLType.Q5_K:
+        blk = raw.view(rows, k // 256, 176)
+        return mk(WT_Q5_K, [blk[:, :, 48:].reshape(rows, k // 2), blk[:, :, :16].reshape(rows, k // 256 * 16),
+                            blk[:, :, 16:48].reshape(rows, k // 8)])
+    if t == GGMLType.Q6_K:
+        blk = raw.view(rows, k // 256, 210)
+        return mk(WT_Q6_K, [blk[:, :, :128].reshape(rows, k // 2), blk[:, :, 128:192].reshape(rows, k // 4),
+                            blk[:, :, 192:208].reshape(rows, k // 16).view(torch.int8),
+                            blk[:, :, 208:210].reshape(rows, k // 256 * 2).view(torch.float16)])
+    # anything else (Q2_K, Q3_K, Q4_1, Q5_0, Q5_1, IQ4_NL ...) is expanded once at load time
+    deq = quants.dequantize(raw, t, rows * k).view(rows, k).to(torch.float16)
+    return mk(WT_F16, [deq])
+
+
+def dequant_to_bf16(w: DevWeight, row0: int = 0, nrows: int | None = None) -> torch.Tensor:
+    nrows = w.total_rows - row0 if nrows is None else nrows
+    out = torch.empty(nrows, w.k, device=w.planes[0].device, dtype=torch.bfloat16)
+    a = DequantArgs()
+    a.w = w.desc(rows=w.total_rows)
+    a.row0, a.nrows, a.out = row0, nrows, out.data_ptr()
+    _check(lib().b2_dequant_rows(C.byref(a), stream()), "dequant_rows")
+    return out
+
+
+# ---------------------------------------------------------------------------------------------------
+# op wrappers (thin; the engine drives the same entry points with pre-built argument structs)
+# ---------------------------------------------------------------------------------------------------
+@dataclass
+class QAct:
+    """Activations quantised to int8 blocks of 32 (+ the fp32 copy for float-weight consumers)."""
+
+    q: torch.Tensor            # int8 [nb, k]
+    ds: torch.Tensor           # float32 [nb, k/32, 2]
+    f: torch.Tensor | None     # float32 [nb, k]
+
+
+def rmsnorm_quant(x: torch.Tensor, w: torch.Tensor | None, eps: float, do_norm: bool = True, want_f: bool = True,
+                  residual: torch.Tensor | None = None, pdl: bool = False) -> QAct:
+    nb, k = x.shape
+    q = torch.empty(nb, k, device=x.device, dtype=torch.int8)
+    ds = torch.empty(nb, k // 32, 2, device=x.device, dtype=torch.float32)
+    f = torch.empty(nb, k, device=x.device, dtype=torch.float32) if want_f else None
+    a = NormQuantArgs(ptr(x), ptr(w), eps, k, int(do_norm), ptr(q), ptr(ds), ptr(f), ptr(residual))
+    _check(lib().b2_rmsnorm_quant(C.byref(a), nb, int(pdl), stream()), "rmsnorm_quant")
+    return QAct(q, ds, f)
+
+
+def gemv(weights: list[DevWeight], x: QAct, out: torch.Tensor | None = None, accumulate: bool = False, pdl: bool = False) -> torch.Tensor:
+    """y[b] = concat_i(W_i x[b] + bias_i) for up to four weights sharing the input (1..8 tokens)."""
+    nb = x.q.shape[0]
+    total = sum(w.n for w in weights)
+    if out is None:
+        out = torch.empty(nb, total, device=x.q.device, dtype=torch.float32)
+    a = GemvArgs()
+    off = 0
+    for i, w in enumerate(weights):
+        a.seg[i] = w.desc(out_off=off)
+        off += w.n
+    a.nseg, a.nb = len(weights), nb
+    a.xq, a.xds, a.xf = ptr(x.q), ptr(x.ds), ptr(x.f)
+    a.out, a.ldo, a.accumulate = ptr(out), out.stride(0), int(accumulate)
+    _check(lib().b2_gemv(C.byref(a), int(pdl), stream()), "gemv")
+    return out
+
+
+_ACT = {"silu": 0, "gelu_tanh": 1, "swiglu_oai": 2}
+
+
+def gemv_glu_quant(gate: DevWeight, up: DevWeight, x: QAct, act: str, alpha: float = 1.702, limit: float = 7.0,
+                   want_f: bool = False, pdl: bool = False) -> QAct:
+    nb = x.q.shape[0]
+    n = gate.n
+    hq = torch.empty(nb, n, device=x.q.device, dtype=torch.int8)
+    hds = torch.empty(nb, n // 32, 2, device=x.q.device, dtype=torch.float32)
+    hf = torch.empty(nb, n, device=x.q.device, dtype=torch.float32) if want_f else None
+    a = GluArgs()
+    a.gate, a.up = gate.desc(), up.desc()
+    a.nb, a.xq, a.xds, a.xf = nb, ptr(x.q), ptr(x.ds), ptr(x.f)
+    a.act, a.alpha, a.limit = _ACT[act], alpha, limit
+    a.hq, a.hds, a.hf = ptr(hq), ptr(hds), ptr(hf)
+    _check(lib().b2_gemv_glu_quant(C.byref(a), int(pdl), stream()), "gemv_glu_quant")
+    return QAct(hq, hds, hf)
+
+
+def embed(table: DevWeight, ids: torch.Tensor, scale: float = 1.0, out: torch.Tensor | None = None) -> torch.Tensor:
+    nt = ids.numel()
+    if out is None:
+        out = torch.empty(nt, table.k, device=ids.device, dtype=torch.float32)
+    a = EmbedArgs()
+    a.table, a.ids, a.scale, a.out = table.desc(), ptr(ids), scale, ptr(out)
+    _check(lib().b2_embed(C.byref(a), nt, stream()), "embed")
+    return out
+
+
+def argmax(logits: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
+    rows, n = logits.shape
+    if out is None:
+        out = torch.empty(rows, device=logits.device, dtype=torch.int32)
+    lib().b2_argmax.argtypes = [C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_void_p, C.c_void_p]
+    _check(lib().b2_argmax(ptr(logits), rows, n, logits.stride(0), ptr(out), stream()), "argmax")
+    return out
+
+
+def rope_kv(qkv: torch.Tensor, positions: torch.Tensor, slots: torch.Tensor, inv_freq: torch.Tensor, *, n_heads: int,
+            n_kv_heads: int, hd: int, n_rot: int, neox: bool, mscale: float, k_cache: torch.Tensor, v_cache: torch.Tensor,
+            q_norm: torch.Tensor | None = None, k_norm: torch.Tensor | None = None, eps: float = 1e-6,
+            q_out: torch.Tensor | None = None, pdl: bool = False) -> torch.Tensor:
+    nt = qkv.shape[0]
+    if q_out is None:
+        q_out = torch.empty(nt, n_heads, hd, device=qkv.device, dtype=torch.float32)
+    a = RopeKvArgs(ptr(qkv), ptr(positions), ptr(slots), ptr(inv_freq), ptr(q_norm), ptr(k_norm), eps, mscale, n_heads,
+                   n_kv_heads, hd, n_rot, int(neox), k_cache.shape[2], ptr(q_out), ptr(k_cache), ptr(v_cache))
+    _check(lib().b2_rope_kv(C.byref(a), nt, int(pdl), stream()), "rope_kv")
+    return q_out
+
+
+def attn_decode(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, positions: torch.Tensor, slots: torch.Tensor, *,
+                scale: float, n_splits: int, window: int = 0, softcap: float = 0.0, sinks: torch.Tensor | None = None,
+                scratch: tuple[torch.Tensor, torch.Tensor] | None = None, quant_out: bool = True, pdl: bool = False):
+    """q: [nb, H, hd] fp32; caches [slots, Hkv, n_ctx, hd] f16.  Returns (out fp32 [nb, H*hd], QAct or None)."""
+    nb, H, hd = q.shape
+    Hkv, n_ctx = k_cache.shape[1], k_cache.shape[2]
+    dev = q.device
+    if scratch is None:
+        scratch = (torch.empty(nb * H * n_splits * hd, device=dev, dtype=torch.float32),
+                   torch.empty(nb * H * n_splits * 2, device=dev, dtype=torch.float32))
+    out = torch.empty(nb, H * hd, device=dev, dtype=torch.float32)
+    oq = torch.empty(nb, H * hd, device=dev, dtype=torch.int8) if quant_out else None
+    ods = torch.empty(nb, H * hd // 32, 2, device=dev, dtype=torch.float32) if quant_out else None
+    a = AttnDecodeArgs(ptr(q), ptr(k_cache), ptr(v_cache), ptr(positions), ptr(slots), H, Hkv, n_ctx, n_splits, scale, softcap,
+                       window, ptr(scratch[0]), ptr(scratch[1]))
+    c = AttnCombineArgs(ptr(scratch[0]), ptr(scratch[1]), ptr(sinks), H, n_splits, hd, ptr(out), ptr(oq), ptr(ods))
+    _check(lib().b2_attn_decode(C.byref(a), C.byref(c), nb, hd, int(pdl), stream()), "attn_decode")
+    return out, (QAct(oq, ods, out) if quant_out else None)
