@@ -102,6 +102,7 @@ def main() -> None:
     ap.add_argument("--no-graphs", action="store_true")
     ap.add_argument("--no-pdl", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--layers", type=int, default=0, help="truncate the model to this many layers (profiling only; not a benchmark number)")
     args = ap.parse_args()
     if args.impl == "reference":
         reference_arm(args)
@@ -134,6 +135,10 @@ def main() -> None:
     from ollama_b200.models.synth import SyntheticTensors, synthetic_header
 
     dev = f"cuda:{local}"
+    if args.layers:      # profiling aid: a truncated stack keeps ncu captures short; the result is flagged below
+        import dataclasses
+        from ollama_b200.models import synth
+        synth.SPECS[model] = dataclasses.replace(synth.SPECS[model], n_layers=args.layers)
     hdr = synthetic_header(model, wl["ft"])
     cfg = config_from_gguf(hdr)
     t_load = time.time()
@@ -249,7 +254,8 @@ def main() -> None:
                        "generated_tokens": G, "num_ctx": wl["ctx"], "slots": slots,
                        "parallelism": "single" if n_gpus == 1 else f"tp{n_gpus}",
                        "l2": "inputs larger than L2 (weights of several GB are re-read every token)",
-                       "weights": "random-init N(0,0.02), seed 0", "graphs": be.use_graphs, "pdl": be.pdl},
+                       "weights": "random-init N(0,0.02), seed 0", "graphs": be.use_graphs, "pdl": be.pdl,
+                       **({"layers_override": args.layers, "invalid_as_benchmark": True} if args.layers else {})},
             "clocks": clocks, "e2e": e2e, "gpu_launches": int(launches), "load_s": round(t_load, 1), "impl": "ours",
         }
         print(json.dumps(out))

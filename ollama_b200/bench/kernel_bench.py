@@ -1,0 +1,119 @@
+"""Per-kernel timing of the decode hot ops on Llama-8B/70B-shaped operands.
+
+    python -m ollama_b200.bench.kernel_bench [--nb 1,4,8] [--only glu] [--reps 20]
+
+Every case is timed with CUDA events on the launching stream after warm-up.  Each timed launch
+reads a different copy of the weights (the copies add up to more than the 126 MB L2), so the bytes
+really come from HBM.  Reported: microseconds, achieved GB/s over the algorithmic weight bytes and
+the fraction of the measured copy bandwidth in MEASURED_PEAKS.json (fallback 6650 GB/s).
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+
+import torch
+
+from ..gguf.types import GGMLType
+from ..models.weights import QWeight
+from ..ops import cuda as K
+
+CASES = [
+    # name, kind, [(rows, type)], k
+    ("qkv-8b", "gemv", [(4096, GGMLType.Q4_K), (1024, GGMLType.Q4_K), (1024, GGMLType.Q6_K)], 4096),
+    ("o-8b", "gemv", [(4096, GGMLType.Q4_K)], 4096),
+    ("glu-8b", "glu", [(14336, GGMLType.Q4_K)], 4096),
+    ("down-8b-q4k", "gemv", [(4096, GGMLType.Q4_K)], 14336),
+    ("down-8b-q6k", "gemv", [(4096, GGMLType.Q6_K)], 14336),
+    ("head-8b", "gemv", [(128256, GGMLType.Q6_K)], 4096),
+    ("glu-70b", "glu", [(28672, GGMLType.Q4_K)], 8192),
+    ("o-8b-q8", "gemv", [(4096, GGMLType.Q8_0)], 4096),
+    ("o-8b-bf16", "gemv", [(4096, GGMLType.BF16)], 4096),
+]
+
+
+def peak_gbs() -> tuple[float, str]:
+    p = os.path.join(os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__)))), "MEASURED_PEAKS.json")
+    try:
+        with open(p) as f:
+            return float(json.load(f)["hbm_gbs"]), "measured"
+    except (OSError, KeyError, ValueError):
+        return 6650.0, "fallback"
+
+
+def random_weight(n: int, k: int, t: GGMLType, seed: int) -> K.DevWeight:
+    """Random valid blocks: quantise a slab of N(0, 0.02) values and tile it (content does not affect timing)."""
+    g = torch.Generator(device="cuda").manual_seed(seed)
+    rows = min(n, 512)
+    w = torch.randn(rows, k, device="cuda", generator=g) * 0.02
+    q = QWeight.from_float("w", w, t)
+    reps = (n + rows - 1) // rows
+    raw = q.raw.view(rows, -1).repeat(reps, 1)[:n].reshape(-1)
+    return K.repack(QWeight("w", t, (n, k), raw), "cuda")
+
+
+def main() -> None:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--nb", default="1,4,8")
+    ap.add_argument("--only", default="")
+    ap.add_argument("--reps", type=int, default=20)
+    ap.add_argument("--copies", type=int, default=0, help="weight copies to rotate through (0 = enough to exceed L2)")
+    args = ap.parse_args()
+    peak, how = peak_gbs()
+    rows_out = []
+    for name, kind, segs, k in CASES:
+        if args.only and args.only not in name:
+            continue
+        nbytes = 0
+        one = [random_weight(n, k, t, i) for i, (n, t) in enumerate(segs)]
+        if kind == "glu":
+            one = [K.interleave_rows(one[0], random_weight(segs[0][0], k, segs[0][1], 7))]
+        nbytes = sum(w.nbytes for w in one)
+        copies = args.copies or max(2, int(300e6 // nbytes) + 1)
+        sets = [one]
+        for c in range(1, copies):
+            sets.append([K.DevWeight(w.wtype, w.n, w.k, [p.clone() for p in w.planes]) for w in one])
+        for nb in [int(x) for x in args.nb.split(",")]:
+            x = torch.randn(nb, k, device="cuda")
+            act = K.rmsnorm_quant(x, None, 0.0, do_norm=False)
+            n_out = sum(w.n for w in one)
+            out = torch.zeros(nb, n_out, device="cuda")
+
+            def run(ws):
+                if kind == "gemv":
+                    K.gemv(ws, act, out=out, pdl=False)
+                else:
+                    K.gemv_glu_quant(ws[0], act, "silu", pdl=False)
+
+            for i in range(3):
+                run(sets[i % copies])
+            torch.cuda.synchronize()
+            # The launches are recorded into a CUDA graph so that the host-side cost of a launch
+            # (tens of microseconds through Python) does not gate kernels that take a few microseconds.
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph):
+                for i in range(args.reps):
+                    run(sets[i % copies])
+            graph.replay()
+            torch.cuda.synchronize()
+            ts = []
+            for _ in range(5):
+                a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                a.record()
+                graph.replay()
+                b.record()
+                torch.cuda.synchronize()
+                ts.append(a.elapsed_time(b) * 1e3 / args.reps)
+            ts.sort()
+            med = ts[len(ts) // 2]
+            gbs = nbytes / med / 1e3
+            rows_out.append((name, nb, med, gbs, gbs / peak))
+            print(f"{name:14s} nb={nb}  {med:8.1f} us  {gbs:7.0f} GB/s  {gbs / peak:5.2f} of {how} {peak:.0f} GB/s  "
+                  f"({nbytes / 1e6:.1f} MB, {copies} copies)", flush=True)
+        del sets
+        torch.cuda.empty_cache()
+
+
+if __name__ == "__main__":
+    main()

@@ -103,6 +103,12 @@ class B200Backend:
                 L.ffn_norm = vec(p + "post_attention_norm.weight")
             L.post_ffw_norm = vec(p + "post_ffw_norm.weight") if c.sandwich_norm else None
             L.gate, L.up, L.down = mat(p + "ffn_gate"), mat(p + "ffn_up"), mat(p + "ffn_down")
+            if L.gate.wtype != L.up.wtype:
+                L.gu = K.interleave_rows(K.to_f16(L.gate), K.to_f16(L.up))
+            else:
+                L.gu = K.interleave_rows(L.gate, L.up)
+            if self.keep_bf16:      # prefill reads the bf16 copies; the separate quantised planes are no longer needed
+                L.gate.planes, L.up.planes = [], []
             L.sinks = vec(p + "attn_sinks.weight")
             L.swa = c.layer_is_swa(i)
             self.layers.append(L)
@@ -122,7 +128,7 @@ class B200Backend:
     def weight_bytes(self) -> int:
         ws = [self.embd] + ([self.head] if self.head is not self.embd else [])
         for L in self.layers:
-            ws += [L.wq, L.wk, L.wv, L.wo, L.gate, L.up, L.down]
+            ws += [L.wq, L.wk, L.wv, L.wo, L.gu, L.down]
         return sum(w.nbytes for w in ws)
 
     def kv_bytes(self) -> int:
@@ -219,7 +225,7 @@ class B200Backend:
                 self._gemv([L.wo], nb, b.aq, b.ads, b.ao, b.x, b.x.stride(0), accumulate=True)
             self._norm_quant(b.x, L.ffn_norm, nb, c.d_model)
             ga = K.GluArgs()
-            ga.gate, ga.up = L.gate.desc(), L.up.desc()
+            ga.gu = L.gu.desc()
             ga.nb, ga.xq, ga.xds, ga.xf = nb, K.ptr(b.xq), K.ptr(b.xds), K.ptr(b.xf)
             ga.act, ga.alpha, ga.limit = act, c.swiglu_alpha, c.swiglu_limit
             ga.hq, ga.hds, ga.hf = K.ptr(b.hq), K.ptr(b.hds), K.ptr(b.hf) if not L.down.quant_input else None

@@ -14,9 +14,9 @@ enum WType : int {
     WT_F16 = 1,    // p0: half   [N][K]
     WT_BF16 = 2,   // p0: bf16   [N][K]
     WT_Q8_0 = 3,   // p0: int8   [N][K]        p1: half [N][K/32]
-    WT_Q4_K = 4,   // p0: u8     [N][K/2]      p1: 16-byte headers [N][K/256] = {half d, half dmin, u8 scales[12]}
+    WT_Q4_K = 4,   // p0: u8     [N][K/2]      p1: u8 [N][K/256][16] = 4 x {sc(2j), sc(2j+1), min(2j), min(2j+1)}   p2: {half d, half dmin} [N][K/256]
     WT_Q6_K = 5,   // p0: ql u8  [N][K/2]      p1: qh u8 [N][K/4]   p2: int8 scales [N][K/16]   p3: half d [N][K/256]
-    WT_Q5_K = 6,   // p0: u8     [N][K/2]      p1: headers as Q4_K  p2: qh u8 [N][K/8]
+    WT_Q5_K = 6,   // p0..p2 as Q4_K           p3: qh u8 [N][K/8]
     WT_MXFP4 = 7,  // p0: u8     [N][K/2]      p1: e8m0 u8 [N][K/32]
     WT_Q4_0 = 8,   // p0: u8     [N][K/2]      p1: half d [N][K/32]
 };

@@ -20,40 +20,86 @@ struct NormQuantArgs {
     float* residual;     // if set: residual[b][i] += y   (post-norm residual add of sandwich-norm models)
 };
 
+// Each thread owns float4 chunks c = tid + 256 j; a quantisation block of 32 is 8 consecutive chunks =
+// 8 consecutive lanes, so block maxima and sums are 3-step shuffles.  All loads of a row are issued
+// before the first use (rows up to 8192 elements stay in registers).
 __global__ void __launch_bounds__(256) rmsnorm_quant_kernel(const __grid_constant__ NormQuantArgs a) {
+    constexpr int MAXJ = 8;
     __shared__ float red[8];
     const int b = blockIdx.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int nchunk = a.k >> 2;
+    float4 wv[MAXJ];
+    if (a.w) {   // the norm weights do not depend on the producer kernel
+#pragma unroll
+        for (int j = 0; j < MAXJ; j++) {
+            const int c = tid + 256 * j;
+            wv[j] = c < nchunk ? *(const float4*)(a.w + 4 * c) : make_float4(0.f, 0.f, 0.f, 0.f);
+        }
+    }
     pdl_launch();
     pdl_wait();
     const float* x = a.x + (size_t)b * a.k;
-    float inv = 1.f;
-    if (a.do_norm) {
-        float ss = 0.f;
-        for (int i = tid * 4; i < a.k; i += 256 * 4) {
-            const float4 v = *(const float4*)(x + i);
-            ss += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
+    for (int c0 = 0; c0 < nchunk; c0 += 256 * MAXJ) {     // one trip for k <= 8192
+        float4 v[MAXJ];
+#pragma unroll
+        for (int j = 0; j < MAXJ; j++) {
+            const int c = c0 + tid + 256 * j;
+            v[j] = c < nchunk ? *(const float4*)(x + 4 * c) : make_float4(0.f, 0.f, 0.f, 0.f);
         }
-        ss = warp_sum(ss);
-        if (lane == 0) red[warp] = ss;
-        __syncthreads();
-        float t = lane < 8 ? red[lane] : 0.f;
-        t = warp_sum(t);
-        inv = rsqrtf(t / (float)a.k + a.eps);
-    }
-    // each warp handles blocks of 32 consecutive elements
-    for (int blk = warp; blk < (a.k >> 5); blk += 8) {
-        const int i = blk * 32 + lane;
-        float v = x[i] * inv;
-        if (a.w) v *= a.w[i];
-        if (a.xf) a.xf[(size_t)b * a.k + i] = v;
-        if (a.residual) a.residual[(size_t)b * a.k + i] += v;
-        if (a.xq) {
-            const float amax = warp_max(fabsf(v));
-            const float d = amax / 127.f;
-            const int q = d > 0.f ? __float2int_rn(v / d) : 0;
-            const float s = d * warp_sum((float)q);
-            a.xq[(size_t)b * a.k + i] = (int8_t)q;
-            if (lane == 0) a.xds[(size_t)b * (a.k >> 5) + blk] = make_float2(d, s);
+        float inv = 1.f;
+        if (a.do_norm) {
+            float ss = 0.f;
+            if (nchunk <= 256 * MAXJ) {
+#pragma unroll
+                for (int j = 0; j < MAXJ; j++) ss += v[j].x * v[j].x + v[j].y * v[j].y + v[j].z * v[j].z + v[j].w * v[j].w;
+            } else {
+                for (int c = tid; c < nchunk; c += 256) {
+                    const float4 t = *(const float4*)(x + 4 * c);
+                    ss += t.x * t.x + t.y * t.y + t.z * t.z + t.w * t.w;
+                }
+            }
+            ss = warp_sum(ss);
+            __syncthreads();
+            if (lane == 0) red[warp] = ss;
+            __syncthreads();
+            float t = lane < 8 ? red[lane] : 0.f;
+            t = warp_sum(t);
+            inv = rsqrtf(t / (float)a.k + a.eps);
+        }
+#pragma unroll
+        for (int j = 0; j < MAXJ; j++) {
+            const int c = c0 + tid + 256 * j;
+            const bool ok = c < nchunk;
+            float4 y = v[j];
+            y.x *= inv; y.y *= inv; y.z *= inv; y.w *= inv;
+            if (a.w) {
+                float4 ww = wv[j];
+                if (c0) ww = ok ? *(const float4*)(a.w + 4 * c) : ww;
+                y.x *= ww.x; y.y *= ww.y; y.z *= ww.z; y.w *= ww.w;
+            }
+            const size_t o = (size_t)b * a.k + 4 * (size_t)c;
+            if (ok && a.xf) *(float4*)(a.xf + o) = y;
+            if (ok && a.residual) {
+                float4 r = *(float4*)(a.residual + o);
+                r.x += y.x; r.y += y.y; r.z += y.z; r.w += y.w;
+                *(float4*)(a.residual + o) = r;
+            }
+            if (a.xq) {
+                float amax = fmaxf(fmaxf(fabsf(y.x), fabsf(y.y)), fmaxf(fabsf(y.z), fabsf(y.w)));
+                amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
+                amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
+                amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 4));
+                const float d = amax / 127.f, id = d > 0.f ? 1.f / d : 0.f;
+                const int q0 = __float2int_rn(y.x * id), q1 = __float2int_rn(y.y * id), q2 = __float2int_rn(y.z * id), q3 = __float2int_rn(y.w * id);
+                float qs = (float)(q0 + q1 + q2 + q3);
+                qs += __shfl_xor_sync(0xffffffffu, qs, 1);
+                qs += __shfl_xor_sync(0xffffffffu, qs, 2);
+                qs += __shfl_xor_sync(0xffffffffu, qs, 4);
+                if (ok) {
+                    *(uint32_t*)(a.xq + o) = (uint32_t)(q0 & 0xff) | ((uint32_t)(q1 & 0xff) << 8) | ((uint32_t)(q2 & 0xff) << 16) | ((uint32_t)(q3 & 0xff) << 24);
+                    if ((lane & 7) == 0) a.xds[(size_t)b * (a.k >> 5) + (c >> 3)] = make_float2(d, d * qs);
+                }
+            }
         }
     }
 }
@@ -185,18 +231,14 @@ __device__ __forceinline__ float deq_elem(const WDesc& w, int row, int i) {
         case WT_Q4_K:
         case WT_Q5_K: {
             const int sb = i >> 8, r = i & 255, j = r >> 6, hi = (r >> 5) & 1, l = r & 31;
-            const uint4 hd = ((const uint4*)w.p1)[(size_t)row * (K >> 8) + sb];
-            const __half2 dm = *reinterpret_cast<const __half2*>(&hd.x);
-            const uint8_t* sc = reinterpret_cast<const uint8_t*>(&hd.y);
-            const int is = 2 * j + hi;
-            int s, m;
-            if (is < 4) { s = sc[is] & 63; m = sc[is + 4] & 63; }
-            else { s = (sc[is + 4] & 0xF) | ((sc[is - 4] >> 6) << 4); m = (sc[is + 4] >> 4) | ((sc[is] >> 6) << 4); }
+            const uint8_t* sm = (const uint8_t*)w.p1 + ((size_t)row * (K >> 8) + sb) * 16 + 4 * j;
+            const __half2 dm = ((const __half2*)w.p2)[(size_t)row * (K >> 8) + sb];
+            const int s = sm[hi], m = sm[2 + hi];
             const uint8_t qb = ((const uint8_t*)w.p0)[(size_t)row * (K >> 1) + sb * 128 + j * 32 + l];
             int q = hi ? (qb >> 4) : (qb & 15);
             if (w.type == WT_Q5_K) {
-                const uint8_t h = ((const uint8_t*)w.p2)[(size_t)row * (K >> 3) + sb * 32 + l];
-                q |= ((h >> is) & 1) << 4;
+                const uint8_t h = ((const uint8_t*)w.p3)[(size_t)row * (K >> 3) + sb * 32 + l];
+                q |= ((h >> (2 * j + hi)) & 1) << 4;
             }
             return __low2float(dm) * (float)s * (float)q - __high2float(dm) * (float)m;
         }

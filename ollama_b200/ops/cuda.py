@@ -65,7 +65,7 @@ class GemvArgs(C.Structure):
 
 
 class GluArgs(C.Structure):
-    _fields_ = [("gate", WDesc), ("up", WDesc), ("nb", C.c_int), ("xq", C.c_void_p), ("xds", C.c_void_p), ("xf", C.c_void_p),
+    _fields_ = [("gu", WDesc), ("nb", C.c_int), ("xq", C.c_void_p), ("xds", C.c_void_p), ("xf", C.c_void_p),
                 ("act", C.c_int), ("alpha", C.c_float), ("limit", C.c_float), ("hq", C.c_void_p), ("hds", C.c_void_p),
                 ("hf", C.c_void_p)]
 
@@ -177,13 +177,16 @@ def repack(w: QWeight, device, bias: torch.Tensor | None = None) -> DevWeight:
     if t == GGMLType.MXFP4 and k % 32 == 0:
         blk = raw.view(rows, k // 32, 17)
         return mk(WT_MXFP4, [blk[:, :, 1:].reshape(rows, k // 2), blk[:, :, 0].reshape(rows, k // 32)])
-    if t == GGMLType.Q4_K:
-        blk = raw.view(rows, k // 256, 144)
-        return mk(WT_Q4_K, [blk[:, :, 16:].reshape(rows, k // 2), blk[:, :, :16].reshape(rows, k // 256 * 16)])
-    if t == GGMLType.Q5_K:
-        blk = raw.view(rows, k // 256, 176)
-        return mk(WT_Q5_K, [blk[:, :, 48:].reshape(rows, k // 2), blk[:, :, :16].reshape(rows, k // 256 * 16),
-                            blk[:, :, 16:48].reshape(rows, k // 8)])
+    if t in (GGMLType.Q4_K, GGMLType.Q5_K):
+        q5 = t == GGMLType.Q5_K
+        blk = raw.view(rows, k // 256, 176 if q5 else 144)
+        sc, mn = quants._scale_min_k4(blk[:, :, 4:16].reshape(-1, 12))                # two [rows*nsb, 8] float tables
+        sc, mn = sc.to(torch.uint8).view(-1, 4, 2), mn.to(torch.uint8).view(-1, 4, 2)
+        sm = torch.cat([sc, mn], 2).reshape(rows, k // 256 * 16)                        # per 64-group: sc, sc, min, min
+        dd = blk[:, :, :4].reshape(rows, k // 256 * 4)
+        if q5:
+            return mk(WT_Q5_K, [blk[:, :, 48:].reshape(rows, k // 2), sm, dd, blk[:, :, 16:48].reshape(rows, k // 8)])
+        return mk(WT_Q4_K, [blk[:, :, 16:].reshape(rows, k // 2), sm, dd])
     if t == GGMLType.Q6_K:
         blk = raw.view(rows, k // 256, 210)
         return mk(WT_Q6_K, [blk[:, :, :128].reshape(rows, k // 2), blk[:, :, 128:192].reshape(rows, k // 4),
@@ -248,15 +251,36 @@ def gemv(weights: list[DevWeight], x: QAct, out: torch.Tensor | None = None, acc
 _ACT = {"silu": 0, "gelu_tanh": 1, "swiglu_oai": 2}
 
 
-def gemv_glu_quant(gate: DevWeight, up: DevWeight, x: QAct, act: str, alpha: float = 1.702, limit: float = 7.0,
+def interleave_rows(a: DevWeight, b: DevWeight) -> DevWeight:
+    """Row-interleave two equally shaped weights (row 2i = a[i], row 2i+1 = b[i]): the FFN gate/up pair as one matrix."""
+    if a.wtype != b.wtype or a.n != b.n or a.k != b.k or a.experts != b.experts:
+        raise ValueError("interleave_rows needs two weights of the same encoding and shape")
+    rows = a.total_rows
+    planes = [torch.stack([pa.view(rows, -1), pb.view(rows, -1)], 1).reshape(2 * rows, -1).contiguous() for pa, pb in zip(a.planes, b.planes)]
+    bias = None
+    if a.bias is not None or b.bias is not None:
+        za = a.bias if a.bias is not None else torch.zeros(rows, device=planes[0].device)
+        zb = b.bias if b.bias is not None else torch.zeros(rows, device=planes[0].device)
+        bias = torch.stack([za.view(-1), zb.view(-1)], 1).reshape(-1).contiguous()
+    return DevWeight(a.wtype, 2 * a.n, a.k, planes, bias, a.name + "+" + b.name, a.experts)
+
+
+def to_f16(w: DevWeight) -> DevWeight:
+    """Expand any encoding to f16 planes (used when a fused pair does not share one encoding)."""
+    deq = dequant_to_bf16(w).to(torch.float16)
+    return DevWeight(WT_F16, w.n, w.k, [deq], w.bias, w.name, w.experts)
+
+
+def gemv_glu_quant(gu: DevWeight, x: QAct, act: str, alpha: float = 1.702, limit: float = 7.0,
                    want_f: bool = False, pdl: bool = False) -> QAct:
+    """h = act(gate x) * (up x) on the interleaved gate/up matrix, returned as int8 blocks (+ fp32 on request)."""
     nb = x.q.shape[0]
-    n = gate.n
+    n = gu.n // 2
     hq = torch.empty(nb, n, device=x.q.device, dtype=torch.int8)
     hds = torch.empty(nb, n // 32, 2, device=x.q.device, dtype=torch.float32)
     hf = torch.empty(nb, n, device=x.q.device, dtype=torch.float32) if want_f else None
     a = GluArgs()
-    a.gate, a.up = gate.desc(), up.desc()
+    a.gu = gu.desc()
     a.nb, a.xq, a.xds, a.xf = nb, ptr(x.q), ptr(x.ds), ptr(x.f)
     a.act, a.alpha, a.limit = _ACT[act], alpha, limit
     a.hq, a.hds, a.hf = ptr(hq), ptr(hds), ptr(hf)

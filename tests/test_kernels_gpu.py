@@ -97,10 +97,10 @@ def test_glu_quant(act):
     n, k, nb = 256, 512, 3
     qg, bg = _weight(GGMLType.Q4_K, n, k, seed=1, bias=True)
     qu, bu = _weight(GGMLType.Q4_K, n, k, seed=2, bias=True)
-    g, u = K.repack(qg, "cuda", bias=bg), K.repack(qu, "cuda", bias=bu)
+    gu = K.interleave_rows(K.repack(qg, "cuda", bias=bg), K.repack(qu, "cuda", bias=bu))
     x = torch.randn(nb, k).cuda() * 3
     xa = K.rmsnorm_quant(x, None, 0.0, do_norm=False)
-    h = K.gemv_glu_quant(g, u, xa, act, want_f=True)
+    h = K.gemv_glu_quant(gu, xa, act, want_f=True)
     xr = _quant_act_ref(x.cpu())
     ref = R.glu(xr @ qg.dequant().t() + bg, xr @ qu.dequant().t() + bu, act)
     assert torch.allclose(h.f.cpu(), ref, atol=2e-3 * ref.abs().max().item(), rtol=2e-3)
@@ -216,3 +216,20 @@ def test_engine_matches_reference_graph(tmp_path, spec, ft):
     a = eng.decode_argmax([1], [tok], [len(prompt) + 6])
     eng2 = eng.decode([1], [tok], [len(prompt) + 6])
     assert a[0] == int(eng2[0].argmax())
+
+
+@pytest.mark.parametrize("t", [GGMLType.Q4_K, GGMLType.Q6_K, GGMLType.Q8_0, GGMLType.BF16])
+@pytest.mark.parametrize("nb", [1, 2, 4, 8])
+def test_gemv_model_shapes(t, nb):
+    """Shapes of an 8B model: exercises the row-length split across warps (small n) and long rows."""
+    K = _K()
+    for n, k in ((4096, 4096), (1024, 14336), (20000, 1024)):
+        qw, bias = _weight(t, n, k, bias=True)
+        dw = K.repack(qw, "cuda", bias=bias)
+        x = torch.randn(nb, k, generator=torch.Generator().manual_seed(nb)).cuda()
+        act = K.rmsnorm_quant(x, None, 0.0, do_norm=False)
+        y = K.gemv([dw], act)
+        wf = qw.dequant()
+        xr = _quant_act_ref(x.cpu()) if dw.quant_input else x.cpu()
+        ref = xr @ wf.t() + bias
+        assert torch.allclose(y.cpu(), ref, atol=2e-3 * ref.abs().max().item(), rtol=1e-3)
