@@ -373,8 +373,8 @@ class Runner:
             return
         piece = b""
         if tk is not None:
-            if tok in tk.special and not s.req.preserved_tokens:
-                piece = b""
+            if 0 <= tok < tk.n_vocab and tk.types[tok] == 3 and not s.req.preserved_tokens:
+                piece = b""               # control tokens are not part of the visible text; user-defined tokens are
             else:
                 piece = tk.token_bytes(tok) if 0 <= tok < tk.n_vocab else b""
         s.pending_bytes += piece

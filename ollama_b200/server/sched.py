@@ -1,0 +1,334 @@
+"""Model scheduler: load / reuse / evict runners, keep-alive timers, bounded request queue.
+
+Semantics follow the reference scheduler (server/sched.go):
+  * one runner per model; requests for a loaded model whose load-time options still match reuse it
+    (:169-211, reload predicate :1381-1431 -- adapters/projectors, num_ctx / num_batch / num_gpu /
+    main_gpu / use_mmap / num_thread with "automatic" values ignored, failed ping);
+  * one model loads at a time (:66-74, :517-606); the queue holds OLLAMA_MAX_QUEUE requests, beyond
+    that callers get "server busy" / HTTP 503 (:88, :204-208);
+  * at most OLLAMA_MAX_LOADED_MODELS runners (default 3 x GPUs, :83-86, :280-291); to make room the
+    idle runner with the shortest session is unloaded first (:1557-1693);
+  * a finished request restarts the keep-alive timer; zero keep-alive unloads immediately, a negative
+    one never expires (:374-413); expiry waits until the reference count drops to zero (:414-468);
+  * predicted memory = weights + KV cache of num_ctx x num_parallel tokens (:535-536); a model that
+    does not fit the free memory of one GPU is spread over the GPUs of the node (:972-1031);
+  * num_ctx floor 4 (:170-172), default context tier by total VRAM (server/routes.go:2043-2058).
+Dependencies (runner factory, device query, clock) are constructor arguments so tests can run the
+whole matrix with fabricated devices and fake runners, as the reference's tests do (sched_test.go).
+"""
+from __future__ import annotations
+
+import logging
+import math
+import threading
+import time
+from dataclasses import dataclass, field
+from typing import Any, Callable
+
+from .. import envconfig
+from ..api.types import runner_options
+from ..discover.devices import GPU_OVERHEAD_DEFAULT, DeviceInfo
+
+log = logging.getLogger("ollama_b200.sched")
+
+
+class SchedulerError(Exception):
+    def __init__(self, msg: str, status: int = 500):
+        super().__init__(msg)
+        self.status = status
+
+
+ERR_MAX_QUEUE = "server busy, please try again.  maximum pending requests exceeded"
+
+
+@dataclass
+class RunnerRef:
+    model_key: str
+    model: Any
+    runner: Any
+    options: dict[str, Any]
+    num_parallel: int = 1
+    ref_count: int = 0
+    session_duration: float = 300.0
+    expires_at: float = math.inf
+    total_size: int = 0
+    vram_size: int = 0
+    gpus: list[str] = field(default_factory=list)
+    loaded_at: float = 0.0
+    timer: threading.Timer | None = None
+    context_length: int = 0
+
+    def needs_reload(self, model: Any, opts: dict[str, Any]) -> bool:
+        if list(getattr(model, "adapter_paths", [])) != list(getattr(self.model, "adapter_paths", [])):
+            return True
+        if list(getattr(model, "projector_paths", [])) != list(getattr(self.model, "projector_paths", [])):
+            return True
+        want, have = runner_options(opts), self.options
+        for k in ("num_batch", "num_thread", "main_gpu", "use_mmap", "draft_num_predict"):
+            if want.get(k) is not None and want.get(k) != have.get(k):
+                return True
+        if want.get("num_ctx") and want["num_ctx"] != have.get("num_ctx"):
+            return True
+        if want.get("num_gpu", -1) not in (-1, None) and want["num_gpu"] != have.get("num_gpu"):
+            return True
+        try:
+            return not self.runner.ping()
+        except Exception:
+            return True
+
+
+def default_context(gpus: list[DeviceInfo]) -> int:
+    """4k / 32k / 256k tokens by total VRAM (< 24, 24-48, >= 48 GiB)."""
+    total = sum(g.total_memory for g in gpus)
+    if total >= 47 << 30:
+        return 262144
+    if total >= 23 << 30:
+        return 32768
+    return 4096
+
+
+def predict_memory(model: Any, num_ctx: int, num_parallel: int) -> int:
+    """Weights + f16 KV cache for num_ctx x num_parallel tokens (llm/llama_server.go:2681-2700)."""
+    size = int(getattr(model, "size", 0) or 0)
+    kv = getattr(model, "kv", lambda: {})() or {}
+    arch = kv.get("general.architecture", "")
+
+    def first(v, default=0):
+        if v is None:
+            return default
+        try:
+            return int(v[0]) if hasattr(v, "__len__") and not isinstance(v, str) else int(v)
+        except (TypeError, ValueError, IndexError):
+            return default
+
+    layers = first(kv.get(f"{arch}.block_count"))
+    heads = first(kv.get(f"{arch}.attention.head_count"), 1) or 1
+    kvh = first(kv.get(f"{arch}.attention.head_count_kv"), heads) or heads
+    d = first(kv.get(f"{arch}.embedding_length"))
+    hd = first(kv.get(f"{arch}.attention.key_length"), d // heads if heads else 0)
+    return size + 2 * layers * kvh * hd * num_ctx * num_parallel * 2
+
+
+class Scheduler:
+    def __init__(self, new_runner_fn: Callable[..., Any] | None = None, get_gpus_fn: Callable[[], list[DeviceInfo]] | None = None,
+                 now: Callable[[], float] = time.monotonic):
+        self.new_runner_fn = new_runner_fn or _default_runner
+        self.get_gpus_fn = get_gpus_fn or (lambda: [])
+        self.now = now
+        self.loaded: dict[str, RunnerRef] = {}
+        self.lock = threading.Condition()
+        self.load_lock = threading.Lock()
+        self.pending = 0
+        self._gpus: list[DeviceInfo] | None = None
+
+    # -- configuration ----------------------------------------------------------------------------------
+    def gpus(self, refresh: bool = False) -> list[DeviceInfo]:
+        if self._gpus is None or refresh:
+            self._gpus = list(self.get_gpus_fn())
+        return self._gpus
+
+    def max_runners(self) -> int:
+        n = envconfig.max_runners()
+        return n if n > 0 else 3 * max(1, len(self.gpus()))
+
+    def free_memory(self) -> int:
+        """Free VRAM of the node after subtracting what our own runners hold and the per-device reserve."""
+        gpus = self.gpus(refresh=True)
+        reserve = (GPU_OVERHEAD_DEFAULT + envconfig.gpu_overhead()) * len(gpus)
+        total = sum(g.total_memory for g in gpus)
+        reported = sum(g.free_memory for g in gpus)
+        ours = sum(r.vram_size for r in self.loaded.values())
+        return max(0, min(reported, total - ours) - reserve)
+
+    # -- public API --------------------------------------------------------------------------------------
+    def get_runner(self, model: Any, opts: dict[str, Any], keep_alive: float | None = None) -> RunnerRef:
+        key = getattr(model, "model_path", None) or getattr(model, "name", "")
+        opts = dict(opts)
+        if opts.get("num_ctx", 0) and opts["num_ctx"] < 4:
+            opts["num_ctx"] = 4
+        session = envconfig.keep_alive() if keep_alive is None else keep_alive
+        with self.lock:
+            ref = self.loaded.get(key)
+            if ref is not None and not ref.needs_reload(model, opts):
+                self._acquire(ref, session)
+                return ref
+            if self.pending >= envconfig.max_queue():
+                raise SchedulerError(ERR_MAX_QUEUE, 503)
+            self.pending += 1
+        try:
+            with self.load_lock:          # one model loads at a time
+                with self.lock:
+                    ref = self.loaded.get(key)
+                    if ref is not None and not ref.needs_reload(model, opts):
+                        self._acquire(ref, session)
+                        return ref
+                    if ref is not None:
+                        self._wait_idle_then_unload(ref)
+                ref = self._load(key, model, opts, session)
+                with self.lock:
+                    self.loaded[key] = ref
+                    self._acquire(ref, session)
+                    self.lock.notify_all()
+                return ref
+        finally:
+            with self.lock:
+                self.pending -= 1
+
+    def release(self, ref: RunnerRef) -> None:
+        with self.lock:
+            ref.ref_count = max(0, ref.ref_count - 1)
+            if ref.ref_count == 0:
+                if ref.session_duration <= 0:
+                    self._unload(ref)
+                else:
+                    self._arm_timer(ref)
+            self.lock.notify_all()
+
+    def expire_runner(self, model: Any) -> None:
+        """Unload as soon as the runner is idle (``keep_alive: 0`` with an empty prompt, ``ollama stop``)."""
+        key = getattr(model, "model_path", None) or getattr(model, "name", "")
+        with self.lock:
+            ref = self.loaded.get(key)
+            if ref is None:
+                return
+            ref.session_duration = 0
+            ref.expires_at = self.now()
+            if ref.ref_count == 0:
+                self._unload(ref)
+
+    def unload_all(self) -> None:
+        with self.lock:
+            for ref in list(self.loaded.values()):
+                self._unload(ref)
+
+    def ps(self) -> list[RunnerRef]:
+        with self.lock:
+            return sorted(self.loaded.values(), key=lambda r: r.expires_at)
+
+    # -- internals ---------------------------------------------------------------------------------------
+    def _acquire(self, ref: RunnerRef, session: float) -> None:
+        ref.ref_count += 1
+        ref.session_duration = session
+        if ref.timer is not None:
+            ref.timer.cancel()
+            ref.timer = None
+        ref.expires_at = math.inf if math.isinf(session) else self.now() + session
+
+    def _arm_timer(self, ref: RunnerRef) -> None:
+        if ref.timer is not None:
+            ref.timer.cancel()
+            ref.timer = None
+        if math.isinf(ref.session_duration):
+            ref.expires_at = math.inf
+            return
+        ref.expires_at = self.now() + ref.session_duration
+
+        def fire():
+            with self.lock:
+                if self.loaded.get(ref.model_key) is ref and ref.ref_count == 0 and self.now() >= ref.expires_at - 1e-3:
+                    self._unload(ref)
+                    self.lock.notify_all()
+
+        ref.timer = threading.Timer(ref.session_duration, fire)
+        ref.timer.daemon = True
+        ref.timer.start()
+
+    def _unload(self, ref: RunnerRef) -> None:
+        if ref.timer is not None:
+            ref.timer.cancel()
+            ref.timer = None
+        if self.loaded.get(ref.model_key) is ref:
+            del self.loaded[ref.model_key]
+        try:
+            ref.runner.close()
+        except Exception as e:  # a runner that fails to shut down is dropped anyway
+            log.warning("runner close failed: %s", e)
+
+    def _wait_idle_then_unload(self, ref: RunnerRef) -> None:
+        deadline = time.monotonic() + 600
+        while ref.ref_count > 0 and time.monotonic() < deadline:
+            self.lock.wait(timeout=0.05)
+        self._unload(ref)
+
+    def _find_runner_to_unload(self) -> RunnerRef | None:
+        refs = sorted(self.loaded.values(), key=lambda r: (r.session_duration, r.model_key))
+        for r in refs:
+            if r.ref_count == 0:
+                return r
+        return refs[0] if refs else None
+
+    def _load(self, key: str, model: Any, opts: dict[str, Any], session: float) -> RunnerRef:
+        gpus = self.gpus(refresh=True)
+        num_parallel = max(1, envconfig.num_parallel())
+        caps = getattr(model, "capabilities", lambda: [])()
+        if "embedding" in caps:
+            num_parallel = 1                       # pooling models run one sequence at a time (sched.go:497-510)
+        auto_ctx = not opts.get("num_ctx")
+        if auto_ctx:
+            opts["num_ctx"] = default_context(gpus) if gpus else 4096
+        # make room: model count first, then memory
+        with self.lock:
+            while len(self.loaded) >= self.max_runners():
+                victim = self._find_runner_to_unload()
+                if victim is None:
+                    break
+                self._wait_idle_then_unload(victim)
+        ladder = [opts["num_ctx"]] + ([c for c in (32768, 4096) if c < opts["num_ctx"]] if auto_ctx else [])
+        last_err: Exception | None = None
+        for attempt, ctx in enumerate(ladder):
+            opts["num_ctx"] = ctx
+            need = predict_memory(model, ctx, num_parallel)
+            if gpus:
+                with self.lock:
+                    while need > self.free_memory() and self.loaded:
+                        victim = self._find_runner_to_unload()
+                        if victim is None:
+                            break
+                        self._wait_idle_then_unload(victim)
+                if need > self.free_memory() and attempt + 1 < len(ladder):
+                    continue                      # automatic context shrinks 256k -> 32k -> 4k before giving up (sched.go:649-669)
+            use = self._place(gpus, need)
+            try:
+                t0 = time.time()
+                runner = self.new_runner_fn(model, dict(opts), num_parallel, use)
+                mem = runner.memory() if hasattr(runner, "memory") else {}
+                ref = RunnerRef(key, model, runner, runner_options(opts), num_parallel, 0, session, total_size=int(mem.get("total", need)),
+                                vram_size=int(mem.get("vram", need if gpus else 0)), gpus=[g.id for g in use], loaded_at=time.time(),
+                                context_length=int(getattr(runner, "n_ctx", ctx)))
+                log.info("loaded %s in %.2fs (ctx %d x %d slots, %d GPUs)", key, time.time() - t0, ctx, num_parallel, len(use))
+                return ref
+            except MemoryError as e:
+                last_err = e
+                with self.lock:                   # out of memory: unload everything else and retry once (sched.go:641-673)
+                    for r in list(self.loaded.values()):
+                        if r.ref_count == 0:
+                            self._unload(r)
+                continue
+            except Exception as e:
+                raise SchedulerError(f"failed to load model: {e}", 500) from e
+        raise SchedulerError(f"model requires more system memory than is available: {last_err}", 500)
+
+    @staticmethod
+    def _place(gpus: list[DeviceInfo], need: int) -> list[DeviceInfo]:
+        """Single GPU when the model fits 80 % of its free memory (most free first), otherwise every GPU."""
+        if not gpus:
+            return []
+        if envconfig.sched_spread():
+            return list(gpus)
+        by_free = sorted(gpus, key=lambda g: -g.free_memory)
+        for g in by_free:
+            if need <= 0.8 * g.free_memory:
+                return [g]
+        return list(gpus)
+
+
+def _default_runner(model: Any, opts: dict[str, Any], num_parallel: int, gpus: list[DeviceInfo]):
+    from ..engine.runner import Runner, RunnerOptions
+    ro = RunnerOptions(num_ctx=int(opts.get("num_ctx") or 4096), num_batch=int(opts.get("num_batch") or 512), num_parallel=num_parallel,
+                       kv_cache_type=envconfig.kv_cache_type() or "f16", device=envconfig.device(), tp=max(1, len(gpus)))
+    try:
+        return Runner(model.model_path, ro)
+    except RuntimeError as e:
+        if "out of memory" in str(e).lower():
+            raise MemoryError(str(e)) from e
+        raise

@@ -74,9 +74,11 @@ class Tokenizer:
             if i is not None and self.types[i] in (TOKEN_CONTROL, TOKEN_USER) and name not in ("<|end|>",):
                 self.eog.add(i)
         self.special = {i for i, t in enumerate(self.types) if t in (TOKEN_CONTROL, TOKEN_USER)}
-        sp = sorted((self.tokens[i] for i in self.special if self.tokens[i]), key=len, reverse=True)
-        # one alternation, longest first, so that "<|eot_id|>" wins over any prefix of it
-        self._special_re = regex.compile("|".join(regex.escape(s) for s in sp)) if sp else None
+        # special tokens are matched verbatim, longest first, so that "<|eot_id|>" wins over any prefix of it;
+        # lookups go through a set per length (a vocabulary may carry tens of thousands of them)
+        self._special_set = {self.tokens[i] for i in self.special if self.tokens[i]}
+        self._special_lens = sorted({len(s) for s in self._special_set}, reverse=True)
+        self._special_first = {s[0] for s in self._special_set}
 
     @property
     def n_vocab(self) -> int:
@@ -112,16 +114,27 @@ class Tokenizer:
         return self._encode_piece(frag)
 
     def _split_special(self, text: str, parse_special: bool):
-        if not parse_special or self._special_re is None:
+        if not parse_special or not self._special_set:
             yield False, text
             return
-        pos = 0
-        for m in self._special_re.finditer(text):
-            if m.start() > pos:
-                yield False, text[pos:m.start()]
-            yield True, m.group(0)
-            pos = m.end()
-        if pos < len(text):
+        pos, i, n = 0, 0, len(text)
+        first, lens, sset = self._special_first, self._special_lens, self._special_set
+        while i < n:
+            if text[i] in first:
+                hit = 0
+                for ln in lens:
+                    if text[i:i + ln] in sset and i + ln <= n:
+                        hit = ln
+                        break
+                if hit:
+                    if i > pos:
+                        yield False, text[pos:i]
+                    yield True, text[i:i + hit]
+                    i += hit
+                    pos = i
+                    continue
+            i += 1
+        if pos < n:
             yield False, text[pos:]
 
     def decode_bytes(self, ids: Iterable[int], skip_special: bool = False) -> bytes:

@@ -1,0 +1,145 @@
+"""REST surface driven through the ASGI app on CPU with a tiny random-init model (pattern of the reference's
+server/routes_*_test.go: handlers exercised directly, temp OLLAMA_MODELS, NDJSON streams asserted line by line)."""
+import hashlib
+import json
+import os
+
+import pytest
+
+
+@pytest.fixture(scope="module")
+def client(tmp_path_factory):
+    root = tmp_path_factory.mktemp("store")
+    old = {k: os.environ.get(k) for k in ("OLLAMA_MODELS", "B200_DEVICE", "OLLAMA_CONTEXT_LENGTH")}
+    os.environ.update(OLLAMA_MODELS=str(root), B200_DEVICE="cpu", OLLAMA_CONTEXT_LENGTH="256")
+    from starlette.testclient import TestClient
+
+    from ollama_b200.models.synth import write_synthetic_gguf
+    from ollama_b200.server.routes import create_app
+    p = str(root / "m.gguf")
+    write_synthetic_gguf(p, "tiny-llama", "F32")
+    data = open(p, "rb").read()
+    digest = "sha256:" + hashlib.sha256(data).hexdigest()
+    with TestClient(create_app()) as c:
+        assert c.head(f"/api/blobs/{digest}").status_code == 404
+        assert c.post(f"/api/blobs/{digest}", content=data).status_code == 201
+        assert c.post(f"/api/blobs/{digest}", content=data).status_code == 200
+        assert c.post("/api/blobs/sha256:" + "0" * 64, content=b"x").status_code == 400
+        r = c.post("/api/create", json={"model": "tiny", "files": {"m.gguf": digest}, "template": "{{ .Prompt }}",
+                                        "parameters": {"temperature": 0, "num_predict": 6}, "system": "", "stream": False})
+        assert r.status_code == 200 and r.json()["status"] == "success"
+        yield c
+    for k, v in old.items():
+        if v is None:
+            os.environ.pop(k, None)
+        else:
+            os.environ[k] = v
+
+
+def test_root_version_tags(client):
+    assert client.get("/").text == "Ollama is running"
+    assert "version" in client.get("/api/version").json()
+    models = client.get("/api/tags").json()["models"]
+    assert models[0]["name"] == "tiny:latest" and models[0]["details"]["family"] == "llama"
+    assert client.get("/v1/models").json()["data"][0]["id"] == "tiny:latest"
+
+
+def test_generate_stream_and_collapse(client):
+    r = client.post("/api/generate", json={"model": "tiny", "prompt": "<t300><t301><t302>", "stream": False})
+    j = r.json()
+    assert r.status_code == 200 and j["done"] and j["done_reason"] == "length" and j["eval_count"] == 6
+    assert j["prompt_eval_count"] == 3 and j["context"][:3] == [300, 301, 302] and len(j["context"]) == 9
+    assert j["response"].count("<t") == 6
+    r = client.post("/api/generate", json={"model": "tiny", "prompt": "<t300><t301><t302>"})
+    assert r.headers["content-type"].startswith("application/x-ndjson")
+    lines = [json.loads(l) for l in r.text.strip().split("\n")]
+    assert lines[-1]["done"] and not lines[0]["done"]
+    assert "".join(l["response"] for l in lines) == j["response"]          # greedy: stream == collapsed
+    # context continuation reuses the returned token array
+    r2 = client.post("/api/generate", json={"model": "tiny", "prompt": "<t5>", "context": j["context"], "stream": False}).json()
+    assert r2["context"][:9] == j["context"]
+
+
+def test_generate_load_unload_and_errors(client):
+    assert client.post("/api/generate", json={"model": "tiny"}).json()["done_reason"] == "load"
+    assert any(m["name"] == "tiny:latest" for m in client.get("/api/ps").json()["models"])
+    assert client.post("/api/generate", json={"model": "tiny", "keep_alive": 0}).json()["done_reason"] == "unload"
+    assert client.get("/api/ps").json()["models"] == []
+    assert client.post("/api/generate", json={"model": "missing", "prompt": "x"}).status_code == 404
+    assert client.post("/api/generate", json={"prompt": "x"}).status_code == 400
+    assert client.post("/api/generate", json={"model": "tiny", "prompt": "x", "options": {"top_k": "many"}}).status_code == 400
+    assert client.post("/api/generate", json={"model": "tiny", "prompt": "x", "top_logprobs": 21}).status_code == 400
+    assert client.post("/api/generate", json={"model": "tiny", "prompt": "x", "raw": True, "system": "s"}).status_code == 400
+    assert client.post("/api/generate", content=b"{bad").status_code == 400
+    r = client.post("/api/generate", json={"model": "tiny", "prompt": "<t9>", "_debug_render_only": True}).json()
+    assert r["_debug_info"]["rendered_template"] == "<t9>"
+
+
+def test_chat_logprobs_format(client):
+    r = client.post("/api/chat", json={"model": "tiny", "messages": [{"role": "user", "content": "<t400>"}], "stream": False,
+                                       "logprobs": True, "top_logprobs": 2})
+    j = r.json()
+    assert j["message"]["role"] == "assistant" and j["eval_count"] == 6 and len(j["logprobs"]) == 6
+    assert len(j["logprobs"][0]["top_logprobs"]) == 2 and j["logprobs"][0]["logprob"] <= 0
+    r = client.post("/api/generate", json={"model": "tiny", "prompt": "<t300>", "format": "json", "options": {"num_predict": 10}, "stream": False})
+    text = r.json()["response"]
+    assert text.strip() == "" or text.lstrip().startswith("{")             # only grammar-legal text comes out
+    assert client.post("/api/generate", json={"model": "tiny", "prompt": "x", "format": "yaml"}).status_code == 400
+    assert client.post("/api/chat", json={"model": "tiny", "messages": []}).json()["done_reason"] == "load"
+
+
+def test_tokenize_embed_show_copy_delete(client):
+    assert client.post("/api/tokenize", json={"model": "tiny", "content": "<t300>ab"}).json()["tokens"] == [300, 100, 101]
+    assert client.post("/api/detokenize", json={"model": "tiny", "tokens": [300, 100, 101]}).json()["content"] == "<t300>ab"
+    e = client.post("/api/embed", json={"model": "tiny", "input": ["<t500>", "<t600><t700>"]}).json()
+    assert len(e["embeddings"]) == 2 and abs(sum(x * x for x in e["embeddings"][0]) - 1) < 1e-4 and e["prompt_eval_count"] == 3
+    assert len(client.post("/api/embed", json={"model": "tiny", "input": "<t5>", "dimensions": 16}).json()["embeddings"][0]) == 16
+    assert len(client.post("/api/embeddings", json={"model": "tiny", "prompt": "<t5>"}).json()["embedding"]) == 256
+    s = client.post("/api/show", json={"model": "tiny", "verbose": True}).json()
+    assert s["capabilities"] == ["completion"] and s["model_info"]["general.architecture"] == "llama"
+    assert "PARAMETER temperature 0" in s["modelfile"] and any(t["name"] == "token_embd.weight" for t in s["tensors"])
+    assert client.post("/api/copy", json={"source": "tiny", "destination": "copy/tiny2:v1"}).status_code == 200
+    assert client.post("/api/copy", json={"source": "nope", "destination": "x"}).status_code == 404
+    assert client.request("DELETE", "/api/delete", json={"model": "copy/tiny2:v1"}).status_code == 200
+    assert client.request("DELETE", "/api/delete", json={"model": "copy/tiny2:v1"}).status_code == 404
+
+
+def test_create_from_existing_model(client):
+    r = client.post("/api/create", json={"model": "child", "from": "tiny", "system": "be brief", "parameters": {"stop": ["<t1>"]},
+                                         "stream": False})
+    assert r.status_code == 200
+    s = client.post("/api/show", json={"model": "child"}).json()
+    assert s["system"] == "be brief" and "stop" in s["parameters"] and "temperature" in s["parameters"]
+    assert client.post("/api/create", json={"model": "x", "from": "nope", "stream": False}).status_code == 404
+    assert client.post("/api/create", json={"model": "x", "stream": False}).status_code == 400
+
+
+def test_openai_and_anthropic_facades(client):
+    body = {"model": "tiny", "messages": [{"role": "user", "content": [{"type": "text", "text": "<t400>"}]}], "max_tokens": 4}
+    j = client.post("/v1/chat/completions", json=body).json()
+    assert j["object"] == "chat.completion" and j["choices"][0]["finish_reason"] == "length" and j["usage"]["completion_tokens"] == 4
+    r = client.post("/v1/chat/completions", json={**body, "stream": True, "stream_options": {"include_usage": True}})
+    events = [l[6:] for l in r.text.split("\n") if l.startswith("data: ")]
+    assert events[-1] == "[DONE]" and json.loads(events[-2])["usage"]["completion_tokens"] == 4
+    assert json.loads(events[0])["choices"][0]["delta"]["role"] == "assistant"
+    j = client.post("/v1/completions", json={"model": "tiny", "prompt": "<t400>", "max_tokens": 3}).json()
+    assert j["object"] == "text_completion" and j["choices"][0]["text"].count("<t") == 3
+    j = client.post("/v1/embeddings", json={"model": "tiny", "input": ["<t5>"]}).json()
+    assert j["data"][0]["object"] == "embedding" and len(j["data"][0]["embedding"]) == 256
+    assert client.post("/v1/chat/completions", json={"model": "nope", "messages": [{"role": "user", "content": "x"}]}).status_code == 404
+    assert client.get("/v1/models/tiny").json()["id"] == "tiny:latest"
+    j = client.post("/v1/responses", json={"model": "tiny", "input": "<t400>", "max_output_tokens": 3}).json()
+    assert j["status"] == "completed" and j["usage"]["output_tokens"] == 3
+    j = client.post("/v1/messages", json={"model": "tiny", "messages": [{"role": "user", "content": "<t400>"}], "max_tokens": 3}).json()
+    assert j["type"] == "message" and j["stop_reason"] == "max_tokens" and j["usage"]["output_tokens"] == 3
+    r = client.post("/v1/messages", json={"model": "tiny", "messages": [{"role": "user", "content": "<t400>"}], "max_tokens": 3, "stream": True})
+    assert "event: message_start" in r.text and "event: message_stop" in r.text
+
+
+def test_host_allow_list_and_cors(client):
+    assert client.get("/", headers={"Host": "evil.example.com"}).status_code == 403
+    assert client.get("/", headers={"Host": "localhost:11434"}).status_code == 200
+    r = client.options("/api/generate", headers={"Origin": "http://localhost:3000", "Access-Control-Request-Method": "POST"})
+    assert r.headers.get("access-control-allow-origin") == "http://localhost:3000"
+    r = client.options("/api/generate", headers={"Origin": "http://evil.example.com", "Access-Control-Request-Method": "POST"})
+    assert "access-control-allow-origin" not in r.headers
