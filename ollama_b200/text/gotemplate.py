@@ -285,6 +285,8 @@ def _fmt(v: Any) -> str:
         return "true" if v else "false"
     if isinstance(v, float):
         return repr(v) if v != int(v) else str(int(v))
+    if isinstance(v, (list, dict)) and type(v).__str__ not in (list.__str__, dict.__str__):
+        return str(v)                 # values that define their own text form (tool lists, call arguments: JSON)
     if isinstance(v, (list, tuple)):
         return "[" + " ".join(_fmt(x) for x in v) + "]"
     if isinstance(v, dict):

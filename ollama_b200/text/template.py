@@ -54,18 +54,28 @@ class _Args(dict):
         return json.dumps(self, separators=(",", ":"), ensure_ascii=False)
 
 
+class _Tool(dict):
+    """One tool: Go field names for templates, the wire form when printed."""
+
+    wire: dict[str, Any] = {}
+
+    def __str__(self) -> str:
+        return json.dumps(self.wire, separators=(",", ":"), ensure_ascii=False)
+
+
 class _Tools(list):
     def __str__(self) -> str:
-        return json.dumps(self, separators=(",", ":"), ensure_ascii=False)
+        return json.dumps([t.wire for t in self], separators=(",", ":"), ensure_ascii=False)
 
 
 def _tmpl_tools(tools: list[dict[str, Any]] | None) -> _Tools:
     out = _Tools()
     for t in tools or []:
         fn = t.get("function", {})
-        out.append({"Type": t.get("type", "function"), "Function": {"Name": fn.get("name", ""), "Description": fn.get("description", ""),
-                                                                    "Parameters": fn.get("parameters") or {}},
-                    "type": t.get("type", "function"), "function": fn})
+        d = _Tool({"Type": t.get("type", "function"), "Function": {"Name": fn.get("name", ""), "Description": fn.get("description", ""),
+                                                                  "Parameters": fn.get("parameters") or {}}})
+        d.wire = t
+        out.append(d)
     return out
 
 

@@ -1,0 +1,200 @@
+"""Scheduler behaviour with fake runners and fabricated devices (the reference tests its scheduler the same way:
+injected newServerFn / getGpuFn and mock runners, server/sched_test.go:210-276, 1221-2049)."""
+import math
+import threading
+import time
+
+import pytest
+
+from ollama_b200.discover.devices import DeviceInfo
+from ollama_b200.server.sched import ERR_MAX_QUEUE, Scheduler, SchedulerError, default_context, predict_memory
+
+GiB = 1 << 30
+
+
+class FakeModel:
+    def __init__(self, name, size=1 * GiB, adapters=()):
+        self.name = self.short_name = name
+        self.model_path = f"/blobs/{name}"
+        self.size = size
+        self.adapter_paths = list(adapters)
+        self.projector_paths = []
+        self.digest = name
+
+    def kv(self):
+        return {"general.architecture": "llama", "llama.block_count": 2, "llama.attention.head_count": 4,
+                "llama.attention.head_count_kv": 2, "llama.embedding_length": 256}
+
+    def capabilities(self):
+        return ["completion"]
+
+
+class FakeRunner:
+    def __init__(self, model, opts, num_parallel, gpus, fail=None):
+        if fail:
+            raise fail
+        self.model, self.opts, self.num_parallel, self.gpus = model, opts, num_parallel, gpus
+        self.closed = False
+        self.alive = True
+        self.n_ctx = opts["num_ctx"]
+
+    def ping(self):
+        return self.alive and not self.closed
+
+    def close(self):
+        self.closed = True
+
+    def memory(self):
+        return {"total": self.model.size, "vram": self.model.size if self.gpus else 0}
+
+
+def gpus(n=1, free=80 * GiB):
+    return [DeviceInfo(id=f"GPU-{i}", index=i, name="B200", compute_major=10, total_memory=180 * GiB, free_memory=free) for i in range(n)]
+
+
+def make(n_gpus=1, free=80 * GiB, **kw):
+    created = []
+
+    def factory(model, opts, num_parallel, use):
+        r = FakeRunner(model, opts, num_parallel, use)
+        created.append(r)
+        return r
+
+    s = Scheduler(new_runner_fn=kw.get("factory", factory), get_gpus_fn=lambda: gpus(n_gpus, free))
+    return s, created
+
+
+OPTS = {"num_ctx": 2048, "num_batch": 512, "num_gpu": -1, "main_gpu": None, "use_mmap": None, "num_thread": 0, "draft_num_predict": 4}
+
+
+def test_reuse_and_reload_predicate():
+    s, created = make()
+    m = FakeModel("a")
+    r1 = s.get_runner(m, dict(OPTS), 60)
+    r2 = s.get_runner(m, dict(OPTS), 60)
+    assert r1 is r2 and len(created) == 1 and r1.ref_count == 2
+    s.release(r1); s.release(r2)
+    # automatic values do not force a reload, explicit changes do
+    r3 = s.get_runner(m, {**OPTS, "num_ctx": 0, "num_gpu": -1}, 60)
+    assert r3 is r1
+    s.release(r3)
+    r4 = s.get_runner(m, {**OPTS, "num_ctx": 4096}, 60)
+    assert r4 is not r1 and created[0].closed and r4.options["num_ctx"] == 4096
+    s.release(r4)
+    r5 = s.get_runner(FakeModel("a", adapters=["/lora"]), {**OPTS, "num_ctx": 4096}, 60)
+    assert r5 is not r4
+    s.release(r5)
+    created[-1].alive = False                      # failed ping -> replaced
+    r6 = s.get_runner(FakeModel("a", adapters=["/lora"]), {**OPTS, "num_ctx": 4096}, 60)
+    assert r6 is not r5
+    s.unload_all()
+    assert all(r.closed for r in created)
+
+
+def test_keep_alive_timer_zero_and_forever():
+    s, created = make()
+    a = s.get_runner(FakeModel("a"), dict(OPTS), 0.15)
+    s.release(a)
+    assert not created[0].closed
+    time.sleep(0.5)
+    assert created[0].closed and s.ps() == []
+    b = s.get_runner(FakeModel("b"), dict(OPTS), 0)       # zero keep-alive: unloaded as soon as it is idle
+    assert not created[1].closed
+    s.release(b)
+    assert created[1].closed
+    c = s.get_runner(FakeModel("c"), dict(OPTS), math.inf)
+    s.release(c)
+    assert math.isinf(c.expires_at) and not created[2].closed
+    s.expire_runner(FakeModel("c"))
+    assert created[2].closed
+
+
+def test_expire_waits_for_inflight_request():
+    s, created = make()
+    m = FakeModel("a")
+    r = s.get_runner(m, dict(OPTS), 60)
+    s.expire_runner(m)
+    assert not created[0].closed                           # still referenced
+    s.release(r)
+    assert created[0].closed
+
+
+def test_max_loaded_models_evicts_idle_shortest_session(monkeypatch):
+    monkeypatch.setenv("OLLAMA_MAX_LOADED_MODELS", "2")
+    s, created = make()
+    a = s.get_runner(FakeModel("a"), dict(OPTS), 600); s.release(a)
+    b = s.get_runner(FakeModel("b"), dict(OPTS), 30); s.release(b)
+    c = s.get_runner(FakeModel("c"), dict(OPTS), 60); s.release(c)
+    names = sorted(r.model.name for r in s.ps())
+    assert names == ["a", "c"] and created[1].closed       # "b" had the shortest session
+    s.unload_all()
+
+
+def test_memory_eviction_and_multi_gpu_placement():
+    s, created = make(n_gpus=2, free=20 * GiB)
+    small = s.get_runner(FakeModel("small", 4 * GiB), dict(OPTS), 60)
+    assert len(created[0].gpus) == 1                       # fits 80 % of one GPU
+    s.release(small)
+    big = s.get_runner(FakeModel("big", int(39.5 * GiB)), dict(OPTS), 60)
+    assert len(created[1].gpus) == 2                       # does not fit one GPU: spread over the node
+    assert created[0].closed                               # and the idle small model was evicted to make room
+    s.release(big)
+    s.unload_all()
+
+
+def test_auto_context_shrinks_when_memory_is_short():
+    assert default_context(gpus(1)) == 262144 and default_context([]) == 4096
+    m = FakeModel("a", 1 * GiB)
+    assert predict_memory(m, 4096, 1) == 1 * GiB + 2 * 2 * 2 * 64 * 4096 * 2
+    s, created = make(n_gpus=1, free=int(1.6 * GiB))      # 256k tokens of KV do not fit, 32k do
+    r = s.get_runner(m, {**OPTS, "num_ctx": 0}, 60)
+    assert created[0].opts["num_ctx"] in (32768, 4096) and created[0].opts["num_ctx"] < 262144
+    s.release(r)
+    s.unload_all()
+
+
+def test_queue_limit_and_single_loader(monkeypatch):
+    monkeypatch.setenv("OLLAMA_MAX_QUEUE", "1")
+    gate = threading.Event()
+    started = threading.Event()
+
+    def slow_factory(model, opts, num_parallel, use):
+        started.set()
+        gate.wait(5)
+        return FakeRunner(model, opts, num_parallel, use)
+
+    s, _ = make(factory=slow_factory)
+    out = {}
+    t = threading.Thread(target=lambda: out.setdefault("a", s.get_runner(FakeModel("a"), dict(OPTS), 60)))
+    t.start()
+    assert started.wait(5)
+    with pytest.raises(SchedulerError) as e:              # queue of one is taken by the loading request
+        s.get_runner(FakeModel("b"), dict(OPTS), 60)
+    assert e.value.status == 503 and str(e.value) == ERR_MAX_QUEUE
+    gate.set()
+    t.join(5)
+    assert out["a"].ref_count == 1
+    s.unload_all()
+
+
+def test_load_failure_and_oom_retry():
+    calls = []
+
+    def factory(model, opts, num_parallel, use):
+        calls.append(opts["num_ctx"])
+        if len(calls) == 1:
+            raise MemoryError("CUDA out of memory")
+        return FakeRunner(model, opts, num_parallel, use)
+
+    s, _ = make(factory=factory)
+    r = s.get_runner(FakeModel("a"), {**OPTS, "num_ctx": 0}, 60)     # automatic context: retried smaller after the OOM
+    assert len(calls) == 2 and calls[1] < calls[0]
+    s.release(r)
+
+    def broken(model, opts, num_parallel, use):
+        raise RuntimeError("bad file")
+
+    s2, _ = make(factory=broken)
+    with pytest.raises(SchedulerError) as e:
+        s2.get_runner(FakeModel("a"), dict(OPTS), 60)
+    assert e.value.status == 500 and "bad file" in str(e.value)

@@ -1,0 +1,179 @@
+"""Prompt templates, output parsers, tokenizers and the grammar engine."""
+import pytest
+
+from ollama_b200.engine.grammar import JSON_GRAMMAR, Grammar, GrammarError, GrammarMatcher, grammar_for_format, json_schema_to_gbnf, parse_gbnf
+from ollama_b200.text import harmony
+from ollama_b200.text.gotemplate import GoTemplate, TemplateError
+from ollama_b200.text.template import JinjaChatTemplate, Template, collate
+from ollama_b200.text.thinking import ThinkingParser, infer_tags, strip_thinking
+from ollama_b200.text.tokenizer import BPETokenizer, SPMTokenizer, _byte_to_unicode, tokenizer_from_gguf
+from ollama_b200.text.tools import ToolParser, infer_tag
+
+CHATML = """{{- range $i, $_ := .Messages }}{{- $last := eq (len (slice $.Messages $i)) 1 }}<|im_start|>{{ .Role }}
+{{ .Content }}{{ if not $last }}<|im_end|>
+{{ end }}{{ if and $last (ne .Role "assistant") }}<|im_end|>
+<|im_start|>assistant
+{{ end }}{{- end }}"""
+
+
+def test_go_template_language():
+    t = GoTemplate('{{ if and .A (not .B) }}x{{ else if .C }}y{{ else }}z{{ end }}|{{ range $i, $v := .L }}{{ $i }}={{ $v }},{{ end }}'
+                   '|{{ with .M }}{{ .k }}{{ end }}|{{ printf "%s-%d" .S 7 }}|{{ .Missing }}|{{ len .L }}|{{ index .L 1 }}|{{ json .M }}')
+    out = t.render({"A": True, "B": False, "C": True, "L": ["p", "q"], "M": {"k": "v"}, "S": "s"})
+    assert out == 'x|0=p,1=q,|v|s-7||2|q|{"k":"v"}'
+    assert GoTemplate("a  {{- 1 }}  {{ 2 -}}  b").render({}) == "a1  2b"
+    assert GoTemplate("{{/* c */}}x{{ range .L }}{{ if eq . 2 }}{{ break }}{{ end }}{{ . }}{{ end }}").render({"L": [1, 2, 3]}) == "x1"
+    assert GoTemplate("{{ $x := 1 }}{{ if true }}{{ $x = 2 }}{{ end }}{{ $x }}").render({}) == "2"
+    assert GoTemplate("{{ range .L }}a{{ else }}empty{{ end }}").render({"L": []}) == "empty"
+    with pytest.raises(TemplateError):
+        GoTemplate("{{ if .A }}x")
+    with pytest.raises(TemplateError):
+        GoTemplate("{{ nosuchfunc 1 }}").render({})
+
+
+def test_template_modes_and_collate():
+    legacy = Template("{{ if .System }}<|system|>{{ .System }}<|end|>{{ end }}{{ if .Prompt }}<|user|>{{ .Prompt }}<|end|>{{ end }}"
+                      "<|assistant|>{{ .Response }}<|end|>")
+    msgs = [{"role": "system", "content": "S"}, {"role": "user", "content": "hi"}, {"role": "assistant", "content": "yo"},
+            {"role": "user", "content": "again"}]
+    assert legacy.execute(messages=msgs) == "<|system|>S<|end|><|user|>hi<|end|><|assistant|>yo<|end|><|user|>again<|end|><|assistant|>"
+    # an assistant message at the end is a prefill: the prompt ends with it
+    assert legacy.execute(messages=msgs[:2] + [{"role": "assistant", "content": "par"}]).endswith("<|assistant|>par")
+    chat = Template(CHATML)
+    assert chat.execute(messages=msgs[1:]) == ("<|im_start|>user\nhi<|im_end|>\n<|im_start|>assistant\nyo<|im_end|>\n"
+                                               "<|im_start|>user\nagain<|im_end|>\n<|im_start|>assistant\n")
+    assert Template("{{ .Prompt }}").t.src.endswith("{{ .Response }}")      # response slot appended when absent
+    assert Template("<PRE> {{ .Prompt }} <SUF>{{ .Suffix }} <MID>").execute(prompt="a", suffix="b") == "<PRE> a <SUF>b <MID>"
+    system, merged = collate([{"role": "system", "content": "a"}, {"role": "user", "content": "1"}, {"role": "user", "content": "2"},
+                              {"role": "system", "content": "b"}])
+    assert system == "a\n\nb" and merged[1]["content"] == "1\n\n2"
+    tools = Template("{{ if .Tools }}T:{{ .Tools }}{{ end }}{{ range .Messages }}{{ range .ToolCalls }}[{{ .Function.Name }} {{ .Function.Arguments }}]{{ end }}{{ end }}")
+    out = tools.execute(messages=[{"role": "assistant", "tool_calls": [{"function": {"name": "f", "arguments": {"x": 1}}}]}],
+                        tools=[{"type": "function", "function": {"name": "f", "parameters": {}}}])
+    assert '"name":"f"' in out and '[f {"x":1}]' in out
+
+
+def test_jinja_chat_template():
+    t = JinjaChatTemplate("{{ bos_token }}{% for m in messages %}<{{ m.role }}>{{ m.content }}{% endfor %}"
+                          "{% if add_generation_prompt %}<assistant>{% if enable_thinking %}<think>{% endif %}{% endif %}", bos_token="<s>")
+    assert t.render([{"role": "user", "content": "hi"}], enable_thinking=True) == "<s><user>hi<assistant><think>"
+    with pytest.raises(TemplateError):
+        JinjaChatTemplate("{{ raise_exception('no') }}").render([])
+
+
+def test_thinking_parser_streaming():
+    p = ThinkingParser()
+    chunks = ["  <th", "ink>  a", "bc </th", "ink>\n\n he", "llo"]
+    got = [p.add(c) for c in chunks]
+    assert "".join(t for t, _ in got) == "abc " and "".join(c for _, c in got) == "hello"
+    p = ThinkingParser()
+    assert p.add("no tags here") == ("", "no tags here")
+    p = ThinkingParser(started=True)                       # the prompt already opened the block
+    assert p.add("reason</think>answer") == ("reason", "answer")
+    assert infer_tags("{{ if .Thinking }}<think>{{ .Thinking }}</think>{{ end }}{{ .Content }}") == ("<think>", "</think>")
+    assert strip_thinking("<think>x</think>\n\nfinal") == "final"
+
+
+def test_tool_parser():
+    tools = [{"type": "function", "function": {"name": "get_weather", "parameters": {"properties": {"city": {}}}}}]
+    p = ToolParser(tools, "<tool_call>")
+    out = [p.add(c) for c in ["Sure <tool", '_call>{"name":"get_weather",', '"arguments":{"city":"Paris"}}</tool_call>']]
+    calls = [c for cs, _ in out for c in cs]
+    assert "".join(t for _, t in out).strip() == "Sure" and calls[0]["function"] == {"index": 0, "name": "get_weather", "arguments": {"city": "Paris"}}
+    p = ToolParser(tools, "{")
+    calls, text = p.add('{"name": "get_weather", "parameters": {"city": "Oslo"}}')
+    assert calls and calls[0]["function"]["arguments"] == {"city": "Oslo"} and text == ""
+    p = ToolParser(tools, "{")
+    calls, text = p.add('The set {1, 2} is small')
+    assert not calls and text == "The set {1, 2} is small"
+    p = ToolParser(tools, "<tool_call>")
+    calls, text = p.add('<tool_call>{"name": "unknown_tool", "arguments": {}}')
+    assert not calls and "unknown_tool" in text
+    assert infer_tag("{{ range .ToolCalls }}x{{ end }}") in ("{", "x")
+    assert infer_tag('{{ if .ToolCalls }}<tool_call>\n{{ range .ToolCalls }}{"name"...{{ end }}{{ end }}') == "<tool_call>"
+
+
+def test_harmony_parser_and_renderer():
+    h = harmony.HarmonyParser()
+    parts = ["<|channel|>analysis<|message|>think", "ing<|end|><|start|>assistant<|channel|>commentary to=functions.get_w ",
+             '<|constrain|>json<|message|>{"a":1}<|call|>', "<|start|>assistant<|channel|>final<|mess", "age|>Hi!<|return|>"]
+    th, ct, calls = "", "", []
+    for p in parts:
+        a, b, c = h.add(p)
+        th, ct, calls = th + a, ct + b, calls + c
+    assert th == "thinking" and ct == "Hi!" and calls[0]["function"]["name"] == "get_w" and calls[0]["function"]["arguments"] == {"a": 1}
+    names = harmony.FunctionNameMap()
+    assert names.convert("get-weather now") == "get_weather_now" and names.original("get_weather_now") == "get-weather now"
+    assert names.convert("get_weather_now") == "get_weather_now_2"
+    tools = [{"type": "function", "function": {"name": "get-w", "description": "d", "parameters": {
+        "type": "object", "properties": {"city": {"type": "string"}, "n": {"type": "integer"}}, "required": ["city"]}}}]
+    p = harmony.render_prompt([{"role": "system", "content": "be nice"}, {"role": "user", "content": "hi"},
+                               {"role": "assistant", "content": "", "tool_calls": [{"function": {"name": "get-w", "arguments": {"city": "x"}}}]},
+                               {"role": "tool", "tool_name": "get-w", "content": "sunny"}], tools, "high", today="2025-01-01")
+    assert p.endswith("<|start|>assistant") and "Reasoning: high" in p and "type get_w = (_: {" in p and "city: string," in p and "n?: number," in p
+    assert "<|start|>developer<|message|># Instructions\n\nbe nice" in p and 'to=functions.get_w <|constrain|>json<|message|>{"city":"x"}<|call|>' in p
+    assert "<|start|>functions.get_w to=assistant<|channel|>commentary<|message|>sunny<|end|>" in p
+
+
+def _bpe():
+    b2u = _byte_to_unicode()
+    tokens = [b2u[i] for i in range(256)] + ["he", "ll", "hell", "hello", "Ġw", "Ġwo", "Ġwor", "Ġworld", "<|eot|>", "<|eot|>x"]
+    types = [1] * (len(tokens) - 2) + [3, 4]
+    merges = ["h e", "l l", "he ll", "hell o", "Ġ w", "Ġw o", "Ġwo r", "Ġwor l", "Ġworl d"]
+    tokens.insert(-2, "Ġworl")
+    types.insert(-2, 1)
+    return BPETokenizer(tokens, types, merges, "llama-bpe", bos=-1, eos=len(tokens) - 2)
+
+
+def test_bpe_tokenizer():
+    tk = _bpe()
+    ids = tk.encode("hello world")
+    assert [tk.tokens[i] for i in ids] == ["hello", "Ġworld"] and tk.decode(ids) == "hello world"
+    ids = tk.encode("hello<|eot|>x!")                       # the longer special token wins
+    assert tk.tokens[ids[1]] == "<|eot|>x" and tk.decode(ids) == "hello<|eot|>x!"
+    assert tk.tokens[tk.encode("a<|eot|>", parse_special=True)[1]] == "<|eot|>"
+    assert len(tk.encode("<|eot|>", parse_special=False)) > 1
+    assert tk.decode(tk.encode("héllo ☃ 123456")) == "héllo ☃ 123456"
+    assert tk.is_eog(tk.vocab["<|eot|>"])
+
+
+def test_spm_tokenizer_and_gguf_selection():
+    tokens = ["<unk>", "<s>", "</s>"] + [f"<0x{i:02X}>" for i in range(256)] + ["▁", "h", "e", "l", "o", "▁h", "he", "ll", "▁he", "llo", "▁hello", "w"]
+    types = [2, 3, 3] + [6] * 256 + [1] * 12
+    scores = [0.0] * 259 + [-1, -2, -2, -2, -2, -3, -4, -5, -6, -7, -0.5, -2]
+    kv = {"tokenizer.ggml.model": "llama", "tokenizer.ggml.tokens": tokens, "tokenizer.ggml.token_type": types, "tokenizer.ggml.scores": scores,
+          "tokenizer.ggml.bos_token_id": 1, "tokenizer.ggml.eos_token_id": 2, "tokenizer.ggml.unknown_token_id": 0}
+    tk = tokenizer_from_gguf(kv)
+    assert isinstance(tk, SPMTokenizer)
+    ids = tk.encode("hello")
+    assert ids[0] == 1 and tk.tokens[ids[1]] == "▁hello" and tk.decode(ids[1:]) == " hello"
+    ids = tk.encode("hé", add_special=False)                # byte fallback for the unknown code point
+    assert tk.decode(ids) == " hé" and any(tk.types[i] == 6 for i in ids)
+
+
+def test_grammar_engine():
+    m = GrammarMatcher(parse_gbnf(JSON_GRAMMAR))
+    assert m.accepts('{"a": [1, 2.5e3, true, null, "x\\n"]}') and not m.accepts('{"a": }') and not m.accepts("[1]")
+    g = parse_gbnf('root ::= "ab" [0-9]{2,3} ("x" | "y")? # tail\n')
+    m = GrammarMatcher(g)
+    assert m.accepts("ab12") and m.accepts("ab123y") and not m.accepts("ab1x") and not m.accepts("ab1234")
+    with pytest.raises(GrammarError):
+        parse_gbnf("root ::= missing")
+    schema = {"type": "object", "properties": {"name": {"type": "string"}, "age": {"type": "integer"},
+                                               "tags": {"type": "array", "items": {"type": "string"}}, "k": {"enum": ["a", "b"]}},
+              "required": ["name", "age"]}
+    m = GrammarMatcher(parse_gbnf(json_schema_to_gbnf(schema)))
+    assert m.accepts('{"name": "bob", "age": 3}') and m.accepts('{"name":"bob","age":3,"tags":["x","y"],"k":"a"}')
+    assert not m.accepts('{"age": 3}') and not m.accepts('{"name":"b","age":"3"}')
+    m.advance('{"name":"bob","age":3}')
+    assert m.can_end()
+    assert grammar_for_format(None) is None and grammar_for_format("json") == JSON_GRAMMAR and "root" in grammar_for_format({"type": "object"})
+    with pytest.raises(GrammarError):
+        grammar_for_format("yaml")
+    tk = _bpe()
+    gr = Grammar('root ::= "hello" " world"?', tk)
+    assert gr.allows(tk.vocab["hello"]) and not gr.allows(tk.vocab["Ġworld"])
+    gr.accept(tk.vocab["hello"])
+    assert gr.allows(tk.vocab["Ġworld"]) and gr.allows(tk.eos) and not gr.done()
+    gr.accept(tk.vocab["Ġworld"])
+    assert gr.done()
