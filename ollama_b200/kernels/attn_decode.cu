@@ -228,3 +228,61 @@ B2_API int b2_attn_decode(const AttnDecodeArgs* a, const AttnCombineArgs* c, int
     void* args2[] = {&cc};
     return (int)launch1((const void*)attn_combine_kernel, dim3(a->n_heads, nb), dim3(hd), args2, st, pdl);
 }
+
+// ---------------------------------------------------------------------------------------------
+// Allocation-free entry point (declared in no_alloc.h)
+// ---------------------------------------------------------------------------------------------
+#include "no_alloc.h"
+
+#include <mutex>
+
+// The split-K partials live in these two arrays instead of caller-provided scratch.  They belong to the
+// library image: every GPU that loads the library carries them (about 8.5 MB) until the process exits.
+static __device__ __align__(256) float g_na_part_acc[B2_NA_MAX_ACC_FLOATS];
+static __device__ __align__(256) float2 g_na_part_ml[B2_NA_MAX_ML_ENTRIES];
+
+// In host code the two names above are only handles for the runtime; the device addresses that a kernel
+// can dereference are looked up once per device and kept here.
+static constexpr int kNaMaxDevices = 64;
+static float* s_na_acc[kNaMaxDevices];
+static float2* s_na_ml[kNaMaxDevices];
+static std::mutex s_na_mutex;
+
+B2_API int b2_attn_decode_noalloc(const AttnDecodeArgs* a, const AttnCombineArgs* c, int nb, int hd, cudaStream_t st) {
+    if (!a || !c || nb < 1 || a->n_heads < 1 || a->n_kv_heads < 1 || a->n_splits < 1 || hd < 1) return (int)cudaErrorInvalidValue;
+    const long long entries = (long long)nb * a->n_heads * a->n_splits;
+    if (entries > B2_NA_MAX_ML_ENTRIES || entries * hd > B2_NA_MAX_ACC_FLOATS) return B2_NA_ERR_TOO_LARGE;
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return (int)e;
+    if (dev < 0 || dev >= kNaMaxDevices) return (int)cudaErrorInvalidDevice;
+    float* acc;
+    float2* ml;
+    {
+        std::lock_guard<std::mutex> lock(s_na_mutex);
+        if (!s_na_acc[dev]) {      // first call on this device (the device is current): resolve the symbols
+            void* p0 = nullptr;
+            void* p1 = nullptr;
+            e = cudaGetSymbolAddress(&p0, g_na_part_acc);
+            if (e != cudaSuccess) return (int)e;
+            e = cudaGetSymbolAddress(&p1, g_na_part_ml);
+            if (e != cudaSuccess) return (int)e;
+            s_na_acc[dev] = (float*)p0;
+            s_na_ml[dev] = (float2*)p1;
+        }
+        acc = s_na_acc[dev];
+        ml = s_na_ml[dev];
+    }
+    AttnDecodeArgs da = *a;
+    AttnCombineArgs ca = *c;
+    da.part_acc = acc;
+    da.part_ml = ml;
+    ca.part_acc = acc;
+    ca.part_ml = ml;
+    ca.n_heads = a->n_heads;
+    ca.n_splits = a->n_splits;
+    ca.hd = hd;
+    // Every (sequence, head, split) slot that the combine step reads is written by the attention kernel of
+    // the same call -- empty splits store a neutral partial -- so nothing has to be cleared between calls.
+    return b2_attn_decode(&da, &ca, nb, hd, 0, st);
+}
