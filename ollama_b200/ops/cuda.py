@@ -338,3 +338,24 @@ def attn_decode(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, p
     c = AttnCombineArgs(ptr(scratch[0]), ptr(scratch[1]), ptr(sinks), H, n_splits, hd, ptr(out), ptr(oq), ptr(ods))
     _check(lib().b2_attn_decode(C.byref(a), C.byref(c), nb, hd, int(pdl), stream()), "attn_decode")
     return out, (QAct(oq, ods, out) if quant_out else None)
+
+
+def gemm_bf16(a: torch.Tensor, b: torch.Tensor, bias: torch.Tensor | None = None, out: torch.Tensor | None = None,
+              accumulate: bool = False) -> torch.Tensor:
+    """out[m, n] (+)= a[m, k] @ b[n, k]^T + bias on the tcgen05 tensor-core kernel (bf16 operands, fp32 result)."""
+    m, k = a.shape
+    n = b.shape[0]
+    if a.dtype != torch.bfloat16 or b.dtype != torch.bfloat16 or b.shape[1] != k:
+        raise ValueError("gemm_bf16 needs bf16 operands [m, k] and [n, k]")
+    a, b = a.contiguous(), b.contiguous()
+    if out is None:
+        out = torch.empty(m, n, device=a.device, dtype=torch.float32)
+    f = lib().b2_gemm_bf16
+    f.argtypes = [C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_void_p, C.c_int, C.c_void_p, C.c_int, C.c_void_p]
+    _check(f(ptr(a), ptr(b), m, n, k, ptr(out), out.stride(0), ptr(bias), int(accumulate), stream()), "gemm_bf16")
+    return out
+
+
+def gemm_status() -> int:
+    """0 = ok; 1 = a bounded wait inside the tensor-core GEMM expired."""
+    return int(lib().b2_gemm_status())

@@ -233,3 +233,21 @@ def test_gemv_model_shapes(t, nb):
         xr = _quant_act_ref(x.cpu()) if dw.quant_input else x.cpu()
         ref = xr @ wf.t() + bias
         assert torch.allclose(y.cpu(), ref, atol=2e-3 * ref.abs().max().item(), rtol=1e-3)
+
+
+@pytest.mark.parametrize("m,n,k", [(128, 256, 64), (128, 128, 512), (512, 4096, 4096), (300, 200, 1000), (64, 64, 72), (1, 1024, 4096)])
+def test_gemm_bf16_tensor_core(m, n, k):
+    """tcgen05 GEMM against an fp32 matmul of the same bf16 operands."""
+    K = _K()
+    g = torch.Generator().manual_seed(m + n + k)
+    a = (torch.randn(m, k, generator=g) * 0.5).to(torch.bfloat16).cuda()
+    b = (torch.randn(n, k, generator=g) * 0.5).to(torch.bfloat16).cuda()
+    bias = torch.randn(n, generator=g).cuda()
+    ref = a.float() @ b.float().t() + bias
+    out = K.gemm_bf16(a, b, bias)
+    torch.cuda.synchronize()
+    assert K.gemm_status() == 0
+    assert torch.allclose(out, ref, atol=1e-2 + 1e-3 * ref.abs().max().item(), rtol=1e-3), (out - ref).abs().max()
+    acc = torch.ones(m, n, device="cuda")
+    K.gemm_bf16(a, b, None, out=acc, accumulate=True)
+    assert torch.allclose(acc, ref - bias + 1, atol=1e-2 + 1e-3 * ref.abs().max().item(), rtol=1e-3)
