@@ -357,5 +357,29 @@ def gemm_bf16(a: torch.Tensor, b: torch.Tensor, bias: torch.Tensor | None = None
 
 
 def gemm_status() -> int:
-    """0 = ok; 1 = a bounded wait inside the tensor-core GEMM expired."""
-    return int(lib().b2_gemm_status())
+    """0 = ok; 1 = a bounded wait inside a tensor-core GEMM expired."""
+    return int(lib().b2_gemm_status()) | int(lib().b2_gemm_q_status())
+
+
+GEMM_Q_TYPES = {WT_Q4_K, WT_Q6_K, WT_Q8_0, WT_BF16, WT_F16}
+
+
+def gemm_q_supported(w: DevWeight) -> bool:
+    if w.wtype not in GEMM_Q_TYPES or w.n % 4:
+        return False
+    return w.k % (256 if w.wtype in (WT_Q4_K, WT_Q6_K) else 64) == 0
+
+
+def gemm_q(x: torch.Tensor, w: DevWeight, out: torch.Tensor | None = None, accumulate: bool = False, out_off: int = 0) -> torch.Tensor:
+    """out[:, out_off:out_off+n] (+)= x[m, k] (bf16) @ dequant(w)[n, k]^T + bias, weights expanded inside the tensor-core kernel."""
+    m, k = x.shape
+    if x.dtype != torch.bfloat16 or k != w.k:
+        raise ValueError("gemm_q needs a bf16 activation matrix [m, k] matching the weight")
+    x = x.contiguous()
+    if out is None:
+        out = torch.empty(m, w.n, device=x.device, dtype=torch.float32)
+    d = w.desc(out_off=out_off)
+    f = lib().b2_gemm_q
+    f.argtypes = [C.c_void_p, C.c_int, C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_void_p]
+    _check(f(ptr(x), m, C.addressof(d), ptr(out), out.stride(0), int(accumulate), stream()), "gemm_q")
+    return out

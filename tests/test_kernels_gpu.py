@@ -251,3 +251,23 @@ def test_gemm_bf16_tensor_core(m, n, k):
     acc = torch.ones(m, n, device="cuda")
     K.gemm_bf16(a, b, None, out=acc, accumulate=True)
     assert torch.allclose(acc, ref - bias + 1, atol=1e-2 + 1e-3 * ref.abs().max().item(), rtol=1e-3)
+
+
+@pytest.mark.parametrize("t", [GGMLType.Q4_K, GGMLType.Q6_K, GGMLType.Q8_0, GGMLType.BF16, GGMLType.F16])
+@pytest.mark.parametrize("m,n,k", [(128, 128, 256), (512, 1024, 4096), (77, 200, 512), (1, 128, 1024)])
+def test_gemm_q_dequant_fused(t, m, n, k):
+    """Dequant-fused tcgen05 GEMM: the reference multiplies the same bf16 activations with the bf16-rounded decoded weights."""
+    K = _K()
+    qw, bias = _weight(t, n, k, seed=m + n, bias=True)
+    dw = K.repack(qw, "cuda", bias=bias)
+    x = (torch.randn(m, k, generator=torch.Generator().manual_seed(k)) * 0.5).to(torch.bfloat16).cuda()
+    ref = x.float().cpu() @ qw.dequant().to(torch.bfloat16).float().t() + bias
+    out = torch.zeros(m, n + 8, device="cuda")
+    K.gemm_q(x, dw, out=out, out_off=4)
+    torch.cuda.synchronize()
+    assert K.gemm_status() == 0
+    tol = 1e-3 + 2e-3 * ref.abs().max().item()
+    assert torch.allclose(out[:, 4:4 + n].cpu(), ref, atol=tol, rtol=2e-3), (out[:, 4:4 + n].cpu() - ref).abs().max()
+    assert out[:, :4].abs().max() == 0 and out[:, 4 + n:].abs().max() == 0      # neighbours of the output window stay untouched
+    K.gemm_q(x, dw, out=out, accumulate=True, out_off=4)
+    assert torch.allclose(out[:, 4:4 + n].cpu(), 2 * ref, atol=2 * tol, rtol=2e-3)
