@@ -46,7 +46,7 @@ class B200Backend:
     name = "b200"
 
     def __init__(self, g: GGUFFile | None, device: str = "cuda", opts=None, cfg: ModelConfig | None = None,
-                 tensors: dict[str, QWeight] | None = None, keep_bf16: bool = True):
+                 tensors: dict[str, QWeight] | None = None, keep_bf16: bool = False):
         """Load from an opened GGUF, or from ``cfg`` + an iterable source of :class:`QWeight` (synthetic checkpoints)."""
         self.device = torch.device(device if device != "cuda" else f"cuda:{torch.cuda.current_device()}")
         self.cfg = cfg if cfg is not None else config_from_gguf(g)
@@ -82,14 +82,14 @@ class B200Backend:
 
         def mat(name) -> K.DevWeight:
             w = K.repack(get(name + ".weight"), dev, bias=vec(name + ".bias"))
-            if self.keep_bf16:
-                w.bf16 = K.dequant_to_bf16(w)
+            if self.keep_bf16 or not K.gemm_q_supported(w):
+                w.bf16 = K.dequant_to_bf16(w)     # encodings the fused GEMM cannot expand keep a 16-bit copy for prefill
             return w
 
         self.embd = K.repack(get("token_embd.weight"), dev)
         self.out_norm = vec("output_norm.weight")
         self.head = mat("output") if has("output.weight") else self.embd
-        if self.keep_bf16 and not hasattr(self.head, "bf16"):
+        if (self.keep_bf16 or not K.gemm_q_supported(self.head)) and not hasattr(self.head, "bf16"):
             self.head.bf16 = K.dequant_to_bf16(self.head)
         self.layers: list[_Layer] = []
         for i in range(c.n_layers):
@@ -107,7 +107,7 @@ class B200Backend:
                 L.gu = K.interleave_rows(K.to_f16(L.gate), K.to_f16(L.up))
             else:
                 L.gu = K.interleave_rows(L.gate, L.up)
-            if self.keep_bf16:      # prefill reads the bf16 copies; the separate quantised planes are no longer needed
+            if K.gemm_q_supported(L.gu) or hasattr(L.gate, "bf16"):      # the interleaved matrix (or the 16-bit copies) serve every path
                 L.gate.planes, L.up.planes = [], []
             L.sinks = vec(p + "attn_sinks.weight")
             L.swa = c.layer_is_swa(i)
@@ -315,13 +315,19 @@ class B200Backend:
         return out
 
     # -- prefill --------------------------------------------------------------------------------------
-    def _mm(self, x_bf16: torch.Tensor, w: K.DevWeight) -> torch.Tensor:
+    def _mm(self, x_bf16: torch.Tensor, w: K.DevWeight, out: torch.Tensor | None = None, out_off: int = 0) -> torch.Tensor:
+        """x @ W^T + bias for a prefill chunk: the dequantisation-fused tcgen05 GEMM, or a 16-bit copy for other encodings."""
+        if K.gemm_q_supported(w) and not self.keep_bf16:
+            self.kernel_launches += 1
+            return K.gemm_q(x_bf16, w, out=out, out_off=out_off)
         wb = getattr(w, "bf16", None)
         if wb is None:
             wb = K.dequant_to_bf16(w)
-        y = (x_bf16 @ wb.t()).float()
-        if w.bias is not None:
-            y = y + w.bias
+        y = K.gemm_bf16(x_bf16, wb, w.bias)
+        self.kernel_launches += 1
+        if out is not None:
+            out[:, out_off:out_off + w.n] = y
+            return out
         return y
 
     @torch.no_grad()
@@ -341,7 +347,10 @@ class B200Backend:
         group = c.n_heads // c.n_kv_heads
         for i, L in enumerate(self.layers):
             h = R.rmsnorm(x, L.attn_norm, c.norm_eps).to(torch.bfloat16)
-            qkv = torch.cat([self._mm(h, L.wq), self._mm(h, L.wk), self._mm(h, L.wv)], 1).contiguous()
+            qkv = torch.empty(T, (c.n_heads + 2 * c.n_kv_heads) * c.head_dim, device=dev, dtype=torch.float32)
+            self._mm(h, L.wq, qkv, 0)
+            self._mm(h, L.wk, qkv, c.q_dim)
+            self._mm(h, L.wv, qkv, c.q_dim + c.kv_dim)
             local = L.swa and c.rope_base_local > 0
             q = K.rope_kv(qkv, pos, slots, self.inv_freq_local if local else self.inv_freq, n_heads=c.n_heads, n_kv_heads=c.n_kv_heads,
                           hd=c.head_dim, n_rot=c.rope_dim, neox=c.rope_style == "neox", mscale=1.0 if local else self.mscale,
@@ -362,7 +371,12 @@ class B200Backend:
                 o = R.rmsnorm(o, L.post_attn_norm, c.norm_eps)
             x = x + o
             h = R.rmsnorm(x, L.ffn_norm, c.norm_eps).to(torch.bfloat16)
-            f = R.glu(self._mm(h, L.gate), self._mm(h, L.up), c.act, c.swiglu_alpha, c.swiglu_limit)
+            if L.gate.planes or hasattr(L.gate, "bf16"):
+                g_, u_ = self._mm(h, L.gate), self._mm(h, L.up)
+            else:
+                gu = self._mm(h, L.gu)                      # rows interleaved: even = gate, odd = up
+                g_, u_ = gu[:, 0::2], gu[:, 1::2]
+            f = R.glu(g_, u_, c.act, c.swiglu_alpha, c.swiglu_limit)
             f = self._mm(f.to(torch.bfloat16), L.down)
             if c.sandwich_norm:
                 f = R.rmsnorm(f, L.post_ffw_norm, c.norm_eps)

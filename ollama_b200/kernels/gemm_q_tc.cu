@@ -2,14 +2,18 @@
 //   out[M, N] (+)= X[M, K] (bf16) . W[N, K]^T (GGUF-quantised, plane layout) + bias
 //
 // The activation tile (A operand) arrives by TMA as in gemm_tc.cu.  The weight tile (B operand) never
-// exists in global memory in 16-bit form: four producer warps read the quantised planes of 128 weight
-// rows x 64 columns, expand them to bf16 in registers and write them into the stage buffer in exactly
-// the 128-byte-swizzled K-major layout that the tcgen05 shared-memory descriptor expects (16-byte chunk
-// c of row r lives at chunk c ^ (r & 7)); a proxy fence publishes those generic-proxy writes to the
-// tensor core.  One elected thread issues tcgen05.mma (M = 128 tokens, N = 128 weight rows) into a TMEM
-// accumulator; the producer warps turn into epilogue warps once their last stage is written.  Two CTAs
-// fit on an SM (96 KB of stages, 128 TMEM columns each), so one CTA's epilogue overlaps the other's
-// main loop.  All mbarrier waits are bounded (KS_TIMEOUT in the status word on expiry).
+// exists in global memory in 16-bit form: eight producer warps read the quantised planes of 128 weight
+// rows x 64 columns (one thread = 32 columns of one row), expand them to bf16 in registers and write
+// them into the stage buffer in exactly the 128-byte-swizzled K-major layout that the tcgen05
+// shared-memory descriptor expects (16-byte chunk c of row r lives at chunk c ^ (r & 7)); a proxy
+// fence publishes those generic-proxy writes to the tensor core.  The raw bytes of the next K block
+// are requested before the current one is expanded, so global latency stays off the critical path.
+// 4- and 6-bit codes become bf16 with one byte-permute and one packed FMA per pair: the code q is
+// dropped into the mantissa of 128.0 (bf16 0x43qq = 128 + q, exact for q < 128) and
+// w = (128 + q) * scale + (offset - 128 * scale) is a single fma.rn.bf16x2.
+// One elected thread issues tcgen05.mma (M = 128 tokens, N = 128 weight rows) into a TMEM accumulator;
+// four of the producer warps drain it once their last stage is written.  All mbarrier waits are
+// bounded (KS_TIMEOUT in the status word on expiry).
 //
 // This is the counterpart of ggml-cuda's mmq kernels (in-kernel dequantisation feeding mma.sync) and of
 // its dequantise-then-cuBLAS path, redone for tcgen05 / TMEM.
@@ -24,7 +28,8 @@ constexpr int BN = 128;          // weight rows per CTA (MMA N)
 constexpr int STAGES = 3;
 constexpr int A_BYTES = BM * BK * 2, B_BYTES = BN * BK * 2, STAGE_BYTES = A_BYTES + B_BYTES;
 constexpr int SMEM_TOTAL = STAGES * STAGE_BYTES + 1024 + 256;
-constexpr int DEQ_WARPS = 4;
+constexpr int DEQ_WARPS = 8;
+constexpr int THREADS = (2 + DEQ_WARPS) * 32;
 
 struct QGemmParams {
     WDesc w;                // quantised weight [n][k]
@@ -34,124 +39,152 @@ struct QGemmParams {
     int accumulate;
 };
 
+// Raw bytes of 32 columns of one weight row (what a producer thread fetches per K block).
+struct Raw {
+    uint4 a, b, c, d;
+    uint32_t s0, s1;
+};
+
 __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
     const __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
     return *reinterpret_cast<const uint32_t*>(&v);
 }
+__device__ __forceinline__ uint32_t bf16x2_fma(uint32_t a, uint32_t b, uint32_t c) {
+    uint32_t d;
+    asm("fma.rn.bf16x2 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(c));
+    return d;
+}
+__device__ __forceinline__ uint32_t bf16x2_splat(float v) { return pack_bf16(v, v); }
 
-// Store 64 consecutive K values of one weight row (already bf16-packed, 32 words) into the swizzled stage tile.
-__device__ __forceinline__ void store_row_swizzled(uint8_t* tile, int r, const uint32_t (&w)[32]) {
-    uint8_t* row = tile + r * 128;
-#pragma unroll
-    for (int c = 0; c < 8; c++) {
-        const uint4 v = make_uint4(w[4 * c], w[4 * c + 1], w[4 * c + 2], w[4 * c + 3]);
-        *reinterpret_cast<uint4*>(row + ((c ^ (r & 7)) << 4)) = v;
-    }
+// Four byte-sized codes (one per byte of `codes`) -> two bf16x2 words of scale * code + offset.
+__device__ __forceinline__ void expand4(uint32_t codes, uint32_t scale2, uint32_t off2, uint32_t& w01, uint32_t& w23) {
+    const uint32_t m01 = __byte_perm(codes, 0x43434343u, 0x4140);      // {code0, 0x43, code1, 0x43} = bf16 (128 + code0), (128 + code1)
+    const uint32_t m23 = __byte_perm(codes, 0x43434343u, 0x4342);
+    w01 = bf16x2_fma(m01, scale2, off2);
+    w23 = bf16x2_fma(m23, scale2, off2);
 }
 
-// Expand columns [64 kb, 64 kb + 64) of weight row `row` to bf16 words.
-__device__ __forceinline__ void dequant64(const WDesc& w, int row, int kb, uint32_t (&o)[32]) {
+// half h (0/1) of K block kb of row `row`: columns 64 kb + 32 h .. + 31
+__device__ __forceinline__ void load_raw(const WDesc& w, int row, int kb, int h, Raw& r) {
     const int K = w.k;
     switch (w.type) {
         case WT_Q4_K: {
             const uint8_t* qp = (const uint8_t*)w.p0 + (size_t)row * (K >> 1) + kb * 32;
-            const uint4 qa = ldg16(qp), qb = ldg16(qp + 16);
-            const uint32_t sm = __ldg((const uint32_t*)((const uint8_t*)w.p1 + (size_t)row * (K >> 4) + kb * 4));
-            const float2 df = __half22float2(__ldg((const __half2*)w.p2 + (size_t)row * (K >> 8) + (kb >> 2)));
-            const float dl = df.x * (float)(sm & 0xff), dh = df.x * (float)((sm >> 8) & 0xff);
-            const float ml = df.y * (float)((sm >> 16) & 0xff), mh = df.y * (float)(sm >> 24);
-            const uint32_t q[8] = {qa.x, qa.y, qa.z, qa.w, qb.x, qb.y, qb.z, qb.w};
+            r.a = ldg16(qp);
+            r.b = ldg16(qp + 16);
+            r.s0 = __ldg((const uint32_t*)((const uint8_t*)w.p1 + (size_t)row * (K >> 4) + kb * 4));
+            r.s1 = __ldg((const uint32_t*)w.p2 + (size_t)row * (K >> 8) + (kb >> 2));
+            break;
+        }
+        case WT_Q6_K: {
+            const int sb = kb >> 2, n = (kb >> 1) & 1, hi = kb & 1;
+            const uint8_t* lp = (const uint8_t*)w.p0 + (size_t)row * (K >> 1) + sb * 128 + 64 * n + 32 * h;
+            const uint8_t* hp = (const uint8_t*)w.p1 + (size_t)row * (K >> 2) + sb * 64 + 32 * n;
+            r.a = ldg16(lp);
+            r.b = ldg16(lp + 16);
+            r.c = ldg16(hp);
+            r.d = ldg16(hp + 16);
+            r.s0 = __ldg((const uint32_t*)((const int8_t*)w.p2 + (size_t)row * (K >> 4) + sb * 16 + 8 * n + 4 * hi));
+            r.s1 = __ldg((const unsigned short*)w.p3 + (size_t)row * (K >> 8) + sb);
+            break;
+        }
+        case WT_Q8_0: {
+            const int8_t* qp = (const int8_t*)w.p0 + (size_t)row * K + kb * 64 + 32 * h;
+            r.a = ldg16(qp);
+            r.b = ldg16(qp + 16);
+            r.s1 = __ldg((const unsigned short*)w.p1 + (size_t)row * (K >> 5) + kb * 2 + h);
+            break;
+        }
+        default: {   // BF16 / F16: 32 values = 64 bytes
+            const uint8_t* p = (const uint8_t*)w.p0 + ((size_t)row * K + kb * 64 + 32 * h) * 2;
+            r.a = ldg16(p);
+            r.b = ldg16(p + 16);
+            r.c = ldg16(p + 32);
+            r.d = ldg16(p + 48);
+            break;
+        }
+    }
+}
+
+__device__ __forceinline__ float half_bits_to_float(uint32_t bits) {
+    return __half2float(__ushort_as_half((unsigned short)bits));
+}
+
+// Raw -> 16 bf16x2 words (32 consecutive columns)
+__device__ __forceinline__ void expand_raw(int type, const Raw& r, int kb, int h, uint32_t (&o)[16]) {
+    switch (type) {
+        case WT_Q4_K: {
+            const float2 df = __half22float2(*reinterpret_cast<const __half2*>(&r.s1));
+            const float sc = df.x * (float)((r.s0 >> (8 * h)) & 0xff), mn = df.y * (float)((r.s0 >> (16 + 8 * h)) & 0xff);
+            const uint32_t s2 = bf16x2_splat(sc), o2 = bf16x2_splat(-128.f * sc - mn);
+            const uint32_t q[8] = {r.a.x, r.a.y, r.a.z, r.a.w, r.b.x, r.b.y, r.b.z, r.b.w};
 #pragma unroll
-            for (int i = 0; i < 8; i++) {      // word i: bytes 4i .. 4i+3 -> low nibbles = columns 4i.., high = 32 + 4i..
-                const uint32_t v = q[i];
-                o[2 * i] = pack_bf16(dl * (float)(v & 15) - ml, dl * (float)((v >> 8) & 15) - ml);
-                o[2 * i + 1] = pack_bf16(dl * (float)((v >> 16) & 15) - ml, dl * (float)((v >> 24) & 15) - ml);
-                o[16 + 2 * i] = pack_bf16(dh * (float)((v >> 4) & 15) - mh, dh * (float)((v >> 12) & 15) - mh);
-                o[16 + 2 * i + 1] = pack_bf16(dh * (float)((v >> 20) & 15) - mh, dh * (float)(v >> 28) - mh);
+            for (int i = 0; i < 8; i++) {      // byte j of word i = column 4i + j (low nibble: half 0, high nibble: half 1)
+                const uint32_t codes = (h ? (q[i] >> 4) : q[i]) & 0x0f0f0f0fu;
+                expand4(codes, s2, o2, o[2 * i], o[2 * i + 1]);
             }
             return;
         }
         case WT_Q6_K: {
-            // 64 columns = two quarters (32 each) of half n of super-block sb
-            const int sb = kb >> 2, n = (kb >> 1) & 1, hi = kb & 1;      // hi: quarters 2,3 use the high nibbles
-            const uint8_t* lp = (const uint8_t*)w.p0 + (size_t)row * (K >> 1) + sb * 128 + 64 * n;
-            const uint8_t* hp = (const uint8_t*)w.p1 + (size_t)row * (K >> 2) + sb * 64 + 32 * n;
-            const int8_t* sp = (const int8_t*)w.p2 + (size_t)row * (K >> 4) + sb * 16 + 8 * n + 4 * hi;
-            const float d = __half2float(__ldg((const __half*)w.p3 + (size_t)row * (K >> 8) + sb));
-            const uint32_t s4 = __ldg((const uint32_t*)sp);             // scales of (quarter 2hi, l<16), (2hi, l>=16), (2hi+1, ..)
-            const float sc[4] = {d * (float)(int8_t)(s4 & 0xff), d * (float)(int8_t)((s4 >> 8) & 0xff),
-                                 d * (float)(int8_t)((s4 >> 16) & 0xff), d * (float)(int8_t)(s4 >> 24)};
+            // quarter 2 hi + h of the half: low (hi = 0) or high (hi = 1) nibbles of ql, two bits of qh at 2 (2 hi + h)
+            const int hi = kb & 1, hs = 2 * (2 * hi + h);
+            const float d = half_bits_to_float(r.s1);
+            const uint32_t L[8] = {r.a.x, r.a.y, r.a.z, r.a.w, r.b.x, r.b.y, r.b.z, r.b.w};
+            const uint32_t H[8] = {r.c.x, r.c.y, r.c.z, r.c.w, r.d.x, r.d.y, r.d.z, r.d.w};
 #pragma unroll
-            for (int qd = 0; qd < 2; qd++) {           // quarter 2hi + qd reads ql[32 qd + l], qh bits 2(2hi+qd)
+            for (int c = 0; c < 2; c++) {      // 16 columns share one scale
+                const float sc = d * (float)(int8_t)((r.s0 >> (8 * (2 * h + c))) & 0xff);
+                const uint32_t s2 = bf16x2_splat(sc), o2 = bf16x2_splat(-160.f * sc);       // (128 + q) * s - 160 s = (q - 32) s
 #pragma unroll
-                for (int c = 0; c < 2; c++) {          // 16 values per 16-byte load
-                    const uint4 lq = ldg16(lp + 32 * qd + 16 * c), hq = ldg16(hp + 16 * c);
-                    const uint32_t L[4] = {lq.x, lq.y, lq.z, lq.w}, H[4] = {hq.x, hq.y, hq.z, hq.w};
-                    const float s = sc[2 * qd + c];
-                    const int hs = 2 * (2 * hi + qd);
-#pragma unroll
-                    for (int i = 0; i < 4; i++) {
-                        const uint32_t lo = hi ? (L[i] >> 4) & 0x0f0f0f0fu : L[i] & 0x0f0f0f0fu;
-                        const uint32_t v = lo | (((H[i] >> hs) & 0x03030303u) << 4);
-                        const int base = 16 * qd + 8 * c + 2 * i;
-                        o[base] = pack_bf16(s * (float)((int)(v & 63) - 32), s * (float)((int)((v >> 8) & 63) - 32));
-                        o[base + 1] = pack_bf16(s * (float)((int)((v >> 16) & 63) - 32), s * (float)((int)((v >> 24) & 63) - 32));
-                    }
+                for (int i = 0; i < 4; i++) {
+                    const uint32_t lo = (hi ? (L[4 * c + i] >> 4) : L[4 * c + i]) & 0x0f0f0f0fu;
+                    const uint32_t codes = lo | (((H[4 * c + i] >> hs) & 0x03030303u) << 4);
+                    expand4(codes, s2, o2, o[8 * c + 2 * i], o[8 * c + 2 * i + 1]);
                 }
             }
             return;
         }
         case WT_Q8_0: {
-            const int8_t* qp = (const int8_t*)w.p0 + (size_t)row * K + kb * 64;
-            const __half* dp = (const __half*)w.p1 + (size_t)row * (K >> 5) + kb * 2;
+            const float d = half_bits_to_float(r.s1);
+            const uint32_t Q[8] = {r.a.x, r.a.y, r.a.z, r.a.w, r.b.x, r.b.y, r.b.z, r.b.w};
 #pragma unroll
-            for (int h = 0; h < 2; h++) {
-                const float d = __half2float(__ldg(dp + h));
-#pragma unroll
-                for (int c = 0; c < 2; c++) {
-                    const uint4 q = ldg16(qp + 32 * h + 16 * c);
-                    const uint32_t Q[4] = {q.x, q.y, q.z, q.w};
-#pragma unroll
-                    for (int i = 0; i < 4; i++) {
-                        const int base = 16 * h + 8 * c + 2 * i;
-                        o[base] = pack_bf16(d * (float)(int8_t)(Q[i] & 0xff), d * (float)(int8_t)((Q[i] >> 8) & 0xff));
-                        o[base + 1] = pack_bf16(d * (float)(int8_t)((Q[i] >> 16) & 0xff), d * (float)(int8_t)(Q[i] >> 24));
-                    }
-                }
+            for (int i = 0; i < 8; i++) {
+                o[2 * i] = pack_bf16(d * (float)(int8_t)(Q[i] & 0xff), d * (float)(int8_t)((Q[i] >> 8) & 0xff));
+                o[2 * i + 1] = pack_bf16(d * (float)(int8_t)((Q[i] >> 16) & 0xff), d * (float)(int8_t)(Q[i] >> 24));
             }
             return;
         }
         case WT_BF16: {
-            const uint8_t* p = (const uint8_t*)w.p0 + ((size_t)row * K + kb * 64) * 2;
+            const uint32_t V[16] = {r.a.x, r.a.y, r.a.z, r.a.w, r.b.x, r.b.y, r.b.z, r.b.w, r.c.x, r.c.y, r.c.z, r.c.w, r.d.x, r.d.y, r.d.z, r.d.w};
 #pragma unroll
-            for (int c = 0; c < 8; c++) {
-                const uint4 v = ldg16(p + 16 * c);
-                o[4 * c] = v.x; o[4 * c + 1] = v.y; o[4 * c + 2] = v.z; o[4 * c + 3] = v.w;
-            }
+            for (int i = 0; i < 16; i++) o[i] = V[i];
             return;
         }
-        case WT_F16: {
-            const uint8_t* p = (const uint8_t*)w.p0 + ((size_t)row * K + kb * 64) * 2;
+        default: {   // F16
+            const uint32_t V[16] = {r.a.x, r.a.y, r.a.z, r.a.w, r.b.x, r.b.y, r.b.z, r.b.w, r.c.x, r.c.y, r.c.z, r.c.w, r.d.x, r.d.y, r.d.z, r.d.w};
 #pragma unroll
-            for (int c = 0; c < 8; c++) {
-                const uint4 v = ldg16(p + 16 * c);
-                const uint32_t V[4] = {v.x, v.y, v.z, v.w};
-#pragma unroll
-                for (int i = 0; i < 4; i++) {
-                    const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&V[i]));
-                    o[4 * c + i] = pack_bf16(f.x, f.y);
-                }
+            for (int i = 0; i < 16; i++) {
+                const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&V[i]));
+                o[i] = pack_bf16(f.x, f.y);
             }
             return;
         }
     }
+}
+
+// Store 32 consecutive K values (16 words) of row r, half h, into the swizzled stage tile.
+__device__ __forceinline__ void store_half_row(uint8_t* tile, int r, int h, const uint32_t (&w)[16]) {
+    uint8_t* row = tile + r * 128;
 #pragma unroll
-    for (int i = 0; i < 32; i++) o[i] = 0;
+    for (int c = 0; c < 4; c++) {
+        const uint4 v = make_uint4(w[4 * c], w[4 * c + 1], w[4 * c + 2], w[4 * c + 3]);
+        *reinterpret_cast<uint4*>(row + (((4 * h + c) ^ (r & 7)) << 4)) = v;
+    }
 }
 
 // grid = (M tiles, N tiles): CTAs that share a weight tile are adjacent in launch order and run together,
 // so the quantised planes are fetched from HBM once and re-read from L2.
-__global__ void __launch_bounds__(192, 2) gemm_q_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ QGemmParams p) {
+__global__ void __launch_bounds__(THREADS, 2) gemm_q_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ QGemmParams p) {
     extern __shared__ uint8_t smem_raw[];
     uint8_t* tiles = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
     uint64_t* full = reinterpret_cast<uint64_t*>(tiles + STAGES * STAGE_BYTES);
@@ -208,31 +241,38 @@ __global__ void __launch_bounds__(192, 2) gemm_q_tc_kernel(const __grid_constant
             if (ok) umma_commit(acc_ready);
         }
     } else {
-        // warps 2..5: dequantise the weight tile, one row per thread, then drain the accumulator
-        const int r = (warp - 2) * 32 + lane;                 // row inside the tile
+        // warps 2..9: expand the weight tile (thread = 32 columns of one row), then drain the accumulator
+        const int dt = threadIdx.x - 64;
+        const int r = dt & 127, h = dt >> 7;
         const int wrow = min(n0 + r, p.w.n - 1);
+        const int type = p.w.type;
         bool ok = true;
+        Raw cur, nxt;
+        load_raw(p.w, wrow, 0, h, cur);
         for (int kb = 0; kb < k_blocks && ok; kb++) {
             const int s = kb % STAGES;
-            uint32_t vals[32];
-            dequant64(p.w, wrow, kb, vals);                   // global loads first, they do not need the stage
+            if (kb + 1 < k_blocks) load_raw(p.w, wrow, kb + 1, h, nxt);      // next block's bytes are in flight while this one is expanded
+            uint32_t vals[16];
+            expand_raw(type, cur, kb, h, vals);
             if (kb >= STAGES) ok = mbar_wait(&empty[s], ((kb / STAGES) - 1) & 1);
             if (ok) {
-                store_row_swizzled(tiles + s * STAGE_BYTES + A_BYTES, r, vals);
+                store_half_row(tiles + s * STAGE_BYTES + A_BYTES, r, h, vals);
                 asm volatile("fence.proxy.async.shared::cta;" ::: "memory");      // make the stores visible to the tensor core
             }
             __syncwarp();
             if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(&full[s])) : "memory");
+            cur = nxt;
         }
         if (!ok) atomicExch(&s_failed, 1);
         const int q = warp & 3;                               // TMEM lane quarter this warp may read
+        const int chalf = (warp - 2) >> 2;                    // which 64 accumulator columns this warp drains
         const bool ready = ok && mbar_wait(acc_ready, 0);
         if (!ready) atomicExch(&s_failed, 1);
         tc_fence_after();
         const int row = m0 + q * 32 + lane;
         if (ready) {
 #pragma unroll 1
-            for (int c0 = 0; c0 < BN; c0 += 32) {
+            for (int c0 = 64 * chalf; c0 < 64 * chalf + 64; c0 += 32) {
                 uint32_t v[32];
                 tmem_ld32(tmem_acc + ((uint32_t)(q * 32) << 16) + (uint32_t)c0, v);
                 if (row < p.m) {
@@ -289,10 +329,9 @@ B2_API int b2_gemm_q(const void* x, int m, const WDesc* w, float* out, int ldo, 
     }
     QGemmParams p{*w, m, out, ldo, accumulate};
     dim3 grid((m + BM - 1) / BM, (w->n + BN - 1) / BN);
-    gemm_q_tc_kernel<<<grid, 192, SMEM_TOTAL, st>>>(ma, p);
+    gemm_q_tc_kernel<<<grid, THREADS, SMEM_TOTAL, st>>>(ma, p);
     return (int)cudaGetLastError();
 }
-
 
 B2_API int b2_gemm_q_status() {
     int v = 0;
