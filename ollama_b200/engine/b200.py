@@ -46,13 +46,23 @@ class B200Backend:
     name = "b200"
 
     def __init__(self, g: GGUFFile | None, device: str = "cuda", opts=None, cfg: ModelConfig | None = None,
-                 tensors: dict[str, QWeight] | None = None, keep_bf16: bool = False):
-        """Load from an opened GGUF, or from ``cfg`` + an iterable source of :class:`QWeight` (synthetic checkpoints)."""
+                 tensors: dict[str, QWeight] | None = None, keep_bf16: bool | None = None, prefill_gemm: str = "bf16"):
+        """Load from an opened GGUF, or from ``cfg`` + an iterable source of :class:`QWeight` (synthetic checkpoints).
+
+        ``keep_bf16``: keep a resident 16-bit copy of every matrix for prefill (None: when it fits in 40% of the free HBM;
+        otherwise each matrix is expanded into scratch right before its GEMM).  ``prefill_gemm``: "bf16" (expand, then the
+        bf16 tensor-core GEMM) or "fused" (weights expanded inside the GEMM kernel; no 16-bit copy anywhere).
+        """
         self.device = torch.device(device if device != "cuda" else f"cuda:{torch.cuda.current_device()}")
         self.cfg = cfg if cfg is not None else config_from_gguf(g)
         if not supports(self.cfg):
             raise NotImplementedError(f"{self.cfg.arch} is not supported by the sm_100a engine")
         K.lib()
+        self.prefill_gemm = prefill_gemm
+        if keep_bf16 is None:
+            c = self.cfg
+            est = 2 * (c.n_layers * (c.d_model * (2 * c.q_dim + 2 * c.kv_dim) + 3 * c.d_model * c.d_ff) + c.vocab_size * c.d_model)
+            keep_bf16 = prefill_gemm == "bf16" and est < 0.4 * torch.cuda.mem_get_info(self.device)[0]
         self.keep_bf16 = keep_bf16
         self.n_slots = self.n_ctx = 0
         self._graphs: dict[tuple[int, bool], torch.cuda.CUDAGraph] = {}
@@ -80,16 +90,16 @@ class B200Backend:
                 return None
             return get(name).dequant().to(dev).contiguous()
 
-        def mat(name) -> K.DevWeight:
+        def mat(name, keep=True) -> K.DevWeight:
             w = K.repack(get(name + ".weight"), dev, bias=vec(name + ".bias"))
-            if self.keep_bf16 or not K.gemm_q_supported(w):
-                w.bf16 = K.dequant_to_bf16(w)     # encodings the fused GEMM cannot expand keep a 16-bit copy for prefill
+            if self.keep_bf16 and keep:
+                w.bf16 = K.dequant_to_bf16(w)
             return w
 
         self.embd = K.repack(get("token_embd.weight"), dev)
         self.out_norm = vec("output_norm.weight")
         self.head = mat("output") if has("output.weight") else self.embd
-        if (self.keep_bf16 or not K.gemm_q_supported(self.head)) and not hasattr(self.head, "bf16"):
+        if self.keep_bf16 and not hasattr(self.head, "bf16"):
             self.head.bf16 = K.dequant_to_bf16(self.head)
         self.layers: list[_Layer] = []
         for i in range(c.n_layers):
@@ -102,13 +112,14 @@ class B200Backend:
             if L.ffn_norm is None:
                 L.ffn_norm = vec(p + "post_attention_norm.weight")
             L.post_ffw_norm = vec(p + "post_ffw_norm.weight") if c.sandwich_norm else None
-            L.gate, L.up, L.down = mat(p + "ffn_gate"), mat(p + "ffn_up"), mat(p + "ffn_down")
+            L.gate, L.up, L.down = mat(p + "ffn_gate", False), mat(p + "ffn_up", False), mat(p + "ffn_down")
             if L.gate.wtype != L.up.wtype:
                 L.gu = K.interleave_rows(K.to_f16(L.gate), K.to_f16(L.up))
             else:
                 L.gu = K.interleave_rows(L.gate, L.up)
-            if K.gemm_q_supported(L.gu) or hasattr(L.gate, "bf16"):      # the interleaved matrix (or the 16-bit copies) serve every path
-                L.gate.planes, L.up.planes = [], []
+            L.gate.planes, L.up.planes = [], []      # the interleaved matrix serves decode and prefill
+            if self.keep_bf16:
+                L.gu.bf16 = K.dequant_to_bf16(L.gu)
             L.sinks = vec(p + "attn_sinks.weight")
             L.swa = c.layer_is_swa(i)
             self.layers.append(L)
@@ -317,18 +328,17 @@ class B200Backend:
     # -- prefill --------------------------------------------------------------------------------------
     def _mm(self, x_bf16: torch.Tensor, w: K.DevWeight, out: torch.Tensor | None = None, out_off: int = 0) -> torch.Tensor:
         """x @ W^T + bias for a prefill chunk: the dequantisation-fused tcgen05 GEMM, or a 16-bit copy for other encodings."""
-        if K.gemm_q_supported(w) and not self.keep_bf16:
+        if self.prefill_gemm == "fused" and K.gemm_q_supported(w):
             self.kernel_launches += 1
             return K.gemm_q(x_bf16, w, out=out, out_off=out_off)
         wb = getattr(w, "bf16", None)
         if wb is None:
-            wb = K.dequant_to_bf16(w)
-        y = K.gemm_bf16(x_bf16, wb, w.bias)
+            wb = K.dequant_to_bf16(w)        # scratch: freed (back to the caching allocator) when this call returns
+            self.kernel_launches += 1
         self.kernel_launches += 1
         if out is not None:
-            out[:, out_off:out_off + w.n] = y
-            return out
-        return y
+            return K.gemm_bf16(x_bf16, wb, w.bias, out=out[:, out_off:out_off + w.n])
+        return K.gemm_bf16(x_bf16, wb, w.bias)
 
     @torch.no_grad()
     def _forward_chunk(self, slot: int, tokens: Sequence[int], pos0: int) -> torch.Tensor:
@@ -371,12 +381,8 @@ class B200Backend:
                 o = R.rmsnorm(o, L.post_attn_norm, c.norm_eps)
             x = x + o
             h = R.rmsnorm(x, L.ffn_norm, c.norm_eps).to(torch.bfloat16)
-            if L.gate.planes or hasattr(L.gate, "bf16"):
-                g_, u_ = self._mm(h, L.gate), self._mm(h, L.up)
-            else:
-                gu = self._mm(h, L.gu)                      # rows interleaved: even = gate, odd = up
-                g_, u_ = gu[:, 0::2], gu[:, 1::2]
-            f = R.glu(g_, u_, c.act, c.swiglu_alpha, c.swiglu_limit)
+            gu = self._mm(h, L.gu)                          # rows interleaved: even = gate, odd = up
+            f = R.glu(gu[:, 0::2], gu[:, 1::2], c.act, c.swiglu_alpha, c.swiglu_limit)
             f = self._mm(f.to(torch.bfloat16), L.down)
             if c.sandwich_norm:
                 f = R.rmsnorm(f, L.post_ffw_norm, c.norm_eps)

@@ -3,6 +3,7 @@
 // neighbours where the data flow allows (RMSNorm + int8 block quantisation of the GEMV input;
 // per-head QK-norm + RoPE + f16 conversion + scatter into the slot-partitioned cache).
 #include "common.cuh"
+#include "comm.cuh"
 
 // ---------------------------------------------------------------------------------------------
 // y = rmsnorm(x) * w  ->  fp32 copy (optional) + int8 blocks of 32 with (d, d*sum q)
@@ -18,6 +19,12 @@ struct NormQuantArgs {
     float2* xds;         // [nb][k/32]
     float* xf;           // [nb][k] or null
     float* residual;     // if set: residual[b][i] += y   (post-norm residual add of sandwich-norm models)
+    // tensor parallel: x[b] += sum over ranks of the partial rows received from the group, before anything else
+    const float* parts;      // [2 halves][n_part][rows][k] in this rank's peer-mapped region (null: none)
+    int n_part;
+    long long part_stride;   // elements between the slabs of two ranks
+    long long parity_stride; // elements between the two halves
+    CommChan* chan;
 };
 
 // Each thread owns float4 chunks c = tid + 256 j; a quantisation block of 32 is 8 consecutive chunks =
@@ -39,12 +46,36 @@ __global__ void __launch_bounds__(256) rmsnorm_quant_kernel(const __grid_constan
     pdl_launch();
     pdl_wait();
     const float* x = a.x + (size_t)b * a.k;
+    const float* part = nullptr;
+    if (a.n_part) {      // the producer of this rank has finished (grid dependency); wait for the other ranks' rows
+        const unsigned e = ld_volatile_u32(&a.chan->epoch);
+        comm_wait_flags(a.chan, a.n_part, e);
+        __syncthreads();
+        part = a.parts + ((e & 1u) ? a.parity_stride : 0ll) + (size_t)b * a.k;
+    }
     for (int c0 = 0; c0 < nchunk; c0 += 256 * MAXJ) {     // one trip for k <= 8192
         float4 v[MAXJ];
 #pragma unroll
         for (int j = 0; j < MAXJ; j++) {
             const int c = c0 + tid + 256 * j;
             v[j] = c < nchunk ? *(const float4*)(x + 4 * c) : make_float4(0.f, 0.f, 0.f, 0.f);
+        }
+        if (part) {      // k <= 8192 here (checked by the launcher): the reduced row is complete in registers
+            for (int r = 0; r < a.n_part; r++) {
+#pragma unroll
+                for (int j = 0; j < MAXJ; j++) {
+                    const int c = tid + 256 * j;
+                    if (c < nchunk) {
+                        const float4 t = __ldcg((const float4*)(part + r * a.part_stride + 4 * c));   // written by a peer: read through L2
+                        v[j].x += t.x; v[j].y += t.y; v[j].z += t.z; v[j].w += t.w;
+                    }
+                }
+            }
+#pragma unroll
+            for (int j = 0; j < MAXJ; j++) {
+                const int c = tid + 256 * j;
+                if (c < nchunk) *(float4*)(const_cast<float*>(x) + 4 * c) = v[j];
+            }
         }
         float inv = 1.f;
         if (a.do_norm) {
@@ -106,6 +137,7 @@ __global__ void __launch_bounds__(256) rmsnorm_quant_kernel(const __grid_constan
 
 B2_API int b2_rmsnorm_quant(const NormQuantArgs* a, int nb, int pdl, cudaStream_t st) {
     if (a->k & 31) return (int)cudaErrorInvalidValue;
+    if (a->n_part && (a->k > 8192 || a->n_part > COMM_MAX_RANKS || !a->parts || !a->chan)) return (int)cudaErrorInvalidValue;
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(nb);
     cfg.blockDim = dim3(256);

@@ -8,9 +8,9 @@
 // shared-memory descriptor expects (16-byte chunk c of row r lives at chunk c ^ (r & 7)); a proxy
 // fence publishes those generic-proxy writes to the tensor core.  The raw bytes of the next K block
 // are requested before the current one is expanded, so global latency stays off the critical path.
-// 4- and 6-bit codes become bf16 with one byte-permute and one packed FMA per pair: the code q is
-// dropped into the mantissa of 128.0 (bf16 0x43qq = 128 + q, exact for q < 128) and
-// w = (128 + q) * scale + (offset - 128 * scale) is a single fma.rn.bf16x2.
+// 4- and 6-bit codes become bf16 with one byte-permute, one packed subtraction and one packed FMA per
+// pair: the code q is dropped into the mantissa of 128.0 (bf16 0x43qq = 128 + q, exact for q < 128),
+// 128 + zero-point is subtracted (exact) and w = (q - zero) * scale + offset is a fma.rn.bf16x2.
 // One elected thread issues tcgen05.mma (M = 128 tokens, N = 128 weight rows) into a TMEM accumulator;
 // four of the producer warps drain it once their last stage is written.  All mbarrier waits are
 // bounded (KS_TIMEOUT in the status word on expiry).
@@ -18,6 +18,7 @@
 // This is the counterpart of ggml-cuda's mmq kernels (in-kernel dequantisation feeding mma.sync) and of
 // its dequantise-then-cuBLAS path, redone for tcgen05 / TMEM.
 #include "tc_common.cuh"
+#include "comm.cuh"
 
 __device__ int g_gemm_q_status = 0;
 
@@ -37,6 +38,10 @@ struct QGemmParams {
     float* out;
     int ldo;
     int accumulate;
+    // tensor parallel (cm.n_dst > 0): row m of the result belongs to rank m / rows_per_rank; the tile is stored into that
+    // rank's buffer cm.dst[owner] (pitch ldo, row index relative to the owner's first row) and the exchange is announced.
+    CommSend cm;
+    int rows_per_rank;
 };
 
 // Raw bytes of 32 columns of one weight row (what a producer thread fetches per K block).
@@ -56,12 +61,19 @@ __device__ __forceinline__ uint32_t bf16x2_fma(uint32_t a, uint32_t b, uint32_t 
 }
 __device__ __forceinline__ uint32_t bf16x2_splat(float v) { return pack_bf16(v, v); }
 
-// Four byte-sized codes (one per byte of `codes`) -> two bf16x2 words of scale * code + offset.
-__device__ __forceinline__ void expand4(uint32_t codes, uint32_t scale2, uint32_t off2, uint32_t& w01, uint32_t& w23) {
+__device__ __forceinline__ uint32_t bf16x2_sub(uint32_t a, uint32_t b) {
+    uint32_t d;
+    asm("sub.rn.bf16x2 %0, %1, %2;" : "=r"(d) : "r"(a), "r"(b));
+    return d;
+}
+
+// Four byte-sized codes (one per byte of `codes`) -> two bf16x2 words of scale * (code - zero) + offset.
+// `magic_zero2` is bf16x2 (128 + zero); the subtraction is exact, so the only roundings are those of scale, offset and the result.
+__device__ __forceinline__ void expand4(uint32_t codes, uint32_t magic_zero2, uint32_t scale2, uint32_t off2, uint32_t& w01, uint32_t& w23) {
     const uint32_t m01 = __byte_perm(codes, 0x43434343u, 0x4140);      // {code0, 0x43, code1, 0x43} = bf16 (128 + code0), (128 + code1)
     const uint32_t m23 = __byte_perm(codes, 0x43434343u, 0x4342);
-    w01 = bf16x2_fma(m01, scale2, off2);
-    w23 = bf16x2_fma(m23, scale2, off2);
+    w01 = bf16x2_fma(bf16x2_sub(m01, magic_zero2), scale2, off2);
+    w23 = bf16x2_fma(bf16x2_sub(m23, magic_zero2), scale2, off2);
 }
 
 // half h (0/1) of K block kb of row `row`: columns 64 kb + 32 h .. + 31
@@ -116,12 +128,12 @@ __device__ __forceinline__ void expand_raw(int type, const Raw& r, int kb, int h
         case WT_Q4_K: {
             const float2 df = __half22float2(*reinterpret_cast<const __half2*>(&r.s1));
             const float sc = df.x * (float)((r.s0 >> (8 * h)) & 0xff), mn = df.y * (float)((r.s0 >> (16 + 8 * h)) & 0xff);
-            const uint32_t s2 = bf16x2_splat(sc), o2 = bf16x2_splat(-128.f * sc - mn);
+            const uint32_t s2 = bf16x2_splat(sc), o2 = bf16x2_splat(-mn);
             const uint32_t q[8] = {r.a.x, r.a.y, r.a.z, r.a.w, r.b.x, r.b.y, r.b.z, r.b.w};
 #pragma unroll
             for (int i = 0; i < 8; i++) {      // byte j of word i = column 4i + j (low nibble: half 0, high nibble: half 1)
                 const uint32_t codes = (h ? (q[i] >> 4) : q[i]) & 0x0f0f0f0fu;
-                expand4(codes, s2, o2, o[2 * i], o[2 * i + 1]);
+                expand4(codes, 0x43004300u, s2, o2, o[2 * i], o[2 * i + 1]);
             }
             return;
         }
@@ -134,12 +146,12 @@ __device__ __forceinline__ void expand_raw(int type, const Raw& r, int kb, int h
 #pragma unroll
             for (int c = 0; c < 2; c++) {      // 16 columns share one scale
                 const float sc = d * (float)(int8_t)((r.s0 >> (8 * (2 * h + c))) & 0xff);
-                const uint32_t s2 = bf16x2_splat(sc), o2 = bf16x2_splat(-160.f * sc);       // (128 + q) * s - 160 s = (q - 32) s
+                const uint32_t s2 = bf16x2_splat(sc);
 #pragma unroll
                 for (int i = 0; i < 4; i++) {
                     const uint32_t lo = (hi ? (L[4 * c + i] >> 4) : L[4 * c + i]) & 0x0f0f0f0fu;
                     const uint32_t codes = lo | (((H[4 * c + i] >> hs) & 0x03030303u) << 4);
-                    expand4(codes, s2, o2, o[8 * c + 2 * i], o[8 * c + 2 * i + 1]);
+                    expand4(codes, 0x43204320u, s2, 0u, o[8 * c + 2 * i], o[8 * c + 2 * i + 1]);      // bf16 0x4320 = 160 = 128 + 32
                 }
             }
             return;
@@ -276,7 +288,13 @@ __global__ void __launch_bounds__(THREADS, 2) gemm_q_tc_kernel(const __grid_cons
                 uint32_t v[32];
                 tmem_ld32(tmem_acc + ((uint32_t)(q * 32) << 16) + (uint32_t)c0, v);
                 if (row < p.m) {
-                    float* o = p.out + (size_t)row * p.ldo + p.w.out_off + n0 + c0;
+                    float* o;
+                    if (p.cm.n_dst > 0) {
+                        const int owner = row / p.rows_per_rank;
+                        o = p.cm.dst[owner] + (size_t)(row - owner * p.rows_per_rank) * p.ldo + p.w.out_off + n0 + c0;
+                    } else {
+                        o = p.out + (size_t)row * p.ldo + p.w.out_off + n0 + c0;
+                    }
 #pragma unroll
                     for (int j = 0; j < 32; j += 4) {
                         if (n0 + c0 + j >= p.w.n) break;
@@ -302,6 +320,7 @@ __global__ void __launch_bounds__(THREADS, 2) gemm_q_tc_kernel(const __grid_cons
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_acc), "r"(BN) : "memory");
     }
     if (threadIdx.x == 0 && s_failed) atomicExch(&g_gemm_q_status, KS_TIMEOUT);
+    if (p.cm.n_dst > 0) comm_publish(p.cm, gridDim.x * gridDim.y, comm_next_epoch(p.cm));
 }
 
 bool q_supported(const WDesc& w) {
@@ -327,7 +346,23 @@ B2_API int b2_gemm_q(const void* x, int m, const WDesc* w, float* out, int ldo, 
         cudaFuncSetAttribute(gemm_q_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_TOTAL);
         attr = true;
     }
-    QGemmParams p{*w, m, out, ldo, accumulate};
+    QGemmParams p{*w, m, out, ldo, accumulate, {}, 0};
+    dim3 grid((m + BM - 1) / BM, (w->n + BN - 1) / BN);
+    gemm_q_tc_kernel<<<grid, THREADS, SMEM_TOTAL, st>>>(ma, p);
+    return (int)cudaGetLastError();
+}
+
+// Row-parallel GEMM of a tensor-parallel group: the partial result tile of rows owned by rank r is stored straight into
+// cm->dst[r] (a peer address, pitch ldo) from the epilogue and the exchange is announced on cm's channel.
+B2_API int b2_gemm_q_scatter(const void* x, int m, const WDesc* w, int ldo, const CommSend* cm, int rows_per_rank, cudaStream_t st) {
+    if (!w || !cm || m < 1 || w->n < 1 || (w->n & 3) || (ldo & 3) || (w->out_off & 3) || ((uintptr_t)x & 15) || rows_per_rank < 1 ||
+        cm->n_dst < 1 || cm->n_dst > COMM_MAX_RANKS || (m + rows_per_rank - 1) / rows_per_rank > cm->n_dst)
+        return (int)cudaErrorInvalidValue;
+    if (!q_supported(*w)) return (int)cudaErrorNotSupported;
+    CUtensorMap ma;
+    if (!tc::make_map(&ma, x, m, w->k, BM)) return (int)cudaErrorNotSupported;
+    cudaFuncSetAttribute(gemm_q_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_TOTAL);
+    QGemmParams p{*w, m, nullptr, ldo, 0, *cm, rows_per_rank};
     dim3 grid((m + BM - 1) / BM, (w->n + BN - 1) / BN);
     gemm_q_tc_kernel<<<grid, THREADS, SMEM_TOTAL, st>>>(ma, p);
     return (int)cudaGetLastError();

@@ -1,54 +1,86 @@
-// Tensor-core GEMM for prefill on sm_100a: D[M,N] (+)= A[M,K] . B[N,K]^T (+ bias), bf16 operands, fp32 result.
+// Tensor-core GEMM for prefill on sm_100a: D[M,N] (+)= A[M,K] . B[N,K]^T (+ bias), bf16 operands, fp32 or bf16 result.
 //
 // Blackwell path: operand tiles are fetched by TMA (cp.async.bulk.tensor, 128-byte swizzle) into a
 // multi-stage shared-memory ring, one elected thread issues tcgen05.mma (cta_group::1, M = 128, N up to
 // 256, K = 16 per instruction) with the accumulator in tensor memory, and four epilogue warps read the
-// accumulator back with tcgen05.ld, add the bias and store / accumulate into the fp32 output.  Roles
-// are warp-specialised: warp 0 = TMA producer, warp 1 = MMA issuer (+ TMEM allocation), warps 2..5 =
-// epilogue.  Every mbarrier wait is bounded; on expiry the kernel records KS_TIMEOUT in its status word,
-// skips the remaining work, still releases its tensor memory and returns.
+// accumulator back with tcgen05.ld, add the bias and store / accumulate into the output.  Roles are
+// warp-specialised: warp 0 = TMA producer, warp 1 = MMA issuer (+ TMEM allocation), warps 2..5 = epilogue.
+//
+// The kernel is persistent: one CTA per SM walks a static list of output tiles.  The accumulator is double
+// buffered in tensor memory (2 x BN columns), so the epilogue of tile i overlaps the MMAs of tile i+1, and
+// the shared-memory ring keeps running across tile boundaries.  Tiles are ordered M-fastest inside groups
+// of 16 M-tiles: the CTAs that run at the same time share a handful of weight tiles (read from HBM once,
+// from L2 afterwards) and the activation panel stays in L2.
+//
+// Tensor-parallel variant: with a CommSend the epilogue stores each row of the partial result straight into
+// the buffer of the rank that owns that row (peer addresses over NVLink) and announces the exchange, which
+// makes the kernel a fused GEMM + reduce-scatter (the reduction itself happens in the consumer).
+//
+// Every mbarrier wait is bounded; on expiry the kernel records KS_TIMEOUT in its status word, skips the
+// remaining work, still releases its tensor memory and returns.
 //
 // In the reference stack this role is played by ggml-cuda's mmq kernels (int8 mma.sync tiles) and the
 // dequantise + cuBLAS path.
 #include "tc_common.cuh"
+#include "comm.cuh"
 
 __device__ int g_gemm_status = 0;
 
 namespace {
 
 using namespace tc;
-constexpr int STAGES = 4;
+constexpr int GROUP_M = 16;      // M-tiles per rasterisation group
 
 struct GemmParams {
     int m, n, k;
-    float* out;
-    int ldo;
+    void* out;              // fp32 or bf16 [m][ldo]
+    int ldo;                // elements
     const float* bias;      // [n] or null
-    int accumulate;         // out += result
+    int accumulate;         // out += result (fp32 output only)
+    int out_bf16;
+    CommSend cm;            // cm.n_dst > 0: row r goes to cm.dst[r / rows_per_rank] at row r % rows_per_rank (fp32)
+    int rows_per_rank;
 };
 
 template <int BN>
-struct SmemLayout {
+struct Cfg {
+    static constexpr int STAGES = BN == 256 ? 4 : 6;
     static constexpr int A_BYTES = BM * BK * 2;
     static constexpr int B_BYTES = BN * BK * 2;
     static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
     static constexpr int TOTAL = STAGES * STAGE_BYTES + 1024 /*alignment slack*/ + 256 /*barriers*/;
+    static constexpr int TMEM_COLS = 2 * BN < 32 ? 32 : 2 * BN;
 };
+
+__device__ __forceinline__ void tile_coords(int t, int tiles_m, int tiles_n, int& mt, int& nt) {
+    const int per_group = GROUP_M * tiles_n;
+    const int g = t / per_group, r = t - g * per_group;
+    const int gm = min(GROUP_M, tiles_m - g * GROUP_M);
+    mt = g * GROUP_M + r % gm;
+    nt = r / gm;
+}
+
+__device__ __forceinline__ uint32_t pack2_bf16(float lo, float hi) {
+    const __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<const uint32_t*>(&v);
+}
 
 template <int BN>
 __global__ void __launch_bounds__(192, 1) gemm_bf16_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
-                                                              const GemmParams p) {
+                                                              const __grid_constant__ GemmParams p) {
     extern __shared__ uint8_t smem_raw[];
-    using L = SmemLayout<BN>;
+    using L = Cfg<BN>;
+    constexpr int STAGES = L::STAGES;
     uint8_t* tiles = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);     // 128-byte swizzle wants 1024-byte alignment
     uint64_t* full = reinterpret_cast<uint64_t*>(tiles + STAGES * L::STAGE_BYTES);
     uint64_t* empty = full + STAGES;
-    uint64_t* acc_ready = empty + STAGES;
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_ready + 1);
+    uint64_t* acc_full = empty + STAGES;
+    uint64_t* acc_empty = acc_full + 2;
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
     __shared__ int s_failed;
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int m0 = blockIdx.y * BM, n0 = blockIdx.x * BN;
+    const int tiles_m = (p.m + BM - 1) / BM, tiles_n = (p.n + BN - 1) / BN, total = tiles_m * tiles_n;
     const int k_blocks = (p.k + BK - 1) / BK;
 
     if (threadIdx.x == 0) {
@@ -57,89 +89,157 @@ __global__ void __launch_bounds__(192, 1) gemm_bf16_tc_kernel(const __grid_const
             mbar_init(&full[s], 1);
             mbar_init(&empty[s], 1);
         }
-        mbar_init(acc_ready, 1);
+        for (int b = 0; b < 2; b++) {
+            mbar_init(&acc_full[b], 1);
+            mbar_init(&acc_empty[b], 4);       // one arrival per epilogue warp
+        }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     if (warp == 1) {     // one warp allocates the accumulator columns (power of two >= 32)
-        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(BN) : "memory");
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(L::TMEM_COLS) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
-    const uint32_t tmem_acc = *tmem_slot;
+    const uint32_t tmem_base = *tmem_slot;
 
     if (warp == 0) {
         if (lane == 0) {
-            for (int kb = 0; kb < k_blocks; kb++) {
-                const int s = kb % STAGES;
-                if (kb >= STAGES && !mbar_wait(&empty[s], ((kb / STAGES) - 1) & 1)) { atomicExch(&s_failed, 1); break; }
-                uint8_t* a_dst = tiles + s * L::STAGE_BYTES;
-                uint8_t* b_dst = a_dst + L::A_BYTES;
-                mbar_expect_tx(&full[s], L::STAGE_BYTES);
-                tma_load_2d(a_dst, &map_a, kb * BK, m0, &full[s]);
-                tma_load_2d(b_dst, &map_b, kb * BK, n0, &full[s]);
+            int it = 0;
+            bool ok = true;
+            for (int t = blockIdx.x; t < total && ok; t += gridDim.x) {
+                int mt, nt;
+                tile_coords(t, tiles_m, tiles_n, mt, nt);
+                for (int kb = 0; kb < k_blocks; kb++, it++) {
+                    const int s = it % STAGES;
+                    if (it >= STAGES && !mbar_wait(&empty[s], ((it / STAGES) - 1) & 1)) { ok = false; break; }
+                    uint8_t* a_dst = tiles + s * L::STAGE_BYTES;
+                    mbar_expect_tx(&full[s], L::STAGE_BYTES);
+                    tma_load_2d(a_dst, &map_a, kb * BK, mt * BM, &full[s]);
+                    tma_load_2d(a_dst + L::A_BYTES, &map_b, kb * BK, nt * BN, &full[s]);
+                }
             }
+            if (!ok) atomicExch(&s_failed, 1);
         }
     } else if (warp == 1) {
         if (lane == 0) {
             constexpr uint32_t idesc = umma_idesc(BM, BN);
+            int it = 0, i = 0;
             bool ok = true;
-            for (int kb = 0; kb < k_blocks; kb++) {
-                const int s = kb % STAGES;
-                if (!mbar_wait(&full[s], (kb / STAGES) & 1)) { ok = false; atomicExch(&s_failed, 1); break; }
+            for (int t = blockIdx.x; t < total && ok; t += gridDim.x, i++) {
+                const int buf = i & 1, use = i >> 1;
+                if (use >= 1 && !mbar_wait(&acc_empty[buf], (use - 1) & 1)) { ok = false; break; }
                 tc_fence_after();
-                const uint8_t* a_src = tiles + s * L::STAGE_BYTES;
-                const uint64_t adesc = umma_desc(a_src), bdesc = umma_desc(a_src + L::A_BYTES);
+                const uint32_t acc = tmem_base + (uint32_t)(buf * BN);
+                for (int kb = 0; kb < k_blocks; kb++, it++) {
+                    const int s = it % STAGES;
+                    if (!mbar_wait(&full[s], (it / STAGES) & 1)) { ok = false; break; }
+                    tc_fence_after();
+                    const uint8_t* a_src = tiles + s * L::STAGE_BYTES;
+                    const uint64_t adesc = umma_desc(a_src), bdesc = umma_desc(a_src + L::A_BYTES);
 #pragma unroll
-                for (int k = 0; k < BK / UMMA_K; k++) {
-                    // advancing 16 elements along K inside the swizzle span = 32 bytes = 2 descriptor units
-                    umma_bf16(tmem_acc, adesc + 2 * k, bdesc + 2 * k, idesc, (kb | k) != 0);
+                    for (int k = 0; k < BK / UMMA_K; k++) {
+                        // advancing 16 elements along K inside the swizzle span = 32 bytes = 2 descriptor units
+                        umma_bf16(acc, adesc + 2 * k, bdesc + 2 * k, idesc, (kb | k) != 0);
+                    }
+                    umma_commit(&empty[s]);        // frees the stage once these MMAs have read it
                 }
-                umma_commit(&empty[s]);        // frees the stage once these MMAs have read it
+                if (ok) umma_commit(&acc_full[buf]);
             }
-            if (ok) umma_commit(acc_ready);
+            if (!ok) atomicExch(&s_failed, 1);
         }
     } else {
         // epilogue warps 2..5: warp w may touch TMEM lanes 32*(w%4) .. +31
         const int q = warp & 3;
-        const bool ready = mbar_wait(acc_ready, 0);
-        if (!ready) atomicExch(&s_failed, 1);
-        tc_fence_after();
-        const int row = m0 + q * 32 + lane;
-        if (ready) {
+        int i = 0;
+        bool ok = true;
+        for (int t = blockIdx.x; t < total && ok; t += gridDim.x, i++) {
+            int mt, nt;
+            tile_coords(t, tiles_m, tiles_n, mt, nt);
+            const int buf = i & 1, use = i >> 1;
+            if (!mbar_wait(&acc_full[buf], use & 1)) { ok = false; break; }
+            tc_fence_after();
+            const int row = mt * BM + q * 32 + lane, n0 = nt * BN;
+            float* of = nullptr;
+            __nv_bfloat16* oh = nullptr;
+            if (row < p.m) {
+                if (p.cm.n_dst > 0) {
+                    const int owner = row / p.rows_per_rank;
+                    of = p.cm.dst[owner] + (size_t)(row - owner * p.rows_per_rank) * p.ldo + n0;
+                } else if (p.out_bf16) {
+                    oh = (__nv_bfloat16*)p.out + (size_t)row * p.ldo + n0;
+                } else {
+                    of = (float*)p.out + (size_t)row * p.ldo + n0;
+                }
+            }
 #pragma unroll 1
             for (int c0 = 0; c0 < BN; c0 += 32) {
                 uint32_t v[32];
-                const uint32_t taddr = tmem_acc + ((uint32_t)(q * 32) << 16) + (uint32_t)c0;
+                const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(buf * BN + c0);
                 tmem_ld32(taddr, v);
-                if (row < p.m) {
-                    float* o = p.out + (size_t)row * p.ldo + n0 + c0;
+                if (n0 + c0 >= p.n) continue;       // warp-uniform
+                if (p.bias) {
+#pragma unroll
+                    for (int j = 0; j < 32; j += 4) {
+                        if (n0 + c0 + j < p.n) {
+                            const float4 b = *(const float4*)(p.bias + n0 + c0 + j);
+                            v[j] = __float_as_uint(__uint_as_float(v[j]) + b.x);
+                            v[j + 1] = __float_as_uint(__uint_as_float(v[j + 1]) + b.y);
+                            v[j + 2] = __float_as_uint(__uint_as_float(v[j + 2]) + b.z);
+                            v[j + 3] = __float_as_uint(__uint_as_float(v[j + 3]) + b.w);
+                        }
+                    }
+                }
+                if (of) {
 #pragma unroll
                     for (int j = 0; j < 32; j += 4) {
                         if (n0 + c0 + j >= p.n) break;
                         float4 r = make_float4(__uint_as_float(v[j]), __uint_as_float(v[j + 1]), __uint_as_float(v[j + 2]), __uint_as_float(v[j + 3]));
-                        if (p.bias) {
-                            const float4 b = *(const float4*)(p.bias + n0 + c0 + j);
-                            r.x += b.x; r.y += b.y; r.z += b.z; r.w += b.w;
-                        }
                         if (p.accumulate) {
-                            const float4 old = *(const float4*)(o + j);
+                            const float4 old = *(const float4*)(of + c0 + j);
                             r.x += old.x; r.y += old.y; r.z += old.z; r.w += old.w;
                         }
-                        *(float4*)(o + j) = r;
+                        *(float4*)(of + c0 + j) = r;
+                    }
+                } else if (oh) {
+#pragma unroll
+                    for (int j = 0; j < 32; j += 8) {
+                        if (n0 + c0 + j >= p.n) break;
+                        uint4 r;
+                        r.x = pack2_bf16(__uint_as_float(v[j]), __uint_as_float(v[j + 1]));
+                        r.y = pack2_bf16(__uint_as_float(v[j + 2]), __uint_as_float(v[j + 3]));
+                        r.z = pack2_bf16(__uint_as_float(v[j + 4]), __uint_as_float(v[j + 5]));
+                        r.w = pack2_bf16(__uint_as_float(v[j + 6]), __uint_as_float(v[j + 7]));
+                        *(uint4*)(oh + c0 + j) = r;
                     }
                 }
             }
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(&acc_empty[buf])) : "memory");
         }
+        if (!ok) atomicExch(&s_failed, 1);
     }
     tc_fence_before();
     __syncthreads();
     if (warp == 1) {
         tc_fence_after();
-        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_acc), "r"(BN) : "memory");
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(L::TMEM_COLS) : "memory");
     }
     if (threadIdx.x == 0 && s_failed) atomicExch(&g_gemm_status, KS_TIMEOUT);
+    if (p.cm.n_dst > 0) comm_publish(p.cm, gridDim.x, comm_next_epoch(p.cm));
+}
+
+int sm_count() {
+    static int n = 0;
+    if (!n) {
+        int dev = 0;
+        cudaGetDevice(&dev);
+        cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
+        if (n <= 0) n = 148;
+    }
+    return n;
 }
 
 template <int BN>
@@ -148,12 +248,25 @@ int launch(const void* a, const void* b, const GemmParams& p, cudaStream_t st) {
     if (!make_map(&ma, a, p.m, p.k, BM) || !make_map(&mb, b, p.n, p.k, BN)) return (int)cudaErrorNotSupported;
     static bool attr = false;
     if (!attr) {
-        cudaFuncSetAttribute(gemm_bf16_tc_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, SmemLayout<BN>::TOTAL);
+        cudaFuncSetAttribute(gemm_bf16_tc_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg<BN>::TOTAL);
         attr = true;
     }
-    dim3 grid((p.n + BN - 1) / BN, (p.m + BM - 1) / BM);
-    gemm_bf16_tc_kernel<BN><<<grid, 192, SmemLayout<BN>::TOTAL, st>>>(ma, mb, p);
+    const int total = ((p.m + BM - 1) / BM) * ((p.n + BN - 1) / BN);
+    const int grid = total < sm_count() ? total : sm_count();
+    gemm_bf16_tc_kernel<BN><<<grid, 192, Cfg<BN>::TOTAL, st>>>(ma, mb, p);
     return (int)cudaGetLastError();
+}
+
+int dispatch(const void* a, const void* b, const GemmParams& p, cudaStream_t st) {
+    // wide tiles once they fill the machine; narrower ones keep more SMs busy on small problems
+    const long tiles_m = (p.m + BM - 1) / BM;
+    if (p.n >= 256 && tiles_m * ((p.n + 255) / 256) >= sm_count()) return launch<256>(a, b, p, st);
+    if (p.n >= 128) return launch<128>(a, b, p, st);
+    return launch<64>(a, b, p, st);
+}
+
+bool bad_operands(const void* a, const void* b, int m, int n, int k, int ldo) {
+    return m < 1 || n < 1 || k < 8 || (k & 7) || (n & 3) || (ldo & 3) || ((uintptr_t)a & 15) || ((uintptr_t)b & 15);
 }
 
 }  // namespace
@@ -162,12 +275,27 @@ int launch(const void* a, const void* b, const GemmParams& p, cudaStream_t st) {
 // out fp32 with ldo % 4 == 0, n % 4 == 0.  Returns a cudaError_t value.
 B2_API int b2_gemm_bf16(const void* a, const void* b, int m, int n, int k, float* out, int ldo, const float* bias, int accumulate,
                         cudaStream_t st) {
-    if (m < 1 || n < 1 || k < 8 || (k & 7) || (n & 3) || (ldo & 3) || ((uintptr_t)a & 15) || ((uintptr_t)b & 15) || ((uintptr_t)out & 15))
+    if (bad_operands(a, b, m, n, k, ldo) || ((uintptr_t)out & 15)) return (int)cudaErrorInvalidValue;
+    GemmParams p{m, n, k, out, ldo, bias, accumulate, 0, {}, 0};
+    return dispatch(a, b, p, st);
+}
+
+// Same product with a bf16 result (n % 8 == 0, ldo % 8 == 0); no accumulation.
+B2_API int b2_gemm_bf16_out16(const void* a, const void* b, int m, int n, int k, void* out, int ldo, const float* bias, cudaStream_t st) {
+    if (bad_operands(a, b, m, n, k, ldo) || (n & 7) || (ldo & 7) || ((uintptr_t)out & 15)) return (int)cudaErrorInvalidValue;
+    GemmParams p{m, n, k, out, ldo, bias, 0, 1, {}, 0};
+    return dispatch(a, b, p, st);
+}
+
+// Row-parallel GEMM of a tensor-parallel group: row r of the fp32 partial result is stored into cm->dst[r / rows_per_rank]
+// (a peer address; row index relative to the owner's first row, pitch ldo) and the exchange is announced on cm's channel.
+B2_API int b2_gemm_bf16_scatter(const void* a, const void* b, int m, int n, int k, int ldo, const float* bias, const CommSend* cm,
+                                int rows_per_rank, cudaStream_t st) {
+    if (bad_operands(a, b, m, n, k, ldo) || !cm || rows_per_rank < 1 || cm->n_dst < 1 || cm->n_dst > COMM_MAX_RANKS ||
+        (m + rows_per_rank - 1) / rows_per_rank > cm->n_dst)
         return (int)cudaErrorInvalidValue;
-    GemmParams p{m, n, k, out, ldo, bias, accumulate};
-    if (n >= 256) return launch<256>(a, b, p, st);
-    if (n >= 128) return launch<128>(a, b, p, st);
-    return launch<64>(a, b, p, st);
+    GemmParams p{m, n, k, nullptr, ldo, bias, 0, 0, *cm, rows_per_rank};
+    return dispatch(a, b, p, st);
 }
 
 B2_API int b2_gemm_status() {

@@ -18,6 +18,7 @@
 //     activation and re-quantises the result for the following down projection.
 // Weight loads bypass L1 (streamed once); activation loads stay cached.
 #include "gemv_dot.cuh"
+#include "comm.cuh"
 
 struct GemvArgs {
     WDesc seg[4];
@@ -29,6 +30,7 @@ struct GemvArgs {
     float* out;           // [nb][ldo]
     int ldo;
     int accumulate;       // 1: out += result (residual add)
+    CommSend cm;          // cm.n_dst > 0: write the result to every rank's buffer instead of `out` (pitch ldo) and announce it
 };
 
 struct GluArgs {
@@ -109,7 +111,8 @@ __device__ __forceinline__ void prefetch_rows(const Planes& pl, int row0, int nr
 }
 
 // CTA = 8 warps = (8/KS) row groups x KS slices of the row length.
-template <int NB, int KS>
+// COMM: the epilogue stores to every rank of the tensor-parallel group (peer addresses) and publishes the exchange.
+template <int NB, int KS, bool COMM>
 __global__ void __launch_bounds__(256, (NB <= 2 ? 2 : 1)) gemv_kernel(const __grid_constant__ GemvArgs a) {
     constexpr int RGS = 8 / KS;
     constexpr int M = R * NB;
@@ -149,8 +152,8 @@ __global__ void __launch_bounds__(256, (NB <= 2 ? 2 : 1)) gemv_kernel(const __gr
             for (int e = 0; e < OWN; e++) red[warp][base + e] = flat[e];
         }
         __syncthreads();
-        if (ks != 0 || !active) return;
-        if (owner) {
+        if (!COMM && (ks != 0 || !active)) return;
+        if (owner && ks == 0 && active) {
 #pragma unroll
             for (int e = 0; e < OWN; e++) {
                 float v = 0.f;
@@ -160,16 +163,34 @@ __global__ void __launch_bounds__(256, (NB <= 2 ? 2 : 1)) gemv_kernel(const __gr
             }
         }
     }
-    if (!active || !owner) return;
+    if (!COMM) {
+        if (!active || !owner) return;
 #pragma unroll
-    for (int e = 0; e < OWN; e++) {
-        const int idx = base + e, r = idx / NB, b = idx % NB;
-        const int row = row0 + r;
-        if (row < w.n && b < a.nb) {
-            float* o = a.out + (size_t)b * a.ldo + w.out_off + row;
-            const float v = flat[e] + (w.bias ? w.bias[row] : 0.f);
-            *o = a.accumulate ? *o + v : v;
+        for (int e = 0; e < OWN; e++) {
+            const int idx = base + e, r = idx / NB, b = idx % NB;
+            const int row = row0 + r;
+            if (row < w.n && b < a.nb) {
+                float* o = a.out + (size_t)b * a.ldo + w.out_off + row;
+                const float v = flat[e] + (w.bias ? w.bias[row] : 0.f);
+                *o = a.accumulate ? *o + v : v;
+            }
         }
+    } else {
+        const unsigned ep = comm_next_epoch(a.cm);
+        if (active && owner && ks == 0) {
+            const long long poff = comm_parity_off(a.cm, ep);
+#pragma unroll
+            for (int e = 0; e < OWN; e++) {
+                const int idx = base + e, r = idx / NB, b = idx % NB;
+                const int row = row0 + r;
+                if (row < w.n && b < a.nb) {
+                    const float v = flat[e] + (w.bias ? w.bias[row] : 0.f);
+                    const long long o = poff + (long long)b * a.ldo + w.out_off + row;
+                    for (int d = 0; d < a.cm.n_dst; d++) a.cm.dst[d][o] = v;
+                }
+            }
+        }
+        comm_publish(a.cm, gridDim.x, ep);
     }
 }
 
@@ -251,14 +272,19 @@ static cudaError_t launch_pdl(const void* fn, dim3 grid, dim3 block, size_t smem
     return cudaLaunchKernelExC(&cfg, fn, args);
 }
 
-template <int NB>
+template <int NB, bool COMM>
 static const void* pick_ks(int ks) {
     switch (ks) {
-        case 8: return (const void*)gemv_kernel<NB, 8>;
-        case 4: return (const void*)gemv_kernel<NB, 4>;
-        case 2: return (const void*)gemv_kernel<NB, 2>;
-        default: return (const void*)gemv_kernel<NB, 1>;
+        case 8: return (const void*)gemv_kernel<NB, 8, COMM>;
+        case 4: return (const void*)gemv_kernel<NB, 4, COMM>;
+        case 2: return (const void*)gemv_kernel<NB, 2, COMM>;
+        default: return (const void*)gemv_kernel<NB, 1, COMM>;
     }
+}
+
+template <bool COMM>
+static const void* pick_nb(int nb, int ks) {
+    return nb <= 1 ? pick_ks<1, COMM>(ks) : nb <= 2 ? pick_ks<2, COMM>(ks) : nb <= 4 ? pick_ks<4, COMM>(ks) : pick_ks<8, COMM>(ks);
 }
 
 // Runs y = W x for 1..8 tokens.  Returns a cudaError_t value.
@@ -277,7 +303,8 @@ B2_API int b2_gemv(const GemvArgs* a, int pdl, cudaStream_t st) {
     dim3 grid((unsigned)((groups + rgs - 1) / rgs)), block(256);
     GemvArgs copy = *a;
     void* args[] = {&copy};
-    const void* fn = a->nb <= 1 ? pick_ks<1>(ks) : a->nb <= 2 ? pick_ks<2>(ks) : a->nb <= 4 ? pick_ks<4>(ks) : pick_ks<8>(ks);
+    if (a->cm.n_dst < 0 || a->cm.n_dst > COMM_MAX_RANKS || (a->cm.n_dst > 0 && a->accumulate)) return (int)cudaErrorInvalidValue;
+    const void* fn = a->cm.n_dst > 0 ? pick_nb<true>(a->nb, ks) : pick_nb<false>(a->nb, ks);
     return (int)launch_pdl(fn, grid, block, 0, args, st, pdl);
 }
 

@@ -52,6 +52,7 @@ SPECS: dict[str, ArchSpec] = {
                                        "rope.scaling.original_context_length": 4096,
                                        "rope.scaling.yarn_beta_fast": 32.0, "rope.scaling.yarn_beta_slow": 1.0}),
     # small stand-ins of every family for tests
+    "tiny-tp": ArchSpec("llama", 2, 1024, 16, 8, 64, 4096, 4096, 500000.0, 1e-5, 4096),      # divides 2, 4 and 8 ways
     "tiny-qwen3": ArchSpec("qwen3", 2, 256, 4, 2, 64, 768, 4096, 1e6, 1e-6, 4096),
     "tiny-qwen2": ArchSpec("qwen2", 2, 256, 4, 2, 64, 768, 4096, 1e6, 1e-6, 4096),
     "tiny-qwen3moe": ArchSpec("qwen3moe", 2, 256, 4, 2, 64, 768, 4096, 1e6, 1e-6, 4096, n_experts=8, n_experts_used=2, d_ff_expert=256),

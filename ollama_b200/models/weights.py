@@ -9,7 +9,7 @@ import torch
 
 from ..gguf import quants
 from ..gguf.reader import GGUFFile
-from ..gguf.types import GGMLType, row_bytes
+from ..gguf.types import GGMLType, block_size, row_bytes
 
 
 @dataclass
@@ -40,6 +40,16 @@ class QWeight:
         """Slice of the outermost dimension."""
         inner = self.raw.numel() // self.shape[0]
         return QWeight(self.name, self.dtype, (stop - start,) + tuple(self.shape[1:]), self.raw[start * inner: stop * inner])
+
+    def cols(self, start: int, stop: int) -> "QWeight":
+        """Slice of the innermost (quantisation) dimension; both ends must fall on block boundaries."""
+        bs = block_size(self.dtype)
+        if start % bs or stop % bs or not 0 <= start < stop <= self.shape[-1]:
+            raise ValueError(f"{self.name}: columns [{start}, {stop}) do not fall on {bs}-element block boundaries")
+        rb = self.row_nbytes
+        per = rb // (self.shape[-1] // bs)
+        raw = self.raw.view(-1, rb)[:, start // bs * per: stop // bs * per].contiguous().view(-1)
+        return QWeight(self.name, self.dtype, tuple(self.shape[:-1]) + (stop - start,), raw)
 
     def expert(self, e: int) -> "QWeight":
         inner = self.raw.numel() // self.shape[0]

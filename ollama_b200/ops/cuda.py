@@ -59,9 +59,18 @@ class WDesc(C.Structure):
                 ("type", C.c_int), ("n", C.c_int), ("k", C.c_int), ("out_off", C.c_int)]
 
 
+COMM_MAX_RANKS = 8
+
+
+class CommSend(C.Structure):
+    """Destinations and flags of one producer-side exchange (kernels/comm.cuh)."""
+    _fields_ = [("n_dst", C.c_int), ("rank", C.c_int), ("local", C.c_void_p), ("peer_flag", C.c_void_p * COMM_MAX_RANKS),
+                ("dst", C.c_void_p * COMM_MAX_RANKS), ("parity_stride", C.c_longlong)]
+
+
 class GemvArgs(C.Structure):
     _fields_ = [("seg", WDesc * 4), ("nseg", C.c_int), ("nb", C.c_int), ("xq", C.c_void_p), ("xds", C.c_void_p),
-                ("xf", C.c_void_p), ("out", C.c_void_p), ("ldo", C.c_int), ("accumulate", C.c_int)]
+                ("xf", C.c_void_p), ("out", C.c_void_p), ("ldo", C.c_int), ("accumulate", C.c_int), ("cm", CommSend)]
 
 
 class GluArgs(C.Structure):
@@ -72,7 +81,9 @@ class GluArgs(C.Structure):
 
 class NormQuantArgs(C.Structure):
     _fields_ = [("x", C.c_void_p), ("w", C.c_void_p), ("eps", C.c_float), ("k", C.c_int), ("do_norm", C.c_int),
-                ("xq", C.c_void_p), ("xds", C.c_void_p), ("xf", C.c_void_p), ("residual", C.c_void_p)]
+                ("xq", C.c_void_p), ("xds", C.c_void_p), ("xf", C.c_void_p), ("residual", C.c_void_p),
+                ("parts", C.c_void_p), ("n_part", C.c_int), ("part_stride", C.c_longlong), ("parity_stride", C.c_longlong),
+                ("chan", C.c_void_p)]
 
 
 class RopeKvArgs(C.Structure):
@@ -354,6 +365,39 @@ def gemm_bf16(a: torch.Tensor, b: torch.Tensor, bias: torch.Tensor | None = None
     f.argtypes = [C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_void_p, C.c_int, C.c_void_p, C.c_int, C.c_void_p]
     _check(f(ptr(a), ptr(b), m, n, k, ptr(out), out.stride(0), ptr(bias), int(accumulate), stream()), "gemm_bf16")
     return out
+
+
+def gemm_bf16_out16(a: torch.Tensor, b: torch.Tensor, bias: torch.Tensor | None = None, out: torch.Tensor | None = None) -> torch.Tensor:
+    """Same product as :func:`gemm_bf16` with a bf16 result (n % 8 == 0)."""
+    m, k = a.shape
+    n = b.shape[0]
+    a, b = a.contiguous(), b.contiguous()
+    if out is None:
+        out = torch.empty(m, n, device=a.device, dtype=torch.bfloat16)
+    f = lib().b2_gemm_bf16_out16
+    f.argtypes = [C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_void_p, C.c_int, C.c_void_p, C.c_void_p]
+    _check(f(ptr(a), ptr(b), m, n, k, ptr(out), out.stride(0), ptr(bias), stream()), "gemm_bf16_out16")
+    return out
+
+
+def gemm_bf16_scatter(a: torch.Tensor, b: torch.Tensor, ldo: int, cm: "CommSend", rows_per_rank: int, bias: torch.Tensor | None = None) -> None:
+    """Row-parallel GEMM of a tensor-parallel group: partial rows go straight to their owners' buffers (kernels/gemm_tc.cu)."""
+    m, k = a.shape
+    n = b.shape[0]
+    a, b = a.contiguous(), b.contiguous()
+    f = lib().b2_gemm_bf16_scatter
+    f.argtypes = [C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_int, C.c_void_p, C.c_void_p, C.c_int, C.c_void_p]
+    _check(f(ptr(a), ptr(b), m, n, k, ldo, ptr(bias), C.addressof(cm), rows_per_rank, stream()), "gemm_bf16_scatter")
+
+
+def gemm_q_scatter(x: torch.Tensor, w: DevWeight, ldo: int, cm: "CommSend", rows_per_rank: int) -> None:
+    """Dequantisation-fused variant of :func:`gemm_bf16_scatter`."""
+    m, k = x.shape
+    x = x.contiguous()
+    d = w.desc()
+    f = lib().b2_gemm_q_scatter
+    f.argtypes = [C.c_void_p, C.c_int, C.c_void_p, C.c_int, C.c_void_p, C.c_int, C.c_void_p]
+    _check(f(ptr(x), m, C.addressof(d), ldo, C.addressof(cm), rows_per_rank, stream()), "gemm_q_scatter")
 
 
 def gemm_status() -> int:

@@ -253,6 +253,29 @@ def test_gemm_bf16_tensor_core(m, n, k):
     assert torch.allclose(acc, ref - bias + 1, atol=1e-2 + 1e-3 * ref.abs().max().item(), rtol=1e-3)
 
 
+@pytest.mark.parametrize("mode,keep", [("fused", False), ("bf16", False), ("bf16", True)])
+def test_engine_prefill_gemm_modes(tmp_path, mode, keep):
+    """Prefill logits agree with the fp32 graph whichever way the weights reach the tensor cores."""
+    from ollama_b200.engine.b200 import B200Backend
+    from ollama_b200.engine.backend import TorchBackend, open_model
+    from ollama_b200.models.synth import write_synthetic_gguf
+    p = str(tmp_path / "m.gguf")
+    write_synthetic_gguf(p, "tiny-qwen3", "Q4_K_M")
+    g = open_model(p)
+    ref, eng = TorchBackend(g, "cpu"), B200Backend(g, "cuda", keep_bf16=keep, prefill_gemm=mode)
+    ref.alloc(1, 256)
+    eng.alloc(1, 256)
+    prompt = torch.randint(259, 4096, (150,), generator=torch.Generator().manual_seed(5)).tolist()
+    lr = ref.prefill(0, prompt, 0)
+    le = eng.prefill(0, prompt, 0).cpu()
+    assert (le - lr).abs().max().item() < 0.05 * lr.abs().max().item()
+    assert K_status_ok()
+
+
+def K_status_ok() -> bool:
+    return _K().gemm_status() == 0
+
+
 @pytest.mark.parametrize("t", [GGMLType.Q4_K, GGMLType.Q6_K, GGMLType.Q8_0, GGMLType.BF16, GGMLType.F16])
 @pytest.mark.parametrize("m,n,k", [(128, 128, 256), (512, 1024, 4096), (77, 200, 512), (1, 128, 1024)])
 def test_gemm_q_dequant_fused(t, m, n, k):
@@ -266,7 +289,8 @@ def test_gemm_q_dequant_fused(t, m, n, k):
     K.gemm_q(x, dw, out=out, out_off=4)
     torch.cuda.synchronize()
     assert K.gemm_status() == 0
-    tol = 1e-3 + 2e-3 * ref.abs().max().item()
+    # block scales / minima of the K-quants are rounded to bf16 inside the kernel (the expansion runs in packed bf16 arithmetic)
+    tol = 1e-3 + (6e-3 if t in (GGMLType.Q4_K, GGMLType.Q6_K) else 2e-3) * ref.abs().max().item()
     assert torch.allclose(out[:, 4:4 + n].cpu(), ref, atol=tol, rtol=2e-3), (out[:, 4:4 + n].cpu() - ref).abs().max()
     assert out[:, :4].abs().max() == 0 and out[:, 4 + n:].abs().max() == 0      # neighbours of the output window stay untouched
     K.gemm_q(x, dw, out=out, accumulate=True, out_off=4)
