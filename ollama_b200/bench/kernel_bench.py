@@ -28,6 +28,15 @@ CASES = [
     ("down-8b-q6k", "gemv", [(4096, GGMLType.Q6_K)], 14336),
     ("head-8b", "gemv", [(128256, GGMLType.Q6_K)], 4096),
     ("glu-70b", "glu", [(28672, GGMLType.Q4_K)], 8192),
+    # per-rank shards of Llama-70B split 2 and 8 ways
+    ("qkv-70b-tp2", "gemv", [(4096, GGMLType.Q4_K), (512, GGMLType.Q4_K), (512, GGMLType.Q6_K)], 8192),
+    ("o-70b-tp2", "gemv", [(8192, GGMLType.Q4_K)], 4096),
+    ("glu-70b-tp2", "glu", [(14336, GGMLType.Q4_K)], 8192),
+    ("down-70b-tp2", "gemv", [(8192, GGMLType.Q6_K)], 14336),
+    ("qkv-70b-tp8", "gemv", [(1024, GGMLType.Q4_K), (128, GGMLType.Q4_K), (128, GGMLType.Q6_K)], 8192),
+    ("o-70b-tp8", "gemv", [(8192, GGMLType.Q4_K)], 1024),
+    ("glu-70b-tp8", "glu", [(3584, GGMLType.Q4_K)], 8192),
+    ("down-70b-tp8", "gemv", [(8192, GGMLType.Q6_K)], 3584),
     ("o-8b-q8", "gemv", [(4096, GGMLType.Q8_0)], 4096),
     ("o-8b-bf16", "gemv", [(4096, GGMLType.BF16)], 4096),
 ]

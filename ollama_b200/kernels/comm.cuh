@@ -38,6 +38,7 @@ struct CommSend {
     unsigned* peer_flag[COMM_MAX_RANKS];   // &channel_on_rank_r->flag[rank]
     float* dst[COMM_MAX_RANKS];      // destination base on rank r, already offset to this rank's slab or column range
     long long parity_stride;         // elements between the two halves of a double-buffered destination (0: single buffer)
+    int ll;                          // 1: low-latency protocol, dst holds (value, epoch) pairs and nothing is announced (see below)
 };
 
 __device__ __forceinline__ unsigned ld_volatile_u32(const unsigned* p) {
@@ -67,9 +68,11 @@ __device__ __forceinline__ long long comm_parity_off(const CommSend& c, unsigned
 
 // Called by every thread of every CTA of a producer kernel after its last peer store.
 __device__ __forceinline__ void comm_publish(const CommSend& c, unsigned total_ctas, unsigned e) {
-    __threadfence_system();
+    // The CTA barrier orders every thread's stores before thread 0's fence, and the fence is cumulative, so one
+    // system-scope fence per CTA is enough (a fence in every warp costs microseconds once thousands of them queue up).
     __syncthreads();
     if (threadIdx.x == 0) {
+        __threadfence_system();
         const unsigned t = atomicAdd(&c.local->ticket, 1u);
         if (t == total_ctas - 1u) {
             __threadfence();
@@ -87,6 +90,7 @@ __device__ __forceinline__ bool comm_wait_flags(CommChan* ch, int n, unsigned e)
     if ((int)threadIdx.x >= n) return true;
     const unsigned* f = &ch->flag[threadIdx.x];
     if ((int)(ld_acquire_sys_u32(f) - e) >= 0) return true;
+    if (*(volatile int*)&ch->status != 0) return false;      // an earlier wait already ran out: the host clears the status
     const unsigned long long t0 = global_ns();
     const unsigned ms = ld_volatile_u32(&ch->wait_ms);
     const unsigned long long limit = (unsigned long long)(ms ? ms : 2000u) * 1000000ull;
@@ -96,6 +100,57 @@ __device__ __forceinline__ bool comm_wait_flags(CommChan* ch, int n, unsigned e)
         if (global_ns() - t0 > limit) {
             atomicExch(&ch->status, (int)KS_TIMEOUT);
             return false;
+        }
+    }
+}
+
+// ---------------------------------------------------------------------------------------------
+// Low-latency exchange for small messages (decode): every 8-byte word carries a value and the epoch it
+// belongs to, so the data is its own flag.  The producer needs no fence, ticket or flag store (an aligned
+// 8-byte store arrives whole), and the consumer polls the words it is about to use.  Destinations are
+// double-buffered on the epoch's parity, so a stale word carries epoch e - 2 and can never be mistaken
+// for a fresh one.  The consumer advances the channel's epoch when its last CTA finishes.
+// ---------------------------------------------------------------------------------------------
+__device__ __forceinline__ uint4 ld_volatile_u4(const void* p) {
+    uint4 v;
+    asm volatile("ld.volatile.global.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p) : "memory");
+    return v;
+}
+
+// Two consecutive (value, epoch) words; spins (bounded) until both carry epoch e.  Returns false after the time limit.
+__device__ __forceinline__ bool ll_read2(const void* p, unsigned e, CommChan* ch, float& v0, float& v1) {
+    uint4 w = ld_volatile_u4(p);
+    if (w.y != e || w.w != e) {
+        if (*(volatile int*)&ch->status != 0) {      // an earlier wait already ran out: do not wait again until the host clears it
+            v0 = v1 = 0.f;
+            return false;
+        }
+        const unsigned long long t0 = global_ns();
+        const unsigned ms = ld_volatile_u32(&ch->wait_ms);
+        const unsigned long long limit = (unsigned long long)(ms ? ms : 2000u) * 1000000ull;
+        for (;;) {
+            w = ld_volatile_u4(p);
+            if (w.y == e && w.w == e) break;
+            if (global_ns() - t0 > limit) {
+                atomicExch(&ch->status, (int)KS_TIMEOUT);
+                v0 = v1 = 0.f;
+                return false;
+            }
+        }
+    }
+    v0 = __uint_as_float(w.x);
+    v1 = __uint_as_float(w.z);
+    return true;
+}
+
+// Consumer side: called by every thread at the end of the kernel; the last CTA makes `e` the channel's epoch.
+__device__ __forceinline__ void ll_consumed(CommChan* ch, unsigned total_ctas, unsigned e) {
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        const unsigned t = atomicAdd(&ch->ticket, 1u);
+        if (t == total_ctas - 1u) {
+            *(volatile unsigned*)&ch->ticket = 0u;
+            *(volatile unsigned*)&ch->epoch = e;
         }
     }
 }

@@ -20,10 +20,10 @@ struct NormQuantArgs {
     float* xf;           // [nb][k] or null
     float* residual;     // if set: residual[b][i] += y   (post-norm residual add of sandwich-norm models)
     // tensor parallel: x[b] += sum over ranks of the partial rows received from the group, before anything else
-    const float* parts;      // [2 halves][n_part][rows][k] in this rank's peer-mapped region (null: none)
+    const uint2* parts;      // [2 halves][n_part][rows][k] (value, epoch) pairs in this rank's peer-mapped region (null: none)
     int n_part;
-    long long part_stride;   // elements between the slabs of two ranks
-    long long parity_stride; // elements between the two halves
+    long long part_stride;   // pairs between the slabs of two ranks
+    long long parity_stride; // pairs between the two halves
     CommChan* chan;
 };
 
@@ -46,12 +46,11 @@ __global__ void __launch_bounds__(256) rmsnorm_quant_kernel(const __grid_constan
     pdl_launch();
     pdl_wait();
     const float* x = a.x + (size_t)b * a.k;
-    const float* part = nullptr;
-    if (a.n_part) {      // the producer of this rank has finished (grid dependency); wait for the other ranks' rows
-        const unsigned e = ld_volatile_u32(&a.chan->epoch);
-        comm_wait_flags(a.chan, a.n_part, e);
-        __syncthreads();
-        part = a.parts + ((e & 1u) ? a.parity_stride : 0ll) + (size_t)b * a.k;
+    const uint2* part = nullptr;
+    unsigned ep = 0;
+    if (a.n_part) {      // low-latency exchange: the words of this epoch arrive from every rank while we poll them
+        ep = ld_volatile_u32(&a.chan->epoch) + 1u;
+        part = a.parts + ((ep & 1u) ? a.parity_stride : 0ll) + (size_t)b * a.k;
     }
     for (int c0 = 0; c0 < nchunk; c0 += 256 * MAXJ) {     // one trip for k <= 8192
         float4 v[MAXJ];
@@ -66,8 +65,11 @@ __global__ void __launch_bounds__(256) rmsnorm_quant_kernel(const __grid_constan
                 for (int j = 0; j < MAXJ; j++) {
                     const int c = tid + 256 * j;
                     if (c < nchunk) {
-                        const float4 t = __ldcg((const float4*)(part + r * a.part_stride + 4 * c));   // written by a peer: read through L2
-                        v[j].x += t.x; v[j].y += t.y; v[j].z += t.z; v[j].w += t.w;
+                        const uint2* pp = part + r * a.part_stride + 4 * c;
+                        float t0, t1, t2, t3;
+                        ll_read2(pp, ep, a.chan, t0, t1);
+                        ll_read2(pp + 2, ep, a.chan, t2, t3);
+                        v[j].x += t0; v[j].y += t1; v[j].z += t2; v[j].w += t3;
                     }
                 }
             }
@@ -133,6 +135,7 @@ __global__ void __launch_bounds__(256) rmsnorm_quant_kernel(const __grid_constan
             }
         }
     }
+    if (a.n_part) ll_consumed(a.chan, gridDim.x, ep);
 }
 
 B2_API int b2_rmsnorm_quant(const NormQuantArgs* a, int nb, int pdl, cudaStream_t st) {

@@ -186,11 +186,16 @@ __global__ void __launch_bounds__(256, (NB <= 2 ? 2 : 1)) gemv_kernel(const __gr
                 if (row < w.n && b < a.nb) {
                     const float v = flat[e] + (w.bias ? w.bias[row] : 0.f);
                     const long long o = poff + (long long)b * a.ldo + w.out_off + row;
-                    for (int d = 0; d < a.cm.n_dst; d++) a.cm.dst[d][o] = v;
+                    if (a.cm.ll) {
+                        const uint2 pair = make_uint2(__float_as_uint(v), ep);       // the value travels with its epoch
+                        for (int d = 0; d < a.cm.n_dst; d++) reinterpret_cast<uint2*>(a.cm.dst[d])[o] = pair;
+                    } else {
+                        for (int d = 0; d < a.cm.n_dst; d++) a.cm.dst[d][o] = v;
+                    }
                 }
             }
         }
-        comm_publish(a.cm, gridDim.x, ep);
+        if (!a.cm.ll) comm_publish(a.cm, gridDim.x, ep);
     }
 }
 

@@ -65,7 +65,7 @@ COMM_MAX_RANKS = 8
 class CommSend(C.Structure):
     """Destinations and flags of one producer-side exchange (kernels/comm.cuh)."""
     _fields_ = [("n_dst", C.c_int), ("rank", C.c_int), ("local", C.c_void_p), ("peer_flag", C.c_void_p * COMM_MAX_RANKS),
-                ("dst", C.c_void_p * COMM_MAX_RANKS), ("parity_stride", C.c_longlong)]
+                ("dst", C.c_void_p * COMM_MAX_RANKS), ("parity_stride", C.c_longlong), ("ll", C.c_int)]
 
 
 class GemvArgs(C.Structure):

@@ -124,7 +124,7 @@ class TPBackend(B200Backend):
             self.region.close()
         lay = Layout()
         self.rpr_max = (self.max_chunk + N - 1) // N
-        self.b_dec = lay.add("dec_parts", 2 * N * MB * c.d_model * 4)
+        self.b_dec = lay.add("dec_parts", 2 * N * MB * c.d_model * 8)          # (value, epoch) pairs, two halves
         self.b_logits = lay.add("logits", MB * c.vocab_size * 4)
         self.b_parts = lay.add("pre_parts", N * self.rpr_max * c.d_model * 4)
         self.b_h = lay.add("h_full", self.max_chunk * c.d_model * 2)
@@ -133,9 +133,10 @@ class TPBackend(B200Backend):
         b.logits = reg.tensor(self.b_logits, (MB, c.vocab_size), torch.float32)
         self.h_full = reg.tensor(self.b_h, (self.max_chunk, c.d_model), torch.bfloat16)
         self.xs = torch.zeros(self.rpr_max, c.d_model, device=self.device, dtype=torch.float32)
-        slab = MB * c.d_model * 4
-        # partial rows of a decode exchange land in slab `rank` of every rank's receive buffer
+        slab = MB * c.d_model * 8
+        # partial rows of a decode exchange land in slab `rank` of every rank's receive buffer (low-latency protocol)
         self.cm_dec = reg.send(CH_DEC, [reg.addr(self.b_dec, r, self.rank * slab) for r in range(N)], parity_stride=N * MB * c.d_model)
+        self.cm_dec.ll = 1
         # logits: this rank's vocabulary rows are columns [v_lo, v_lo + n) of every rank's logits buffer
         self.cm_logits = reg.send(CH_LOGITS, [reg.addr(self.b_logits, r, self.v_lo * 4) for r in range(N)])
         self.cm_ag = reg.send(CH_AG, [reg.addr(self.b_h, r) for r in range(N)])
