@@ -202,8 +202,17 @@ def main() -> None:
 
     # ---- end to end through the public runner API --------------------------------------------------
     e2e = None
-    if not args.no_e2e and n_gpus == 1:
-        r = Runner(None, RunnerOptions(num_ctx=wl["ctx"], num_parallel=slots, device=dev, num_batch=max(P, 512)), backend=be)
+    runner_be = be
+    if not args.no_e2e and n_gpus > 1:
+        # the serving stack runs in rank 0 only; the other ranks repeat its backend calls until it closes the group
+        from ollama_b200.parallel.control import TPControl, TPLeader, follow
+        ctl = TPControl(rank, world)
+        if rank == 0:
+            runner_be = TPLeader(be, ctl)
+        else:
+            follow(be, ctl)
+    if not args.no_e2e and rank == 0:
+        r = Runner(None, RunnerOptions(num_ctx=wl["ctx"], num_parallel=slots, device=dev, num_batch=max(P, 512)), backend=runner_be)
         r.n_ctx = wl["ctx"]
         sp = SamplingParams(temperature=0)
         def one_epoch():

@@ -1,0 +1,117 @@
+"""Host-side logic of the tensor-parallel engine: weight sharding and the leader/follower control channel (gloo, CPU)."""
+import json
+import os
+import socket
+
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+from ollama_b200.models.config import config_from_gguf
+from ollama_b200.models.synth import SyntheticTensors, synthetic_header
+
+
+def test_shards_recombine_to_the_full_matrices():
+    from ollama_b200.parallel.tp_engine import ShardedTensors, shard_plan
+    cfg = config_from_gguf(synthetic_header("tiny-tp", "Q4_K_M"))
+    src = SyntheticTensors("tiny-tp", "Q4_K_M")
+    world = 4
+    shards = [ShardedTensors(src, cfg, r, world) for r in range(world)]
+    # column-parallel: rows concatenate
+    for leaf in ("attn_q", "attn_k", "attn_v", "ffn_gate", "ffn_up"):
+        name = f"blk.1.{leaf}.weight"
+        full = src[name].dequant()
+        assert torch.equal(torch.cat([s[name].dequant() for s in shards]), full)
+    # row-parallel: partial products add up
+    for leaf, k in (("attn_output", cfg.q_dim), ("ffn_down", cfg.d_ff)):
+        name = f"blk.0.{leaf}.weight"
+        full = src[name].dequant()
+        x = torch.randn(3, k, generator=torch.Generator().manual_seed(1))
+        acc = sum(x[:, r * k // world:(r + 1) * k // world] @ shards[r][name].dequant().t() for r in range(world))
+        assert torch.allclose(acc, x @ full.t(), atol=1e-5)
+    # vocabulary rows
+    out = torch.cat([s["output.weight"].dequant() for s in shards])
+    assert torch.equal(out, src["output.weight"].dequant())
+    # replicated tensors pass through
+    assert torch.equal(shards[2]["blk.0.attn_norm.weight"].dequant(), src["blk.0.attn_norm.weight"].dequant())
+    with pytest.raises(ValueError):
+        shard_plan(cfg, 3)
+    with pytest.raises(ValueError):      # 16 heads x 64 / 16 ranks = 64 columns: not a multiple of the 256-element K-quant block
+        shard_plan(config_from_gguf(synthetic_header("tiny-tp", "Q4_K_M")), 16)
+
+
+class _FakeBackend:
+    name = "fake"
+
+    def __init__(self, log):
+        self.log, self.use_graphs, self.pdl = log, True, True
+
+    def _rec(self, *a):
+        self.log.append(list(a))
+
+    def alloc(self, n_slots, n_ctx):
+        self._rec("alloc", n_slots, n_ctx)
+
+    def prefill(self, slot, tokens, pos0, need_logits=True):
+        self._rec("prefill", slot, list(tokens), pos0, bool(need_logits))
+        return torch.zeros(4)
+
+    def hidden(self, slot, tokens):
+        self._rec("hidden", slot, list(tokens))
+        return torch.zeros(1, 4)
+
+    def decode(self, slots, tokens, positions):
+        self._rec("decode", list(slots), list(tokens), list(positions))
+        return torch.zeros(len(slots), 4)
+
+    def decode_argmax(self, slots, tokens, positions):
+        self._rec("decode_argmax", list(slots), list(tokens), list(positions))
+        return [0] * len(slots)
+
+    def decode_loop(self, slots, tokens, positions, n_steps, first_tokens=None):
+        self._rec("decode_loop", list(slots), list(tokens), list(positions), n_steps)
+        return torch.zeros(n_steps, len(slots))
+
+    def close(self):
+        self._rec("close")
+
+
+def _worker(rank, world, port, out_dir):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    from ollama_b200.parallel.control import TPControl, TPLeader, follow
+    log = []
+    be = _FakeBackend(log)
+    ctl = TPControl(rank, world)
+    if rank == 0:
+        lead = TPLeader(be, ctl)
+        lead.set_flags(False, True)
+        lead.alloc(4, 256)
+        lead.prefill(2, list(range(100)), 0, True)        # longer than one record: travels as a second message
+        lead.prefill(1, [5, 6, 7], 100, False)
+        lead.decode([0, 3], [11, 12], [7, 9])
+        lead.decode_argmax([1], [42], [103])
+        lead.decode_loop([0, 1], [0, 0], [5, 6], 3, first_tokens=torch.tensor([8, 9]))
+        lead.hidden(0, [1, 2, 3])
+        lead.close()
+    else:
+        follow(be, ctl)
+    with open(os.path.join(out_dir, f"log{rank}.json"), "w") as f:
+        json.dump({"log": log, "flags": [be.use_graphs, be.pdl]}, f)
+    dist.destroy_process_group()
+
+
+def test_followers_repeat_the_leaders_calls(tmp_path):
+    s = socket.socket()
+    s.bind(("127.0.0.1", 0))
+    port = s.getsockname()[1]
+    s.close()
+    world = 3
+    mp.spawn(_worker, args=(world, port, str(tmp_path)), nprocs=world, join=True)
+    logs = [json.load(open(tmp_path / f"log{r}.json")) for r in range(world)]
+    assert logs[0]["log"][0] == ["alloc", 4, 256] and logs[0]["log"][-1] == ["close"]
+    assert ["decode_loop", [0, 1], [8, 9], [5, 6], 3] in logs[0]["log"]
+    for r in (1, 2):
+        assert logs[r]["log"] == logs[0]["log"]
+        assert logs[r]["flags"] == [False, True]
