@@ -33,8 +33,10 @@ MAX_DECODE_BATCH = 8
 
 
 def supports(cfg: ModelConfig) -> bool:
-    return cfg.arch in ("llama", "mistral", "qwen2", "qwen3", "gemma", "gemma2", "gemma3") and not cfg.is_moe \
-        and cfg.head_dim in (32, 64, 128, 256) and cfg.head_dim == cfg.v_head_dim and cfg.d_model % 256 == 0 \
+    if cfg.is_moe and (cfg.n_experts > 512 or cfg.n_experts_used > 16 or cfg.d_ff_expert % 32):
+        return False
+    return cfg.arch in ("llama", "mistral", "qwen2", "qwen3", "qwen3moe", "gpt-oss", "gemma", "gemma2", "gemma3") \
+        and cfg.head_dim in (32, 64, 128, 256) and cfg.head_dim == cfg.v_head_dim and cfg.d_model % 32 == 0 \
         and cfg.d_ff % 32 == 0
 
 
@@ -64,6 +66,8 @@ class B200Backend:
             est = 2 * (c.n_layers * (c.d_model * (2 * c.q_dim + 2 * c.kv_dim) + 3 * c.d_model * c.d_ff) + c.vocab_size * c.d_model)
             keep_bf16 = prefill_gemm == "bf16" and est < 0.4 * torch.cuda.mem_get_info(self.device)[0]
         self.keep_bf16 = keep_bf16
+        if not hasattr(self, "e_lo"):       # experts resident on this GPU (a tensor-parallel subclass narrows the range)
+            self.e_lo, self.e_cnt = 0, self.cfg.n_experts
         self.n_slots = self.n_ctx = 0
         self._graphs: dict[tuple[int, bool], torch.cuda.CUDAGraph] = {}
         self.pdl = True
@@ -112,13 +116,25 @@ class B200Backend:
             if L.ffn_norm is None:
                 L.ffn_norm = vec(p + "post_attention_norm.weight")
             L.post_ffw_norm = vec(p + "post_ffw_norm.weight") if c.sandwich_norm else None
-            L.gate, L.up, L.down = mat(p + "ffn_gate", False), mat(p + "ffn_up", False), mat(p + "ffn_down")
+            L.moe = c.is_moe and has(p + "ffn_gate_inp.weight")
+            if L.moe:
+                # experts stay stacked: [E][n][k] planes, the expert index selects a row range inside the kernels
+                L.router = mat(p + "ffn_gate_inp", False)
+                L.router_f32 = get(p + "ffn_gate_inp.weight").dequant().to(dev).contiguous()
+
+                def exps(kind):
+                    b = vec(p + f"ffn_{kind}_exps.bias")
+                    return K.repack(get(p + f"ffn_{kind}_exps.weight"), dev, bias=b.reshape(-1) if b is not None else None)
+
+                L.gate, L.up, L.down = exps("gate"), exps("up"), exps("down")
+            else:
+                L.gate, L.up, L.down = mat(p + "ffn_gate", False), mat(p + "ffn_up", False), mat(p + "ffn_down")
             if L.gate.wtype != L.up.wtype:
                 L.gu = K.interleave_rows(K.to_f16(L.gate), K.to_f16(L.up))
             else:
                 L.gu = K.interleave_rows(L.gate, L.up)
             L.gate.planes, L.up.planes = [], []      # the interleaved matrix serves decode and prefill
-            if self.keep_bf16:
+            if self.keep_bf16 and not L.moe:
                 L.gu.bf16 = K.dequant_to_bf16(L.gu)
             L.sinks = vec(p + "attn_sinks.weight")
             L.swa = c.layer_is_swa(i)
@@ -167,9 +183,17 @@ class B200Backend:
         b.ao = torch.zeros(MB, c.q_dim, device=dev, dtype=f32)
         b.aq = torch.zeros(MB, c.q_dim, device=dev, dtype=i8)
         b.ads = torch.zeros(MB, c.q_dim // 32, 2, device=dev, dtype=f32)
-        b.hq = torch.zeros(MB, c.d_ff, device=dev, dtype=i8)
-        b.hds = torch.zeros(MB, c.d_ff // 32, 2, device=dev, dtype=f32)
-        b.hf = torch.zeros(MB, c.d_ff, device=dev, dtype=f32)
+        ff = max(c.d_ff_expert, c.d_ff) if c.is_moe else c.d_ff
+        hr = MB * max(c.n_experts_used, 1) if c.is_moe else MB          # MoE: one row per (token, expert-slot) pair
+        b.hq = torch.zeros(hr, ff, device=dev, dtype=i8)
+        b.hds = torch.zeros(hr, ff // 32, 2, device=dev, dtype=f32)
+        b.hf = torch.zeros(hr, ff, device=dev, dtype=f32)
+        if c.is_moe:
+            b.rlogits = torch.zeros(MB, c.n_experts, device=dev, dtype=f32)
+            b.moe_ids = torch.zeros(hr, device=dev, dtype=i32)
+            b.moe_lids = torch.zeros(hr, device=dev, dtype=i32)
+            b.moe_w = torch.zeros(hr, device=dev, dtype=f32)
+            b.ey = torch.zeros(hr, c.d_model, device=dev, dtype=f32)
         b.logits = torch.zeros(MB, c.vocab_size, device=dev, dtype=f32)
         b.part_acc = torch.zeros(MB * c.n_heads * self.n_splits * c.head_dim, device=dev, dtype=f32)
         b.part_ml = torch.zeros(MB * c.n_heads * self.n_splits * 2, device=dev, dtype=f32)
@@ -206,6 +230,77 @@ class B200Backend:
         K._check(K.lib().b2_gemv(C.byref(a), int(self.pdl), K.stream()), "gemv")
         self._n += 1
 
+    def _route(self, logits: torch.Tensor, tokens: int, ids, lids, wts, pdl: bool) -> None:
+        c = self.cfg
+        a = K.MoeRouteArgs(K.ptr(logits), logits.stride(0), c.n_experts, c.n_experts_used, 0 if c.moe_router == "softmax_topk" else 1,
+                           int(c.moe_norm_topk), self.e_lo, self.e_cnt, K.ptr(ids), K.ptr(lids), K.ptr(wts))
+        K._check(K.lib().b2_moe_route(C.byref(a), tokens, int(pdl), K.stream()), "moe_route")
+
+    def _moe_decode(self, L, nb: int, act: int, cm=None) -> None:
+        """Router -> top-k -> expert gate/up + GLU -> expert down -> weighted sum into the residual stream.
+
+        Every (token, expert-slot) pair is one grid row of the indirect GEMV kernels; experts that live on another
+        GPU produce zero rows.  With ``cm`` the weighted sum is sent to the tensor-parallel group instead of being added.
+        """
+        c, b, lib, st = self.cfg, self.buf, K.lib(), K.stream
+        k = c.n_experts_used
+        pairs = nb * k
+        self._gemv([L.router], nb, b.xq, b.xds, b.xf, b.rlogits, b.rlogits.stride(0))
+        self._route(b.rlogits, nb, b.moe_ids, b.moe_lids, b.moe_w, self.pdl)
+        ga = K.GluArgs()
+        ga.gu = L.gu.desc()
+        ga.nb, ga.xq, ga.xds, ga.xf = 1, K.ptr(b.xq), K.ptr(b.xds), K.ptr(b.xf)
+        ga.act, ga.alpha, ga.limit = act, c.swiglu_alpha, c.swiglu_limit
+        ga.hq, ga.hds, ga.hf = K.ptr(b.hq), K.ptr(b.hds), K.ptr(b.hf) if not L.down.quant_input else None
+        ga.ids, ga.x_div, ga.n_pairs = K.ptr(b.moe_lids), k, pairs
+        K._check(lib.b2_gemv_glu_quant(C.byref(ga), int(self.pdl), st()), "gemv_glu_quant(moe)")
+        a = K.GemvArgs()
+        a.seg[0] = L.down.desc()
+        a.nseg, a.nb = 1, 1
+        a.xq, a.xds, a.xf, a.out, a.ldo, a.accumulate = K.ptr(b.hq), K.ptr(b.hds), K.ptr(b.hf), K.ptr(b.ey), c.d_model, 0
+        a.ids, a.x_div, a.n_pairs = K.ptr(b.moe_lids), 1, pairs
+        K._check(lib.b2_gemv(C.byref(a), int(self.pdl), st()), "gemv(moe down)")
+        ca = K.MoeCombineArgs(K.ptr(b.ey), K.ptr(b.moe_w), k, c.d_model, K.ptr(b.x))
+        if cm is not None:
+            ca.cm = cm
+        K._check(lib.b2_moe_combine(C.byref(ca), nb, int(self.pdl), st()), "moe_combine")
+        self._n += 4
+
+    def _moe_prefill(self, h: torch.Tensor, L) -> torch.Tensor:
+        """Expert FFN of a prefill chunk: tokens are grouped by expert and each resident expert runs one pair of GEMMs.
+
+        ``h``: [T, d_model] bf16.  Returns this GPU's (partial, under expert parallelism) FFN output [T, d_model] fp32.
+        """
+        c, dev = self.cfg, self.device
+        T, k, F = h.shape[0], c.n_experts_used, c.d_ff_expert
+        logits = h.float() @ L.router_f32.t()                       # [T, E]: tiny; kept in fp32 so that near-ties select as the fp32 graph does
+        if L.router.bias is not None:
+            logits = logits + L.router.bias
+        ids = torch.empty(T * k, device=dev, dtype=torch.int32)
+        lids, wts = torch.empty_like(ids), torch.empty(T * k, device=dev, dtype=torch.float32)
+        self._route(logits.contiguous(), T, ids, lids, wts, False)
+        order = torch.argsort(lids, stable=True)                     # pairs of experts that live elsewhere (-1) come first
+        counts = torch.bincount(lids[lids >= 0], minlength=self.e_cnt).tolist()
+        xs = h[(order // k).long()]                                  # activation row of every pair, grouped by expert
+        ys = torch.zeros(T * k, c.d_model, device=dev, dtype=torch.float32)
+        off = T * k - sum(counts)
+        for e, n in enumerate(counts):
+            if n == 0:
+                continue
+            wg = K.dequant_to_bf16(L.gu, e * 2 * F, 2 * F)
+            gb = L.gu.bias[e * 2 * F:(e + 1) * 2 * F] if L.gu.bias is not None else None
+            gu = K.gemm_bf16(xs[off:off + n], wg, gb)
+            f = R.glu(gu[:, 0::2], gu[:, 1::2], c.act, c.swiglu_alpha, c.swiglu_limit).to(torch.bfloat16)
+            wd = K.dequant_to_bf16(L.down, e * c.d_model, c.d_model)
+            db = L.down.bias[e * c.d_model:(e + 1) * c.d_model] if L.down.bias is not None else None
+            K.gemm_bf16(f, wd, db, out=ys[off:off + n])
+            self.kernel_launches += 4
+            off += n
+        y = torch.zeros_like(ys)
+        y[order] = ys
+        self.kernel_launches += 1
+        return (y.view(T, k, c.d_model) * wts.view(T, k, 1)).sum(1)
+
     def _decode_kernels(self, nb: int, want_argmax: bool) -> None:
         """Enqueue one decode step for ``nb`` sequences on the current stream (inputs: buf.tokens/positions/slots)."""
         c, b, lib, st = self.cfg, self.buf, K.lib(), K.stream
@@ -235,6 +330,9 @@ class B200Backend:
             else:
                 self._gemv([L.wo], nb, b.aq, b.ads, b.ao, b.x, b.x.stride(0), accumulate=True)
             self._norm_quant(b.x, L.ffn_norm, nb, c.d_model)
+            if L.moe:
+                self._moe_decode(L, nb, act)
+                continue
             ga = K.GluArgs()
             ga.gu = L.gu.desc()
             ga.nb, ga.xq, ga.xds, ga.xf = nb, K.ptr(b.xq), K.ptr(b.xds), K.ptr(b.xf)
@@ -381,9 +479,12 @@ class B200Backend:
                 o = R.rmsnorm(o, L.post_attn_norm, c.norm_eps)
             x = x + o
             h = R.rmsnorm(x, L.ffn_norm, c.norm_eps).to(torch.bfloat16)
-            gu = self._mm(h, L.gu)                          # rows interleaved: even = gate, odd = up
-            f = R.glu(gu[:, 0::2], gu[:, 1::2], c.act, c.swiglu_alpha, c.swiglu_limit)
-            f = self._mm(f.to(torch.bfloat16), L.down)
+            if L.moe:
+                f = self._moe_prefill(h, L)
+            else:
+                gu = self._mm(h, L.gu)                      # rows interleaved: even = gate, odd = up
+                f = R.glu(gu[:, 0::2], gu[:, 1::2], c.act, c.swiglu_alpha, c.swiglu_limit)
+                f = self._mm(f.to(torch.bfloat16), L.down)
             if c.sandwich_norm:
                 f = R.rmsnorm(f, L.post_ffw_norm, c.norm_eps)
             x = x + f

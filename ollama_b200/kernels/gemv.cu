@@ -31,6 +31,12 @@ struct GemvArgs {
     int ldo;
     int accumulate;       // 1: out += result (residual add)
     CommSend cm;          // cm.n_dst > 0: write the result to every rank's buffer instead of `out` (pitch ldo) and announce it
+    // mixture of experts (ids != null, nb = 1, one segment holding E stacked [n][k] matrices): grid.y enumerates
+    // (token, expert-slot) pairs; pair p multiplies expert ids[p] with activation row p / x_div and writes output row p.
+    // ids[p] < 0 (expert not resident on this GPU) gives a zero row.
+    const int* ids;
+    int x_div;
+    int n_pairs;
 };
 
 struct GluArgs {
@@ -44,6 +50,10 @@ struct GluArgs {
     int8_t* hq;           // [nb][d_ff]
     float2* hds;          // [nb][d_ff/32]
     float* hf;            // [nb][d_ff] or null
+    // mixture of experts (ids != null, nb = 1, gu holds E stacked matrices): see GemvArgs
+    const int* ids;
+    int x_div;
+    int n_pairs;
 };
 
 __device__ __forceinline__ Planes planes_of(const WDesc& w) {
@@ -137,11 +147,15 @@ __global__ void __launch_bounds__(256, (NB <= 2 ? 2 : 1)) gemv_kernel(const __gr
         for (int b = 0; b < NB; b++) acc[r][b] = 0.f;
     pdl_launch();
     const Planes pl = planes_of(w);
-    if (active) prefetch_rows(pl, row0, R, w.n, ks * 32 + lane, KS * 32);
+    if (active && !a.ids) prefetch_rows(pl, row0, R, w.n, ks * 32 + lane, KS * 32);
     pdl_wait();
-    if (active) {
-        XRef<NB> x{a.xq, a.xds, a.xf, w.k, a.nb};
-        dot_any<R, NB>(w.type, pl, row0, w.n - 1, x, acc, ks * 32 + lane, KS * 32);
+    const int pair = a.ids ? (int)blockIdx.y : 0;
+    const int expert = a.ids ? a.ids[pair] : 0;
+    const int erow = expert * w.n;                   // first row of the selected expert in the stacked planes
+    if (active && expert >= 0) {
+        const size_t xo = a.ids ? (size_t)(pair / a.x_div) : 0;
+        XRef<NB> x{a.xq + xo * w.k, a.xds + xo * (w.k >> 5), a.xf ? a.xf + xo * w.k : nullptr, w.k, a.nb};
+        dot_any<R, NB>(w.type, pl, erow + row0, erow + w.n - 1, x, acc, ks * 32 + lane, KS * 32);
     }
     float(&flat)[M] = reinterpret_cast<float(&)[M]>(acc);
     const int base = warp_reduce_scatter<M>(flat, lane);
@@ -170,8 +184,8 @@ __global__ void __launch_bounds__(256, (NB <= 2 ? 2 : 1)) gemv_kernel(const __gr
             const int idx = base + e, r = idx / NB, b = idx % NB;
             const int row = row0 + r;
             if (row < w.n && b < a.nb) {
-                float* o = a.out + (size_t)b * a.ldo + w.out_off + row;
-                const float v = flat[e] + (w.bias ? w.bias[row] : 0.f);
+                float* o = a.out + (size_t)(pair + b) * a.ldo + w.out_off + row;
+                const float v = expert >= 0 ? flat[e] + (w.bias ? w.bias[erow + row] : 0.f) : 0.f;
                 *o = a.accumulate ? *o + v : v;
             }
         }
@@ -210,9 +224,13 @@ __global__ void __launch_bounds__(WARPS * 32) glu_kernel(const __grid_constant__
     const int n_out = a.gu.n >> 1;
     pdl_launch();
     const Planes pl = planes_of(a.gu);
-    prefetch_rows(pl, (blockIdx.x * 32 + warp * PASSES * 2) * 2, R * PASSES, a.gu.n, lane, 32);
+    if (!a.ids) prefetch_rows(pl, (blockIdx.x * 32 + warp * PASSES * 2) * 2, R * PASSES, a.gu.n, lane, 32);
     pdl_wait();
-    XRef<NB> x{a.xq, a.xds, a.xf, a.gu.k, a.nb};
+    const int pair = a.ids ? (int)blockIdx.y : 0;
+    const int expert = a.ids ? a.ids[pair] : 0;
+    const int erow = expert * a.gu.n;
+    const size_t xo = a.ids ? (size_t)(pair / a.x_div) : 0;
+    XRef<NB> x{a.xq + xo * a.gu.k, a.xds + xo * (a.gu.k >> 5), a.xf ? a.xf + xo * a.gu.k : nullptr, a.gu.k, a.nb};
 #pragma unroll 1
     for (int pass = 0; pass < PASSES; pass++) {
         const int slot = (warp * PASSES + pass) * 2;         // position of this warp's two outputs in the block of 32
@@ -223,13 +241,13 @@ __global__ void __launch_bounds__(WARPS * 32) glu_kernel(const __grid_constant__
         for (int r = 0; r < R; r++)
 #pragma unroll
             for (int b = 0; b < NB; b++) acc[r][b] = 0.f;
-        if (out0 < n_out) dot_any<R, NB>(a.gu.type, pl, row0, a.gu.n - 1, x, acc, lane, 32);
+        if (out0 < n_out && expert >= 0) dot_any<R, NB>(a.gu.type, pl, erow + row0, erow + a.gu.n - 1, x, acc, lane, 32);
         // biases join lane 0's partial sums: row r of the warp is gate (r even) or up (r odd)
-        if (a.gu.bias && out0 < n_out && lane == 0) {
+        if (a.gu.bias && out0 < n_out && lane == 0 && expert >= 0) {
 #pragma unroll
             for (int r = 0; r < R; r++)
 #pragma unroll
-                for (int b = 0; b < NB; b++) acc[r][b] += a.gu.bias[min(row0 + r, a.gu.n - 1)];
+                for (int b = 0; b < NB; b++) acc[r][b] += a.gu.bias[erow + min(row0 + r, a.gu.n - 1)];
         }
         // plain reductions here: gate and up of one output must end up in the same lane
 #pragma unroll
@@ -252,11 +270,12 @@ __global__ void __launch_bounds__(WARPS * 32) glu_kernel(const __grid_constant__
         const int q = d > 0.f ? __float2int_rn(v / d) : 0;
         const float s = d * warp_sum((float)q);
         const int col = blockIdx.x * 32 + lane;
+        const size_t orow = (size_t)(pair + b);
         if (col < n_out) {
-            a.hq[(size_t)b * n_out + col] = (int8_t)q;
-            if (a.hf) a.hf[(size_t)b * n_out + col] = v;
+            a.hq[orow * n_out + col] = (int8_t)q;
+            if (a.hf) a.hf[orow * n_out + col] = v;
         }
-        if (lane == 0) a.hds[(size_t)b * (n_out >> 5) + blockIdx.x] = make_float2(d, s);
+        if (lane == 0) a.hds[orow * (n_out >> 5) + blockIdx.x] = make_float2(d, s);
     }
 }
 
@@ -302,10 +321,12 @@ B2_API int b2_gemv(const GemvArgs* a, int pdl, cudaStream_t st) {
         min_items = min(min_items, items_per_row(a->seg[s].type, a->seg[s].k));
     }
     // split the row length over KS warps until ~4000 warps exist (148 SMs x ~28) or a lane has one item left
+    const int pairs = a->ids ? a->n_pairs : 1;
+    if (a->ids && (a->nb != 1 || a->nseg != 1 || a->cm.n_dst > 0 || a->x_div < 1 || pairs < 1 || pairs > 65535)) return (int)cudaErrorInvalidValue;
     int ks = 1;
-    while (ks < 8 && groups * ks < 4000 && min_items / (32 * ks * 2) >= 1) ks <<= 1;
+    while (ks < 8 && groups * pairs * ks < 4000 && min_items / (32 * ks * 2) >= 1) ks <<= 1;
     const int rgs = 8 / ks;
-    dim3 grid((unsigned)((groups + rgs - 1) / rgs)), block(256);
+    dim3 grid((unsigned)((groups + rgs - 1) / rgs), (unsigned)pairs), block(256);
     GemvArgs copy = *a;
     void* args[] = {&copy};
     if (a->cm.n_dst < 0 || a->cm.n_dst > COMM_MAX_RANKS || (a->cm.n_dst > 0 && a->accumulate)) return (int)cudaErrorInvalidValue;
@@ -315,7 +336,8 @@ B2_API int b2_gemv(const GemvArgs* a, int pdl, cudaStream_t st) {
 
 B2_API int b2_gemv_glu_quant(const GluArgs* a, int pdl, cudaStream_t st) {
     if (a->nb < 1 || a->nb > 8 || (a->gu.n & 63)) return (int)cudaErrorInvalidValue;
-    dim3 grid(a->gu.n / 64), block(a->nb <= 2 ? 512 : 256);
+    if (a->ids && (a->nb != 1 || a->x_div < 1 || a->n_pairs < 1 || a->n_pairs > 65535)) return (int)cudaErrorInvalidValue;
+    dim3 grid(a->gu.n / 64, a->ids ? a->n_pairs : 1), block(a->nb <= 2 ? 512 : 256);
     GluArgs copy = *a;
     void* args[] = {&copy};
     const void* fn = a->nb <= 1 ? (const void*)glu_kernel<1, 16> : a->nb <= 2 ? (const void*)glu_kernel<2, 16>

@@ -70,13 +70,23 @@ class CommSend(C.Structure):
 
 class GemvArgs(C.Structure):
     _fields_ = [("seg", WDesc * 4), ("nseg", C.c_int), ("nb", C.c_int), ("xq", C.c_void_p), ("xds", C.c_void_p),
-                ("xf", C.c_void_p), ("out", C.c_void_p), ("ldo", C.c_int), ("accumulate", C.c_int), ("cm", CommSend)]
+                ("xf", C.c_void_p), ("out", C.c_void_p), ("ldo", C.c_int), ("accumulate", C.c_int), ("cm", CommSend),
+                ("ids", C.c_void_p), ("x_div", C.c_int), ("n_pairs", C.c_int)]
 
 
 class GluArgs(C.Structure):
     _fields_ = [("gu", WDesc), ("nb", C.c_int), ("xq", C.c_void_p), ("xds", C.c_void_p), ("xf", C.c_void_p),
                 ("act", C.c_int), ("alpha", C.c_float), ("limit", C.c_float), ("hq", C.c_void_p), ("hds", C.c_void_p),
-                ("hf", C.c_void_p)]
+                ("hf", C.c_void_p), ("ids", C.c_void_p), ("x_div", C.c_int), ("n_pairs", C.c_int)]
+
+
+class MoeRouteArgs(C.Structure):
+    _fields_ = [("logits", C.c_void_p), ("ld", C.c_int), ("n_experts", C.c_int), ("k", C.c_int), ("mode", C.c_int), ("norm_topk", C.c_int),
+                ("e_lo", C.c_int), ("e_cnt", C.c_int), ("ids", C.c_void_p), ("lids", C.c_void_p), ("wts", C.c_void_p)]
+
+
+class MoeCombineArgs(C.Structure):
+    _fields_ = [("y", C.c_void_p), ("wts", C.c_void_p), ("k", C.c_int), ("d", C.c_int), ("x", C.c_void_p), ("cm", CommSend)]
 
 
 class NormQuantArgs(C.Structure):

@@ -188,7 +188,25 @@ def test_embed_and_argmax():
     assert K.argmax(lg).cpu().tolist() == lg.argmax(-1).cpu().tolist()
 
 
-@pytest.mark.parametrize("spec,ft", [("tiny-qwen3", "Q4_K_M"), ("tiny-gemma3", "Q8_0"), ("tiny-qwen2", "F16"), ("tiny-gemma2", "Q4_K_M")])
+def test_moe_route_kernel():
+    K = _K()
+    import ctypes as C
+    T, E, k = 37, 128, 8
+    logits = torch.randn(T, E, generator=torch.Generator().manual_seed(2)).cuda()
+    for mode, router, norm in ((0, "softmax_topk", True), (0, "softmax_topk", False), (1, "topk_softmax", True)):
+        ids = torch.zeros(T * k, dtype=torch.int32, device="cuda")
+        lids, wts = torch.zeros_like(ids), torch.zeros(T * k, device="cuda")
+        a = K.MoeRouteArgs(K.ptr(logits), E, E, k, mode, int(norm), 32, 64, K.ptr(ids), K.ptr(lids), K.ptr(wts))
+        K._check(K.lib().b2_moe_route(C.byref(a), T, 0, K.stream()), "moe_route")
+        rid, rw = R.moe_route(logits.cpu(), k, router, norm)
+        assert torch.equal(ids.view(T, k).cpu().long(), rid)
+        assert torch.allclose(wts.view(T, k).cpu(), rw, atol=1e-6, rtol=1e-5)
+        exp_l = torch.where((rid >= 32) & (rid < 96), rid - 32, torch.full_like(rid, -1))
+        assert torch.equal(lids.view(T, k).cpu().long(), exp_l)
+
+
+@pytest.mark.parametrize("spec,ft", [("tiny-qwen3", "Q4_K_M"), ("tiny-gemma3", "Q8_0"), ("tiny-qwen2", "F16"), ("tiny-gemma2", "Q4_K_M"),
+                                     ("tiny-qwen3moe", "Q4_K_M"), ("tiny-gpt-oss", "MXFP4"), ("tiny-mixtral", "Q8_0")])
 def test_engine_matches_reference_graph(tmp_path, spec, ft):
     """Whole-model check: prefill logits and 6 decode steps of the sm_100a engine vs the fp32 reference graph."""
     from ollama_b200.engine.b200 import B200Backend
