@@ -42,12 +42,19 @@ class TpNormGatherArgs(C.Structure):
 
 def shard_plan(cfg: ModelConfig, world: int, types: dict[str, int] | None = None) -> dict:
     """Per-rank sizes of a tensor-parallel split, or a ValueError saying why ``world`` does not divide the model."""
-    if cfg.n_heads % world or cfg.n_kv_heads % world:
-        raise ValueError(f"{world} ranks do not divide {cfg.n_heads} heads / {cfg.n_kv_heads} KV heads")
+    kv_rep = 1                     # ranks that share one KV head (its projection and cache are replicated on them)
+    if cfg.n_kv_heads % world:
+        if world % cfg.n_kv_heads:
+            raise ValueError(f"{world} ranks neither divide nor are a multiple of {cfg.n_kv_heads} KV heads")
+        kv_rep = world // cfg.n_kv_heads
+    if cfg.n_heads % world:
+        raise ValueError(f"{world} ranks do not divide {cfg.n_heads} heads")
     if cfg.d_ff % world:
         raise ValueError(f"{world} ranks do not divide the FFN width {cfg.d_ff}")
-    hl, kvl, fl = cfg.n_heads // world, cfg.n_kv_heads // world, cfg.d_ff // world
-    for name, cols in (("attn_output", hl * cfg.head_dim), ("ffn_down", fl)):
+    if cfg.is_moe and cfg.n_experts % world:
+        raise ValueError(f"{world} ranks do not divide {cfg.n_experts} experts")
+    hl, kvl, fl = cfg.n_heads // world, max(cfg.n_kv_heads // world, 1), cfg.d_ff // world
+    for name, cols in (("attn_output", hl * cfg.head_dim),) + (() if cfg.is_moe else (("ffn_down", fl),)):
         bs = max([block_size(t) for n, t in (types or {}).items() if n.endswith(name + ".weight")] or [256])
         if cols % bs:
             raise ValueError(f"{name}: {cols} columns per rank do not fall on {bs}-element quantisation blocks")
@@ -55,7 +62,7 @@ def shard_plan(cfg: ModelConfig, world: int, types: dict[str, int] | None = None
         raise ValueError(f"FFN width per rank {fl} is not a multiple of 32")
     vl = (cfg.vocab_size + world - 1) // world
     vl = (vl + 7) // 8 * 8
-    return {"heads": hl, "kv_heads": kvl, "d_ff": fl, "vocab_rows": vl}
+    return {"heads": hl, "kv_heads": kvl, "kv_rep": kv_rep, "d_ff": fl, "vocab_rows": vl, "experts": cfg.n_experts // world if cfg.is_moe else 0}
 
 
 class ShardedTensors:
@@ -85,7 +92,10 @@ class ShardedTensors:
         if leaf == "attn_q":
             return w.rows(r * p["heads"] * hd, (r + 1) * p["heads"] * hd)
         if leaf in ("attn_k", "attn_v"):
-            return w.rows(r * p["kv_heads"] * hd, (r + 1) * p["kv_heads"] * hd)
+            h0 = (r // p["kv_rep"]) * p["kv_heads"]
+            return w.rows(h0 * hd, (h0 + p["kv_heads"]) * hd)
+        if "_exps." in name:               # expert parallelism: whole experts, E / world per rank (weights [E, n, k], biases [E, n])
+            return w.rows(r * p["experts"], (r + 1) * p["experts"])
         if leaf in ("ffn_gate", "ffn_up"):
             return w.rows(r * p["d_ff"], (r + 1) * p["d_ff"])
         if name.endswith(".weight") and leaf == "attn_output":
@@ -111,6 +121,7 @@ class TPBackend(B200Backend):
         sh = ShardedTensors(tensors, cfg, rank, world)
         self.plan = sh.plan
         local = dataclasses.replace(cfg, n_heads=sh.plan["heads"], n_kv_heads=sh.plan["kv_heads"], d_ff=sh.plan["d_ff"])
+        self.e_lo, self.e_cnt = rank * sh.plan["experts"], sh.plan["experts"]      # expert parallelism: this rank's experts
         super().__init__(None, device=device, cfg=local, tensors=sh, keep_bf16=keep_bf16)
         self.v_lo = min(rank * sh.plan["vocab_rows"], cfg.vocab_size)
         if self.head.n != min(self.v_lo + sh.plan["vocab_rows"], cfg.vocab_size) - self.v_lo:
@@ -199,6 +210,9 @@ class TPBackend(B200Backend):
             self._n += 3
             self._gemv_send(L.wo, nb, b.aq, b.ads, b.ao, self.cm_dec, c.d_model)
             self._norm_quant_reduce(L.ffn_norm, nb)
+            if L.moe:      # expert parallel: local experts only; the weighted partial sum goes to every rank like a row-parallel GEMV
+                self._moe_decode(L, nb, act, cm=self.cm_dec)
+                continue
             ga = K.GluArgs()
             ga.gu = L.gu.desc()
             ga.nb, ga.xq, ga.xds, ga.xf = nb, K.ptr(b.xq), K.ptr(b.xds), K.ptr(b.xf)
@@ -288,6 +302,14 @@ class TPBackend(B200Backend):
                 o = o[0].transpose(0, 1).reshape(T, -1)
             self._mm_scatter(o.to(torch.bfloat16), L.wo, rpr)
             self._norm_gather(L.ffn_norm, rows, row0, reduce=True)
+            if L.moe:
+                # every rank holds all rows of h (the all-gather was the dispatch); its experts' partial output rows go to their owners
+                part = self._moe_prefill(h, L).contiguous()
+                f_sc = K.lib().b2_tp_scatter_rows
+                f_sc.argtypes = [C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_void_p, C.c_void_p]
+                K._check(f_sc(K.ptr(part), T, c.d_model, rpr, C.addressof(self.cm_rs), K.stream()), "tp_scatter_rows")
+                self.kernel_launches += 1
+                continue
             gu = self._mm(h, L.gu)
             f = R.glu(gu[:, 0::2], gu[:, 1::2], c.act, c.swiglu_alpha, c.swiglu_limit)
             self._mm_scatter(f.to(torch.bfloat16), L.down, rpr)

@@ -21,9 +21,10 @@ def _run(world: int, port: int, *extra: str) -> dict:
     return json.loads(lines[-1])
 
 
-@pytest.mark.parametrize("world,quant", [(2, "Q4_K_M"), (4, "Q8_0")])
-def test_tp_matches_single_gpu(world, quant):
+@pytest.mark.parametrize("world,model,quant", [(2, "tiny-tp", "Q4_K_M"), (2, "tiny-qwen3moe", "Q8_0"), (2, "tiny-gpt-oss", "MXFP4"),
+                                               (4, "tiny-tp", "Q8_0"), (8, "tiny-tp", "Q8_0")])
+def test_tp_matches_single_gpu(world, model, quant):
     if torch.cuda.device_count() < world:
         pytest.skip(f"needs {world} GPUs")
-    res = _run(world, 29540 + world, "--quant", quant)
+    res = _run(world, 29540 + world, "--model", model, "--quant", quant)
     assert res["ok"] and res["comm_status"] == 0
