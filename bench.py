@@ -29,8 +29,12 @@ sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
 WORKLOADS = {
     "llama-3.1-8b": dict(prompt=512, gen=128, ctx=8192, ft="Q4_K_M"),
     "llama-3.1-70b": dict(prompt=2048, gen=256, ctx=8192, ft="Q4_K_M"),
+    "gpt-oss-120b": dict(prompt=1024, gen=256, ctx=8192, ft="MXFP4", slots=16),
+    "qwen3-235b-a22b": dict(prompt=8192, gen=512, ctx=32768, ft="Q4_K_M", slots=32),
     "tiny-qwen3": dict(prompt=64, gen=32, ctx=512, ft="Q4_K_M"),
+    "tiny-qwen3moe": dict(prompt=64, gen=32, ctx=512, ft="Q8_0"),
 }
+PREFILL_CHUNK = 2048
 
 
 class ClockSampler:
@@ -95,7 +99,7 @@ def main() -> None:
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours")
     ap.add_argument("--model", default="auto")
-    ap.add_argument("--slots", type=int, default=1)
+    ap.add_argument("--slots", type=int, default=0, help="parallel sequences (0 = the workload's default)")
     ap.add_argument("--prompt", type=int, default=0)
     ap.add_argument("--gen", type=int, default=0)
     ap.add_argument("--ctx", type=int, default=0)
@@ -127,7 +131,7 @@ def main() -> None:
     for k in ("prompt", "gen", "ctx"):
         if getattr(args, k):
             wl[k] = getattr(args, k)
-    slots = args.slots
+    slots = args.slots if args.slots > 0 else wl.get("slots", 1)
 
     from ollama_b200.engine.runner import CompletionRequest, Runner, RunnerOptions
     from ollama_b200.engine.sampler import SamplingParams
@@ -165,7 +169,9 @@ def main() -> None:
         e0.record()
         firsts = []
         for s in slot_ids:
-            logits = be.prefill(s, prompts[s].tolist(), 0)
+            toks = prompts[s].tolist()
+            for c0 in range(0, P, PREFILL_CHUNK):
+                logits = be.prefill(s, toks[c0:c0 + PREFILL_CHUNK], c0, need_logits=c0 + PREFILL_CHUNK >= P)
             firsts.append(logits.argmax())
         first = torch.stack(firsts).to(torch.int32)
         e1.record()
@@ -212,7 +218,7 @@ def main() -> None:
         else:
             follow(be, ctl)
     if not args.no_e2e and rank == 0:
-        r = Runner(None, RunnerOptions(num_ctx=wl["ctx"], num_parallel=slots, device=dev, num_batch=max(P, 512)), backend=runner_be)
+        r = Runner(None, RunnerOptions(num_ctx=wl["ctx"], num_parallel=slots, device=dev, num_batch=min(max(P, 512), PREFILL_CHUNK)), backend=runner_be)
         r.n_ctx = wl["ctx"]
         sp = SamplingParams(temperature=0)
         def one_epoch():

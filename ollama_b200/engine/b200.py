@@ -393,6 +393,12 @@ class B200Backend:
 
     @torch.no_grad()
     def decode_argmax(self, slots: Sequence[int], tokens: Sequence[int], positions: Sequence[int]) -> list[int]:
+        if len(slots) > MAX_DECODE_BATCH:      # more sequences than one step takes: consecutive steps of up to eight
+            out: list[int] = []
+            for i in range(0, len(slots), MAX_DECODE_BATCH):
+                j = i + MAX_DECODE_BATCH
+                out += self.decode_argmax(slots[i:j], tokens[i:j], positions[i:j])
+            return out
         nb = self._stage(slots, tokens, positions)
         self._run_step(nb, True)
         self.buf.host_out.copy_(self.buf.sampled, non_blocking=True)
@@ -402,6 +408,9 @@ class B200Backend:
 
     @torch.no_grad()
     def decode(self, slots, tokens, positions) -> torch.Tensor:
+        if len(slots) > MAX_DECODE_BATCH:
+            return torch.cat([self.decode(slots[i:i + MAX_DECODE_BATCH], tokens[i:i + MAX_DECODE_BATCH], positions[i:i + MAX_DECODE_BATCH])
+                              for i in range(0, len(slots), MAX_DECODE_BATCH)])
         nb = self._stage(slots, tokens, positions)
         self._run_step(nb, False)
         return R.softcap(self.buf.logits[:nb].clone(), self.cfg.final_softcap)
@@ -414,6 +423,13 @@ class B200Backend:
         Returns the sampled ids as an int32 tensor [n_steps, nb] (still on the device).  Used by the
         benchmark's kernel-only measurement and by speculative prefixes where no stop condition can fire.
         """
+        if len(slots) > MAX_DECODE_BATCH:      # groups of up to eight sequences, one group after the other
+            parts = []
+            for i in range(0, len(slots), MAX_DECODE_BATCH):
+                j = i + MAX_DECODE_BATCH
+                parts.append(self.decode_loop(slots[i:j], tokens[i:j], positions[i:j], n_steps,
+                                              None if first_tokens is None else first_tokens[i:j]))
+            return torch.cat(parts, 1)
         nb = self._stage(slots, tokens, positions)
         if first_tokens is not None:          # ids that are already on the device (e.g. the arg-max of the prefill logits)
             self.buf.tokens[:nb].copy_(first_tokens.to(torch.int32))
@@ -438,6 +454,23 @@ class B200Backend:
             return K.gemm_bf16(x_bf16, wb, w.bias, out=out[:, out_off:out_off + w.n])
         return K.gemm_bf16(x_bf16, wb, w.bias)
 
+    def _attn_prefill(self, q: torch.Tensor, i: int, L, slot: int, pos0: int, p_end: int) -> torch.Tensor:
+        """Attention of a prefill chunk over cache positions [0, p_end): q [T, H, hd] fp32 -> bf16 [T, H * hd]."""
+        c = self.cfg
+        T = q.shape[0]
+        window = c.sliding_window if L.swa else 0
+        if c.head_dim in K.ATTN_PREFILL_HEAD_DIMS:
+            self.kernel_launches += 1
+            return K.attn_prefill(q, self.k_cache[i], self.v_cache[i], slot, pos0, p_end, self.attn_scale, c.causal, window,
+                                  c.attn_softcap, L.sinks)
+        # head sizes without a flash-attention instantiation (32, 256): plain torch attention over the same cache rows
+        kk = self.k_cache[i][slot, :, :p_end].transpose(0, 1)        # [S, Hkv, hd] f16
+        vv = self.v_cache[i][slot, :, :p_end].transpose(0, 1)
+        pos = torch.arange(pos0, p_end, device=q.device)
+        o = R.attention(q, kk, vv, pos, torch.arange(p_end, device=q.device), scale=self.attn_scale, causal=c.causal, window=window,
+                        softcap=c.attn_softcap, sinks=L.sinks)
+        return o.reshape(T, -1).to(torch.bfloat16)
+
     @torch.no_grad()
     def _forward_chunk(self, slot: int, tokens: Sequence[int], pos0: int) -> torch.Tensor:
         """Chunked prefill: returns the final hidden states [T, d_model] (fp32, before the output norm)."""
@@ -448,11 +481,6 @@ class B200Backend:
         slots = torch.full((T,), slot, device=dev, dtype=torch.int32)
         x = K.embed(self.embd, ids, c.embed_scale)
         p_end = pos0 + T
-        kpos = torch.arange(p_end, device=dev)
-        dp = pos.long()[:, None] - kpos[None, :]
-        base_mask = dp >= 0 if c.causal else torch.ones_like(dp, dtype=torch.bool)
-        swa_mask = base_mask & (dp < c.sliding_window) if c.sliding_window > 0 else base_mask
-        group = c.n_heads // c.n_kv_heads
         for i, L in enumerate(self.layers):
             h = R.rmsnorm(x, L.attn_norm, c.norm_eps).to(torch.bfloat16)
             qkv = torch.empty(T, (c.n_heads + 2 * c.n_kv_heads) * c.head_dim, device=dev, dtype=torch.float32)
@@ -463,18 +491,7 @@ class B200Backend:
             q = K.rope_kv(qkv, pos, slots, self.inv_freq_local if local else self.inv_freq, n_heads=c.n_heads, n_kv_heads=c.n_kv_heads,
                           hd=c.head_dim, n_rot=c.rope_dim, neox=c.rope_style == "neox", mscale=1.0 if local else self.mscale,
                           k_cache=self.k_cache[i], v_cache=self.v_cache[i], q_norm=L.q_norm, k_norm=L.k_norm, eps=c.norm_eps)
-            kk = self.k_cache[i][slot, :, :p_end]                    # [Hkv, S, hd] f16
-            vv = self.v_cache[i][slot, :, :p_end]
-            qh = q.transpose(0, 1).to(torch.float16)[None]              # [1, H, T, hd]
-            mask = swa_mask if L.swa else base_mask
-            if c.attn_softcap > 0 or L.sinks is not None:
-                o = R.attention(q, kk.transpose(0, 1), vv.transpose(0, 1), pos.long(), kpos, scale=self.attn_scale, causal=c.causal,
-                                window=c.sliding_window if L.swa else 0, softcap=c.attn_softcap, sinks=L.sinks).reshape(T, -1)
-            else:
-                o = torch.nn.functional.scaled_dot_product_attention(qh, kk[None], vv[None], attn_mask=mask, scale=self.attn_scale,
-                                                                     enable_gqa=group > 1)
-                o = o[0].transpose(0, 1).reshape(T, -1).float()
-            o = self._mm(o.to(torch.bfloat16), L.wo)
+            o = self._mm(self._attn_prefill(q, i, L, slot, pos0, p_end), L.wo)
             if c.sandwich_norm:
                 o = R.rmsnorm(o, L.post_attn_norm, c.norm_eps)
             x = x + o

@@ -410,6 +410,27 @@ def gemm_q_scatter(x: torch.Tensor, w: DevWeight, ldo: int, cm: "CommSend", rows
     _check(f(ptr(x), m, C.addressof(d), ldo, C.addressof(cm), rows_per_rank, stream()), "gemm_q_scatter")
 
 
+class AttnPrefillArgs(C.Structure):
+    _fields_ = [("q", C.c_void_p), ("k_cache", C.c_void_p), ("v_cache", C.c_void_p), ("out", C.c_void_p), ("sinks", C.c_void_p),
+                ("T", C.c_int), ("H", C.c_int), ("Hkv", C.c_int), ("n_ctx", C.c_int), ("slot", C.c_int), ("pos0", C.c_int),
+                ("kv_len", C.c_int), ("causal", C.c_int), ("window", C.c_int), ("scale", C.c_float), ("softcap", C.c_float)]
+
+
+ATTN_PREFILL_HEAD_DIMS = (64, 128)
+
+
+def attn_prefill(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, slot: int, pos0: int, kv_len: int, scale: float,
+                 causal: bool = True, window: int = 0, softcap: float = 0.0, sinks: torch.Tensor | None = None) -> torch.Tensor:
+    """Flash attention of a prefill chunk (kernels/attn_prefill.cu): q [T, H, D] fp32 -> bf16 [T, H * D]."""
+    T, H, D = q.shape
+    n_slots, Hkv, n_ctx, _ = k_cache.shape
+    out = torch.empty(T, H * D, device=q.device, dtype=torch.bfloat16)
+    a = AttnPrefillArgs(ptr(q.contiguous()), ptr(k_cache), ptr(v_cache), ptr(out), ptr(sinks), T, H, Hkv, n_ctx, slot, pos0, kv_len,
+                        int(causal), window, scale, softcap)
+    _check(lib().b2_attn_prefill(C.byref(a), D, stream()), "attn_prefill")
+    return out
+
+
 def gemm_status() -> int:
     """0 = ok; 1 = a bounded wait inside a tensor-core GEMM expired."""
     return int(lib().b2_gemm_status()) | int(lib().b2_gemm_q_status())

@@ -274,11 +274,6 @@ class TPBackend(B200Backend):
         if rows > 0:
             K.embed(self.embd, ids[row0:row0 + rows], c.embed_scale, out=self.xs)
         p_end = pos0 + T
-        kpos = torch.arange(p_end, device=dev)
-        dp = pos.long()[:, None] - kpos[None, :]
-        base_mask = dp >= 0 if c.causal else torch.ones_like(dp, dtype=torch.bool)
-        swa_mask = base_mask & (dp < c.sliding_window) if c.sliding_window > 0 else base_mask
-        group = c.n_heads // c.n_kv_heads
         h = self.h_full[:T]
         for i, L in enumerate(self.layers):
             self._norm_gather(L.attn_norm, rows, row0, reduce=i > 0)
@@ -290,17 +285,7 @@ class TPBackend(B200Backend):
             q = K.rope_kv(qkv, pos, slots, self.inv_freq_local if local else self.inv_freq, n_heads=c.n_heads, n_kv_heads=c.n_kv_heads,
                           hd=c.head_dim, n_rot=c.rope_dim, neox=c.rope_style == "neox", mscale=1.0 if local else self.mscale,
                           k_cache=self.k_cache[i], v_cache=self.v_cache[i], q_norm=L.q_norm, k_norm=L.k_norm, eps=c.norm_eps)
-            kk = self.k_cache[i][slot, :, :p_end]
-            vv = self.v_cache[i][slot, :, :p_end]
-            if c.attn_softcap > 0 or L.sinks is not None:
-                o = R.attention(q, kk.transpose(0, 1), vv.transpose(0, 1), pos.long(), kpos, scale=self.attn_scale, causal=c.causal,
-                                window=c.sliding_window if L.swa else 0, softcap=c.attn_softcap, sinks=L.sinks).reshape(T, -1)
-            else:
-                qh = q.transpose(0, 1).to(torch.float16)[None]
-                o = torch.nn.functional.scaled_dot_product_attention(qh, kk[None], vv[None], attn_mask=swa_mask if L.swa else base_mask,
-                                                                     scale=self.attn_scale, enable_gqa=group > 1)
-                o = o[0].transpose(0, 1).reshape(T, -1)
-            self._mm_scatter(o.to(torch.bfloat16), L.wo, rpr)
+            self._mm_scatter(self._attn_prefill(q, i, L, slot, pos0, p_end), L.wo, rpr)
             self._norm_gather(L.ffn_norm, rows, row0, reduce=True)
             if L.moe:
                 # every rank holds all rows of h (the all-gather was the dispatch); its experts' partial output rows go to their owners

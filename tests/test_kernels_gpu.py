@@ -188,6 +188,28 @@ def test_embed_and_argmax():
     assert K.argmax(lg).cpu().tolist() == lg.argmax(-1).cpu().tolist()
 
 
+@pytest.mark.parametrize("hd,H,Hkv", [(128, 8, 2), (64, 4, 4), (64, 6, 1)])
+@pytest.mark.parametrize("T,pos0,window,softcap,use_sinks,causal", [(150, 0, 0, 0.0, False, True), (70, 131, 48, 0.0, True, True),
+                                                                    (64, 64, 0, 30.0, False, True), (33, 0, 0, 0.0, False, False)])
+def test_attn_prefill(hd, H, Hkv, T, pos0, window, softcap, use_sinks, causal):
+    """Flash-attention prefill kernel against the fp32 statement of attention over the same f16 cache."""
+    K = _K()
+    n_slots, n_ctx, slot = 2, 300, 1
+    g = torch.Generator().manual_seed(hd + T)
+    kc = (torch.randn(n_slots, Hkv, n_ctx, hd, generator=g) * 0.7).to(torch.float16).cuda()
+    vc = (torch.randn(n_slots, Hkv, n_ctx, hd, generator=g) * 0.7).to(torch.float16).cuda()
+    q = torch.randn(T, H, hd, generator=g).cuda()
+    sinks = torch.randn(H, generator=g).cuda() if use_sinks else None
+    scale = 1 / math.sqrt(hd)
+    p_end = pos0 + T
+    out = K.attn_prefill(q, kc, vc, slot, pos0, p_end, scale, causal, window, softcap, sinks).float().cpu().view(T, H, hd)
+    qh = q.to(torch.float16).float().cpu()            # the kernel multiplies f16 operands
+    ref = R.attention(qh, kc[slot, :, :p_end].transpose(0, 1).float().cpu(), vc[slot, :, :p_end].transpose(0, 1).float().cpu(),
+                      torch.arange(pos0, p_end), torch.arange(p_end), scale=scale, causal=causal, window=window, softcap=softcap,
+                      sinks=sinks.cpu() if use_sinks else None)
+    assert torch.allclose(out, ref, atol=1e-2, rtol=2e-2), (out - ref).abs().max()
+
+
 def test_moe_route_kernel():
     K = _K()
     import ctypes as C
