@@ -110,6 +110,12 @@ class B200Backend:
             p, L = f"blk.{i}.", _Layer()
             L.attn_norm = vec(p + "attn_norm.weight")
             L.wq, L.wk, L.wv, L.wo = mat(p + "attn_q"), mat(p + "attn_k"), mat(p + "attn_v"), mat(p + "attn_output")
+            L.wqkv16 = L.bqkv = None
+            if self.keep_bf16:          # prefill multiplies Q, K and V in one GEMM
+                L.wqkv16 = torch.cat([L.wq.bf16, L.wk.bf16, L.wv.bf16])
+                del L.wq.bf16, L.wk.bf16, L.wv.bf16
+                if any(w.bias is not None for w in (L.wq, L.wk, L.wv)):
+                    L.bqkv = torch.cat([w.bias if w.bias is not None else torch.zeros(w.n, device=dev) for w in (L.wq, L.wk, L.wv)])
             L.q_norm, L.k_norm = vec(p + "attn_q_norm.weight"), vec(p + "attn_k_norm.weight")
             L.post_attn_norm = vec(p + "post_attention_norm.weight") if c.sandwich_norm else None
             L.ffn_norm = vec(p + "ffn_norm.weight")
@@ -440,18 +446,26 @@ class B200Backend:
         return out
 
     # -- prefill --------------------------------------------------------------------------------------
-    def _mm(self, x_bf16: torch.Tensor, w: K.DevWeight, out: torch.Tensor | None = None, out_off: int = 0) -> torch.Tensor:
-        """x @ W^T + bias for a prefill chunk: the dequantisation-fused tcgen05 GEMM, or a 16-bit copy for other encodings."""
+    def _mm(self, x_bf16: torch.Tensor, w: K.DevWeight, out: torch.Tensor | None = None, out_off: int = 0, accumulate: bool = False,
+            out16: bool = False) -> torch.Tensor:
+        """x @ W^T + bias for a prefill chunk on the tcgen05 GEMM.
+
+        ``out`` / ``out_off`` place the fp32 result in a column window of a wider buffer, ``accumulate`` adds to it (the
+        residual add of the output and down projections happens in the GEMM epilogue), ``out16`` returns bf16 instead.
+        """
         if self.prefill_gemm == "fused" and K.gemm_q_supported(w):
             self.kernel_launches += 1
-            return K.gemm_q(x_bf16, w, out=out, out_off=out_off)
+            y = K.gemm_q(x_bf16, w, out=out, accumulate=accumulate, out_off=out_off)
+            return y.to(torch.bfloat16) if out16 else y
         wb = getattr(w, "bf16", None)
         if wb is None:
             wb = K.dequant_to_bf16(w)        # scratch: freed (back to the caching allocator) when this call returns
             self.kernel_launches += 1
         self.kernel_launches += 1
+        if out16:
+            return K.gemm_bf16_out16(x_bf16, wb, w.bias)
         if out is not None:
-            return K.gemm_bf16(x_bf16, wb, w.bias, out=out[:, out_off:out_off + w.n])
+            return K.gemm_bf16(x_bf16, wb, w.bias, out=out[:, out_off:out_off + w.n], accumulate=accumulate)
         return K.gemm_bf16(x_bf16, wb, w.bias)
 
     def _attn_prefill(self, q: torch.Tensor, i: int, L, slot: int, pos0: int, p_end: int) -> torch.Tensor:
@@ -482,29 +496,35 @@ class B200Backend:
         x = K.embed(self.embd, ids, c.embed_scale)
         p_end = pos0 + T
         for i, L in enumerate(self.layers):
-            h = R.rmsnorm(x, L.attn_norm, c.norm_eps).to(torch.bfloat16)
+            h = K.rmsnorm_bf16(x, L.attn_norm, c.norm_eps)
             qkv = torch.empty(T, (c.n_heads + 2 * c.n_kv_heads) * c.head_dim, device=dev, dtype=torch.float32)
-            self._mm(h, L.wq, qkv, 0)
-            self._mm(h, L.wk, qkv, c.q_dim)
-            self._mm(h, L.wv, qkv, c.q_dim + c.kv_dim)
+            if getattr(L, "wqkv16", None) is not None:      # resident 16-bit copies: one GEMM for Q, K and V
+                K.gemm_bf16(h, L.wqkv16, L.bqkv, out=qkv)
+                self.kernel_launches += 1
+            else:
+                self._mm(h, L.wq, qkv, 0)
+                self._mm(h, L.wk, qkv, c.q_dim)
+                self._mm(h, L.wv, qkv, c.q_dim + c.kv_dim)
             local = L.swa and c.rope_base_local > 0
             q = K.rope_kv(qkv, pos, slots, self.inv_freq_local if local else self.inv_freq, n_heads=c.n_heads, n_kv_heads=c.n_kv_heads,
                           hd=c.head_dim, n_rot=c.rope_dim, neox=c.rope_style == "neox", mscale=1.0 if local else self.mscale,
                           k_cache=self.k_cache[i], v_cache=self.v_cache[i], q_norm=L.q_norm, k_norm=L.k_norm, eps=c.norm_eps)
-            o = self._mm(self._attn_prefill(q, i, L, slot, pos0, p_end), L.wo)
+            o = self._attn_prefill(q, i, L, slot, pos0, p_end)
             if c.sandwich_norm:
-                o = R.rmsnorm(o, L.post_attn_norm, c.norm_eps)
-            x = x + o
-            h = R.rmsnorm(x, L.ffn_norm, c.norm_eps).to(torch.bfloat16)
-            if L.moe:
-                f = self._moe_prefill(h, L)
+                x = x + R.rmsnorm(self._mm(o, L.wo), L.post_attn_norm, c.norm_eps)
             else:
-                gu = self._mm(h, L.gu)                      # rows interleaved: even = gate, odd = up
-                f = R.glu(gu[:, 0::2], gu[:, 1::2], c.act, c.swiglu_alpha, c.swiglu_limit)
-                f = self._mm(f.to(torch.bfloat16), L.down)
+                self._mm(o, L.wo, x, 0, accumulate=True)                  # residual add in the GEMM epilogue
+            h = K.rmsnorm_bf16(x, L.ffn_norm, c.norm_eps)
+            if L.moe:
+                x = x + self._moe_prefill(h, L)
+                continue
+            gu = self._mm(h, L.gu, out16=True)                            # columns interleaved: even = gate, odd = up
+            f = K.glu_rows(gu, c.act, c.swiglu_alpha, c.swiglu_limit)
             if c.sandwich_norm:
-                f = R.rmsnorm(f, L.post_ffw_norm, c.norm_eps)
-            x = x + f
+                x = x + R.rmsnorm(self._mm(f, L.down), L.post_ffw_norm, c.norm_eps)
+            else:
+                self._mm(f, L.down, x, 0, accumulate=True)
+            self.kernel_launches += 3
         return x
 
     @torch.no_grad()

@@ -410,6 +410,28 @@ def gemm_q_scatter(x: torch.Tensor, w: DevWeight, ldo: int, cm: "CommSend", rows
     _check(f(ptr(x), m, C.addressof(d), ldo, C.addressof(cm), rows_per_rank, stream()), "gemm_q_scatter")
 
 
+class GluRowsArgs(C.Structure):
+    _fields_ = [("gu", C.c_void_p), ("out", C.c_void_p), ("f", C.c_int), ("act", C.c_int), ("alpha", C.c_float), ("limit", C.c_float)]
+
+
+def glu_rows(gu: torch.Tensor, act: str, alpha: float = 1.702, limit: float = 7.0) -> torch.Tensor:
+    """Gated activation on a bf16 [rows, 2F] gate/up GEMM result with interleaved columns -> bf16 [rows, F]."""
+    rows, f2 = gu.shape
+    out = torch.empty(rows, f2 // 2, device=gu.device, dtype=torch.bfloat16)
+    a = GluRowsArgs(ptr(gu), ptr(out), f2 // 2, _ACT[act], alpha, limit)
+    _check(lib().b2_glu_rows(C.byref(a), rows, stream()), "glu_rows")
+    return out
+
+
+def rmsnorm_bf16(x: torch.Tensor, w: torch.Tensor | None, eps: float, do_norm: bool = True) -> torch.Tensor:
+    """Row-wise RMSNorm of fp32 [rows, k] with a bf16 result (the A operand of the prefill GEMMs)."""
+    rows, k = x.shape
+    out = torch.empty(rows, k, device=x.device, dtype=torch.bfloat16)
+    a = NormCastArgs(ptr(x), ptr(w), eps, k, int(do_norm), ptr(out))
+    _check(lib().b2_rmsnorm_bf16(C.byref(a), rows, stream()), "rmsnorm_bf16")
+    return out
+
+
 class AttnPrefillArgs(C.Structure):
     _fields_ = [("q", C.c_void_p), ("k_cache", C.c_void_p), ("v_cache", C.c_void_p), ("out", C.c_void_p), ("sinks", C.c_void_p),
                 ("T", C.c_int), ("H", C.c_int), ("Hkv", C.c_int), ("n_ctx", C.c_int), ("slot", C.c_int), ("pos0", C.c_int),

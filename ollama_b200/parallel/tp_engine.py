@@ -278,9 +278,13 @@ class TPBackend(B200Backend):
         for i, L in enumerate(self.layers):
             self._norm_gather(L.attn_norm, rows, row0, reduce=i > 0)
             qkv = torch.empty(T, (c.n_heads + 2 * c.n_kv_heads) * c.head_dim, device=dev, dtype=torch.float32)
-            self._mm(h, L.wq, qkv, 0)
-            self._mm(h, L.wk, qkv, c.q_dim)
-            self._mm(h, L.wv, qkv, c.q_dim + c.kv_dim)
+            if L.wqkv16 is not None:
+                K.gemm_bf16(h, L.wqkv16, L.bqkv, out=qkv)
+                self.kernel_launches += 1
+            else:
+                self._mm(h, L.wq, qkv, 0)
+                self._mm(h, L.wk, qkv, c.q_dim)
+                self._mm(h, L.wv, qkv, c.q_dim + c.kv_dim)
             local = L.swa and c.rope_base_local > 0
             q = K.rope_kv(qkv, pos, slots, self.inv_freq_local if local else self.inv_freq, n_heads=c.n_heads, n_kv_heads=c.n_kv_heads,
                           hd=c.head_dim, n_rot=c.rope_dim, neox=c.rope_style == "neox", mscale=1.0 if local else self.mscale,
@@ -295,9 +299,9 @@ class TPBackend(B200Backend):
                 K._check(f_sc(K.ptr(part), T, c.d_model, rpr, C.addressof(self.cm_rs), K.stream()), "tp_scatter_rows")
                 self.kernel_launches += 1
                 continue
-            gu = self._mm(h, L.gu)
-            f = R.glu(gu[:, 0::2], gu[:, 1::2], c.act, c.swiglu_alpha, c.swiglu_limit)
-            self._mm_scatter(f.to(torch.bfloat16), L.down, rpr)
+            gu = self._mm(h, L.gu, out16=True)
+            self._mm_scatter(K.glu_rows(gu, c.act, c.swiglu_alpha, c.swiglu_limit), L.down, rpr)
+            self.kernel_launches += 1
         self._norm_gather(self.out_norm, rows, row0, reduce=True)
         return h
 
