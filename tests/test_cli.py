@@ -1,0 +1,99 @@
+"""Command line against a live server (uvicorn in a thread, CPU backend, temp model store)."""
+import io
+import json
+import os
+import socket
+import threading
+import time
+from contextlib import redirect_stderr, redirect_stdout
+
+import pytest
+
+
+@pytest.fixture(scope="module")
+def server(tmp_path_factory):
+    root = tmp_path_factory.mktemp("cli_store")
+    s = socket.socket()
+    s.bind(("127.0.0.1", 0))
+    port = s.getsockname()[1]
+    s.close()
+    keys = ("OLLAMA_MODELS", "B200_DEVICE", "OLLAMA_CONTEXT_LENGTH", "OLLAMA_HOST")
+    old = {k: os.environ.get(k) for k in keys}
+    os.environ.update(OLLAMA_MODELS=str(root), B200_DEVICE="cpu", OLLAMA_CONTEXT_LENGTH="256", OLLAMA_HOST=f"127.0.0.1:{port}")
+    import uvicorn
+
+    from ollama_b200.models.synth import write_synthetic_gguf
+    from ollama_b200.server.routes import create_app
+    write_synthetic_gguf(str(root / "m.gguf"), "tiny-llama", "F32")
+    (root / "Modelfile").write_text('FROM ./m.gguf\nTEMPLATE "{{ .Prompt }}"\nPARAMETER temperature 0\nPARAMETER num_predict 5\nSYSTEM be brief\n')
+    srv = uvicorn.Server(uvicorn.Config(create_app(), host="127.0.0.1", port=port, log_level="warning"))
+    t = threading.Thread(target=srv.run, daemon=True)
+    t.start()
+    for _ in range(200):
+        if srv.started:
+            break
+        time.sleep(0.05)
+    yield root
+    srv.should_exit = True
+    t.join(timeout=10)
+    for k, v in old.items():
+        if v is None:
+            os.environ.pop(k, None)
+        else:
+            os.environ[k] = v
+
+
+def run_cli(*argv):
+    from ollama_b200.cli.main import main
+    out, err = io.StringIO(), io.StringIO()
+    with redirect_stdout(out), redirect_stderr(err):
+        rc = main(list(argv))
+    return rc, out.getvalue(), err.getvalue()
+
+
+def test_create_list_show_run_cp_rm(server, monkeypatch):
+    monkeypatch.setattr("sys.stdin", io.StringIO(""))          # not a tty: `run` takes the prompt from argv only
+    rc, out, err = run_cli("create", "tiny", "-f", str(server / "Modelfile"))
+    assert rc == 0 and "success" in err
+    rc, out, _ = run_cli("list")
+    assert rc == 0 and out.splitlines()[0].split() == ["NAME", "ID", "SIZE", "MODIFIED"] and "tiny:latest" in out
+    rc, out, _ = run_cli("show", "tiny")
+    assert rc == 0 and "architecture" in out and "llama" in out
+    rc, out, _ = run_cli("show", "tiny", "--system")
+    assert out.strip() == "be brief"
+    rc, out, err = run_cli("run", "tiny", "<t300><t301>", "--verbose")
+    assert rc == 0 and out.count("<t") == 5 and "eval rate" in err
+    rc, out, _ = run_cli("ps")
+    assert rc == 0 and "tiny:latest" in out and "CPU" in out
+    rc, out, _ = run_cli("cp", "tiny", "tiny2")
+    assert rc == 0
+    rc, out, _ = run_cli("rm", "tiny2")
+    assert rc == 0 and "deleted" in out
+    rc, out, err = run_cli("rm", "tiny2")
+    assert rc == 1 and "not found" in err
+    rc, _, _ = run_cli("stop", "tiny")
+    assert rc == 0
+
+
+def test_bench_formats(server):
+    run_cli("create", "tiny", "-f", str(server / "Modelfile"))
+    rc, out, _ = run_cli("bench", "--model", "tiny", "--epochs", "2", "--max-tokens", "4", "--prompt-tokens", "8", "--format", "json")
+    res = json.loads(out)
+    assert rc == 0 and res[0]["model"] == "tiny" and res[0]["generate_tok_s"] > 0 and res[0]["ttft_ms"] > 0
+    rc, out, _ = run_cli("bench", "--model", "tiny", "--epochs", "1", "--max-tokens", "3")
+    assert "BenchmarkModel/name=tiny/step=generate" in out and "token/sec" in out
+
+
+def test_repl_commands(server, monkeypatch):
+    from ollama_b200.api.client import Client
+    from ollama_b200.cli.main import Repl
+    run_cli("create", "tiny", "-f", str(server / "Modelfile"))
+    lines = iter(["/set parameter num_predict 3", "/set system terse", '"""<t300>', '<t301>"""', "/clear", "/bogus", "/bye"])
+    monkeypatch.setattr("builtins.input", lambda prompt="": next(lines))
+    out = io.StringIO()
+    r = Repl(Client(), "tiny", {}, "", None, None, False)
+    with redirect_stdout(out):
+        r.loop()
+    text = out.getvalue()
+    assert r.opts == {"num_predict": 3} and r.system == "terse" and r.messages == []
+    assert text.count("<t") == 3 and "Unknown command '/bogus'" in text and "Cleared session context" in text
