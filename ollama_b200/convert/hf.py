@@ -1,0 +1,344 @@
+"""Hugging Face checkpoint directory (config.json + *.safetensors + tokenizer files) -> GGUF.
+
+Covers the decoder families this runtime executes: Llama / Mistral, Mixtral, Qwen2, Qwen3, Qwen3-MoE,
+Gemma, Gemma 2 and Gemma 3 (text tower).  Mirrors convert/convert.go:279-379 (dispatch by
+``architectures[0]``), convert/convert_llama.go (key/value metadata, the Q/K row permutation that turns the
+checkpoint's half-split rotary layout into the interleaved one llama-arch GGUFs use:189-232),
+convert/convert_qwen3.go, convert_gemma*.go, convert_mixtral.go (expert stacking) and convert/tokenizer.go
+(vocabulary, merges, token types, pretokenizer identification, special token ids, chat template).
+
+Tensors keep their source precision (F16/BF16 matrices, F32 vectors) unless ``outtype`` asks otherwise;
+quantisation is a separate pass (store/create.py quantize_gguf).
+"""
+from __future__ import annotations
+
+import json
+import os
+import re
+from typing import Any, Callable, Iterator
+
+import torch
+
+from ..gguf import quants
+from ..gguf.types import GGMLType
+from ..gguf.writer import WriteTensor, write_gguf
+from .safetensors import ModelDir
+
+
+class ConvertError(ValueError):
+    pass
+
+
+ARCHS = {
+    "LlamaForCausalLM": "llama", "MistralForCausalLM": "llama", "MixtralForCausalLM": "llama", "Qwen2ForCausalLM": "qwen2",
+    "Qwen3ForCausalLM": "qwen3", "Qwen3MoeForCausalLM": "qwen3moe", "GemmaForCausalLM": "gemma", "Gemma2ForCausalLM": "gemma2",
+    "Gemma3ForCausalLM": "gemma3", "Gemma3ForConditionalGeneration": "gemma3",
+}
+
+# (pattern on the checkpoint name, GGUF name); {n} = layer index, {e} = expert index
+_LAYER = r"(?:model\.|language_model\.model\.|model\.language_model\.)?layers\.(\d+)\."
+_RULES: list[tuple[str, str]] = [
+    (r"(?:model\.|language_model\.model\.|model\.language_model\.)?embed_tokens\.weight", "token_embd.weight"),
+    (r"(?:model\.|language_model\.model\.|model\.language_model\.)?norm\.weight", "output_norm.weight"),
+    (r"(?:language_model\.)?lm_head\.weight", "output.weight"),
+    (_LAYER + r"input_layernorm\.weight", "blk.{n}.attn_norm.weight"),
+    (_LAYER + r"self_attn\.q_proj\.(weight|bias)", "blk.{n}.attn_q.{1}"),
+    (_LAYER + r"self_attn\.k_proj\.(weight|bias)", "blk.{n}.attn_k.{1}"),
+    (_LAYER + r"self_attn\.v_proj\.(weight|bias)", "blk.{n}.attn_v.{1}"),
+    (_LAYER + r"self_attn\.o_proj\.(weight|bias)", "blk.{n}.attn_output.{1}"),
+    (_LAYER + r"self_attn\.q_norm\.weight", "blk.{n}.attn_q_norm.weight"),
+    (_LAYER + r"self_attn\.k_norm\.weight", "blk.{n}.attn_k_norm.weight"),
+    (_LAYER + r"mlp\.gate_proj\.weight", "blk.{n}.ffn_gate.weight"),
+    (_LAYER + r"mlp\.up_proj\.weight", "blk.{n}.ffn_up.weight"),
+    (_LAYER + r"mlp\.down_proj\.weight", "blk.{n}.ffn_down.weight"),
+    (_LAYER + r"mlp\.gate\.weight", "blk.{n}.ffn_gate_inp.weight"),
+    (_LAYER + r"block_sparse_moe\.gate\.weight", "blk.{n}.ffn_gate_inp.weight"),
+    (_LAYER + r"mlp\.experts\.(\d+)\.gate_proj\.weight", "blk.{n}.ffn_gate_exps.weight#{1}"),
+    (_LAYER + r"mlp\.experts\.(\d+)\.up_proj\.weight", "blk.{n}.ffn_up_exps.weight#{1}"),
+    (_LAYER + r"mlp\.experts\.(\d+)\.down_proj\.weight", "blk.{n}.ffn_down_exps.weight#{1}"),
+    (_LAYER + r"block_sparse_moe\.experts\.(\d+)\.w1\.weight", "blk.{n}.ffn_gate_exps.weight#{1}"),
+    (_LAYER + r"block_sparse_moe\.experts\.(\d+)\.w3\.weight", "blk.{n}.ffn_up_exps.weight#{1}"),
+    (_LAYER + r"block_sparse_moe\.experts\.(\d+)\.w2\.weight", "blk.{n}.ffn_down_exps.weight#{1}"),
+]
+# post_attention_layernorm is the FFN pre-norm for llama/qwen but a sandwich post-norm for gemma 2/3
+_RULES_PRENORM = [(_LAYER + r"post_attention_layernorm\.weight", "blk.{n}.ffn_norm.weight")]
+_RULES_SANDWICH = [(_LAYER + r"post_attention_layernorm\.weight", "blk.{n}.post_attention_norm.weight"),
+                   (_LAYER + r"pre_feedforward_layernorm\.weight", "blk.{n}.ffn_norm.weight"),
+                   (_LAYER + r"post_feedforward_layernorm\.weight", "blk.{n}.post_ffw_norm.weight")]
+_SKIP = re.compile(r".*(rotary_emb\.inv_freq|vision_tower|multi_modal_projector|vision_model|audio_tower).*")
+
+
+def map_name(name: str, arch: str) -> str | None:
+    rules = _RULES + (_RULES_SANDWICH if arch in ("gemma2", "gemma3") else _RULES_PRENORM)
+    for pat, repl in rules:
+        m = re.fullmatch(pat, name)
+        if m:
+            groups = m.groups()
+            out = repl
+            if "{n}" in repl:
+                out = out.replace("{n}", groups[0])
+                groups = groups[1:]
+            for i, g in enumerate(groups, 1):
+                out = out.replace("{%d}" % i, g)
+            return out
+    return None
+
+
+def permute_qk(w: torch.Tensor, n_head: int) -> torch.Tensor:
+    """Rows of a Q or K projection: half-split rotary order (HF) -> interleaved pairs (llama-arch GGUF)."""
+    rows = w.shape[0]
+    hd = rows // n_head
+    rest = w.shape[1:]
+    return w.reshape(n_head, 2, hd // 2, *rest).transpose(1, 2).reshape(rows, *rest)
+
+
+def _kv(cfg: dict[str, Any], arch: str, name: str) -> dict[str, Any]:
+    c = cfg.get("text_config", cfg) if arch == "gemma3" else cfg
+    n_head = c["num_attention_heads"]
+    hd = c.get("head_dim") or c["hidden_size"] // n_head
+    kv: dict[str, Any] = {
+        "general.architecture": arch, "general.name": name, "general.file_type": 1,
+        f"{arch}.context_length": c.get("max_position_embeddings", 8192), f"{arch}.embedding_length": c["hidden_size"],
+        f"{arch}.block_count": c["num_hidden_layers"], f"{arch}.feed_forward_length": c.get("intermediate_size", 0),
+        f"{arch}.attention.head_count": n_head, f"{arch}.attention.head_count_kv": c.get("num_key_value_heads", n_head),
+        f"{arch}.attention.layer_norm_rms_epsilon": float(c.get("rms_norm_eps", 1e-6)),
+        f"{arch}.rope.freq_base": float(c.get("rope_theta", 10000.0)), f"{arch}.vocab_size": c.get("vocab_size", 0),
+    }
+    if c.get("head_dim") or arch in ("qwen3", "qwen3moe", "gemma", "gemma2", "gemma3"):
+        kv[f"{arch}.attention.key_length"] = hd
+        kv[f"{arch}.attention.value_length"] = hd
+    if arch == "llama":
+        kv["llama.rope.dimension_count"] = hd
+    rs = c.get("rope_scaling") or {}
+    rtype = rs.get("rope_type") or rs.get("type")
+    if rtype in ("linear", "yarn"):
+        kv[f"{arch}.rope.scaling.type"] = rtype
+        kv[f"{arch}.rope.scaling.factor"] = float(rs.get("factor", 1.0))
+        if rs.get("original_max_position_embeddings"):
+            kv[f"{arch}.rope.scaling.original_context_length"] = rs["original_max_position_embeddings"]
+    n_exp = c.get("num_local_experts") or c.get("num_experts") or 0
+    if n_exp:
+        kv[f"{arch}.expert_count"] = n_exp
+        kv[f"{arch}.expert_used_count"] = c.get("num_experts_per_tok", 2)
+        if c.get("moe_intermediate_size"):
+            kv[f"{arch}.expert_feed_forward_length"] = c["moe_intermediate_size"]
+        if "norm_topk_prob" in c:
+            kv[f"{arch}.norm_top_k_prob"] = bool(c["norm_topk_prob"])
+    if c.get("sliding_window") and arch in ("gemma2", "gemma3", "llama"):
+        kv[f"{arch}.attention.sliding_window"] = c["sliding_window"]
+    if arch == "gemma2":
+        kv["gemma2.attn_logit_softcapping"] = float(c.get("attn_logit_softcapping") or 50.0)
+        kv["gemma2.final_logit_softcapping"] = float(c.get("final_logit_softcapping") or 30.0)
+    if arch == "gemma3" and c.get("rope_local_base_freq"):
+        kv["gemma3.rope.local.freq_base"] = float(c["rope_local_base_freq"])
+    if arch in ("gemma2", "gemma3") and c.get("query_pre_attn_scalar"):
+        kv[f"{arch}.attention.query_pre_attn_scalar"] = c["query_pre_attn_scalar"]
+    return kv
+
+
+def rope_freq_factors(cfg: dict[str, Any]) -> torch.Tensor | None:
+    """llama3-style rope scaling is baked into a ``rope_freqs.weight`` tensor of per-frequency divisors."""
+    rs = cfg.get("rope_scaling") or {}
+    if (rs.get("rope_type") or rs.get("type")) != "llama3":
+        return None
+    hd = cfg.get("head_dim") or cfg["hidden_size"] // cfg["num_attention_heads"]
+    base = float(cfg.get("rope_theta", 10000.0))
+    factor, lo, hi = float(rs.get("factor", 8.0)), float(rs.get("low_freq_factor", 1.0)), float(rs.get("high_freq_factor", 4.0))
+    orig = float(rs.get("original_max_position_embeddings", 8192))
+    out = []
+    for i in range(0, hd, 2):
+        freq = base ** (-i / hd)
+        wavelen = 2 * torch.pi / freq
+        if wavelen < orig / hi:
+            out.append(1.0)
+        elif wavelen > orig / lo:
+            out.append(factor)
+        else:
+            smooth = (orig / wavelen - lo) / (hi - lo)
+            out.append(1.0 / ((1 - smooth) / factor + smooth))
+    return torch.tensor(out, dtype=torch.float32)
+
+
+# ---------------------------------------------------------------------------------------------------
+# tokenizer
+# ---------------------------------------------------------------------------------------------------
+_PRE_BY_MARK = [("(?i:'s|'t|'re|'ve|'m|'ll|'d)|[^\\r\\n\\p{L}\\p{N}]?\\p{L}+|\\p{N}{1,3}", "llama-bpe"),
+                ("(?i:'s|'t|'re|'ve|'m|'ll|'d)|[^\\r\\n\\p{L}\\p{N}]?\\p{L}+|\\p{N}|", "qwen2")]
+
+
+def _pretokenizer(tj: dict[str, Any]) -> str:
+    pats: list[str] = []
+
+    def walk(node):
+        if isinstance(node, dict):
+            if node.get("type") == "Split" and isinstance(node.get("pattern"), dict):
+                pats.append(node["pattern"].get("Regex", ""))
+            for v in node.values():
+                walk(v)
+        elif isinstance(node, list):
+            for v in node:
+                walk(v)
+
+    walk(tj.get("pre_tokenizer"))
+    joined = "".join(pats)
+    for mark, name in _PRE_BY_MARK:
+        if mark in joined:
+            return name
+    return "default"
+
+
+def tokenizer_kv(path: str, vocab_size: int) -> dict[str, Any]:
+    kv: dict[str, Any] = {}
+    tj_path = os.path.join(path, "tokenizer.json")
+    tc: dict[str, Any] = {}
+    if os.path.exists(os.path.join(path, "tokenizer_config.json")):
+        with open(os.path.join(path, "tokenizer_config.json"), encoding="utf-8") as f:
+            tc = json.load(f)
+    if os.path.exists(tj_path):
+        with open(tj_path, encoding="utf-8") as f:
+            tj = json.load(f)
+        model = tj.get("model", {})
+        vocab: dict[str, int] = dict(model.get("vocab", {}))
+        special = set()
+        for a in tj.get("added_tokens", []):
+            vocab[a["content"]] = a["id"]
+            if a.get("special"):
+                special.add(a["id"])
+        n = max(max(vocab.values()) + 1 if vocab else 0, vocab_size)
+        tokens = [f"[PAD{i}]" for i in range(n)]
+        types = [5] * n                      # unused
+        for tok, i in vocab.items():
+            tokens[i] = tok
+            types[i] = 3 if i in special else 1
+        if model.get("type") == "BPE" and not model.get("byte_fallback"):
+            kv["tokenizer.ggml.model"] = "gpt2"
+            kv["tokenizer.ggml.pre"] = _pretokenizer(tj)
+            merges = model.get("merges", [])
+            kv["tokenizer.ggml.merges"] = [m if isinstance(m, str) else " ".join(m) for m in merges]
+        else:                                # SentencePiece-style vocabulary expressed in tokenizer.json (byte fallback, "▁" spaces)
+            kv["tokenizer.ggml.model"] = "llama"
+            kv["tokenizer.ggml.scores"] = [0.0 if types[i] == 3 else -float(i) for i in range(n)]
+            for i, t in enumerate(tokens):
+                if re.fullmatch(r"<0x[0-9A-F]{2}>", t):
+                    types[i] = 6
+            kv["tokenizer.ggml.add_space_prefix"] = not any(isinstance(nz, dict) and nz.get("type") == "Replace"
+                                                            for nz in [tj.get("normalizer") or {}])
+        kv["tokenizer.ggml.tokens"] = tokens
+        kv["tokenizer.ggml.token_type"] = types
+    else:
+        raise ConvertError("tokenizer.json not found (SentencePiece .model files need the `sentencepiece` converter path)")
+
+    def tok_id(key: str) -> int | None:
+        v = tc.get(key)
+        if isinstance(v, dict):
+            v = v.get("content")
+        return vocab.get(v) if isinstance(v, str) else None
+
+    for key, out in (("bos_token", "bos_token_id"), ("eos_token", "eos_token_id"), ("unk_token", "unknown_token_id"), ("pad_token", "padding_token_id")):
+        i = tok_id(key)
+        if i is not None:
+            kv[f"tokenizer.ggml.{out}"] = i
+    gen_path = os.path.join(path, "generation_config.json")
+    if os.path.exists(gen_path):
+        with open(gen_path, encoding="utf-8") as f:
+            gc = json.load(f)
+        eos = gc.get("eos_token_id")
+        if isinstance(eos, list) and eos:
+            kv["tokenizer.ggml.eos_token_ids"] = [int(e) for e in eos]
+            kv.setdefault("tokenizer.ggml.eos_token_id", int(eos[0]))
+        elif isinstance(eos, int):
+            kv.setdefault("tokenizer.ggml.eos_token_id", eos)
+        if isinstance(gc.get("bos_token_id"), int):
+            kv.setdefault("tokenizer.ggml.bos_token_id", gc["bos_token_id"])
+    if "add_bos_token" in tc:
+        kv["tokenizer.ggml.add_bos_token"] = bool(tc["add_bos_token"])
+    if "add_eos_token" in tc:
+        kv["tokenizer.ggml.add_eos_token"] = bool(tc["add_eos_token"])
+    if isinstance(tc.get("chat_template"), str):
+        kv["tokenizer.chat_template"] = tc["chat_template"]
+    return kv
+
+
+# ---------------------------------------------------------------------------------------------------
+# conversion
+# ---------------------------------------------------------------------------------------------------
+def _encode(t: torch.Tensor, name: str, outtype: str) -> tuple[GGMLType, torch.Tensor]:
+    if t.dim() < 2 or name.endswith(("_norm.weight", ".bias")) or "ffn_gate_inp" in name:
+        return GGMLType.F32, quants.quantize(t.float(), GGMLType.F32)
+    want = {"f32": GGMLType.F32, "f16": GGMLType.F16, "bf16": GGMLType.BF16}.get(outtype)
+    if want is None:
+        want = GGMLType.BF16 if t.dtype == torch.bfloat16 else GGMLType.F16 if t.dtype == torch.float16 else GGMLType.F32
+    return want, quants.quantize(t.float(), want)
+
+
+def convert_tensors(src: ModelDir, cfg: dict[str, Any], arch: str, outtype: str = "auto",
+                    progress: Callable[[str], None] | None = None) -> Iterator[WriteTensor]:
+    c = cfg.get("text_config", cfg) if arch == "gemma3" else cfg
+    n_head, n_kv = c["num_attention_heads"], c.get("num_key_value_heads", c["num_attention_heads"])
+    experts: dict[str, dict[int, str]] = {}
+    names: dict[str, str] = {}
+    for name in src.keys():
+        if _SKIP.fullmatch(name):
+            continue
+        out = map_name(name, arch)
+        if out is None:
+            raise ConvertError(f"tensor {name} has no GGUF counterpart for architecture {arch}")
+        if "#" in out:
+            base, e = out.split("#")
+            experts.setdefault(base, {})[int(e)] = name
+        else:
+            names[out] = name
+    tied = "output.weight" not in names
+
+    def emit(out: str, t: torch.Tensor) -> WriteTensor:
+        if progress:
+            progress(out)
+        if arch == "llama" and re.fullmatch(r"blk\.\d+\.attn_[qk]\.(weight|bias)", out):
+            t = permute_qk(t, n_head if ".attn_q." in out else n_kv)
+        if arch in ("gemma", "gemma2", "gemma3") and out.endswith("_norm.weight"):
+            t = t.float() + 1.0              # the checkpoint stores w - 1
+        dt, raw = _encode(t, out, outtype)
+        return WriteTensor(out, tuple(reversed(t.shape)), dt, raw.cpu().numpy())
+
+    for out in sorted(names, key=_order):
+        if out == "output.weight" and tied:
+            continue
+        yield emit(out, src.tensor(names[out]))
+    for base in sorted(experts, key=_order):
+        idx = experts[base]
+        if sorted(idx) != list(range(len(idx))):
+            raise ConvertError(f"{base}: expert indices are not contiguous")
+        yield emit(base, torch.stack([src.tensor(idx[e]) for e in range(len(idx))]))
+    ff = rope_freq_factors(c)
+    if ff is not None:
+        yield emit("rope_freqs.weight", ff)
+
+
+def _order(name: str) -> tuple:
+    m = re.match(r"blk\.(\d+)\.(.*)", name)
+    return (1, int(m.group(1)), m.group(2)) if m else (0, 0, name)
+
+
+def convert_hf(path: str, out_path: str, outtype: str = "auto", progress: Callable[[str], None] | None = None) -> dict[str, Any]:
+    """Convert the checkpoint directory ``path`` into the GGUF file ``out_path``; returns the metadata written."""
+    with open(os.path.join(path, "config.json"), encoding="utf-8") as f:
+        cfg = json.load(f)
+    archs = cfg.get("architectures") or []
+    if not archs or archs[0] not in ARCHS:
+        raise ConvertError(f"unsupported architecture {archs[0] if archs else '(none)'}")
+    arch = ARCHS[archs[0]]
+    src = ModelDir(path)
+    try:
+        kv = _kv(cfg, arch, os.path.basename(os.path.normpath(path)))
+        kv.update(tokenizer_kv(path, kv.get(f"{arch}.vocab_size", 0)))
+        tensors = list(convert_tensors(src, cfg, arch, outtype, progress))
+        types = {t.dtype for t in tensors if len(t.shape) >= 2}
+        kv["general.file_type"] = 32 if GGMLType.BF16 in types else 1 if GGMLType.F16 in types else 0
+        write_gguf(out_path, kv, tensors)
+    finally:
+        src.close()
+    return kv
+
+
+def is_hf_dir_listing(names: list[str]) -> bool:
+    return "config.json" in names and any(n.endswith(".safetensors") for n in names)

@@ -100,6 +100,10 @@ def quantize_gguf(src: str, dst: str, target: str, progress: Callable[[str], Non
         g.close()
 
 
+def _is_checkpoint_dir(names: list[str]) -> bool:
+    return "config.json" in names and any(n.endswith(".safetensors") for n in names)
+
+
 def create_model(req: dict[str, Any]) -> Iterator[dict[str, Any]]:
     """Generator of progress objects ({"status": ...}); raises :class:`CreateError` on bad requests."""
     name = parse_name(req.get("model") or req.get("name") or "")
@@ -125,6 +129,26 @@ def create_model(req: dict[str, Any]) -> Iterator[dict[str, Any]]:
         config.update(base.config)
         base_opts, base_template, base_system = dict(base.options), base.template, base.system
         base_messages, base_license = list(base.messages), list(base.license)
+    elif req.get("files") and _is_checkpoint_dir(list(req["files"])):
+        # a Hugging Face checkpoint (config.json + *.safetensors + tokenizer files): convert to GGUF first
+        from ..convert.hf import ConvertError, convert_hf
+        yield {"status": "converting model"}
+        with tempfile.TemporaryDirectory(dir=M.blobs_dir()) as tmp:
+            for fname, digest in req["files"].items():
+                p = M.blob_path(digest)
+                if not os.path.exists(p):
+                    raise CreateError(f"blob {digest} for file {fname} not found")
+                if os.path.basename(fname) != fname or fname in ("", ".", ".."):
+                    raise CreateError(f"invalid file name {fname!r}")
+                os.symlink(p, os.path.join(tmp, fname))
+            out = os.path.join(tmp, "model.gguf")
+            try:
+                convert_hf(tmp, out)
+            except (ConvertError, KeyError, OSError) as e:
+                raise CreateError(f"conversion failed: {e}") from None
+            layer = M.new_layer(out, M.MT_MODEL)
+        layers.append(layer)
+        config.update(gguf_config(layer.path()))
     elif req.get("files"):
         for fname, digest in req["files"].items():
             p = M.blob_path(digest)

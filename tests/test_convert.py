@@ -1,0 +1,86 @@
+"""Hugging Face checkpoint -> GGUF: logits of the converted file on the fp32 graph equal the transformers model's."""
+import json
+import os
+
+import pytest
+import torch
+
+from ollama_b200.convert.hf import convert_hf, map_name, permute_qk
+from ollama_b200.convert.safetensors import SafetensorsError, SafetensorsFile, save_file
+
+
+def test_safetensors_roundtrip_and_limits(tmp_path):
+    t = {"a": torch.randn(3, 5), "b": torch.arange(7, dtype=torch.int32), "c": torch.randn(2, 2).to(torch.bfloat16), "s": torch.tensor(3.0)}
+    p = tmp_path / "x.safetensors"
+    save_file(t, p, {"format": "pt"})
+    with SafetensorsFile(p) as f:
+        assert set(f.keys()) == set(t) and f.metadata == {"format": "pt"}
+        for k, v in t.items():
+            assert torch.equal(f.tensor(k), v) and f.shape(k) == tuple(v.shape)
+    raw = bytearray(p.read_bytes())
+    raw[:8] = (10 ** 12).to_bytes(8, "little")
+    (tmp_path / "bad.safetensors").write_bytes(bytes(raw))
+    with pytest.raises(SafetensorsError):
+        SafetensorsFile(tmp_path / "bad.safetensors")
+
+
+def test_name_mapping_and_permutation():
+    assert map_name("model.layers.3.self_attn.q_proj.weight", "llama") == "blk.3.attn_q.weight"
+    assert map_name("model.layers.0.post_attention_layernorm.weight", "llama") == "blk.0.ffn_norm.weight"
+    assert map_name("model.layers.0.post_attention_layernorm.weight", "gemma2") == "blk.0.post_attention_norm.weight"
+    assert map_name("model.layers.1.mlp.experts.5.down_proj.weight", "qwen3moe") == "blk.1.ffn_down_exps.weight#5"
+    assert map_name("model.layers.1.block_sparse_moe.experts.2.w3.weight", "llama") == "blk.1.ffn_up_exps.weight#2"
+    assert map_name("lm_head.weight", "qwen3") == "output.weight" and map_name("model.foo", "llama") is None
+    w = torch.arange(16.0).view(8, 2)          # 2 heads x head_dim 4
+    p = permute_qk(w, 2)
+    assert p[:, 0].tolist() == [0.0, 4.0, 2.0, 6.0, 8.0, 12.0, 10.0, 14.0]     # (i, i + hd/2) pairs become neighbours
+
+
+def _tiny_tokenizer(path):
+    from tokenizers import Tokenizer, models, pre_tokenizers
+    vocab = {chr(ord("a") + i): i for i in range(26)}
+    vocab.update({"ab": 26, "<s>": 27, "</s>": 28})
+    tok = Tokenizer(models.BPE(vocab=vocab, merges=[("a", "b")]))
+    tok.pre_tokenizer = pre_tokenizers.ByteLevel(add_prefix_space=False)
+    tok.add_special_tokens(["<s>", "</s>"])
+    tok.save(os.path.join(path, "tokenizer.json"))
+    with open(os.path.join(path, "tokenizer_config.json"), "w") as f:
+        json.dump({"bos_token": "<s>", "eos_token": "</s>", "add_bos_token": True, "chat_template": "{{ messages }}"}, f)
+
+
+@pytest.mark.parametrize("family", ["llama", "qwen3", "qwen3moe"])
+def test_converted_checkpoint_matches_transformers(tmp_path, family):
+    transformers = pytest.importorskip("transformers")
+    torch.manual_seed(0)
+    common = dict(vocab_size=64, hidden_size=64, intermediate_size=96, num_hidden_layers=2, num_attention_heads=4, num_key_value_heads=2,
+                  max_position_embeddings=128, rms_norm_eps=1e-5, rope_theta=10000.0, tie_word_embeddings=False)
+    if family == "llama":
+        cfg = transformers.LlamaConfig(**common)
+        model = transformers.LlamaForCausalLM(cfg)
+    elif family == "qwen3":
+        cfg = transformers.Qwen3Config(head_dim=32, **common)
+        model = transformers.Qwen3ForCausalLM(cfg)
+    else:
+        cfg = transformers.Qwen3MoeConfig(head_dim=16, num_experts=4, num_experts_per_tok=2, moe_intermediate_size=32, norm_topk_prob=True,
+                                          decoder_sparse_step=1, mlp_only_layers=[], **common)
+        model = transformers.Qwen3MoeForCausalLM(cfg)
+    model = model.float().eval()
+    src = tmp_path / "hf"
+    model.save_pretrained(src, safe_serialization=True)
+    _tiny_tokenizer(str(src))
+    names = os.listdir(src)
+    if not any(n.endswith(".safetensors") for n in names):
+        pytest.skip("this transformers build did not write safetensors")
+    out = str(tmp_path / "m.gguf")
+    kv = convert_hf(str(src), out, outtype="f32")
+    assert kv["general.architecture"] == family and kv["tokenizer.ggml.model"] == "gpt2" and kv["tokenizer.ggml.bos_token_id"] == 27
+    assert kv["tokenizer.chat_template"] == "{{ messages }}" and len(kv["tokenizer.ggml.tokens"]) == 64
+
+    from ollama_b200.engine.backend import TorchBackend, open_model
+    be = TorchBackend(open_model(out), "cpu")
+    be.alloc(1, 64)
+    ids = torch.randint(0, 64, (11,), generator=torch.Generator().manual_seed(1))
+    with torch.no_grad():
+        ref = model(ids[None]).logits[0, -1]
+    got = be.prefill(0, ids.tolist(), 0)
+    assert torch.allclose(got, ref, atol=2e-4, rtol=1e-3), (got - ref).abs().max()
