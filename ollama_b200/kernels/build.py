@@ -84,6 +84,12 @@ def build_host(verbose: bool = False, force: bool = False) -> str | None:
             sys.stderr.write(r.stdout + r.stderr)
         if r.returncode:
             raise RuntimeError("host library build failed")
+    probe_src, probe_bin = os.path.join(NATIVE, "devquery.cpp"), os.path.join(NATIVE, "devquery")
+    if os.path.exists(probe_src) and (force or _stale(probe_bin, [probe_src])):      # the device probe also exists as a stand-alone child program
+        r = subprocess.run(["g++", "-O2", "-std=c++17", "-DB2_DEVQUERY_MAIN", probe_src, "-ldl", "-o", probe_bin], capture_output=True, text=True)
+        if r.returncode:
+            sys.stderr.write(r.stdout + r.stderr)
+            raise RuntimeError("device probe build failed")
     return HOSTLIB
 
 
