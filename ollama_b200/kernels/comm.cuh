@@ -154,3 +154,47 @@ __device__ __forceinline__ void ll_consumed(CommChan* ch, unsigned total_ctas, u
         }
     }
 }
+
+// Adds one rank's partial row (low-latency protocol) to acc: thread `tid` of 256 owns float4 chunks tid + 256 j.
+// All loads of the row are issued back to back and only then checked, so a row costs one L2 round trip when the
+// data is already there (polling word by word would cost one round trip per word); words that have not arrived
+// yet are re-read until the channel's time limit.
+template <int MAXJ>
+__device__ __forceinline__ void ll_add_row(const uint2* row, int tid, int nchunk, unsigned e, CommChan* ch, float4 (&acc)[MAXJ]) {
+    uint4 w0[MAXJ], w1[MAXJ];
+    unsigned long long t0 = 0, limit = 0;
+    for (;;) {
+#pragma unroll
+        for (int j = 0; j < MAXJ; j++) {
+            const int c = tid + 256 * j;
+            if (c < nchunk) {
+                w0[j] = ld_volatile_u4(row + 4 * c);
+                w1[j] = ld_volatile_u4(row + 4 * c + 2);
+            }
+        }
+        bool pending = false;
+#pragma unroll
+        for (int j = 0; j < MAXJ; j++) {
+            const int c = tid + 256 * j;
+            if (c < nchunk) pending |= (w0[j].y != e) | (w0[j].w != e) | (w1[j].y != e) | (w1[j].w != e);
+        }
+        if (!pending) break;
+        if (*(volatile int*)&ch->status != 0) return;           // an earlier wait already ran out: contribute nothing
+        if (limit == 0) {
+            t0 = global_ns();
+            const unsigned ms = ld_volatile_u32(&ch->wait_ms);
+            limit = (unsigned long long)(ms ? ms : 2000u) * 1000000ull;
+        } else if (global_ns() - t0 > limit) {
+            atomicExch(&ch->status, (int)KS_TIMEOUT);
+            return;
+        }
+    }
+#pragma unroll
+    for (int j = 0; j < MAXJ; j++) {
+        const int c = tid + 256 * j;
+        if (c < nchunk) {
+            acc[j].x += __uint_as_float(w0[j].x); acc[j].y += __uint_as_float(w0[j].z);
+            acc[j].z += __uint_as_float(w1[j].x); acc[j].w += __uint_as_float(w1[j].z);
+        }
+    }
+}

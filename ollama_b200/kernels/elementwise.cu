@@ -60,19 +60,7 @@ __global__ void __launch_bounds__(256) rmsnorm_quant_kernel(const __grid_constan
             v[j] = c < nchunk ? *(const float4*)(x + 4 * c) : make_float4(0.f, 0.f, 0.f, 0.f);
         }
         if (part) {      // k <= 8192 here (checked by the launcher): the reduced row is complete in registers
-            for (int r = 0; r < a.n_part; r++) {
-#pragma unroll
-                for (int j = 0; j < MAXJ; j++) {
-                    const int c = tid + 256 * j;
-                    if (c < nchunk) {
-                        const uint2* pp = part + r * a.part_stride + 4 * c;
-                        float t0, t1, t2, t3;
-                        ll_read2(pp, ep, a.chan, t0, t1);
-                        ll_read2(pp + 2, ep, a.chan, t2, t3);
-                        v[j].x += t0; v[j].y += t1; v[j].z += t2; v[j].w += t3;
-                    }
-                }
-            }
+            for (int r = 0; r < a.n_part; r++) ll_add_row<MAXJ>(part + r * a.part_stride, tid, nchunk, ep, a.chan, v);
 #pragma unroll
             for (int j = 0; j < MAXJ; j++) {
                 const int c = tid + 256 * j;

@@ -48,7 +48,9 @@ struct Cfg {
     static constexpr int A_BYTES = BM * BK * 2;
     static constexpr int B_BYTES = BN * BK * 2;
     static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
-    static constexpr int TOTAL = STAGES * STAGE_BYTES + 1024 /*alignment slack*/ + 256 /*barriers*/;
+    static constexpr int EPI_LD = 36;                                   // padded row of the epilogue's 32 x 32 transpose tile (floats)
+    static constexpr int EPI_BYTES = 4 * 32 * EPI_LD * 4;              // one tile per epilogue warp
+    static constexpr int TOTAL = STAGES * STAGE_BYTES + EPI_BYTES + 1024 /*alignment slack*/ + 256 /*barriers*/;
     static constexpr int TMEM_COLS = 2 * BN < 32 ? 32 : 2 * BN;
 };
 
@@ -72,7 +74,8 @@ __global__ void __launch_bounds__(192, 1) gemm_bf16_tc_kernel(const __grid_const
     using L = Cfg<BN>;
     constexpr int STAGES = L::STAGES;
     uint8_t* tiles = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);     // 128-byte swizzle wants 1024-byte alignment
-    uint64_t* full = reinterpret_cast<uint64_t*>(tiles + STAGES * L::STAGE_BYTES);
+    float* epi = reinterpret_cast<float*>(tiles + STAGES * L::STAGE_BYTES);
+    uint64_t* full = reinterpret_cast<uint64_t*>(tiles + STAGES * L::STAGE_BYTES + L::EPI_BYTES);
     uint64_t* empty = full + STAGES;
     uint64_t* acc_full = empty + STAGES;
     uint64_t* acc_empty = acc_full + 2;
@@ -160,60 +163,46 @@ __global__ void __launch_bounds__(192, 1) gemm_bf16_tc_kernel(const __grid_const
             const int buf = i & 1, use = i >> 1;
             if (!mbar_wait(&acc_full[buf], use & 1)) { ok = false; break; }
             tc_fence_after();
-            const int row = mt * BM + q * 32 + lane, n0 = nt * BN;
-            float* of = nullptr;
-            __nv_bfloat16* oh = nullptr;
-            if (row < p.m) {
-                if (p.cm.n_dst > 0) {
-                    const int owner = row / p.rows_per_rank;
-                    of = p.cm.dst[owner] + (size_t)(row - owner * p.rows_per_rank) * p.ldo + n0;
-                } else if (p.out_bf16) {
-                    oh = (__nv_bfloat16*)p.out + (size_t)row * p.ldo + n0;
-                } else {
-                    of = (float*)p.out + (size_t)row * p.ldo + n0;
-                }
-            }
+            // Each thread reads 32 columns of its own accumulator row; a 32 x 32 transpose through shared memory turns that into
+            // stores of 4 rows x 128 contiguous bytes per warp instruction (full lines for HBM, full packets for NVLink peers).
+            const int n0 = nt * BN;
+            float* st = epi + (warp - 2) * 32 * L::EPI_LD;
+            const int sub = lane >> 3, cq = (lane & 7) * 4;                 // store phase: row within a group of 4, first of 4 columns
 #pragma unroll 1
             for (int c0 = 0; c0 < BN; c0 += 32) {
                 uint32_t v[32];
                 const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(buf * BN + c0);
                 tmem_ld32(taddr, v);
                 if (n0 + c0 >= p.n) continue;       // warp-uniform
-                if (p.bias) {
 #pragma unroll
-                    for (int j = 0; j < 32; j += 4) {
-                        if (n0 + c0 + j < p.n) {
-                            const float4 b = *(const float4*)(p.bias + n0 + c0 + j);
-                            v[j] = __float_as_uint(__uint_as_float(v[j]) + b.x);
-                            v[j + 1] = __float_as_uint(__uint_as_float(v[j + 1]) + b.y);
-                            v[j + 2] = __float_as_uint(__uint_as_float(v[j + 2]) + b.z);
-                            v[j + 3] = __float_as_uint(__uint_as_float(v[j + 3]) + b.w);
-                        }
-                    }
-                }
-                if (of) {
+                for (int j = 0; j < 32; j += 4)
+                    *(uint4*)(st + lane * L::EPI_LD + j) = make_uint4(v[j], v[j + 1], v[j + 2], v[j + 3]);
+                __syncwarp();
+                const int col = n0 + c0 + cq;
+                float4 bias = make_float4(0.f, 0.f, 0.f, 0.f);
+                if (p.bias && col < p.n) bias = *(const float4*)(p.bias + col);
 #pragma unroll
-                    for (int j = 0; j < 32; j += 4) {
-                        if (n0 + c0 + j >= p.n) break;
-                        float4 r = make_float4(__uint_as_float(v[j]), __uint_as_float(v[j + 1]), __uint_as_float(v[j + 2]), __uint_as_float(v[j + 3]));
+                for (int rr = 0; rr < 8; rr++) {
+                    const int lr = rr * 4 + sub;
+                    const int row = mt * BM + q * 32 + lr;
+                    if (row >= p.m || col >= p.n) continue;
+                    float4 r = *(const float4*)(st + lr * L::EPI_LD + cq);
+                    r.x += bias.x; r.y += bias.y; r.z += bias.z; r.w += bias.w;
+                    if (p.cm.n_dst > 0) {
+                        const int owner = row / p.rows_per_rank;
+                        *(float4*)(p.cm.dst[owner] + (size_t)(row - owner * p.rows_per_rank) * p.ldo + col) = r;
+                    } else if (p.out_bf16) {
+                        *(uint2*)((__nv_bfloat16*)p.out + (size_t)row * p.ldo + col) = make_uint2(pack2_bf16(r.x, r.y), pack2_bf16(r.z, r.w));
+                    } else {
+                        float* o = (float*)p.out + (size_t)row * p.ldo + col;
                         if (p.accumulate) {
-                            const float4 old = *(const float4*)(of + c0 + j);
+                            const float4 old = *(const float4*)o;
                             r.x += old.x; r.y += old.y; r.z += old.z; r.w += old.w;
                         }
-                        *(float4*)(of + c0 + j) = r;
-                    }
-                } else if (oh) {
-#pragma unroll
-                    for (int j = 0; j < 32; j += 8) {
-                        if (n0 + c0 + j >= p.n) break;
-                        uint4 r;
-                        r.x = pack2_bf16(__uint_as_float(v[j]), __uint_as_float(v[j + 1]));
-                        r.y = pack2_bf16(__uint_as_float(v[j + 2]), __uint_as_float(v[j + 3]));
-                        r.z = pack2_bf16(__uint_as_float(v[j + 4]), __uint_as_float(v[j + 5]));
-                        r.w = pack2_bf16(__uint_as_float(v[j + 6]), __uint_as_float(v[j + 7]));
-                        *(uint4*)(oh + c0 + j) = r;
+                        *(float4*)o = r;
                     }
                 }
+                __syncwarp();
             }
             tc_fence_before();
             __syncwarp();
