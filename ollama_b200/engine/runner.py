@@ -110,6 +110,12 @@ class Runner:
         self.path = model_path
         t0 = time.time()
         self.gguf = open_model(model_path) if model_path else None     # a ready backend may come without a file
+        self._tp_group = None
+        if backend is None and self._tp_devices():
+            # the model is split over several GPUs: this process leads, one spawned follower per further GPU repeats its calls
+            from ..parallel.launcher import TPGroup
+            self._tp_group = TPGroup(model_path, self._tp_devices(), max_chunk=max(512, min(int(self.opts.num_batch), 2048)))
+            backend = self._tp_group.backend
         self.backend = backend if backend is not None else make_backend(self.gguf, self.opts.device, opts=self.opts)
         self.cfg = self.backend.cfg
         try:
@@ -199,12 +205,35 @@ class Runner:
             raise RunnerError(ch.error)
         return ch.embedding or [], ch.prompt_eval_count
 
+    def _tp_devices(self) -> list[int]:
+        """GPUs of a tensor-parallel group for this model ([] = single device): ``tp`` option or B200_TP, when the split divides the model."""
+        from .. import envconfig
+        tp = int(self.opts.tp) if int(self.opts.tp) > 1 else envconfig.tp_degree()
+        if tp < 2 or self.gguf is None or str(self.opts.device).startswith("cpu"):
+            return []
+        import torch
+        if not torch.cuda.is_available() or torch.cuda.device_count() < tp:
+            return []
+        try:
+            from ..models.config import config_from_gguf
+            from ..parallel.tp_engine import shard_plan
+            cfg = config_from_gguf(self.gguf)
+            shard_plan(cfg, tp, {n: t.dtype for n, t in self.gguf.tensors.items()})
+            if cfg.sandwich_norm or cfg.d_model > 8192:
+                return []
+        except (ValueError, NotImplementedError):
+            return []
+        return list(range(tp))
+
     def close(self) -> None:
         with self.cv:
             self.closed = True
             self.cv.notify_all()
         self.thread.join(timeout=30)
-        self.backend.close()
+        if self._tp_group is not None:
+            self._tp_group.close()
+        else:
+            self.backend.close()
         if self.gguf is not None:
             self.gguf.close()
 

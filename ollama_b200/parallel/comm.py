@@ -1,8 +1,9 @@
 """Peer-mapped memory and flag channels for the tensor-parallel engine.
 
 Each rank (one process per GPU) allocates one region with ``cudaMalloc``, exports it as a CUDA IPC handle,
-and opens every other rank's region; handles travel through the ``torch.distributed`` process group (NCCL or
-gloo), which is used for this rendezvous and for barriers only.  All data of a forward pass moves through
+and opens every other rank's region; handles travel over the group's host transport (``parallel/transport.py``:
+a ``torch.distributed`` group or pipes to spawned followers), which carries this rendezvous, barriers and the
+leader's call records and nothing else.  All data of a forward pass moves through
 stores to peer addresses issued by the compute kernels themselves (``kernels/comm.cuh``).
 
 The reference stack spreads a model over GPUs by layer / row splits inside ggml's scheduler and exchanges
@@ -65,7 +66,9 @@ class PeerRegion:
     """One peer-mapped allocation per rank; ``base[r]`` is rank r's region as seen from this process."""
 
     def __init__(self, nbytes: int, rank: int, world: int, device, group=None):
-        import torch.distributed as dist
+        """``group``: a transport (parallel/transport.py), or a torch.distributed group / None for the default group."""
+        from .transport import DistTransport
+        tr = group if hasattr(group, "all_gather") else DistTransport(rank, world, group)
         self.rank, self.world, self.device, self.nbytes = rank, world, torch.device(device), nbytes
         if world > K.COMM_MAX_RANKS:
             raise ValueError(f"at most {K.COMM_MAX_RANKS} ranks per tensor-parallel group")
@@ -78,8 +81,7 @@ class PeerRegion:
         handle = C.create_string_buffer(64)
         with torch.cuda.device(self.device):
             K._check(lib.b2_ipc_alloc(nbytes, C.byref(p), handle), "ipc_alloc")
-            handles: list = [None] * world
-            dist.all_gather_object(handles, handle.raw, group=group)
+            handles: list = tr.all_gather(handle.raw)
             self.base: list[int] = []
             for r in range(world):
                 if r == rank:
@@ -88,8 +90,8 @@ class PeerRegion:
                 q = C.c_void_p()
                 K._check(lib.b2_ipc_open(handles[r], C.byref(q)), f"ipc_open(rank {r})")
                 self.base.append(q.value)
-        dist.barrier(group=group)
-        self.group = group
+        tr.barrier()
+        self.transport = tr
         self._open = True
 
     def chan(self, idx: int, r: int | None = None) -> int:
@@ -136,11 +138,10 @@ class PeerRegion:
     def close(self) -> None:
         if not self._open:
             return
-        import torch.distributed as dist
         self._open = False
         torch.cuda.synchronize(self.device)
         try:
-            dist.barrier(group=self.group)      # nobody may still be writing into a region that is about to go away
+            self.transport.barrier()      # nobody may still be writing into a region that is about to go away
         except Exception:
             pass
         lib = K.lib()

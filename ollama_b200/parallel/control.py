@@ -1,8 +1,8 @@
 """Leader / follower control of a tensor-parallel group.
 
 The serving stack (scheduler, runner, HTTP) lives in rank 0 only.  Every call rank 0 makes on its
-tensor-parallel backend is first announced to the other ranks over a host-side channel (a gloo broadcast of a
-small int32 record), and each follower repeats the call on its own shard; the device-side exchanges then
+tensor-parallel backend is first announced to the other ranks over the group's host transport (a gloo broadcast
+or a pipe per follower carrying a small int32 record), and each follower repeats the call on its own shard; the device-side exchanges then
 meet inside the kernels.  Followers never see requests, samplers or tokenizers: what they need is the call
 and its integer arguments.
 
@@ -18,7 +18,6 @@ from __future__ import annotations
 from typing import Sequence
 
 import torch
-import torch.distributed as dist
 
 OP_ALLOC, OP_PREFILL, OP_DECODE, OP_DECODE_ARGMAX, OP_DECODE_LOOP, OP_HIDDEN, OP_CLOSE, OP_SET = range(8)
 REC = 40          # int32 words per record: [op, seq, a, b, c, d, n, payload[32] ...]
@@ -27,39 +26,33 @@ _HDR = 8
 
 class TPControl:
     def __init__(self, rank: int, world: int, group=None):
-        """``group`` must be a gloo group spanning the tensor-parallel ranks (created on every rank in the same order)."""
+        """``group``: a transport (parallel/transport.py), or a torch.distributed group / None for the default group."""
+        from .transport import DistTransport
         self.rank, self.world = rank, world
-        self.group = group if group is not None else dist.new_group(backend="gloo")
+        self.tr = group if hasattr(group, "bcast_ints") else DistTransport(rank, world, group)
         self.seq = 0
-        self.src = dist.get_global_rank(self.group, 0) if hasattr(dist, "get_global_rank") else 0
 
     # -- leader -------------------------------------------------------------------------------------
     def send(self, op: int, a: int = 0, b: int = 0, c: int = 0, d: int = 0, payload: Sequence[int] = ()) -> None:
         self.seq += 1
-        rec = torch.zeros(REC, dtype=torch.int32)
+        payload = [int(v) for v in payload]
         n = len(payload)
-        rec[0], rec[1], rec[2], rec[3], rec[4], rec[5], rec[6] = op, self.seq & 0x7FFFFFFF, a, b, c, d, n
+        rec = [op, self.seq & 0x7FFFFFFF, a, b, c, d, n, 0] + [0] * (REC - _HDR)
         inline = n <= REC - _HDR
-        if inline and n:
-            rec[_HDR:_HDR + n] = torch.as_tensor(list(payload), dtype=torch.int32)
-        dist.broadcast(rec, self.src, group=self.group)
+        if inline:
+            rec[_HDR:_HDR + n] = payload
+        self.tr.bcast_ints(rec, REC)
         if not inline:
-            dist.broadcast(torch.as_tensor(list(payload), dtype=torch.int32), self.src, group=self.group)
+            self.tr.bcast_ints(payload, n)
 
     # -- follower -----------------------------------------------------------------------------------
     def recv(self) -> tuple[int, int, int, int, int, list[int]]:
-        rec = torch.zeros(REC, dtype=torch.int32)
-        dist.broadcast(rec, self.src, group=self.group)
-        op, seq, a, b, c, d, n = rec[:7].tolist()
+        rec = self.tr.bcast_ints(None, REC)
+        op, seq, a, b, c, d, n = rec[:7]
         self.seq += 1
         if seq != self.seq & 0x7FFFFFFF:
             raise RuntimeError(f"tensor-parallel control channel out of step: got record {seq}, expected {self.seq}")
-        if n <= REC - _HDR:
-            payload = rec[_HDR:_HDR + n].tolist()
-        else:
-            buf = torch.zeros(n, dtype=torch.int32)
-            dist.broadcast(buf, self.src, group=self.group)
-            payload = buf.tolist()
+        payload = rec[_HDR:_HDR + n] if n <= REC - _HDR else self.tr.bcast_ints(None, n)
         return op, a, b, c, d, payload
 
 

@@ -28,3 +28,32 @@ def test_tp_matches_single_gpu(world, model, quant):
         pytest.skip(f"needs {world} GPUs")
     res = _run(world, 29540 + world, "--model", model, "--quant", quant)
     assert res["ok"] and res["comm_status"] == 0
+
+
+def test_runner_leads_a_spawned_group(tmp_path):
+    """The public runner with tp=2: followers are spawned per GPU, connected by pipes, and the tokens equal the single-GPU run."""
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs 2 GPUs")
+    from ollama_b200.engine.runner import CompletionRequest, Runner, RunnerOptions
+    from ollama_b200.engine.sampler import SamplingParams
+    from ollama_b200.models.synth import write_synthetic_gguf
+    p = str(tmp_path / "m.gguf")
+    write_synthetic_gguf(p, "tiny-tp", "Q8_0")
+    prompt = torch.randint(259, 4000, (40,), generator=torch.Generator().manual_seed(2)).tolist()
+    outs = []
+    for tp in (1, 2):
+        r = Runner(p, RunnerOptions(num_ctx=256, num_parallel=2, device="cuda", tp=tp))
+        try:
+            assert (r._tp_group is not None) == (tp == 2)
+            seq = r.submit(CompletionRequest(prompt=prompt, sampling=SamplingParams(temperature=0), num_predict=12, ignore_eos=True))
+            toks = []
+            while True:
+                ch = seq.out.get(timeout=120)
+                assert not ch.error, ch.error
+                toks += ch.tokens
+                if ch.done:
+                    break
+            outs.append(toks)
+        finally:
+            r.close()
+    assert len(outs[0]) == 12 and outs[0] == outs[1]
