@@ -117,6 +117,12 @@ class Sampler:
         probs = torch.softmax(vals / max(p.temperature, 1e-6), -1)
         return idx, probs
 
+    def _on_device(self, logits: torch.Tensor, allowed) -> bool:
+        """The sampling kernel covers top-k candidate sets up to 256 without typical-p, grammar or log-probabilities."""
+        p = self.p
+        return (logits.is_cuda and allowed is None and not p.logprobs and 0 < p.top_k <= 256 and not (0.0 < p.typical_p < 1.0)
+                and logits.shape[-1] >= p.top_k)
+
     def sample(self, logits: torch.Tensor, allowed=None) -> tuple[int, TokenLogprob | None]:
         """Draw one token from ``logits`` ([vocab]).  ``allowed(token) -> bool`` is the grammar filter."""
         p = self.p
@@ -126,6 +132,18 @@ class Sampler:
             tok = int(torch.argmax(lg).item())
             if allowed is not None and not allowed(tok):
                 tok = self._constrained(lg, allowed, greedy=True)
+        elif self._on_device(logits, allowed):
+            # the whole chain in one kernel on the logits where they are; only the sampled id comes back
+            from collections import Counter
+
+            from ..ops import cuda as K
+            u = float(torch.rand(1, generator=self.gen).item())
+            hist = dict(Counter(t for t in self.history if 0 <= t < logits.shape[-1])) if (p.has_penalties and self.history) else {}
+            row = logits.reshape(1, -1)
+            if row.dtype != torch.float32 or not row.is_contiguous():
+                row = row.float().contiguous()
+            tok = int(K.sample(row, [u], p.top_k, p.top_p, p.min_p, p.temperature, [hist], p.repeat_penalty, p.frequency_penalty,
+                               p.presence_penalty)[0].item())
         else:
             idx, probs = self.distribution(logits)
             j = int(torch.multinomial(probs.cpu(), 1, generator=self.gen).item())

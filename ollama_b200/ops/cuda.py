@@ -410,6 +410,54 @@ def gemm_q_scatter(x: torch.Tensor, w: DevWeight, ldo: int, cm: "CommSend", rows
     _check(f(ptr(x), m, C.addressof(d), ldo, C.addressof(cm), rows_per_rank, stream()), "gemm_q_scatter")
 
 
+class SampleRow(C.Structure):
+    _fields_ = [("n_hist", C.c_int), ("hist_off", C.c_int), ("u", C.c_float)]
+
+
+class SampleArgs(C.Structure):
+    _fields_ = [("logits", C.c_void_p), ("ld", C.c_int), ("vocab", C.c_int), ("rows", C.c_void_p), ("hist_ids", C.c_void_p),
+                ("hist_counts", C.c_void_p), ("repeat_penalty", C.c_float), ("freq_penalty", C.c_float), ("presence_penalty", C.c_float),
+                ("top_k", C.c_int), ("top_p", C.c_float), ("min_p", C.c_float), ("temperature", C.c_float), ("out_token", C.c_void_p),
+                ("out_prob", C.c_void_p), ("cand_idx", C.c_void_p), ("cand_prob", C.c_void_p), ("cand_n", C.c_void_p)]
+
+
+SAMPLE_MAX_K = 256
+
+
+def sample(logits: torch.Tensor, us: list[float], top_k: int, top_p: float, min_p: float, temperature: float,
+           history: list[dict[int, int]] | None = None, repeat_penalty: float = 1.0, freq_penalty: float = 0.0, presence_penalty: float = 0.0,
+           want_candidates: bool = False):
+    """Draw one token per row of ``logits`` [rows, vocab] (fp32, modified in place by the penalties) on the device.
+
+    ``us``: one uniform number per row; ``history``: per row, token id -> count inside the penalty window.
+    Returns the ids (int32 tensor on the device) or, with ``want_candidates``, (ids, probs, cand_idx, cand_prob, cand_n).
+    """
+    rows, vocab = logits.shape
+    dev = logits.device
+    meta = torch.zeros(rows, 3, dtype=torch.int32)
+    ids, cnts = [], []
+    for r in range(rows):
+        h = history[r] if history else {}
+        meta[r, 0], meta[r, 1] = len(h), len(ids)
+        ids += list(h.keys())
+        cnts += list(h.values())
+    meta[:, 2] = torch.tensor(us, dtype=torch.float32).view(torch.int32)
+    meta_d = meta.to(dev)
+    ids_d = torch.tensor(ids or [0], dtype=torch.int32, device=dev)
+    cnt_d = torch.tensor(cnts or [0], dtype=torch.int32, device=dev)
+    out = torch.empty(rows, dtype=torch.int32, device=dev)
+    prob = torch.empty(rows, dtype=torch.float32, device=dev)
+    ci = cp = cn = None
+    if want_candidates:
+        ci = torch.empty(rows, SAMPLE_MAX_K, dtype=torch.int32, device=dev)
+        cp = torch.empty(rows, SAMPLE_MAX_K, dtype=torch.float32, device=dev)
+        cn = torch.empty(rows, dtype=torch.int32, device=dev)
+    a = SampleArgs(ptr(logits), logits.stride(0), vocab, ptr(meta_d), ptr(ids_d), ptr(cnt_d), repeat_penalty, freq_penalty, presence_penalty,
+                   top_k, top_p, min_p, temperature, ptr(out), ptr(prob), ptr(ci), ptr(cp), ptr(cn))
+    _check(lib().b2_sample(C.byref(a), rows, stream()), "sample")
+    return (out, prob, ci, cp, cn) if want_candidates else out
+
+
 class GluRowsArgs(C.Structure):
     _fields_ = [("gu", C.c_void_p), ("out", C.c_void_p), ("f", C.c_int), ("act", C.c_int), ("alpha", C.c_float), ("limit", C.c_float)]
 

@@ -210,6 +210,41 @@ def test_attn_prefill(hd, H, Hkv, T, pos0, window, softcap, use_sinks, causal):
     assert torch.allclose(out, ref, atol=1e-2, rtol=2e-2), (out - ref).abs().max()
 
 
+@pytest.mark.parametrize("top_k,top_p,min_p,temp,penalties", [(40, 0.9, 0.0, 0.8, False), (1, 1.0, 0.0, 1.0, False), (256, 0.5, 0.05, 1.3, True),
+                                                              (64, 1.0, 0.2, 0.7, True)])
+def test_sample_kernel_matches_filter_chain(top_k, top_p, min_p, temp, penalties):
+    """Device sampler: candidate set and probabilities equal the torch filter chain; the draw follows the inverse CDF."""
+    K = _K()
+    from ollama_b200.engine.sampler import Sampler, SamplingParams
+    V, rows = 50257, 3
+    g = torch.Generator().manual_seed(top_k)
+    logits = (torch.randn(rows, V, generator=g) * 3).cuda()
+    logits[1, 100:110] = logits[1].max() + 1.0              # equal values at the top: ties are taken lowest id first
+    hist = [{5: 2, 77: 1, 40000: 3}, {}, {104: 1}] if penalties else None
+    params = SamplingParams(temperature=temp, top_k=top_k, top_p=top_p, min_p=min_p, repeat_penalty=1.3 if penalties else 1.0,
+                            frequency_penalty=0.2 if penalties else 0.0, presence_penalty=0.1 if penalties else 0.0, repeat_last_n=64)
+    us = [0.0, 0.37, 0.999]
+    ref_in = logits.clone()
+    tok, prob, ci, cp, cn = K.sample(logits.clone(), us, top_k, top_p, min_p, temp, hist, params.repeat_penalty, params.frequency_penalty,
+                                     params.presence_penalty, want_candidates=True)
+    for r in range(rows):
+        s = Sampler(params, V)
+        s.history = [t for t, c in (hist[r] if hist else {}).items() for _ in range(c)]
+        idx, probs = s.distribution(ref_in[r])
+        n = int(cn[r])
+        assert n == idx.numel(), (r, n, idx.numel())
+        got_i, got_p = ci[r, :n].cpu().long(), cp[r, :n].cpu()
+        assert torch.allclose(got_p, probs.cpu(), atol=1e-5, rtol=1e-4)
+        same = got_i == idx.cpu()
+        # equal logits may be ordered differently by torch.topk; everywhere else the ids agree
+        assert bool((same | (got_p == probs.cpu())).all()) and set(got_i.tolist()) == set(idx.cpu().tolist())
+        cdf = torch.cumsum(got_p, 0)
+        want = int(torch.searchsorted(cdf, torch.tensor(us[r] * float(cdf[-1])), right=True).clamp(max=n - 1))
+        assert int(tok[r]) == int(got_i[want]) and abs(float(prob[r]) - float(got_p[want])) < 1e-6
+    if top_k >= 10 and not penalties:
+        assert ci[1, :min(10, int(cn[1]))].tolist() == list(range(100, 110))[:min(10, int(cn[1]))]
+
+
 def test_moe_route_kernel():
     K = _K()
     import ctypes as C
