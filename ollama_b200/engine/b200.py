@@ -71,6 +71,7 @@ class B200Backend:
         self.n_slots = self.n_ctx = 0
         self._graphs: dict[tuple[int, bool], torch.cuda.CUDAGraph] = {}
         self.pdl = True
+        self.fuse_attn_combine = False    # one launch (last CTA merges the splits) measured slower than two launches joined by PDL
         self.use_graphs = True
         self.launches_per_step = 0
         self.launches_by_key: dict = {}
@@ -203,6 +204,7 @@ class B200Backend:
         b.logits = torch.zeros(MB, c.vocab_size, device=dev, dtype=f32)
         b.part_acc = torch.zeros(MB * c.n_heads * self.n_splits * c.head_dim, device=dev, dtype=f32)
         b.part_ml = torch.zeros(MB * c.n_heads * self.n_splits * 2, device=dev, dtype=f32)
+        b.attn_tickets = torch.zeros(MB * c.n_heads, device=dev, dtype=i32)
         b.meta = torch.zeros(3, MB, device=dev, dtype=i32)          # tokens | positions | slots of the decode batch
         b.tokens, b.positions, b.slots = b.meta[0], b.meta[1], b.meta[2]
         b.sampled = torch.zeros(MB, device=dev, dtype=i32)
@@ -328,8 +330,13 @@ class B200Backend:
                                   c.sliding_window if L.swa else 0, K.ptr(b.part_acc), K.ptr(b.part_ml))
             ca = K.AttnCombineArgs(K.ptr(b.part_acc), K.ptr(b.part_ml), K.ptr(L.sinks), c.n_heads, self.n_splits, c.head_dim,
                                    K.ptr(b.ao), K.ptr(b.aq), K.ptr(b.ads))
-            K._check(lib.b2_attn_decode(C.byref(aa), C.byref(ca), nb, c.head_dim, int(self.pdl), st()), "attn_decode")
-            self._n += 3
+            if self.fuse_attn_combine:      # the last CTA of every head group merges the splits: one launch instead of two
+                K._check(lib.b2_attn_decode_fused(C.byref(aa), C.byref(ca), C.c_void_p(K.ptr(b.attn_tickets)), nb, c.head_dim, int(self.pdl), st()),
+                         "attn_decode_fused")
+                self._n += 2
+            else:
+                K._check(lib.b2_attn_decode(C.byref(aa), C.byref(ca), nb, c.head_dim, int(self.pdl), st()), "attn_decode")
+                self._n += 3
             if c.sandwich_norm:
                 self._gemv([L.wo], nb, b.aq, b.ads, b.ao, b.tmp, b.tmp.stride(0))
                 self._norm_quant(b.tmp, L.post_attn_norm, nb, c.d_model, residual=b.x)

@@ -26,7 +26,7 @@ struct AttnDecodeArgs {
 };
 
 template <int HD, int G>
-__global__ void __launch_bounds__(128) attn_decode_kernel(const __grid_constant__ AttnDecodeArgs a) {
+__device__ __forceinline__ void attn_decode_body(const AttnDecodeArgs& a) {
     constexpr int LP = HD / 16;          // lanes per position
     constexpr int PPW = 32 / LP;         // positions per warp step
     const int split = blockIdx.x, b = blockIdx.z;
@@ -149,6 +149,11 @@ __global__ void __launch_bounds__(128) attn_decode_kernel(const __grid_constant_
     }
 }
 
+template <int HD, int G>
+__global__ void __launch_bounds__(128) attn_decode_kernel(const __grid_constant__ AttnDecodeArgs a) {
+    attn_decode_body<HD, G>(a);
+}
+
 struct AttnCombineArgs {
     const float* part_acc;
     const float2* part_ml;
@@ -189,6 +194,68 @@ __global__ void attn_combine_kernel(const __grid_constant__ AttnCombineArgs a) {
     }
 }
 
+// Split-K attention with the combine folded in: the CTA that finishes last for a (sequence, head group) merges the
+// splits of its heads, applies the sink, normalises and re-quantises, so the step needs one launch instead of two.
+struct AttnFusedArgs {
+    AttnDecodeArgs d;
+    AttnCombineArgs c;
+    unsigned* tickets;       // [nb][gridDim.y], zero before the first launch (the last CTA of a group resets its counter)
+};
+
+template <int HD, int G>
+__global__ void __launch_bounds__(128) attn_decode_fused_kernel(const __grid_constant__ AttnFusedArgs f) {
+    attn_decode_body<HD, G>(f.d);
+    __shared__ int s_last;
+    __threadfence();                     // this CTA's partials are visible before its ticket is
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        unsigned* t = f.tickets + (size_t)blockIdx.z * gridDim.y + blockIdx.y;
+        const unsigned prev = atomicAdd(t, 1u);
+        s_last = prev == gridDim.x - 1;
+        if (s_last) *t = 0u;
+    }
+    __syncthreads();
+    if (!s_last) return;
+    __threadfence();
+    const AttnCombineArgs& c = f.c;
+    const int b = blockIdx.z;
+    const int group = f.d.n_heads / f.d.n_kv_heads, hg_per_kv = group / G;
+    const int head0 = (blockIdx.y / hg_per_kv) * group + (blockIdx.y % hg_per_kv) * G;
+    for (int idx = threadIdx.x; idx < G * HD; idx += 128) {
+        const int h = head0 + idx / HD, d = idx % HD;
+        const size_t p0 = ((size_t)b * c.n_heads + h) * c.n_splits;
+        float mn = -1e30f;
+        for (int s = 0; s < c.n_splits; s++) mn = fmaxf(mn, __ldcg(&c.part_ml[p0 + s]).x);
+        if (c.sinks) mn = fmaxf(mn, c.sinks[h]);
+        float o = 0.f, l = 0.f;
+        for (int s = 0; s < c.n_splits; s++) {
+            const float2 ml = __ldcg(&c.part_ml[p0 + s]);
+            const float w = __expf(ml.x - mn);
+            o += __ldcg(&c.part_acc[(p0 + s) * HD + d]) * w;
+            l += ml.y * w;
+        }
+        if (c.sinks) l += __expf(c.sinks[h] - mn);
+        const float v = l > 0.f ? o / l : 0.f;
+        const size_t oi = ((size_t)b * c.n_heads + h) * HD + d;
+        if (c.out) c.out[oi] = v;
+        if (c.out_q) {
+            const float amax = warp_max(fabsf(v));
+            const float dq = amax / 127.f;
+            const int q = dq > 0.f ? __float2int_rn(v / dq) : 0;
+            const float sq = dq * warp_sum((float)q);
+            c.out_q[oi] = (int8_t)q;
+            if ((d & 31) == 0) c.out_ds[oi >> 5] = make_float2(dq, sq);
+        }
+    }
+}
+
+template <int HD>
+static const void* pick_decode_fused(int g) {
+    if (g >= 4) return (const void*)attn_decode_fused_kernel<HD, 4>;
+    if (g >= 2) return (const void*)attn_decode_fused_kernel<HD, 2>;
+    return (const void*)attn_decode_fused_kernel<HD, 1>;
+}
+
 template <int HD>
 static const void* pick_decode(int g) {
     if (g >= 4) return (const void*)attn_decode_kernel<HD, 4>;
@@ -227,6 +294,23 @@ B2_API int b2_attn_decode(const AttnDecodeArgs* a, const AttnCombineArgs* c, int
     AttnCombineArgs cc = *c;
     void* args2[] = {&cc};
     return (int)launch1((const void*)attn_combine_kernel, dim3(a->n_heads, nb), dim3(hd), args2, st, pdl);
+}
+
+// One launch: split-K attention with the merge of the splits done by the last CTA of every head group.
+// `tickets`: nb * n_kv_heads * (group / G) zero-initialised counters (at most nb * n_heads).
+B2_API int b2_attn_decode_fused(const AttnDecodeArgs* a, const AttnCombineArgs* c, unsigned* tickets, int nb, int hd, int pdl, cudaStream_t st) {
+    const int group = a->n_heads / a->n_kv_heads;
+    int G = group >= 4 && group % 4 == 0 ? 4 : (group % 2 == 0 ? 2 : 1);
+    const void* fn = nullptr;
+    if (hd == 64) fn = pick_decode_fused<64>(G);
+    else if (hd == 128) fn = pick_decode_fused<128>(G);
+    else if (hd == 256) fn = pick_decode_fused<256>(G);
+    else if (hd == 32) fn = pick_decode_fused<32>(G);
+    else return (int)cudaErrorInvalidValue;
+    dim3 grid(a->n_splits, a->n_kv_heads * (group / G), nb);
+    AttnFusedArgs f{*a, *c, tickets};
+    void* args[] = {&f};
+    return (int)launch1(fn, grid, dim3(128), args, st, pdl);
 }
 
 // ---------------------------------------------------------------------------------------------

@@ -4,10 +4,11 @@ One process per GPU.  Attention heads, KV cache and FFN columns are split N ways
 column-parallel, attention-output and FFN-down are row-parallel), the vocabulary projection is split by
 rows, norms and the token embedding are replicated.  Every rank runs the same sequence of calls (SPMD).
 
-Decode (1..8 sequences per step): the row-parallel GEMV writes its partial output rows straight into a
-receive buffer on every rank and raises a flag; the following fused add + RMSNorm + quantise kernel waits
-for the flags, sums the N partial rows into its replica of the residual stream and carries on.  There is
-no separate all-reduce kernel and the whole step still replays as one CUDA graph per rank.
+Decode (1..8 sequences per step): the row-parallel GEMV writes its partial output rows, each value tagged
+with the exchange's epoch, straight into a receive buffer on every rank; the following fused add + RMSNorm
++ quantise kernel polls the words of that epoch, sums the N partial rows into its replica of the residual
+stream and carries on.  There is no separate all-reduce kernel, no fence and no flag on this path, and the
+whole step still replays as one CUDA graph per rank.
 
 Prefill: the residual stream is sharded by token rows.  The row-parallel GEMM stores each partial tile
 into the owner of those rows (GEMM + reduce-scatter in one kernel), and one kernel per exchange does
@@ -206,8 +207,13 @@ class TPBackend(B200Backend):
                                   c.sliding_window if L.swa else 0, K.ptr(b.part_acc), K.ptr(b.part_ml))
             ca = K.AttnCombineArgs(K.ptr(b.part_acc), K.ptr(b.part_ml), K.ptr(L.sinks), c.n_heads, self.n_splits, c.head_dim,
                                    K.ptr(b.ao), K.ptr(b.aq), K.ptr(b.ads))
-            K._check(lib.b2_attn_decode(C.byref(aa), C.byref(ca), nb, c.head_dim, int(self.pdl), st()), "attn_decode")
-            self._n += 3
+            if self.fuse_attn_combine:      # the last CTA of every head group merges the splits: one launch instead of two
+                K._check(lib.b2_attn_decode_fused(C.byref(aa), C.byref(ca), C.c_void_p(K.ptr(b.attn_tickets)), nb, c.head_dim, int(self.pdl), st()),
+                         "attn_decode_fused")
+                self._n += 2
+            else:
+                K._check(lib.b2_attn_decode(C.byref(aa), C.byref(ca), nb, c.head_dim, int(self.pdl), st()), "attn_decode")
+                self._n += 3
             self._gemv_send(L.wo, nb, b.aq, b.ads, b.ao, self.cm_dec, c.d_model)
             self._norm_quant_reduce(L.ffn_norm, nb)
             if L.moe:      # expert parallel: local experts only; the weighted partial sum goes to every rank like a row-parallel GEMV

@@ -291,6 +291,10 @@ def test_engine_matches_reference_graph(tmp_path, spec, ft):
     a = eng.decode_argmax([1], [tok], [len(prompt) + 6])
     eng2 = eng.decode([1], [tok], [len(prompt) + 6])
     assert a[0] == int(eng2[0].argmax())
+    # the single-launch attention (last CTA of a head group merges the splits) gives the same logits
+    eng.fuse_attn_combine, eng.use_graphs = True, False
+    eng3 = eng.decode([1], [tok], [len(prompt) + 6])
+    assert torch.allclose(eng3, eng2, atol=1e-4 * eng2.abs().max().item() + 1e-5)
 
 
 @pytest.mark.parametrize("t", [GGMLType.Q4_K, GGMLType.Q6_K, GGMLType.Q8_0, GGMLType.BF16])
