@@ -78,6 +78,8 @@ def progress_line(ev: dict[str, Any], last: dict[str, Any]) -> None:
 def cmd_serve(args) -> int:
     import uvicorn
     from ..server.routes import create_app
+    from ..utils import logutil
+    logutil.setup()
     h = envconfig.host()
     print(f"ollama-b200 {VERSION} listening on {h.netloc}", file=sys.stderr)
     for k, (v, desc) in envconfig.as_map().items():

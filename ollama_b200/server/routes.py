@@ -69,6 +69,8 @@ class Server:
         from ..discover.devices import gpu_devices
         self.sched = sched or Scheduler(get_gpus_fn=gpu_devices)
         self.renderers: dict[str, PromptRenderer] = {}
+        from .request_log import RequestLogger
+        self.request_log = RequestLogger()
         self.app = self._build()
 
     # -- plumbing ---------------------------------------------------------------------------------------
@@ -117,6 +119,7 @@ class Server:
         body = await request.body()
         if not body:
             raise APIError(400, "missing request body")
+        self.request_log.record(request.url.path, body)
         try:
             d = json.loads(body)
         except ValueError as e:

@@ -84,3 +84,34 @@ def test_converted_checkpoint_matches_transformers(tmp_path, family):
         ref = model(ids[None]).logits[0, -1]
     got = be.prefill(0, ids.tolist(), 0)
     assert torch.allclose(got, ref, atol=2e-4, rtol=1e-3), (got - ref).abs().max()
+
+
+def test_create_from_checkpoint_directory_through_the_api(tmp_path, monkeypatch):
+    """POST /api/create with the files of a Hugging Face checkpoint: converted to GGUF, then served."""
+    transformers = pytest.importorskip("transformers")
+    import hashlib
+
+    from starlette.testclient import TestClient
+    monkeypatch.setenv("OLLAMA_MODELS", str(tmp_path / "store"))
+    monkeypatch.setenv("B200_DEVICE", "cpu")
+    monkeypatch.setenv("OLLAMA_CONTEXT_LENGTH", "128")
+    torch.manual_seed(0)
+    cfg = transformers.LlamaConfig(vocab_size=64, hidden_size=64, intermediate_size=96, num_hidden_layers=2, num_attention_heads=4,
+                                   num_key_value_heads=2, max_position_embeddings=128, tie_word_embeddings=False)
+    src = tmp_path / "hf"
+    transformers.LlamaForCausalLM(cfg).float().save_pretrained(src, safe_serialization=True)
+    _tiny_tokenizer(str(src))
+    from ollama_b200.server.routes import create_app
+    with TestClient(create_app()) as c:
+        files = {}
+        for n in sorted(os.listdir(src)):
+            data = open(src / n, "rb").read()
+            digest = "sha256:" + hashlib.sha256(data).hexdigest()
+            assert c.post(f"/api/blobs/{digest}", content=data).status_code in (200, 201)
+            files[n] = digest
+        r = c.post("/api/create", json={"model": "conv", "files": files, "template": "{{ .Prompt }}", "stream": False})
+        assert r.status_code == 200 and r.json()["status"] == "success", r.text
+        info = c.post("/api/show", json={"model": "conv"}).json()
+        assert info["details"]["family"] == "llama" and info["model_info"]["llama.block_count"] == 2
+        out = c.post("/api/generate", json={"model": "conv", "prompt": "abab", "stream": False, "options": {"num_predict": 4, "temperature": 0}}).json()
+        assert out["done"] and out["eval_count"] == 4
