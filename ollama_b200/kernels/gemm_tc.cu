@@ -44,14 +44,15 @@ struct GemmParams {
 
 template <int BN>
 struct Cfg {
-    static constexpr int STAGES = BN == 256 ? 4 : 6;
+    static constexpr int STAGES = BN == 256 ? 4 : (BN == 192 ? 5 : 6);
     static constexpr int A_BYTES = BM * BK * 2;
     static constexpr int B_BYTES = BN * BK * 2;
     static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
     static constexpr int EPI_LD = 36;                                   // padded row of the epilogue's 32 x 32 transpose tile (floats)
     static constexpr int EPI_BYTES = 4 * 32 * EPI_LD * 4;              // one tile per epilogue warp
     static constexpr int TOTAL = STAGES * STAGE_BYTES + EPI_BYTES + 1024 /*alignment slack*/ + 256 /*barriers*/;
-    static constexpr int TMEM_COLS = 2 * BN < 32 ? 32 : 2 * BN;
+    static constexpr int ACC_STRIDE = BN == 192 ? 256 : BN;            // column distance of the two accumulators
+    static constexpr int TMEM_COLS = 2 * ACC_STRIDE < 32 ? 32 : 2 * ACC_STRIDE;      // a power of two
 };
 
 __device__ __forceinline__ void tile_coords(int t, int tiles_m, int tiles_n, int& mt, int& nt) {
@@ -134,7 +135,7 @@ __global__ void __launch_bounds__(192, 1) gemm_bf16_tc_kernel(const __grid_const
                 const int buf = i & 1, use = i >> 1;
                 if (use >= 1 && !mbar_wait(&acc_empty[buf], (use - 1) & 1)) { ok = false; break; }
                 tc_fence_after();
-                const uint32_t acc = tmem_base + (uint32_t)(buf * BN);
+                const uint32_t acc = tmem_base + (uint32_t)(buf * L::ACC_STRIDE);
                 for (int kb = 0; kb < k_blocks; kb++, it++) {
                     const int s = it % STAGES;
                     if (!mbar_wait(&full[s], (it / STAGES) & 1)) { ok = false; break; }
@@ -171,7 +172,7 @@ __global__ void __launch_bounds__(192, 1) gemm_bf16_tc_kernel(const __grid_const
 #pragma unroll 1
             for (int c0 = 0; c0 < BN; c0 += 32) {
                 uint32_t v[32];
-                const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(buf * BN + c0);
+                const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(buf * L::ACC_STRIDE + c0);
                 tmem_ld32(taddr, v);
                 if (n0 + c0 >= p.n) continue;       // warp-uniform
 #pragma unroll
@@ -250,6 +251,8 @@ int dispatch(const void* a, const void* b, const GemmParams& p, cudaStream_t st)
     // wide tiles once they fill the machine; narrower ones keep more SMs busy on small problems
     const long tiles_m = (p.m + BM - 1) / BM;
     if (p.n >= 256 && tiles_m * ((p.n + 255) / 256) >= sm_count()) return launch<256>(a, b, p, st);
+    // one round either way: the widest tile that still gives every SM at most one tile
+    if (p.n >= 192 && tiles_m * ((p.n + 191) / 192) <= sm_count() && tiles_m * ((p.n + 127) / 128) > sm_count()) return launch<192>(a, b, p, st);
     if (p.n >= 128) return launch<128>(a, b, p, st);
     return launch<64>(a, b, p, st);
 }

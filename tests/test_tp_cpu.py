@@ -115,3 +115,44 @@ def test_followers_repeat_the_leaders_calls(tmp_path):
     for r in (1, 2):
         assert logs[r]["log"] == logs[0]["log"]
         assert logs[r]["flags"] == [False, True]
+
+
+def _pipe_follower(conn, rank, world, out_path):
+    from ollama_b200.parallel.control import TPControl, follow
+    from ollama_b200.parallel.transport import PipeTransport
+    log = []
+    tr = PipeTransport(rank, world, [conn])
+    assert tr.all_gather(f"h{rank}") == ["h0", "h1", "h2"]
+    tr.barrier()
+    follow(_FakeBackend(log), TPControl(rank, world, tr))
+    with open(out_path, "w") as f:
+        json.dump(log, f)
+
+
+def test_pipe_transport_carries_rendezvous_and_call_records(tmp_path):
+    """The server-side carrier: pipes from a leader to spawned followers (no torch.distributed in the leader)."""
+    from ollama_b200.parallel.control import TPControl, TPLeader
+    from ollama_b200.parallel.transport import PipeTransport
+    ctx = mp.get_context("spawn")
+    world, conns, procs = 3, [], []
+    for r in range(1, world):
+        parent, child = ctx.Pipe()
+        p = ctx.Process(target=_pipe_follower, args=(child, r, world, str(tmp_path / f"f{r}.json")))
+        p.start()
+        child.close()
+        conns.append(parent)
+        procs.append(p)
+    tr = PipeTransport(0, world, conns)
+    assert tr.all_gather("h0") == ["h0", "h1", "h2"]
+    tr.barrier()
+    log = []
+    lead = TPLeader(_FakeBackend(log), TPControl(0, world, tr))
+    lead.alloc(2, 128)
+    lead.prefill(0, list(range(70)), 0, True)
+    lead.decode_argmax([0, 1], [3, 4], [70, 9])
+    lead.close()
+    for p in procs:
+        p.join(timeout=60)
+        assert p.exitcode == 0
+    for r in (1, 2):
+        assert json.load(open(tmp_path / f"f{r}.json")) == log
