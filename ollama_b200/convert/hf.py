@@ -1,7 +1,8 @@
 """Hugging Face checkpoint directory (config.json + *.safetensors + tokenizer files) -> GGUF.
 
 Covers the decoder families this runtime executes: Llama / Mistral, Mixtral, Qwen2, Qwen3, Qwen3-MoE,
-Gemma, Gemma 2 and Gemma 3 (text tower).  Mirrors convert/convert.go:279-379 (dispatch by
+Gemma, Gemma 2 and Gemma 3 (text tower), gpt-oss (16-bit expert tensors; checkpoints that ship the experts as
+packed MXFP4 blocks + scales are not read).  Mirrors convert/convert.go:279-379 (dispatch by
 ``architectures[0]``), convert/convert_llama.go (key/value metadata, the Q/K row permutation that turns the
 checkpoint's half-split rotary layout into the interleaved one llama-arch GGUFs use:189-232),
 convert/convert_qwen3.go, convert_gemma*.go, convert_mixtral.go (expert stacking) and convert/tokenizer.go
@@ -32,7 +33,7 @@ class ConvertError(ValueError):
 ARCHS = {
     "LlamaForCausalLM": "llama", "MistralForCausalLM": "llama", "MixtralForCausalLM": "llama", "Qwen2ForCausalLM": "qwen2",
     "Qwen3ForCausalLM": "qwen3", "Qwen3MoeForCausalLM": "qwen3moe", "GemmaForCausalLM": "gemma", "Gemma2ForCausalLM": "gemma2",
-    "Gemma3ForCausalLM": "gemma3", "Gemma3ForConditionalGeneration": "gemma3",
+    "Gemma3ForCausalLM": "gemma3", "Gemma3ForConditionalGeneration": "gemma3", "GptOssForCausalLM": "gpt-oss",
 }
 
 # (pattern on the checkpoint name, GGUF name); {n} = layer index, {e} = expert index
@@ -59,6 +60,13 @@ _RULES: list[tuple[str, str]] = [
     (_LAYER + r"block_sparse_moe\.experts\.(\d+)\.w1\.weight", "blk.{n}.ffn_gate_exps.weight#{1}"),
     (_LAYER + r"block_sparse_moe\.experts\.(\d+)\.w3\.weight", "blk.{n}.ffn_up_exps.weight#{1}"),
     (_LAYER + r"block_sparse_moe\.experts\.(\d+)\.w2\.weight", "blk.{n}.ffn_down_exps.weight#{1}"),
+    # gpt-oss: stacked experts stored [expert, in, out] with gate / up interleaved along `out` (split and transposed in convert_tensors)
+    (_LAYER + r"self_attn\.sinks", "blk.{n}.attn_sinks.weight"),
+    (_LAYER + r"mlp\.router\.(weight|bias)", "blk.{n}.ffn_gate_inp.{1}"),
+    (_LAYER + r"mlp\.experts\.gate_up_proj", "blk.{n}.ffn_gate_up_exps.weight"),
+    (_LAYER + r"mlp\.experts\.gate_up_proj_bias", "blk.{n}.ffn_gate_up_exps.bias"),
+    (_LAYER + r"mlp\.experts\.down_proj", "blk.{n}.ffn_down_exps.weight@T"),
+    (_LAYER + r"mlp\.experts\.down_proj_bias", "blk.{n}.ffn_down_exps.bias"),
 ]
 # post_attention_layernorm is the FFN pre-norm for llama/qwen but a sandwich post-norm for gemma 2/3
 _RULES_PRENORM = [(_LAYER + r"post_attention_layernorm\.weight", "blk.{n}.ffn_norm.weight")]
@@ -102,20 +110,24 @@ def _kv(cfg: dict[str, Any], arch: str, name: str) -> dict[str, Any]:
         f"{arch}.block_count": c["num_hidden_layers"], f"{arch}.feed_forward_length": c.get("intermediate_size", 0),
         f"{arch}.attention.head_count": n_head, f"{arch}.attention.head_count_kv": c.get("num_key_value_heads", n_head),
         f"{arch}.attention.layer_norm_rms_epsilon": float(c.get("rms_norm_eps", 1e-6)),
-        f"{arch}.rope.freq_base": float(c.get("rope_theta", 10000.0)), f"{arch}.vocab_size": c.get("vocab_size", 0),
+        f"{arch}.rope.freq_base": float(c.get("rope_theta") or (c.get("rope_parameters") or {}).get("rope_theta") or 10000.0),
+        f"{arch}.vocab_size": c.get("vocab_size", 0),
     }
     if c.get("head_dim") or arch in ("qwen3", "qwen3moe", "gemma", "gemma2", "gemma3"):
         kv[f"{arch}.attention.key_length"] = hd
         kv[f"{arch}.attention.value_length"] = hd
     if arch == "llama":
         kv["llama.rope.dimension_count"] = hd
-    rs = c.get("rope_scaling") or {}
+    rs = c.get("rope_scaling") or c.get("rope_parameters") or {}      # newer configs keep theta and scaling in one `rope_parameters` table
     rtype = rs.get("rope_type") or rs.get("type")
     if rtype in ("linear", "yarn"):
         kv[f"{arch}.rope.scaling.type"] = rtype
         kv[f"{arch}.rope.scaling.factor"] = float(rs.get("factor", 1.0))
         if rs.get("original_max_position_embeddings"):
             kv[f"{arch}.rope.scaling.original_context_length"] = rs["original_max_position_embeddings"]
+        if rtype == "yarn":
+            kv[f"{arch}.rope.scaling.yarn_beta_fast"] = float(rs.get("beta_fast", 32.0))
+            kv[f"{arch}.rope.scaling.yarn_beta_slow"] = float(rs.get("beta_slow", 1.0))
     n_exp = c.get("num_local_experts") or c.get("num_experts") or 0
     if n_exp:
         kv[f"{arch}.expert_count"] = n_exp
@@ -124,7 +136,7 @@ def _kv(cfg: dict[str, Any], arch: str, name: str) -> dict[str, Any]:
             kv[f"{arch}.expert_feed_forward_length"] = c["moe_intermediate_size"]
         if "norm_topk_prob" in c:
             kv[f"{arch}.norm_top_k_prob"] = bool(c["norm_topk_prob"])
-    if c.get("sliding_window") and arch in ("gemma2", "gemma3", "llama"):
+    if c.get("sliding_window") and arch in ("gemma2", "gemma3", "llama", "gpt-oss"):
         kv[f"{arch}.attention.sliding_window"] = c["sliding_window"]
     if arch == "gemma2":
         kv["gemma2.attn_logit_softcapping"] = float(c.get("attn_logit_softcapping") or 50.0)
@@ -138,11 +150,11 @@ def _kv(cfg: dict[str, Any], arch: str, name: str) -> dict[str, Any]:
 
 def rope_freq_factors(cfg: dict[str, Any]) -> torch.Tensor | None:
     """llama3-style rope scaling is baked into a ``rope_freqs.weight`` tensor of per-frequency divisors."""
-    rs = cfg.get("rope_scaling") or {}
+    rs = cfg.get("rope_scaling") or cfg.get("rope_parameters") or {}
     if (rs.get("rope_type") or rs.get("type")) != "llama3":
         return None
     hd = cfg.get("head_dim") or cfg["hidden_size"] // cfg["num_attention_heads"]
-    base = float(cfg.get("rope_theta", 10000.0))
+    base = float(cfg.get("rope_theta") or rs.get("rope_theta") or 10000.0)
     factor, lo, hi = float(rs.get("factor", 8.0)), float(rs.get("low_freq_factor", 1.0)), float(rs.get("high_freq_factor", 4.0))
     orig = float(rs.get("original_max_position_embeddings", 8192))
     out = []
@@ -263,7 +275,7 @@ def tokenizer_kv(path: str, vocab_size: int) -> dict[str, Any]:
 # conversion
 # ---------------------------------------------------------------------------------------------------
 def _encode(t: torch.Tensor, name: str, outtype: str) -> tuple[GGMLType, torch.Tensor]:
-    if t.dim() < 2 or name.endswith(("_norm.weight", ".bias")) or "ffn_gate_inp" in name:
+    if t.dim() < 2 or name.endswith(("_norm.weight", ".bias")) or "ffn_gate_inp" in name or "attn_sinks" in name:
         return GGMLType.F32, quants.quantize(t.float(), GGMLType.F32)
     want = {"f32": GGMLType.F32, "f16": GGMLType.F16, "bf16": GGMLType.BF16}.get(outtype)
     if want is None:
@@ -303,7 +315,18 @@ def convert_tensors(src: ModelDir, cfg: dict[str, Any], arch: str, outtype: str 
     for out in sorted(names, key=_order):
         if out == "output.weight" and tied:
             continue
-        yield emit(out, src.tensor(names[out]))
+        t = src.tensor(names[out])
+        if out.endswith("@T"):                         # stored [expert, in, out]
+            yield emit(out[:-2], t.transpose(1, 2).contiguous())
+        elif ".ffn_gate_up_exps." in out:              # even columns gate, odd columns up
+            if out.endswith(".weight"):
+                yield emit(out.replace("gate_up", "gate"), t[..., 0::2].transpose(1, 2).contiguous())
+                yield emit(out.replace("gate_up", "up"), t[..., 1::2].transpose(1, 2).contiguous())
+            else:
+                yield emit(out.replace("gate_up", "gate"), t[..., 0::2].contiguous())
+                yield emit(out.replace("gate_up", "up"), t[..., 1::2].contiguous())
+        else:
+            yield emit(out, t)
     for base in sorted(experts, key=_order):
         idx = experts[base]
         if sorted(idx) != list(range(len(idx))):

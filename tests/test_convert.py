@@ -48,7 +48,7 @@ def _tiny_tokenizer(path):
         json.dump({"bos_token": "<s>", "eos_token": "</s>", "add_bos_token": True, "chat_template": "{{ messages }}"}, f)
 
 
-@pytest.mark.parametrize("family", ["llama", "qwen3", "qwen3moe"])
+@pytest.mark.parametrize("family", ["llama", "qwen3", "qwen3moe", "gpt-oss"])
 def test_converted_checkpoint_matches_transformers(tmp_path, family):
     transformers = pytest.importorskip("transformers")
     torch.manual_seed(0)
@@ -60,10 +60,21 @@ def test_converted_checkpoint_matches_transformers(tmp_path, family):
     elif family == "qwen3":
         cfg = transformers.Qwen3Config(head_dim=32, **common)
         model = transformers.Qwen3ForCausalLM(cfg)
-    else:
+    elif family == "qwen3moe":
         cfg = transformers.Qwen3MoeConfig(head_dim=16, num_experts=4, num_experts_per_tok=2, moe_intermediate_size=32, norm_topk_prob=True,
                                           decoder_sparse_step=1, mlp_only_layers=[], **common)
         model = transformers.Qwen3MoeForCausalLM(cfg)
+    else:       # gpt-oss: YaRN beyond the original context, sinks, alternating 8-token window, biased router, clamped SwiGLU
+        cfg = transformers.GptOssConfig(vocab_size=64, hidden_size=64, intermediate_size=32, num_hidden_layers=2, num_attention_heads=4,
+                                        num_key_value_heads=2, head_dim=16, num_local_experts=4, num_experts_per_tok=2, sliding_window=8,
+                                        max_position_embeddings=2048, rope_theta=150000.0, tie_word_embeddings=False,
+                                        rope_scaling={"rope_type": "yarn", "factor": 32.0, "beta_fast": 32.0, "beta_slow": 1.0,
+                                                      "truncate": False, "original_max_position_embeddings": 64})
+        model = transformers.GptOssForCausalLM(cfg)
+        with torch.no_grad():
+            for n, p in model.named_parameters():
+                if "bias" in n or "sinks" in n:
+                    p.normal_(0, 0.5)
     model = model.float().eval()
     src = tmp_path / "hf"
     model.save_pretrained(src, safe_serialization=True)
@@ -78,8 +89,8 @@ def test_converted_checkpoint_matches_transformers(tmp_path, family):
 
     from ollama_b200.engine.backend import TorchBackend, open_model
     be = TorchBackend(open_model(out), "cpu")
-    be.alloc(1, 64)
-    ids = torch.randint(0, 64, (11,), generator=torch.Generator().manual_seed(1))
+    be.alloc(1, 128)
+    ids = torch.randint(0, 64, (90 if family == "gpt-oss" else 11,), generator=torch.Generator().manual_seed(1))
     with torch.no_grad():
         ref = model(ids[None]).logits[0, -1]
     got = be.prefill(0, ids.tolist(), 0)
