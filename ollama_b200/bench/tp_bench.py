@@ -63,7 +63,7 @@ def prefill_exchanges(tp, L, T: int, dev: str, reps: int = 10) -> dict:
     t_local = timed(lambda: K.gemm_bf16(x, wb, None, out=local))
     peak, _ = peak_tflops()
     flops = 2.0 * T * c.d_model * L.wo.k
-    remote = (T - rows) * c.d_model * 4
+    remote = (T - rows) * c.d_model * 2          # partial rows travel as bf16
     target_rs = max(flops / (peak * 1e6), remote / 770e3)                     # us
     target_ag = rows * c.d_model * 2 * (N - 1) / 770e3
     t_rs = t_pair - t_ag

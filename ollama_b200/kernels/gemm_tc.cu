@@ -38,7 +38,7 @@ struct GemmParams {
     const float* bias;      // [n] or null
     int accumulate;         // out += result (fp32 output only)
     int out_bf16;
-    CommSend cm;            // cm.n_dst > 0: row r goes to cm.dst[r / rows_per_rank] at row r % rows_per_rank (fp32)
+    CommSend cm;            // cm.n_dst > 0: row r goes to cm.dst[r / rows_per_rank] at row r % rows_per_rank (bf16)
     int rows_per_rank;
 };
 
@@ -189,9 +189,10 @@ __global__ void __launch_bounds__(192, 1) gemm_bf16_tc_kernel(const __grid_const
                     if (row >= p.m || col >= p.n) continue;
                     float4 r = *(const float4*)(st + lr * L::EPI_LD + cq);
                     r.x += bias.x; r.y += bias.y; r.z += bias.z; r.w += bias.w;
-                    if (p.cm.n_dst > 0) {
+                    if (p.cm.n_dst > 0) {      // partial rows travel as bf16: half the NVLink bytes of fp32
                         const int owner = row / p.rows_per_rank;
-                        *(float4*)(p.cm.dst[owner] + (size_t)(row - owner * p.rows_per_rank) * p.ldo + col) = r;
+                        __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(p.cm.dst[owner]) + (size_t)(row - owner * p.rows_per_rank) * p.ldo + col;
+                        *(uint2*)dst = make_uint2(pack2_bf16(r.x, r.y), pack2_bf16(r.z, r.w));
                     } else if (p.out_bf16) {
                         *(uint2*)((__nv_bfloat16*)p.out + (size_t)row * p.ldo + col) = make_uint2(pack2_bf16(r.x, r.y), pack2_bf16(r.z, r.w));
                     } else {
@@ -279,8 +280,8 @@ B2_API int b2_gemm_bf16_out16(const void* a, const void* b, int m, int n, int k,
     return dispatch(a, b, p, st);
 }
 
-// Row-parallel GEMM of a tensor-parallel group: row r of the fp32 partial result is stored into cm->dst[r / rows_per_rank]
-// (a peer address; row index relative to the owner's first row, pitch ldo) and the exchange is announced on cm's channel.
+// Row-parallel GEMM of a tensor-parallel group: row r of the partial result is stored, as bf16, into cm->dst[r / rows_per_rank]
+// (a peer address; row index relative to the owner's first row, pitch ldo elements) and the exchange is announced on cm's channel.
 B2_API int b2_gemm_bf16_scatter(const void* a, const void* b, int m, int n, int k, int ldo, const float* bias, const CommSend* cm,
                                 int rows_per_rank, cudaStream_t st) {
     if (bad_operands(a, b, m, n, k, ldo) || !cm || rows_per_rank < 1 || cm->n_dst < 1 || cm->n_dst > COMM_MAX_RANKS ||

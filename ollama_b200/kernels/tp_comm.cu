@@ -3,7 +3,7 @@
 //
 // Prefill keeps the residual stream sharded by token rows: rank r owns rows [r * rows_per_rank, ...).  A
 // row-parallel GEMM (attention output / FFN down) writes each partial output tile straight into the parts
-// buffer of the rank that owns those rows (kernels/gemm_q_tc.cu, scatter epilogue).  The kernel below then
+// buffer of the rank that owns those rows, as bf16 (kernels/gemm_tc.cu, scatter epilogue).  The kernel below then
 // sums the partial rows into its shard of the residual stream, normalises, converts to bf16 and stores the
 // row into the activation buffer of EVERY rank (peer stores), which is the operand of the next
 // column-parallel GEMM.  One kernel therefore plays the parts of reduce-scatter's reduction, the residual add,
@@ -97,7 +97,7 @@ B2_API int b2_comm_status(const CommChan* ch, int* status, cudaStream_t st) {
 // ---------------------------------------------------------------------------------------------
 struct TpNormGatherArgs {
     float* x;                 // [rows][k] this rank's shard of the residual stream (updated in place)
-    const float* parts;       // [n_part][part_rows][k] partial rows received from the group (n_part = 0: nothing to add)
+    const __nv_bfloat16* parts;   // [n_part][part_rows][k] partial rows (bf16) received from the group (n_part = 0: nothing to add)
     int n_part;
     long long part_stride;    // elements between the slabs of two ranks
     CommChan* rs_chan;        // channel the partial rows were announced on
@@ -129,13 +129,15 @@ __global__ void __launch_bounds__(256) tp_norm_gather_kernel(const __grid_consta
         }
         if (a.n_part) {
             for (int r = 0; r < a.n_part; r++) {
-                const float* p = a.parts + r * a.part_stride + (size_t)b * a.k;
+                const __nv_bfloat16* p = a.parts + r * a.part_stride + (size_t)b * a.k;
 #pragma unroll
                 for (int j = 0; j < MAXJ; j++) {
                     const int c = tid + 256 * j;
                     if (c < nchunk) {
-                        const float4 t = __ldcg((const float4*)(p + 4 * c));
-                        v[j].x += t.x; v[j].y += t.y; v[j].z += t.z; v[j].w += t.w;
+                        const uint2 t = __ldcg((const uint2*)(p + 4 * c));        // written by a peer: read through L2
+                        const float2 lo = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&t.x));
+                        const float2 hi = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&t.y));
+                        v[j].x += lo.x; v[j].y += lo.y; v[j].z += hi.x; v[j].w += hi.y;
                     }
                 }
             }
@@ -195,9 +197,16 @@ __global__ void __launch_bounds__(256) tp_scatter_rows_kernel(const float* src, 
     const int nchunk = k >> 2;
     for (int row = blockIdx.x; row < m; row += gridDim.x) {
         const int owner = row / rows_per_rank, lrow = row - owner * rows_per_rank;
-        float* dst = cm.dst[owner] + (size_t)lrow * k;
+        __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(cm.dst[owner]) + (size_t)lrow * k;
         const float* s = src + (size_t)row * k;
-        for (int c = threadIdx.x; c < nchunk; c += 256) *(float4*)(dst + 4 * c) = *(const float4*)(s + 4 * c);
+        for (int c = threadIdx.x; c < nchunk; c += 256) {
+            const float4 v = *(const float4*)(s + 4 * c);
+            const __nv_bfloat162 lo = __floats2bfloat162_rn(v.x, v.y), hi = __floats2bfloat162_rn(v.z, v.w);
+            uint2 pk;
+            pk.x = *reinterpret_cast<const uint32_t*>(&lo);
+            pk.y = *reinterpret_cast<const uint32_t*>(&hi);
+            *(uint2*)(dst + 4 * c) = pk;
+        }
     }
     comm_publish(cm, gridDim.x, ep);
 }

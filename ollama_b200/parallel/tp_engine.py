@@ -138,7 +138,7 @@ class TPBackend(B200Backend):
         self.rpr_max = (self.max_chunk + N - 1) // N
         self.b_dec = lay.add("dec_parts", 2 * N * MB * c.d_model * 8)          # (value, epoch) pairs, two halves
         self.b_logits = lay.add("logits", MB * c.vocab_size * 4)
-        self.b_parts = lay.add("pre_parts", N * self.rpr_max * c.d_model * 4)
+        self.b_parts = lay.add("pre_parts", N * self.rpr_max * c.d_model * 2)       # bf16 partial rows
         self.b_h = lay.add("h_full", self.max_chunk * c.d_model * 2)
         self.region = reg = PeerRegion(lay.size, self.rank, N, self.device, self.group)
         b = self.buf
@@ -152,7 +152,7 @@ class TPBackend(B200Backend):
         # logits: this rank's vocabulary rows are columns [v_lo, v_lo + n) of every rank's logits buffer
         self.cm_logits = reg.send(CH_LOGITS, [reg.addr(self.b_logits, r, self.v_lo * 4) for r in range(N)])
         self.cm_ag = reg.send(CH_AG, [reg.addr(self.b_h, r) for r in range(N)])
-        pslab = self.rpr_max * c.d_model * 4
+        pslab = self.rpr_max * c.d_model * 2
         self.cm_rs = reg.send(CH_RS, [reg.addr(self.b_parts, r, self.rank * pslab) for r in range(N)])
 
     def close(self) -> None:
