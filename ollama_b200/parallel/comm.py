@@ -121,6 +121,11 @@ class PeerRegion:
         """0 = ok, 1 = a wait on this channel ran out on this rank (synchronises the current stream)."""
         return int(tensor_at(self.chan(chan_idx) + _OFF_STATUS, (1,), torch.int32, self.device).item())
 
+    def failed_channels(self) -> list[int]:
+        """Channels whose waits ran out on this rank since the last clear (one device read of the channel block)."""
+        words = tensor_at(self.chan(0), (N_CHANNELS, CHAN_BYTES // 4), torch.int32, self.device)[:, _OFF_STATUS // 4].tolist()
+        return [i for i, w in enumerate(words) if w != 0]
+
     def clear_status(self, chan_idx: int) -> None:
         tensor_at(self.chan(chan_idx) + _OFF_STATUS, (1,), torch.int32, self.device).zero_()
 

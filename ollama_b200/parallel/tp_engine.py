@@ -164,6 +164,30 @@ class TPBackend(B200Backend):
     def comm_status(self) -> int:
         return max(self.region.status(ch) for ch in (CH_DEC, CH_LOGITS, CH_RS, CH_AG, CH_BAR))
 
+    def check_exchanges(self) -> None:
+        """Raise if a bounded wait of an exchange ran out on this rank (a peer is late, gone or out of step).
+
+        The kernels that waited contributed zeros and returned, so the step's result is unusable; the status words are
+        cleared so that the group can be torn down or retried by the caller.
+        """
+        bad = self.region.failed_channels()
+        if bad:
+            for ch in bad:
+                self.region.clear_status(ch)
+            names = {CH_DEC: "decode all-reduce", CH_LOGITS: "logits gather", CH_RS: "prefill reduce-scatter", CH_AG: "prefill all-gather",
+                     CH_BAR: "chunk barrier"}
+            raise RuntimeError("tensor-parallel exchange timed out on rank %d: %s" % (self.rank, ", ".join(names.get(c, str(c)) for c in bad)))
+
+    def decode_argmax(self, slots, tokens, positions):
+        out = super().decode_argmax(slots, tokens, positions)
+        self.check_exchanges()
+        return out
+
+    def decode(self, slots, tokens, positions):
+        out = super().decode(slots, tokens, positions)
+        self.check_exchanges()
+        return out
+
     # -- decode ---------------------------------------------------------------------------------------
     def _norm_quant_reduce(self, w, nb):
         """x += sum of the partial rows of the last exchange; then RMSNorm + int8 quantisation of x."""
@@ -326,7 +350,9 @@ class TPBackend(B200Backend):
         self._gemv_send(self.head, 1, b.xq, b.xds, b.xf, self.cm_logits, c.vocab_size)
         self.region.wait(CH_LOGITS)
         self.kernel_launches += 3
-        return R.softcap(b.logits[0].clone(), c.final_softcap)
+        out = R.softcap(b.logits[0].clone(), c.final_softcap)
+        self.check_exchanges()
+        return out
 
     @torch.no_grad()
     def hidden(self, slot: int, tokens: Sequence[int]) -> torch.Tensor:

@@ -71,3 +71,18 @@ class PipeTransport:
         if not isinstance(got, list) or len(got) != n:
             raise RuntimeError("tensor-parallel control channel out of step")
         return got
+
+
+class LocalTransport:
+    """A group of one: nothing to exchange (single-GPU use of the peer-region plumbing, tests of the bounded waits)."""
+
+    rank, world = 0, 1
+
+    def all_gather(self, obj: Any) -> list[Any]:
+        return [obj]
+
+    def barrier(self) -> None:
+        pass
+
+    def bcast_ints(self, ints: list[int] | None, n: int) -> list[int]:
+        return list(ints or [])

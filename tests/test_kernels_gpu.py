@@ -374,3 +374,59 @@ def test_gemm_q_dequant_fused(t, m, n, k):
     assert out[:, :4].abs().max() == 0 and out[:, 4 + n:].abs().max() == 0      # neighbours of the output window stay untouched
     K.gemm_q(x, dw, out=out, accumulate=True, out_off=4)
     assert torch.allclose(out[:, 4:4 + n].cpu(), 2 * ref, atol=2 * tol, rtol=2e-3)
+
+
+def test_bounded_waits_report_a_missing_rank():
+    """Failure detection on the device without a fault: a wait for a rank that never writes gives up after the channel's
+    time limit, records a status that the host reads, and leaves the context usable."""
+    import ctypes as C
+    import time
+
+    from ollama_b200.parallel.comm import CHAN_BYTES, Layout, PeerRegion
+    from ollama_b200.parallel.transport import LocalTransport
+    K = _K()
+    lay = Layout()
+    k = 512
+    blk = lay.add("parts", 2 * 2 * 8 * k * 8)                 # two halves x two ranks x eight rows of (value, epoch) pairs
+    reg = PeerRegion(lay.size, 0, 1, "cuda", LocalTransport())
+    try:
+        for ch in (0, 1):
+            reg.set_wait_ms(ch, 200)
+        # 1. flag wait: two ranks expected at epoch 5; rank 0 has announced it, nobody ever raises flag 1
+        from ollama_b200.parallel.comm import tensor_at
+        tensor_at(reg.chan(1) + 4, (1,), torch.int32, reg.device).fill_(5)          # this rank's epoch
+        tensor_at(reg.chan(1) + 32, (1,), torch.int32, reg.device).fill_(5)         # flag[0]
+        torch.cuda.synchronize()
+        t0 = time.time()
+        reg.world = 2
+        reg.wait(1)
+        torch.cuda.synchronize()
+        reg.world = 1
+        assert 0.15 < time.time() - t0 < 5.0
+        assert reg.failed_channels() == [1] and reg.status(1) == 1
+        reg.clear_status(1)
+        assert reg.failed_channels() == []
+        # 2. low-latency reduce: rank 0's partial row is there (epoch 1), rank 1's never arrives
+        parts = reg.tensor(blk, (2, 2, 8, k, 2), torch.int32)
+        parts.zero_()
+        vals = torch.randn(k, device="cuda")
+        half = 1                                               # epoch 1 uses the odd half
+        parts[half, 0, 0, :, 0] = vals.view(torch.int32)
+        parts[half, 0, 0, :, 1] = 1
+        x = torch.ones(1, k, device="cuda")
+        xq = torch.empty(1, k, dtype=torch.int8, device="cuda")
+        xds = torch.empty(1, k // 32, 2, device="cuda")
+        xf = torch.empty(1, k, device="cuda")
+        a = K.NormQuantArgs(K.ptr(x), None, 1e-5, k, 0, K.ptr(xq), K.ptr(xds), K.ptr(xf), None)
+        a.parts, a.n_part, a.part_stride, a.parity_stride, a.chan = reg.addr(blk), 2, 8 * k, 2 * 8 * k, reg.chan(0)
+        t0 = time.time()
+        K._check(K.lib().b2_rmsnorm_quant(C.byref(a), 1, 0, K.stream()), "rmsnorm_quant")
+        torch.cuda.synchronize()
+        assert 0.15 < time.time() - t0 < 5.0
+        assert reg.failed_channels() == [0]
+        assert torch.allclose(x[0], 1.0 + vals, atol=1e-6)     # the rank that did arrive was added; the missing one contributed zeros
+        # the context is intact: an ordinary kernel still runs
+        assert float(K.rmsnorm_quant(torch.ones(1, 64, device="cuda"), None, 1e-5).f.sum()) == pytest.approx(64.0, rel=1e-4)
+    finally:
+        reg.clear_status(0)
+        reg.close()
