@@ -48,12 +48,16 @@ class B200Backend:
     name = "b200"
 
     def __init__(self, g: GGUFFile | None, device: str = "cuda", opts=None, cfg: ModelConfig | None = None,
-                 tensors: dict[str, QWeight] | None = None, keep_bf16: bool | None = None, prefill_gemm: str = "bf16"):
+                 tensors: dict[str, QWeight] | None = None, keep_bf16: bool | None = None, prefill_gemm: str = "bf16",
+                 kv_type: str | None = None):
         """Load from an opened GGUF, or from ``cfg`` + an iterable source of :class:`QWeight` (synthetic checkpoints).
 
         ``keep_bf16``: keep a resident 16-bit copy of every matrix for prefill (None: when it fits in 40% of the free HBM;
         otherwise each matrix is expanded into scratch right before its GEMM).  ``prefill_gemm``: "bf16" (expand, then the
         bf16 tensor-core GEMM) or "fused" (weights expanded inside the GEMM kernel; no 16-bit copy anywhere).
+        ``kv_type``: "f16" or "q8_0" (int8 values with one f16 scale per 32 dims, written by the rope kernel and expanded
+        inside the attention kernels; "q4_0" is served as q8_0); default: ``opts.kv_cache_type``
+        (envconfig/config.go:183 OLLAMA_KV_CACHE_TYPE).
         """
         self.device = torch.device(device if device != "cuda" else f"cuda:{torch.cuda.current_device()}")
         self.cfg = cfg if cfg is not None else config_from_gguf(g)
@@ -61,6 +65,12 @@ class B200Backend:
             raise NotImplementedError(f"{self.cfg.arch} is not supported by the sm_100a engine")
         K.lib()
         self.prefill_gemm = prefill_gemm
+        kv_type = (kv_type or getattr(opts, "kv_cache_type", None) or "f16").lower()
+        if kv_type not in ("f16", "q8_0", "q4_0"):
+            raise ValueError(f"unknown K/V cache type {kv_type!r}")
+        # quantised blocks cover 32 dims; head sizes outside the flash-attention kernel read the cache through torch
+        self.kv_q8 = kv_type != "f16" and self.cfg.head_dim % 32 == 0 and self.cfg.head_dim in K.ATTN_PREFILL_HEAD_DIMS
+        self.kv_type = "q8_0" if self.kv_q8 else "f16"
         if keep_bf16 is None:
             c = self.cfg
             est = 2 * (c.n_layers * (c.d_model * (2 * c.q_dim + 2 * c.kv_dim) + 3 * c.d_model * c.d_ff) + c.vocab_size * c.d_model)
@@ -166,14 +176,21 @@ class B200Backend:
         return sum(w.nbytes for w in ws)
 
     def kv_bytes(self) -> int:
-        return sum(t.numel() * 2 for t in getattr(self, "k_cache", [])) * 2
+        n = sum(t.numel() * t.element_size() for t in getattr(self, "k_cache", [])) * 2
+        return n + sum(t.numel() * 2 for t in getattr(self, "k_scale", []) if t is not None) * 2
 
     # -- buffers --------------------------------------------------------------------------------------
     def alloc(self, n_slots: int, n_ctx: int) -> None:
         c, dev = self.cfg, self.device
         self.n_slots, self.n_ctx = n_slots, n_ctx
-        self.k_cache = [torch.zeros(n_slots, c.n_kv_heads, n_ctx, c.head_dim, device=dev, dtype=torch.float16) for _ in range(c.n_layers)]
-        self.v_cache = [torch.zeros(n_slots, c.n_kv_heads, n_ctx, c.head_dim, device=dev, dtype=torch.float16) for _ in range(c.n_layers)]
+        kv_dt = torch.int8 if self.kv_q8 else torch.float16
+        self.k_cache = [torch.zeros(n_slots, c.n_kv_heads, n_ctx, c.head_dim, device=dev, dtype=kv_dt) for _ in range(c.n_layers)]
+        self.v_cache = [torch.zeros(n_slots, c.n_kv_heads, n_ctx, c.head_dim, device=dev, dtype=kv_dt) for _ in range(c.n_layers)]
+        self.k_scale = self.v_scale = [None] * c.n_layers
+        if self.kv_q8:
+            def sc():
+                return [torch.zeros(n_slots, c.n_kv_heads, n_ctx, c.head_dim // 32, device=dev, dtype=torch.float16) for _ in range(c.n_layers)]
+            self.k_scale, self.v_scale = sc(), sc()
         MB = MAX_DECODE_BATCH
         f32, i8, i32 = torch.float32, torch.int8, torch.int32
         qkv_dim = (c.n_heads + 2 * c.n_kv_heads) * c.head_dim
@@ -216,7 +233,7 @@ class B200Backend:
 
     def close(self) -> None:
         self._graphs.clear()
-        self.k_cache = self.v_cache = []
+        self.k_cache = self.v_cache = self.k_scale = self.v_scale = []
         self.buf = None
 
     # -- decode ---------------------------------------------------------------------------------------
@@ -323,11 +340,12 @@ class B200Backend:
             ra = K.RopeKvArgs(K.ptr(b.qkv), K.ptr(b.positions), K.ptr(b.slots), K.ptr(self.inv_freq_local if local else self.inv_freq),
                               K.ptr(L.q_norm), K.ptr(L.k_norm), c.norm_eps, 1.0 if local else self.mscale, c.n_heads, c.n_kv_heads,
                               c.head_dim, c.rope_dim, int(c.rope_style == "neox"), self.n_ctx, K.ptr(b.q), K.ptr(self.k_cache[i]),
-                              K.ptr(self.v_cache[i]))
+                              K.ptr(self.v_cache[i]), K.ptr(self.k_scale[i]), K.ptr(self.v_scale[i]))
             K._check(lib.b2_rope_kv(C.byref(ra), nb, int(self.pdl), st()), "rope_kv")
             aa = K.AttnDecodeArgs(K.ptr(b.q), K.ptr(self.k_cache[i]), K.ptr(self.v_cache[i]), K.ptr(b.positions), K.ptr(b.slots),
                                   c.n_heads, c.n_kv_heads, self.n_ctx, self.n_splits, self.attn_scale, c.attn_softcap,
-                                  c.sliding_window if L.swa else 0, K.ptr(b.part_acc), K.ptr(b.part_ml))
+                                  c.sliding_window if L.swa else 0, K.ptr(b.part_acc), K.ptr(b.part_ml), K.ptr(self.k_scale[i]),
+                                  K.ptr(self.v_scale[i]))
             ca = K.AttnCombineArgs(K.ptr(b.part_acc), K.ptr(b.part_ml), K.ptr(L.sinks), c.n_heads, self.n_splits, c.head_dim,
                                    K.ptr(b.ao), K.ptr(b.aq), K.ptr(b.ads))
             if self.fuse_attn_combine:      # the last CTA of every head group merges the splits: one launch instead of two
@@ -483,7 +501,7 @@ class B200Backend:
         if c.head_dim in K.ATTN_PREFILL_HEAD_DIMS:
             self.kernel_launches += 1
             return K.attn_prefill(q, self.k_cache[i], self.v_cache[i], slot, pos0, p_end, self.attn_scale, c.causal, window,
-                                  c.attn_softcap, L.sinks)
+                                  c.attn_softcap, L.sinks, k_scale=self.k_scale[i], v_scale=self.v_scale[i])
         # head sizes without a flash-attention instantiation (32, 256): plain torch attention over the same cache rows
         kk = self.k_cache[i][slot, :, :p_end].transpose(0, 1)        # [S, Hkv, hd] f16
         vv = self.v_cache[i][slot, :, :p_end].transpose(0, 1)
@@ -515,7 +533,8 @@ class B200Backend:
             local = L.swa and c.rope_base_local > 0
             q = K.rope_kv(qkv, pos, slots, self.inv_freq_local if local else self.inv_freq, n_heads=c.n_heads, n_kv_heads=c.n_kv_heads,
                           hd=c.head_dim, n_rot=c.rope_dim, neox=c.rope_style == "neox", mscale=1.0 if local else self.mscale,
-                          k_cache=self.k_cache[i], v_cache=self.v_cache[i], q_norm=L.q_norm, k_norm=L.k_norm, eps=c.norm_eps)
+                          k_cache=self.k_cache[i], v_cache=self.v_cache[i], q_norm=L.q_norm, k_norm=L.k_norm, eps=c.norm_eps,
+                          k_scale=self.k_scale[i], v_scale=self.v_scale[i])
             o = self._attn_prefill(q, i, L, slot, pos0, p_end)
             if c.sandwich_norm:
                 x = x + R.rmsnorm(self._mm(o, L.wo), L.post_attn_norm, c.norm_eps)

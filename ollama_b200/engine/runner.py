@@ -114,7 +114,8 @@ class Runner:
         if backend is None and self._tp_devices():
             # the model is split over several GPUs: this process leads, one spawned follower per further GPU repeats its calls
             from ..parallel.launcher import TPGroup
-            self._tp_group = TPGroup(model_path, self._tp_devices(), max_chunk=max(512, min(int(self.opts.num_batch), 2048)))
+            self._tp_group = TPGroup(model_path, self._tp_devices(), max_chunk=max(512, min(int(self.opts.num_batch), 2048)),
+                                    kv_type=self.opts.kv_cache_type or "f16")
             backend = self._tp_group.backend
         self.backend = backend if backend is not None else make_backend(self.gguf, self.opts.device, opts=self.opts)
         self.cfg = self.backend.cfg

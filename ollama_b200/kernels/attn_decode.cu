@@ -23,6 +23,8 @@ struct AttnDecodeArgs {
     int window;              // 0 = full
     float* part_acc;         // scratch [nb][H][splits][HD]
     float2* part_ml;         // scratch [nb][H][splits] (max, sum)
+    const __half* k_scale;   // q8_0 cache (k_cache / v_cache hold int8): [slots][Hkv][n_ctx][HD/32] scales, or null for f16
+    const __half* v_scale;
 };
 
 template <int HD, int G>
@@ -68,12 +70,23 @@ __device__ __forceinline__ void attn_decode_body(const AttnDecodeArgs& a) {
         const int p = pb + pg;
         const bool valid = p < p1;
         const int pc = valid ? p : p1 - 1;
-        const __half* kp = a.k_cache + (base + pc) * HD + sub * 16;
-        const __half* vp = a.v_cache + (base + pc) * HD + sub * 16;
-        const uint4 k0 = *(const uint4*)kp, k1 = *(const uint4*)(kp + 8);
-        const uint4 v0 = *(const uint4*)vp, v1 = *(const uint4*)(vp + 8);
         float kf[16], vf[16];
-        {
+        if (a.k_scale) {      // q8_0 cache: 16 int8 per lane and the scale of their block of 32
+            const uint4 kq = *(const uint4*)(reinterpret_cast<const int8_t*>(a.k_cache) + (base + pc) * HD + sub * 16);
+            const uint4 vq = *(const uint4*)(reinterpret_cast<const int8_t*>(a.v_cache) + (base + pc) * HD + sub * 16);
+            const float dk = __half2float(a.k_scale[(base + pc) * (HD / 32) + (sub >> 1)]);
+            const float dv = __half2float(a.v_scale[(base + pc) * (HD / 32) + (sub >> 1)]);
+            const uint32_t kw[4] = {kq.x, kq.y, kq.z, kq.w}, vw[4] = {vq.x, vq.y, vq.z, vq.w};
+#pragma unroll
+            for (int i = 0; i < 16; i++) {
+                kf[i] = dk * (float)(int8_t)((kw[i >> 2] >> (8 * (i & 3))) & 0xff);
+                vf[i] = dv * (float)(int8_t)((vw[i >> 2] >> (8 * (i & 3))) & 0xff);
+            }
+        } else {
+            const __half* kp = a.k_cache + (base + pc) * HD + sub * 16;
+            const __half* vp = a.v_cache + (base + pc) * HD + sub * 16;
+            const uint4 k0 = *(const uint4*)kp, k1 = *(const uint4*)(kp + 8);
+            const uint4 v0 = *(const uint4*)vp, v1 = *(const uint4*)(vp + 8);
             const __half2* h = reinterpret_cast<const __half2*>(&k0);
             const __half2* h2 = reinterpret_cast<const __half2*>(&k1);
             const __half2* w = reinterpret_cast<const __half2*>(&v0);

@@ -29,6 +29,8 @@ struct AttnPrefillArgs {
     int causal;
     int window;              // 0 = none; key k is visible to query p when p - k < window
     float scale, softcap;
+    const __half* k_scale;   // q8_0 cache (k_cache / v_cache hold int8): [slots][Hkv][n_ctx][D/32] scales, or null for f16
+    const __half* v_scale;
 };
 
 namespace {
@@ -78,6 +80,32 @@ __global__ void __launch_bounds__(128) attn_prefill_kernel(const __grid_constant
         const int n0 = k_begin + tile * BN;
         __half* dk = sK + stage * BN * LD;
         __half* dv = sV + stage * BN * LD;
+        if (a.k_scale) {      // q8_0 cache: plain loads, expanded to f16 on the way into shared memory (16 dims per thread and trip)
+            const int8_t* kq = reinterpret_cast<const int8_t*>(a.k_cache) + ((size_t)a.slot * a.Hkv + hkv) * a.n_ctx * D;
+            const int8_t* vq = reinterpret_cast<const int8_t*>(a.v_cache) + ((size_t)a.slot * a.Hkv + hkv) * a.n_ctx * D;
+            const __half* ks = a.k_scale + ((size_t)a.slot * a.Hkv + hkv) * a.n_ctx * (D / 32);
+            const __half* vs = a.v_scale + ((size_t)a.slot * a.Hkv + hkv) * a.n_ctx * (D / 32);
+            for (int c = tid; c < BN * (D / 16); c += 128) {
+                const int r = c / (D / 16), col = (c % (D / 16)) * 16;
+                const int pos = min(n0 + r, a.n_ctx - 1);
+                const uint4 k4 = *(const uint4*)(kq + (size_t)pos * D + col), v4 = *(const uint4*)(vq + (size_t)pos * D + col);
+                const float dkf = __half2float(ks[(size_t)pos * (D / 32) + (col >> 5)]), dvf = __half2float(vs[(size_t)pos * (D / 32) + (col >> 5)]);
+                const uint32_t kw[4] = {k4.x, k4.y, k4.z, k4.w}, vw[4] = {v4.x, v4.y, v4.z, v4.w};
+                uint32_t ko[8], vo[8];
+#pragma unroll
+                for (int i = 0; i < 8; i++) {
+                    const uint32_t kb = kw[i >> 1] >> (16 * (i & 1)), vb = vw[i >> 1] >> (16 * (i & 1));
+                    ko[i] = pack_half2(dkf * (float)(int8_t)(kb & 0xff), dkf * (float)(int8_t)((kb >> 8) & 0xff));
+                    vo[i] = pack_half2(dvf * (float)(int8_t)(vb & 0xff), dvf * (float)(int8_t)((vb >> 8) & 0xff));
+                }
+                *(uint4*)(dk + r * LD + col) = make_uint4(ko[0], ko[1], ko[2], ko[3]);
+                *(uint4*)(dk + r * LD + col + 8) = make_uint4(ko[4], ko[5], ko[6], ko[7]);
+                *(uint4*)(dv + r * LD + col) = make_uint4(vo[0], vo[1], vo[2], vo[3]);
+                *(uint4*)(dv + r * LD + col + 8) = make_uint4(vo[4], vo[5], vo[6], vo[7]);
+            }
+            asm volatile("cp.async.commit_group;" ::: "memory");      // keeps the group counting of the f16 path
+            return;
+        }
         for (int c = tid; c < BN * (D / 8); c += 128) {
             const int r = c / (D / 8), col = (c % (D / 8)) * 8;
             const int pos = min(n0 + r, a.n_ctx - 1);           // rows past the cache repeat its last row (masked below)

@@ -157,8 +157,10 @@ struct RopeKvArgs {
     float eps, mscale;
     int n_heads, n_kv_heads, hd, n_rot, neox, n_ctx;
     float* q_out;            // [nt][H][hd]
-    __half* k_cache;         // [slots][Hkv][n_ctx][hd]
+    __half* k_cache;         // [slots][Hkv][n_ctx][hd]  (int8 when the scale arrays are given)
     __half* v_cache;
+    __half* k_scale;         // q8_0 cache: [slots][Hkv][n_ctx][hd/32] one f16 scale per 32 dims, or null for an f16 cache
+    __half* v_scale;
 };
 
 __global__ void __launch_bounds__(128) rope_kv_kernel(const __grid_constant__ RopeKvArgs a) {
@@ -203,13 +205,29 @@ __global__ void __launch_bounds__(128) rope_kv_kernel(const __grid_constant__ Ro
         for (int i = tid; i < hd; i += 128) dst[i] = sh[i];
     } else {
         const int kvh = is_k ? head - H : head - H - Hkv;
-        __half* dst = (is_k ? a.k_cache : a.v_cache) + (((size_t)slot * Hkv + kvh) * a.n_ctx + pos) * hd;
-        for (int i = tid; i < hd; i += 128) dst[i] = __float2half_rn(sh[i]);
+        const size_t rowi = ((size_t)slot * Hkv + kvh) * a.n_ctx + pos;
+        __half* sc = is_k ? a.k_scale : a.v_scale;
+        if (sc) {      // q8_0: a warp covers one block of 32 dims per trip (hd is a multiple of 32)
+            int8_t* dst = reinterpret_cast<int8_t*>(is_k ? a.k_cache : a.v_cache) + rowi * hd;
+            for (int i0 = 0; i0 < hd; i0 += 128) {
+                const int i = i0 + tid;
+                const float v = i < hd ? sh[i] : 0.f;
+                const __half dh = __float2half_rn(warp_max(fabsf(v)) / 127.f);
+                const float d = __half2float(dh);
+                if (i < hd) {
+                    dst[i] = (int8_t)(d > 0.f ? max(-127, min(127, __float2int_rn(v / d))) : 0);
+                    if ((tid & 31) == 0) sc[rowi * (hd >> 5) + (i >> 5)] = dh;
+                }
+            }
+        } else {
+            __half* dst = (is_k ? a.k_cache : a.v_cache) + rowi * hd;
+            for (int i = tid; i < hd; i += 128) dst[i] = __float2half_rn(sh[i]);
+        }
     }
 }
 
 B2_API int b2_rope_kv(const RopeKvArgs* a, int nt, int pdl, cudaStream_t st) {
-    if (a->hd > 512) return (int)cudaErrorInvalidValue;
+    if (a->hd > 512 || ((a->k_scale || a->v_scale) && ((a->hd & 31) || !a->k_scale || !a->v_scale))) return (int)cudaErrorInvalidValue;
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(nt, a->n_heads + 2 * a->n_kv_heads);
     cfg.blockDim = dim3(128);

@@ -100,7 +100,8 @@ class RopeKvArgs(C.Structure):
     _fields_ = [("qkv", C.c_void_p), ("positions", C.c_void_p), ("slots", C.c_void_p), ("inv_freq", C.c_void_p),
                 ("q_norm", C.c_void_p), ("k_norm", C.c_void_p), ("eps", C.c_float), ("mscale", C.c_float),
                 ("n_heads", C.c_int), ("n_kv_heads", C.c_int), ("hd", C.c_int), ("n_rot", C.c_int), ("neox", C.c_int),
-                ("n_ctx", C.c_int), ("q_out", C.c_void_p), ("k_cache", C.c_void_p), ("v_cache", C.c_void_p)]
+                ("n_ctx", C.c_int), ("q_out", C.c_void_p), ("k_cache", C.c_void_p), ("v_cache", C.c_void_p),
+                ("k_scale", C.c_void_p), ("v_scale", C.c_void_p)]
 
 
 class EmbedArgs(C.Structure):
@@ -118,7 +119,8 @@ class NormCastArgs(C.Structure):
 class AttnDecodeArgs(C.Structure):
     _fields_ = [("q", C.c_void_p), ("k_cache", C.c_void_p), ("v_cache", C.c_void_p), ("positions", C.c_void_p),
                 ("slots", C.c_void_p), ("n_heads", C.c_int), ("n_kv_heads", C.c_int), ("n_ctx", C.c_int), ("n_splits", C.c_int),
-                ("scale", C.c_float), ("softcap", C.c_float), ("window", C.c_int), ("part_acc", C.c_void_p), ("part_ml", C.c_void_p)]
+                ("scale", C.c_float), ("softcap", C.c_float), ("window", C.c_int), ("part_acc", C.c_void_p), ("part_ml", C.c_void_p),
+                ("k_scale", C.c_void_p), ("v_scale", C.c_void_p)]
 
 
 class AttnCombineArgs(C.Structure):
@@ -331,20 +333,23 @@ def argmax(logits: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tenso
 def rope_kv(qkv: torch.Tensor, positions: torch.Tensor, slots: torch.Tensor, inv_freq: torch.Tensor, *, n_heads: int,
             n_kv_heads: int, hd: int, n_rot: int, neox: bool, mscale: float, k_cache: torch.Tensor, v_cache: torch.Tensor,
             q_norm: torch.Tensor | None = None, k_norm: torch.Tensor | None = None, eps: float = 1e-6,
-            q_out: torch.Tensor | None = None, pdl: bool = False) -> torch.Tensor:
+            q_out: torch.Tensor | None = None, pdl: bool = False, k_scale: torch.Tensor | None = None,
+            v_scale: torch.Tensor | None = None) -> torch.Tensor:
+    """``k_scale`` / ``v_scale`` (f16 [slots, Hkv, n_ctx, hd/32]) select a q8_0 cache: the caches then hold int8."""
     nt = qkv.shape[0]
     if q_out is None:
         q_out = torch.empty(nt, n_heads, hd, device=qkv.device, dtype=torch.float32)
     a = RopeKvArgs(ptr(qkv), ptr(positions), ptr(slots), ptr(inv_freq), ptr(q_norm), ptr(k_norm), eps, mscale, n_heads,
-                   n_kv_heads, hd, n_rot, int(neox), k_cache.shape[2], ptr(q_out), ptr(k_cache), ptr(v_cache))
+                   n_kv_heads, hd, n_rot, int(neox), k_cache.shape[2], ptr(q_out), ptr(k_cache), ptr(v_cache), ptr(k_scale), ptr(v_scale))
     _check(lib().b2_rope_kv(C.byref(a), nt, int(pdl), stream()), "rope_kv")
     return q_out
 
 
 def attn_decode(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, positions: torch.Tensor, slots: torch.Tensor, *,
                 scale: float, n_splits: int, window: int = 0, softcap: float = 0.0, sinks: torch.Tensor | None = None,
-                scratch: tuple[torch.Tensor, torch.Tensor] | None = None, quant_out: bool = True, pdl: bool = False):
-    """q: [nb, H, hd] fp32; caches [slots, Hkv, n_ctx, hd] f16.  Returns (out fp32 [nb, H*hd], QAct or None)."""
+                scratch: tuple[torch.Tensor, torch.Tensor] | None = None, quant_out: bool = True, pdl: bool = False,
+                k_scale: torch.Tensor | None = None, v_scale: torch.Tensor | None = None):
+    """q: [nb, H, hd] fp32; caches [slots, Hkv, n_ctx, hd] f16 (int8 + scales for q8_0).  Returns (out fp32 [nb, H*hd], QAct or None)."""
     nb, H, hd = q.shape
     Hkv, n_ctx = k_cache.shape[1], k_cache.shape[2]
     dev = q.device
@@ -355,7 +360,7 @@ def attn_decode(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, p
     oq = torch.empty(nb, H * hd, device=dev, dtype=torch.int8) if quant_out else None
     ods = torch.empty(nb, H * hd // 32, 2, device=dev, dtype=torch.float32) if quant_out else None
     a = AttnDecodeArgs(ptr(q), ptr(k_cache), ptr(v_cache), ptr(positions), ptr(slots), H, Hkv, n_ctx, n_splits, scale, softcap,
-                       window, ptr(scratch[0]), ptr(scratch[1]))
+                       window, ptr(scratch[0]), ptr(scratch[1]), ptr(k_scale), ptr(v_scale))
     c = AttnCombineArgs(ptr(scratch[0]), ptr(scratch[1]), ptr(sinks), H, n_splits, hd, ptr(out), ptr(oq), ptr(ods))
     _check(lib().b2_attn_decode(C.byref(a), C.byref(c), nb, hd, int(pdl), stream()), "attn_decode")
     return out, (QAct(oq, ods, out) if quant_out else None)
@@ -483,20 +488,22 @@ def rmsnorm_bf16(x: torch.Tensor, w: torch.Tensor | None, eps: float, do_norm: b
 class AttnPrefillArgs(C.Structure):
     _fields_ = [("q", C.c_void_p), ("k_cache", C.c_void_p), ("v_cache", C.c_void_p), ("out", C.c_void_p), ("sinks", C.c_void_p),
                 ("T", C.c_int), ("H", C.c_int), ("Hkv", C.c_int), ("n_ctx", C.c_int), ("slot", C.c_int), ("pos0", C.c_int),
-                ("kv_len", C.c_int), ("causal", C.c_int), ("window", C.c_int), ("scale", C.c_float), ("softcap", C.c_float)]
+                ("kv_len", C.c_int), ("causal", C.c_int), ("window", C.c_int), ("scale", C.c_float), ("softcap", C.c_float),
+                ("k_scale", C.c_void_p), ("v_scale", C.c_void_p)]
 
 
 ATTN_PREFILL_HEAD_DIMS = (64, 128)
 
 
 def attn_prefill(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, slot: int, pos0: int, kv_len: int, scale: float,
-                 causal: bool = True, window: int = 0, softcap: float = 0.0, sinks: torch.Tensor | None = None) -> torch.Tensor:
+                 causal: bool = True, window: int = 0, softcap: float = 0.0, sinks: torch.Tensor | None = None,
+                 k_scale: torch.Tensor | None = None, v_scale: torch.Tensor | None = None) -> torch.Tensor:
     """Flash attention of a prefill chunk (kernels/attn_prefill.cu): q [T, H, D] fp32 -> bf16 [T, H * D]."""
     T, H, D = q.shape
     n_slots, Hkv, n_ctx, _ = k_cache.shape
     out = torch.empty(T, H * D, device=q.device, dtype=torch.bfloat16)
     a = AttnPrefillArgs(ptr(q.contiguous()), ptr(k_cache), ptr(v_cache), ptr(out), ptr(sinks), T, H, Hkv, n_ctx, slot, pos0, kv_len,
-                        int(causal), window, scale, softcap)
+                        int(causal), window, scale, softcap, ptr(k_scale), ptr(v_scale))
     _check(lib().b2_attn_prefill(C.byref(a), D, stream()), "attn_prefill")
     return out
 

@@ -112,7 +112,7 @@ class TPBackend(B200Backend):
     name = "b200-tp"
 
     def __init__(self, cfg: ModelConfig, tensors, device: str = "cuda", rank: int = 0, world: int = 1, group=None,
-                 max_chunk: int = 2048, keep_bf16: bool | None = None):
+                 max_chunk: int = 2048, keep_bf16: bool | None = None, kv_type: str | None = None):
         if cfg.sandwich_norm:
             raise NotImplementedError("tensor parallelism is implemented for pre-norm models")
         if cfg.d_model > 8192:
@@ -123,7 +123,7 @@ class TPBackend(B200Backend):
         self.plan = sh.plan
         local = dataclasses.replace(cfg, n_heads=sh.plan["heads"], n_kv_heads=sh.plan["kv_heads"], d_ff=sh.plan["d_ff"])
         self.e_lo, self.e_cnt = rank * sh.plan["experts"], sh.plan["experts"]      # expert parallelism: this rank's experts
-        super().__init__(None, device=device, cfg=local, tensors=sh, keep_bf16=keep_bf16)
+        super().__init__(None, device=device, cfg=local, tensors=sh, keep_bf16=keep_bf16, kv_type=kv_type)
         self.v_lo = min(rank * sh.plan["vocab_rows"], cfg.vocab_size)
         if self.head.n != min(self.v_lo + sh.plan["vocab_rows"], cfg.vocab_size) - self.v_lo:
             raise RuntimeError("vocabulary shard has an unexpected number of rows")
@@ -224,11 +224,12 @@ class TPBackend(B200Backend):
             ra = K.RopeKvArgs(K.ptr(b.qkv), K.ptr(b.positions), K.ptr(b.slots), K.ptr(self.inv_freq_local if local else self.inv_freq),
                               K.ptr(L.q_norm), K.ptr(L.k_norm), c.norm_eps, 1.0 if local else self.mscale, c.n_heads, c.n_kv_heads,
                               c.head_dim, c.rope_dim, int(c.rope_style == "neox"), self.n_ctx, K.ptr(b.q), K.ptr(self.k_cache[i]),
-                              K.ptr(self.v_cache[i]))
+                              K.ptr(self.v_cache[i]), K.ptr(self.k_scale[i]), K.ptr(self.v_scale[i]))
             K._check(lib.b2_rope_kv(C.byref(ra), nb, int(self.pdl), st()), "rope_kv")
             aa = K.AttnDecodeArgs(K.ptr(b.q), K.ptr(self.k_cache[i]), K.ptr(self.v_cache[i]), K.ptr(b.positions), K.ptr(b.slots),
                                   c.n_heads, c.n_kv_heads, self.n_ctx, self.n_splits, self.attn_scale, c.attn_softcap,
-                                  c.sliding_window if L.swa else 0, K.ptr(b.part_acc), K.ptr(b.part_ml))
+                                  c.sliding_window if L.swa else 0, K.ptr(b.part_acc), K.ptr(b.part_ml), K.ptr(self.k_scale[i]),
+                                  K.ptr(self.v_scale[i]))
             ca = K.AttnCombineArgs(K.ptr(b.part_acc), K.ptr(b.part_ml), K.ptr(L.sinks), c.n_heads, self.n_splits, c.head_dim,
                                    K.ptr(b.ao), K.ptr(b.aq), K.ptr(b.ads))
             if self.fuse_attn_combine:      # the last CTA of every head group merges the splits: one launch instead of two
@@ -318,7 +319,8 @@ class TPBackend(B200Backend):
             local = L.swa and c.rope_base_local > 0
             q = K.rope_kv(qkv, pos, slots, self.inv_freq_local if local else self.inv_freq, n_heads=c.n_heads, n_kv_heads=c.n_kv_heads,
                           hd=c.head_dim, n_rot=c.rope_dim, neox=c.rope_style == "neox", mscale=1.0 if local else self.mscale,
-                          k_cache=self.k_cache[i], v_cache=self.v_cache[i], q_norm=L.q_norm, k_norm=L.k_norm, eps=c.norm_eps)
+                          k_cache=self.k_cache[i], v_cache=self.v_cache[i], q_norm=L.q_norm, k_norm=L.k_norm, eps=c.norm_eps,
+                          k_scale=self.k_scale[i], v_scale=self.v_scale[i])
             self._mm_scatter(self._attn_prefill(q, i, L, slot, pos0, p_end), L.wo, rpr)
             self._norm_gather(L.ffn_norm, rows, row0, reduce=True)
             if L.moe:

@@ -210,6 +210,89 @@ def test_attn_prefill(hd, H, Hkv, T, pos0, window, softcap, use_sinks, causal):
     assert torch.allclose(out, ref, atol=1e-2, rtol=2e-2), (out - ref).abs().max()
 
 
+@pytest.mark.parametrize("hd,H,Hkv", [(128, 8, 2), (64, 6, 3)])
+def test_kv_cache_q8(hd, H, Hkv):
+    """q8_0 K/V cache: the rope kernel writes int8 blocks of 32 dims with an f16 scale; both attention kernels expand them.
+
+    The written blocks are compared with the fp32 values (error within half a quantisation step), the attention
+    kernels with fp32 attention over the dequantised cache.
+    """
+    K = _K()
+    n_slots, n_ctx, slot, T = 2, 192, 1, 150
+    g = torch.Generator().manual_seed(hd)
+    qkv = torch.randn(T, (H + 2 * Hkv) * hd, generator=g).cuda()
+    pos = torch.arange(T, dtype=torch.int32).cuda()
+    slots = torch.full((T,), slot, dtype=torch.int32).cuda()
+    inv, _ = R.rope_inv_freq(hd, 10000.0, device="cuda")
+    kc = torch.zeros(n_slots, Hkv, n_ctx, hd, device="cuda", dtype=torch.int8)
+    vc = torch.zeros_like(kc)
+    ks = torch.zeros(n_slots, Hkv, n_ctx, hd // 32, device="cuda", dtype=torch.float16)
+    vs = torch.zeros_like(ks)
+    q = K.rope_kv(qkv, pos, slots, inv, n_heads=H, n_kv_heads=Hkv, hd=hd, n_rot=hd, neox=True, mscale=1.0, k_cache=kc, v_cache=vc,
+                  k_scale=ks, v_scale=vs)
+    kr = R.rope(qkv[:, H * hd:(H + Hkv) * hd].view(T, Hkv, hd).cpu(), pos.cpu(), inv.cpu(), "neox", 1.0)
+    vr = qkv[:, (H + Hkv) * hd:].view(T, Hkv, hd).cpu()
+
+    def deq(c, s):
+        return (c.float().view(*c.shape[:-1], hd // 32, 32) * s.float().unsqueeze(-1)).view(c.shape)
+
+    kd, vd = deq(kc, ks).cpu(), deq(vc, vs).cpu()
+    for got, want in ((kd[slot, :, :T].transpose(0, 1), kr), (vd[slot, :, :T].transpose(0, 1), vr)):
+        step = want.view(T, Hkv, hd // 32, 32).abs().amax(-1, keepdim=True) / 127
+        err = (got - want).view(T, Hkv, hd // 32, 32).abs()
+        assert (err <= 0.51 * step + 2e-3 * want.abs().max()).all()
+    assert kc[0].abs().max().item() == 0 and kc[slot, :, T:].abs().max().item() == 0      # nothing outside the written rows
+    scale = 1 / math.sqrt(hd)
+    # decode over the quantised cache
+    dpos = torch.tensor([0, 77, T - 1], dtype=torch.int32).cuda()
+    dslots = torch.full((3,), slot, dtype=torch.int32).cuda()
+    qd = torch.randn(3, H, hd, generator=g).cuda()
+    for n_splits in (1, 4):
+        out, _ = K.attn_decode(qd, kc, vc, dpos, dslots, scale=scale, n_splits=n_splits, k_scale=ks, v_scale=vs)
+        for b in range(3):
+            p = int(dpos[b])
+            ref = R.attention(qd[b:b + 1].cpu(), kd[slot, :, :p + 1].transpose(0, 1), vd[slot, :, :p + 1].transpose(0, 1),
+                              torch.tensor([p]), torch.arange(p + 1), scale=scale)
+            assert torch.allclose(out[b].cpu(), ref.reshape(-1), atol=2e-3, rtol=2e-3), (n_splits, b)
+    # prefill over the quantised cache
+    out = K.attn_prefill(q, kc, vc, slot, 0, T, scale, True, 0, 0.0, None, k_scale=ks, v_scale=vs).float().cpu().view(T, H, hd)
+    ref = R.attention(q.to(torch.float16).float().cpu(), kd[slot, :, :T].transpose(0, 1), vd[slot, :, :T].transpose(0, 1),
+                      torch.arange(T), torch.arange(T), scale=scale, causal=True)
+    assert torch.allclose(out, ref, atol=1e-2, rtol=2e-2), (out - ref).abs().max()
+
+
+@pytest.mark.parametrize("spec,ft", [("tiny-qwen3", "Q4_K_M"), ("tiny-gemma3", "Q8_0"), ("tiny-gpt-oss", "MXFP4")])
+def test_engine_kv_cache_q8(tmp_path, spec, ft):
+    """Whole model with the q8_0 K/V cache: logits stay close to the fp32 graph, the cache takes about half the bytes."""
+    from ollama_b200.engine.b200 import B200Backend
+    from ollama_b200.engine.backend import TorchBackend, open_model
+    from ollama_b200.models.synth import write_synthetic_gguf
+    p = str(tmp_path / "m.gguf")
+    write_synthetic_gguf(p, spec, ft)
+    g = open_model(p)
+    ref, eng, f16 = TorchBackend(g, "cpu"), B200Backend(g, "cuda", kv_type="q8_0"), B200Backend(g, "cuda")
+    for b in (ref, eng, f16):
+        b.alloc(2, 64)
+    if eng.cfg.head_dim not in _K().ATTN_PREFILL_HEAD_DIMS:
+        assert eng.kv_type == "f16"
+        return
+    assert eng.kv_type == "q8_0" and eng.kv_bytes() < 0.6 * f16.kv_bytes()
+    prompt = torch.randint(259, 4096, (20,), generator=torch.Generator().manual_seed(3)).tolist()
+    lr = ref.prefill(1, prompt, 0)
+    le = eng.prefill(1, prompt, 0).cpu()
+    tol = 0.06 * lr.abs().max().item()
+    assert (le - lr).abs().max().item() < tol
+    tok = int(lr.argmax())
+    for step in range(6):
+        pos = len(prompt) + step
+        lr = ref.decode([1], [tok], [pos])[0]
+        le = eng.decode([1], [tok], [pos])[0].cpu()
+        assert (le - lr).abs().max().item() < tol, step
+        tok = int(lr.argmax())
+    a = eng.decode_argmax([1], [tok], [len(prompt) + 6])
+    assert a[0] == int(eng.decode([1], [tok], [len(prompt) + 6])[0].argmax())
+
+
 @pytest.mark.parametrize("top_k,top_p,min_p,temp,penalties", [(40, 0.9, 0.0, 0.8, False), (1, 1.0, 0.0, 1.0, False), (256, 0.5, 0.05, 1.3, True),
                                                               (64, 1.0, 0.2, 0.7, True)])
 def test_sample_kernel_matches_filter_chain(top_k, top_p, min_p, temp, penalties):
