@@ -49,7 +49,7 @@ class B200Backend:
 
     def __init__(self, g: GGUFFile | None, device: str = "cuda", opts=None, cfg: ModelConfig | None = None,
                  tensors: dict[str, QWeight] | None = None, keep_bf16: bool | None = None, prefill_gemm: str = "bf16",
-                 kv_type: str | None = None):
+                 kv_type: str | None = None, layers: tuple[int, int] | None = None):
         """Load from an opened GGUF, or from ``cfg`` + an iterable source of :class:`QWeight` (synthetic checkpoints).
 
         ``keep_bf16``: keep a resident 16-bit copy of every matrix for prefill (None: when it fits in 40% of the free HBM;
@@ -57,7 +57,9 @@ class B200Backend:
         bf16 tensor-core GEMM) or "fused" (weights expanded inside the GEMM kernel; no 16-bit copy anywhere).
         ``kv_type``: "f16" or "q8_0" (int8 values with one f16 scale per 32 dims, written by the rope kernel and expanded
         inside the attention kernels; "q4_0" is served as q8_0); default: ``opts.kv_cache_type``
-        (envconfig/config.go:183 OLLAMA_KV_CACHE_TYPE).
+        (envconfig/config.go:183 OLLAMA_KV_CACHE_TYPE).  ``layers`` = (lo, hi): this object is one stage of a layer
+        pipeline and holds blocks lo..hi-1 only; the first stage also holds the embedding, the last one the output
+        norm and head, and the residual stream enters / leaves through ``buf.x`` (decode) or the ``x`` argument (prefill).
         """
         self.device = torch.device(device if device != "cuda" else f"cuda:{torch.cuda.current_device()}")
         self.cfg = cfg if cfg is not None else config_from_gguf(g)
@@ -65,6 +67,10 @@ class B200Backend:
             raise NotImplementedError(f"{self.cfg.arch} is not supported by the sm_100a engine")
         K.lib()
         self.prefill_gemm = prefill_gemm
+        self.l_lo, self.l_hi = layers if layers is not None else (0, self.cfg.n_layers)
+        if not 0 <= self.l_lo < self.l_hi <= self.cfg.n_layers:
+            raise ValueError(f"layer range {layers} outside 0..{self.cfg.n_layers}")
+        self.first, self.last = self.l_lo == 0, self.l_hi == self.cfg.n_layers
         kv_type = (kv_type or getattr(opts, "kv_cache_type", None) or "f16").lower()
         if kv_type not in ("f16", "q8_0", "q4_0"):
             raise ValueError(f"unknown K/V cache type {kv_type!r}")
@@ -111,13 +117,16 @@ class B200Backend:
                 w.bf16 = K.dequant_to_bf16(w)
             return w
 
-        self.embd = K.repack(get("token_embd.weight"), dev)
-        self.out_norm = vec("output_norm.weight")
-        self.head = mat("output") if has("output.weight") else self.embd
-        if self.keep_bf16 and not hasattr(self.head, "bf16"):
-            self.head.bf16 = K.dequant_to_bf16(self.head)
+        tied = not has("output.weight")
+        self.embd = K.repack(get("token_embd.weight"), dev) if self.first or (self.last and tied) else None
+        self.out_norm = self.head = None
+        if self.last:
+            self.out_norm = vec("output_norm.weight")
+            self.head = mat("output") if not tied else self.embd
+            if self.keep_bf16 and not hasattr(self.head, "bf16"):
+                self.head.bf16 = K.dequant_to_bf16(self.head)
         self.layers: list[_Layer] = []
-        for i in range(c.n_layers):
+        for i in range(self.l_lo, self.l_hi):
             p, L = f"blk.{i}.", _Layer()
             L.attn_norm = vec(p + "attn_norm.weight")
             L.wq, L.wk, L.wv, L.wo = mat(p + "attn_q"), mat(p + "attn_k"), mat(p + "attn_v"), mat(p + "attn_output")
@@ -170,7 +179,7 @@ class B200Backend:
         torch.cuda.synchronize(dev)
 
     def weight_bytes(self) -> int:
-        ws = [self.embd] + ([self.head] if self.head is not self.embd else [])
+        ws = [w for w in (self.embd, self.head if self.head is not self.embd else None) if w is not None]
         for L in self.layers:
             ws += [L.wq, L.wk, L.wv, L.wo, L.gu, L.down]
         return sum(w.nbytes for w in ws)
@@ -184,12 +193,12 @@ class B200Backend:
         c, dev = self.cfg, self.device
         self.n_slots, self.n_ctx = n_slots, n_ctx
         kv_dt = torch.int8 if self.kv_q8 else torch.float16
-        self.k_cache = [torch.zeros(n_slots, c.n_kv_heads, n_ctx, c.head_dim, device=dev, dtype=kv_dt) for _ in range(c.n_layers)]
-        self.v_cache = [torch.zeros(n_slots, c.n_kv_heads, n_ctx, c.head_dim, device=dev, dtype=kv_dt) for _ in range(c.n_layers)]
-        self.k_scale = self.v_scale = [None] * c.n_layers
+        self.k_cache = [torch.zeros(n_slots, c.n_kv_heads, n_ctx, c.head_dim, device=dev, dtype=kv_dt) for _ in self.layers]
+        self.v_cache = [torch.zeros(n_slots, c.n_kv_heads, n_ctx, c.head_dim, device=dev, dtype=kv_dt) for _ in self.layers]
+        self.k_scale = self.v_scale = [None] * len(self.layers)
         if self.kv_q8:
             def sc():
-                return [torch.zeros(n_slots, c.n_kv_heads, n_ctx, c.head_dim // 32, device=dev, dtype=torch.float16) for _ in range(c.n_layers)]
+                return [torch.zeros(n_slots, c.n_kv_heads, n_ctx, c.head_dim // 32, device=dev, dtype=torch.float16) for _ in self.layers]
             self.k_scale, self.v_scale = sc(), sc()
         MB = MAX_DECODE_BATCH
         f32, i8, i32 = torch.float32, torch.int8, torch.int32
@@ -330,8 +339,9 @@ class B200Backend:
         """Enqueue one decode step for ``nb`` sequences on the current stream (inputs: buf.tokens/positions/slots)."""
         c, b, lib, st = self.cfg, self.buf, K.lib(), K.stream
         self._n = 0
-        K.embed(self.embd, b.tokens[:nb], c.embed_scale, out=b.x)
-        self._n += 1
+        if self.first:      # later pipeline stages find the residual stream of the previous stage in b.x
+            K.embed(self.embd, b.tokens[:nb], c.embed_scale, out=b.x)
+            self._n += 1
         act = K._ACT[c.act]
         for i, L in enumerate(self.layers):
             self._norm_quant(b.x, L.attn_norm, nb, c.d_model)
@@ -376,6 +386,9 @@ class B200Backend:
                 self._norm_quant(b.tmp, L.post_ffw_norm, nb, c.d_model, residual=b.x)
             else:
                 self._gemv([L.down], nb, b.hq, b.hds, b.hf, b.x, b.x.stride(0), accumulate=True)
+        if not self.last:
+            self.launches_per_step = self._n
+            return
         self._norm_quant(b.x, self.out_norm, nb, c.d_model)
         self._gemv([self.head], nb, b.xq, b.xds, b.xf, b.logits, b.logits.stride(0))
         if want_argmax:
@@ -511,14 +524,18 @@ class B200Backend:
         return o.reshape(T, -1).to(torch.bfloat16)
 
     @torch.no_grad()
-    def _forward_chunk(self, slot: int, tokens: Sequence[int], pos0: int) -> torch.Tensor:
-        """Chunked prefill: returns the final hidden states [T, d_model] (fp32, before the output norm)."""
+    def _forward_chunk(self, slot: int, tokens: Sequence[int], pos0: int, x: torch.Tensor | None = None) -> torch.Tensor:
+        """Chunked prefill: returns the final hidden states [T, d_model] (fp32, before the output norm).
+
+        ``x``: residual stream handed over by the previous pipeline stage (the token ids then only give the chunk length).
+        """
         c, dev = self.cfg, self.device
         T = len(tokens)
         ids = torch.tensor(list(tokens), device=dev, dtype=torch.int32)
         pos = torch.arange(pos0, pos0 + T, device=dev, dtype=torch.int32)
         slots = torch.full((T,), slot, device=dev, dtype=torch.int32)
-        x = K.embed(self.embd, ids, c.embed_scale)
+        if x is None:
+            x = K.embed(self.embd, ids, c.embed_scale)
         p_end = pos0 + T
         for i, L in enumerate(self.layers):
             h = K.rmsnorm_bf16(x, L.attn_norm, c.norm_eps)

@@ -117,6 +117,10 @@ class Runner:
             self._tp_group = TPGroup(model_path, self._tp_devices(), max_chunk=max(512, min(int(self.opts.num_batch), 2048)),
                                     kv_type=self.opts.kv_cache_type or "f16")
             backend = self._tp_group.backend
+        elif backend is None and self._pp_devices():
+            # several GPUs, but the tensor-parallel split does not take this model: consecutive layers on consecutive GPUs
+            from .pipeline import PipelineBackend
+            backend = PipelineBackend(self.gguf, self._pp_devices(), opts=self.opts)
         self.backend = backend if backend is not None else make_backend(self.gguf, self.opts.device, opts=self.opts)
         self.cfg = self.backend.cfg
         try:
@@ -225,6 +229,20 @@ class Runner:
         except (ValueError, NotImplementedError):
             return []
         return list(range(tp))
+
+    def _pp_devices(self) -> list[int]:
+        """GPUs of a layer pipeline ([] = none): B200_PP, or the GPUs meant for a tensor-parallel group that cannot be formed."""
+        from .. import envconfig
+        n = envconfig.pp_degree() or (int(self.opts.tp) if int(self.opts.tp) > 1 else envconfig.tp_degree())
+        if n < 2 or self.gguf is None or str(self.opts.device).startswith("cpu"):
+            return []
+        import torch
+        if not torch.cuda.is_available() or torch.cuda.device_count() < n:
+            return []
+        from ..models.config import config_from_gguf
+        from .b200 import supports
+        cfg = config_from_gguf(self.gguf)
+        return list(range(n)) if supports(cfg) and cfg.n_layers >= n else []
 
     def close(self) -> None:
         with self.cv:

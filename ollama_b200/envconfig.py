@@ -240,6 +240,11 @@ def tp_degree() -> int:
     return _uint("B200_TP", 0)
 
 
+def pp_degree() -> int:
+    """B200_PP: number of GPUs of a layer pipeline (consecutive layers on consecutive GPUs); 0 = only as the fallback of B200_TP."""
+    return _uint("B200_PP", 0)
+
+
 def comm_mode() -> str:
     """B200_COMM: nccl | p2p (fused peer-memory kernels, default) ."""
     return var("B200_COMM") or "p2p"
