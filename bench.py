@@ -106,6 +106,8 @@ def main() -> None:
     ap.add_argument("--no-graphs", action="store_true")
     ap.add_argument("--no-pdl", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--parallelism", default="tp", choices=["tp", "pp"],
+                    help="N > 1: tp = tensor/expert parallel ranks (default), pp = layer pipeline driven by rank 0 (the reference's multi-GPU mode)")
     ap.add_argument("--layers", type=int, default=0, help="truncate the model to this many layers (profiling only; not a benchmark number)")
     args = ap.parse_args()
     if args.impl == "reference":
@@ -146,14 +148,25 @@ def main() -> None:
     hdr = synthetic_header(model, wl["ft"])
     cfg = config_from_gguf(hdr)
     t_load = time.time()
-    if n_gpus == 1:
+    pp = args.parallelism == "pp" and n_gpus > 1
+    if pp and rank != 0:      # the pipeline is driven by one process; the other ranks only keep the launch symmetric
+        dist.barrier()
+        dist.barrier()
+        dist.all_reduce(torch.zeros(2, device=dev, dtype=torch.float64), op=dist.ReduceOp.MAX)
+        dist.destroy_process_group()
+        return
+    if pp:
+        from ollama_b200.engine.pipeline import PipelineBackend
+        be = PipelineBackend(None, list(range(n_gpus)), cfg=cfg, tensors=lambda d: SyntheticTensors(model, wl["ft"], seed=0, device=str(d)))
+    elif n_gpus == 1:
         from ollama_b200.engine.b200 import B200Backend
         be = B200Backend(None, device=dev, cfg=cfg, tensors=SyntheticTensors(model, wl["ft"], seed=0, device=dev))
     else:
         from ollama_b200.parallel.tp_engine import TPBackend
         be = TPBackend(cfg, SyntheticTensors(model, wl["ft"], seed=0, device=dev), device=dev, rank=rank, world=world)
-    be.use_graphs = not args.no_graphs
-    be.pdl = not args.no_pdl
+    for part in (be.stages if pp else [be]):
+        part.use_graphs = not args.no_graphs
+        part.pdl = not args.no_pdl
     be.alloc(slots, wl["ctx"])
     torch.cuda.synchronize()
     t_load = time.time() - t_load
@@ -209,7 +222,7 @@ def main() -> None:
     # ---- end to end through the public runner API --------------------------------------------------
     e2e = None
     runner_be = be
-    if not args.no_e2e and n_gpus > 1:
+    if not args.no_e2e and n_gpus > 1 and not pp:
         # the serving stack runs in rank 0 only; the other ranks repeat its backend calls until it closes the group
         from ollama_b200.parallel.control import TPControl, TPLeader, follow
         ctl = TPControl(rank, world)
@@ -267,9 +280,9 @@ def main() -> None:
             "prompt_eval_tok_s": round(prefill_tok_s, 1), "ttft_ms_p50": round(ttft_p50, 3),
             "config": {"model": model, "quant": wl["ft"], "global_batch": slots, "seq_len": P + G, "prompt_tokens": P,
                        "generated_tokens": G, "num_ctx": wl["ctx"], "slots": slots,
-                       "parallelism": "single" if n_gpus == 1 else f"tp{n_gpus}",
+                       "parallelism": "single" if n_gpus == 1 else f"{args.parallelism}{n_gpus}",
                        "l2": "inputs larger than L2 (weights of several GB are re-read every token)",
-                       "weights": "random-init N(0,0.02), seed 0", "graphs": be.use_graphs, "pdl": be.pdl,
+                       "weights": "random-init N(0,0.02), seed 0", "graphs": not args.no_graphs, "pdl": not args.no_pdl,
                        **({"layers_override": args.layers, "invalid_as_benchmark": True} if args.layers else {})},
             "clocks": clocks, "e2e": e2e, "gpu_launches": int(launches), "load_s": round(t_load, 1), "impl": "ours",
         }

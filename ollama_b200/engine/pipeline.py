@@ -59,7 +59,8 @@ class PipelineBackend:
         self.stages: list[B200Backend] = []
         for dev, rng in zip(self.devices, self.ranges):
             with torch.cuda.device(dev):
-                self.stages.append(B200Backend(g, device=str(dev), opts=opts, cfg=self.cfg, tensors=tensors, layers=rng, **kw))
+                src = tensors(dev) if callable(tensors) else tensors        # a factory gives every stage a source on its own device
+                self.stages.append(B200Backend(g, device=str(dev), opts=opts, cfg=self.cfg, tensors=src, layers=rng, **kw))
         self.device = self.devices[-1]          # logits and sampled ids live on the last stage
         self.n_slots = self.n_ctx = 0
         self.kv_type = self.stages[0].kv_type
@@ -94,19 +95,53 @@ class PipelineBackend:
             s.close()
 
     # -- decode -----------------------------------------------------------------------------------------
-    def _step(self, slots, tokens, positions, mode) -> int:
+    def _step(self, slots, tokens, positions, mode, staged: bool = False) -> int:
         """One decode step through every stage; the hand-over of the residual stream is a device-to-device copy that
-        torch orders after the producer's stream and before the consumer's."""
+        torch orders after the producer's stream and before the consumer's.  ``staged``: the step's inputs are
+        already in every stage's buffers."""
         prev = None
         nb = len(slots)
         for s in self.stages:
             with torch.cuda.device(s.device):
-                s._stage(slots, tokens, positions)
+                if not staged:
+                    s._stage(slots, tokens, positions)
                 if prev is not None:
                     s.buf.x[:nb].copy_(prev.buf.x[:nb], non_blocking=True)
                 s._run_step(nb, mode if s.last else False)
             prev = s
         return nb
+
+    @torch.no_grad()
+    def decode_loop(self, slots: Sequence[int], tokens: Sequence[int], positions: Sequence[int], n_steps: int,
+                    first_tokens: torch.Tensor | None = None) -> torch.Tensor:
+        """Greedy-decode ``n_steps`` tokens per sequence without a host round trip: the sampled ids travel from the last
+        stage back to the first one as a device-to-device copy.  Returns int32 [n_steps, nb] on the last stage's device."""
+        if len(slots) > MAX_DECODE_BATCH:
+            parts = []
+            for i in range(0, len(slots), MAX_DECODE_BATCH):
+                j = i + MAX_DECODE_BATCH
+                parts.append(self.decode_loop(slots[i:j], tokens[i:j], positions[i:j], n_steps,
+                                              None if first_tokens is None else first_tokens[i:j]))
+            return torch.cat(parts, 1)
+        nb = len(slots)
+        first, last = self.stages[0], self.stages[-1]
+        for s in self.stages:
+            with torch.cuda.device(s.device):
+                s._stage(slots, tokens, positions)
+        if first_tokens is not None:
+            with torch.cuda.device(first.device):
+                first.buf.tokens[:nb].copy_(first_tokens.to(torch.int32), non_blocking=True)
+        out = torch.empty(n_steps, nb, device=last.device, dtype=torch.int32)
+        for i in range(n_steps):
+            self._step(slots, tokens, positions, True, staged=True)
+            with torch.cuda.device(last.device):
+                out[i].copy_(last.buf.sampled[:nb])
+            with torch.cuda.device(first.device):
+                first.buf.tokens[:nb].copy_(last.buf.sampled[:nb], non_blocking=True)
+            for s in self.stages:
+                with torch.cuda.device(s.device):
+                    s.buf.positions[:nb] += 1
+        return out
 
     @torch.no_grad()
     def decode(self, slots: Sequence[int], tokens: Sequence[int], positions: Sequence[int]) -> torch.Tensor:

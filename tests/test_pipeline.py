@@ -45,6 +45,9 @@ def _check_pipeline(tmp_path, devices, spec, ft):
         tok = int(da.argmax())
     pos = len(prompt) + 5
     assert pp.decode_argmax([1, 0], [tok, 7], [pos, 0]) == one.decode_argmax([1, 0], [tok, 7], [pos, 0])
+    la = one.decode_loop([1, 0], [tok, 7], [pos + 1, 1], 6).cpu()
+    lb = pp.decode_loop([1, 0], [tok, 7], [pos + 1, 1], 6).cpu()        # ids fed back on the device, stage to stage
+    assert torch.equal(la, lb)
     h1, h2 = one.hidden(0, prompt[:9]).cpu(), pp.hidden(0, prompt[:9]).cpu()
     assert torch.allclose(h1, h2, atol=1e-4 * h1.abs().max().item() + 1e-5)
     pp.close()
