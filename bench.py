@@ -120,11 +120,18 @@ def main() -> None:
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
     local = int(os.environ.get("LOCAL_RANK", "0"))
+    pp_gpus = 0
+    if args.parallelism == "pp" and max(world, args.gpus) > 1:
+        # a layer pipeline is driven by one process: the other launched ranks leave at once, without touching a GPU
+        # (a rank parked in a collective would occupy the very GPU that the driving process needs)
+        if rank != 0:
+            return
+        pp_gpus, world = max(world, args.gpus), 1
     if world > 1:
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
         torch.cuda.set_device(local)
         dist.init_process_group("nccl", device_id=torch.device(f"cuda:{local}"))
-    n_gpus = max(world, 1)
+    n_gpus = pp_gpus or max(world, 1)
     if args.gpus != n_gpus and rank == 0:
         print(f"warning: --gpus {args.gpus} but WORLD_SIZE={world}", file=sys.stderr)
 
@@ -148,13 +155,7 @@ def main() -> None:
     hdr = synthetic_header(model, wl["ft"])
     cfg = config_from_gguf(hdr)
     t_load = time.time()
-    pp = args.parallelism == "pp" and n_gpus > 1
-    if pp and rank != 0:      # the pipeline is driven by one process; the other ranks only keep the launch symmetric
-        dist.barrier()
-        dist.barrier()
-        dist.all_reduce(torch.zeros(2, device=dev, dtype=torch.float64), op=dist.ReduceOp.MAX)
-        dist.destroy_process_group()
-        return
+    pp = pp_gpus > 1
     if pp:
         from ollama_b200.engine.pipeline import PipelineBackend
         be = PipelineBackend(None, list(range(n_gpus)), cfg=cfg, tensors=lambda d: SyntheticTensors(model, wl["ft"], seed=0, device=str(d)))
@@ -175,6 +176,12 @@ def main() -> None:
     gen = torch.Generator().manual_seed(1234)
     slot_ids = list(range(slots))
 
+    def sync_stages():
+        """Pipeline: the events live on the first device, so the work of the later stages is waited for before each record."""
+        if pp:
+            for d in be.devices:
+                torch.cuda.synchronize(d)
+
     def epoch(timed: bool):
         """One request epoch, device-only: returns (prefill_ms, decode_ms)."""
         prompts = torch.randint(0, cfg.vocab_size, (slots, P), generator=gen)   # fresh ids every epoch: no prefix reuse
@@ -187,8 +194,10 @@ def main() -> None:
                 logits = be.prefill(s, toks[c0:c0 + PREFILL_CHUNK], c0, need_logits=c0 + PREFILL_CHUNK >= P)
             firsts.append(logits.argmax())
         first = torch.stack(firsts).to(torch.int32)
+        sync_stages()
         e1.record()
         toks = be.decode_loop(slot_ids, [0] * slots, [P] * slots, G - 1, first_tokens=first)
+        sync_stages()
         e2.record()
         torch.cuda.synchronize()
         return e0.elapsed_time(e1), e1.elapsed_time(e2), toks

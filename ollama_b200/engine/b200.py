@@ -86,6 +86,7 @@ class B200Backend:
             self.e_lo, self.e_cnt = 0, self.cfg.n_experts
         self.n_slots = self.n_ctx = 0
         self._graphs: dict[tuple[int, bool], torch.cuda.CUDAGraph] = {}
+        self._capture_stream = None
         self.pdl = True
         self.fuse_attn_combine = False    # one launch (last CTA merges the splits) measured slower than two launches joined by PDL
         self.use_graphs = True
@@ -417,7 +418,9 @@ class B200Backend:
                 self.launches_by_key[key] = self.launches_per_step
                 return
             g = torch.cuda.CUDAGraph()
-            with torch.cuda.graph(g):
+            if self._capture_stream is None:      # torch's default capture stream belongs to whichever device captured first
+                self._capture_stream = torch.cuda.Stream(device=self.device)
+            with torch.cuda.device(self.device), torch.cuda.graph(g, stream=self._capture_stream):
                 self._decode_kernels(nb, mode)
             self._graphs[key] = g
         g.replay()

@@ -257,11 +257,8 @@ __global__ void __launch_bounds__(128) attn_prefill_kernel(const __grid_constant
 template <int D>
 int launch(const AttnPrefillArgs& a, cudaStream_t st) {
     constexpr int SMEM = (BM + 4 * BN) * (D + PAD) * 2;
-    static bool attr = false;
-    if (!attr) {
-        cudaFuncSetAttribute(attn_prefill_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM);
-        attr = true;
-    }
+    static PerDeviceOnce once;
+    if (once.first()) cudaFuncSetAttribute(attn_prefill_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM);
     dim3 grid((a.T + BM - 1) / BM, a.H);
     attn_prefill_kernel<D><<<grid, 128, SMEM, st>>>(a);
     return (int)cudaGetLastError();

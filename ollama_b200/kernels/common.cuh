@@ -33,6 +33,19 @@ struct WDesc {
     int out_off;         // column offset of this segment in the output row
 };
 
+// Function attributes (dynamic shared memory opt-in) are per device: first() is true once per device and call site.
+struct PerDeviceOnce {
+    bool done[64] = {};
+    bool first() {
+        int d = 0;
+        cudaGetDevice(&d);
+        d &= 63;
+        const bool f = !done[d];
+        done[d] = true;
+        return f;
+    }
+};
+
 // Status word written by kernels that can give up (bounded waits, bad arguments); 0 = ok.
 enum KStatus : int { KS_OK = 0, KS_TIMEOUT = 1, KS_BAD_ARG = 2 };
 

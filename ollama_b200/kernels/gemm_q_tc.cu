@@ -341,11 +341,8 @@ B2_API int b2_gemm_q(const void* x, int m, const WDesc* w, float* out, int ldo, 
     if (!q_supported(*w)) return (int)cudaErrorNotSupported;
     CUtensorMap ma;
     if (!tc::make_map(&ma, x, m, w->k, BM)) return (int)cudaErrorNotSupported;
-    static bool attr = false;
-    if (!attr) {
-        cudaFuncSetAttribute(gemm_q_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_TOTAL);
-        attr = true;
-    }
+    static PerDeviceOnce once;
+    if (once.first()) cudaFuncSetAttribute(gemm_q_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_TOTAL);
     QGemmParams p{*w, m, out, ldo, accumulate, {}, 0};
     dim3 grid((m + BM - 1) / BM, (w->n + BN - 1) / BN);
     gemm_q_tc_kernel<<<grid, THREADS, SMEM_TOTAL, st>>>(ma, p);

@@ -237,11 +237,8 @@ template <int BN>
 int launch(const void* a, const void* b, const GemmParams& p, cudaStream_t st) {
     CUtensorMap ma, mb;
     if (!make_map(&ma, a, p.m, p.k, BM) || !make_map(&mb, b, p.n, p.k, BN)) return (int)cudaErrorNotSupported;
-    static bool attr = false;
-    if (!attr) {
-        cudaFuncSetAttribute(gemm_bf16_tc_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg<BN>::TOTAL);
-        attr = true;
-    }
+    static PerDeviceOnce once;
+    if (once.first()) cudaFuncSetAttribute(gemm_bf16_tc_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg<BN>::TOTAL);
     const int total = ((p.m + BM - 1) / BM) * ((p.n + BN - 1) / BN);
     const int grid = total < sm_count() ? total : sm_count();
     gemm_bf16_tc_kernel<BN><<<grid, 192, Cfg<BN>::TOTAL, st>>>(ma, mb, p);
