@@ -55,9 +55,43 @@ def _scale_min_k4(sc: torch.Tensor) -> tuple[torch.Tensor, torch.Tensor]:
     return torch.cat([lo_sc, hi_sc], 1).float(), torch.cat([lo_m, hi_m], 1).float()
 
 
-def dequantize(raw: torch.Tensor, t: int, n_elements: int | None = None) -> torch.Tensor:
-    """Decode a flat byte tensor of type ``t`` into float32 (flat)."""
+def _native_dequantize(raw: torch.Tensor, t: GGMLType) -> torch.Tensor | None:
+    """Host tensors go through the C++ codecs (native/codecs.cpp) when the library is there; None = use the tensor ops."""
+    if raw.device.type != "cpu":
+        return None
+    from ..utils import hostlib
+    if not hostlib.codec_supported(int(t), False):
+        return None
+    blocks = _blocks(raw, t).contiguous()
+    out = torch.empty(blocks.shape[0] * block_size(t), dtype=torch.float32)
+    if hostlib.lib().b2h_dequantize(int(t), blocks.data_ptr(), out.data_ptr(), blocks.shape[0]) != 0:
+        return None
+    return out
+
+
+def _native_quantize(x: torch.Tensor, t: GGMLType) -> torch.Tensor | None:
+    if x.device.type != "cpu":
+        return None
+    from ..utils import hostlib
+    if not hostlib.codec_supported(int(t), True):
+        return None
+    xf = x.float().contiguous().reshape(-1)
+    n = xf.numel() // block_size(t)
+    out = torch.empty(n * type_size(t), dtype=torch.uint8)
+    if hostlib.lib().b2h_quantize(int(t), xf.data_ptr(), out.data_ptr(), n) != 0:
+        return None
+    return out
+
+
+def dequantize(raw: torch.Tensor, t: int, n_elements: int | None = None, native: bool = True) -> torch.Tensor:
+    """Decode a flat byte tensor of type ``t`` into float32 (flat).  ``native=False`` forces the tensor-op codecs."""
     t = GGMLType(t)
+    if native and t.value >= 2 and t not in (GGMLType.BF16, GGMLType.F64, GGMLType.I8, GGMLType.I16, GGMLType.I32, GGMLType.I64):
+        y = _native_dequantize(raw, t)
+        if y is not None:
+            if n_elements is not None and y.numel() != n_elements:
+                raise ValueError(f"decoded {y.numel()} elements, expected {n_elements}")
+            return y
     if t == GGMLType.F32:
         return raw.reshape(-1).view(torch.uint8).view(torch.float32).clone()
     if t == GGMLType.F16:
@@ -346,11 +380,18 @@ _QUANTIZERS = {
 }
 
 
-def quantize(x: torch.Tensor, t: int) -> torch.Tensor:
-    """Encode a float tensor (last dimension contiguous, multiple of the block size) to flat bytes."""
+def quantize(x: torch.Tensor, t: int, native: bool = True) -> torch.Tensor:
+    """Encode a float tensor (last dimension contiguous, multiple of the block size) to flat bytes.
+
+    Host tensors are encoded by the C++ codecs, which make the same choices as the tensor-op encoders below
+    (identical bytes); ``native=False`` forces the tensor ops."""
     t = GGMLType(t)
     if x.shape[-1] % block_size(t):
         raise ValueError(f"row length {x.shape[-1]} is not a multiple of the {t.name} block size")
+    if native and t in _QUANTIZERS:
+        y = _native_quantize(x, t)
+        if y is not None:
+            return y
     if t == GGMLType.F32:
         return x.float().contiguous().view(-1).view(torch.uint8)
     if t == GGMLType.F16:

@@ -78,7 +78,7 @@ def build_host(verbose: bool = False, force: bool = False) -> str | None:
     if not srcs:
         return None
     if force or _stale(HOSTLIB, srcs):
-        cmd = ["g++", "-O2", "-std=c++17", "-shared", "-fPIC", "-fvisibility=hidden", "-o", HOSTLIB, *srcs, "-ldl", "-lpthread"]
+        cmd = ["g++", "-O2", "-std=c++17", "-ffp-contract=off", "-shared", "-fPIC", "-fvisibility=hidden", "-o", HOSTLIB, *srcs, "-ldl", "-lpthread"]
         r = subprocess.run(cmd, capture_output=True, text=True)
         if verbose or r.returncode:
             sys.stderr.write(r.stdout + r.stderr)

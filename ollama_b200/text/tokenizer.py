@@ -164,6 +164,7 @@ class BPETokenizer(Tokenizer):
         self.pre = pre
         self._pats = [regex.compile(p) for p in pats]
         self._cache: dict[str, list[int]] = {}
+        self._native = None       # (library, table handle, byte -> symbol id) once built; False: not usable
 
     def _pretokenize(self, text: str) -> list[str]:
         pieces = [text]
@@ -225,10 +226,55 @@ class BPETokenizer(Tokenizer):
             self._cache[word] = out
         return out
 
+    def _native_table(self):
+        """Merge table of the C++ merge loop (native/bpe.cpp), or None: no library, a byte symbol missing from the
+        vocabulary, or a merge whose result is not a token (the Python loop then splits such pieces again)."""
+        if self._native is not None:
+            return self._native or None
+        self._native = False
+        from ..utils import hostlib
+        L = hostlib.lib()
+        if L is None or not hasattr(L, "b2h_bpe_new"):
+            return None
+        import ctypes as C
+
+        import numpy as np
+        b2u = _byte_to_unicode()
+        byte_ids = np.array([self.vocab.get(b2u[b], -1) for b in range(256)], dtype=np.int32)
+        triples = np.empty((len(self.ranks), 3), dtype=np.int32)
+        for (a, b), r in self.ranks.items():
+            ia, ib, im = self.vocab.get(a), self.vocab.get(b), self.vocab.get(a + b)
+            if ia is None or ib is None or im is None:
+                return None
+            triples[r] = (ia, ib, im)
+        L.b2h_bpe_new.restype = C.c_void_p
+        L.b2h_bpe_new.argtypes = [C.c_void_p, C.c_int32]
+        L.b2h_bpe_encode.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int32, C.c_void_p, C.c_void_p]
+        h = L.b2h_bpe_new(triples.ctypes.data, len(triples)) if len(triples) == len({tuple(t[:2]) for t in triples.tolist()}) else None
+        if not h:
+            return None
+        self._native = (L, h, byte_ids)
+        return self._native
+
     def _encode_piece(self, text: str) -> list[int]:
+        words = self._pretokenize(text)
+        tab = self._native_table() if len(words) >= 8 else None
+        if tab is not None:
+            import numpy as np
+            L, h, byte_ids = tab
+            enc = [w.encode("utf-8") for w in words]
+            syms = byte_ids[np.frombuffer(b"".join(enc), dtype=np.uint8)]
+            if syms.size and int(syms.min()) >= 0:
+                off = np.zeros(len(enc) + 1, dtype=np.int64)
+                np.cumsum([len(e) for e in enc], out=off[1:])
+                out = np.empty(syms.size, dtype=np.int32)
+                out_off = np.empty(len(enc) + 1, dtype=np.int64)
+                syms = np.ascontiguousarray(syms, dtype=np.int32)
+                if L.b2h_bpe_encode(h, syms.ctypes.data, off.ctypes.data, len(enc), out.ctypes.data, out_off.ctypes.data) == 0:
+                    return out[:int(out_off[-1])].tolist()
         b2u = _byte_to_unicode()
         out: list[int] = []
-        for w in self._pretokenize(text):
+        for w in words:
             out.extend(self._bpe("".join(b2u[b] for b in w.encode("utf-8"))))
         return out
 

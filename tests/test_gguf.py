@@ -180,3 +180,27 @@ def test_mxfp4_values():
     blk[1] = 0x71           # low nibble 1 -> 0.5, high nibble 7 -> 6.0
     y = quants.dequantize(torch.from_numpy(blk), GGMLType.MXFP4)
     assert y[0].item() == 1.0 and y[16].item() == 12.0
+
+
+@pytest.mark.parametrize("t", [GGMLType.Q8_0, GGMLType.Q4_0, GGMLType.Q4_K, GGMLType.Q5_K, GGMLType.Q6_K, GGMLType.MXFP4])
+def test_native_codecs_match_the_tensor_op_codecs(t):
+    """The C++ block codecs (native/codecs.cpp) decode to the same floats and encode to the same bytes as the torch codecs."""
+    from ollama_b200.gguf import quants
+    from ollama_b200.utils import hostlib
+    if hostlib.lib() is None:
+        pytest.skip("host library not built")
+    g = torch.Generator().manual_seed(int(t))
+    x = torch.randn(64, 1024, generator=g) * torch.rand(64, 1, generator=g) * 3
+    x[3, :256] = 0.0                      # an all-zero block
+    x[5, 100] = 70000.0                   # a scale beyond the half range
+    raw = quants.quantize(x, t, native=False)
+    a, b = quants.dequantize(raw, t, native=False), quants.dequantize(raw, t, native=True)
+    ok = torch.isfinite(a)
+    assert torch.equal(ok, torch.isfinite(b)) and torch.allclose(a[ok], b[ok], rtol=1e-6, atol=0)
+    if hostlib.codec_supported(int(t), True):
+        assert torch.equal(quants.quantize(x, t, native=True), raw)
+    # garbage bytes (every bit pattern of the scale fields included) decode identically
+    junk = torch.randint(0, 256, (raw.numel(),), dtype=torch.uint8, generator=g)
+    a, b = quants.dequantize(junk, t, native=False), quants.dequantize(junk, t, native=True)
+    ok = torch.isfinite(a)
+    assert torch.equal(ok, torch.isfinite(b)) and torch.allclose(a[ok], b[ok], rtol=1e-6, atol=0)

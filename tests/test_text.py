@@ -177,3 +177,53 @@ def test_grammar_engine():
     assert gr.allows(tk.vocab["Ġworld"]) and gr.allows(tk.eos) and not gr.done()
     gr.accept(tk.vocab["Ġworld"])
     assert gr.done()
+
+
+def _trained_bpe(corpus: str, n_merges: int) -> BPETokenizer:
+    """A small byte-level BPE table learnt from ``corpus`` (most frequent pair first), so that merges chain as in real vocabularies."""
+    import collections
+
+    import regex
+    b2u = _byte_to_unicode()
+    tokens = [b2u[i] for i in range(256)]
+    words = collections.Counter(tuple(b2u[b] for b in w.encode("utf-8")) for w in regex.findall(r" ?[^\s]+|\s+", corpus))
+    merges = []
+    for _ in range(n_merges):
+        pairs = collections.Counter()
+        for w, c in words.items():
+            for a, b in zip(w, w[1:]):
+                pairs[(a, b)] += c
+        if not pairs:
+            break
+        (a, b), _ = max(pairs.items(), key=lambda kv: (kv[1], kv[0]))
+        merges.append(f"{a} {b}")
+        tokens.append(a + b)
+        nw = collections.Counter()
+        for w, c in words.items():
+            out, i = [], 0
+            while i < len(w):
+                if i + 1 < len(w) and w[i] == a and w[i + 1] == b:
+                    out.append(a + b)
+                    i += 2
+                else:
+                    out.append(w[i])
+                    i += 1
+            nw[tuple(out)] += c
+        words = nw
+    return BPETokenizer(tokens, [1] * len(tokens), merges, "llama-bpe")
+
+
+def test_native_bpe_merge_loop_matches_python():
+    from ollama_b200.utils import hostlib
+    if hostlib.lib() is None:
+        pytest.skip("host library not built")
+    corpus = ("the quick brown fox jumps over the lazy dog. " * 3 + "aaaa aaa aaaaa banana bandana ananas. "
+              "Tokenisation of naïve café text — with ☃ snowmen, 12345 67890 numbers and CamelCaseIdentifiers_like_this(). ") * 4
+    tk = _trained_bpe(corpus, 300)
+    assert tk._native_table() is not None
+    text = corpus + " unseen wörds zzzz aaaaaaaaaaaaaaaa " + "x" * 300 + " done"
+    native = tk.encode(text, add_special=False)
+    tk2 = _trained_bpe(corpus, 300)
+    tk2._native = False                                  # forces the Python merge loop
+    assert native == tk2.encode(text, add_special=False) and tk.decode(native) == text
+    assert len(native) < len(text.encode()) // 2          # merges really happened
