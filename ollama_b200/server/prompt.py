@@ -10,6 +10,7 @@ from __future__ import annotations
 from typing import Any, Callable
 
 from ..text import harmony
+from ..text.builtin import renderer_for
 from ..text.template import DEFAULT_TEMPLATE, JinjaChatTemplate, Template
 
 
@@ -34,6 +35,8 @@ class PromptRenderer:
             except Exception:
                 self.jinja = None
         self.names = harmony.FunctionNameMap()
+        # a renderer named by the model's configuration (Modelfile RENDERER) takes precedence over its templates
+        self.builtin = renderer_for((getattr(model, "config", None) or {}).get("renderer"))
 
     @property
     def template_source(self) -> str:
@@ -44,6 +47,8 @@ class PromptRenderer:
     def render_chat(self, messages: list[dict[str, Any]], tools: list[dict[str, Any]] | None = None, think: Any = None) -> str:
         if self.is_harmony:
             return harmony.render_prompt(messages, tools, think, self.names)
+        if self.builtin is not None:
+            return self.builtin(messages, tools, think)
         if self.go_template is not None:
             level = think if isinstance(think, str) else ""
             return self.go_template.execute(messages=messages, tools=tools, think=bool(think) if think is not None else False,

@@ -35,6 +35,7 @@ from ..store.create import CreateError, create_model
 from ..store.model import CAP_COMPLETION, CAP_EMBEDDING, CAP_INSERT, CAP_THINKING, CAP_TOOLS, CapabilityError, Model, ModelNotFound, get_model
 from ..store.names import parse_name
 from ..text import harmony
+from ..text.builtin import parser_for
 from ..text.gotemplate import TemplateError
 from ..text.thinking import ThinkingParser, infer_tags
 from ..text.tools import ToolParser, infer_tag
@@ -287,6 +288,7 @@ class Server:
                                  preserved_tokens=rend.is_harmony)
         tp = self._thinking_parser(rend, think, text) if not req.get("raw") else None
         hp = harmony.HarmonyParser(rend.names) if rend.is_harmony and not req.get("raw") else None
+        bp = parser_for(model.config.get("parser"), None, think) if hp is None and not req.get("raw") else None
 
         def gen() -> Iterator[dict[str, Any]]:
             out_tokens: list[int] = []
@@ -295,6 +297,8 @@ class Server:
                 content, thinking = ch.content, ""
                 if hp is not None:
                     thinking, content, _ = hp.add(content)
+                elif bp is not None:        # the model names a built-in parser (Modelfile PARSER)
+                    content, thinking, _ = bp.add(content, ch.done)
                 elif tp is not None:
                     thinking, content = tp.add(content)
                 if think is not None and not think_enabled(think):
@@ -412,8 +416,10 @@ class Server:
                                  truncate=req.get("truncate", True) is not False, shift=req.get("shift", True) is not False,
                                  preserved_tokens=rend.is_harmony)
         hp = harmony.HarmonyParser(rend.names) if rend.is_harmony else None
-        tp = self._thinking_parser(rend, think, text)
-        tool_parser = ToolParser(tools, infer_tag(rend.template_source)) if tools and hp is None else None
+        prefill = msgs[-1].get("content", "") if msgs and msgs[-1].get("role") == "assistant" else ""
+        bp = parser_for(model.config.get("parser"), tools, think, prefill) if hp is None else None
+        tp = self._thinking_parser(rend, think, text) if bp is None else None
+        tool_parser = ToolParser(tools, infer_tag(rend.template_source)) if tools and hp is None and bp is None else None
         show_thinking = think is None or think_enabled(think)
 
         def gen() -> Iterator[dict[str, Any]]:
@@ -421,6 +427,8 @@ class Server:
                 content, thinking, calls = ch.content, "", []
                 if hp is not None:
                     thinking, content, calls = hp.add(content)
+                elif bp is not None:
+                    content, thinking, calls = bp.add(content, ch.done)
                 else:
                     if tp is not None:
                         thinking, content = tp.add(content)

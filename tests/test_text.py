@@ -227,3 +227,68 @@ def test_native_bpe_merge_loop_matches_python():
     tk2._native = False                                  # forces the Python merge loop
     assert native == tk2.encode(text, add_special=False) and tk.decode(native) == text
     assert len(native) < len(text.encode()) // 2          # merges really happened
+
+
+_TOOLS = [{"type": "function", "function": {"name": "get_weather", "description": "Weather for a city", "parameters": {
+    "type": "object", "required": ["city"], "properties": {
+        "city": {"type": "string", "description": "City name"}, "days": {"type": "integer"}, "metric": {"type": "boolean"},
+        "tags": {"type": "array"}, "opts": {"type": ["object", "null"]}, "ratio": {"type": "number"}}}}}]
+
+
+def _feed(parser, text, step):
+    """Stream ``text`` in pieces of ``step`` characters; returns (content, thinking, calls)."""
+    c, t, calls = "", "", []
+    for i in range(0, len(text), step):
+        a, b, k = parser.add(text[i:i + step], i + step >= len(text))
+        c, t, calls = c + a, t + b, calls + k
+    return c, t, calls
+
+
+@pytest.mark.parametrize("step", [1, 3, 7, 1000])
+def test_builtin_parsers_split_streams_the_same_way_at_every_chunking(step):
+    from ollama_b200.text.builtin import parser_for, typed_value
+    out = ("I will look it up.\n\n<tool_call>\n<function=get_weather>\n<parameter=city>\nParis\n</parameter>\n<parameter=days>\n3\n</parameter>\n"
+           "<parameter=metric>\nTrue\n</parameter>\n<parameter=tags>\n[\"a\", 1]\n</parameter>\n<parameter=opts>\nnull\n</parameter>\n"
+           "<parameter=ratio>\n2.0\n</parameter>\n<parameter=note>\nline 1\nline 2\n</parameter>\n</function>\n</tool_call>")
+    c, t, calls = _feed(parser_for("qwen3-coder", _TOOLS), out, step)
+    assert c == "I will look it up." and t == "" and len(calls) == 1
+    assert calls[0]["function"] == {"name": "get_weather", "arguments": {"city": "Paris", "days": 3, "metric": True, "tags": ["a", 1], "opts": None,
+                                                                         "ratio": 2, "note": "line 1\nline 2"}}
+    # a reasoning model: the prompt ended inside <think>, some checkpoints repeat the tag
+    for lead in ("", "<think>"):
+        out = lead + "Let me think.\nOK.</think>\n\nThe answer is 4 < 5.\n<tool_call>\n{\"name\": \"get_weather\", \"arguments\": {\"city\": \"Oslo\"}}\n</tool_call>"
+        c, t, calls = _feed(parser_for("qwen3-thinking", _TOOLS, None), out, step)
+        assert t == "Let me think.\nOK." and c == "The answer is 4 < 5." and calls[0]["function"] == {"name": "get_weather", "arguments": {"city": "Oslo"}}
+    # thinking switched off, or an assistant prefill: everything is content; without tools the call markup stays text
+    c, t, calls = _feed(parser_for("qwen3-thinking", None, False), "plain <b>text</b> <tool_call>x</tool_call>", step)
+    assert (c, t, calls) == ("plain <b>text</b> <tool_call>x</tool_call>", "", [])
+    assert _feed(parser_for("qwen3-thinking", None, None, prefill="So"), " it goes", step)[0] == " it goes"
+    out = "[THINK]hmm[/THINK]Sure.[TOOL_CALLS]get_weather[ARGS]{\"city\": \"Rome {x}\", \"n\": {\"a\": \"}\"}}[TOOL_CALLS]get_weather[ARGS]{\"city\": \"Bern\"}"
+    c, t, calls = _feed(parser_for("ministral", _TOOLS), out, step)
+    assert (c, t) == ("Sure.", "hmm") and [k["function"]["arguments"]["city"] for k in calls] == ["Rome {x}", "Bern"]
+    # malformed or unterminated calls come back as the text that was produced
+    c, _, calls = _feed(parser_for("qwen3", _TOOLS), "a <tool_call>not json</tool_call> b <tool_call>{\"name\"", step)
+    assert calls == [] and c == "a<tool_call>not json</tool_call>b<tool_call>{\"name\""
+    assert _feed(parser_for("passthrough"), " raw <think> ", step) == (" raw <think> ", "", [])
+    assert parser_for("unknown-family") is None and parser_for(None) is None
+    assert typed_value("12", ["string", "integer"]) == 12 and typed_value("x", ["integer"]) == "x" and typed_value("maybe", ["boolean"]) is False
+    assert typed_value("1.5", ["number"]) == 1.5 and typed_value("{\"a\":1}", ["object"]) == {"a": 1} and typed_value("NULL", ["string"]) is None
+
+
+def test_qwen3_coder_renderer():
+    from ollama_b200.text.builtin import render_qwen3_coder, renderer_for
+    assert renderer_for("qwen3-coder") is render_qwen3_coder and renderer_for("nope") is None
+    msgs = [{"role": "system", "content": "Be brief."}, {"role": "system", "content": "ignored"}, {"role": "user", "content": "Weather?"},
+            {"role": "assistant", "content": "Checking.", "tool_calls": [{"function": {"name": "get_weather", "arguments": {"city": "Paris", "days": 2, "opts": {"a": 1}}}}]},
+            {"role": "tool", "content": "sunny"}, {"role": "tool", "content": "22C"}]
+    p = render_qwen3_coder(msgs, _TOOLS)
+    assert p.startswith("<|im_start|>system\nBe brief.\n\n# Tools\n\nYou have access to the following functions:\n\n<tools>\n<function>\n<name>get_weather</name>\n"
+                        "<description>Weather for a city</description>\n<parameters>\n<parameter>\n<name>city</name>\n<type>string</type>\n<description>City name</description>\n</parameter>")
+    assert "<type>[\"object\",\"null\"]</type>" in p and "\n<required>[\"city\"]</required>\n</parameters>\n</function>\n</tools>" in p and "ignored" not in p
+    assert ("<|im_start|>assistant\nChecking.\n\n<tool_call>\n<function=get_weather>\n<parameter=city>\nParis\n</parameter>\n<parameter=days>\n2\n</parameter>\n"
+            "<parameter=opts>\n{\"a\":1}\n</parameter>\n</function>\n</tool_call><|im_end|>\n") in p
+    assert p.endswith("<|im_start|>user\n<tool_response>\nsunny\n</tool_response>\n<tool_response>\n22C\n</tool_response><|im_end|>\n<|im_start|>assistant\n")
+    # no system message, no tools: plain ChatML; a trailing assistant message stays open
+    assert render_qwen3_coder([{"role": "user", "content": "hi"}]) == "<|im_start|>user\nhi<|im_end|>\n<|im_start|>assistant\n"
+    assert render_qwen3_coder([{"role": "user", "content": "hi"}, {"role": "assistant", "content": "He"}]).endswith("<|im_start|>assistant\nHe")
+    assert "You are Qwen, a helpful AI assistant" in render_qwen3_coder([{"role": "user", "content": "hi"}], _TOOLS)
