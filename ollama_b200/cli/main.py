@@ -80,6 +80,11 @@ def cmd_serve(args) -> int:
     from ..server.routes import create_app
     from ..utils import logutil
     logutil.setup()
+    try:      # the installation's identity for registry pushes and private pulls (cmd/cmd.go:2015-2077)
+        from .. import auth
+        auth.ensure_key()
+    except (auth.AuthError, OSError) as e:
+        print(f"warning: could not set up the ed25519 key pair: {e}", file=sys.stderr)
     h = envconfig.host()
     print(f"ollama-b200 {VERSION} listening on {h.netloc}", file=sys.stderr)
     for k, (v, desc) in envconfig.as_map().items():

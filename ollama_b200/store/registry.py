@@ -5,8 +5,8 @@ multi-part downloads (up to 16 parts of 100 MB - 1 GB, retried, digest verified;
 policy in server/download.go:31,99-102,278-287,400-434) and finally the manifest is written.  Push:
 ``HEAD`` each blob, upload missing ones (``POST .../blobs/uploads/`` then ``PATCH``/``PUT``), then
 ``PUT`` the manifest (server/upload.go, server/images.go:931-1295).  Bearer-token challenges
-(``WWW-Authenticate``) are followed without credentials; signed requests for private namespaces are
-not implemented.
+(``WWW-Authenticate``) are answered with a token request signed by the installation's ed25519 key
+(``ollama_b200/auth.py``).
 """
 from __future__ import annotations
 
@@ -43,6 +43,23 @@ class _Session:
         self.s = requests.Session()
         self.token = ""
 
+    def _token(self, ch: dict[str, str], url: str):
+        """Answer a bearer challenge: the token request is signed with this installation's key when there is one
+        (server/auth.go:53-100); the realm must be the host that issued the challenge, so that a signature never
+        goes to a third party.  Without a key the request goes out unsigned (public namespaces)."""
+        from urllib.parse import urlsplit
+
+        from .. import auth
+        turl = auth.challenge_url(ch["realm"], ch.get("service", ""), ch.get("scope", ""))
+        if urlsplit(turl).netloc != urlsplit(url).netloc:
+            raise RegistryError(f"realm host {urlsplit(turl).netloc!r} does not match original host {urlsplit(url).netloc!r}", 401)
+        hdr = {}
+        try:
+            hdr["Authorization"] = auth.token_request_signature(turl)
+        except auth.AuthError:
+            pass
+        return self.s.get(turl, headers=hdr, timeout=30)
+
     def request(self, method: str, url: str, **kw):
         import requests
         headers = dict(kw.pop("headers", {}) or {})
@@ -53,8 +70,8 @@ class _Session:
             if r.status_code == 401 and "www-authenticate" in r.headers and not kw.get("_retried"):
                 ch = dict(re.findall(r'(\w+)="([^"]*)"', r.headers["www-authenticate"]))
                 if ch.get("realm"):
-                    tr = self.s.get(ch["realm"], params={k: v for k, v in ch.items() if k != "realm"}, timeout=30)
-                    if tr.ok:
+                    tr = self._token(ch, url)
+                    if tr is not None and tr.ok:
                         self.token = tr.json().get("token", "")
                         headers["Authorization"] = f"Bearer {self.token}"
                         r = self.s.request(method, url, headers=headers, timeout=60, **{k: v for k, v in kw.items() if k != "_retried"})
