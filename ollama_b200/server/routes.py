@@ -39,6 +39,7 @@ from ..text.builtin import parser_for
 from ..text.gotemplate import TemplateError
 from ..text.thinking import ThinkingParser, infer_tags
 from ..text.tools import ToolParser, infer_tag
+from .caches import ModelListCache, ModelShowCache
 from .prompt import PromptRenderer, chat_prompt
 from .sched import Scheduler, SchedulerError
 
@@ -70,9 +71,11 @@ class Server:
         from ..discover.devices import gpu_devices
         self.sched = sched or Scheduler(get_gpus_fn=gpu_devices)
         self.renderers: dict[str, PromptRenderer] = {}
+        self.list_cache, self.show_cache = ModelListCache(), ModelShowCache()
         from .request_log import RequestLogger
         self.request_log = RequestLogger()
         self.app = self._build()
+        self.app.state.server = self        # tests and embedding programs reach the scheduler and the caches through the app
 
     # -- plumbing ---------------------------------------------------------------------------------------
     def _build(self) -> Starlette:
@@ -560,16 +563,17 @@ class Server:
         return JSONResponse({"models": models})
 
     async def tags(self, request: Request):
+        def entry(n, man):
+            cfg = man.config_json()
+            return {"name": n.display(), "model": n.display(),
+                    "modified_at": datetime.datetime.fromtimestamp(man.mtime, datetime.timezone.utc).isoformat(),
+                    "size": man.size(), "digest": man.digest,
+                    "details": {"parent_model": "", "format": cfg.get("model_format", ""), "family": cfg.get("model_family", ""),
+                                "families": cfg.get("model_families"), "parameter_size": cfg.get("model_type", ""),
+                                "quantization_level": cfg.get("file_type", "")}}
+
         def work():
-            out = []
-            for n, man in M.list_manifests():
-                cfg = man.config_json()
-                out.append({"name": n.display(), "model": n.display(),
-                            "modified_at": datetime.datetime.fromtimestamp(man.mtime, datetime.timezone.utc).isoformat(),
-                            "size": man.size(), "digest": man.digest,
-                            "details": {"parent_model": "", "format": cfg.get("model_format", ""), "family": cfg.get("model_family", ""),
-                                        "families": cfg.get("model_families"), "parameter_size": cfg.get("model_type", ""),
-                                        "quantization_level": cfg.get("file_type", "")}})
+            out = self.list_cache.list(entry)        # unchanged manifests are not read again
             out.sort(key=lambda m: m["modified_at"], reverse=True)
             return out
         return JSONResponse({"models": await asyncio.to_thread(work)})
@@ -578,6 +582,11 @@ class Server:
         req = await self._json(request)
         name = req.get("model") or req.get("name") or ""
         model = self._model(name)
+        use_cache = ModelShowCache.cacheable(req)
+        if use_cache:
+            hit = self.show_cache.get(model.name, bool(req.get("verbose")), model.digest)
+            if hit is not None:
+                return JSONResponse(hit)
 
         def work():
             kv = dict(model.kv())
@@ -606,6 +615,8 @@ class Server:
                 out["parser"] = model.config["parser"]
             if req.get("verbose"):
                 out["tensors"] = [{"name": n, "type": t, "shape": s} for n, t, s in tensors]
+            if use_cache:
+                self.show_cache.put(model.name, bool(req.get("verbose")), model.digest, out)
             return out
 
         return JSONResponse(await asyncio.to_thread(work))

@@ -202,8 +202,11 @@ def write_manifest(name: Name, config: Layer, layers: list[Layer]) -> Manifest:
     return read_manifest(name)
 
 
-def list_manifests() -> Iterator[tuple[Name, Manifest]]:
+def manifest_names() -> Iterator[tuple[Name, str]]:
+    """Every stored model name with the path of its manifest file (nothing is read)."""
     root = manifests_dir()
+    if not os.path.isdir(root):
+        return
     for host in sorted(os.listdir(root)):
         hp = os.path.join(root, host)
         if not os.path.isdir(hp):
@@ -217,10 +220,15 @@ def list_manifests() -> Iterator[tuple[Name, Manifest]]:
                     continue
                 n = Name(rel[0], rel[1], rel[2], tag)
                 if n.valid:
-                    try:
-                        yield n, read_manifest(n)
-                    except (StoreError, ValueError, OSError):
-                        continue
+                    yield n, os.path.join(dirpath, tag)
+
+
+def list_manifests() -> Iterator[tuple[Name, Manifest]]:
+    for n, _ in manifest_names():
+        try:
+            yield n, read_manifest(n)
+        except (StoreError, ValueError, OSError):
+            continue
 
 
 def delete_model(name: Name) -> None:

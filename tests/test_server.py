@@ -104,6 +104,27 @@ def test_tokenize_embed_show_copy_delete(client):
     assert client.request("DELETE", "/api/delete", json={"model": "copy/tiny2:v1"}).status_code == 404
 
 
+def test_list_and_show_caches(client):
+    srv = client.app.state.server
+    a = client.post("/api/show", json={"model": "tiny"}).json()
+    h0 = srv.show_cache.hits
+    assert client.post("/api/show", json={"model": "tiny"}).json() == a and srv.show_cache.hits == h0 + 1
+    # overlays change the answer and therefore bypass the cache
+    assert client.post("/api/show", json={"model": "tiny", "system": "x"}).json()["system"] == "x" and srv.show_cache.hits == h0 + 1
+    assert client.post("/api/show", json={"model": "tiny"}).json()["system"] == a["system"]
+    # a changed manifest (new digest) replaces the entry
+    assert client.post("/api/create", json={"model": "tiny3", "from": "tiny", "system": "one", "stream": False}).status_code == 200
+    assert client.post("/api/show", json={"model": "tiny3"}).json()["system"] == "one"
+    assert client.post("/api/create", json={"model": "tiny3", "from": "tiny", "system": "two", "stream": False}).status_code == 200
+    assert client.post("/api/show", json={"model": "tiny3"}).json()["system"] == "two"
+    t1 = client.get("/api/tags").json()["models"]
+    m0 = srv.list_cache.misses
+    t2 = client.get("/api/tags").json()["models"]
+    assert t1 == t2 and srv.list_cache.misses == m0 and any(m["name"] == "tiny3:latest" for m in t2)
+    assert client.request("DELETE", "/api/delete", json={"model": "tiny3"}).status_code == 200
+    assert not any(m["name"] == "tiny3:latest" for m in client.get("/api/tags").json()["models"])
+
+
 def test_create_from_existing_model(client):
     r = client.post("/api/create", json={"model": "child", "from": "tiny", "system": "be brief", "parameters": {"stop": ["<t1>"]},
                                          "stream": False})
