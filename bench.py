@@ -108,6 +108,7 @@ def main() -> None:
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--parallelism", default="tp", choices=["tp", "pp"],
                     help="N > 1: tp = tensor/expert parallel ranks (default), pp = layer pipeline driven by rank 0 (the reference's multi-GPU mode)")
+    ap.add_argument("--kv-type", default="f16", choices=["f16", "q8_0"], help="K/V cache encoding (OLLAMA_KV_CACHE_TYPE)")
     ap.add_argument("--layers", type=int, default=0, help="truncate the model to this many layers (profiling only; not a benchmark number)")
     args = ap.parse_args()
     if args.impl == "reference":
@@ -158,13 +159,14 @@ def main() -> None:
     pp = pp_gpus > 1
     if pp:
         from ollama_b200.engine.pipeline import PipelineBackend
-        be = PipelineBackend(None, list(range(n_gpus)), cfg=cfg, tensors=lambda d: SyntheticTensors(model, wl["ft"], seed=0, device=str(d)))
+        be = PipelineBackend(None, list(range(n_gpus)), cfg=cfg, tensors=lambda d: SyntheticTensors(model, wl["ft"], seed=0, device=str(d)),
+                             kv_type=args.kv_type)
     elif n_gpus == 1:
         from ollama_b200.engine.b200 import B200Backend
-        be = B200Backend(None, device=dev, cfg=cfg, tensors=SyntheticTensors(model, wl["ft"], seed=0, device=dev))
+        be = B200Backend(None, device=dev, cfg=cfg, tensors=SyntheticTensors(model, wl["ft"], seed=0, device=dev), kv_type=args.kv_type)
     else:
         from ollama_b200.parallel.tp_engine import TPBackend
-        be = TPBackend(cfg, SyntheticTensors(model, wl["ft"], seed=0, device=dev), device=dev, rank=rank, world=world)
+        be = TPBackend(cfg, SyntheticTensors(model, wl["ft"], seed=0, device=dev), device=dev, rank=rank, world=world, kv_type=args.kv_type)
     for part in (be.stages if pp else [be]):
         part.use_graphs = not args.no_graphs
         part.pdl = not args.no_pdl
@@ -288,7 +290,7 @@ def main() -> None:
             "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
             "prompt_eval_tok_s": round(prefill_tok_s, 1), "ttft_ms_p50": round(ttft_p50, 3),
             "config": {"model": model, "quant": wl["ft"], "global_batch": slots, "seq_len": P + G, "prompt_tokens": P,
-                       "generated_tokens": G, "num_ctx": wl["ctx"], "slots": slots,
+                       "generated_tokens": G, "num_ctx": wl["ctx"], "slots": slots, "kv_cache": be.kv_type,
                        "parallelism": "single" if n_gpus == 1 else f"{args.parallelism}{n_gpus}",
                        "l2": "inputs larger than L2 (weights of several GB are re-read every token)",
                        "weights": "random-init N(0,0.02), seed 0", "graphs": not args.no_graphs, "pdl": not args.no_pdl,

@@ -245,6 +245,11 @@ def pp_degree() -> int:
     return _uint("B200_PP", 0)
 
 
+def attn_splits() -> int:
+    """B200_ATTN_SPLITS: upper bound of the split-K width of decode attention (CTAs per sequence and KV head)."""
+    return max(1, _uint("B200_ATTN_SPLITS", 32))
+
+
 def comm_mode() -> str:
     """B200_COMM: nccl | p2p (fused peer-memory kernels, default) ."""
     return var("B200_COMM") or "p2p"
