@@ -10,22 +10,9 @@
 // sinks, the normalisation and the int8 re-quantisation for the output projection happen in the
 // combine kernel.  Masks: causal by construction (only positions <= the query position are stored),
 // optional sliding window, optional logit soft-cap.
-#include "common.cuh"
+#include <stdlib.h>
 
-struct AttnDecodeArgs {
-    const float* q;          // [nb][H][HD]
-    const __half* k_cache;   // [slots][Hkv][n_ctx][HD]
-    const __half* v_cache;
-    const int* positions;    // [nb] position of the query token (its K/V is already in the cache)
-    const int* slots;        // [nb]
-    int n_heads, n_kv_heads, n_ctx, n_splits;
-    float scale, softcap;
-    int window;              // 0 = full
-    float* part_acc;         // scratch [nb][H][splits][HD]
-    float2* part_ml;         // scratch [nb][H][splits] (max, sum)
-    const __half* k_scale;   // q8_0 cache (k_cache / v_cache hold int8): [slots][Hkv][n_ctx][HD/32] scales, or null for f16
-    const __half* v_scale;
-};
+#include "attn_args.cuh"
 
 template <int HD, int G>
 __device__ __forceinline__ void attn_decode_body(const AttnDecodeArgs& a) {
@@ -289,6 +276,25 @@ static cudaError_t launch1(const void* fn, dim3 grid, dim3 block, void** args, c
     return cudaLaunchKernelExC(&cfg, fn, args);
 }
 
+// Tensor-core kernel or scalar kernel: B200_ATTN_MMA = 1 / 0 forces the choice; otherwise grouped-query models with
+// an allocated context of at least B200_ATTN_MMA_CTX positions (default 2048) take the tensor-core kernel.
+static int g_mma_mode = -2, g_mma_min_ctx = 2048;      // -2: not read from the environment yet, -1: automatic
+
+static bool use_mma(const AttnDecodeArgs& a, int hd) {
+    if (g_mma_mode == -2) {
+        const char* e = getenv("B200_ATTN_MMA");
+        g_mma_mode = e ? atoi(e) : -1;
+        const char* c = getenv("B200_ATTN_MMA_CTX");
+        if (c) g_mma_min_ctx = atoi(c);
+    }
+    if (hd != 64 && hd != 128) return false;
+    if (g_mma_mode >= 0) return g_mma_mode != 0;
+    return a.n_heads / a.n_kv_heads >= 2 && a.n_ctx >= g_mma_min_ctx;
+}
+
+// Overrides the choice for this process: 1 tensor-core kernel, 0 scalar kernel, -1 automatic.
+B2_API void b2_attn_decode_mode(int mode) { g_mma_mode = mode < -1 ? -1 : mode; }
+
 // Scratch needed by b2_attn_decode: part_acc = nb*H*splits*hd floats, part_ml = nb*H*splits float2.
 B2_API int b2_attn_decode(const AttnDecodeArgs* a, const AttnCombineArgs* c, int nb, int hd, int pdl, cudaStream_t st) {
     const int group = a->n_heads / a->n_kv_heads;
@@ -302,7 +308,9 @@ B2_API int b2_attn_decode(const AttnDecodeArgs* a, const AttnCombineArgs* c, int
     dim3 grid(a->n_splits, a->n_kv_heads * (group / G), nb);
     AttnDecodeArgs ca = *a;
     void* args[] = {&ca};
-    cudaError_t e = launch1(fn, grid, dim3(128), args, st, pdl);
+    cudaError_t e = cudaErrorNotSupported;
+    if (use_mma(*a, hd)) e = (cudaError_t)attn_decode_mma_launch(*a, nb, hd, pdl, st);
+    if (e == cudaErrorNotSupported) e = launch1(fn, grid, dim3(128), args, st, pdl);
     if (e != cudaSuccess) return (int)e;
     AttnCombineArgs cc = *c;
     void* args2[] = {&cc};

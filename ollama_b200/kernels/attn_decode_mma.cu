@@ -1,0 +1,263 @@
+// Split-K decode attention on the tensor cores, sm_100a.
+//
+// Same contract as the scalar kernel of attn_decode.cu (one query token per sequence, partial results
+// (max, sum, unnormalised output) per split, merged by the combine kernel), different inner loop: the
+// query heads that share a KV head are the rows of an m16n8k16 MMA tile (grouped-query attention gives
+// 4..16 such heads; missing rows are zero), so one tile of 64 cached positions costs each warp 32 MMAs
+// instead of some 1800 scalar instructions per 16 positions.  grid = (splits, kv heads, sequences), 4 warps.
+// Cache rows arrive in shared memory through cp.async (two stages); warp w owns positions 16w..16w+15 of
+// every tile and keeps its own running soft-max statistics and output accumulator, the four warps are merged
+// through shared memory at the end.  The scalar kernel stays the choice for short contexts and for head
+// sizes without an instantiation here.
+#include "attn_args.cuh"
+
+namespace {
+
+constexpr int BN = 64, PAD = 8, ROWS = 16;
+
+__device__ __forceinline__ uint32_t smem_addr(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], uint32_t addr) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];" : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t (&r)[4], uint32_t addr) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];" : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+__device__ __forceinline__ void mma_f16(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3]) : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ void cp_async16(void* dst, const void* src) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_addr(dst)), "l"(src) : "memory");
+}
+__device__ __forceinline__ uint32_t pack_half2(float a, float b) {
+    const __half2 h = __floats2half2_rn(a, b);
+    return *reinterpret_cast<const uint32_t*>(&h);
+}
+
+template <int D>
+__global__ void __launch_bounds__(128) attn_decode_mma_kernel(const __grid_constant__ AttnDecodeArgs a) {
+    constexpr int LD = D + PAD;
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    __half* sQ = reinterpret_cast<__half*>(smem_raw);            // [ROWS][LD]
+    __half* sK = sQ + ROWS * LD;                                 // [2][BN][LD]
+    __half* sV = sK + 2 * BN * LD;                               // [2][BN][LD]
+    __shared__ float s_m[4][ROWS], s_l[4][ROWS];
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, tq = lane & 3;
+    const int split = blockIdx.x, kvh = blockIdx.y, b = blockIdx.z;
+    const int group = a.n_heads / a.n_kv_heads;                  // query heads per KV head (<= ROWS, checked by the launcher)
+    const int head0 = kvh * group;
+
+    pdl_launch();
+    pdl_wait();
+    const int qpos = a.positions[b], slot = a.slots[b];
+    const int kv_len = qpos + 1;
+    const int start = (a.window > 0 && kv_len > a.window) ? kv_len - a.window : 0;
+    const int span = kv_len - start;
+    int chunk = (span + a.n_splits - 1) / a.n_splits;
+    chunk = ((chunk + BN - 1) / BN) * BN;
+    const int p0 = start + split * chunk, p1 = min(p0 + chunk, kv_len);
+    const int n_tiles = p1 > p0 ? (p1 - p0 + BN - 1) / BN : 0;
+    const size_t row0 = ((size_t)slot * a.n_kv_heads + kvh) * a.n_ctx;      // first cache row of this (slot, kv head)
+
+    auto load_kv = [&](int tile, int stage) {
+        const int n0 = p0 + tile * BN;
+        __half* dk = sK + stage * BN * LD;
+        __half* dv = sV + stage * BN * LD;
+        if (a.k_scale) {      // q8_0 cache: plain loads, expanded to f16 on the way into shared memory
+            const int8_t* kq = reinterpret_cast<const int8_t*>(a.k_cache) + row0 * D;
+            const int8_t* vq = reinterpret_cast<const int8_t*>(a.v_cache) + row0 * D;
+            const __half* ks = a.k_scale + row0 * (D / 32);
+            const __half* vs = a.v_scale + row0 * (D / 32);
+            for (int c = tid; c < BN * (D / 16); c += 128) {
+                const int r = c / (D / 16), col = (c % (D / 16)) * 16;
+                const int pos = min(n0 + r, a.n_ctx - 1);
+                const uint4 k4 = *(const uint4*)(kq + (size_t)pos * D + col), v4 = *(const uint4*)(vq + (size_t)pos * D + col);
+                const float dkf = __half2float(ks[(size_t)pos * (D / 32) + (col >> 5)]), dvf = __half2float(vs[(size_t)pos * (D / 32) + (col >> 5)]);
+                const uint32_t kw[4] = {k4.x, k4.y, k4.z, k4.w}, vw[4] = {v4.x, v4.y, v4.z, v4.w};
+                uint32_t ko[8], vo[8];
+#pragma unroll
+                for (int i = 0; i < 8; i++) {
+                    const uint32_t kb = kw[i >> 1] >> (16 * (i & 1)), vb = vw[i >> 1] >> (16 * (i & 1));
+                    ko[i] = pack_half2(dkf * (float)(int8_t)(kb & 0xff), dkf * (float)(int8_t)((kb >> 8) & 0xff));
+                    vo[i] = pack_half2(dvf * (float)(int8_t)(vb & 0xff), dvf * (float)(int8_t)((vb >> 8) & 0xff));
+                }
+                *(uint4*)(dk + r * LD + col) = make_uint4(ko[0], ko[1], ko[2], ko[3]);
+                *(uint4*)(dk + r * LD + col + 8) = make_uint4(ko[4], ko[5], ko[6], ko[7]);
+                *(uint4*)(dv + r * LD + col) = make_uint4(vo[0], vo[1], vo[2], vo[3]);
+                *(uint4*)(dv + r * LD + col + 8) = make_uint4(vo[4], vo[5], vo[6], vo[7]);
+            }
+            asm volatile("cp.async.commit_group;" ::: "memory");      // keeps the group counting of the f16 path
+            return;
+        }
+        const __half* kbase = a.k_cache + row0 * D;
+        const __half* vbase = a.v_cache + row0 * D;
+        for (int c = tid; c < BN * (D / 8); c += 128) {
+            const int r = c / (D / 8), col = (c % (D / 8)) * 8;
+            const int pos = min(n0 + r, a.n_ctx - 1);           // rows past the range repeat a valid row (masked below)
+            cp_async16(dk + r * LD + col, kbase + (size_t)pos * D + col);
+            cp_async16(dv + r * LD + col, vbase + (size_t)pos * D + col);
+        }
+        asm volatile("cp.async.commit_group;" ::: "memory");
+    };
+
+    if (n_tiles > 0) load_kv(0, 0);
+    // Q rows: the heads of this KV head, fp32 -> f16, rows beyond the group are zero
+    for (int c = tid; c < ROWS * (D / 4); c += 128) {
+        const int r = c / (D / 4), col = (c % (D / 4)) * 4;
+        float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (r < group) v = *(const float4*)(a.q + ((size_t)b * a.n_heads + head0 + r) * D + col);
+        *reinterpret_cast<uint2*>(sQ + r * LD + col) = make_uint2(pack_half2(v.x, v.y), pack_half2(v.z, v.w));
+    }
+    __syncthreads();
+    uint32_t qf[D / 16][4];
+#pragma unroll
+    for (int kk = 0; kk < D / 16; kk++)
+        ldmatrix_x4(qf[kk], smem_addr(sQ + ((lane & 7) + 8 * ((lane >> 3) & 1)) * LD + kk * 16 + 8 * (lane >> 4)));
+
+    float o[D / 8][4];
+#pragma unroll
+    for (int j = 0; j < D / 8; j++) o[j][0] = o[j][1] = o[j][2] = o[j][3] = 0.f;
+    float m_run[2] = {-1e30f, -1e30f}, l_run[2] = {0.f, 0.f};
+
+    for (int tile = 0; tile < n_tiles; tile++) {
+        const int stage = tile & 1;
+        if (tile + 1 < n_tiles) {
+            load_kv(tile + 1, stage ^ 1);
+            asm volatile("cp.async.wait_group 1;" ::: "memory");
+        } else {
+            asm volatile("cp.async.wait_group 0;" ::: "memory");
+        }
+        __syncthreads();
+        const __half* tk = sK + stage * BN * LD + 16 * warp * LD;       // this warp's 16 positions of the tile
+        const __half* tv = sV + stage * BN * LD + 16 * warp * LD;
+        const int n0 = p0 + tile * BN + 16 * warp;
+
+        float s[2][4];
+        s[0][0] = s[0][1] = s[0][2] = s[0][3] = s[1][0] = s[1][1] = s[1][2] = s[1][3] = 0.f;
+#pragma unroll
+        for (int kk = 0; kk < D / 16; kk++) {
+            uint32_t kb[4];
+            ldmatrix_x4(kb, smem_addr(tk + ((lane & 7) + 8 * (lane >> 4)) * LD + kk * 16 + 8 * ((lane >> 3) & 1)));
+            mma_f16(s[0], qf[kk], kb[0], kb[1]);
+            mma_f16(s[1], qf[kk], kb[2], kb[3]);
+        }
+        // element e of block j: row g + 8 (e >> 1) (a query head), position n0 + 8 j + 2 tq + (e & 1)
+        float mx[2] = {-1e30f, -1e30f};
+        bool ok[2][2];
+#pragma unroll
+        for (int j = 0; j < 2; j++) {
+#pragma unroll
+            for (int e = 0; e < 2; e++) ok[j][e] = n0 + 8 * j + 2 * tq + e < p1;
+#pragma unroll
+            for (int e = 0; e < 4; e++) {
+                float v = s[j][e] * a.scale;
+                if (a.softcap > 0.f) v = a.softcap * tanhf(v / a.softcap);
+                s[j][e] = v;
+                if (ok[j][e & 1]) mx[e >> 1] = fmaxf(mx[e >> 1], v);
+            }
+        }
+        float corr[2];
+#pragma unroll
+        for (int r = 0; r < 2; r++) {
+            mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 1));
+            mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 2));
+            const float m_new = fmaxf(m_run[r], mx[r]);
+            corr[r] = __expf(m_run[r] - m_new);
+            m_run[r] = m_new;
+            l_run[r] *= corr[r];
+        }
+#pragma unroll
+        for (int j = 0; j < 2; j++) {
+#pragma unroll
+            for (int e = 0; e < 4; e++) {
+                const float p = ok[j][e & 1] ? __expf(s[j][e] - m_run[e >> 1]) : 0.f;
+                s[j][e] = p;
+                l_run[e >> 1] += p;
+            }
+        }
+#pragma unroll
+        for (int j = 0; j < D / 8; j++) {
+            o[j][0] *= corr[0]; o[j][1] *= corr[0];
+            o[j][2] *= corr[1]; o[j][3] *= corr[1];
+        }
+        // O += P V: the accumulator fragments of S are the A fragments of P (16 positions = one k step)
+        uint32_t pa[4];
+        pa[0] = pack_half2(s[0][0], s[0][1]);
+        pa[1] = pack_half2(s[0][2], s[0][3]);
+        pa[2] = pack_half2(s[1][0], s[1][1]);
+        pa[3] = pack_half2(s[1][2], s[1][3]);
+#pragma unroll
+        for (int j = 0; j < D / 8; j += 2) {
+            uint32_t vb[4];
+            ldmatrix_x4_trans(vb, smem_addr(tv + ((lane & 7) + 8 * ((lane >> 3) & 1)) * LD + 8 * j + 8 * (lane >> 4)));
+            mma_f16(o[j], pa, vb[0], vb[1]);
+            mma_f16(o[j + 1], pa, vb[2], vb[3]);
+        }
+        __syncthreads();        // everyone is done with this stage before it is overwritten two iterations later
+    }
+
+    // merge the four warps: (max, sum, acc) of every query head through shared memory (the staging area is free now)
+#pragma unroll
+    for (int r = 0; r < 2; r++) {
+        l_run[r] += __shfl_xor_sync(0xffffffffu, l_run[r], 1);
+        l_run[r] += __shfl_xor_sync(0xffffffffu, l_run[r], 2);
+    }
+    float* s_acc = reinterpret_cast<float*>(sK);                 // [4][ROWS][D]
+#pragma unroll
+    for (int r = 0; r < 2; r++) {
+        const int row = g + 8 * r;
+        if (row < group) {
+            float* dst = s_acc + ((size_t)warp * ROWS + row) * D;
+#pragma unroll
+            for (int j = 0; j < D / 8; j++) *reinterpret_cast<float2*>(dst + 8 * j + 2 * tq) = make_float2(o[j][2 * r], o[j][2 * r + 1]);
+            if (tq == 0) {
+                s_m[warp][row] = m_run[r];
+                s_l[warp][row] = l_run[r];
+            }
+        }
+    }
+    __syncthreads();
+    for (int idx = tid; idx < group * D; idx += 128) {
+        const int row = idx / D, d = idx % D;
+        const float mn = fmaxf(fmaxf(s_m[0][row], s_m[1][row]), fmaxf(s_m[2][row], s_m[3][row]));
+        float acc = 0.f, lt = 0.f;
+#pragma unroll
+        for (int w = 0; w < 4; w++) {
+            const float c = __expf(s_m[w][row] - mn);
+            acc += s_acc[((size_t)w * ROWS + row) * D + d] * c;
+            lt += s_l[w][row] * c;
+        }
+        const size_t pi = ((size_t)b * a.n_heads + head0 + row) * a.n_splits + split;
+        a.part_acc[pi * D + d] = acc;
+        if (d == 0) a.part_ml[pi] = make_float2(mn, lt);
+    }
+}
+
+template <int D>
+int launch(const AttnDecodeArgs& a, int nb, int pdl, cudaStream_t st) {
+    constexpr int SMEM = (ROWS + 4 * BN) * (D + PAD) * 2;
+    static PerDeviceOnce once;
+    if (once.first()) cudaFuncSetAttribute(attn_decode_mma_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM);
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(a.n_splits, a.n_kv_heads, nb);
+    cfg.blockDim = dim3(128);
+    cfg.dynamicSmemBytes = SMEM;
+    cfg.stream = st;
+    cudaLaunchAttribute at[1];
+    at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    at[0].val.programmaticStreamSerializationAllowed = pdl ? 1 : 0;
+    cfg.attrs = at;
+    cfg.numAttrs = 1;
+    AttnDecodeArgs copy = a;
+    void* args[] = {&copy};
+    return (int)cudaLaunchKernelExC(&cfg, (const void*)attn_decode_mma_kernel<D>, args);
+}
+
+}  // namespace
+
+int attn_decode_mma_launch(const AttnDecodeArgs& a, int nb, int hd, int pdl, cudaStream_t st) {
+    if (a.n_kv_heads < 1 || a.n_heads % a.n_kv_heads || a.n_heads / a.n_kv_heads > ROWS) return (int)cudaErrorNotSupported;
+    if (hd == 128) return launch<128>(a, nb, pdl, st);
+    if (hd == 64) return launch<64>(a, nb, pdl, st);
+    return (int)cudaErrorNotSupported;
+}

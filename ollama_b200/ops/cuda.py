@@ -345,6 +345,11 @@ def rope_kv(qkv: torch.Tensor, positions: torch.Tensor, slots: torch.Tensor, inv
     return q_out
 
 
+def attn_decode_mode(mode: int) -> None:
+    """Kernel behind :func:`attn_decode`: 1 = tensor-core split-K kernel, 0 = scalar kernel, -1 = by shape (default)."""
+    lib().b2_attn_decode_mode(int(mode))
+
+
 def attn_decode(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, positions: torch.Tensor, slots: torch.Tensor, *,
                 scale: float, n_splits: int, window: int = 0, softcap: float = 0.0, sinks: torch.Tensor | None = None,
                 scratch: tuple[torch.Tensor, torch.Tensor] | None = None, quant_out: bool = True, pdl: bool = False,

@@ -154,8 +154,11 @@ def test_rope_kv(neox, qk_norm, hd, n_rot):
 
 @pytest.mark.parametrize("hd,H,Hkv", [(128, 8, 2), (64, 8, 8), (64, 6, 3), (256, 4, 1), (32, 8, 2)])
 @pytest.mark.parametrize("window,softcap,use_sinks", [(0, 0.0, False), (24, 0.0, True), (0, 30.0, False)])
-def test_attn_decode(hd, H, Hkv, window, softcap, use_sinks):
+@pytest.mark.parametrize("mma", [0, 1])
+def test_attn_decode(hd, H, Hkv, window, softcap, use_sinks, mma, attn_mode):
+    """mma = 1: the tensor-core split-K kernel (head sizes 64 / 128; other sizes fall back to the scalar kernel)."""
     K = _K()
+    attn_mode(mma)
     n_slots, n_ctx, nb = 3, 160, 3
     kc = (torch.randn(n_slots, Hkv, n_ctx, hd) * 0.5).to(torch.float16).cuda()
     vc = (torch.randn(n_slots, Hkv, n_ctx, hd) * 0.5).to(torch.float16).cuda()
@@ -168,10 +171,13 @@ def test_attn_decode(hd, H, Hkv, window, softcap, use_sinks):
         out, qa = K.attn_decode(q, kc, vc, pos, slots, scale=scale, n_splits=n_splits, window=window, softcap=softcap, sinks=sinks)
         for b in range(nb):
             p, s = int(pos[b]), int(slots[b])
-            ref = R.attention(q[b:b + 1].cpu(), kc[s, :, :p + 1].transpose(0, 1).float().cpu(), vc[s, :, :p + 1].transpose(0, 1).float().cpu(),
+            tc = mma and hd in (64, 128)          # the tensor-core kernel multiplies f16 queries and f16 probabilities
+            qr = q[b:b + 1].to(torch.float16).float().cpu() if tc else q[b:b + 1].cpu()
+            ref = R.attention(qr, kc[s, :, :p + 1].transpose(0, 1).float().cpu(), vc[s, :, :p + 1].transpose(0, 1).float().cpu(),
                               torch.tensor([p]), torch.arange(p + 1), scale=scale, window=window, softcap=softcap,
                               sinks=sinks.cpu() if use_sinks else None)
-            assert torch.allclose(out[b].cpu(), ref.reshape(-1), atol=2e-3, rtol=2e-3), (n_splits, b)
+            tol = dict(atol=1e-2, rtol=2e-2) if tc else dict(atol=2e-3, rtol=2e-3)
+            assert torch.allclose(out[b].cpu(), ref.reshape(-1), **tol), (n_splits, b, (out[b].cpu() - ref.reshape(-1)).abs().max())
         deq = (qa.q.cpu().float().view(nb, -1, 32) * qa.ds.cpu()[..., 0:1]).view(nb, -1)
         assert (deq - out.cpu()).abs().max() <= out.abs().max().item() / 127 + 1e-6
 
@@ -210,14 +216,24 @@ def test_attn_prefill(hd, H, Hkv, T, pos0, window, softcap, use_sinks, causal):
     assert torch.allclose(out, ref, atol=1e-2, rtol=2e-2), (out - ref).abs().max()
 
 
+@pytest.fixture
+def attn_mode():
+    """Selects the decode-attention kernel for one test and restores the automatic choice afterwards."""
+    K = _K()
+    yield K.attn_decode_mode
+    K.attn_decode_mode(-1)
+
+
 @pytest.mark.parametrize("hd,H,Hkv", [(128, 8, 2), (64, 6, 3)])
-def test_kv_cache_q8(hd, H, Hkv):
+@pytest.mark.parametrize("mma", [0, 1])
+def test_kv_cache_q8(hd, H, Hkv, mma, attn_mode):
     """q8_0 K/V cache: the rope kernel writes int8 blocks of 32 dims with an f16 scale; both attention kernels expand them.
 
     The written blocks are compared with the fp32 values (error within half a quantisation step), the attention
     kernels with fp32 attention over the dequantised cache.
     """
     K = _K()
+    attn_mode(mma)
     n_slots, n_ctx, slot, T = 2, 192, 1, 150
     g = torch.Generator().manual_seed(hd)
     qkv = torch.randn(T, (H + 2 * Hkv) * hd, generator=g).cuda()
@@ -251,9 +267,10 @@ def test_kv_cache_q8(hd, H, Hkv):
         out, _ = K.attn_decode(qd, kc, vc, dpos, dslots, scale=scale, n_splits=n_splits, k_scale=ks, v_scale=vs)
         for b in range(3):
             p = int(dpos[b])
-            ref = R.attention(qd[b:b + 1].cpu(), kd[slot, :, :p + 1].transpose(0, 1), vd[slot, :, :p + 1].transpose(0, 1),
-                              torch.tensor([p]), torch.arange(p + 1), scale=scale)
-            assert torch.allclose(out[b].cpu(), ref.reshape(-1), atol=2e-3, rtol=2e-3), (n_splits, b)
+            ref = R.attention(qd[b:b + 1].to(torch.float16).float().cpu() if mma else qd[b:b + 1].cpu(), kd[slot, :, :p + 1].transpose(0, 1),
+                              vd[slot, :, :p + 1].transpose(0, 1), torch.tensor([p]), torch.arange(p + 1), scale=scale)
+            tol = dict(atol=1e-2, rtol=2e-2) if mma else dict(atol=2e-3, rtol=2e-3)
+            assert torch.allclose(out[b].cpu(), ref.reshape(-1), **tol), (n_splits, b)
     # prefill over the quantised cache
     out = K.attn_prefill(q, kc, vc, slot, 0, T, scale, True, 0, 0.0, None, k_scale=ks, v_scale=vs).float().cpu().view(T, H, hd)
     ref = R.attention(q.to(torch.float16).float().cpu(), kd[slot, :, :T].transpose(0, 1), vd[slot, :, :T].transpose(0, 1),
