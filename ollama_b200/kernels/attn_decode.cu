@@ -276,9 +276,10 @@ static cudaError_t launch1(const void* fn, dim3 grid, dim3 block, void** args, c
     return cudaLaunchKernelExC(&cfg, fn, args);
 }
 
-// Tensor-core kernel or scalar kernel: B200_ATTN_MMA = 1 / 0 forces the choice; otherwise grouped-query models with
-// an allocated context of at least B200_ATTN_MMA_CTX positions (default 2048) take the tensor-core kernel.
-static int g_mma_mode = -2, g_mma_min_ctx = 2048;      // -2: not read from the environment yet, -1: automatic
+// Tensor-core kernel or scalar kernel: B200_ATTN_MMA = 1 / 0 forces the choice; otherwise grouped-query models
+// (two or more query heads per KV head, head size 64 or 128) take the tensor-core kernel.  Measured on Llama-8B
+// (4 heads per KV head): 443 against 428 tok/s at 0.6 k tokens of context, 383 against 329 at 6.2 k.
+static int g_mma_mode = -2, g_mma_min_ctx = 0;      // -2: not read from the environment yet, -1: automatic
 
 static bool use_mma(const AttnDecodeArgs& a, int hd) {
     if (g_mma_mode == -2) {

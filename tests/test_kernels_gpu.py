@@ -182,6 +182,40 @@ def test_attn_decode(hd, H, Hkv, window, softcap, use_sinks, mma, attn_mode):
         assert (deq - out.cpu()).abs().max() <= out.abs().max().item() / 127 + 1e-6
 
 
+@pytest.mark.parametrize("hd,H,Hkv", [(128, 32, 8), (64, 16, 2), (128, 16, 1)])
+@pytest.mark.parametrize("q8", [False, True])
+def test_attn_decode_tensor_core_long_context(hd, H, Hkv, q8, attn_mode):
+    """Many tiles per split, several splits, 4 / 8 / 16 heads per KV head: the tensor-core kernel against the scalar one
+    and against itself (two runs give the same bits: no dependence on timing)."""
+    K = _K()
+    n_slots, n_ctx, nb = 2, 4096, 2
+    g = torch.Generator().manual_seed(hd + H)
+    kf = torch.randn(n_slots, Hkv, n_ctx, hd, generator=g) * 0.5
+    vf = torch.randn(n_slots, Hkv, n_ctx, hd, generator=g) * 0.5
+    ks = vs = None
+    if q8:
+        def quant(x):
+            b = x.view(n_slots, Hkv, n_ctx, hd // 32, 32)
+            d = (b.abs().amax(-1, keepdim=True) / 127).to(torch.float16)
+            qv = torch.where(d > 0, torch.round(b / d.float().clamp_min(1e-30)), torch.zeros_like(b)).clamp(-127, 127).to(torch.int8)
+            return qv.view(n_slots, Hkv, n_ctx, hd).cuda(), d.squeeze(-1).cuda()
+        (kc, ks), (vc, vs) = quant(kf), quant(vf)
+    else:
+        kc, vc = kf.to(torch.float16).cuda(), vf.to(torch.float16).cuda()
+    q = torch.randn(nb, H, hd, generator=g).cuda()
+    pos = torch.tensor([4001, 130], dtype=torch.int32).cuda()
+    slots = torch.tensor([1, 0], dtype=torch.int32).cuda()
+    scale = 1 / math.sqrt(hd)
+    for n_splits in (1, 8):
+        attn_mode(0)
+        ref, _ = K.attn_decode(q, kc, vc, pos, slots, scale=scale, n_splits=n_splits, k_scale=ks, v_scale=vs)
+        attn_mode(1)
+        a, _ = K.attn_decode(q, kc, vc, pos, slots, scale=scale, n_splits=n_splits, k_scale=ks, v_scale=vs)
+        b, _ = K.attn_decode(q, kc, vc, pos, slots, scale=scale, n_splits=n_splits, k_scale=ks, v_scale=vs)
+        assert torch.equal(a, b)
+        assert torch.allclose(a, ref, atol=3e-3, rtol=2e-2), (a - ref).abs().max()
+
+
 def test_embed_and_argmax():
     K = _K()
     qw, _ = _weight(GGMLType.Q6_K, 300, 512)
@@ -364,7 +398,7 @@ def test_moe_route_kernel():
 
 @pytest.mark.parametrize("spec,ft", [("tiny-qwen3", "Q4_K_M"), ("tiny-gemma3", "Q8_0"), ("tiny-qwen2", "F16"), ("tiny-gemma2", "Q4_K_M"),
                                      ("tiny-qwen3moe", "Q4_K_M"), ("tiny-gpt-oss", "MXFP4"), ("tiny-mixtral", "Q8_0")])
-def test_engine_matches_reference_graph(tmp_path, spec, ft):
+def test_engine_matches_reference_graph(tmp_path, spec, ft, attn_mode):
     """Whole-model check: prefill logits and 6 decode steps of the sm_100a engine vs the fp32 reference graph."""
     from ollama_b200.engine.b200 import B200Backend
     from ollama_b200.engine.backend import TorchBackend, open_model
@@ -391,8 +425,12 @@ def test_engine_matches_reference_graph(tmp_path, spec, ft):
     a = eng.decode_argmax([1], [tok], [len(prompt) + 6])
     eng2 = eng.decode([1], [tok], [len(prompt) + 6])
     assert a[0] == int(eng2[0].argmax())
-    # the single-launch attention (last CTA of a head group merges the splits) gives the same logits
-    eng.fuse_attn_combine, eng.use_graphs = True, False
+    # the single-launch attention (last CTA of a head group merges the splits) gives the same logits as the two-launch
+    # form with the same (scalar) inner loop
+    attn_mode(0)
+    eng.use_graphs = False
+    eng2 = eng.decode([1], [tok], [len(prompt) + 6])
+    eng.fuse_attn_combine = True
     eng3 = eng.decode([1], [tok], [len(prompt) + 6])
     assert torch.allclose(eng3, eng2, atol=1e-4 * eng2.abs().max().item() + 1e-5)
 
