@@ -1,8 +1,8 @@
 """Hugging Face checkpoint directory (config.json + *.safetensors + tokenizer files) -> GGUF.
 
 Covers the decoder families this runtime executes: Llama / Mistral, Mixtral, Qwen2, Qwen3, Qwen3-MoE,
-Gemma, Gemma 2 and Gemma 3 (text tower), gpt-oss (16-bit expert tensors; checkpoints that ship the experts as
-packed MXFP4 blocks + scales are not read).  Mirrors convert/convert.go:279-379 (dispatch by
+Gemma, Gemma 2 and Gemma 3 (text tower), gpt-oss (16-bit expert tensors, or experts packed as
+MXFP4 blocks + scales, which are re-ordered into GGML MXFP4 blocks without re-quantising).  Mirrors convert/convert.go:279-379 (dispatch by
 ``architectures[0]``), convert/convert_llama.go (key/value metadata, the Q/K row permutation that turns the
 checkpoint's half-split rotary layout into the interleaved one llama-arch GGUFs use:189-232),
 convert/convert_qwen3.go, convert_gemma*.go, convert_mixtral.go (expert stacking) and convert/tokenizer.go
@@ -67,6 +67,9 @@ _RULES: list[tuple[str, str]] = [
     (_LAYER + r"mlp\.experts\.gate_up_proj_bias", "blk.{n}.ffn_gate_up_exps.bias"),
     (_LAYER + r"mlp\.experts\.down_proj", "blk.{n}.ffn_down_exps.weight@T"),
     (_LAYER + r"mlp\.experts\.down_proj_bias", "blk.{n}.ffn_down_exps.bias"),
+    # gpt-oss checkpoints with MXFP4-packed experts: [expert, out, in / 32, 16] nibble bytes + [expert, out, in / 32] e8m0 scales
+    (_LAYER + r"mlp\.experts\.gate_up_proj_(blocks|scales)", "blk.{n}.ffn_gate_up_exps.{1}"),
+    (_LAYER + r"mlp\.experts\.down_proj_(blocks|scales)", "blk.{n}.ffn_down_exps.{1}"),
 ]
 # post_attention_layernorm is the FFN pre-norm for llama/qwen but a sandwich post-norm for gemma 2/3
 _RULES_PRENORM = [(_LAYER + r"post_attention_layernorm\.weight", "blk.{n}.ffn_norm.weight")]
@@ -283,6 +286,23 @@ def _encode(t: torch.Tensor, name: str, outtype: str) -> tuple[GGMLType, torch.T
     return want, quants.quantize(t.float(), want)
 
 
+def mxfp4_blocks(blocks: torch.Tensor, scales: torch.Tensor) -> torch.Tensor:
+    """Packed experts of a gpt-oss checkpoint -> GGML MXFP4 blocks (uint8 [..., in / 32, 17]).
+
+    The checkpoint keeps consecutive elements in the two nibbles of a byte (element 2i low, 2i + 1 high); a GGML block
+    keeps elements 0..15 in the low and 16..31 in the high nibbles, preceded by the e8m0 scale byte
+    (convert/convert_gptoss.go:215-262).
+    """
+    if blocks.shape[-1] != 16 or blocks.shape[:-1] != scales.shape:
+        raise ConvertError(f"MXFP4 blocks {tuple(blocks.shape)} do not match scales {tuple(scales.shape)}")
+    blocks, scales = blocks.to(torch.uint8), scales.to(torch.uint8)
+    a, b = blocks[..., :8], blocks[..., 8:]
+    even = (a & 0x0F) | ((b & 0x0F) << 4)          # elements 2j and 16 + 2j
+    odd = (a >> 4) | (b & 0xF0)                    # elements 2j + 1 and 17 + 2j
+    nib = torch.stack([even, odd], -1).reshape(*blocks.shape[:-1], 16)
+    return torch.cat([scales.unsqueeze(-1), nib], -1).contiguous()
+
+
 def convert_tensors(src: ModelDir, cfg: dict[str, Any], arch: str, outtype: str = "auto",
                     progress: Callable[[str], None] | None = None) -> Iterator[WriteTensor]:
     c = cfg.get("text_config", cfg) if arch == "gemma3" else cfg
@@ -312,8 +332,27 @@ def convert_tensors(src: ModelDir, cfg: dict[str, Any], arch: str, outtype: str 
         dt, raw = _encode(t, out, outtype)
         return WriteTensor(out, tuple(reversed(t.shape)), dt, raw.cpu().numpy())
 
+    def emit_mxfp4(out: str, raw: torch.Tensor) -> WriteTensor:
+        if progress:
+            progress(out)
+        e, rows, nb, _ = raw.shape
+        return WriteTensor(out, (nb * 32, rows, e), GGMLType.MXFP4, raw.reshape(-1).cpu().numpy())
+
     for out in sorted(names, key=_order):
         if out == "output.weight" and tied:
+            continue
+        if out.endswith(".scales"):
+            continue                                   # consumed together with the blocks
+        if out.endswith(".blocks"):
+            base = out[:-len(".blocks")]
+            if base + ".scales" not in names:
+                raise ConvertError(f"{names[out]} has no scales tensor")
+            raw = mxfp4_blocks(src.tensor(names[out]), src.tensor(names[base + ".scales"]))
+            if "gate_up" in base:                      # even rows gate, odd rows up
+                yield emit_mxfp4(base.replace("gate_up", "gate") + ".weight", raw[:, 0::2].contiguous())
+                yield emit_mxfp4(base.replace("gate_up", "up") + ".weight", raw[:, 1::2].contiguous())
+            else:
+                yield emit_mxfp4(base + ".weight", raw)
             continue
         t = src.tensor(names[out])
         if out.endswith("@T"):                         # stored [expert, in, out]

@@ -126,3 +126,55 @@ def test_create_from_checkpoint_directory_through_the_api(tmp_path, monkeypatch)
         assert info["details"]["family"] == "llama" and info["model_info"]["llama.block_count"] == 2
         out = c.post("/api/generate", json={"model": "conv", "prompt": "abab", "stream": False, "options": {"num_predict": 4, "temperature": 0}}).json()
         assert out["done"] and out["eval_count"] == 4
+
+
+def test_gpt_oss_checkpoint_with_packed_mxfp4_experts(tmp_path):
+    """Experts shipped as MXFP4 blocks + scales are re-ordered into GGML blocks without re-quantising: the converted
+    model gives the logits of transformers running the same (dequantised) expert weights."""
+    transformers = pytest.importorskip("transformers")
+    st = pytest.importorskip("safetensors.torch")
+    from transformers.integrations.mxfp4 import _convert_moe_packed_tensors
+    from ollama_b200.gguf import quants
+    from ollama_b200.gguf.types import GGMLType
+    torch.manual_seed(0)
+    cfg = transformers.GptOssConfig(vocab_size=64, hidden_size=64, intermediate_size=32, num_hidden_layers=2, num_attention_heads=4,
+                                    num_key_value_heads=2, head_dim=16, num_local_experts=4, num_experts_per_tok=2, sliding_window=8,
+                                    max_position_embeddings=128, rope_theta=150000.0, tie_word_embeddings=False)
+    model = transformers.GptOssForCausalLM(cfg).float().eval()
+    src = tmp_path / "hf"
+    model.save_pretrained(src, safe_serialization=True)
+    _tiny_tokenizer(str(src))
+    files = [n for n in os.listdir(src) if n.endswith(".safetensors")]
+    if len(files) != 1:
+        pytest.skip("expected one safetensors file")
+    tensors = st.load_file(str(src / files[0]))
+    packed = {}
+    for name in [n for n in tensors if n.endswith(("experts.gate_up_proj", "experts.down_proj"))]:
+        w = tensors.pop(name).float().transpose(1, 2).contiguous()          # [expert, out, in]
+        e, rows, k = w.shape
+        blk = quants.quantize(w, GGMLType.MXFP4).view(e, rows, k // 32, 17)
+        deq = quants.dequantize(blk.reshape(-1), GGMLType.MXFP4).view(e, rows, k)
+        nib = blk[..., 1:]
+        lo, hi = nib[..., 0::2], nib[..., 1::2]                             # GGML bytes 2j and 2j + 1
+        a = (lo & 0x0F) | ((hi & 0x0F) << 4)                                # checkpoint bytes 0..7: elements (2j, 2j + 1)
+        b = (lo >> 4) | (hi & 0xF0)                                         # checkpoint bytes 8..15: elements (16 + 2j, 17 + 2j)
+        blocks, scales = torch.cat([a, b], -1).contiguous(), blk[..., 0].contiguous()
+        # the library's own unpacking of this layout gives the same values ([expert, in, out])
+        assert torch.equal(_convert_moe_packed_tensors(blocks, scales, dtype=torch.float32), deq.transpose(1, 2))
+        packed[name + "_blocks"], packed[name + "_scales"] = blocks, scales
+        with torch.no_grad():
+            dict(model.named_parameters())[name].copy_(deq.transpose(1, 2))
+    tensors.update(packed)
+    st.save_file(tensors, str(src / files[0]), metadata={"format": "pt"})
+    out = str(tmp_path / "m.gguf")
+    convert_hf(str(src), out, outtype="f32")
+    from ollama_b200.engine.backend import TorchBackend, open_model
+    g = open_model(out)
+    assert g.tensors["blk.0.ffn_gate_exps.weight"].dtype == GGMLType.MXFP4 and g.tensors["blk.1.ffn_down_exps.weight"].dtype == GGMLType.MXFP4
+    be = TorchBackend(g, "cpu")
+    be.alloc(1, 128)
+    ids = torch.randint(0, 64, (40,), generator=torch.Generator().manual_seed(1))
+    with torch.no_grad():
+        ref = model(ids[None]).logits[0, -1]
+    got = be.prefill(0, ids.tolist(), 0)
+    assert torch.allclose(got, ref, atol=2e-4, rtol=1e-3), (got - ref).abs().max()
