@@ -202,6 +202,67 @@ def _pretokenizer(tj: dict[str, Any]) -> str:
     return "default"
 
 
+_SPM_FORCED_CONTROL = ("<end_of_turn>", "<start_of_turn>", "<start_function_declaration>", "<end_function_declaration>",
+                       "<start_function_call>", "<end_function_call>", "<start_function_response>", "<end_function_response>", "<escape>")
+
+
+def _spm_vocabulary(path: str, vocab_size: int) -> dict[str, Any]:
+    """Vocabulary of a SentencePiece ``tokenizer.model`` (convert/tokenizer_spm.go:18-100): pieces with their scores;
+    unknown / control / unused / byte pieces keep their type, everything else is normal except the additional special
+    tokens of ``special_tokens_map.json`` (and a fixed list of gemma markers), which become control tokens;
+    ``added_tokens.json`` appends user-defined tokens with score -1000."""
+    try:
+        import sentencepiece as spm
+    except ImportError:
+        raise ConvertError("tokenizer.model needs the sentencepiece package") from None
+    sp = spm.SentencePieceProcessor(model_file=os.path.join(path, "tokenizer.model"))
+    extra: set[str] = set(_SPM_FORCED_CONTROL)
+    stm = os.path.join(path, "special_tokens_map.json")
+    if os.path.exists(stm):
+        with open(stm, encoding="utf-8") as f:
+            for t in json.load(f).get("additional_special_tokens") or []:
+                extra.add(t if isinstance(t, str) else t.get("content", ""))
+    tokens, scores, types = [], [], []
+    for i in range(sp.get_piece_size()):
+        piece = sp.id_to_piece(i)
+        tokens.append(piece)
+        scores.append(float(sp.get_score(i)))
+        if sp.is_unknown(i):
+            types.append(2)
+        elif sp.is_control(i):
+            types.append(3)
+        elif sp.is_unused(i):
+            types.append(5)
+        elif sp.is_byte(i):
+            types.append(6)
+        else:
+            types.append(3 if piece in extra else 1)
+    at = os.path.join(path, "added_tokens.json")
+    if os.path.exists(at):
+        with open(at, encoding="utf-8") as f:
+            added = sorted(((i, t) for t, i in json.load(f).items()))
+        for i, t in added:
+            if i < len(tokens):
+                if tokens[i] != t:
+                    raise ConvertError(f"token mismatch: {t} != {tokens[i]} at pos [{i}]")
+                continue
+            if i != len(tokens):
+                raise ConvertError(f"invalid token id: [{i}] as pos [{len(tokens)}]")
+            tokens.append(t)
+            scores.append(-1000.0)
+            types.append(4)
+    for i in range(len(tokens), vocab_size):          # the embedding matrix may be padded beyond the vocabulary
+        tokens.append(f"[PAD{i}]")
+        scores.append(-1000.0)
+        types.append(5)
+    out = {"tokenizer.ggml.model": "llama", "tokenizer.ggml.tokens": tokens, "tokenizer.ggml.scores": scores,
+           "tokenizer.ggml.token_type": types}
+    for key, i in (("bos", sp.bos_id()), ("eos", sp.eos_id()), ("unknown", sp.unk_id()), ("padding", sp.pad_id())):
+        if i >= 0:
+            out[f"tokenizer.ggml.{key}_token_id"] = int(i)
+    return out
+
+
 def tokenizer_kv(path: str, vocab_size: int) -> dict[str, Any]:
     kv: dict[str, Any] = {}
     tj_path = os.path.join(path, "tokenizer.json")
@@ -240,8 +301,11 @@ def tokenizer_kv(path: str, vocab_size: int) -> dict[str, Any]:
                                                             for nz in [tj.get("normalizer") or {}])
         kv["tokenizer.ggml.tokens"] = tokens
         kv["tokenizer.ggml.token_type"] = types
+    elif os.path.exists(os.path.join(path, "tokenizer.model")):
+        kv.update(_spm_vocabulary(path, vocab_size))
+        vocab = {t: i for i, t in enumerate(kv["tokenizer.ggml.tokens"])}
     else:
-        raise ConvertError("tokenizer.json not found (SentencePiece .model files need the `sentencepiece` converter path)")
+        raise ConvertError("neither tokenizer.json nor tokenizer.model found")
 
     def tok_id(key: str) -> int | None:
         v = tc.get(key)

@@ -178,3 +178,34 @@ def test_gpt_oss_checkpoint_with_packed_mxfp4_experts(tmp_path):
         ref = model(ids[None]).logits[0, -1]
     got = be.prefill(0, ids.tolist(), 0)
     assert torch.allclose(got, ref, atol=2e-4, rtol=1e-3), (got - ref).abs().max()
+
+
+def test_sentencepiece_model_file_vocabulary(tmp_path):
+    """A checkpoint that ships only ``tokenizer.model``: pieces, scores and piece types come from the SentencePiece model,
+    added tokens are appended, and the resulting tokenizer encodes like SentencePiece itself."""
+    spm = pytest.importorskip("sentencepiece")
+    from ollama_b200.convert.hf import tokenizer_kv
+    from ollama_b200.text.tokenizer import SPMTokenizer, tokenizer_from_gguf
+    corpus = tmp_path / "corpus.txt"
+    words = "the quick brown fox jumps over the lazy dog while reading tokenizer models about byte fallback and pieces".split()
+    corpus.write_text("\n".join(" ".join(words[(i * 7 + j) % len(words)] for j in range(9)) for i in range(400)))
+    spm.SentencePieceTrainer.train(input=str(corpus), model_prefix=str(tmp_path / "tokenizer"), vocab_size=320, model_type="bpe",
+                                   byte_fallback=True, character_coverage=1.0, bos_id=1, eos_id=2, unk_id=0, pad_id=-1,
+                                   user_defined_symbols=["<start_of_turn>"], minloglevel=2)
+    (tmp_path / "added_tokens.json").write_text(json.dumps({"<extra_a>": 320, "<extra_b>": 321}))
+    (tmp_path / "tokenizer_config.json").write_text(json.dumps({"bos_token": "<s>", "eos_token": {"content": "</s>"}, "add_bos_token": True}))
+    kv = tokenizer_kv(str(tmp_path), 324)
+    sp = spm.SentencePieceProcessor(model_file=str(tmp_path / "tokenizer.model"))
+    toks, types, scores = kv["tokenizer.ggml.tokens"], kv["tokenizer.ggml.token_type"], kv["tokenizer.ggml.scores"]
+    assert kv["tokenizer.ggml.model"] == "llama" and len(toks) == 324 and toks[:3] == ["<unk>", "<s>", "</s>"] and types[:3] == [2, 3, 3]
+    assert types[toks.index("<0x41>")] == 6 and types[toks.index("<start_of_turn>")] in (3, 4) and toks[320:322] == ["<extra_a>", "<extra_b>"]
+    assert types[320:] == [4, 4, 5, 5] and scores[320] == -1000.0 and scores[10] == sp.get_score(10)
+    assert kv["tokenizer.ggml.bos_token_id"] == 1 and kv["tokenizer.ggml.eos_token_id"] == 2 and kv["tokenizer.ggml.add_bos_token"] is True
+    tk = tokenizer_from_gguf(kv)
+    assert isinstance(tk, SPMTokenizer)
+    for text in ("the quick brown fox", "reading about pieces and models", "unseen wörd ☃ 42"):
+        assert tk.encode(text, add_special=False) == sp.encode(text), text
+        assert tk.decode(tk.encode(text, add_special=False)).strip() == text
+    (tmp_path / "added_tokens.json").write_text(json.dumps({"<gap>": 400}))
+    with pytest.raises(Exception, match="invalid token id"):
+        tokenizer_kv(str(tmp_path), 324)
