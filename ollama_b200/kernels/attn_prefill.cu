@@ -266,10 +266,12 @@ int launch(const AttnPrefillArgs& a, cudaStream_t st) {
 
 }  // namespace
 
-// head_dim 64 or 128 (others: cudaErrorNotSupported).  Returns a cudaError_t value.
+// head_dim 32, 64, 128 or 256 (others: cudaErrorNotSupported).  Returns a cudaError_t value.
 B2_API int b2_attn_prefill(const AttnPrefillArgs* a, int head_dim, cudaStream_t st) {
     if (a->T < 1 || a->H < 1 || a->Hkv < 1 || a->H % a->Hkv || a->kv_len < 1 || a->kv_len > a->n_ctx) return (int)cudaErrorInvalidValue;
     if (head_dim == 128) return launch<128>(*a, st);
     if (head_dim == 64) return launch<64>(*a, st);
+    if (head_dim == 256) return launch<256>(*a, st);      // gemma family; 255 registers with a 96-byte spill
+    if (head_dim == 32) return launch<32>(*a, st);
     return (int)cudaErrorNotSupported;
 }

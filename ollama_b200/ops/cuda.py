@@ -497,7 +497,7 @@ class AttnPrefillArgs(C.Structure):
                 ("k_scale", C.c_void_p), ("v_scale", C.c_void_p)]
 
 
-ATTN_PREFILL_HEAD_DIMS = (64, 128)
+ATTN_PREFILL_HEAD_DIMS = (32, 64, 128, 256)
 
 
 def attn_prefill(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, slot: int, pos0: int, kv_len: int, scale: float,

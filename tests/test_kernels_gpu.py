@@ -228,7 +228,7 @@ def test_embed_and_argmax():
     assert K.argmax(lg).cpu().tolist() == lg.argmax(-1).cpu().tolist()
 
 
-@pytest.mark.parametrize("hd,H,Hkv", [(128, 8, 2), (64, 4, 4), (64, 6, 1)])
+@pytest.mark.parametrize("hd,H,Hkv", [(128, 8, 2), (64, 4, 4), (64, 6, 1), (256, 4, 2), (32, 8, 2)])
 @pytest.mark.parametrize("T,pos0,window,softcap,use_sinks,causal", [(150, 0, 0, 0.0, False, True), (70, 131, 48, 0.0, True, True),
                                                                     (64, 64, 0, 30.0, False, True), (33, 0, 0, 0.0, False, False)])
 def test_attn_prefill(hd, H, Hkv, T, pos0, window, softcap, use_sinks, causal):
@@ -258,7 +258,7 @@ def attn_mode():
     K.attn_decode_mode(-1)
 
 
-@pytest.mark.parametrize("hd,H,Hkv", [(128, 8, 2), (64, 6, 3)])
+@pytest.mark.parametrize("hd,H,Hkv", [(128, 8, 2), (64, 6, 3), (256, 4, 2), (32, 8, 2)])
 @pytest.mark.parametrize("mma", [0, 1])
 def test_kv_cache_q8(hd, H, Hkv, mma, attn_mode):
     """q8_0 K/V cache: the rope kernel writes int8 blocks of 32 dims with an f16 scale; both attention kernels expand them.
