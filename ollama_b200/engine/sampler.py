@@ -142,8 +142,9 @@ class Sampler:
             row = logits.reshape(1, -1)
             if row.dtype != torch.float32 or not row.is_contiguous():
                 row = row.float().contiguous()
-            tok = int(K.sample(row, [u], p.top_k, p.top_p, p.min_p, p.temperature, [hist], p.repeat_penalty, p.frequency_penalty,
-                               p.presence_penalty)[0].item())
+            with torch.cuda.device(row.device):      # a pipelined model keeps its logits on the last stage's GPU
+                tok = int(K.sample(row, [u], p.top_k, p.top_p, p.min_p, p.temperature, [hist], p.repeat_penalty, p.frequency_penalty,
+                                   p.presence_penalty)[0].item())
         else:
             idx, probs = self.distribution(logits)
             j = int(torch.multinomial(probs.cpu(), 1, generator=self.gen).item())
