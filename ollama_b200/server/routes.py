@@ -103,6 +103,8 @@ class Server:
             Route("/api/signout", self.cloud_stub, methods=["POST"]),
             Route("/api/experimental/web_search", self.cloud_stub, methods=["POST"]),
             Route("/api/experimental/web_fetch", self.cloud_stub, methods=["POST"]),
+            Route("/api/experimental/model-recommendations", self.cloud_stub, methods=["GET"]),
+            Route("/api/user/keys/{key:path}", self.cloud_stub, methods=["DELETE"]),
         ]
         from .openai import openai_routes
         from .anthropic import anthropic_routes
