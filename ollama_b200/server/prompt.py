@@ -2,7 +2,7 @@
 
 ``chat_prompt`` renders the conversation and, when it does not fit ``num_ctx``, drops the oldest
 messages while always keeping the system messages and the latest message (server/prompt.go:23-92).
-Rendering precedence (server/routes.go:2357-2385, server/images.go:322-339): harmony for gpt-oss, the
+Rendering precedence (server/routes.go:2357-2385, server/images.go:322-339): a built-in RENDERER, harmony for gpt-oss, the
 Modelfile Go TEMPLATE, the GGUF Jinja chat template, otherwise the bare prompt.
 """
 from __future__ import annotations
@@ -45,10 +45,10 @@ class PromptRenderer:
         return self.jinja.raw if self.jinja is not None else ""
 
     def render_chat(self, messages: list[dict[str, Any]], tools: list[dict[str, Any]] | None = None, think: Any = None) -> str:
-        if self.is_harmony:
-            return harmony.render_prompt(messages, tools, think, self.names)
         if self.builtin is not None:
             return self.builtin(messages, tools, think)
+        if self.is_harmony:
+            return harmony.render_prompt(messages, tools, think, self.names)
         if self.go_template is not None:
             level = think if isinstance(think, str) else ""
             return self.go_template.execute(messages=messages, tools=tools, think=bool(think) if think is not None else False,
