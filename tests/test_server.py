@@ -125,6 +125,23 @@ def test_list_and_show_caches(client):
     assert not any(m["name"] == "tiny3:latest" for m in client.get("/api/tags").json()["models"])
 
 
+def test_builtin_renderer_and_parser_from_the_model_config(client):
+    r = client.post("/api/create", json={"model": "coder", "from": "tiny", "renderer": "qwen3-coder", "parser": "qwen3-coder", "stream": False})
+    assert r.status_code == 200
+    s = client.post("/api/show", json={"model": "coder"}).json()
+    assert s["renderer"] == "qwen3-coder" and s["parser"] == "qwen3-coder" and "tools" in s["capabilities"]
+    assert "RENDERER qwen3-coder" in s["modelfile"] and "PARSER qwen3-coder" in s["modelfile"]
+    tools = [{"type": "function", "function": {"name": "f", "parameters": {"type": "object", "properties": {"x": {"type": "integer"}}}}}]
+    d = client.post("/api/chat", json={"model": "coder", "messages": [{"role": "user", "content": "hi"}], "tools": tools,
+                                       "_debug_render_only": True}).json()
+    p = d["_debug_info"]["rendered_template"]
+    assert p.startswith("<|im_start|>system\nYou are Qwen") and "<function>\n<name>f</name>" in p and p.endswith("<|im_start|>user\nhi<|im_end|>\n<|im_start|>assistant\n")
+    # the request still runs end to end with the built-in parser in the stream
+    j = client.post("/api/chat", json={"model": "coder", "messages": [{"role": "user", "content": "<t400>"}], "tools": tools, "stream": False,
+                                       "options": {"num_predict": 4}}).json()
+    assert j["done"] and j["eval_count"] == 4 and "content" in j["message"]
+
+
 def test_create_from_existing_model(client):
     r = client.post("/api/create", json={"model": "child", "from": "tiny", "system": "be brief", "parameters": {"stop": ["<t1>"]},
                                          "stream": False})
