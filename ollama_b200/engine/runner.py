@@ -146,6 +146,8 @@ class Runner:
 
     # -- public calls -------------------------------------------------------------------------------
     def ping(self) -> bool:
+        if self._tp_group is not None and not self._tp_group.alive():
+            return False          # a follower process of the tensor-parallel group is gone: the scheduler reloads the model
         return not self.closed and self.thread.is_alive() and self.error is None
 
     def tokenize(self, text: str, add_special: bool = False, parse_special: bool = True) -> list[int]:

@@ -101,6 +101,11 @@ class TPGroup:
             raise
         self.backend = TPLeader(be, TPControl(0, world, tr))
 
+    def alive(self) -> bool:
+        """Every follower process is still running (the runner's ``ping`` and with it the scheduler's reload check use this,
+        the way the reference asks a runner process for its health: server/sched.go needsReload)."""
+        return all(p.is_alive() for p in self.procs)
+
     def close(self) -> None:
         try:
             self.backend.close()

@@ -156,3 +156,28 @@ def test_pipe_transport_carries_rendezvous_and_call_records(tmp_path):
         assert p.exitcode == 0
     for r in (1, 2):
         assert json.load(open(tmp_path / f"f{r}.json")) == log
+
+
+def test_runner_ping_follows_the_follower_processes():
+    """A follower process that is gone makes the runner unhealthy, so that the scheduler's reload check replaces it."""
+    from ollama_b200.engine.runner import Runner
+    from ollama_b200.parallel.launcher import TPGroup
+
+    class _Proc:
+        def __init__(self, alive):
+            self._alive = alive
+
+        def is_alive(self):
+            return self._alive
+
+    grp = TPGroup.__new__(TPGroup)
+    grp.procs = [_Proc(True), _Proc(True)]
+    assert grp.alive()
+    r = Runner.__new__(Runner)
+    r.closed, r.error, r._tp_group = False, None, grp
+    r.thread = _Proc(True)
+    assert r.ping()
+    grp.procs[1]._alive = False
+    assert not grp.alive() and not r.ping()
+    r._tp_group = None
+    assert r.ping()
