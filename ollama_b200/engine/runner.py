@@ -15,6 +15,8 @@ MemorySize ...).  Semantics kept from there:
 """
 from __future__ import annotations
 
+import contextlib
+import os
 import queue
 import threading
 import time
@@ -96,6 +98,9 @@ class _Seq:
         self.text_len = 0
         self.t_prefill = 0.0
         self.t_decode = 0.0
+        self.t_submit = time.perf_counter()
+        self.t_queue = 0.0              # waiting for a slot
+        self.t_first = 0.0              # submit -> first sampled token
         self.n_decoded = 0
         self.n_prompt_eval = 0
         self.cancelled = False
@@ -141,6 +146,12 @@ class Runner:
         self.closed = False
         self.error: str | None = None
         self.load_duration = time.time() - t0
+        # totals since load, written by the loop thread only (read by /metrics)
+        self.stats: dict[str, float] = {k: 0 for k in (
+            "requests", "prompt_tokens", "cached_prompt_tokens", "generated_tokens", "queue_seconds", "prefill_seconds",
+            "decode_seconds", "ttft_seconds", "decode_steps", "decode_step_sequences", "context_shifts")}
+        self.done_reasons: dict[str, int] = {}
+        self._nvtx = bool(os.environ.get("B200_NVTX")) and str(getattr(self.backend, "device", "cpu")).startswith("cuda")
         self.thread = threading.Thread(target=self._loop, name="runner-loop", daemon=True)
         self.thread.start()
 
@@ -299,6 +310,7 @@ class Runner:
             if seq.req.embedding or not self.cfg.causal:
                 reuse = 0
             seq.slot, seq.n_past, seq.cached = best, reuse, reuse
+            seq.t_queue = time.perf_counter() - seq.t_submit
             del self.slot_tokens[best][reuse:]
             self.slot_seq[best] = seq
             seq.state = "prefill"
@@ -323,7 +335,17 @@ class Runner:
         if dec:
             self._decode(dec)
 
+    def _range(self, name: str):
+        """NVTX range around a phase of the loop when B200_NVTX is set (shows up in Nsight timelines); a no-op otherwise."""
+        if not self._nvtx:
+            return contextlib.nullcontext()
+        return torch.cuda.nvtx.range(name)
+
     def _prefill_chunk(self, s: _Seq) -> None:
+        with self._range("prefill_chunk"):
+            self._prefill_chunk_inner(s)
+
+    def _prefill_chunk_inner(self, s: _Seq) -> None:
         t0 = time.perf_counter()
         remaining = len(s.prompt) - s.n_past
         n = min(remaining, max(1, self.opts.num_batch))
@@ -346,6 +368,7 @@ class Runner:
         if last:
             tok, lp = s.sampler.sample(logits, s.grammar.allows if s.grammar else None)
             s.t_prefill += time.perf_counter() - t0
+            s.t_first = time.perf_counter() - s.t_submit
             s.state = "decode"
             self._accept(s, tok, lp)
         else:
@@ -353,6 +376,10 @@ class Runner:
             s.t_prefill += time.perf_counter() - t0
 
     def _decode(self, seqs: list[_Seq]) -> None:
+        with self._range("decode_step"):
+            self._decode_inner(seqs)
+
+    def _decode_inner(self, seqs: list[_Seq]) -> None:
         t0 = time.perf_counter()
         ready: list[_Seq] = []
         for s in seqs:
@@ -376,6 +403,8 @@ class Runner:
             logits = self.backend.decode(slots, toks, poss)
             sampled = [s.sampler.sample(logits[i], s.grammar.allows if s.grammar else None) for i, s in enumerate(ready)]
         dt = time.perf_counter() - t0
+        self.stats["decode_steps"] += 1
+        self.stats["decode_step_sequences"] += len(ready)
         for s, (tok, lp) in zip(ready, sampled):
             self.slot_tokens[s.slot].append(s.next_token)
             s.n_past += 1
@@ -401,6 +430,7 @@ class Runner:
             pos += len(chunk)
         self.slot_tokens[s.slot] = new
         s.n_past = len(new)
+        self.stats["context_shifts"] += 1
         return True
 
     def _accept(self, s: _Seq, tok: int, lp: TokenLogprob | None) -> None:
@@ -479,6 +509,16 @@ class Runner:
     def _finish(self, s: _Seq, reason: str) -> None:
         if s.state == "done":
             return
+        st = self.stats
+        st["requests"] += 1
+        st["prompt_tokens"] += len(s.prompt)
+        st["cached_prompt_tokens"] += s.cached
+        st["generated_tokens"] += len(s.generated)
+        st["queue_seconds"] += s.t_queue
+        st["prefill_seconds"] += s.t_prefill
+        st["decode_seconds"] += s.t_decode
+        st["ttft_seconds"] += s.t_first
+        self.done_reasons[reason] = self.done_reasons.get(reason, 0) + 1
         s.out.put(CompletionChunk(done=True, done_reason=reason, prompt_eval_count=len(s.prompt),
                                   prompt_eval_duration=s.t_prefill, eval_count=len(s.generated), eval_duration=s.t_decode,
                                   cached_tokens=s.cached, logprobs=self._take_lp(s)))

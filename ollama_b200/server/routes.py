@@ -90,6 +90,7 @@ class Server:
             Route("/api/tokenize", self.tokenize, methods=["POST"]),
             Route("/api/detokenize", self.detokenize, methods=["POST"]),
             Route("/api/ps", self.ps, methods=["GET"]),
+            Route("/metrics", self.metrics, methods=["GET"]),
             Route("/api/tags", self.tags, methods=["GET", "HEAD"]),
             Route("/api/show", self.show, methods=["POST"]),
             Route("/api/create", self.create, methods=["POST"]),
@@ -549,6 +550,39 @@ class Server:
             return _err(e.status, str(e))
         finally:
             self.sched.release(ref)
+
+    async def metrics(self, request: Request):
+        """Prometheus text exposition of the loaded runners' totals (the reference exposes per-response durations and
+        /api/ps only; this adds queue wait, time to first token and per-phase seconds per model for a scraper)."""
+        lines: list[str] = []
+        seen: set[str] = set()
+
+        def emit(name: str, kind: str, help_: str, labels: dict[str, str], value: float) -> None:
+            if name not in seen:
+                seen.add(name)
+                lines.append(f"# HELP {name} {help_}")
+                lines.append(f"# TYPE {name} {kind}")
+            lab = ",".join('%s="%s"' % (k, str(v).replace("\\", "\\\\").replace('"', '\\"')) for k, v in labels.items())
+            lines.append(f"{name}{{{lab}}} {value:g}" if lab else f"{name} {value:g}")
+
+        refs = self.sched.ps()
+        emit("ollama_b200_loaded_models", "gauge", "Models currently loaded.", {}, len(refs))
+        help_ = {"requests": "Completed requests.", "prompt_tokens": "Prompt tokens of completed requests.",
+                 "cached_prompt_tokens": "Prompt tokens served from a slot's cached prefix.", "generated_tokens": "Generated tokens.",
+                 "queue_seconds": "Seconds requests waited for a slot.", "prefill_seconds": "Seconds spent evaluating prompts.",
+                 "decode_seconds": "Seconds spent generating (per sequence).", "ttft_seconds": "Sum of times from submission to first token.",
+                 "decode_steps": "Decode steps run.", "decode_step_sequences": "Sequences advanced, summed over decode steps.",
+                 "context_shifts": "Context shifts performed."}
+        for r in refs:
+            labels = {"model": getattr(r.model, "short_name", "") or getattr(r.model, "name", "")}
+            emit("ollama_b200_model_vram_bytes", "gauge", "Device memory held by the model.", labels, float(r.vram_size))
+            emit("ollama_b200_model_context_length", "gauge", "Context length per slot.", labels, float(r.context_length))
+            stats = getattr(r.runner, "stats", None) or {}
+            for k, v in stats.items():
+                emit(f"ollama_b200_{k}_total", "counter", help_.get(k, k), labels, float(v))
+            for reason, n in (getattr(r.runner, "done_reasons", None) or {}).items():
+                emit("ollama_b200_done_total", "counter", "Completed requests by done_reason.", {**labels, "reason": reason}, float(n))
+        return PlainTextResponse("\n".join(lines) + "\n", media_type="text/plain; version=0.0.4")
 
     # -- model management -----------------------------------------------------------------------------------
     async def ps(self, request: Request):

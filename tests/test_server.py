@@ -142,6 +142,23 @@ def test_builtin_renderer_and_parser_from_the_model_config(client):
     assert j["done"] and j["eval_count"] == 4 and "content" in j["message"]
 
 
+def test_metrics_route_reports_runner_totals(client):
+    client.post("/api/generate", json={"model": "tiny", "prompt": "<t400><t401>", "stream": False, "options": {"num_predict": 3}})
+    r = client.get("/metrics")
+    assert r.status_code == 200 and r.headers["content-type"].startswith("text/plain")
+    vals: dict[str, float] = {}
+    for line in r.text.splitlines():
+        if line and not line.startswith("#"):
+            k, v = line.rsplit(" ", 1)
+            k = k.split("{")[0] + ("{reason=" + k.split('reason="')[1] if 'reason="' in k else "")     # runners are shared by models of one blob
+            vals[k] = vals.get(k, 0.0) + float(v)
+    assert vals["ollama_b200_loaded_models"] >= 1, r.text
+    assert vals["ollama_b200_requests_total"] >= 1 and vals["ollama_b200_generated_tokens_total"] >= 3
+    assert vals["ollama_b200_ttft_seconds_total"] > 0 and vals["ollama_b200_decode_steps_total"] >= 2
+    assert vals['ollama_b200_done_total{reason=length"}'] >= 1
+    assert "# TYPE ollama_b200_requests_total counter" in r.text
+
+
 def test_create_from_existing_model(client):
     r = client.post("/api/create", json={"model": "child", "from": "tiny", "system": "be brief", "parameters": {"stop": ["<t1>"]},
                                          "stream": False})
