@@ -292,3 +292,44 @@ def test_qwen3_coder_renderer():
     assert render_qwen3_coder([{"role": "user", "content": "hi"}]) == "<|im_start|>user\nhi<|im_end|>\n<|im_start|>assistant\n"
     assert render_qwen3_coder([{"role": "user", "content": "hi"}, {"role": "assistant", "content": "He"}]).endswith("<|im_start|>assistant\nHe")
     assert "You are Qwen, a helpful AI assistant" in render_qwen3_coder([{"role": "user", "content": "hi"}], _TOOLS)
+
+
+def _reference_template_dir():
+    """The reference's template directory when its source tree sits next to this repository (golden prompt files)."""
+    import os
+    d = os.path.normpath(os.path.join(os.path.dirname(os.path.abspath(__file__)), "..", "..", "reference", "template"))
+    return d if os.path.isdir(os.path.join(d, "testdata")) else None
+
+
+@pytest.mark.skipif(_reference_template_dir() is None, reason="the reference source tree is not available")
+def test_go_templates_reproduce_the_reference_golden_prompts():
+    """Every bundled chat layout of the reference (template/*.gotmpl) rendered for its three golden conversations
+    (template/template_test.go:66-140) gives the bytes stored under template/testdata/<layout>/<case>."""
+    import glob
+    import os
+    ref = _reference_template_dir()
+    convs = {
+        "user": [("user", "Hello, how are you?")],
+        "user-assistant-user": [("user", "Hello, how are you?"), ("assistant", "I'm doing great. How can I help you today?"),
+                                ("user", "I'd like to show off how chat templating works!")],
+        "system-user-assistant-user": [("system", "You are a helpful assistant."), ("user", "Hello, how are you?"),
+                                       ("assistant", "I'm doing great. How can I help you today?"),
+                                       ("user", "I'd like to show off how chat templating works!")],
+    }
+    files = sorted(glob.glob(os.path.join(ref, "*.gotmpl")))
+    assert len(files) >= 15
+    checked = 0
+    for f in files:
+        name = os.path.basename(f)
+        with open(f, encoding="utf-8") as fh:
+            t = Template(fh.read())
+        for case, conv in convs.items():
+            golden = os.path.join(ref, "testdata", name, case)
+            if not os.path.exists(golden):
+                continue
+            with open(golden, encoding="utf-8") as fh:
+                want = fh.read()
+            got = t.execute(messages=[{"role": r, "content": c} for r, c in conv])
+            assert got == want, (name, case)
+            checked += 1
+    assert checked >= 45
