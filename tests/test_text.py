@@ -333,3 +333,51 @@ def test_go_templates_reproduce_the_reference_golden_prompts():
             assert got == want, (name, case)
             checked += 1
     assert checked >= 45
+
+
+def _reference_llama_vocab():
+    import os
+    d = os.path.normpath(os.path.join(os.path.dirname(os.path.abspath(__file__)), "..", "..", "reference", "tokenizer", "testdata"))
+    return d if os.path.exists(os.path.join(d, "llama3.2", "encoder.json")) else None
+
+
+@pytest.mark.skipif(_reference_llama_vocab() is None, reason="the reference source tree is not available")
+def test_bpe_on_the_llama3_vocabulary_matches_the_reference_ids():
+    """The reference's tokenizer fixture (a full Llama-3 vocabulary with 280 k merges) and the ids its tests expect
+    (tokenizer/bytepairencoding_test.go:82-215): digit grouping, special tokens, and on a long text the C++ merge loop
+    against the Python one."""
+    import json as _json
+    import os
+    d = _reference_llama_vocab()
+    with open(os.path.join(d, "llama3.2", "encoder.json"), encoding="utf-8") as f:
+        vocab = _json.load(f)
+    tokens = [""] * len(vocab)
+    for t, i in vocab.items():
+        tokens[i] = t
+    types = [1] * len(tokens)
+    for t in ("<|begin_of_text|>", "<|end_of_text|>"):
+        if t not in vocab:
+            vocab[t] = len(tokens)
+            tokens.append(t)
+            types.append(3)
+    with open(os.path.join(d, "llama3.2", "vocab.bpe"), encoding="utf-8") as f:
+        merges = [l.rstrip("\n") for l in f if not l.startswith("#") and l.strip()]
+
+    def make():
+        return BPETokenizer(tokens, types, merges, "llama-bpe", bos=vocab["<|begin_of_text|>"], eos=vocab["<|end_of_text|>"])
+
+    tk = make()
+    enc = lambda s: tk.encode(s, add_special=False)      # noqa: E731
+    assert enc("hello world") == [15339, 1917]
+    for n, want in ((1, [15]), (2, [410]), (3, [931]), (4, [931, 15]), (5, [931, 410]), (7, [931, 931, 15]), (12, [931] * 4), (17, [931] * 5 + [410])):
+        assert enc("0" * n) == want, n
+    assert enc("<|begin_of_text|>A B!") == [128000, 32, 426, 0]
+    assert enc("<|begin_of_text|>A<|end_of_text|>B<|begin_of_text|>!<|end_of_text|>") == [128000, 32, 128001, 33, 128000, 0, 128001]
+    with open(os.path.join(d, "war-and-peace.txt"), encoding="utf-8") as f:
+        text = f.read()[:200_000]
+    assert tk._native_table() is not None
+    native = enc(text)
+    slow = make()
+    slow._native = False
+    assert native == slow.encode(text, add_special=False) and tk.decode(native) == text
+    assert len(native) < len(text) / 3
