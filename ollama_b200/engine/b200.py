@@ -19,6 +19,7 @@ from __future__ import annotations
 
 import ctypes as C
 import math
+import os
 from typing import Sequence
 
 import torch
@@ -206,8 +207,9 @@ class B200Backend:
         f32, i8, i32 = torch.float32, torch.int8, torch.int32
         qkv_dim = (c.n_heads + 2 * c.n_kv_heads) * c.head_dim
         kmax = max(c.d_model, c.q_dim)
-        # split-K width of decode attention: one CTA per (sequence, KV head, split).  Measured on Llama-8B (num_ctx 8192):
-        # 16 splits give 429 tok/s at 640 tokens of context and 327 at 6272; 64 splits give 397 and 342
+        # split-K width of decode attention: one CTA per (sequence, KV head, split).  Measured on Llama-8B (num_ctx 8192,
+        # tensor-core kernel): 16 splits give 442 tok/s at 640 tokens of context and 382 at 6272; 32 splits 428 and 396;
+        # 64 splits 409 and 371
         self.n_splits = max(1, min(envconfig.attn_splits(), n_ctx // 512))
         b = self.buf = _Layer()
         b.x = torch.zeros(MB, c.d_model, device=dev, dtype=f32)
