@@ -225,7 +225,7 @@ def cmd_create(args) -> int:
             lp2 = local(p)
             if not lp2:
                 raise SystemExit(f"Error: {p}: no such file")
-            req.setdefault("adapters" if key == "adapter_paths" else "drafts", {})[os.path.basename(lp2)] = _upload(c, lp2)
+            req.setdefault("adapters" if key == "adapter_paths" else "draft_files", {})[os.path.basename(lp2)] = _upload(c, lp2)
     last: dict[str, Any] = {}
     for ev in c.create(**req):
         progress_line(ev, last)

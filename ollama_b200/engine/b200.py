@@ -48,6 +48,7 @@ class _Layer:
 
 class B200Backend:
     name = "b200"
+    supports_verify = True
 
     def __init__(self, g: GGUFFile | None, device: str = "cuda", opts=None, cfg: ModelConfig | None = None,
                  tensors: dict[str, QWeight] | None = None, keep_bf16: bool | None = None, prefill_gemm: str = "bf16",
@@ -586,6 +587,14 @@ class B200Backend:
         h = R.rmsnorm(x[-1:], self.out_norm, self.cfg.norm_eps).to(torch.bfloat16)
         logits = self._mm(h, self.head)[0]
         return R.softcap(logits, self.cfg.final_softcap)
+
+    @torch.no_grad()
+    def verify(self, slot: int, tokens: Sequence[int], pos0: int) -> torch.Tensor:
+        """Logits of every token of the chunk, [T, vocab]: the target-model pass of speculative decoding (one prefill-style
+        pass over the drafted tokens instead of one decode step per token)."""
+        x = self._forward_chunk(slot, tokens, pos0)
+        h = R.rmsnorm(x, self.out_norm, self.cfg.norm_eps).to(torch.bfloat16)
+        return R.softcap(self._mm(h, self.head), self.cfg.final_softcap)
 
     @torch.no_grad()
     def hidden(self, slot: int, tokens: Sequence[int]) -> torch.Tensor:

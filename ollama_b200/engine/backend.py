@@ -36,6 +36,7 @@ class TorchBackend:
     """Reference execution: fp32 torch ops over weights dequantised from the GGUF."""
 
     name = "torch"
+    supports_verify = True
 
     def __init__(self, g: GGUFFile, device: str = "cpu"):
         self.cfg = config_from_gguf(g)
@@ -62,6 +63,13 @@ class TorchBackend:
         for s, t, p in zip(slots, tokens, positions):
             rows.append(self.model.forward(torch.tensor([t]), torch.tensor([p]), self.cache, s)[0])
         return torch.stack(rows)
+
+    @torch.no_grad()
+    def verify(self, slot, tokens, pos0):
+        """Logits of every token of the chunk, [T, vocab]: the target-model pass of speculative decoding."""
+        t = torch.tensor(list(tokens), dtype=torch.long)
+        pos = torch.arange(pos0, pos0 + len(tokens))
+        return self.model.forward(t, pos, self.cache, slot, logit_rows=torch.arange(len(tokens)))
 
     @torch.no_grad()
     def hidden(self, slot, tokens):

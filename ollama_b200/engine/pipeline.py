@@ -48,6 +48,7 @@ def split_layers(n_layers: int, n_stages: int, weights: Sequence[float] | None =
 
 class PipelineBackend:
     name = "b200-pp"
+    supports_verify = True
 
     def __init__(self, g: GGUFFile | None, devices: Sequence[int | str], opts=None, cfg: ModelConfig | None = None, tensors=None,
                  stage_weights: Sequence[float] | None = None, **kw):
@@ -188,6 +189,14 @@ class PipelineBackend:
         with torch.cuda.device(last.device):
             h = R.rmsnorm(x[-1:], last.out_norm, self.cfg.norm_eps).to(torch.bfloat16)
             return R.softcap(last._mm(h, last.head)[0], self.cfg.final_softcap)
+
+    @torch.no_grad()
+    def verify(self, slot: int, tokens: Sequence[int], pos0: int) -> torch.Tensor:
+        x = self._chunk(slot, tokens, pos0)
+        last = self.stages[-1]
+        with torch.cuda.device(last.device):
+            h = R.rmsnorm(x, last.out_norm, self.cfg.norm_eps).to(torch.bfloat16)
+            return R.softcap(last._mm(h, last.head), self.cfg.final_softcap)
 
     @torch.no_grad()
     def hidden(self, slot: int, tokens: Sequence[int]) -> torch.Tensor:

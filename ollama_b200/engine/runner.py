@@ -39,6 +39,8 @@ class RunnerOptions:
     device: str = "auto"
     flash_attention: bool = True
     tp: int = 1
+    draft_path: str = ""              # a smaller model of the same vocabulary that drafts tokens (Modelfile DRAFT)
+    draft_num_predict: int = 4        # tokens drafted per verification pass (api/types.go:1119)
 
 
 @dataclass
@@ -101,6 +103,7 @@ class _Seq:
         self.t_submit = time.perf_counter()
         self.t_queue = 0.0              # waiting for a slot
         self.t_first = 0.0              # submit -> first sampled token
+        self.d_past = 0                 # tokens whose K/V are in the draft model's cache
         self.n_decoded = 0
         self.n_prompt_eval = 0
         self.cancelled = False
@@ -138,6 +141,9 @@ class Runner:
         self.n_ctx = n_ctx
         self.n_slots = max(1, int(self.opts.num_parallel))
         self.backend.alloc(self.n_slots, self.n_ctx)
+        self.draft = None
+        if self.opts.draft_path and int(self.opts.draft_num_predict) > 0 and getattr(self.backend, "supports_verify", False):
+            self._load_draft()
         self.slot_tokens: list[list[int]] = [[] for _ in range(self.n_slots)]
         self.slot_seq: list[_Seq | None] = [None] * self.n_slots
         self.slot_used_at = [0.0] * self.n_slots
@@ -149,11 +155,25 @@ class Runner:
         # totals since load, written by the loop thread only (read by /metrics)
         self.stats: dict[str, float] = {k: 0 for k in (
             "requests", "prompt_tokens", "cached_prompt_tokens", "generated_tokens", "queue_seconds", "prefill_seconds",
-            "decode_seconds", "ttft_seconds", "decode_steps", "decode_step_sequences", "context_shifts")}
+            "decode_seconds", "ttft_seconds", "decode_steps", "decode_step_sequences", "context_shifts", "draft_tokens",
+            "draft_accepted_tokens")}
         self.done_reasons: dict[str, int] = {}
         self._nvtx = bool(os.environ.get("B200_NVTX")) and str(getattr(self.backend, "device", "cpu")).startswith("cuda")
         self.thread = threading.Thread(target=self._loop, name="runner-loop", daemon=True)
         self.thread.start()
+
+    def _load_draft(self) -> None:
+        """Speculative decoding: the draft model runs on the same device with its own slot-partitioned cache.  A draft
+        whose vocabulary differs cannot propose ids of the target model and is ignored."""
+        g = open_model(self.opts.draft_path)
+        dev = str(getattr(self.backend, "device", self.opts.device))
+        draft = make_backend(g, dev if dev.startswith("cuda") else "cpu", opts=self.opts) if dev.startswith("cuda") \
+            else make_backend(g, "cpu")
+        if draft.cfg.vocab_size != self.cfg.vocab_size:
+            draft.close()
+            return
+        draft.alloc(self.n_slots, self.n_ctx)
+        self.draft = draft
 
     # -- public calls -------------------------------------------------------------------------------
     def ping(self) -> bool:
@@ -173,6 +193,8 @@ class Runner:
 
     def memory(self) -> dict:
         w, kv = self.backend.weight_bytes(), self.backend.kv_bytes()
+        if self.draft is not None:
+            w, kv = w + self.draft.weight_bytes(), kv + self.draft.kv_bytes()
         on_gpu = getattr(self.backend, "name", "torch") != "torch" or str(getattr(self.backend, "device", "cpu")).startswith("cuda")
         return {"weights": w, "kv": kv, "total": w + kv, "vram": (w + kv) if on_gpu else 0}
 
@@ -266,6 +288,8 @@ class Runner:
             self._tp_group.close()
         else:
             self.backend.close()
+        if self.draft is not None:
+            self.draft.close()
         if self.gguf is not None:
             self.gguf.close()
 
@@ -310,6 +334,7 @@ class Runner:
             if seq.req.embedding or not self.cfg.causal:
                 reuse = 0
             seq.slot, seq.n_past, seq.cached = best, reuse, reuse
+            seq.d_past = 0
             seq.t_queue = time.perf_counter() - seq.t_submit
             del self.slot_tokens[best][reuse:]
             self.slot_seq[best] = seq
@@ -392,8 +417,10 @@ class Runner:
         slots = [s.slot for s in ready]
         toks = [s.next_token for s in ready]
         poss = [s.n_past for s in ready]
-        fast = hasattr(self.backend, "decode_argmax") and all(
-            s.sampler.p.greedy and not s.sampler.p.has_penalties and s.grammar is None and not s.sampler.p.logprobs for s in ready)
+        plain = all(s.sampler.p.greedy and not s.sampler.p.has_penalties and s.grammar is None and not s.sampler.p.logprobs for s in ready)
+        if self.draft is not None and plain and len(ready) == 1 and self._speculate(ready[0], t0):
+            return
+        fast = hasattr(self.backend, "decode_argmax") and plain
         if fast:
             out = self.backend.decode_argmax(slots, toks, poss)
             sampled = [(int(t), None) for t in out]
@@ -411,6 +438,56 @@ class Runner:
             s.t_decode += dt
             s.n_decoded += 1
             self._accept(s, tok, lp)
+
+    def _speculate(self, s: _Seq, t0: float) -> bool:
+        """One speculative step of a greedy sequence: the draft model proposes ``k`` tokens one by one, the target model
+        scores the pending token and all proposals in one pass, and the longest prefix of proposals that the target
+        would have produced itself is kept, plus the target's own next token.  Both caches are indexed by position, so
+        rows written for rejected proposals are simply overwritten later.  Returns False when the step has to be an
+        ordinary one (no room left in the context)."""
+        k = int(self.opts.draft_num_predict)
+        if s.n_past + k + 1 > self.n_ctx or len(s.generated) + k + 1 > s.limit:
+            return False
+        d, slot = self.draft, s.slot
+        hist = self.slot_tokens[slot]
+        if s.d_past < s.n_past:            # bring the draft cache up to date (the whole prompt at the first step)
+            pos = s.d_past
+            while pos < s.n_past:
+                chunk = hist[pos:pos + max(1, self.opts.num_batch)]
+                d.prefill(slot, chunk, pos, need_logits=False)
+                pos += len(chunk)
+            s.d_past = s.n_past
+        proposals: list[int] = []
+        tok = s.next_token
+        for i in range(k):
+            if hasattr(d, "decode_argmax"):
+                tok = int(d.decode_argmax([slot], [tok], [s.n_past + i])[0])
+            else:
+                tok = int(d.decode([slot], [tok], [s.n_past + i])[0].argmax())
+            proposals.append(tok)
+        logits = self.backend.verify(slot, [s.next_token] + proposals, s.n_past)
+        target = logits.argmax(-1).tolist()                 # target[i]: the token after position n_past + i
+        n_ok = 0
+        while n_ok < k and proposals[n_ok] == target[n_ok]:
+            n_ok += 1
+        produced = target[:n_ok + 1]
+        dt = time.perf_counter() - t0
+        st = self.stats
+        st["decode_steps"] += 1
+        st["decode_step_sequences"] += 1
+        st["draft_tokens"] += k
+        st["draft_accepted_tokens"] += n_ok
+        s.d_past = s.n_past + min(n_ok + 1, k)               # draft inputs were the pending token and proposals 1..k-1
+        s.t_decode += dt
+        for tok in produced:
+            hist.append(s.next_token)
+            s.n_past += 1
+            s.n_decoded += 1
+            s.sampler.accept(tok)
+            self._accept(s, tok, None)
+            if s.state == "done":
+                break
+        return True
 
     def _shift(self, s: _Seq) -> bool:
         """Context is full: drop half of the tokens after ``num_keep`` and rebuild the cache for the rest."""
@@ -430,6 +507,7 @@ class Runner:
             pos += len(chunk)
         self.slot_tokens[s.slot] = new
         s.n_past = len(new)
+        s.d_past = 0                     # positions moved: the draft cache is rebuilt at the next speculative step
         self.stats["context_shifts"] += 1
         return True
 

@@ -110,6 +110,7 @@ class ShardedTensors:
 
 class TPBackend(B200Backend):
     name = "b200-tp"
+    supports_verify = False      # the verification pass of speculative decoding is not part of the follower protocol
 
     def __init__(self, cfg: ModelConfig, tensors, device: str = "cuda", rank: int = 0, world: int = 1, group=None,
                  max_chunk: int = 2048, keep_bf16: bool | None = None, kv_type: str | None = None):

@@ -63,6 +63,8 @@ class RunnerRef:
             return True
         if list(getattr(model, "projector_paths", [])) != list(getattr(self.model, "projector_paths", [])):
             return True
+        if list(getattr(model, "draft_paths", [])) != list(getattr(self.model, "draft_paths", [])):
+            return True
         want, have = runner_options(opts), self.options
         for k in ("num_batch", "num_thread", "main_gpu", "use_mmap", "draft_num_predict"):
             if want.get(k) is not None and want.get(k) != have.get(k):
@@ -325,7 +327,9 @@ class Scheduler:
 def _default_runner(model: Any, opts: dict[str, Any], num_parallel: int, gpus: list[DeviceInfo]):
     from ..engine.runner import Runner, RunnerOptions
     ro = RunnerOptions(num_ctx=int(opts.get("num_ctx") or 4096), num_batch=int(opts.get("num_batch") or 512), num_parallel=num_parallel,
-                       kv_cache_type=envconfig.kv_cache_type() or "f16", device=envconfig.device(), tp=max(1, len(gpus)))
+                       kv_cache_type=envconfig.kv_cache_type() or "f16", device=envconfig.device(), tp=max(1, len(gpus)),
+                       draft_path=(getattr(model, "draft_paths", None) or [""])[0],
+                       draft_num_predict=int(opts.get("draft_num_predict") if opts.get("draft_num_predict") is not None else 4))
     try:
         return Runner(model.model_path, ro)
     except RuntimeError as e:

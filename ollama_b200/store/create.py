@@ -170,6 +170,11 @@ def create_model(req: dict[str, Any]) -> Iterator[dict[str, Any]]:
 
     for fname, digest in (req.get("adapters") or {}).items():
         layers.append(M.layer_from_existing(digest, M.MT_ADAPTER))
+    drafts = req.get("draft_files") or req.get("drafts") or {}
+    if drafts:      # a draft model for speculative decoding (api/types.go:674-675) replaces the one inherited from the base
+        layers = [l for l in layers if l.media_type != M.MT_DRAFT]
+        for fname, digest in drafts.items():
+            layers.append(M.layer_from_existing(digest, M.MT_DRAFT))
 
     q = req.get("quantize") or req.get("quantization")
     if q:

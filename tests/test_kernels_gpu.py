@@ -568,3 +568,41 @@ def test_bounded_waits_report_a_missing_rank():
     finally:
         reg.clear_status(0)
         reg.close()
+
+
+def test_verify_pass_and_speculative_decoding_on_the_engine(tmp_path):
+    """The target pass of speculative decoding on the sm_100a engine: ``verify`` gives the logits of one-by-one decoding
+    for every drafted position, and a runner with a draft model produces the tokens of the plain greedy run."""
+    from ollama_b200.engine.b200 import B200Backend
+    from ollama_b200.engine.backend import open_model
+    from ollama_b200.engine.runner import CompletionRequest, Runner, RunnerOptions
+    from ollama_b200.engine.sampler import SamplingParams
+    from ollama_b200.models.synth import write_synthetic_gguf
+    p, pd = str(tmp_path / "m.gguf"), str(tmp_path / "d.gguf")
+    write_synthetic_gguf(p, "tiny-qwen3", "Q8_0")
+    write_synthetic_gguf(pd, "tiny-qwen3", "Q4_K_M")             # the same weights, coarser: agrees most of the time
+    eng = B200Backend(open_model(p), "cuda")
+    eng.alloc(1, 128)
+    prompt = torch.randint(259, 4096, (24,), generator=torch.Generator().manual_seed(7)).tolist()
+    eng.prefill(0, prompt[:20], 0, need_logits=False)
+    all_logits = eng.verify(0, prompt[20:], 20)
+    assert all_logits.shape == (4, eng.cfg.vocab_size)
+    eng.prefill(0, prompt[:20], 0, need_logits=False)
+    for i, tok in enumerate(prompt[20:]):
+        step = eng.decode([0], [tok], [20 + i])[0]
+        assert (step - all_logits[i]).abs().max().item() < 0.03 * step.abs().max().item(), i
+    eng.close()
+    outs = []
+    for draft in ("", pd):
+        r = Runner(p, RunnerOptions(num_ctx=256, device="cuda", draft_path=draft, draft_num_predict=4))
+        try:
+            out = list(r.completion(CompletionRequest(prompt=prompt, sampling=SamplingParams(temperature=0), num_predict=40, ignore_eos=True)))
+            outs.append([t for c in out for t in c.tokens])
+            if draft:
+                assert r.stats["draft_accepted_tokens"] > 0 and r.stats["decode_steps"] < 39
+        finally:
+            r.close()
+    # the verification pass runs the prefill kernels (bf16 tensor-core GEMMs), the plain run the decode kernels: the
+    # greedy paths agree until a near-tie between two logits
+    same = next((i for i, (a, b) in enumerate(zip(*outs)) if a != b), 40)
+    assert len(outs[0]) == len(outs[1]) == 40 and same >= 8

@@ -81,3 +81,54 @@ def test_stop_strings_and_seeded_sampling(tiny_llama_path):
         assert a == b
     finally:
         r.close()
+
+
+def _tokens(r, n, prompt=None, **kw):
+    out = list(r.completion(CompletionRequest(prompt=prompt or _prompt(), sampling=SamplingParams(temperature=0), num_predict=n, ignore_eos=True, **kw)))
+    return [t for c in out for t in c.tokens], out[-1]
+
+
+def test_speculative_decoding_keeps_the_greedy_tokens(tiny_llama_path, tiny_llama_q8_path):
+    """A draft model (Modelfile DRAFT) only changes how fast tokens appear: the target's greedy sequence stays the same,
+    whether the draft agrees always (the same weights), mostly (their Q8_0 copy) or the context has to shift."""
+    plain = Runner(tiny_llama_path, RunnerOptions(num_ctx=512, device="cpu"))
+    want, fin = _tokens(plain, 41)
+    plain.close()
+    assert len(want) == 41 and fin.done_reason == "length"
+    for draft, k in ((tiny_llama_path, 4), (tiny_llama_q8_path, 3), (tiny_llama_q8_path, 7)):
+        r = Runner(tiny_llama_path, RunnerOptions(num_ctx=512, device="cpu", draft_path=draft, draft_num_predict=k))
+        try:
+            assert r.draft is not None
+            got, fin = _tokens(r, 41)
+            assert got == want and fin.eval_count == 41 and fin.done_reason == "length", (draft, k)
+            st = r.stats
+            assert st["draft_tokens"] > 0 and 0 < st["draft_accepted_tokens"] <= st["draft_tokens"]
+            assert st["decode_steps"] < 40                       # several tokens per step
+            if draft == tiny_llama_path:
+                assert st["draft_accepted_tokens"] == st["draft_tokens"]
+            # a second request on the same slot (prefix reuse on the target, draft cache rebuilt) and a stop string
+            again, _ = _tokens(r, 9)
+            assert again == want[:9]
+            stop_at = f"<t{want[5]}>"
+            out = list(r.completion(CompletionRequest(prompt=_prompt(), sampling=SamplingParams(temperature=0), num_predict=30, stop=[stop_at])))
+            assert out[-1].done_reason == "stop" and stop_at not in "".join(c.content for c in out)
+        finally:
+            r.close()
+    # sampling with a temperature, or two sequences at once, take the ordinary step
+    r = Runner(tiny_llama_path, RunnerOptions(num_ctx=512, device="cpu", draft_path=tiny_llama_q8_path))
+    try:
+        list(r.completion(CompletionRequest(prompt=_prompt(), sampling=SamplingParams(temperature=0.8, seed=1), num_predict=6)))
+        assert r.stats["draft_tokens"] == 0
+    finally:
+        r.close()
+    # a full context: speculation stops short of the end, the shift rebuilds both caches, the tokens equal the plain run
+    outs = []
+    for draft in ("", tiny_llama_q8_path):
+        r = Runner(tiny_llama_path, RunnerOptions(num_ctx=32, device="cpu", draft_path=draft))
+        try:
+            outs.append(_tokens(r, 40)[0])
+            if draft:
+                assert r.stats["context_shifts"] >= 1 and r.stats["draft_accepted_tokens"] > 0
+        finally:
+            r.close()
+    assert outs[0] == outs[1] and len(outs[0]) == 40

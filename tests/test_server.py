@@ -159,6 +159,23 @@ def test_metrics_route_reports_runner_totals(client):
     assert "# TYPE ollama_b200_requests_total counter" in r.text
 
 
+def test_draft_model_from_create_reaches_the_runner(client):
+    """``draft_files`` (Modelfile DRAFT) becomes a draft layer; the scheduler hands it to the runner, which then speculates."""
+    import glob
+    tiny = client.post("/api/show", json={"model": "tiny"}).json()
+    ggufs = [p for p in glob.glob(os.path.join(os.environ["OLLAMA_MODELS"], "blobs", "sha256-*")) if open(p, "rb").read(4) == b"GGUF"]
+    digest = "sha256:" + os.path.basename(ggufs[0])[len("sha256-"):]
+    r = client.post("/api/create", json={"model": "spec", "from": "tiny", "draft_files": {"draft.gguf": digest}, "parameters": {"num_ctx": 192},
+                                         "stream": False})
+    assert r.status_code == 200 and tiny["details"]["format"] == "gguf"
+    a = client.post("/api/generate", json={"model": "tiny", "prompt": "<t400><t401>", "stream": False, "options": {"num_predict": 12, "num_ctx": 192}}).json()
+    b = client.post("/api/generate", json={"model": "spec", "prompt": "<t400><t401>", "stream": False, "options": {"num_predict": 12}}).json()
+    assert a["response"] == b["response"] and b["eval_count"] == 12
+    text = client.get("/metrics").text
+    accepted = [float(l.rsplit(" ", 1)[1]) for l in text.splitlines() if l.startswith("ollama_b200_draft_accepted_tokens_total")]
+    assert accepted and max(accepted) > 0
+
+
 def test_create_from_existing_model(client):
     r = client.post("/api/create", json={"model": "child", "from": "tiny", "system": "be brief", "parameters": {"stop": ["<t1>"]},
                                          "stream": False})
