@@ -88,7 +88,7 @@ class ClockSampler:
 
 def reference_arm(args) -> None:
     why = ("the reference is a Go program that drives an externally fetched llama.cpp build; this image has no Go toolchain and "
-           "no network, and `pip install /root/reference` fails (no setup.py / pyproject.toml)")
+           "no network, and a pip install of the reference tree fails (no setup.py / pyproject.toml)")
     print(json.dumps({"impl": "reference", "unavailable": why}))
 
 

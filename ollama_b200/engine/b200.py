@@ -12,7 +12,7 @@ captured once per batch size into a CUDA graph (kernels are launched with progra
 launch so that the launch latency of kernel i+1 hides behind kernel i) and replayed with device-side
 token / position / slot arrays.  Prefill runs chunked through the tensor-core GEMM path.
 
-In the reference this layer is the external engine process (SURVEY of the runner protocol:
+In the reference this layer is the external engine process (its runner interface:
 llm/server.go:59-78); its kernels are ggml-cuda's mmvq / mmq / fattn / norm / rope families.
 """
 from __future__ import annotations
