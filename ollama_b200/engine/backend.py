@@ -38,10 +38,18 @@ class TorchBackend:
     name = "torch"
     supports_verify = True
 
-    def __init__(self, g: GGUFFile, device: str = "cpu"):
+    def __init__(self, g: GGUFFile, device: str = "cpu", adapters: Sequence[str] = ()):
         self.cfg = config_from_gguf(g)
         self.device = device
         self.weights = load_all(g, "cpu")
+        if adapters:                 # LoRA adapters are merged into the matrices they name (models/lora.py)
+            from ..models.lora import LoraTensors
+            src = LoraTensors(g, adapters)
+            try:
+                for name in src.touched:
+                    self.weights[name] = src[name]
+            finally:
+                src.close()
         self.model = ReferenceModel(self.cfg, self.weights, device)
         self.cache = None
         self.n_slots = self.n_ctx = 0
@@ -90,13 +98,21 @@ def open_model(path: str) -> GGUFFile:
     return normalise(open_gguf(path))
 
 
-def make_backend(g: GGUFFile, device: str = "auto", **kw):
-    """Pick the engine: the sm_100a kernels when a CUDA device is present, the torch graph otherwise."""
+def make_backend(g: GGUFFile, device: str = "auto", adapters: Sequence[str] = (), **kw):
+    """Pick the engine: the sm_100a kernels when a CUDA device is present, the torch graph otherwise.
+    ``adapters``: LoRA adapter files merged into the weights at load time."""
     if device == "auto":
         device = "cuda" if torch.cuda.is_available() else "cpu"
     if device.startswith("cuda"):
         from .b200 import B200Backend, supports
         if supports(config_from_gguf(g)):
+            if adapters:
+                from ..models.lora import LoraTensors
+                src = LoraTensors(g, adapters)
+                try:
+                    return B200Backend(g, device=device, tensors=src, **kw)
+                finally:
+                    src.close()
             return B200Backend(g, device=device, **kw)
-        return TorchBackend(g, device)
-    return TorchBackend(g, device)
+        return TorchBackend(g, device, adapters)
+    return TorchBackend(g, device, adapters)

@@ -39,6 +39,7 @@ class RunnerOptions:
     device: str = "auto"
     flash_attention: bool = True
     tp: int = 1
+    adapter_paths: tuple = ()         # LoRA adapter files merged into the weights at load time (Modelfile ADAPTER)
     draft_path: str = ""              # a smaller model of the same vocabulary that drafts tokens (Modelfile DRAFT)
     draft_num_predict: int = 4        # tokens drafted per verification pass (api/types.go:1119)
 
@@ -123,13 +124,23 @@ class Runner:
             # the model is split over several GPUs: this process leads, one spawned follower per further GPU repeats its calls
             from ..parallel.launcher import TPGroup
             self._tp_group = TPGroup(model_path, self._tp_devices(), max_chunk=max(512, min(int(self.opts.num_batch), 2048)),
-                                    kv_type=self.opts.kv_cache_type or "f16")
+                                    kv_type=self.opts.kv_cache_type or "f16", adapters=tuple(self.opts.adapter_paths or ()))
             backend = self._tp_group.backend
         elif backend is None and self._pp_devices():
             # several GPUs, but the tensor-parallel split does not take this model: consecutive layers on consecutive GPUs
             from .pipeline import PipelineBackend
-            backend = PipelineBackend(self.gguf, self._pp_devices(), opts=self.opts)
-        self.backend = backend if backend is not None else make_backend(self.gguf, self.opts.device, opts=self.opts)
+            src = None
+            if self.opts.adapter_paths:
+                from ..models.lora import LoraTensors
+                src = LoraTensors(self.gguf, self.opts.adapter_paths)
+            try:
+                backend = PipelineBackend(self.gguf, self._pp_devices(), opts=self.opts, tensors=src)
+            finally:
+                if src is not None:
+                    src.close()
+        if backend is None:
+            backend = make_backend(self.gguf, self.opts.device, opts=self.opts, adapters=tuple(self.opts.adapter_paths or ()))
+        self.backend = backend
         self.cfg = self.backend.cfg
         try:
             self.tokenizer: Tokenizer | None = tokenizer_from_gguf(self.gguf.kv) if self.gguf is not None else None

@@ -40,7 +40,15 @@ class GGUFTensors:
         return load_tensor(self.g, name)
 
 
-def _follower(model_path: str, rank: int, world: int, device: str, conn, max_chunk: int, kv_type: str = "f16") -> None:
+def _source(g: GGUFFile, adapters):
+    """Tensor source of a rank: the GGUF itself, or the GGUF with LoRA adapters merged in."""
+    if adapters:
+        from ..models.lora import LoraTensors
+        return LoraTensors(g, adapters)
+    return GGUFTensors(g)
+
+
+def _follower(model_path: str, rank: int, world: int, device: str, conn, max_chunk: int, kv_type: str = "f16", adapters=()) -> None:
     import torch
 
     from ..engine.backend import open_model
@@ -51,7 +59,7 @@ def _follower(model_path: str, rank: int, world: int, device: str, conn, max_chu
     tr = PipeTransport(rank, world, [conn])
     try:
         g = open_model(model_path)
-        be = TPBackend(config_from_gguf(g), GGUFTensors(g), device=device, rank=rank, world=world, group=tr, max_chunk=max_chunk,
+        be = TPBackend(config_from_gguf(g), _source(g, adapters), device=device, rank=rank, world=world, group=tr, max_chunk=max_chunk,
                        kv_type=kv_type)
         conn.send(("ready", rank))
     except Exception as e:      # the leader turns this into a load error
@@ -63,7 +71,7 @@ def _follower(model_path: str, rank: int, world: int, device: str, conn, max_chu
 class TPGroup:
     """Owns the follower processes of one model; ``backend`` is the leader-side backend for the runner."""
 
-    def __init__(self, model_path: str, devices: Sequence[int], max_chunk: int = 2048, kv_type: str = "f16"):
+    def __init__(self, model_path: str, devices: Sequence[int], max_chunk: int = 2048, kv_type: str = "f16", adapters: Sequence[str] = ()):
         import torch
 
         from ..engine.backend import open_model
@@ -77,7 +85,7 @@ class TPGroup:
         self.procs, conns = [], []
         for r in range(1, world):
             parent, child = ctx.Pipe()
-            p = ctx.Process(target=_follower, args=(model_path, r, world, f"cuda:{devices[r]}", child, max_chunk, kv_type), daemon=True)
+            p = ctx.Process(target=_follower, args=(model_path, r, world, f"cuda:{devices[r]}", child, max_chunk, kv_type, tuple(adapters)), daemon=True)
             p.start()
             child.close()
             self.procs.append(p)
@@ -88,7 +96,7 @@ class TPGroup:
             torch.cuda.set_device(torch.device(dev0))
             g = open_model(model_path)
             tr = PipeTransport(0, world, conns)
-            be = TPBackend(config_from_gguf(g), GGUFTensors(g), device=dev0, rank=0, world=world, group=tr, max_chunk=max_chunk,
+            be = TPBackend(config_from_gguf(g), _source(g, adapters), device=dev0, rank=0, world=world, group=tr, max_chunk=max_chunk,
                            kv_type=kv_type)
             for c in conns:
                 if not c.poll(float(os.environ.get("B200_TP_LOAD_TIMEOUT", "600"))):

@@ -328,6 +328,7 @@ def _default_runner(model: Any, opts: dict[str, Any], num_parallel: int, gpus: l
     from ..engine.runner import Runner, RunnerOptions
     ro = RunnerOptions(num_ctx=int(opts.get("num_ctx") or 4096), num_batch=int(opts.get("num_batch") or 512), num_parallel=num_parallel,
                        kv_cache_type=envconfig.kv_cache_type() or "f16", device=envconfig.device(), tp=max(1, len(gpus)),
+                       adapter_paths=tuple(getattr(model, "adapter_paths", None) or ()),
                        draft_path=(getattr(model, "draft_paths", None) or [""])[0],
                        draft_num_predict=int(opts.get("draft_num_predict") if opts.get("draft_num_predict") is not None else 4))
     try:

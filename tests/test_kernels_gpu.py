@@ -606,3 +606,37 @@ def test_verify_pass_and_speculative_decoding_on_the_engine(tmp_path):
     # greedy paths agree until a near-tie between two logits
     same = next((i for i, (a, b) in enumerate(zip(*outs)) if a != b), 40)
     assert len(outs[0]) == len(outs[1]) == 40 and same >= 8
+
+
+def test_engine_with_a_lora_adapter(tmp_path):
+    """LoRA adapters merged at load: the sm_100a engine (merged matrices as F16 next to quantised ones, mixed gate / up
+    encodings included) against the fp32 graph with the same adapter."""
+    from ollama_b200.engine.backend import TorchBackend, make_backend, open_model
+    from ollama_b200.gguf.types import GGMLType
+    from ollama_b200.gguf.writer import WriteTensor, write_gguf
+    from ollama_b200.models.synth import write_synthetic_gguf
+    p, ad = str(tmp_path / "m.gguf"), str(tmp_path / "a.gguf")
+    write_synthetic_gguf(p, "tiny-qwen3", "Q4_K_M")
+    g = open_model(p)
+    gen = torch.Generator().manual_seed(0)
+    tensors = []
+    for n in ("blk.0.attn_q.weight", "blk.0.ffn_gate.weight", "blk.1.attn_output.weight", "blk.1.ffn_down.weight"):
+        out_dim, in_dim = g.tensors[n].torch_shape
+        a, b = torch.randn(4, in_dim, generator=gen) * 0.05, torch.randn(out_dim, 4, generator=gen) * 0.05
+        tensors += [WriteTensor(n + ".lora_a", (in_dim, 4), GGMLType.F32, a.numpy().tobytes()),
+                    WriteTensor(n + ".lora_b", (4, out_dim), GGMLType.F32, b.numpy().tobytes())]
+    write_gguf(ad, {"general.architecture": "qwen3", "general.type": "adapter", "adapter.type": "lora", "adapter.lora.alpha": 8.0}, tensors)
+    ref, base, eng = TorchBackend(g, "cpu", adapters=[ad]), TorchBackend(g, "cpu"), make_backend(g, "cuda", adapters=[ad])
+    assert eng.name == "b200"
+    for b in (ref, base, eng):
+        b.alloc(1, 64)
+    prompt = torch.randint(259, 4096, (20,), generator=torch.Generator().manual_seed(3)).tolist()
+    lr, lb, le = ref.prefill(0, prompt, 0), base.prefill(0, prompt, 0), eng.prefill(0, prompt, 0).cpu()
+    tol = 0.05 * lr.abs().max().item()
+    assert (le - lr).abs().max().item() < tol and (lb - lr).abs().max().item() > 0.01 * lr.abs().max().item()
+    tok = int(lr.argmax())
+    for step in range(4):
+        lr = ref.decode([0], [tok], [20 + step])[0]
+        le = eng.decode([0], [tok], [20 + step])[0].cpu()
+        assert (le - lr).abs().max().item() < tol, step
+        tok = int(lr.argmax())

@@ -1,4 +1,5 @@
 """CPU plumbing: tiny llama (2 layers, d 256, 4/2 heads, FFN 688, vocab 32000) through the runner."""
+import pytest
 import torch
 
 from ollama_b200.engine.runner import CompletionRequest, Runner, RunnerOptions
@@ -132,3 +133,66 @@ def test_speculative_decoding_keeps_the_greedy_tokens(tiny_llama_path, tiny_llam
         finally:
             r.close()
     assert outs[0] == outs[1] and len(outs[0]) == 40
+
+
+def _write_adapter(path, base_gguf, names, rank=4, alpha=8.0, seed=0):
+    """A LoRA adapter GGUF for ``names`` of the base model: random A [r, in] and B [out, r]."""
+    from ollama_b200.gguf.types import GGMLType
+    from ollama_b200.gguf.writer import WriteTensor, write_gguf
+    g = torch.Generator().manual_seed(seed)
+    tensors, deltas = [], {}
+    for n in names:
+        out_dim, in_dim = base_gguf.tensors[n].torch_shape
+        a = torch.randn(rank, in_dim, generator=g) * 0.05
+        b = torch.randn(out_dim, rank, generator=g) * 0.05
+        deltas[n] = (b @ a) * (alpha / rank)
+        tensors.append(WriteTensor(n + ".lora_a", (in_dim, rank), GGMLType.F32, a.numpy().tobytes()))
+        tensors.append(WriteTensor(n + ".lora_b", (rank, out_dim), GGMLType.F32, b.numpy().tobytes()))
+    write_gguf(path, {"general.architecture": "llama", "general.type": "adapter", "adapter.type": "lora", "adapter.lora.alpha": alpha}, tensors)
+    return deltas
+
+
+def test_lora_adapter_is_merged_at_load(tmp_path, tiny_llama_q8_path):
+    """Modelfile ADAPTER: the low-rank update lands in the matrices it names (kept as F16), the rest keeps its encoding,
+    and the runner's tokens are those of a model whose weights were updated by hand."""
+    from ollama_b200.engine.backend import TorchBackend, open_model
+    from ollama_b200.gguf.types import GGMLType
+    from ollama_b200.models.lora import LoraError, LoraTensors
+    g = open_model(tiny_llama_q8_path)
+    names = ["blk.0.attn_q.weight", "blk.1.attn_v.weight", "blk.1.ffn_down.weight"]
+    ad = str(tmp_path / "adapter.gguf")
+    deltas = _write_adapter(ad, g, names)
+    src = LoraTensors(g, [ad])
+    plain = TorchBackend(g, "cpu")
+    for n in names:
+        w = src[n]
+        assert w.dtype == GGMLType.F16 and src.type_of(n) == GGMLType.F16
+        assert torch.allclose(w.dequant(), plain.weights[n].dequant() + deltas[n], atol=2e-3)
+    assert src["blk.0.attn_k.weight"].dtype == GGMLType.Q8_0 and src.type_of("blk.0.attn_norm.weight") == GGMLType.F32
+    src.close()
+    be = TorchBackend(g, "cpu", adapters=[ad])
+    plain.alloc(1, 64)
+    be.alloc(1, 64)
+    prompt = _prompt()
+    la, lb = plain.prefill(0, prompt, 0), be.prefill(0, prompt, 0)
+    assert (la - lb).abs().max().item() > 1e-3                       # the adapter changes the model ...
+    for n in names:                                                  # ... exactly like editing the weights by hand
+        plain.weights[n] = type(plain.weights[n]).from_float(n, plain.weights[n].dequant() + deltas[n], GGMLType.F16)
+    from ollama_b200.models.reference import ReferenceModel
+    plain.model = ReferenceModel(plain.cfg, plain.weights, "cpu")
+    plain.alloc(1, 64)
+    assert torch.allclose(plain.prefill(0, prompt, 0), lb, atol=1e-4)
+    r = Runner(tiny_llama_q8_path, RunnerOptions(num_ctx=128, device="cpu", adapter_paths=(ad,)))
+    try:
+        toks, _ = _tokens(r, 6)
+        assert toks[0] == int(lb.argmax())
+    finally:
+        r.close()
+    # an adapter for another model is refused
+    bad = str(tmp_path / "bad.gguf")
+    from ollama_b200.gguf.writer import WriteTensor, write_gguf
+    write_gguf(bad, {"general.architecture": "llama", "general.type": "adapter", "adapter.type": "lora", "adapter.lora.alpha": 1.0},
+               [WriteTensor("blk.9.attn_q.weight.lora_a", (8, 2), GGMLType.F32, bytes(64)), WriteTensor("blk.9.attn_q.weight.lora_b", (2, 8), GGMLType.F32, bytes(64))])
+    with pytest.raises(LoraError):
+        LoraTensors(g, [bad])
+    g.close()
