@@ -466,5 +466,46 @@ def convert_hf(path: str, out_path: str, outtype: str = "auto", progress: Callab
     return kv
 
 
+_LORA_NAME = re.compile(r"(?:base_model\.model\.)?(.+)\.lora_([AB])(?:\.default)?\.weight")
+
+
+def convert_adapter(path: str, out_path: str, arch: str, n_head: int = 0, n_kv_head: int = 0) -> dict[str, Any]:
+    """PEFT LoRA adapter directory (adapter_config.json + adapter_model.safetensors) -> adapter GGUF for a base model of
+    architecture ``arch`` (convert/convert.go:182-238, convert_llama_adapter.go): tensors ``<base name>.lora_a`` [r, in]
+    and ``<base name>.lora_b`` [out, r], ``adapter.lora.alpha`` from the configuration.  For llama-arch bases the rows of
+    the B factor of Q and K projections get the same rotary re-ordering as the base matrices (``n_head`` / ``n_kv_head``
+    of the base model are needed for that)."""
+    with open(os.path.join(path, "adapter_config.json"), encoding="utf-8") as f:
+        ac = json.load(f)
+    if str(ac.get("peft_type", "LORA")).upper() != "LORA":
+        raise ConvertError(f"unsupported adapter type {ac.get('peft_type')!r}")
+    src = ModelDir(path)
+    tensors: list[WriteTensor] = []
+    try:
+        for name in sorted(src.keys()):
+            m = _LORA_NAME.fullmatch(name)
+            if m is None:
+                continue
+            base = map_name(m.group(1) + ".weight", arch)
+            if base is None or "#" in base or "@" in base:
+                raise ConvertError(f"adapter tensor {name} has no GGUF counterpart for architecture {arch}")
+            t = src.tensor(name).float()
+            if m.group(2) == "B" and arch == "llama" and re.fullmatch(r"blk\.\d+\.attn_[qk]\.weight", base):
+                heads = n_head if ".attn_q." in base else n_kv_head
+                if heads <= 0:
+                    raise ConvertError("the head counts of the base model are needed to convert Q/K adapters of a llama-arch model")
+                t = permute_qk(t, heads)
+            out = f"{base}.lora_{m.group(2).lower()}"
+            tensors.append(WriteTensor(out, tuple(reversed(t.shape)), GGMLType.F32, quants.quantize(t, GGMLType.F32).numpy()))
+        if not tensors:
+            raise ConvertError("no LoRA tensors found in the adapter")
+        kv = {"general.architecture": arch, "general.type": "adapter", "adapter.type": "lora",
+              "adapter.lora.alpha": float(ac.get("lora_alpha", ac.get("alpha", 0.0)))}
+        write_gguf(out_path, kv, tensors)
+    finally:
+        src.close()
+    return kv
+
+
 def is_hf_dir_listing(names: list[str]) -> bool:
     return "config.json" in names and any(n.endswith(".safetensors") for n in names)

@@ -168,8 +168,35 @@ def create_model(req: dict[str, Any]) -> Iterator[dict[str, Any]]:
     else:
         raise CreateError("neither 'from' or 'files' was specified")
 
-    for fname, digest in (req.get("adapters") or {}).items():
-        layers.append(M.layer_from_existing(digest, M.MT_ADAPTER))
+    adapters = req.get("adapters") or {}
+    if "adapter_config.json" in adapters and any(n.endswith(".safetensors") for n in adapters):
+        # a PEFT LoRA directory: converted to an adapter GGUF for the architecture of the base model
+        from ..convert.hf import ConvertError, convert_adapter
+        from ..gguf.reader import open_gguf
+        base_layer = next((l for l in layers if l.media_type == M.MT_MODEL), None)
+        if base_layer is None:
+            raise CreateError("an adapter needs a base model")
+        yield {"status": "converting adapter"}
+        with open_gguf(base_layer.path(), max_array=64, metadata_only=True) as bg:
+            arch = bg.kv.get("general.architecture", "")
+            n_head, n_kv = int(bg.kv.get(f"{arch}.attention.head_count", 0) or 0), int(bg.kv.get(f"{arch}.attention.head_count_kv", 0) or 0)
+        with tempfile.TemporaryDirectory(dir=M.blobs_dir()) as tmp:
+            for fname, digest in adapters.items():
+                p = M.blob_path(digest)
+                if not os.path.exists(p):
+                    raise CreateError(f"blob {digest} for file {fname} not found")
+                if os.path.basename(fname) != fname or fname in ("", ".", ".."):
+                    raise CreateError(f"invalid file name {fname!r}")
+                os.symlink(p, os.path.join(tmp, fname))
+            out = os.path.join(tmp, "adapter.gguf")
+            try:
+                convert_adapter(tmp, out, arch, n_head, n_kv or n_head)
+            except (ConvertError, KeyError, OSError) as e:
+                raise CreateError(f"adapter conversion failed: {e}") from None
+            layers.append(M.new_layer(out, M.MT_ADAPTER))
+    else:
+        for fname, digest in adapters.items():
+            layers.append(M.layer_from_existing(digest, M.MT_ADAPTER))
     drafts = req.get("draft_files") or req.get("drafts") or {}
     if drafts:      # a draft model for speculative decoding (api/types.go:674-675) replaces the one inherited from the base
         layers = [l for l in layers if l.media_type != M.MT_DRAFT]

@@ -209,3 +209,53 @@ def test_sentencepiece_model_file_vocabulary(tmp_path):
     (tmp_path / "added_tokens.json").write_text(json.dumps({"<gap>": 400}))
     with pytest.raises(Exception, match="invalid token id"):
         tokenizer_kv(str(tmp_path), 324)
+
+
+def test_peft_lora_adapter_conversion_matches_merged_weights(tmp_path):
+    """A PEFT LoRA directory converted to an adapter GGUF and merged at load equals transformers running the merged
+    weights; the Q projection's B factor needs the llama rotary row permutation for that to hold."""
+    transformers = pytest.importorskip("transformers")
+    st = pytest.importorskip("safetensors.torch")
+    from ollama_b200.convert.hf import convert_adapter
+    from ollama_b200.engine.backend import TorchBackend, open_model
+    torch.manual_seed(0)
+    cfg = transformers.LlamaConfig(vocab_size=64, hidden_size=64, intermediate_size=96, num_hidden_layers=2, num_attention_heads=4,
+                                   num_key_value_heads=2, max_position_embeddings=128, rms_norm_eps=1e-5, rope_theta=10000.0, tie_word_embeddings=False)
+    model = transformers.LlamaForCausalLM(cfg).float().eval()
+    src = tmp_path / "hf"
+    model.save_pretrained(src, safe_serialization=True)
+    _tiny_tokenizer(str(src))
+    base = str(tmp_path / "base.gguf")
+    convert_hf(str(src), base, outtype="f32")
+    # adapter on q_proj, k_proj and down_proj of both layers
+    r, alpha = 4, 8.0
+    ad_dir = tmp_path / "peft"
+    ad_dir.mkdir()
+    tensors = {}
+    params = dict(model.named_parameters())
+    with torch.no_grad():
+        for i in range(2):
+            for mod in ("self_attn.q_proj", "self_attn.k_proj", "mlp.down_proj"):
+                w = params[f"model.layers.{i}.{mod}.weight"]
+                a, b = torch.randn(r, w.shape[1]) * 0.1, torch.randn(w.shape[0], r) * 0.1
+                tensors[f"base_model.model.model.layers.{i}.{mod}.lora_A.weight"] = a
+                tensors[f"base_model.model.model.layers.{i}.{mod}.lora_B.weight"] = b
+                w.add_((b @ a) * (alpha / r))                    # the reference result: merged weights
+    st.save_file(tensors, str(ad_dir / "adapter_model.safetensors"), metadata={"format": "pt"})
+    (ad_dir / "adapter_config.json").write_text(json.dumps({"peft_type": "LORA", "r": r, "lora_alpha": alpha, "target_modules": ["q_proj", "k_proj", "down_proj"]}))
+    ad = str(tmp_path / "adapter.gguf")
+    kv = convert_adapter(str(ad_dir), ad, "llama", n_head=4, n_kv_head=2)
+    assert kv["adapter.lora.alpha"] == alpha and kv["general.type"] == "adapter"
+    g = open_model(base)
+    be = TorchBackend(g, "cpu", adapters=[ad])
+    be.alloc(1, 128)
+    ids = torch.randint(0, 64, (13,), generator=torch.Generator().manual_seed(1))
+    with torch.no_grad():
+        ref = model(ids[None]).logits[0, -1]
+    got = be.prefill(0, ids.tolist(), 0)
+    assert torch.allclose(got, ref, atol=2e-4, rtol=1e-3), (got - ref).abs().max()
+    plain = TorchBackend(g, "cpu")
+    plain.alloc(1, 128)
+    assert (plain.prefill(0, ids.tolist(), 0) - ref).abs().max().item() > 1e-2
+    with pytest.raises(Exception, match="head counts"):
+        convert_adapter(str(ad_dir), str(tmp_path / "x.gguf"), "llama")
