@@ -172,12 +172,12 @@ def create_model(req: dict[str, Any]) -> Iterator[dict[str, Any]]:
     if "adapter_config.json" in adapters and any(n.endswith(".safetensors") for n in adapters):
         # a PEFT LoRA directory: converted to an adapter GGUF for the architecture of the base model
         from ..convert.hf import ConvertError, convert_adapter
-        from ..gguf.reader import open_gguf
+        from ..gguf.reader import open_gguf as _open_meta
         base_layer = next((l for l in layers if l.media_type == M.MT_MODEL), None)
         if base_layer is None:
             raise CreateError("an adapter needs a base model")
         yield {"status": "converting adapter"}
-        with open_gguf(base_layer.path(), max_array=64, metadata_only=True) as bg:
+        with _open_meta(base_layer.path(), max_array=64, metadata_only=True) as bg:
             arch = bg.kv.get("general.architecture", "")
             n_head, n_kv = int(bg.kv.get(f"{arch}.attention.head_count", 0) or 0), int(bg.kv.get(f"{arch}.attention.head_count_kv", 0) or 0)
         with tempfile.TemporaryDirectory(dir=M.blobs_dir()) as tmp:
