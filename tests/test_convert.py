@@ -259,3 +259,33 @@ def test_peft_lora_adapter_conversion_matches_merged_weights(tmp_path):
     assert (plain.prefill(0, ids.tolist(), 0) - ref).abs().max().item() > 1e-2
     with pytest.raises(Exception, match="head counts"):
         convert_adapter(str(ad_dir), str(tmp_path / "x.gguf"), "llama")
+
+
+def test_create_with_a_peft_adapter_directory(tmp_path, monkeypatch):
+    """``create`` with the files of a PEFT adapter: an adapter layer (GGUF) is added to the model and named by `show`."""
+    st = pytest.importorskip("safetensors.torch")
+    from ollama_b200.gguf.reader import open_gguf
+    from ollama_b200.models.synth import write_synthetic_gguf
+    from ollama_b200.store import manifest as M
+    from ollama_b200.store.create import CreateError, create_model
+    from ollama_b200.store.model import get_model
+    monkeypatch.setenv("OLLAMA_MODELS", str(tmp_path / "store"))
+    base = tmp_path / "m.gguf"
+    write_synthetic_gguf(str(base), "tiny-llama", "Q8_0")
+    model_layer = M.new_layer(str(base), M.MT_MODEL)
+    a, b = torch.randn(4, 256) * 0.1, torch.randn(256, 4) * 0.1
+    f = tmp_path / "adapter_model.safetensors"
+    st.save_file({"base_model.model.model.layers.0.self_attn.q_proj.lora_A.weight": a,
+                  "base_model.model.model.layers.0.self_attn.q_proj.lora_B.weight": b}, str(f), metadata={"format": "pt"})
+    c = tmp_path / "adapter_config.json"
+    c.write_text(json.dumps({"peft_type": "LORA", "r": 4, "lora_alpha": 16}))
+    files = {"adapter_model.safetensors": M.new_layer(str(f), "application/octet-stream").digest,
+             "adapter_config.json": M.new_layer(str(c), "application/octet-stream").digest}
+    ev = list(create_model({"model": "tuned", "files": {"m.gguf": model_layer.digest}, "adapters": files}))
+    assert ev[-1]["status"] == "success" and any(e["status"] == "converting adapter" for e in ev)
+    m = get_model("tuned")
+    assert len(m.adapter_paths) == 1 and "ADAPTER " in m.modelfile()
+    with open_gguf(m.adapter_paths[0]) as g:
+        assert g.kv["adapter.lora.alpha"] == 16.0 and set(g.tensors) == {"blk.0.attn_q.weight.lora_a", "blk.0.attn_q.weight.lora_b"}
+    with pytest.raises(CreateError):
+        list(create_model({"model": "bad", "adapters": files}))
