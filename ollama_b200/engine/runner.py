@@ -52,6 +52,7 @@ class CompletionRequest:
     num_keep: int = 4
     stop: list[str] = field(default_factory=list)
     grammar: str | None = None
+    grammar_after: str = ""           # the grammar starts to constrain only after this text was generated (end of a reasoning block)
     truncate: bool = True
     shift: bool = True
     cache_prompt: bool = True
@@ -95,6 +96,8 @@ class _Seq:
         self.state = "pending"          # pending -> prefill -> decode -> done
         self.sampler: Sampler | None = None
         self.grammar = None
+        self.grammar_pending = ""       # grammar text waiting for ``grammar_after`` to appear in the output
+        self.gate_text = ""
         self.next_token = -1
         self.pending_bytes = b""
         self.held_text = ""
@@ -352,7 +355,9 @@ class Runner:
             seq.state = "prefill"
             r = seq.req
             seq.sampler = Sampler(r.sampling, self.cfg.vocab_size, self.n_ctx, history=seq.prompt)
-            if r.grammar:
+            if r.grammar and r.grammar_after and self.tokenizer is not None:
+                seq.grammar_pending = r.grammar          # free-form reasoning first, constrained answer afterwards
+            elif r.grammar:
                 from .grammar import Grammar
                 seq.grammar = Grammar(r.grammar, self.tokenizer)
             seq.limit = r.num_predict if r.num_predict >= 0 else 10 * self.n_ctx
@@ -528,6 +533,11 @@ class Runner:
         s.generated.append(tok)
         if s.grammar is not None:
             s.grammar.accept(tok)
+        elif s.grammar_pending and tk is not None and 0 <= tok < tk.n_vocab:
+            s.gate_text = (s.gate_text + tk.token_bytes(tok).decode("utf-8", "ignore"))[-4 * len(s.req.grammar_after) - 64:]
+            if s.req.grammar_after in s.gate_text:
+                from .grammar import Grammar
+                s.grammar, s.grammar_pending = Grammar(s.grammar_pending, tk), ""
         if s.next_token == tok:
             s.repeat_run += 1
         else:

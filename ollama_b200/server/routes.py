@@ -417,8 +417,19 @@ class Server:
         if req.get("_debug_render_only"):
             self.sched.release(ref)
             return JSONResponse({"model": name, "created_at": _now(), "_debug_info": {"rendered_template": text}})
+        # structured output of a reasoning model: the reasoning stays free-form, the grammar applies to the answer
+        # (the reference re-issues the request once the reasoning ended, server/routes.go:2910-2935; here the runner arms
+        # the grammar when the end of the reasoning block shows up in the output)
+        gate = ""
+        if grammar and (think is None or think_enabled(think)):
+            if rend.is_harmony:
+                gate = "<|channel|>final<|message|>"
+            else:
+                tpx = self._thinking_parser(rend, think, text)
+                if tpx is not None and text.rstrip().endswith(tpx.opening):
+                    gate = tpx.closing
         creq = CompletionRequest(prompt=text, sampling=self._sampling(opts, bool(req.get("logprobs")), top_lp), num_predict=opts["num_predict"],
-                                 num_keep=opts["num_keep"], stop=list(opts.get("stop") or []), grammar=grammar,
+                                 num_keep=opts["num_keep"], stop=list(opts.get("stop") or []), grammar=grammar, grammar_after=gate,
                                  truncate=req.get("truncate", True) is not False, shift=req.get("shift", True) is not False,
                                  preserved_tokens=rend.is_harmony)
         hp = harmony.HarmonyParser(rend.names) if rend.is_harmony else None

@@ -196,3 +196,26 @@ def test_lora_adapter_is_merged_at_load(tmp_path, tiny_llama_q8_path):
     with pytest.raises(LoraError):
         LoraTensors(g, [bad])
     g.close()
+
+
+def test_grammar_waits_for_the_end_of_the_reasoning_block(tiny_llama_path):
+    """Structured output of a reasoning model: tokens are free until ``grammar_after`` has been generated, then the
+    grammar constrains the answer and ends the request when it is complete."""
+    r = Runner(tiny_llama_path, RunnerOptions(num_ctx=256, device="cpu"))
+    try:
+        free, _ = _tokens(r, 8)
+        marker = r.tokenizer.decode(free[3:4])
+        assert marker.startswith("<t")
+        req = CompletionRequest(prompt=_prompt(), sampling=SamplingParams(temperature=0), num_predict=32, cache_prompt=False,
+                                grammar='root ::= "<t300>" "<t301>"', grammar_after=marker)
+        out = list(r.completion(req))
+        toks = [t for c in out for t in c.tokens]
+        text = "".join(c.content for c in out)
+        assert toks[:4] == free[:4] and out[-1].done_reason == "stop"
+        assert text == r.tokenizer.decode(free[:4]) + "<t300><t301>"          # spelled with whatever tokens the model prefers
+        # without the gate the grammar applies from the first token
+        req = CompletionRequest(prompt=_prompt(), sampling=SamplingParams(temperature=0), num_predict=32, cache_prompt=False,
+                                grammar='root ::= "<t300>" "<t301>"')
+        assert "".join(c.content for c in r.completion(req)) == "<t300><t301>"
+    finally:
+        r.close()
