@@ -20,6 +20,7 @@ from __future__ import annotations
 
 import logging
 import math
+import os
 import threading
 import time
 from dataclasses import dataclass, field
@@ -90,7 +91,7 @@ def default_context(gpus: list[DeviceInfo]) -> int:
 
 
 def predict_memory(model: Any, num_ctx: int, num_parallel: int) -> int:
-    """Weights + f16 KV cache for num_ctx x num_parallel tokens (llm/llama_server.go:2681-2700)."""
+    """Weights (+ draft model) + KV cache of the configured type for num_ctx x num_parallel tokens (llm/llama_server.go:2681-2700)."""
     size = int(getattr(model, "size", 0) or 0)
     kv = getattr(model, "kv", lambda: {})() or {}
     arch = kv.get("general.architecture", "")
@@ -108,7 +109,11 @@ def predict_memory(model: Any, num_ctx: int, num_parallel: int) -> int:
     kvh = first(kv.get(f"{arch}.attention.head_count_kv"), heads) or heads
     d = first(kv.get(f"{arch}.embedding_length"))
     hd = first(kv.get(f"{arch}.attention.key_length"), d // heads if heads else 0)
-    return size + 2 * layers * kvh * hd * num_ctx * num_parallel * 2
+    per_elem = 2.0                                   # f16 cache
+    if (envconfig.kv_cache_type() or "f16").lower() in ("q8_0", "q4_0") and hd % 32 == 0:
+        per_elem = 1.0 + 2.0 / 32                    # int8 + one f16 scale per 32 dims (q4_0 requests are served as q8_0)
+    extra = sum(os.path.getsize(p) for p in list(getattr(model, "draft_paths", None) or []) if os.path.exists(p))
+    return size + extra + int(2 * layers * kvh * hd * num_ctx * num_parallel * per_elem)
 
 
 class Scheduler:
