@@ -290,6 +290,7 @@ class Server:
             tokens = [int(t) for t in req["context"]] + runner.tokenize(text, add_special=False)
         creq = CompletionRequest(prompt=tokens, sampling=self._sampling(opts, bool(req.get("logprobs")), top_lp), num_predict=opts["num_predict"],
                                  num_keep=opts["num_keep"], stop=list(opts.get("stop") or []), grammar=grammar,
+                                 grammar_after="" if req.get("raw") else self._grammar_gate(rend, grammar, think, text),
                                  truncate=req.get("truncate", True) is not False, shift=req.get("shift", True) is not False,
                                  preserved_tokens=rend.is_harmony)
         tp = self._thinking_parser(rend, think, text) if not req.get("raw") else None
@@ -340,6 +341,18 @@ class Server:
             return final
 
         return self._stream(gen, stream, ref, collapse)
+
+    def _grammar_gate(self, rend: PromptRenderer, grammar: str | None, think: Any, prompt_text: str) -> str:
+        """Text after which a structured-output grammar starts to apply: the end of the reasoning block when the model
+        reasons first (a prompt that ends inside the block, or harmony's analysis channel), "" otherwise."""
+        if not grammar or not (think is None or think_enabled(think)):
+            return ""
+        if rend.is_harmony:
+            return "<|channel|>final<|message|>"
+        tp = self._thinking_parser(rend, think, prompt_text)
+        if tp is not None and prompt_text.rstrip().endswith(tp.opening):
+            return tp.closing
+        return ""
 
     def _thinking_parser(self, rend: PromptRenderer, think: Any, prompt_text: str) -> ThinkingParser | None:
         if rend.is_harmony:
@@ -420,14 +433,7 @@ class Server:
         # structured output of a reasoning model: the reasoning stays free-form, the grammar applies to the answer
         # (the reference re-issues the request once the reasoning ended, server/routes.go:2910-2935; here the runner arms
         # the grammar when the end of the reasoning block shows up in the output)
-        gate = ""
-        if grammar and (think is None or think_enabled(think)):
-            if rend.is_harmony:
-                gate = "<|channel|>final<|message|>"
-            else:
-                tpx = self._thinking_parser(rend, think, text)
-                if tpx is not None and text.rstrip().endswith(tpx.opening):
-                    gate = tpx.closing
+        gate = self._grammar_gate(rend, grammar, think, text)
         creq = CompletionRequest(prompt=text, sampling=self._sampling(opts, bool(req.get("logprobs")), top_lp), num_predict=opts["num_predict"],
                                  num_keep=opts["num_keep"], stop=list(opts.get("stop") or []), grammar=grammar, grammar_after=gate,
                                  truncate=req.get("truncate", True) is not False, shift=req.get("shift", True) is not False,
