@@ -211,7 +211,7 @@ class B200Backend:
         # split-K width of decode attention: one CTA per (sequence, KV head, split).  Measured on Llama-8B (num_ctx 8192,
         # tensor-core kernel): 16 splits give 442 tok/s at 640 tokens of context and 382 at 6272; 32 splits 428 and 396;
         # 64 splits 409 and 371
-        self.n_splits = max(1, min(envconfig.attn_splits(), n_ctx // 512))
+        self.n_splits = max(1, min(envconfig.attn_splits(), n_ctx // envconfig.attn_split_len()))
         b = self.buf = _Layer()
         b.x = torch.zeros(MB, c.d_model, device=dev, dtype=f32)
         b.tmp = torch.zeros(MB, c.d_model, device=dev, dtype=f32)

@@ -250,6 +250,11 @@ def attn_splits() -> int:
     return max(1, _uint("B200_ATTN_SPLITS", 32))
 
 
+def attn_split_len() -> int:
+    """B200_ATTN_SPLIT_LEN: positions of allocated context per split of decode attention (splits = num_ctx / this, capped)."""
+    return max(64, _uint("B200_ATTN_SPLIT_LEN", 512))
+
+
 def comm_mode() -> str:
     """B200_COMM: nccl | p2p (fused peer-memory kernels, default) ."""
     return var("B200_COMM") or "p2p"
