@@ -290,6 +290,12 @@ def as_map() -> dict[str, tuple[object, str]]:
         "OLLAMA_NO_CLOUD": (no_cloud(), "Disable cloud features"),
         "CUDA_VISIBLE_DEVICES": (cuda_visible_devices(), "Set which NVIDIA devices are visible"),
         "B200_TP": (tp_degree(), "Tensor-parallel degree (0 = automatic)"),
+        "B200_PP": (pp_degree(), "GPUs of a layer pipeline (0 = only as the fallback of B200_TP)"),
+        "B200_ATTN_SPLITS": (attn_splits(), "Upper bound of the split-K width of decode attention"),
+        "B200_ATTN_SPLIT_LEN": (attn_split_len(), "Positions of allocated context per split of decode attention"),
+        "B200_ATTN_MMA": (var("B200_ATTN_MMA") or "auto", "Decode attention kernel: 1 tensor cores, 0 scalar, auto by model shape"),
+        "B200_NVTX": (_bool("B200_NVTX"), "NVTX ranges around prefill chunks and decode steps"),
+        "B200_NO_NATIVE": (_bool("B200_NO_NATIVE"), "Do not load the C++ host helpers (codecs, BPE merges)"),
         "B200_COMM": (comm_mode(), "Collective implementation: p2p (fused kernels) or nccl"),
         "B200_DEVICE": (device(), "Execution device: auto, cpu or cuda[:N]"),
     }
