@@ -84,6 +84,14 @@ class Client:
     def embed(self, **req) -> dict[str, Any]:
         return self.request("POST", "/api/embed", req)
 
+    def embeddings(self, **req) -> dict[str, Any]:
+        """Legacy single-prompt embedding route (api/client.go Embeddings)."""
+        return self.request("POST", "/api/embeddings", req)
+
+    def status(self) -> dict[str, Any]:
+        """Cloud status of the server (api/client.go CloudStatusExperimental)."""
+        return self.request("GET", "/api/status")
+
     def tokenize(self, **req) -> dict[str, Any]:
         return self.request("POST", "/api/tokenize", req)
 
