@@ -39,6 +39,7 @@ class RunnerOptions:
     device: str = "auto"
     flash_attention: bool = True
     tp: int = 1
+    gpu_ids: tuple = ()               # device indices chosen by the scheduler (empty: devices 0..tp-1 / the current device)
     adapter_paths: tuple = ()         # LoRA adapter files merged into the weights at load time (Modelfile ADAPTER)
     draft_path: str = ""              # a smaller model of the same vocabulary that drafts tokens (Modelfile DRAFT)
     draft_num_predict: int = 4        # tokens drafted per verification pass (api/types.go:1119)
@@ -142,8 +143,13 @@ class Runner:
                 if src is not None:
                     src.close()
         if backend is None:
-            backend = make_backend(self.gguf, self.opts.device, opts=self.opts, adapters=tuple(self.opts.adapter_paths or ()))
+            with self._on(self.opts.device):
+                backend = make_backend(self.gguf, self.opts.device, opts=self.opts, adapters=tuple(self.opts.adapter_paths or ()))
         self.backend = backend
+        # kernels are launched on the current device's stream: the loop thread and the calls below make the backend's
+        # device current (a layer pipeline switches devices itself)
+        dev = str(getattr(self.backend, "device", "")) if getattr(self.backend, "name", "") != "b200-pp" else ""
+        self._cuda_device = dev if dev.startswith("cuda") else ""
         self.cfg = self.backend.cfg
         try:
             self.tokenizer: Tokenizer | None = tokenizer_from_gguf(self.gguf.kv) if self.gguf is not None else None
@@ -154,10 +160,11 @@ class Runner:
             n_ctx = min(n_ctx, self.cfg.ctx_train)          # llm/server.go:111-116
         self.n_ctx = n_ctx
         self.n_slots = max(1, int(self.opts.num_parallel))
-        self.backend.alloc(self.n_slots, self.n_ctx)
-        self.draft = None
-        if self.opts.draft_path and int(self.opts.draft_num_predict) > 0 and getattr(self.backend, "supports_verify", False):
-            self._load_draft()
+        with self._on(self._cuda_device):
+            self.backend.alloc(self.n_slots, self.n_ctx)
+            self.draft = None
+            if self.opts.draft_path and int(self.opts.draft_num_predict) > 0 and getattr(self.backend, "supports_verify", False):
+                self._load_draft()
         self.slot_tokens: list[list[int]] = [[] for _ in range(self.n_slots)]
         self.slot_seq: list[_Seq | None] = [None] * self.n_slots
         self.slot_used_at = [0.0] * self.n_slots
@@ -277,7 +284,12 @@ class Runner:
                 return []
         except (ValueError, NotImplementedError):
             return []
-        return list(range(tp))
+        return self._pick(tp)
+
+    def _pick(self, n: int) -> list[int]:
+        """``n`` device indices: the scheduler's choice when it names enough devices, else 0..n-1."""
+        ids = [int(i) for i in (self.opts.gpu_ids or ())]
+        return ids[:n] if len(ids) >= n else list(range(n))
 
     def _pp_devices(self) -> list[int]:
         """GPUs of a layer pipeline ([] = none): B200_PP, or the GPUs meant for a tensor-parallel group that cannot be formed."""
@@ -291,7 +303,7 @@ class Runner:
         from ..models.config import config_from_gguf
         from .b200 import supports
         cfg = config_from_gguf(self.gguf)
-        return list(range(n)) if supports(cfg) and cfg.n_layers >= n else []
+        return self._pick(n) if supports(cfg) and cfg.n_layers >= n else []
 
     def close(self) -> None:
         with self.cv:
@@ -308,8 +320,17 @@ class Runner:
             self.gguf.close()
 
     # -- batching loop -------------------------------------------------------------------------------
+    @staticmethod
+    def _on(device: str):
+        """Context that makes ``device`` ("cuda:N") the current CUDA device; a no-op for anything else."""
+        if isinstance(device, str) and device.startswith("cuda:") and torch.cuda.is_available():
+            return torch.cuda.device(torch.device(device))
+        return contextlib.nullcontext()
+
     def _loop(self) -> None:
         try:
+            if self._cuda_device.startswith("cuda:") and torch.cuda.is_available():
+                torch.cuda.set_device(torch.device(self._cuda_device))
             while True:
                 with self.cv:
                     while not self.closed and not self.pending and not any(self.slot_seq):

@@ -317,22 +317,30 @@ class Scheduler:
 
     @staticmethod
     def _place(gpus: list[DeviceInfo], need: int) -> list[DeviceInfo]:
-        """Single GPU when the model fits 80 % of its free memory (most free first), otherwise every GPU."""
+        """The smallest group of 1, 2, 4, ... GPUs (most free memory first) whose members can each hold their share within
+        80 % of their free memory; every GPU when no such group exists."""
         if not gpus:
             return []
         if envconfig.sched_spread():
             return list(gpus)
         by_free = sorted(gpus, key=lambda g: -g.free_memory)
-        for g in by_free:
-            if need <= 0.8 * g.free_memory:
-                return [g]
+        k = 1
+        while k <= len(by_free):                     # 1, 2, 4, 8 ... GPUs: group sizes a tensor-parallel split divides by
+            group = by_free[:k]
+            if need <= 0.8 * k * min(g.free_memory for g in group):
+                return group
+            k *= 2
         return list(gpus)
 
 
 def _default_runner(model: Any, opts: dict[str, Any], num_parallel: int, gpus: list[DeviceInfo]):
     from ..engine.runner import Runner, RunnerOptions
+    device = envconfig.device()
+    if len(gpus) == 1 and device in ("auto", "cuda"):
+        device = f"cuda:{gpus[0].index}"            # the GPU the placement chose, not whichever is current
     ro = RunnerOptions(num_ctx=int(opts.get("num_ctx") or 4096), num_batch=int(opts.get("num_batch") or 512), num_parallel=num_parallel,
-                       kv_cache_type=envconfig.kv_cache_type() or "f16", device=envconfig.device(), tp=max(1, len(gpus)),
+                       kv_cache_type=envconfig.kv_cache_type() or "f16", device=device, tp=max(1, len(gpus)),
+                       gpu_ids=tuple(g.index for g in gpus),
                        adapter_paths=tuple(getattr(model, "adapter_paths", None) or ()),
                        draft_path=(getattr(model, "draft_paths", None) or [""])[0],
                        draft_num_predict=int(opts.get("draft_num_predict") if opts.get("draft_num_predict") is not None else 4))

@@ -94,3 +94,41 @@ def test_runner_falls_back_to_the_pipeline(tmp_path, monkeypatch):
         finally:
             r.close()
     assert len(outs[0]) == 8 and outs[0] == outs[1]
+
+
+@pytest.mark.gpu
+def test_runner_on_the_gpu_the_scheduler_chose(tmp_path):
+    """A single-GPU model placed on a GPU other than the first one: weights, caches and kernel launches all land there,
+    and a tensor-parallel group uses the listed devices in the listed order."""
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    from ollama_b200.engine.runner import CompletionRequest, Runner, RunnerOptions
+    from ollama_b200.engine.sampler import SamplingParams
+    from ollama_b200.models.synth import write_synthetic_gguf
+    p = str(tmp_path / "m.gguf")
+    write_synthetic_gguf(p, "tiny-tp", "Q8_0")
+    prompt = list(range(300, 340))
+    outs = []
+    for opts in (dict(device="cuda:0"), dict(device="cuda:1", gpu_ids=(1,)), dict(device="cuda", tp=2, gpu_ids=(1, 0))):
+        before = [torch.cuda.memory_allocated(i) for i in range(2)]
+        r = Runner(p, RunnerOptions(num_ctx=256, **opts))
+        try:
+            if opts.get("tp"):
+                assert r._tp_group is not None and str(r.backend.device) == "cuda:1"
+            else:
+                assert str(r.backend.device) == opts["device"]
+                other = 1 - int(opts["device"][-1])
+                assert torch.cuda.memory_allocated(other) == before[other]          # nothing was placed on the other GPU
+            seq = r.submit(CompletionRequest(prompt=prompt, sampling=SamplingParams(temperature=0.7, seed=3, top_k=20), num_predict=10, ignore_eos=True))
+            toks = []
+            while True:
+                ch = seq.out.get(timeout=120)
+                assert not ch.error, ch.error
+                toks += ch.tokens
+                if ch.done:
+                    break
+            outs.append(toks)
+        finally:
+            r.close()
+    assert len(outs[0]) == 10 and outs[0] == outs[1]
+    assert len(outs[2]) == 10

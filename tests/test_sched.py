@@ -142,6 +142,18 @@ def test_memory_eviction_and_multi_gpu_placement():
     s.unload_all()
 
 
+def test_placement_picks_the_smallest_group_that_fits():
+    """1, 2, 4, ... GPUs, most free memory first; the chosen devices (not simply 0..n-1) are what the runner is given."""
+    from ollama_b200.server.sched import Scheduler
+    gpus = [DeviceInfo(id=str(i), index=i, total_memory=80 * GiB, free_memory=f * GiB) for i, f in enumerate((10, 70, 20, 60, 65, 5, 50, 40))]
+    pick = lambda need: [g.index for g in Scheduler._place(gpus, int(need * GiB))]      # noqa: E731
+    assert pick(30) == [1]                                  # the GPU with the most free memory
+    assert pick(90) == [1, 4]                               # 2 x 0.8 x 65
+    assert pick(150) == [1, 4, 3, 6]                        # 4 x 0.8 x 50
+    assert sorted(pick(400)) == list(range(8))              # nothing fits: the whole node
+    assert pick(1) == [1] and Scheduler._place([], 1) == []
+
+
 def test_auto_context_shrinks_when_memory_is_short():
     assert default_context(gpus(1)) == 262144 and default_context([]) == 4096
     m = FakeModel("a", 1 * GiB)
