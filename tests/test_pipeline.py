@@ -118,7 +118,7 @@ def test_runner_on_the_gpu_the_scheduler_chose(tmp_path):
             else:
                 assert str(r.backend.device) == opts["device"]
                 other = 1 - int(opts["device"][-1])
-                assert torch.cuda.memory_allocated(other) == before[other]          # nothing was placed on the other GPU
+                assert torch.cuda.memory_allocated(other) <= before[other]          # nothing was placed on the other GPU
             seq = r.submit(CompletionRequest(prompt=prompt, sampling=SamplingParams(temperature=0.7, seed=3, top_k=20), num_predict=10, ignore_eos=True))
             toks = []
             while True:
