@@ -381,3 +381,34 @@ def test_bpe_on_the_llama3_vocabulary_matches_the_reference_ids():
     slow._native = False
     assert native == slow.encode(text, add_special=False) and tk.decode(native) == text
     assert len(native) < len(text) / 3
+
+
+@pytest.mark.skipif(_reference_template_dir() is None, reason="the reference source tree is not available")
+def test_jinja_engine_runs_the_known_chat_templates():
+    """The Jinja chat templates the reference recognises (template/index.json, 37 real-world layouts): every one parses
+    and renders three conversations; the only failures allowed are the templates' own ``raise_exception`` calls, and the
+    rendering contains every message of the conversation."""
+    import json as _json
+    import os
+    from ollama_b200.text.template import JinjaChatTemplate
+    with open(os.path.join(_reference_template_dir(), "index.json"), encoding="utf-8") as f:
+        idx = _json.load(f)
+    assert len(idx) >= 30
+    convs = [[("user", "Hello, how are you?")],
+             [("user", "Hello, how are you?"), ("assistant", "I'm doing great."), ("user", "Show me templating!")],
+             [("system", "You are a helpful assistant."), ("user", "Hello, how are you?"), ("assistant", "I'm doing great."), ("user", "Show me templating!")]]
+    rendered = refused = 0
+    for e in idx:
+        t = JinjaChatTemplate(e["template"], e.get("bos_token", "<s>"), e.get("eos_token", "</s>"))
+        for conv in convs:
+            try:
+                out = t.render([{"role": r, "content": c} for r, c in conv], None, True)
+            except TemplateError as ex:
+                assert any(w in str(ex).lower() for w in ("system", "alternate", "role")), (e["name"], ex)
+                refused += 1
+                continue
+            rendered += 1
+            for r, c in conv:
+                if r != "system":
+                    assert c in out, (e["name"], c)
+    assert rendered >= 100 and refused <= 8
