@@ -412,3 +412,32 @@ def test_jinja_engine_runs_the_known_chat_templates():
                 if r != "system":
                     assert c in out, (e["name"], c)
     assert rendered >= 100 and refused <= 8
+
+
+def test_builtin_parsers_are_chunking_invariant_under_random_splits():
+    """Property: however the output is cut into chunks, the concatenated (content, thinking, calls) is the same."""
+    hyp = pytest.importorskip("hypothesis")
+    from hypothesis import strategies as stg
+    from ollama_b200.text.builtin import parser_for
+    outputs = {
+        "qwen3-coder": "Sure <b>.\n\n<tool_call>\n<function=get_weather>\n<parameter=city>\nParis\n</parameter>\n</function>\n</tool_call>\n\nand <tool_ca not a call",
+        "qwen3-thinking": "<think>\nstep 1 < step 2\n</think>\n\nAnswer: 4.\n<tool_call>\n{\"name\": \"get_weather\", \"arguments\": {\"city\": \"Oslo\"}}\n</tool_call>\n",
+        "qwen3": "plain </think> text <tool_call>{\"name\": \"get_weather\", \"arguments\": {\"days\": 2}}</tool_call> tail  ",
+        "ministral": "[THINK]a [b] c[/THINK] ok [TOOL_CALLS]get_weather[ARGS]{\"city\": \"R}\"} rest",
+    }
+    whole = {n: parser_for(n, _TOOLS).add(t, True) for n, t in outputs.items()}
+
+    @hyp.settings(max_examples=150, deadline=None)
+    @hyp.given(stg.sampled_from(sorted(outputs)), stg.lists(stg.integers(min_value=1, max_value=40), min_size=1, max_size=60))
+    def check(name, sizes):
+        text, p = outputs[name], parser_for(name, _TOOLS)
+        c, t, calls, i, k = "", "", [], 0, 0
+        while i < len(text):
+            n = sizes[k % len(sizes)]
+            k += 1
+            a, b, cc = p.add(text[i:i + n], i + n >= len(text))
+            c, t, calls, i = c + a, t + b, calls + cc, i + n
+        assert (c, t, calls) == whole[name]
+
+    check()
+    assert whole["qwen3-coder"][2][0]["function"]["arguments"] == {"city": "Paris"} and whole["ministral"][1] == "a [b] c"
