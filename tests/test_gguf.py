@@ -204,3 +204,35 @@ def test_native_codecs_match_the_tensor_op_codecs(t):
     a, b = quants.dequantize(junk, t, native=False), quants.dequantize(junk, t, native=True)
     ok = torch.isfinite(a)
     assert torch.equal(ok, torch.isfinite(b)) and torch.allclose(a[ok], b[ok], rtol=1e-6, atol=0)
+
+
+def test_reader_survives_corrupted_files(tmp_path):
+    """Random byte flips and truncations of a valid file (the reference fuzzes its reader the same way,
+    fs/gguf/gguf_internal_test.go): the reader either opens the file or raises GGUFError, nothing else."""
+    import random
+    p = str(tmp_path / "a.gguf")
+    write_gguf(p, {"general.architecture": "llama", "llama.block_count": 2, "tokenizer.ggml.tokens": ["a", "b", "c"], "x.arr": [1, 2, 3],
+                   "general.name": "t"},
+               [WriteTensor("a.weight", (32, 4), GGMLType.F32, np.zeros((4, 32), np.float32).tobytes()),
+                WriteTensor("b.weight", (64,), GGMLType.Q8_0, bytes(68))])
+    data = open(p, "rb").read()
+    rnd = random.Random(0)
+    q = str(tmp_path / "m.gguf")
+    opened = 0
+    for _ in range(800):
+        b = bytearray(data)
+        for _ in range(rnd.randint(1, 4)):
+            b[rnd.randrange(0, min(len(b), 400))] = rnd.randrange(256)
+        if rnd.random() < 0.2:
+            b = b[:rnd.randrange(1, len(b))]
+        with open(q, "wb") as f:
+            f.write(b)
+        try:
+            g = open_gguf(q)
+            for n in g.tensors:
+                g.tensor_bytes(n)
+            g.close()
+            opened += 1
+        except GGUFError:
+            pass
+    assert 0 < opened < 800
