@@ -199,7 +199,12 @@ class _GbnfParser:
 
 
 def parse_gbnf(src: str) -> Rules:
-    return _GbnfParser(src).parse()
+    try:
+        return _GbnfParser(src).parse()
+    except GrammarError:
+        raise
+    except (ValueError, IndexError, KeyError, RecursionError) as e:       # cut-off escapes, text ending inside a construct
+        raise GrammarError(f"malformed grammar: {e}") from None
 
 
 def _match(el: Element, cp: int) -> bool:
@@ -234,7 +239,12 @@ class GrammarMatcher:
             if el[0] == "char":
                 out.add(st)
             else:
-                base = st[:-1] + ((rule, ai, pos + 1),)
+                # a reference in the last position needs no return frame: repetitions (R ::= X R | "") then keep a constant
+                # depth, and a repetition whose body can match nothing comes back to a stack already seen instead of
+                # growing for ever
+                base = st[:-1] if pos + 1 >= len(alt) else st[:-1] + ((rule, ai, pos + 1),)
+                if len(base) > 2048:
+                    raise GrammarError("grammar nests too deeply (left recursion?)")
                 for bi in range(len(self.rules[el[1]])):
                     work.append(base + ((el[1], bi, 0),))
         return out

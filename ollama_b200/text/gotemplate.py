@@ -395,7 +395,12 @@ FUNCS: dict[str, Callable[..., Any]] = {
 class GoTemplate:
     def __init__(self, src: str):
         self.src = src
-        self.root, _, _ = _Parser(_split(src)).block(())
+        try:
+            self.root, _, _ = _Parser(_split(src)).block(())
+        except TemplateError:
+            raise
+        except (ValueError, IndexError, KeyError, TypeError, RecursionError) as e:      # e.g. a malformed string literal
+            raise TemplateError(f"template: {e}") from None
 
     # -- introspection (thinking / tool tag inference walks the tree) ---------------------------------
     def identifiers(self) -> set[str]:
@@ -427,7 +432,13 @@ class GoTemplate:
     # -- execution --------------------------------------------------------------------------------------
     def render(self, data: Any, nodes: list[Node] | None = None) -> str:
         out: list[str] = []
-        self._exec(self.root if nodes is None else nodes, data, [{"$": data}], out)
+        try:
+            self._exec(self.root if nodes is None else nodes, data, [{"$": data}], out)
+        except TemplateError:
+            raise
+        except (TypeError, ValueError, IndexError, KeyError, AttributeError, RecursionError) as e:
+            # an operation on values of the wrong kind (Go reports these as execution errors of the template)
+            raise TemplateError(f"template: error executing: {e}") from None
         return "".join(out)
 
     def _lookup(self, scopes, name):

@@ -441,3 +441,50 @@ def test_builtin_parsers_are_chunking_invariant_under_random_splits():
 
     check()
     assert whole["qwen3-coder"][2][0]["function"]["arguments"] == {"city": "Paris"} and whole["ministral"][1] == "a [b] c"
+
+
+def test_parsers_reject_mutated_input_with_their_own_error_types():
+    """Mutations of valid Go templates, GBNF grammars and Modelfiles either still work or fail with the error type the
+    server turns into a 400 (TemplateError, GrammarError, ModelfileError / OptionError): no other exception escapes."""
+    import random
+    from ollama_b200.api.types import OptionError
+    from ollama_b200.store.modelfile import ModelfileError, parse_modelfile
+    rnd = random.Random(1)
+
+    def mutate(s):
+        b = list(s)
+        for _ in range(rnd.randint(1, 3)):
+            op, i = rnd.random(), rnd.randrange(len(b)) if b else 0
+            if op < 0.4 and b:
+                b[i] = rnd.choice('{}|.()"$ -:=\\n' + s[rnd.randrange(len(s))])
+            elif op < 0.7 and b:
+                del b[i:i + rnd.randint(1, 5)]
+            else:
+                b.insert(i, rnd.choice(["{{", "}}", "{{-", " end ", '"', "(", ")", "|", "range ", "if ", "::=", "[", "\\\\"]))
+        return "".join(b)
+
+    tmpls = ['{{- $system := "" }}{{- range .Messages }}{{- if eq .Role "system" }}{{ $system = .Content }}{{- else if eq .Role "user" }}'
+             '[INST] {{ if $system }}{{ $system }}\\n\\n{{ end }}{{ .Content }}[/INST]{{- else }} {{ .Content }}</s>{{- end }}{{- end }}',
+             '{{ if .System }}<|im_start|>system\\n{{ .System }}<|im_end|>\\n{{ end }}{{ range $i, $m := .Messages }}{{ if gt $i 0 }}\\n{{ end }}'
+             '<|im_start|>{{ $m.Role }}\\n{{ $m.Content }}{{ if lt (len (slice $.Messages $i)) 2 }}<|im_end|>{{ end }}{{ end }}']
+    msgs = [{"role": "system", "content": "s"}, {"role": "user", "content": "u"}, {"role": "assistant", "content": "a"}, {"role": "user", "content": "q"}]
+    worked = 0
+    for _ in range(600):
+        src = mutate(rnd.choice(tmpls))
+        try:
+            Template(src).execute(messages=[dict(m) for m in msgs])
+            worked += 1
+        except TemplateError:
+            pass
+    assert 0 < worked < 600
+    for _ in range(400):
+        try:
+            GrammarMatcher(parse_gbnf(mutate(JSON_GRAMMAR))).accepts('{"a": [1, true]}')
+        except GrammarError:
+            pass
+    mf = 'FROM llama3\\nTEMPLATE """{{ .Prompt }}"""\\nSYSTEM "hi"\\nPARAMETER temperature 0.5\\nPARAMETER stop "x"\\nMESSAGE user hello\\nADAPTER ./a.gguf\\n'
+    for _ in range(400):
+        try:
+            parse_modelfile(mutate(mf)).create_request()
+        except (ModelfileError, OptionError):
+            pass
