@@ -150,7 +150,10 @@ class JinjaChatTemplate:
         env.globals["raise_exception"] = raise_exception
         env.globals["strftime_now"] = lambda fmt: datetime.datetime.now().strftime(fmt)
         env.filters["tojson"] = lambda v, indent=None, **kw: json.dumps(v, ensure_ascii=False, indent=indent)
-        self.t = env.from_string(src)
+        try:
+            self.t = env.from_string(src)
+        except Exception as e:          # jinja2.TemplateSyntaxError and friends
+            raise TemplateError(f"chat template: {e}") from None
         self.bos_token, self.eos_token = bos_token, eos_token
 
     def render(self, messages: list[dict[str, Any]], tools: list[dict[str, Any]] | None = None, add_generation_prompt: bool = True,
@@ -169,8 +172,13 @@ class JinjaChatTemplate:
             if m.get("tool_call_id"):
                 d["tool_call_id"] = m["tool_call_id"]
             msgs.append(d)
-        return self.t.render(messages=msgs, tools=tools or None, add_generation_prompt=add_generation_prompt,
-                             bos_token=self.bos_token, eos_token=self.eos_token, **kwargs)
+        try:
+            return self.t.render(messages=msgs, tools=tools or None, add_generation_prompt=add_generation_prompt,
+                                 bos_token=self.bos_token, eos_token=self.eos_token, **kwargs)
+        except TemplateError:
+            raise
+        except Exception as e:          # undefined names, operations on the wrong kind of value, sandbox violations
+            raise TemplateError(f"chat template: {type(e).__name__}: {e}") from None
 
 
 # Named templates recognised from a GGUF chat template (the reference matches against its catalogue by edit
