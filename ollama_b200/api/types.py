@@ -47,7 +47,7 @@ def options_from_map(opts: dict[str, Any], m: dict[str, Any] | None) -> dict[str
             continue
         kind = spec[0]
         if kind in ("int", "int?"):
-            if isinstance(val, bool) or not isinstance(val, (int, float)):
+            if isinstance(val, bool) or not isinstance(val, (int, float)) or val != val or val in (float("inf"), float("-inf")):
                 raise OptionError(f'option "{key}" must be of type integer')
             opts[key] = int(val)
         elif kind == "float":

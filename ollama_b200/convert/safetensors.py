@@ -43,13 +43,19 @@ class SafetensorsFile:
         self.metadata: dict[str, str] = hdr.pop("__metadata__", {}) or {}
         self.data_start = 8 + n
         self.entries: dict[str, tuple[str, tuple[int, ...], int, int]] = {}
+        if not isinstance(hdr, dict) or not isinstance(self.metadata, dict):
+            raise SafetensorsError(f"{self.path}: header is not a JSON object")
         for name, e in hdr.items():
-            b, end = e["data_offsets"]
-            if e["dtype"] not in _DTYPES or _DTYPES[e["dtype"]] is None:
-                raise SafetensorsError(f"{self.path}: tensor {name} has unsupported dtype {e['dtype']}")
-            if not 0 <= b <= end <= size - self.data_start:
+            try:
+                b, end = (int(v) for v in e["data_offsets"])
+                dtype, shape = e["dtype"], tuple(int(d) for d in e["shape"])
+            except (KeyError, TypeError, ValueError):
+                raise SafetensorsError(f"{self.path}: tensor {name} has a malformed header entry") from None
+            if dtype not in _DTYPES or _DTYPES[dtype] is None:
+                raise SafetensorsError(f"{self.path}: tensor {name} has unsupported dtype {dtype}")
+            if not 0 <= b <= end <= size - self.data_start or any(d < 0 for d in shape):
                 raise SafetensorsError(f"{self.path}: tensor {name} lies outside the file")
-            self.entries[name] = (e["dtype"], tuple(e["shape"]), b, end)
+            self.entries[name] = (dtype, shape, b, end)
         self._mm = mmap.mmap(self._f.fileno(), 0, access=mmap.ACCESS_READ) if size > 0 else None
 
     def keys(self) -> Iterator[str]:

@@ -289,3 +289,33 @@ def test_create_with_a_peft_adapter_directory(tmp_path, monkeypatch):
         assert g.kv["adapter.lora.alpha"] == 16.0 and set(g.tensors) == {"blk.0.attn_q.weight.lora_a", "blk.0.attn_q.weight.lora_b"}
     with pytest.raises(CreateError):
         list(create_model({"model": "bad", "adapters": files}))
+
+
+def test_safetensors_reader_survives_corrupted_headers(tmp_path):
+    """Byte flips and truncations of a valid file: the reader opens it or raises SafetensorsError, nothing else."""
+    import random
+    st = pytest.importorskip("safetensors.torch")
+    from ollama_b200.convert.safetensors import SafetensorsError, SafetensorsFile
+    p = str(tmp_path / "a.safetensors")
+    st.save_file({"a": torch.zeros(4, 8), "b": torch.ones(3, dtype=torch.float16), "c": torch.zeros((), dtype=torch.bfloat16)}, p)
+    data = open(p, "rb").read()
+    rnd = random.Random(3)
+    q = str(tmp_path / "m.safetensors")
+    opened = 0
+    for _ in range(800):
+        b = bytearray(data)
+        for _ in range(rnd.randint(1, 4)):
+            b[rnd.randrange(0, min(len(b), 300))] = rnd.randrange(256)
+        if rnd.random() < 0.2:
+            b = b[:rnd.randrange(1, len(b))]
+        with open(q, "wb") as f:
+            f.write(b)
+        try:
+            sf = SafetensorsFile(q)
+            for k in sf.keys():
+                sf.tensor(k)
+            sf.close()
+            opened += 1
+        except SafetensorsError:
+            pass
+    assert 0 < opened < 800
