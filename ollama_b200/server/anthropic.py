@@ -72,18 +72,32 @@ def _stop_reason(done_reason: str, has_tools: bool) -> str:
 
 
 def anthropic_routes(server) -> list[Route]:
-    from .openai import _native_objects
+    from .openai import FIELD_KINDS, _int, _native_objects, _num, _strs, bad_field
+    from .routes import APIError
+    from .routes import _check_types as check_native
+    _KINDS = {**FIELD_KINDS, "system": ("a string or an array of text blocks", lambda v: isinstance(v, (str, list))),
+              "stop_sequences": ("an array of strings", lambda v: isinstance(v, list) and _strs(v)),
+              "thinking": ("an object", lambda v: isinstance(v, dict)), "top_k": ("an integer", _int), "temperature": ("a number", _num)}
 
     async def messages(request: Request):
         try:
             req = json.loads(await request.body())
         except ValueError:
             return _err(400, "invalid JSON body")
+        bad = bad_field(req, _KINDS)
+        if bad:
+            return _err(400, bad)
         if not req.get("model"):
             return _err(400, "model is required")
         if not req.get("max_tokens"):
             return _err(400, "max_tokens is required")
-        native = _to_native(req)
+        try:
+            native = _to_native(req)
+            check_native(native)
+        except (TypeError, AttributeError, KeyError, ValueError) as e:       # content blocks of the wrong shape
+            return _err(400, f"invalid request: {e}")
+        except APIError as e:
+            return _err(e.status, e.msg)
         mid = "msg_" + uuid.uuid4().hex[:24]
         resp = await asyncio.to_thread(server._chat, native)
         if not native["stream"]:

@@ -117,19 +117,66 @@ async def _native_objects(resp) -> AsyncIterator[dict[str, Any]]:
                 yield json.loads(line)
 
 
+def _num(v: Any) -> bool:
+    return isinstance(v, (int, float)) and not isinstance(v, bool) and v == v and abs(v) != float("inf")
+
+
+def _int(v: Any) -> bool:
+    return isinstance(v, int) and not isinstance(v, bool)
+
+
+def _strs(v: Any) -> bool:
+    return isinstance(v, str) or (isinstance(v, list) and all(isinstance(x, str) for x in v))
+
+
+_OBJS = lambda v: isinstance(v, list) and all(isinstance(x, dict) for x in v)      # noqa: E731
+# JSON kinds of the request fields of the façade routes (openai/openai.go request structs)
+FIELD_KINDS: dict[str, tuple[str, Any]] = {
+    "model": ("a string", lambda v: isinstance(v, str)), "messages": ("an array of objects", _OBJS), "tools": ("an array of objects", _OBJS),
+    "stream": ("a boolean", lambda v: isinstance(v, bool)), "logprobs": ("a boolean or an integer", lambda v: isinstance(v, (bool, int))),
+    "max_tokens": ("an integer", _int), "max_completion_tokens": ("an integer", _int), "max_output_tokens": ("an integer", _int),
+    "seed": ("an integer", _int), "top_logprobs": ("an integer", _int), "dimensions": ("an integer", _int), "n": ("an integer", _int),
+    "temperature": ("a number", _num), "top_p": ("a number", _num), "frequency_penalty": ("a number", _num), "presence_penalty": ("a number", _num),
+    "response_format": ("an object", lambda v: isinstance(v, dict)), "stream_options": ("an object", lambda v: isinstance(v, dict)),
+    "reasoning": ("an object", lambda v: isinstance(v, dict)), "reasoning_effort": ("a string", lambda v: isinstance(v, str)),
+    "stop": ("a string or an array of strings", _strs), "suffix": ("a string", lambda v: isinstance(v, str)),
+    "prompt": ("a string or an array of strings", _strs), "encoding_format": ("a string", lambda v: isinstance(v, str)),
+    "instructions": ("a string", lambda v: isinstance(v, str)),
+    "input": ("a string or an array", lambda v: isinstance(v, (str, list))),
+}
+
+
+def bad_field(req: Any, kinds: dict[str, tuple[str, Any]] = FIELD_KINDS) -> str | None:
+    """Message for the first field whose JSON kind is not the one the API defines (null counts as absent)."""
+    if not isinstance(req, dict):
+        return "request body must be a JSON object"
+    for k, v in req.items():
+        spec = kinds.get(k)
+        if spec is not None and v is not None and not spec[1](v):
+            return f"invalid value for '{k}': expected {spec[0]}"
+    return None
+
+
 def openai_routes(server) -> list[Route]:
     async def chat_completions(request: Request):
         try:
             req = json.loads(await request.body())
         except ValueError:
             return _oa_err(400, "invalid JSON body")
+        if bad_field(req):
+            return _oa_err(400, bad_field(req))
         if not req.get("messages"):
             return _oa_err(400, "[] is too short - 'messages'")
         try:
             native: dict[str, Any] = {"model": req.get("model", ""), "messages": _messages(req), "options": _options(req),
                                       "stream": bool(req.get("stream")), "tools": req.get("tools") or []}
-        except ValueError as e:
-            return _oa_err(400, str(e))
+        except (ValueError, TypeError, AttributeError, KeyError) as e:
+            return _oa_err(400, f"invalid message: {e}")
+        try:
+            from .routes import APIError, _check_types
+            _check_types(native)
+        except APIError as e:
+            return _oa_err(e.status, e.msg)
         rf = req.get("response_format") or {}
         if rf.get("type") == "json_object":
             native["format"] = "json"
@@ -209,6 +256,8 @@ def openai_routes(server) -> list[Route]:
             req = json.loads(await request.body())
         except ValueError:
             return _oa_err(400, "invalid JSON body")
+        if bad_field(req):
+            return _oa_err(400, bad_field(req))
         prompt = req.get("prompt", "")
         if isinstance(prompt, list):
             prompt = prompt[0] if prompt else ""
@@ -247,6 +296,8 @@ def openai_routes(server) -> list[Route]:
             req = json.loads(await request.body())
         except ValueError:
             return _oa_err(400, "invalid JSON body")
+        if bad_field(req):
+            return _oa_err(400, bad_field(req))
         if req.get("input") in (None, "", []):
             return _oa_err(400, "invalid input")
         native = {"model": req.get("model", ""), "input": req["input"]}
@@ -284,6 +335,8 @@ def openai_routes(server) -> list[Route]:
             req = json.loads(await request.body())
         except ValueError:
             return _oa_err(400, "invalid JSON body")
+        if bad_field(req):
+            return _oa_err(400, bad_field(req))
         inp = req.get("input")
         msgs: list[dict[str, Any]] = []
         if req.get("instructions"):
@@ -292,10 +345,15 @@ def openai_routes(server) -> list[Route]:
             msgs.append({"role": "user", "content": inp})
         else:
             for it in inp or []:
+                if not isinstance(it, dict):
+                    return _oa_err(400, "invalid value for 'input': expected a string or an array of message objects")
                 c = it.get("content")
                 if isinstance(c, list):
-                    c = "".join(p.get("text", "") for p in c if p.get("type") in ("input_text", "output_text", "text"))
-                msgs.append({"role": "system" if it.get("role") == "developer" else it.get("role", "user"), "content": c or ""})
+                    c = "".join(p.get("text", "") for p in c if isinstance(p, dict) and p.get("type") in ("input_text", "output_text", "text"))
+                role = it.get("role", "user")
+                if not isinstance(role, str) or not isinstance(c or "", str):
+                    return _oa_err(400, "invalid value for 'input': a message needs a string role and text content")
+                msgs.append({"role": "system" if role == "developer" else role, "content": c or ""})
         opts = {}
         if req.get("max_output_tokens") is not None:
             opts["num_predict"] = req["max_output_tokens"]

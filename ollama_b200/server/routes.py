@@ -133,6 +133,7 @@ class Server:
             raise APIError(400, f"invalid JSON: {e}") from None
         if not isinstance(d, dict):
             raise APIError(400, "request body must be a JSON object")
+        _check_types(d)
         return d
 
     def _model(self, name: str) -> Model:
@@ -696,7 +697,7 @@ class Server:
 
     async def copy(self, request: Request):
         req = await self._json(request)
-        src, dst = parse_name(req.get("source", "")), parse_name(req.get("destination", ""))
+        src, dst = parse_name(req.get("source") or ""), parse_name(req.get("destination") or "")
         if not src.valid:
             return _err(400, f"source {req.get('source')!r} is invalid")
         if not dst.valid:
@@ -777,6 +778,55 @@ class Server:
 
 
 # ---------------------------------------------------------------------------------------------------------
+def _is_num(v: Any) -> bool:
+    return isinstance(v, (int, float)) and not isinstance(v, bool) and v == v and abs(v) != math.inf
+
+
+def _is_int(v: Any) -> bool:
+    return isinstance(v, int) and not isinstance(v, bool)
+
+
+# JSON kinds of the request fields of the native routes (api/types.go: a value of another kind fails to decode there)
+_FIELD_KINDS: dict[str, tuple[str, Callable[[Any], bool]]] = {
+    **{k: ("a string", lambda v: isinstance(v, str)) for k in (
+        "model", "name", "prompt", "suffix", "system", "template", "from", "quantize", "quantization", "source", "destination", "content",
+        "renderer", "parser", "draft_quantize")},
+    **{k: ("a boolean", lambda v: isinstance(v, bool)) for k in (
+        "stream", "raw", "verbose", "insecure", "truncate", "shift", "logprobs", "add_special")},
+    **{k: ("an object", lambda v: isinstance(v, dict)) for k in ("options", "parameters", "files", "adapters", "draft_files", "drafts")},
+    **{k: ("an array of objects", lambda v: isinstance(v, list) and all(isinstance(x, dict) for x in v)) for k in ("messages", "tools")},
+    **{k: ("an array of integers", lambda v: isinstance(v, list) and all(_is_int(x) for x in v)) for k in ("context", "tokens")},
+    "images": ("an array of strings", lambda v: isinstance(v, list) and all(isinstance(x, str) for x in v)),
+    "format": ("a string or an object", lambda v: isinstance(v, (str, dict))),
+    "keep_alive": ("a duration string or a number", lambda v: isinstance(v, str) or _is_num(v)),
+    "think": ("a boolean or a string", lambda v: isinstance(v, (bool, str))),
+    "top_logprobs": ("an integer", _is_int),
+    "dimensions": ("an integer", _is_int),
+    "input": ("a string or an array of strings", lambda v: isinstance(v, str) or (isinstance(v, list) and all(isinstance(x, str) for x in v))),
+    "license": ("a string or an array of strings", lambda v: isinstance(v, str) or (isinstance(v, list) and all(isinstance(x, str) for x in v))),
+}
+
+
+def _check_types(req: dict[str, Any]) -> None:
+    """400 for a field whose JSON kind is not the one the API defines (null counts as absent)."""
+    for k, v in req.items():
+        spec = _FIELD_KINDS.get(k)
+        if spec is not None and v is not None and not spec[1](v):
+            raise APIError(400, f"invalid request: {k!r} must be {spec[0]}")
+    for m in req.get("messages") or []:
+        for fk, ok, what in (("role", lambda v: isinstance(v, str), "a string"), ("content", lambda v: isinstance(v, str), "a string"),
+                             ("thinking", lambda v: isinstance(v, str), "a string"),
+                             ("tool_calls", lambda v: isinstance(v, list) and all(isinstance(x, dict) and isinstance(x.get("function"), dict) for x in v),
+                              "an array of tool calls"),
+                             ("images", lambda v: isinstance(v, list), "an array")):
+            if m.get(fk) is not None and not ok(m[fk]):
+                raise APIError(400, f"invalid request: message field {fk!r} must be {what}")
+    for t in req.get("tools") or []:
+        f = t.get("function")
+        if not isinstance(f, dict) or not isinstance(f.get("name"), str) or not isinstance(f.get("parameters") or {}, dict):
+            raise APIError(400, "invalid request: every tool needs a function object with a name")
+
+
 def _details(m: Any) -> dict[str, Any]:
     cfg = getattr(m, "config", {}) or {}
     return {"parent_model": getattr(m, "parent_model", ""), "format": cfg.get("model_format", ""), "family": cfg.get("model_family", ""),

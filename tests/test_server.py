@@ -215,3 +215,39 @@ def test_host_allow_list_and_cors(client):
     assert r.headers.get("access-control-allow-origin") == "http://localhost:3000"
     r = client.options("/api/generate", headers={"Origin": "http://evil.example.com", "Access-Control-Request-Method": "POST"})
     assert "access-control-allow-origin" not in r.headers
+
+
+def test_malformed_request_fields_are_client_errors(client):
+    """Every route answers a body whose fields have the wrong JSON kind with a 4xx (or a normal answer), never a 5xx:
+    the native routes check the kinds up front, the OpenAI and Anthropic façades check theirs before translating."""
+    import random
+    rnd = random.Random(11)
+    junk = [None, True, 0, -1, 1.5, "x", "", [], {}, [1, "a"], {"a": 1}, "tiny", [{"role": "user", "content": "hi"}], [{"role": 1, "content": [1]}],
+            {"type": "object"}, "json", 1e30, [[]], {"num_predict": 2}, {"num_predict": "x"}, [{"type": "function", "function": {"name": "f"}}],
+            [{"function": 1}], "5m", -5]
+    keys = {"/api/generate": ["model", "prompt", "suffix", "system", "template", "context", "stream", "raw", "format", "options", "keep_alive", "think", "images", "logprobs", "top_logprobs"],
+            "/api/chat": ["model", "messages", "tools", "stream", "format", "options", "keep_alive", "think", "logprobs", "top_logprobs"],
+            "/api/embed": ["model", "input", "truncate", "options", "dimensions", "keep_alive"], "/api/embeddings": ["model", "prompt", "options"],
+            "/api/show": ["model", "verbose", "system", "options"], "/api/tokenize": ["model", "content", "add_special"], "/api/detokenize": ["model", "tokens"],
+            "/api/create": ["model", "from", "files", "adapters", "template", "system", "parameters", "messages", "quantize", "stream", "draft_files", "license"],
+            "/api/copy": ["source", "destination"],
+            "/v1/chat/completions": ["model", "messages", "tools", "stream", "max_tokens", "temperature", "response_format", "stop", "logprobs", "top_logprobs", "stream_options", "reasoning_effort", "seed"],
+            "/v1/completions": ["model", "prompt", "max_tokens", "stream", "suffix", "stop"], "/v1/embeddings": ["model", "input", "encoding_format", "dimensions"],
+            "/v1/responses": ["model", "input", "instructions", "tools", "stream", "max_output_tokens"],
+            "/v1/messages": ["model", "messages", "max_tokens", "system", "tools", "stream", "thinking", "stop_sequences"]}
+    seen = set()
+    for _ in range(260):
+        path = rnd.choice(list(keys))
+        body = {k: rnd.choice(junk) for k in rnd.sample(keys[path], rnd.randint(0, len(keys[path])))}
+        if rnd.random() < 0.7:
+            body["model"] = "tiny"
+        if "stream" in keys[path]:
+            body["stream"] = False
+        if path == "/api/create":
+            body["model"] = rnd.choice(["t2", "", "a/b:c"])
+        r = client.post(path, json=body)
+        seen.add(r.status_code)
+        assert r.status_code < 500 or r.status_code in (501, 503), (path, body, r.status_code, r.text[:200])
+    assert 400 in seen and 200 in seen
+    assert client.post("/api/chat", json={"model": "tiny", "messages": "hi"}).json()["error"] == "invalid request: 'messages' must be an array of objects"
+    assert client.post("/v1/chat/completions", json={"model": "tiny", "messages": [{"role": "user", "content": "x"}], "temperature": "hot"}).status_code == 400
