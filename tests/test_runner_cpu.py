@@ -219,3 +219,48 @@ def test_grammar_waits_for_the_end_of_the_reasoning_block(tiny_llama_path):
         assert "".join(c.content for c in r.completion(req)) == "<t300><t301>"
     finally:
         r.close()
+
+
+def test_concurrent_random_requests_neither_fail_nor_stall(tiny_llama_path):
+    """Three client threads submit requests with random sampling settings, stop strings, grammars, cancellations, context
+    shifts and embeddings against three slots: every request ends, none with an error, and the runner stays healthy."""
+    import random
+    import threading
+    r = Runner(tiny_llama_path, RunnerOptions(num_ctx=96, num_parallel=3, device="cpu", num_batch=16))
+    errs, done = [], [0]
+
+    def worker(seed):
+        rr = random.Random(seed)
+        for _ in range(5):
+            prompt = [rr.randint(259, 31999) for _ in range(rr.randint(1, 90))]
+            sp = SamplingParams(temperature=rr.choice([0, 0.8]), seed=rr.randint(0, 99), top_k=rr.choice([1, 40]), repeat_penalty=rr.choice([1.0, 1.2]),
+                                logprobs=rr.random() < 0.2, top_logprobs=2)
+            req = CompletionRequest(prompt=prompt, sampling=sp, num_predict=rr.choice([1, 5, 30, 120]), stop=rr.choice([[], ["<t5"], ["a"]]),
+                                    grammar=rr.choice([None, None, 'root ::= "<t300>" ("<t301>")*']), shift=rr.random() < 0.7,
+                                    cache_prompt=rr.random() < 0.7, embedding=rr.random() < 0.1, ignore_eos=rr.random() < 0.5)
+            seq = r.submit(req)
+            cancel_at, k = rr.choice([None, None, 1, 3]), 0
+            while True:
+                try:
+                    ch = seq.out.get(timeout=60)
+                except Exception:
+                    errs.append(("stalled", seed))
+                    return
+                k += 1
+                if ch.error:
+                    errs.append(ch.error)
+                if ch.done or ch.error:
+                    break
+                if cancel_at and k >= cancel_at:
+                    seq.cancelled, cancel_at = True, None
+            done[0] += 1
+
+    ths = [threading.Thread(target=worker, args=(s,)) for s in range(3)]
+    try:
+        for t in ths:
+            t.start()
+        for t in ths:
+            t.join(timeout=240)
+        assert not errs and done[0] == 15 and not any(t.is_alive() for t in ths) and r.ping()
+    finally:
+        r.close()
