@@ -12,10 +12,11 @@ name                 reasoning block             tool call
 ``qwen3-thinking``   starts inside ``<think>``   same
 ``qwen3-coder``      none                        ``<tool_call><function=f><parameter=k>\\nv\\n</parameter></function></tool_call>``
 ``ministral``        ``[THINK]..[/THINK]``       ``[TOOL_CALLS]name[ARGS]{json}``
+``functiongemma``    none                        ``<start_function_call>call:name{k:<escape>v<escape>}<end_function_call>``
 ``passthrough``      none                        none
 ===================  ==========================  ===================================================================
 
-``harmony`` is handled by :mod:`ollama_b200.text.harmony`.  Renderers: ``qwen3-coder``.
+``harmony`` is handled by :mod:`ollama_b200.text.harmony`.  Renderers: ``qwen3-coder``, ``functiongemma``.
 """
 from __future__ import annotations
 
@@ -269,7 +270,72 @@ def _ministral_call(body: str) -> dict[str, Any] | None:
     return {"function": {"name": name.strip(), "arguments": obj}} if isinstance(obj, dict) and name.strip() else None
 
 
-PARSERS = ("qwen3", "qwen3-thinking", "qwen3-coder", "ministral", "passthrough")
+# -- functiongemma: call:name{key:value,...} with strings between <escape> marks ----------------------------------
+_ESC = "<escape>"
+
+
+def _fg_split(s: str) -> list[str]:
+    """Top-level comma split that respects {...}, [...] and <escape>...<escape> spans."""
+    parts, cur, depth, esc, i = [], [], 0, False, 0
+    while i < len(s):
+        if s.startswith(_ESC, i):
+            esc = not esc
+            cur.append(_ESC)
+            i += len(_ESC)
+            continue
+        ch = s[i]
+        if not esc and ch in "{[":
+            depth += 1
+        elif not esc and ch in "}]":
+            depth -= 1
+        if not esc and ch == "," and depth == 0:
+            if cur:
+                parts.append("".join(cur))
+                cur = []
+        else:
+            cur.append(ch)
+        i += 1
+    if cur:
+        parts.append("".join(cur))
+    return parts
+
+
+def _fg_value(v: str) -> Any:
+    if v.startswith(_ESC) and v.endswith(_ESC) and len(v) >= 2 * len(_ESC):
+        return v[len(_ESC):-len(_ESC)]
+    if v in ("true", "false"):
+        return v == "true"
+    if re.fullmatch(r"-?\d+", v):
+        return int(v)
+    if re.fullmatch(r"-?\d+\.\d+(?:[eE][-+]?\d+)?", v):
+        return float(v)
+    if v.startswith("[") and v.endswith("]"):
+        return [_fg_value(x) for x in _fg_split(v[1:-1])]
+    if v.startswith("{") and v.endswith("}"):
+        return _fg_object(v[1:-1])
+    return v
+
+
+def _fg_object(body: str) -> dict[str, Any]:
+    out: dict[str, Any] = {}
+    for part in _fg_split(body):
+        k, sep, v = part.partition(":")
+        if sep:
+            out[k] = _fg_value(v)
+    return out
+
+
+_FG_CALL = re.compile(r"call:([^{]+)\{(.*)\}", re.S)
+
+
+def _functiongemma_call(body: str) -> dict[str, Any] | None:
+    m = _FG_CALL.search(body)
+    if m is None:
+        return None
+    return {"function": {"name": m.group(1), "arguments": _fg_object(m.group(2))}}
+
+
+PARSERS = ("qwen3", "qwen3-thinking", "qwen3-coder", "ministral", "functiongemma", "passthrough")
 
 
 def parser_for(name: str | None, tools: list[dict[str, Any]] | None = None, think: Any = None,
@@ -288,6 +354,8 @@ def parser_for(name: str | None, tools: list[dict[str, Any]] | None = None, thin
                                tool_close="</tool_call>", decode_call=_json_call if want_tools else None)
     if name == "qwen3-coder":
         return TagStreamParser(tool_open="<tool_call>", tool_close="</tool_call>", decode_call=_xml_call(tools))
+    if name == "functiongemma":
+        return TagStreamParser(tool_open="<start_function_call>", tool_close="<end_function_call>", decode_call=_functiongemma_call)
     if name == "ministral":
         return TagStreamParser(think_open="[THINK]", think_close="[/THINK]", tool_open="[TOOL_CALLS]", tool_close=None,
                                decode_call=_ministral_call, body_end=_ministral_end)
@@ -399,7 +467,103 @@ def render_qwen3_coder(messages: list[dict[str, Any]], tools: list[dict[str, Any
     return "".join(sb)
 
 
-RENDERERS: dict[str, Callable[..., str]] = {"qwen3-coder": render_qwen3_coder}
+def _fg_arg(v: Any) -> str:
+    if isinstance(v, str):
+        return _ESC + v + _ESC
+    if isinstance(v, bool):
+        return "true" if v else "false"
+    if isinstance(v, float) and v == int(v):
+        return str(int(v))
+    if isinstance(v, dict):
+        return "{" + ",".join(f"{k}:{_fg_arg(v[k])}" for k in sorted(v)) + "}"
+    if isinstance(v, list):
+        return "[" + ",".join(_fg_arg(x) for x in v) + "]"
+    return str(v)
+
+
+def render_functiongemma(messages: list[dict[str, Any]], tools: list[dict[str, Any]] | None = None, think: Any = None) -> str:
+    """Gemma turns with function declarations in a developer turn, calls as ``call:name{k:v}`` and tool results as
+    ``response:name{...}`` inside the model turn (model/renderers/functiongemma.go:20-125): strings travel between
+    ``<escape>`` marks, keys are sorted, types are upper-cased."""
+    default = "You can do function calling with the following functions:"
+    sb = ["<bos>"]
+    system, loop = "", list(messages)
+    if loop and loop[0].get("role") in ("system", "developer"):
+        system, loop = loop[0].get("content", "") or "", loop[1:]
+    if system or tools:
+        sb.append("<start_of_turn>developer\n")
+        if system:
+            sb.append(system.strip())
+        if tools:
+            if system:
+                sb.append("\n")
+            if system.strip() != default:
+                sb.append(default)
+        for t in tools or []:
+            f = t.get("function", {})
+            sb.append(f"<start_function_declaration>declaration:{f.get('name', '')}{{description:{_ESC}{f.get('description', '')}{_ESC}")
+            params = f.get("parameters") or {}
+            props, ptype = params.get("properties") or {}, params.get("type") or ""
+            if props or ptype or "properties" in params:
+                sb.append(",parameters:{")
+                items = []
+                if props:
+                    inner = []
+                    for name in sorted(props):
+                        pr = props[name] or {}
+                        ty = pr.get("type")
+                        ty = ty if isinstance(ty, str) else (ty[0] if ty else "")
+                        inner.append(f"{name}:{{description:{_ESC}{pr.get('description', '')}{_ESC}" + (f",type:{_ESC}{ty.upper()}{_ESC}" if ty else "") + "}")
+                    items.append("properties:{" + ",".join(inner) + "}")
+                if params.get("required"):
+                    items.append("required:[" + ",".join(_ESC + r + _ESC for r in params["required"]) + "]")
+                if ptype:
+                    items.append(f"type:{_ESC}{str(ptype).upper()}{_ESC}")
+                sb.append(",".join(items) + "}")
+            sb.append("}<end_function_declaration>")
+        sb.append("<end_of_turn>\n")
+    prev = ""
+    for i, m in enumerate(loop):
+        role, content = m.get("role", "user"), m.get("content", "") or ""
+        if role == "assistant":
+            if prev != "tool_response":
+                sb.append("<start_of_turn>model\n")
+            prev = ""
+            if content:
+                sb.append(content.strip())
+            calls = m.get("tool_calls") or []
+            for c in calls:
+                f = c.get("function", {})
+                args = f.get("arguments") or {}
+                sb.append("<start_function_call>call:" + f.get("name", "") + "{" + ",".join(f"{k}:{_fg_arg(args[k])}" for k in sorted(args)) + "}<end_function_call>")
+            if calls and i + 1 < len(loop) and loop[i + 1].get("role") == "tool":
+                sb.append("<start_function_response>")
+                prev = "tool_call"
+            else:
+                sb.append("<end_of_turn>\n")
+        elif role == "tool":
+            name = ""
+            for j in range(i - 1, -1, -1):          # the call this result answers: n-th result after the last assistant turn with calls
+                if loop[j].get("role") == "assistant" and loop[j].get("tool_calls"):
+                    n = sum(1 for k in range(j + 1, i) if loop[k].get("role") == "tool")
+                    if n < len(loop[j]["tool_calls"]):
+                        name = loop[j]["tool_calls"][n].get("function", {}).get("name", "")
+                    break
+            if prev != "tool_call":
+                sb.append("<start_function_response>")
+            sb.append("response:" + name + "{" + _fg_arg(content) + "}<end_function_response>")
+            prev = "tool_response"
+        else:
+            if role != "user" or prev != "tool_response":
+                sb.append(f"<start_of_turn>{role}\n")
+            prev = ""
+            sb.append(content.strip() + "<end_of_turn>\n")
+    if prev != "tool_response":
+        sb.append("<start_of_turn>model\n")
+    return "".join(sb)
+
+
+RENDERERS: dict[str, Callable[..., str]] = {"qwen3-coder": render_qwen3_coder, "functiongemma": render_functiongemma}
 
 
 def renderer_for(name: str | None) -> Callable[..., str] | None:

@@ -488,3 +488,43 @@ def test_parsers_reject_mutated_input_with_their_own_error_types():
             parse_modelfile(mutate(mf)).create_request()
         except (ModelfileError, OptionError):
             pass
+
+
+def test_functiongemma_renderer_and_parser():
+    """Expected prompts are the golden strings of the reference's renderer tests (model/renderers/functiongemma_test.go)."""
+    from ollama_b200.text.builtin import parser_for, render_functiongemma
+    weather = [{"type": "function", "function": {"name": "get_weather", "description": "Get weather", "parameters": {
+        "type": "object", "properties": {"city": {"type": "string", "description": "City"}}}}}]
+    decl = ("<start_function_declaration>declaration:get_weather{description:<escape>Get weather<escape>,parameters:{properties:{city:{description:"
+            "<escape>City<escape>,type:<escape>STRING<escape>}},type:<escape>OBJECT<escape>}}<end_function_declaration>")
+    hello = [{"role": "user", "content": "Hello!"}]
+    assert render_functiongemma(hello) == "<bos><start_of_turn>user\nHello!<end_of_turn>\n<start_of_turn>model\n"
+    assert render_functiongemma([{"role": "system", "content": "You are helpful"}] + hello) == \
+        "<bos><start_of_turn>developer\nYou are helpful<end_of_turn>\n<start_of_turn>user\nHello!<end_of_turn>\n<start_of_turn>model\n"
+    assert render_functiongemma([]) == "<bos><start_of_turn>model\n"
+    q = [{"role": "user", "content": "Weather?"}]
+    assert render_functiongemma([{"role": "system", "content": "You are a weather expert."}] + q, weather) == \
+        ("<bos><start_of_turn>developer\nYou are a weather expert.\nYou can do function calling with the following functions:" + decl +
+         "<end_of_turn>\n<start_of_turn>user\nWeather?<end_of_turn>\n<start_of_turn>model\n")
+    head = "<bos><start_of_turn>developer\nYou can do function calling with the following functions:" + decl + "<end_of_turn>\n<start_of_turn>user\nWeather?<end_of_turn>\n<start_of_turn>model\n"
+    assert render_functiongemma(q, weather) == head
+    call = {"role": "assistant", "content": "Let me check.", "tool_calls": [{"function": {"name": "get_weather", "arguments": {"city": "Paris"}}}]}
+    assert render_functiongemma(q + [call, {"role": "tool", "content": "Sunny"}], weather) == \
+        head + "Let me check.<start_function_call>call:get_weather{city:<escape>Paris<escape>}<end_function_call><start_function_response>response:get_weather{<escape>Sunny<escape>}<end_function_response>"
+    add = [{"type": "function", "function": {"name": "add", "description": "Add numbers", "parameters": {
+        "type": "object", "properties": {"a": {"type": "number"}, "b": {"type": "number"}}}}}]
+    got = render_functiongemma([{"role": "user", "content": "Add"}, {"role": "assistant", "tool_calls": [{"function": {"name": "add", "arguments": {"b": 2, "a": 1.0}}}]},
+                                {"role": "tool", "content": "3"}], add)
+    assert got.endswith("<start_of_turn>model\n<start_function_call>call:add{a:1,b:2}<end_function_call><start_function_response>response:add{<escape>3<escape>}<end_function_response>")
+    assert "a:{description:<escape><escape>,type:<escape>NUMBER<escape>},b:{description:<escape><escape>,type:<escape>NUMBER<escape>}" in got
+    req = [{"type": "function", "function": {"name": "get_weather", "description": "Gets the weather for a given city", "parameters": {
+        "type": "object", "required": ["city"], "properties": {"city": {"type": "string", "description": "City Name"}, "country": {"type": "string", "description": "Country Name"}}}}}]
+    assert ("country:{description:<escape>Country Name<escape>,type:<escape>STRING<escape>}},required:[<escape>city<escape>],type:<escape>OBJECT<escape>}}"
+            "<end_function_declaration>") in render_functiongemma(q, req)
+    # the parser reads what the renderer writes, nested values included, at any chunking
+    out = ("I will call it.<start_function_call>call:plan{city:<escape>Paris, France<escape>,days:3,ratio:1.5,ok:true,tags:[<escape>a,b<escape>,2],"
+           "opts:{unit:<escape>C<escape>,deep:{x:1}}}<end_function_call>")
+    for step in (1, 5, 1000):
+        c, t, calls = _feed(parser_for("functiongemma", weather), out, step)
+        assert c == "I will call it." and t == "" and calls == [{"function": {"name": "plan", "arguments": {
+            "city": "Paris, France", "days": 3, "ratio": 1.5, "ok": True, "tags": ["a,b", 2], "opts": {"unit": "C", "deep": {"x": 1}}}}}]
