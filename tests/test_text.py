@@ -528,3 +528,34 @@ def test_functiongemma_renderer_and_parser():
         c, t, calls = _feed(parser_for("functiongemma", weather), out, step)
         assert c == "I will call it." and t == "" and calls == [{"function": {"name": "plan", "arguments": {
             "city": "Paris, France", "days": 3, "ratio": 1.5, "ok": True, "tags": ["a,b", 2], "opts": {"unit": "C", "deep": {"x": 1}}}}}]
+
+
+@pytest.mark.skipif(_reference_template_dir() is None, reason="the reference source tree is not available")
+def test_qwen3_coder_renderer_matches_the_reference_golden_prompts():
+    """Two conversations of the reference's renderer test (model/renderers/qwen3coder_test.go): tool definitions with extra
+    schema keys, a tool call with its response, parallel calls whose responses share one user turn."""
+    import os
+    from ollama_b200.text.builtin import render_qwen3_coder
+    path = os.path.join(os.path.dirname(_reference_template_dir()), "model", "renderers", "qwen3coder_test.go")
+    with open(path, encoding="utf-8") as f:
+        src = f.read()
+
+    def golden(case):
+        i = src.index(f'name: "{case}"')
+        j = src.index("expected: `", i) + len("expected: `")
+        return src[j:src.index("`,", j)]
+
+    msgs = [{"role": "system", "content": "You are a helpful assistant with access to tools."}, {"role": "user", "content": "What is the weather like in San Francisco?"},
+            {"role": "assistant", "content": "I'll check the weather in San Francisco for you.", "tool_calls": [{"function": {"name": "get_weather", "arguments": {"unit": "fahrenheit"}}}]},
+            {"role": "tool", "content": '{"location": "San Francisco, CA", "temperature": 68, "condition": "partly cloudy", "humidity": 65, "wind_speed": 12}', "tool_name": "get_weather"},
+            {"role": "user", "content": "That sounds nice! What about New York?"}]
+    tools = [{"type": "function", "function": {"name": "get_weather", "description": "Get the current weather in a given location", "parameters": {
+        "required": ["unit"], "properties": {"unit": {"type": "string", "enum": ["celsius", "fahrenheit"], "description": "The unit of temperature"}}}}}]
+    assert render_qwen3_coder(msgs, tools) == golden("with tools and response")
+    msgs = [{"role": "system", "content": "You are a helpful assistant with access to tools."}, {"role": "user", "content": "call double(1) and triple(2)"},
+            {"role": "assistant", "content": "I'll call double(1) and triple(2) for you.", "tool_calls": [
+                {"function": {"name": "double", "arguments": {"number": "1"}}}, {"function": {"name": "triple", "arguments": {"number": "2"}}}]},
+            {"role": "tool", "content": '{"number": 2}', "tool_name": "double"}, {"role": "tool", "content": '{"number": 6}', "tool_name": "triple"}]
+    tools = [{"type": "function", "function": {"name": n, "description": d, "parameters": {"properties": {"number": {"type": "string", "description": pd}}}}}
+             for n, d, pd in (("double", "Double a number", "The number to double"), ("triple", "Triple a number", "The number to triple"))]
+    assert render_qwen3_coder(msgs, tools) == golden("parallel tool calls")
