@@ -559,3 +559,29 @@ def test_qwen3_coder_renderer_matches_the_reference_golden_prompts():
     tools = [{"type": "function", "function": {"name": n, "description": d, "parameters": {"properties": {"number": {"type": "string", "description": pd}}}}}
              for n, d, pd in (("double", "Double a number", "The number to double"), ("triple", "Triple a number", "The number to triple"))]
     assert render_qwen3_coder(msgs, tools) == golden("parallel tool calls")
+
+
+def test_harmony_header_forms():
+    """Header variants of the reference's parser test (harmony/harmonyparser_test.go:9-92): recipient before or after the
+    channel, a constrain tag with or without a space, extra tokens after the recipient."""
+    cases = [("assistant<|channel|>analysis", "analysis", ""),
+             ("assistant<|channel|>analysis to=functions.get_weather", "analysis", "functions.get_weather"),
+             ("assistant to=functions.get_weather<|channel|>analysis", "analysis", "functions.get_weather"),
+             ("to=functions.get_weather<|channel|>analysis", "analysis", "functions.get_weather"),
+             ("assistant to=functions.get_weather abc<|channel|>analysis", "analysis", "functions.get_weather"),
+             ("assistant<|channel|>commentary to=functions.get_weather <|constrain|>json", "commentary", "functions.get_weather"),
+             ("assistant to=functions.get_weather<|channel|>commentary <|constrain|>json", "commentary", "functions.get_weather"),
+             ("assistant<|channel|>commentary to=functions.get_weather<|constrain|>json", "commentary", "functions.get_weather"),
+             ("assistant to=functions.get_weather<|channel|>commentary<|constrain|>json", "commentary", "functions.get_weather")]
+    for header, channel, recipient in cases:
+        p = harmony.HarmonyParser(harmony.FunctionNameMap())
+        p._parse_header(header)
+        assert (p.channel, p.recipient) == (channel, recipient), header
+    # and end to end: a call in the commentary channel with a constrain tag glued to the recipient
+    p = harmony.HarmonyParser(harmony.FunctionNameMap())
+    th, ct, calls = "", "", []
+    for piece in ("<|channel|>analysis<|message|>need weather<|end|><|start|>assistant<|channel|>commentary to=functions.get_weather<|constrain|>json<|message|>",
+                  '{"city":"Paris"}<|call|>'):
+        a, b, c = p.add(piece)
+        th, ct, calls = th + a, ct + b, calls + c
+    assert th == "need weather" and ct == "" and calls[0]["function"]["name"] == "get_weather" and calls[0]["function"]["arguments"] == {"city": "Paris"}
