@@ -23,25 +23,48 @@ _ANY_TAG = re.compile("|".join(re.escape(t) for t in TAGS))
 HEADER, BODY, BETWEEN = range(3)
 
 
+_BUILTIN_TOOLS = ("browser.open", "browser.search", "browser.find", "python")
+
+
 class FunctionNameMap:
-    """user tool name <-> identifier-safe harmony name."""
+    """user tool name <-> identifier-safe harmony name (harmony/harmonyparser.go:476-556).
+
+    Spaces, hyphens and periods become underscores; letters, digits (Unicode categories L* and Nd), ``_`` and ``$`` stay;
+    everything else is dropped; an empty result is ``unnamed``; a leading digit gets an underscore in front; a name that
+    is taken gets ``_2``, ``_3`` ...; the built-in tool names are kept as they are.
+    """
 
     def __init__(self):
         self.to_h: dict[str, str] = {}
         self.from_h: dict[str, str] = {}
 
-    def convert(self, name: str) -> str:
-        if name in self.to_h:
-            return self.to_h[name]
-        h = re.sub(r"[^A-Za-z0-9_$]", "_", name.replace("-", "_").replace(" ", "_")) or "unnamed"
-        if h[0].isdigit():
-            h = "_" + h
-        base, k = h, 2
+    @staticmethod
+    def valid_chars(name: str) -> str:
+        import unicodedata
+        out = []
+        for ch in name:
+            if ch in " -.":
+                out.append("_")
+            elif ch in "_$" or unicodedata.category(ch)[0] == "L" or unicodedata.category(ch) == "Nd":
+                out.append(ch)
+        h = "".join(out) or "unnamed"
+        return "_" + h if h[0] in "0123456789" else h
+
+    def add(self, name: str) -> str:
+        """A new harmony name for ``name``, even when the same user name was added before (duplicate tool definitions)."""
+        base = self.valid_chars(name)
+        h, k = base, 2
         while h in self.from_h:
             h = f"{base}_{k}"
             k += 1
+        if name in _BUILTIN_TOOLS:
+            h = name
         self.to_h[name], self.from_h[h] = h, name
         return h
+
+    def convert(self, name: str) -> str:
+        """The harmony name of ``name``: the one it already has, else a new one."""
+        return self.to_h[name] if name in self.to_h else self.add(name)
 
     def original(self, h: str) -> str:
         return self.from_h.get(h, h)

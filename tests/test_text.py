@@ -585,3 +585,21 @@ def test_harmony_header_forms():
         a, b, c = p.add(piece)
         th, ct, calls = th + a, ct + b, calls + c
     assert th == "need weather" and ct == "" and calls[0]["function"]["name"] == "get_weather" and calls[0]["function"]["arguments"] == {"city": "Paris"}
+
+
+def test_harmony_function_name_map_follows_the_reference_table():
+    """harmony/harmonyparser_test.go:473-560."""
+    M = harmony.FunctionNameMap
+    for name, want in (("get weather", "get_weather"), ("get-weather", "get_weather"), ("get.weather", "get_weather"), ("get weather!", "get_weather"),
+                       ("a🫠bc", "abc"), ("🫠", "unnamed"), ("123", "_123"), ("$", "$"), ("𝓸𝓵𝓵𝓪𝓶𝓪", "𝓸𝓵𝓵𝓪𝓶𝓪"), ("ⓞⓛⓛⓐⓜⓐ123", "_123")):
+        assert M.valid_chars(name) == want, name
+    for names, want in ((["get weather", "get weather"], ["get_weather", "get_weather_2"]),
+                        (["get weather", "get_weather", "get-weather", "something-different"], ["get_weather", "get_weather_2", "get_weather_3", "something_different"]),
+                        (["a", "a", "b", "a", "a", "b", "a"], ["a", "a_2", "b", "a_3", "a_4", "b_2", "a_5"]),
+                        (["browser.open", "python", "not.a.built-in.function", "browser.not_a_real_built_in"],
+                         ["browser.open", "python", "not_a_built_in_function", "browser_not_a_real_built_in"])):
+        m = M()
+        got = [m.add(n) for n in names]
+        assert got == want and all(m.original(h) == n for n, h in zip(names, got))
+    m = M()
+    assert m.convert("get-w") == "get_w" and m.convert("get-w") == "get_w" and m.original("get_w") == "get-w"      # lookups do not rename
