@@ -150,7 +150,7 @@ class ToolParser:
             return [], content + out
         if end:
             self.buf = self.buf[end:]
-        return calls, content.rstrip() if calls or self.in_call else content
+        return calls, content        # text before the tag is passed on unchanged (tools/tools_test.go "text before tool call")
 
     def flush(self) -> str:
         out, self.buf = self.buf, ""

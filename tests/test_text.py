@@ -603,3 +603,42 @@ def test_harmony_function_name_map_follows_the_reference_table():
         assert got == want and all(m.original(h) == n for n, h in zip(names, got))
     m = M()
     assert m.convert("get-w") == "get_w" and m.convert("get-w") == "get_w" and m.original("get_w") == "get-w"      # lookups do not rename
+
+
+def test_generic_tool_parser_on_the_reference_cases():
+    """A selection of the reference's tool-parser table (tools/tools_test.go:156-790): tag and bare-JSON forms, lists,
+    names that are prefixes of other names, arguments before the name, JSON that is not a call, split input."""
+    def tool(n, props=()):
+        return {"type": "function", "function": {"name": n, "description": "d", "parameters": {"type": "object", "properties": {k: {"type": "string"} for k in props}}}}
+    tools = [tool("get_temperature", ("format", "city")), tool("get_conditions", ("location",)), tool("say_hello"), tool("say_hello_world"),
+             tool("get_address", ("location",)), tool("add", ("a", "b"))]
+
+    def run(tag, inputs):
+        p, c, calls = ToolParser(tools, tag), "", []
+        for s in inputs:
+            k, t = p.add(s)
+            calls, c = calls + k, c + t
+        return c + p.flush(), [(x["function"]["name"], x["function"]["arguments"]) for x in calls]
+
+    london = ("get_temperature", {"city": "London", "format": "fahrenheit"})
+    tokyo = ("get_conditions", {"location": "Tokyo"})
+    cases = [
+        ("<tool_call>", ['<tool_call>{"name": "get_conditions", "arguments": {"location": "San Francisco"}}</tool_call>'], "", [("get_conditions", {"location": "San Francisco"})]),
+        ("<tool_call>", ['Let me check the weather. <tool_call>{"name": "get_temperature", "arguments": {"city": "New York"}}</tool_call>'],
+         "Let me check the weather. ", [("get_temperature", {"city": "New York"})]),
+        ("<tool_call>", ["Let me say hello to the user. I'll use the say_hello tool. "], "Let me say hello to the user. I'll use the say_hello tool. ", []),
+        ("[TOOL_CALLS]", ['[TOOL_CALLS] [{"name": "get_temperature", "arguments": {"city": "London", "format": "fahrenheit"}}, '
+                          '{"name": "get_conditions", "arguments": {"location": "Tokyo"}}][/TOOL_CALLS]'], "", [london, tokyo]),
+        ("<tool_call>", ['Okay, let\'s call both tools! <tool_call>{"name": "get_temperature", "arguments": {"city": "London", "format": "fahrenheit"}}</tool_call>'
+                         '<tool_call>{"name": "get_conditions", "arguments": {"location": "Tokyo"}}</tool_call>'], "Okay, let's call both tools! ", [london, tokyo]),
+        ("<tool_call>", ['<tool_call>{"name": "say_hello", "arguments": {}}</tool_call><tool_call>{"name": "get_temperature", "arguments": '
+                         '{"city": "London", "format": "fahrenheit"}}</tool_call>'], "", [("say_hello", {}), london]),
+        ("{", ['{"name": "get_temperature", "arguments": {"city": "London", "format": "fahrenheit"}}'], "", [london]),
+        ("{", ['{"name": "search", ', '"arguments": {"query": "What is the capital of Canada?"}}'],
+         '{"name": "search", "arguments": {"query": "What is the capital of Canada?"}}', []),
+        ("<tool_call>", ['<tool_call>{"name": "say_hello_world", "arguments": {}}'], "", [("say_hello_world", {})]),
+        ("<tool_call>", ['<tool_call>{"name": "say_hello', '_world", ', '"arguments": {}}</tool_call>'], "", [("say_hello_world", {})]),
+        ("<tool_call>", ['<tool_call>{"arguments": {"a": "5", "b": "10"}, "name": "add"}</tool_call>'], "", [("add", {"a": "5", "b": "10"})]),
+    ]
+    for tag, inputs, content, calls in cases:
+        assert run(tag, inputs) == (content, calls), inputs
