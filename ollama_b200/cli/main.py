@@ -196,7 +196,7 @@ def _upload(c: Client, path: str) -> str:
 def cmd_create(args) -> int:
     from ..store.modelfile import parse_modelfile
     path = args.file or "Modelfile"
-    with open(path, encoding="utf-8") as f:
+    with open(path, "rb") as f:
         mf = parse_modelfile(f.read())
     req = mf.create_request()
     req["model"] = args.model
@@ -225,6 +225,8 @@ def cmd_create(args) -> int:
             lp2 = local(p)
             if not lp2:
                 raise SystemExit(f"Error: {p}: no such file")
+            if key == "draft_paths" and lp and os.path.realpath(lp2) == os.path.realpath(lp):
+                raise SystemExit("Error: DRAFT must not reference the same local path as FROM")
             req.setdefault("adapters" if key == "adapter_paths" else "draft_files", {})[os.path.basename(lp2)] = _upload(c, lp2)
     last: dict[str, Any] = {}
     for ev in c.create(**req):

@@ -87,33 +87,43 @@ def _quote(s: str) -> str:
     return s
 
 
+def _unquote(s: str) -> tuple[str, bool]:
+    """Value of a (possibly quoted) buffer and whether its quotes are closed (parser/parser.go:656-675)."""
+    if s.startswith('"""'):
+        return (s[3:-3], True) if len(s) >= 6 and s.endswith('"""') else ("", False)
+    if s.startswith('"'):
+        return (s[1:-1], True) if len(s) >= 2 and s.endswith('"') else ("", False)
+    return s, True
+
+
 def _take_value(text: str, i: int) -> tuple[str, int]:
-    """Read one value starting at ``i`` (after leading blanks): triple-quoted, quoted, or to end of line."""
+    """Read one value starting at ``i``: the rest of the line, or, when it opens with ``"`` or ``\"\"\"``, every line
+    up to the first one that ends with the closing quotes (so quotes inside a line never end the value)."""
     n = len(text)
-    while i < n and text[i] in " \t":
-        i += 1
-    if text.startswith('"""', i):
-        j = text.find('"""', i + 3)
-        if j < 0:
-            raise ModelfileError("unterminated multiline string")
-        val = text[i + 3:j]
-        k = text.find("\n", j + 3)
-        return val, (n if k < 0 else k + 1)
-    if i < n and text[i] == '"':
-        j = i + 1
-        while j < n and text[j] != '"' and text[j] != "\n":
-            j += 1
-        if j < n and text[j] == '"':
-            k = text.find("\n", j + 1)
-            return text[i + 1:j], (n if k < 0 else k + 1)
-    k = text.find("\n", i)
-    end = n if k < 0 else k
-    return text[i:end].rstrip(" \t\r"), (n if k < 0 else k + 1)
+    j = i
+    while True:
+        k = text.find("\n", j)
+        val, ok = _unquote(text[i:(n if k < 0 else k)].strip())
+        if ok:
+            return val, (n if k < 0 else k + 1)
+        if k < 0:
+            raise ModelfileError("unexpected EOF: unterminated quoted value")
+        j = k + 1
 
 
-def parse_modelfile(text: str) -> Modelfile:
+def decode_modelfile(data: bytes) -> str:
+    """Text of a Modelfile: UTF-8 unless a byte-order mark says UTF-16, as the reference's BOM-overriding
+    reader does (parser/parser.go:462-463)."""
+    if data[:2] in (b"\xff\xfe", b"\xfe\xff"):
+        return data.decode("utf-16")
+    return data.decode("utf-8-sig", "replace")
+
+
+def parse_modelfile(text: str | bytes) -> Modelfile:
+    if isinstance(text, (bytes, bytearray)):
+        text = decode_modelfile(bytes(text))
     text = text.replace("\r\n", "\n")
-    if text.startswith("﻿"):
+    if text.startswith("\ufeff"):
         text = text[1:]
     mf = Modelfile()
     i, n = 0, len(text)
@@ -145,8 +155,8 @@ def parse_modelfile(text: str) -> Modelfile:
             while e < n and not text[e].isspace():
                 e += 1
             pname = text[k:e].lower()
-            if not pname:
-                raise ModelfileError("missing parameter name")
+            if not pname or e >= n or text[e] == "\n":
+                raise ModelfileError("unexpected EOF: PARAMETER needs a name and a value")
             val, i = _take_value(text, e)
             if pname not in DEPRECATED_PARAMETERS or True:
                 mf.commands.append(Command(pname, val, True))
@@ -159,6 +169,8 @@ def parse_modelfile(text: str) -> Modelfile:
             role = text[k:e].lower()
             if role not in ROLES:
                 raise ModelfileError('message role must be one of "system", "user", or "assistant"')
+            if e >= n or text[e] == "\n":
+                raise ModelfileError("unexpected EOF: MESSAGE needs a role and a text")
             val, i = _take_value(text, e)
             mf.commands.append(Command("message", f"{role}: {val}"))
         else:

@@ -11,7 +11,7 @@ DEFAULT_HOST = "registry.ollama.ai"
 DEFAULT_NAMESPACE = "library"
 DEFAULT_TAG = "latest"
 
-_HOST = re.compile(r"^[A-Za-z0-9][A-Za-z0-9_.:\-]{0,349}$")
+_HOST = re.compile(r"^[A-Za-z0-9_][A-Za-z0-9_.:\-]{0,349}$")
 _NAMESPACE = re.compile(r"^[A-Za-z0-9_][A-Za-z0-9_\-]{0,79}$")
 _MODEL = re.compile(r"^[A-Za-z0-9_][A-Za-z0-9_.\-]{0,79}$")
 _TAG = re.compile(r"^[A-Za-z0-9_][A-Za-z0-9_.\-]{0,79}$")

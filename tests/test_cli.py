@@ -75,6 +75,13 @@ def test_create_list_show_run_cp_rm(server, monkeypatch):
     assert rc == 0
 
 
+def test_create_refuses_a_draft_that_is_the_model_itself(server):
+    """parser/parser_test.go:93-121 of the reference: DRAFT and FROM must not be the same local path."""
+    (server / "SameDraft").write_text("FROM ./m.gguf\nDRAFT ./m.gguf\n")
+    with pytest.raises(SystemExit, match="DRAFT must not reference the same local path as FROM"):
+        run_cli("create", "same", "-f", str(server / "SameDraft"))
+
+
 def test_bench_formats(server):
     run_cli("create", "tiny", "-f", str(server / "Modelfile"))
     rc, out, _ = run_cli("bench", "--model", "tiny", "--epochs", "2", "--max-tokens", "4", "--prompt-tokens", "8", "--format", "json")

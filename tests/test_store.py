@@ -22,6 +22,34 @@ def test_names():
         assert not parse_name(bad).valid
 
 
+def test_names_on_the_reference_table():
+    """Validity, round trip, parts and shortest display of the reference's name tests (types/model/name_test.go:14-333)."""
+    p80, p350 = "8" * 80, "3" * 350
+    valid = {"": False, "_why/_the/_lucky:_stiff": True, "h/n/m:t": True, "host/namespace/model:tag": True, "host/namespace/model": False,
+             "namespace/model": False, "model": False, f"{p80}/{p80}/{p80}:{p80}": True, f"{p350}/{p80}/{p80}:{p80}": True, "h/nn/mm:t": True,
+             "m": False, "n/m:": False, "h/n/m": False, "@t": False, "m@d": False, "^": False, "mm:": False, "/nn/mm": False, "//": False,
+             "//mm": False, "hh//": False, "//mm:@": False, "00@": False, "@": False, "-hh/nn/mm:tt": False, "hh/-nn/mm:tt": False,
+             "hh/nn/-mm:tt": False, "hh/nn/mm:-tt": False, "host:https/namespace/model:tag": True, "host/name:space/model:tag": False,
+             f"{p350}3/n/m:t": False, f"h/{p80}8/m:t": False, "h/n.s/m:t": False, "h./n/m:t": True}
+    for s, want in valid.items():
+        n = parse_name(s, fill_defaults=False)
+        assert n.valid == want, s
+        if want:
+            assert str(n) == s
+    parts = {"scheme://host:port/namespace/model:tag": ("host:port", "namespace", "model", "tag"),
+             "host:port/namespace/model": ("host:port", "namespace", "model", ""), "namespace/model": ("", "namespace", "model", ""),
+             "model": ("", "", "model", ""), "registry.ollama.ai/library/dolphin-mistral:7b-v2.6-dpo-laser-q6_K":
+             ("registry.ollama.ai", "library", "dolphin-mistral", "7b-v2.6-dpo-laser-q6_K")}
+    for s, want in parts.items():
+        n = parse_name(s, fill_defaults=False)
+        assert (n.host, n.namespace, n.model, n.tag) == want
+    assert parse_name("namespace/model").filepath() == "registry.ollama.ai/namespace/model/latest"
+    assert parse_name("model").filepath() == "registry.ollama.ai/library/model/latest"
+    for s, want in {"registry.ollama.ai/library/model:latest": "model:latest", "registry.ollama.ai/namespace/model:tag": "namespace/model:tag",
+                    "host/namespace/model:tag": "host/namespace/model:tag", "host/library/model:tag": "host/library/model:tag"}.items():
+        assert parse_name(s).display() == want
+
+
 def test_modelfile_parser():
     mf = parse_modelfile('# comment\nFROM llama3\nPARAMETER temperature 0.5\nparameter stop "<|a|>"\nPARAMETER stop b\n'
                          'SYSTEM """multi\nline"""\nMESSAGE user hello there\nTEMPLATE "{{ .Prompt }}"\nLICENSE MIT\nADAPTER ./lora.gguf\n')
@@ -42,6 +70,63 @@ def test_modelfile_parser():
     with pytest.raises(OptionError, match="unknown parameter"):
         parse_modelfile("FROM x\nPARAMETER nope 1\n").create_request()
     assert parse_modelfile("FROM x\nPARAMETER mirostat 1\n").create_request().get("parameters") in (None, {})   # deprecated: ignored
+
+
+def _cmds(text):
+    return [("model" if c.name == "from" and not c.is_parameter else c.name, c.args) for c in parse_modelfile(text).commands]
+
+
+def test_modelfile_on_the_reference_tables():
+    """Commands and values of the reference's parser tests (parser/parser_test.go:123-766): trimming, quoting over several lines,
+    quotes inside a value, parameters, messages, comments, UTF-16 input and the inputs that must be refused."""
+    ok = [
+        ('FROM "FOO  BAR  "', [("model", "FOO  BAR  ")]),
+        ('FROM "FOO BAR"\nPARAMETER param1 value1', [("model", "FOO BAR"), ("param1", "value1")]),
+        ("FROM     FOOO BAR    ", [("model", "FOOO BAR")]),
+        ("FROM /what/is/the path ", [("model", "/what/is/the path")]),
+        ("FROM llama3:7b-instruct-q4_K_M", [("model", "llama3:7b-instruct-q4_K_M")]),
+        ("PARAMETER param1 value1\nFROM foo", [("param1", "value1"), ("model", "foo")]),
+        ("PARAMETER what the \nFROM lemons make lemonade ", [("what", "the"), ("model", "lemons make lemonade")]),
+        ('\nFROM "     model 1"\nADAPTER      adapter3\nLICENSE "MIT       "\nPARAMETER param1        value1\nTEMPLATE """   {{ a }}\n\n{{ b }}   """    \n',
+         [("model", "     model 1"), ("adapter", "adapter3"), ("license", "MIT       "), ("param1", "value1"), ("template", "   {{ a }}\n\n{{ b }}   ")]),
+        ("\nFROM foo\nMESSAGE system You are a file parser. Always parse things.", [("model", "foo"), ("message", "system: You are a file parser. Always parse things.")]),
+        ('\nFROM foo\nMESSAGE system """\nYou are a multiline file parser.\n"""\n\t\t\t', [("model", "foo"), ("message", "system: \nYou are a multiline file parser.\n")]),
+        ('\nFROM foo\nSYSTEM """\nThis is a\nmultiline system.\n"""\n\t\t\t', [("model", "foo"), ("system", "\nThis is a\nmultiline system.\n")]),
+        ('\nFROM foo\nSYSTEM """This is a\nmultiline system."""\n\t\t\t', [("model", "foo"), ("system", "This is a\nmultiline system.")]),
+        ('\nFROM foo\nSYSTEM """\nThis is a multiline system with "quotes".\n"""\n', [("model", "foo"), ("system", '\nThis is a multiline system with "quotes".\n')]),
+        ('\nFROM foo\nSYSTEM """\nUse """three quotes""" inside a line\n"""\n', [("model", "foo"), ("system", '\nUse """three quotes""" inside a line\n')]),
+        ('\nFROM foo\nSYSTEM """"""\n', [("model", "foo"), ("system", "")]),
+        ('\nFROM foo\nSYSTEM ""\n', [("model", "foo"), ("system", "")]),
+        ('\nFROM foo\nSYSTEM "\'"\n', [("model", "foo"), ("system", "'")]),
+        ('\nFROM foo\nSYSTEM """\'\'"\'""\'""\'"\'\'\'\'\'""\'""\'"""\n', [("model", "foo"), ("system", '\'\'"\'""\'""\'"\'\'\'\'\'""\'""\'')]),
+        ('\nFROM foo\nTEMPLATE """\n{{ .Prompt }}\n"""', [("model", "foo"), ("template", "\n{{ .Prompt }}\n")]),
+        ("\n# comment\nFROM foo\n\t", [("model", "foo")]),
+        ("\nFROM base\nDRAFT ./assistant\n", [("model", "base"), ("draft", "./assistant")]),
+        ("FROM test\n\tSYSTEM 你好👋", [("model", "test"), ("system", "你好👋")]),
+    ]
+    for text, want in ok:
+        assert _cmds(text) == want, text
+    params = {"numa true": ("numa", "true"), "top_p 1.0": ("top_p", "1.0"), "stop ### User:": ("stop", "### User:"), "stop ### User: ": ("stop", "### User:"),
+              'stop "### User:"': ("stop", "### User:"), 'stop "### User: "': ("stop", "### User: "), 'stop """### User:"""': ("stop", "### User:"),
+              'stop """### User:\n"""': ("stop", "### User:\n"), "stop <|endoftext|>": ("stop", "<|endoftext|>"), "stop </s>": ("stop", "</s>")}
+    for line, want in params.items():
+        assert _cmds(f"FROM foo\nPARAMETER {line}\n") == [("model", "foo"), want], line
+    for bad in ("", "PARAMETER param1 value1", "\nFROM foo\nPARAMETER param1\n", "\nFROM foo\nBADCOMMAND param1 value1\n", "\nFROM foo\nMESSAGE badguy I'm a bad guy!\n",
+                "\nFROM foo\nMESSAGE system\n", "\nFROM foo\nMESSAGE system", '\nFROM foo\nSYSTEM """This is a multiline system.""\n\t\t\t', '\nFROM foo\nSYSTEM "\n\t\t\t'):
+        with pytest.raises(ModelfileError):
+            parse_modelfile(bad)
+    text = "FROM bob\nPARAMETER param1 1\nPARAMETER param2 4096\nSYSTEM You are a utf16 file. 你好👋\n"
+    want = [("model", "bob"), ("param1", "1"), ("param2", "4096"), ("system", "You are a utf16 file. 你好👋")]
+    for data in (b"\xff\xfe" + text.encode("utf-16-le"), b"\xfe\xff" + text.encode("utf-16-be"), b"\xef\xbb\xbf" + text.encode(), text.encode()):
+        assert _cmds(data) == want
+    # serialise -> parse gives the same commands (TestParseFileFormatParseFile)
+    for text in ('\nFROM foo\nADAPTER adapter1\nLICENSE """\nVery long and boring legal text.\nBlah blah blah.\n"Oh look, a quote!"\n"""\n\nPARAMETER param1 value1\nTEMPLATE template1\n'
+                 'MESSAGE system """\nYou are a store greeter. Always respond with "Hello!".\n"""\nMESSAGE user Hey there!\n', '\nFROM foo\nSYSTEM ""\n'):
+        assert _cmds(str(parse_modelfile(text))) == _cmds(text)
+    req = parse_modelfile("FROM test\nPARAMETER temperature 0.5\nPARAMETER top_k 1\nSYSTEM You are a bot.\nLICENSE license1\nLICENSE license2\n"
+                          "MESSAGE user Hello there!\nMESSAGE assistant Hi! How are you?\n").create_request()
+    assert req == {"from": "test", "license": ["license1", "license2"], "system": "You are a bot.", "parameters": {"temperature": 0.5, "top_k": 1},
+                   "messages": [{"role": "user", "content": "Hello there!"}, {"role": "assistant", "content": "Hi! How are you?"}]}
 
 
 def test_manifest_blob_store(tmp_path, monkeypatch):
