@@ -23,7 +23,7 @@ class ResponseError(Exception):
 
 class Client:
     def __init__(self, base: str | None = None, timeout: float | None = None):
-        self.base = (base or str(envconfig.host())).rstrip("/")
+        self.base = (base or str(envconfig.connectable_host())).rstrip("/")
         self.timeout = timeout
 
     # -- transport ----------------------------------------------------------------------------------

@@ -89,7 +89,7 @@ def cmd_serve(args) -> int:
     print(f"ollama-b200 {VERSION} listening on {h.netloc}", file=sys.stderr)
     for k, (v, desc) in envconfig.as_map().items():
         print(f"  {k}={v}", file=sys.stderr)
-    uvicorn.run(create_app(), host=h.host, port=h.port, log_level="info" if envconfig.log_level() <= 20 else "warning")
+    uvicorn.run(create_app(), host=h.host or "0.0.0.0", port=h.port, log_level="info" if envconfig.log_level() <= 20 else "warning")
     return 0
 
 

@@ -107,7 +107,7 @@ class HostURL:
 def host() -> HostURL:
     """OLLAMA_HOST -> scheme/host/port; default http://127.0.0.1:11434."""
     default_port = 11434
-    s = var("OLLAMA_HOST")
+    s = var("OLLAMA_HOST").strip()
     scheme, sep, hostport = s.partition("://")
     if not sep:
         scheme, hostport = "http", s
@@ -123,8 +123,7 @@ def host() -> HostURL:
     if m:
         h = m.group(1) if m.group(1) is not None else m.group(3)
         ps = m.group(2) if m.group(2) is not None else m.group(4)
-        h = h or "127.0.0.1"
-        try:
+        try:            # an empty host (":1234") stays empty: every interface when listening, this machine when connecting
             port = int(ps)
             if not 0 <= port <= 65535:
                 port = default_port
@@ -137,6 +136,17 @@ def host() -> HostURL:
         except ValueError:
             h = hostport
     return HostURL(scheme, h, port, path)
+
+
+def connectable_host() -> HostURL:
+    """``host()`` for a client: the unspecified addresses a server may listen on (0.0.0.0, ::, empty) become the loopback
+    address of the same family (envconfig/config.go ConnectableHost)."""
+    u = host()
+    if u.host in ("", "0.0.0.0"):
+        u.host = "127.0.0.1"
+    elif u.host == "::":
+        u.host = "::1"
+    return u
 
 
 def allowed_origins() -> list[str]:
@@ -161,7 +171,8 @@ def load_timeout() -> float:
 
 
 def log_level() -> int:
-    """Python logging level: INFO by default, DEBUG for OLLAMA_DEBUG=1/true, TRACE (5) for 2."""
+    """Python logging level: INFO by default, DEBUG for OLLAMA_DEBUG=1/true, TRACE (5) for 2 and above; negative values
+    lower the verbosity (-1 WARNING, -2 ERROR)."""
     s = var("OLLAMA_DEBUG")
     if not s:
         return 20
@@ -171,6 +182,8 @@ def log_level() -> int:
         i = int(s)
     except ValueError:
         return 20
+    if i < 0:
+        return min(50, 20 - 10 * i)
     return 20 if i == 0 else (10 if i == 1 else 5)
 
 
@@ -202,8 +215,25 @@ def sched_spread() -> bool:
     return _bool("OLLAMA_SCHED_SPREAD")
 
 
+def _no_cloud_config() -> bool:
+    """``disable_ollama_cloud`` of ~/.ollama/server.json; a missing or unreadable file counts as false."""
+    import json
+    try:
+        with open(os.path.join(os.path.expanduser("~"), ".ollama", "server.json"), encoding="utf-8") as f:
+            return bool(json.load(f).get("disable_ollama_cloud", False))
+    except (OSError, ValueError, AttributeError):
+        return False
+
+
 def no_cloud() -> bool:
-    return _bool("OLLAMA_NO_CLOUD")
+    """Cloud features are off when OLLAMA_NO_CLOUD is set or the server's config file disables them."""
+    return _bool("OLLAMA_NO_CLOUD") or _no_cloud_config()
+
+
+def no_cloud_source() -> str:
+    """Which of the two switched cloud features off: "env", "config", "both" or "none"."""
+    e, c = _bool("OLLAMA_NO_CLOUD"), _no_cloud_config()
+    return "both" if e and c else "env" if e else "config" if c else "none"
 
 
 def context_length() -> int:

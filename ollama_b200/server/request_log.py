@@ -45,7 +45,7 @@ class RequestLogger:
             f.write(text + "\n")
         with open(stem + ".sh", "w", encoding="utf-8") as f:
             f.write("#!/bin/sh\n"
-                    f'curl -sS -X POST "${{OLLAMA_HOST:-{envconfig.host()}}}{route}" -H "Content-Type: application/json" '
+                    f'curl -sS -X POST "${{OLLAMA_HOST:-{envconfig.connectable_host()}}}{route}" -H "Content-Type: application/json" '
                     f'--data-binary "@{os.path.basename(stem)}.json"\n')
         os.chmod(stem + ".sh", 0o755)
         return stem + ".json"

@@ -182,7 +182,7 @@ def test_envconfig(monkeypatch):
     for k in ("OLLAMA_HOST", "OLLAMA_KEEP_ALIVE", "OLLAMA_ORIGINS", "OLLAMA_DEBUG", "OLLAMA_NUM_PARALLEL"):
         monkeypatch.delenv(k, raising=False)
     assert str(envconfig.host()) == "http://127.0.0.1:11434" and envconfig.keep_alive() == 300 and envconfig.num_parallel() == 1
-    cases = {"1.2.3.4": "http://1.2.3.4:11434", ":1234": "http://127.0.0.1:1234", "example.com:99": "http://example.com:99",
+    cases = {"1.2.3.4": "http://1.2.3.4:11434", ":1234": "http://:1234", "example.com:99": "http://example.com:99",
              "https://example.com": "https://example.com:443", "http://h/path": "http://h:80/path", "[::1]": "http://[::1]:11434",
              "[::1]:8080": "http://[::1]:8080", "0.0.0.0:66000": "http://0.0.0.0:11434", "ollama.com": "https://ollama.com:443"}
     for k, v in cases.items():
@@ -198,6 +198,61 @@ def test_envconfig(monkeypatch):
     assert envconfig.log_level() == 5
     monkeypatch.setenv("OLLAMA_NUM_PARALLEL", "x")
     assert envconfig.num_parallel() == 1 and "OLLAMA_MAX_QUEUE" in envconfig.as_map()
+
+
+def test_envconfig_on_the_reference_tables(monkeypatch):
+    """Hosts, booleans, unsigned values, durations, quoting and log levels of envconfig/config_test.go:13-330 of the reference."""
+    hosts = {"": "http://127.0.0.1:11434", "1.2.3.4": "http://1.2.3.4:11434", ":1234": "http://:1234", "1.2.3.4:1234": "http://1.2.3.4:1234",
+             "example.com": "http://example.com:11434", ":0": "http://:0", ":66000": "http://:11434", ":-1": "http://:11434",
+             "[::1]": "http://[::1]:11434", "[::]": "http://[::]:11434", "::1": "http://[::1]:11434", "[::1]:1337": "http://[::1]:1337",
+             " 1.2.3.4 ": "http://1.2.3.4:11434", '"1.2.3.4"': "http://1.2.3.4:11434", ' " 1.2.3.4 " ': "http://1.2.3.4:11434",
+             "'1.2.3.4'": "http://1.2.3.4:11434", "http://1.2.3.4": "http://1.2.3.4:80", "http://1.2.3.4:4321": "http://1.2.3.4:4321",
+             "https://1.2.3.4": "https://1.2.3.4:443", "https://example.com/ollama": "https://example.com:443/ollama",
+             "ollama.com": "https://ollama.com:443"}
+    for v, want in hosts.items():
+        monkeypatch.setenv("OLLAMA_HOST", v)
+        assert str(envconfig.host()) == want, v
+    connectable = {"": "http://127.0.0.1:11434", "127.0.0.1:1234": "http://127.0.0.1:1234", "0.0.0.0": "http://127.0.0.1:11434",
+                   "0.0.0.0:1234": "http://127.0.0.1:1234", "[::]": "http://[::1]:11434", "[::]:1234": "http://[::1]:1234",
+                   "[::1]:1234": "http://[::1]:1234", "192.168.1.5:8080": "http://192.168.1.5:8080", "example.com": "http://example.com:11434",
+                   "https://0.0.0.0:4321": "https://127.0.0.1:4321", ":1234": "http://127.0.0.1:1234"}
+    for v, want in connectable.items():
+        monkeypatch.setenv("OLLAMA_HOST", v)
+        assert str(envconfig.connectable_host()) == want, v
+    for v, want in {"": False, "true": True, "false": False, "1": True, "0": False, "random": True, "something": True}.items():
+        monkeypatch.setenv("OLLAMA_NOPRUNE", v)
+        assert envconfig.no_prune() is want, v
+    for v, want in {"0": 0, "1": 1, "1337": 1337, "": 512, "-1": 512, "0o10": 512, "0x10": 512, "string": 512}.items():
+        monkeypatch.setenv("OLLAMA_MAX_QUEUE", v)
+        assert envconfig.max_queue() == want, v
+    inf = math.inf
+    for v, want in {"": 300, "1s": 1, "1m": 60, "1h": 3600, "5m0s": 300, "1h2m3s": 3723, "0": 0, "60": 60, "3600": 3600, "-0": 0, "-1": inf,
+                    "-1m": inf, " ": 300, "???": 300, "1d": 300, "1y": 300, "1w": 300}.items():
+        monkeypatch.setenv("OLLAMA_KEEP_ALIVE", v)
+        assert envconfig.keep_alive() == want, v
+    for v, want in {"": 300, "1s": 1, "5m0s": 300, "1h2m3s": 3723, "0": inf, "60": 60, "-0": inf, "-1": inf, "-1m": inf, "???": 300, "1d": 300}.items():
+        monkeypatch.setenv("OLLAMA_LOAD_TIMEOUT", v)
+        assert envconfig.load_timeout() == want, v
+    for v, want in {"value": "value", " value ": "value", " 'value' ": "value", ' "value" ': "value", " ' value ' ": " value ", ' " value " ': " value "}.items():
+        monkeypatch.setenv("OLLAMA_LLM_LIBRARY", v)
+        assert envconfig.llm_library() == want, v
+    for v, want in {"": 20, "false": 20, "f": 20, "0": 20, "true": 10, "t": 10, "1": 10, "2": 5, "-1": 30, "-2": 40}.items():
+        monkeypatch.setenv("OLLAMA_DEBUG", v)
+        assert envconfig.log_level() == want, v
+
+
+def test_no_cloud_from_environment_or_config_file(monkeypatch, tmp_path):
+    """envconfig/config_test.go:332-420 of the reference."""
+    for env, content, disabled, source in (("", None, False, "none"), ("1", None, True, "env"), ("", '{"disable_ollama_cloud": true}', True, "config"),
+                                           ("1", '{"disable_ollama_cloud": true}', True, "both"), ("", '{"disable_ollama_cloud": false}', False, "none"),
+                                           ("", "{invalid json", False, "none")):
+        home = tmp_path / f"h{abs(hash((env, content)))}"
+        (home / ".ollama").mkdir(parents=True)
+        if content is not None:
+            (home / ".ollama" / "server.json").write_text(content)
+        monkeypatch.setenv("HOME", str(home))
+        monkeypatch.setenv("OLLAMA_NO_CLOUD", env)
+        assert envconfig.no_cloud() is disabled and envconfig.no_cloud_source() == source
 
 
 def test_options_and_wire_values():
