@@ -19,36 +19,13 @@ from typing import Any
 
 from .. import envconfig
 from ..api.client import Client, ResponseError
+from ..utils.format import human_ago, human_bytes
 from ..version import VERSION
 
 
 # ---------------------------------------------------------------------------------------------------
 # formatting helpers
 # ---------------------------------------------------------------------------------------------------
-def human_bytes(n: float) -> str:
-    for unit, div in (("TB", 1e12), ("GB", 1e9), ("MB", 1e6), ("KB", 1e3)):
-        if n >= div:
-            v = n / div
-            return f"{v:.1f} {unit}" if v < 10 else f"{v:.0f} {unit}"
-    return f"{int(n)} B"
-
-
-def human_ago(iso: str) -> str:
-    import datetime as dt
-    try:
-        t = dt.datetime.fromisoformat(iso.replace("Z", "+00:00"))
-    except ValueError:
-        return iso
-    s = (dt.datetime.now(dt.timezone.utc) - t).total_seconds()
-    sign = "ago" if s >= 0 else "from now"
-    s = abs(s)
-    for unit, div in (("year", 31536000), ("month", 2592000), ("week", 604800), ("day", 86400), ("hour", 3600), ("minute", 60)):
-        if s >= div:
-            n = int(s // div)
-            return f"{n} {unit}{'s' if n != 1 else ''} {sign}"
-    return "Less than a minute " + sign if sign == "ago" else "Less than a minute from now"
-
-
 def table(rows: list[list[str]], header: list[str]) -> str:
     cols = [header] + rows
     widths = [max(len(r[i]) for r in cols) for i in range(len(header))]

@@ -31,10 +31,8 @@ class CreateError(Exception):
 
 
 def _param_size(n: int) -> str:
-    for unit, div in (("T", 1e12), ("B", 1e9), ("M", 1e6), ("K", 1e3)):
-        if n >= div:
-            return f"{n / div:.1f}{unit}"
-    return str(n)
+    from ..utils.format import human_number
+    return human_number(n)
 
 
 def gguf_config(path: str) -> dict[str, Any]:
