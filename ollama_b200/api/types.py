@@ -137,7 +137,7 @@ def format_parameters(params: dict[str, list[str]]) -> dict[str, Any]:
             else:
                 out[key] = list(vals)
         except ValueError:
-            raise OptionError(f"invalid {'int' if kind.startswith('int') else 'float' if kind == 'float' else 'bool'} value {vals}") from None
+            raise OptionError(f"invalid {'int' if kind.startswith('int') else 'float' if kind == 'float' else 'bool'} value [{' '.join(vals)}]") from None
     return out
 
 

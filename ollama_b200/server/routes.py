@@ -38,7 +38,7 @@ from ..text import harmony
 from ..text.builtin import parser_for
 from ..text.gotemplate import TemplateError
 from ..text.thinking import ThinkingParser, infer_tags
-from ..text.tools import ToolParser, infer_tag
+from ..text.tools import ToolParser, infer_tag, tool_call_id
 from .caches import ModelListCache, ModelShowCache
 from .prompt import PromptRenderer, chat_prompt
 from .sched import Scheduler, SchedulerError
@@ -412,7 +412,7 @@ class Server:
             self.sched.release(ref)
             return _err(400, str(e))
         rend = self._renderer(model, runner)
-        msgs = list(model.messages) + [dict(m) for m in messages]
+        msgs = list(model.messages) + [{**m, "role": str(m.get("role", "")).lower()} for m in messages]     # roles compare in lower case
         if model.system and not any(m.get("role") == "system" for m in msgs):
             msgs.insert(0, {"role": "system", "content": model.system})
         if think == "max" and rend.is_harmony:
@@ -446,13 +446,20 @@ class Server:
         tool_parser = ToolParser(tools, infer_tag(rend.template_source)) if tools and hp is None and bp is None else None
         show_thinking = think is None or think_enabled(think)
 
+        n_calls = 0
+
         def gen() -> Iterator[dict[str, Any]]:
+            nonlocal n_calls
             for ch in runner.completion(creq):
                 content, thinking, calls = ch.content, "", []
                 if hp is not None:
                     thinking, content, calls = hp.add(content)
                 elif bp is not None:
                     content, thinking, calls = bp.add(content, ch.done)
+                    for c in calls:         # calls of the built-in parsers get their id and running index here
+                        c.setdefault("id", tool_call_id())
+                        c["function"].setdefault("index", n_calls)
+                        n_calls += 1
                 else:
                     if tp is not None:
                         thinking, content = tp.add(content)

@@ -142,6 +142,30 @@ def test_builtin_renderer_and_parser_from_the_model_config(client):
     assert j["done"] and j["eval_count"] == 4 and "content" in j["message"]
 
 
+def test_tool_calls_of_the_builtin_parser_carry_ids_and_indices_and_roles_compare_in_lower_case(client, monkeypatch):
+    """A scripted model output through /api/chat: each parsed call gets an id and its running index (api/types_test.go:408-430 of the
+    reference: the index is always present); an upper-case role is the same as its lower-case form (api/types_test.go:286-307)."""
+    from ollama_b200.engine.runner import CompletionChunk, Runner
+    script = ["Let me look.", "<tool_call>\n<function=f>\n<parameter=x>\n3\n</parameter>\n</function>\n</tool_call>",
+              "<tool_call>\n<function=f>\n<parameter=x>\n4\n</parameter>\n</function>\n</tool_call>"]
+
+    def scripted(self, req):
+        for i, piece in enumerate(script):
+            yield CompletionChunk(content=piece)
+        yield CompletionChunk(done=True, done_reason="stop", eval_count=len(script))
+
+    monkeypatch.setattr(Runner, "completion", scripted)
+    assert client.post("/api/create", json={"model": "coder2", "from": "tiny", "renderer": "qwen3-coder", "parser": "qwen3-coder", "stream": False}).status_code == 200
+    tools = [{"type": "function", "function": {"name": "f", "parameters": {"type": "object", "properties": {"x": {"type": "integer"}}}}}]
+    j = client.post("/api/chat", json={"model": "coder2", "messages": [{"role": "USER", "content": "hi"}], "tools": tools, "stream": False}).json()
+    calls = j["message"]["tool_calls"]
+    assert [c["function"]["index"] for c in calls] == [0, 1] and [c["function"]["arguments"] for c in calls] == [{"x": 3}, {"x": 4}]
+    assert all(c["id"].startswith("call_") for c in calls) and calls[0]["id"] != calls[1]["id"] and j["message"]["content"] == "Let me look."
+    d = client.post("/api/chat", json={"model": "coder2", "messages": [{"role": "SYSTEM", "content": "be kind"}, {"role": "User", "content": "hi"}],
+                                       "_debug_render_only": True}).json()["_debug_info"]["rendered_template"]
+    assert d.startswith("<|im_start|>system\nbe kind<|im_end|>\n<|im_start|>user\nhi<|im_end|>")
+
+
 def test_metrics_route_reports_runner_totals(client):
     client.post("/api/generate", json={"model": "tiny", "prompt": "<t400><t401>", "stream": False, "options": {"num_predict": 3}})
     r = client.get("/metrics")
