@@ -53,6 +53,7 @@ def _options(req: dict[str, Any]) -> dict[str, Any]:
 
 def _messages(req: dict[str, Any]) -> list[dict[str, Any]]:
     out = []
+    call_names: dict[str, str] = {}        # id of an earlier call -> its function, to name a tool answer that only gives the id
     for m in req.get("messages") or []:
         role = m.get("role", "")
         if role == "developer":
@@ -87,18 +88,69 @@ def _messages(req: dict[str, Any]) -> list[dict[str, Any]]:
                     except ValueError:
                         raise ValueError("invalid tool call arguments") from None
                 calls.append({"id": tc.get("id", ""), "function": {"name": fn.get("name", ""), "arguments": args or {}}})
+                if tc.get("id"):
+                    call_names[tc["id"]] = fn.get("name", "")
             d["tool_calls"] = calls
         if role == "tool":
             d["tool_call_id"] = m.get("tool_call_id", "")
-            d["tool_name"] = m.get("name", "")
+            d["tool_name"] = m.get("name") or call_names.get(d["tool_call_id"], "")
         out.append(d)
     return out
 
 
 def _finish(reason: str, has_tools: bool) -> str:
-    if has_tools:
-        return "tool_calls"
-    return "length" if reason == "length" else "stop"
+    """Finish reason of a whole answer: calls turn "stop" into "tool_calls"; any other reason (length, ...) passes through."""
+    reason = reason or "stop"
+    return "tool_calls" if reason == "stop" and has_tools else reason
+
+
+class ChatStreamState:
+    """What a chat stream remembers between native responses: whether the role went out and whether a call was sent."""
+
+    def __init__(self):
+        self.first_sent = False
+        self.tool_sent = False
+
+
+def chat_stream_frames(state: ChatStreamState, obj: dict[str, Any], base: dict[str, Any], want_usage: bool) -> list[dict[str, Any]]:
+    """Chunks of an OpenAI chat stream for one native response (middleware/openai.go:80-164, openai/openai.go:344-395 of the
+    reference).  The role is on the first chunk only; reasoning that arrives together with content or calls goes out as a chunk
+    of its own first; the closing response with an empty message adds no empty content chunk; the finish reason has its own
+    chunk with an empty delta ("tool_calls" replaces "stop" once a call was streamed, other reasons pass through); the usage
+    chunk, when asked for, has an empty choices list."""
+    msg = obj.get("message") or {}
+    content, thinking, calls = msg.get("content", "") or "", msg.get("thinking", "") or "", msg.get("tool_calls") or []
+    done = bool(obj.get("done"))
+    frames: list[dict[str, Any]] = []
+    trailer = done and state.first_sent and not content and not thinking and not calls and not obj.get("logprobs")
+    if not trailer:
+        deltas: list[dict[str, Any]] = []
+        if thinking and (content or calls):
+            deltas.append({"reasoning": thinking})
+        d: dict[str, Any] = {"content": content}
+        if thinking and not deltas:
+            d["reasoning"] = thinking
+        if calls:
+            d["tool_calls"] = _tool_calls(calls)
+            state.tool_sent = True
+        deltas.append(d)
+        if not state.first_sent:
+            deltas[0] = {"role": "assistant", **deltas[0]}
+            state.first_sent = True
+        for i, d in enumerate(deltas):
+            choice: dict[str, Any] = {"index": 0, "delta": d, "finish_reason": None}
+            if obj.get("logprobs") and i == 0:
+                choice["logprobs"] = {"content": obj["logprobs"]}
+            frames.append(dict(base, choices=[choice]))
+    if done:
+        reason = obj.get("done_reason") or "stop"
+        if reason == "stop" and state.tool_sent:
+            reason = "tool_calls"
+        frames.append(dict(base, choices=[{"index": 0, "delta": {}, "finish_reason": reason}]))
+        if want_usage:
+            n_in, n_out = obj.get("prompt_eval_count", 0), obj.get("eval_count", 0)
+            frames.append(dict(base, choices=[], usage={"prompt_tokens": n_in, "completion_tokens": n_out, "total_tokens": n_in + n_out}))
+    return frames
 
 
 def _tool_calls(calls: list[dict[str, Any]]) -> list[dict[str, Any]]:
@@ -218,35 +270,13 @@ def openai_routes(server) -> list[Route]:
         async def sse():
             base = {"id": cid, "object": "chat.completion.chunk", "created": created, "model": req.get("model", ""),
                     "system_fingerprint": "fp_ollama"}
-            saw_tools = False
-            first = True
+            state = ChatStreamState()
             async for obj in _native_objects(resp):
                 if "error" in obj:
                     yield f"data: {json.dumps({'error': {'message': obj['error'], 'type': 'api_error'}})}\n\n".encode()
                     break
-                msg = obj.get("message", {})
-                delta: dict[str, Any] = {"content": msg.get("content", "")}
-                if first:
-                    delta["role"] = "assistant"
-                    first = False
-                if msg.get("thinking"):
-                    delta["reasoning"] = msg["thinking"]
-                if msg.get("tool_calls"):
-                    delta["tool_calls"] = _tool_calls(msg["tool_calls"])
-                    saw_tools = True
-                choice: dict[str, Any] = {"index": 0, "delta": delta, "finish_reason": None}
-                if obj.get("logprobs"):
-                    choice["logprobs"] = {"content": obj["logprobs"]}
-                if obj.get("done"):
-                    choice["finish_reason"] = _finish(obj.get("done_reason", ""), saw_tools)
-                chunk = dict(base, choices=[choice])
-                if want_usage:
-                    chunk["usage"] = None
-                yield f"data: {json.dumps(chunk)}\n\n".encode()
-                if obj.get("done") and want_usage:
-                    usage = {"prompt_tokens": obj.get("prompt_eval_count", 0), "completion_tokens": obj.get("eval_count", 0),
-                             "total_tokens": obj.get("prompt_eval_count", 0) + obj.get("eval_count", 0)}
-                    yield f"data: {json.dumps(dict(base, choices=[], usage=usage))}\n\n".encode()
+                for frame in chat_stream_frames(state, obj, base, want_usage):
+                    yield f"data: {json.dumps(frame, separators=(',', ':'))}\n\n".encode()
             yield b"data: [DONE]\n\n"
 
         return StreamingResponse(sse(), media_type="text/event-stream")

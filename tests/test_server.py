@@ -232,6 +232,56 @@ def test_openai_and_anthropic_facades(client):
     assert "event: message_start" in r.text and "event: message_stop" in r.text
 
 
+def test_openai_stream_frames_and_message_conversion_follow_the_reference_cases():
+    """The wire cases of middleware/openai_test.go:92-812 and :926-1220 of the reference on the two pure converters."""
+    from ollama_b200.server.openai import ChatStreamState, _messages, _options, chat_stream_frames
+    base = {"id": "chatcmpl-test", "object": "chat.completion.chunk", "created": 1, "model": "m", "system_fingerprint": "fp_ollama"}
+
+    def run(objs, usage=False):
+        st, out = ChatStreamState(), []
+        for o in objs:
+            out += chat_stream_frames(st, o, base, usage)
+        return out
+
+    # reasoning and answer in one response: two chunks, then the finish chunk with an empty delta, then usage with no choices
+    f = run([{"message": {"thinking": "reasoning", "content": "final answer"}, "done": True, "done_reason": "stop", "prompt_eval_count": 3, "eval_count": 2}], True)
+    assert len(f) == 4 and f[0]["choices"][0]["delta"] == {"role": "assistant", "reasoning": "reasoning"} and f[0]["choices"][0]["finish_reason"] is None
+    assert f[1]["choices"][0]["delta"] == {"content": "final answer"} and f[2]["choices"][0] == {"index": 0, "delta": {}, "finish_reason": "stop"}
+    assert f[3]["choices"] == [] and f[3]["usage"]["total_tokens"] == 5
+    # reasoning with a call, not final: two chunks and nothing else
+    call = {"id": "call_234", "function": {"index": 0, "name": "get_weather", "arguments": {"location": "Portland"}}}
+    f = run([{"message": {"thinking": "reasoning", "tool_calls": [call]}, "done": False}])
+    assert len(f) == 2 and "tool_calls" not in f[0]["choices"][0]["delta"] and f[1]["choices"][0]["delta"]["tool_calls"][0]["function"]["name"] == "get_weather"
+    assert f[1]["choices"][0]["delta"]["tool_calls"][0]["function"]["arguments"] == '{"location": "Portland"}'
+    # the role is on the first chunk only; the finish chunk closes the stream
+    f = run([{"message": {"content": "Hello"}}, {"message": {"content": " world"}}, {"message": {"content": "!"}, "done": True, "done_reason": "stop"}])
+    assert [c["choices"][0]["delta"] for c in f] == [{"role": "assistant", "content": "Hello"}, {"content": " world"}, {"content": "!"}, {}]
+    assert all(c["created"] == 1 for c in f)
+    # the closing response with an empty message adds no empty content chunk; its finish reason passes through
+    f = run([{"message": {"content": "Hi"}}, {"message": {"content": ""}, "done": True, "done_reason": "length", "prompt_eval_count": 3, "eval_count": 1}], True)
+    assert len(f) == 3 and f[1]["choices"][0] == {"index": 0, "delta": {}, "finish_reason": "length"} and f[2]["choices"] == []
+    # ... unless it carries the log-probabilities of the last token
+    f = run([{"message": {"content": "Hi"}}, {"message": {"content": ""}, "done": True, "done_reason": "stop", "logprobs": [{"token": "Hi", "logprob": -0.1}]}])
+    assert len(f) == 3 and f[1]["choices"][0]["logprobs"]["content"][0]["logprob"] == -0.1 and f[2]["choices"][0]["delta"] == {}
+    # an empty completion still opens with the role; a streamed call turns "stop" into "tool_calls" but leaves "length" alone
+    f = run([{"message": {"content": ""}, "done": True, "done_reason": "stop"}])
+    assert len(f) == 2 and f[0]["choices"][0]["delta"] == {"role": "assistant", "content": ""} and f[1]["choices"][0]["finish_reason"] == "stop"
+    assert run([{"message": {"tool_calls": [call]}}, {"message": {}, "done": True, "done_reason": "stop"}])[-1]["choices"][0]["finish_reason"] == "tool_calls"
+    assert run([{"message": {"tool_calls": [call]}}, {"message": {}, "done": True, "done_reason": "length"}])[-1]["choices"][0]["finish_reason"] == "length"
+
+    args = '{"location": "Paris, France", "format": "celsius"}'
+    calls = [{"id": "id_abc", "type": "function", "function": {"name": "get_current_weather", "arguments": args}}]
+    m = _messages({"messages": [{"role": "user", "content": "weather?"}, {"role": "assistant", "reasoning": "let me see", "tool_calls": calls},
+                                {"role": "tool", "tool_call_id": "id_abc", "content": "20 degrees"}, {"role": "tool", "name": "other", "content": "x"},
+                                {"role": "developer", "content": "rules"}]})
+    assert m[1] == {"role": "assistant", "content": "", "thinking": "let me see",
+                    "tool_calls": [{"id": "id_abc", "function": {"name": "get_current_weather", "arguments": {"location": "Paris, France", "format": "celsius"}}}]}
+    assert m[2]["tool_name"] == "get_current_weather" and m[2]["tool_call_id"] == "id_abc" and m[3]["tool_name"] == "other" and m[4]["role"] == "system"
+    o = _options({"max_tokens": 999, "seed": 123, "stop": ["\n", "stop"], "temperature": 3.0, "frequency_penalty": 4.0, "presence_penalty": 5.0, "top_p": 6.0})
+    assert o == {"num_predict": 999, "seed": 123, "stop": ["\n", "stop"], "temperature": 3.0, "frequency_penalty": 4.0, "presence_penalty": 5.0, "top_p": 6.0}
+    assert _options({}) == {"temperature": 1.0, "top_p": 1.0} and _options({"stop": "x"})["stop"] == ["x"]
+
+
 def test_host_allow_list_and_cors(client):
     assert client.get("/", headers={"Host": "evil.example.com"}).status_code == 403
     assert client.get("/", headers={"Host": "localhost:11434"}).status_code == 200
