@@ -81,16 +81,20 @@ class PromptRenderer:
 
 def chat_prompt(render: Callable[[list[dict[str, Any]]], str], count_tokens: Callable[[str], int], messages: list[dict[str, Any]],
                 num_ctx: int, truncate: bool = True) -> tuple[str, list[dict[str, Any]]]:
-    """Return (prompt, messages actually used)."""
-    n = len(messages) - 1
+    """Return (prompt, messages actually used).
+
+    With ``truncate`` the oldest messages are dropped (system messages stay) until the rendered prompt fits ``num_ctx``; the
+    last message is always kept.  The walk starts from the whole conversation, so a chat that fits costs one rendering and
+    one tokenisation (server/prompt.go:23-92 of the reference)."""
+    n = 0
     if truncate:
-        # walk backwards from the newest message, find the longest suffix (plus all system messages) that fits
-        for i in range(n, -1, -1):
-            system = [m for m in messages[:i] if m.get("role") == "system"]
-            cand = system + messages[i:]
+        last = len(messages) - 1
+        for i in range(last + 1):
+            cand = [m for m in messages[:i] if m.get("role") == "system"] + messages[i:]
             p = render(cand)
-            if count_tokens(p) > num_ctx:
-                break
+            if count_tokens(p) <= num_ctx:
+                return p, cand
             n = i
+        n = max(last, 0)
     used = [m for m in messages[:n] if m.get("role") == "system"] + messages[n:]
     return render(used), used

@@ -282,6 +282,40 @@ def test_openai_stream_frames_and_message_conversion_follow_the_reference_cases(
     assert _options({}) == {"temperature": 1.0, "top_p": 1.0} and _options({"stop": "x"})["stop"] == ["x"]
 
 
+def test_chat_prompt_truncation_on_the_reference_cases():
+    """Text cases of server/prompt_test.go:24-320 of the reference: what is kept when the conversation does not fit, system messages
+    that survive, no truncation on request, and how many tokenisations that costs."""
+    from ollama_b200.server.prompt import chat_prompt
+    from ollama_b200.text.template import Template
+    t = Template("{{- if .System }}{{ .System }} {{ end }}\n{{- if .Prompt }}{{ .Prompt }} {{ end }}\n{{- if .Response }}{{ .Response }} {{ end }}")
+    render = lambda ms: t.execute(messages=ms)                  # noqa: E731
+    n_calls = [0]
+
+    def count(s):
+        n_calls[0] += 1
+        return len(s.split())
+
+    harry = [{"role": "user", "content": "You're a test, Harry!"}, {"role": "assistant", "content": "I-I'm a what?"},
+             {"role": "user", "content": "A test. And a thumping good one at that, I'd wager."}]
+    whole = "You're a test, Harry! I-I'm a what? A test. And a thumping good one at that, I'd wager. "
+    assert chat_prompt(render, count, harry, 64)[0] == whole
+    assert chat_prompt(render, count, harry, 1)[0] == "A test. And a thumping good one at that, I'd wager. "
+    assert chat_prompt(render, count, harry, 10, truncate=False)[0] == whole
+    system = {"role": "system", "content": "You are the Test Who Lived."}
+    assert chat_prompt(render, count, [system] + harry, 2048)[0] == "You are the Test Who Lived. " + whole
+    assert chat_prompt(render, count, harry[:2] + [system] + harry[2:], 2048)[0] == \
+        "You're a test, Harry! I-I'm a what? You are the Test Who Lived. A test. And a thumping good one at that, I'd wager. "
+    p, used = chat_prompt(render, count, [system] + harry, 18)          # the system message survives the cut
+    assert p == "You are the Test Who Lived. A test. And a thumping good one at that, I'd wager. " and [m["role"] for m in used] == ["system", "user"]
+    five = [{"role": "user" if i % 2 == 0 else "assistant", "content": f"message {i}"} for i in range(5)]
+    n_calls[0] = 0
+    chat_prompt(render, count, five, 2048)
+    assert n_calls[0] == 1                                              # a chat that fits is tokenised once
+    n_calls[0] = 0
+    assert chat_prompt(render, count, five, 2)[0] == "message 4 " and n_calls[0] <= 5
+    assert chat_prompt(render, count, [], 10)[0] == ""
+
+
 def test_host_allow_list_and_cors(client):
     assert client.get("/", headers={"Host": "evil.example.com"}).status_code == 403
     assert client.get("/", headers={"Host": "localhost:11434"}).status_code == 200
