@@ -302,7 +302,10 @@ def _field(v: Any, name: str) -> Any:
             return v[name]
         # wire structs use snake_case keys; templates use Go field names
         snake = re.sub(r"(?<!^)(?=[A-Z])", "_", name).lower()
-        return v.get(snake, v.get(name.lower()))
+        found = v.get(snake, v.get(name.lower()))
+        if found is None and name[:1].isupper() and type(v) is not dict and callable(getattr(type(v), name, None)):
+            return getattr(v, name)()           # a method of a value that models a Go struct (e.g. ToTypeScriptType)
+        return found
     if hasattr(v, name):
         a = getattr(v, name)
         return a() if callable(a) else a

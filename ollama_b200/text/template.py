@@ -63,6 +63,42 @@ class _Tool(dict):
         return json.dumps(self.wire, separators=(",", ":"), ensure_ascii=False)
 
 
+_TS_TYPES = {"string": "string", "number": "number", "integer": "number", "boolean": "boolean", "array": "any[]",
+             "object": "Record<string, any>", "null": "null"}
+
+
+class _Prop(dict):
+    """One property of a tool's parameters: the wire keys, the nested properties as :class:`_Props`, and the TypeScript
+    spelling of its type that some templates ask for (api/types.go:429-471 of the reference)."""
+
+    def __init__(self, wire: dict[str, Any]):
+        super().__init__(wire)
+        if isinstance(wire.get("properties"), dict):
+            self["properties"] = _Props(wire["properties"])
+        if isinstance(wire.get("items"), dict):
+            self["items"] = _Prop(wire["items"])
+        if isinstance(wire.get("anyOf"), list):
+            self["anyOf"] = [_Prop(x) if isinstance(x, dict) else x for x in wire["anyOf"]]
+
+    def ToTypeScriptType(self) -> str:      # noqa: N802 -- the name templates use
+        if self.get("anyOf"):
+            return " | ".join(x.ToTypeScriptType() for x in self["anyOf"] if isinstance(x, _Prop))
+        t = self.get("type")
+        types = [t] if isinstance(t, str) else [x for x in t if isinstance(x, str)] if isinstance(t, list) else []
+        return " | ".join(_TS_TYPES.get(t, "any") for t in types) if types else "any"
+
+
+class _Props(dict):
+    """The properties of a tool's parameters: values are :class:`_Prop`; prints as JSON (template/template.go:396-404)."""
+
+    def __init__(self, wire: dict[str, Any]):
+        super().__init__({k: _Prop(v) if isinstance(v, dict) else v for k, v in wire.items()})
+        self.wire = wire
+
+    def __str__(self) -> str:
+        return json.dumps(self.wire, separators=(",", ":"), ensure_ascii=False)
+
+
 class _Tools(list):
     def __str__(self) -> str:
         return json.dumps([t.wire for t in self], separators=(",", ":"), ensure_ascii=False)
@@ -72,8 +108,11 @@ def _tmpl_tools(tools: list[dict[str, Any]] | None) -> _Tools:
     out = _Tools()
     for t in tools or []:
         fn = t.get("function", {})
+        params = dict(fn.get("parameters") or {})
+        if isinstance(params.get("properties"), dict):
+            params["properties"] = _Props(params["properties"])
         d = _Tool({"Type": t.get("type", "function"), "Function": {"Name": fn.get("name", ""), "Description": fn.get("description", ""),
-                                                                  "Parameters": fn.get("parameters") or {}}})
+                                                                  "Parameters": params}})
         d.wire = t
         out.append(d)
     return out

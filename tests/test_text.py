@@ -53,6 +53,38 @@ def test_template_modes_and_collate():
     assert '"name":"f"' in out and '[f {"x":1}]' in out
 
 
+def test_template_values_of_tools_and_calls_as_in_the_reference():
+    """template/template_test.go:455-790 and api/types.go:429-471 of the reference: date helpers, call arguments and tool
+    properties print as JSON, both can be ranged over by key, a property knows the TypeScript spelling of its type."""
+    import datetime
+    import json as js
+    from ollama_b200.text.template import Template, collate
+    user = [{"role": "user", "content": "Hello"}]
+    today = datetime.date.today()
+    assert Template("{{- range .Messages }}{{ .Content }}{{ end }} Today is {{ currentDate }}").execute(messages=user) == f"Hello Today is {today.isoformat()}"
+    assert Template("{{- range .Messages }}{{ end }}{{ yesterdayDate }}").execute(messages=user) == (today - datetime.timedelta(days=1)).isoformat()
+    call = [{"role": "assistant", "content": "", "tool_calls": [{"function": {"name": "get_weather", "arguments": {"location": "Tokyo", "unit": "celsius"}}}]}]
+    out = Template("{{- range .Messages }}{{- range .ToolCalls }}{{ .Function.Arguments }}{{- end }}{{- end }}").execute(messages=call)
+    assert js.loads(out) == {"location": "Tokyo", "unit": "celsius"}
+    rng = "{{- range .Messages }}{{- range .ToolCalls }}{{- range $k, $v := .Function.Arguments }}{{ $k }}={{ $v }};{{- end }}{{- end }}{{- end }}"
+    assert Template(rng).execute(messages=call) == "location=Tokyo;unit=celsius;"
+    props = {"zeta": {"type": "string", "description": "zz", "enum": ["a", "b"]}, "alpha": {"type": ["number", "null"]},
+             "obj": {"type": "object", "properties": {"k": {"type": "integer"}}}, "u": {"anyOf": [{"type": "string"}, {"type": "array", "items": {"type": "string"}}]}, "n": {}}
+    tools = [{"type": "function", "function": {"name": "f", "description": "d", "parameters": {"type": "object", "required": ["zeta"], "properties": props}}}]
+    head = "{{- range .Messages }}{{- end }}"
+    assert js.loads(Template(head + "{{- range .Tools }}{{ .Function.Parameters.Properties }}{{ end }}").execute(messages=user, tools=tools)) == props
+    assert js.loads(Template(head + "{{ range .Tools }}{{ json .Function.Parameters }}{{ end }}").execute(messages=user, tools=tools)) == tools[0]["function"]["parameters"]
+    assert js.loads(Template(head + "{{ .Tools }}").execute(messages=user, tools=tools)) == tools
+    each = head + "{{- range .Tools }}{{- range $name, $prop := .Function.Parameters.Properties }}{{ $name }}:{{ $prop.Type }}:{{ $prop.ToTypeScriptType }};{{- end }}{{- end }}"
+    assert Template(each).execute(messages=user, tools=tools) == \
+        "alpha:[number null]:number | null;n::any;obj:object:Record<string, any>;u::string | any[];zeta:string:string;"
+    # consecutive messages of one role merge, tool answers never do (template_test.go:521-615)
+    assert collate([{"role": "user", "content": "Hello"}, {"role": "user", "content": "How are you?"}]) == ("", [{"role": "user", "content": "Hello\n\nHow are you?"}])
+    two = [{"role": "tool", "content": "sunny", "tool_name": "get_weather"}, {"role": "tool", "content": "72F", "tool_name": "get_temperature"}]
+    assert collate(two) == ("", two)
+    assert collate([{"role": "system", "content": "You are helpful"}] + user + two)[0] == "You are helpful"
+
+
 def test_jinja_chat_template():
     t = JinjaChatTemplate("{{ bos_token }}{% for m in messages %}<{{ m.role }}>{{ m.content }}{% endfor %}"
                           "{% if add_generation_prompt %}<assistant>{% if enable_thinking %}<think>{% endif %}{% endif %}", bos_token="<s>")
