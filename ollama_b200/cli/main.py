@@ -62,6 +62,15 @@ def cmd_serve(args) -> int:
         auth.ensure_key()
     except (auth.AuthError, OSError) as e:
         print(f"warning: could not set up the ed25519 key pair: {e}", file=sys.stderr)
+    try:      # start-up housekeeping of the blob store (server/routes.go Serve: fixBlobs, then PruneLayers unless OLLAMA_NOPRUNE)
+        from ..store import manifest
+        if os.path.isdir(manifest.blobs_dir()):
+            manifest.fix_blobs()
+            if not envconfig.no_prune():
+                manifest.prune_layers()
+                manifest.prune_empty_dirs(manifest.manifests_dir())
+    except OSError as e:
+        print(f"warning: could not tidy the model store: {e}", file=sys.stderr)
     h = envconfig.host()
     print(f"ollama-b200 {VERSION} listening on {h.netloc}", file=sys.stderr)
     for k, (v, desc) in envconfig.as_map().items():

@@ -375,12 +375,16 @@ class Runner:
             self.slot_seq[best] = seq
             seq.state = "prefill"
             r = seq.req
-            seq.sampler = Sampler(r.sampling, self.cfg.vocab_size, self.n_ctx, history=seq.prompt)
-            if r.grammar and r.grammar_after and self.tokenizer is not None:
-                seq.grammar_pending = r.grammar          # free-form reasoning first, constrained answer afterwards
-            elif r.grammar:
-                from .grammar import Grammar
-                seq.grammar = Grammar(r.grammar, self.tokenizer)
+            try:
+                seq.sampler = Sampler(r.sampling, self.cfg.vocab_size, self.n_ctx, history=seq.prompt)
+                if r.grammar and r.grammar_after and self.tokenizer is not None:
+                    seq.grammar_pending = r.grammar          # free-form reasoning first, constrained answer afterwards
+                elif r.grammar:
+                    from .grammar import Grammar
+                    seq.grammar = Grammar(r.grammar, self.tokenizer)
+            except Exception as e:      # a bad grammar or sampler setting is this request's problem only
+                self._fail(seq, e)
+                continue
             seq.limit = r.num_predict if r.num_predict >= 0 else 10 * self.n_ctx
 
     def _step(self) -> None:
@@ -428,11 +432,10 @@ class Runner:
         s.n_prompt_eval += n
         self.slot_tokens[s.slot].extend(chunk)
         if last:
-            tok, lp = s.sampler.sample(logits, s.grammar.allows if s.grammar else None)
             s.t_prefill += time.perf_counter() - t0
             s.t_first = time.perf_counter() - s.t_submit
             s.state = "decode"
-            self._accept(s, tok, lp)
+            self._sample_accept(s, logits)
         else:
             _sync(None)
             s.t_prefill += time.perf_counter() - t0
@@ -465,16 +468,44 @@ class Runner:
                 s.sampler.accept(t)
         else:
             logits = self.backend.decode(slots, toks, poss)
-            sampled = [s.sampler.sample(logits[i], s.grammar.allows if s.grammar else None) for i, s in enumerate(ready)]
+            sampled = [None] * len(ready)        # drawn per sequence below, so that one failing sampler stops one sequence
         dt = time.perf_counter() - t0
         self.stats["decode_steps"] += 1
         self.stats["decode_step_sequences"] += len(ready)
-        for s, (tok, lp) in zip(ready, sampled):
+        for i, s in enumerate(ready):
             self.slot_tokens[s.slot].append(s.next_token)
             s.n_past += 1
             s.t_decode += dt
             s.n_decoded += 1
+            if sampled[i] is None:
+                self._sample_accept(s, logits[i])
+            else:
+                self._sample_accept(s, None, sampled[i])
+
+    def _sample_accept(self, s: _Seq, logits, drawn: tuple | None = None) -> None:
+        """Draw the next token of one sequence (unless ``drawn`` already holds it) and process it.
+
+        Errors raised here come from this sequence's own sampler, grammar or stop handling (for instance a grammar
+        that rejects every token the vocabulary offers): they end this sequence with an error chunk and leave the
+        other slots running.  Device errors are not caught: they poison the runner and the scheduler replaces it.
+        """
+        try:
+            tok, lp = drawn if drawn is not None else s.sampler.sample(logits, s.grammar.allows if s.grammar else None)
             self._accept(s, tok, lp)
+        except Exception as e:
+            if _is_device_error(e):
+                raise
+            self._fail(s, e)
+
+    def _fail(self, s: _Seq, e: Exception) -> None:
+        """End one sequence with an error chunk and free its slot."""
+        if s.state == "done":
+            return
+        self.stats["failed_requests"] = self.stats.get("failed_requests", 0) + 1
+        s.out.put(CompletionChunk(done=True, error=f"{type(e).__name__}: {e}"))
+        if s.slot >= 0:
+            self.slot_tokens[s.slot] = self.slot_tokens[s.slot][:s.n_past]
+        self._release(s)
 
     def _speculate(self, s: _Seq, t0: float) -> bool:
         """One speculative step of a greedy sequence: the draft model proposes ``k`` tokens one by one, the target model
@@ -649,6 +680,16 @@ class Runner:
         if s.slot >= 0 and self.slot_seq[s.slot] is s:
             self.slot_seq[s.slot] = None
             self.slot_used_at[s.slot] = time.time()
+
+
+def _is_device_error(e: Exception) -> bool:
+    """True for failures of the backend itself (CUDA runtime, kernel library, exchange time-outs) as opposed to host-side
+    per-request logic."""
+    from ..ops.cuda import CudaKernelError
+    if isinstance(e, CudaKernelError):
+        return True
+    msg = str(e)
+    return isinstance(e, RuntimeError) and ("CUDA" in msg or "cuda" in msg or "tensor-parallel exchange" in msg)
 
 
 def _common_prefix(a: Sequence[int], b: Sequence[int]) -> int:

@@ -82,3 +82,15 @@ __device__ __forceinline__ float e8m0_to_float(uint32_t e) {
     // 2^(e-127); e == 0 denotes 2^-127 (subnormal in fp32)
     return e == 0 ? __uint_as_float(0x00400000u) : __uint_as_float(e << 23);
 }
+
+// Gated FFN activation: 0 = SiLU(g) * u, 1 = tanh-GELU(g) * u, 2 = clamped SwiGLU with alpha and limit (gpt-oss).
+__device__ __forceinline__ float glu_act(float g, float u, int act, float alpha, float limit) {
+    if (act == 0) return g / (1.f + __expf(-g)) * u;
+    if (act == 1) {
+        const float t = tanhf(0.7978845608028654f * (g + 0.044715f * g * g * g));
+        return 0.5f * g * (1.f + t) * u;
+    }
+    g = fminf(g, limit);
+    u = fminf(fmaxf(u, -limit), limit);
+    return g / (1.f + __expf(-alpha * g)) * (u + 1.f);
+}

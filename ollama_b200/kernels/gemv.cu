@@ -63,17 +63,6 @@ __device__ __forceinline__ Planes planes_of(const WDesc& w) {
     return p;
 }
 
-__device__ __forceinline__ float glu_act(float g, float u, int act, float alpha, float limit) {
-    if (act == 0) return g / (1.f + __expf(-g)) * u;
-    if (act == 1) {
-        const float t = tanhf(0.7978845608028654f * (g + 0.044715f * g * g * g));
-        return 0.5f * g * (1.f + t) * u;
-    }
-    g = fminf(g, limit);
-    u = fminf(fmaxf(u, -limit), limit);
-    return g / (1.f + __expf(-alpha * g)) * (u + 1.f);
-}
-
 // Sum M per-lane values across the warp with a halving exchange (about M + 5 shuffles instead of
 // 5 M).  On return lane L owns elements e = base(L) + i, i < max(M/32, 1), in v[i]; base(L) is
 // returned.  For M < 32 several lanes own the same element (the one with the low bits clear stores).

@@ -232,9 +232,27 @@ def list_manifests() -> Iterator[tuple[Name, Manifest]]:
 
 
 def delete_model(name: Name) -> None:
+    """Remove the manifest and those of its own blobs that no other manifest uses (manifest/manifest.go RemoveLayers).
+
+    Blobs that belong to no manifest at all are left alone: they may be uploads waiting for a create, or the finished
+    layers of a pull or create that has not written its manifest yet.  Unreferenced blobs are only swept at start-up
+    (:func:`prune_layers`).  A manifest that cannot be parsed counts as using nothing, exactly as at start-up, but its
+    blobs are not candidates here either, because only the deleted manifest's layers are.
+    """
     m = read_manifest(name)
     os.unlink(m.path)
-    prune_layers()
+    mine = {m.config.digest.replace(":", "-")} | {l.digest.replace(":", "-") for l in m.layers}
+    mine.discard("")
+    in_use = set()
+    for _, other in list_manifests():
+        in_use.add(other.config.digest.replace(":", "-"))
+        in_use.update(l.digest.replace(":", "-") for l in other.layers)
+    for fn in mine - in_use:
+        if fn.startswith("sha256-") and len(fn) == 71:
+            try:
+                os.unlink(os.path.join(blobs_dir(), fn))
+            except FileNotFoundError:
+                pass
     prune_empty_dirs(manifests_dir())
 
 

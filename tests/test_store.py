@@ -145,9 +145,12 @@ def test_manifest_blob_store(tmp_path, monkeypatch):
     assert sorted(x.display() for x, _ in M.list_manifests()) == ["me/other:latest", "me/thing:v1"]
     orphan = M.new_layer(b"orphan", M.MT_LICENSE)
     M.delete_model(n)
-    assert not os.path.exists(orphan.path()) and os.path.exists(a.path())          # still referenced by me/other
+    # a delete removes only the deleted manifest's own unused layers: a blob no manifest names (an upload waiting for
+    # its create, a layer of a pull in progress) stays, and so does one that another manifest still uses
+    assert os.path.exists(orphan.path()) and os.path.exists(a.path())
     M.delete_model(parse_name("me/other"))
-    assert not os.path.exists(a.path())
+    assert not os.path.exists(a.path()) and not os.path.exists(cfg.path()) and os.path.exists(orphan.path())
+    assert M.prune_layers() == 1 and not os.path.exists(orphan.path())             # the start-up sweep takes the orphan
     with pytest.raises(M.StoreError):
         M.blob_path("sha256:xyz")
     with pytest.raises(M.StoreError):
