@@ -30,8 +30,10 @@ from ..models.config import ModelConfig, config_from_gguf
 from ..models.weights import QWeight, load_tensor
 from ..ops import cuda as K
 from ..ops import reference as R
+from ..ops import sk as SK
 
-MAX_DECODE_BATCH = 8
+MAX_DECODE_BATCH = 8             # sequences per launch of the dp4a kernels (kernels/gemv.cu)
+MAX_STREAM_BATCH = 32            # sequences per step when every matrix runs on the streaming kernel (kernels/gemv_sk.cu)
 
 
 def supports(cfg: ModelConfig) -> bool:
@@ -91,6 +93,10 @@ class B200Backend:
         self._graphs: dict[tuple[int, bool], torch.cuda.CUDAGraph] = {}
         self._capture_stream = None
         self.pdl = True
+        # Decode matrices in unit order for the streaming GEMV (Q4_K / Q6_K layers without experts or sandwich norms); B200_SK=0
+        # keeps every layer on the dp4a kernels.
+        self.use_sk = os.environ.get("B200_SK", "1") != "0" and not self.cfg.sandwich_norm
+        self.max_batch = MAX_DECODE_BATCH
         self.fuse_attn_combine = False    # one launch (last CTA merges the splits) measured slower than two launches joined by PDL
         self.use_graphs = True
         self.launches_per_step = 0
@@ -168,7 +174,16 @@ class B200Backend:
                 L.gu.bf16 = K.dequant_to_bf16(L.gu)
             L.sinks = vec(p + "attn_sinks.weight")
             L.swa = c.layer_is_swa(i)
+            L.sk = self._load_sk_layer(p, L, get, vec) if self.use_sk and not L.moe else None
             self.layers.append(L)
+        self.sk_head = None
+        if self.use_sk and self.last and all(L.sk is not None for L in self.layers):
+            hw = get("output.weight" if not tied else "token_embd.weight")
+            if SK.supported(hw.dtype, *hw.shape) and self.head.bias is None:
+                self.sk_head = SK.repack(hw, dev)
+        # a step takes up to 32 sequences only when no layer falls back to the dp4a kernels (eight per launch)
+        if all(L.sk is not None for L in self.layers) and (self.sk_head is not None or not self.last) and type(self) is B200Backend:
+            self.max_batch = MAX_STREAM_BATCH
         ff = vec("rope_freqs.weight")
         kw = dict(scaling=c.rope_scaling_type if c.rope_scaling_type != "llama3" else "none", factor=c.rope_scaling_factor,
                   orig_ctx=c.rope_orig_ctx, beta_fast=c.yarn_beta_fast, beta_slow=c.yarn_beta_slow, device=dev)
@@ -182,10 +197,36 @@ class B200Backend:
             self.attn_scale = 1.0 / math.sqrt(c.d_model / c.n_heads)
         torch.cuda.synchronize(dev)
 
+    def _load_sk_layer(self, p: str, L, get, vec):
+        """Unit-ordered copies of a layer's seven matrices for the streaming decode GEMV, or None when one of them has no unit
+        layout (other encodings, odd shapes).  With a resident 16-bit copy for prefill the dp4a planes are dropped."""
+        names = ("attn_q", "attn_k", "attn_v", "attn_output", "ffn_gate", "ffn_up", "ffn_down")
+        qs = {n: get(p + n + ".weight") for n in names}
+        if any(len(q.shape) != 2 or not SK.supported(q.dtype, *q.shape) for q in qs.values()) or qs["ffn_gate"].dtype != qs["ffn_up"].dtype:
+            return None
+        dev, o = self.device, _Layer()
+        o.qkv = [SK.repack(qs[n], dev, bias=vec(p + n + ".bias")) for n in ("attn_q", "attn_k", "attn_v")]
+        o.o = SK.repack(qs["attn_output"], dev, bias=vec(p + "attn_output.bias"))
+        bg, bu = vec(p + "ffn_gate.bias"), vec(p + "ffn_up.bias")
+        gub = None
+        if bg is not None or bu is not None:
+            z = torch.zeros(qs["ffn_gate"].shape[0], device=dev)
+            gub = torch.stack([bg if bg is not None else z, bu if bu is not None else z], 1).reshape(-1)
+        o.gu = SK.repack(SK.interleave(qs["ffn_gate"], qs["ffn_up"]), dev, bias=gub)
+        o.down = SK.repack(qs["ffn_down"], dev, bias=vec(p + "ffn_down.bias"))
+        if self.keep_bf16:
+            for w in (L.wq, L.wk, L.wv, L.wo, L.gu, L.down):
+                w.planes = []
+        return o
+
     def weight_bytes(self) -> int:
         ws = [w for w in (self.embd, self.head if self.head is not self.embd else None) if w is not None]
         for L in self.layers:
             ws += [L.wq, L.wk, L.wv, L.wo, L.gu, L.down]
+            if L.sk is not None:
+                ws += L.sk.qkv + [L.sk.o, L.sk.gu, L.sk.down]
+        if self.sk_head is not None:
+            ws.append(self.sk_head)
         return sum(w.nbytes for w in ws)
 
     def kv_bytes(self) -> int:
@@ -204,7 +245,7 @@ class B200Backend:
             def sc():
                 return [torch.zeros(n_slots, c.n_kv_heads, n_ctx, c.head_dim // 32, device=dev, dtype=torch.float16) for _ in self.layers]
             self.k_scale, self.v_scale = sc(), sc()
-        MB = MAX_DECODE_BATCH
+        MB = self.max_batch
         f32, i8, i32 = torch.float32, torch.int8, torch.int32
         qkv_dim = (c.n_heads + 2 * c.n_kv_heads) * c.head_dim
         kmax = max(c.d_model, c.q_dim)
@@ -241,6 +282,10 @@ class B200Backend:
         b.meta = torch.zeros(3, MB, device=dev, dtype=i32)          # tokens | positions | slots of the decode batch
         b.tokens, b.positions, b.slots = b.meta[0], b.meta[1], b.meta[2]
         b.sampled = torch.zeros(MB, device=dev, dtype=i32)
+        if any(L.sk is not None for L in self.layers):      # pre-quantised inputs of the streaming GEMV (rows too wide to quantise in place)
+            kq = max(kmax, ff)
+            b.sk_x = (torch.zeros(MB * kq, device=dev, dtype=i8), torch.zeros(MB * (kq // 256 + 1), device=dev, dtype=f32),
+                      torch.zeros(MB * (kq // 32 + 1), device=dev, dtype=torch.int16))
         b.host_in = torch.zeros(3, MB, dtype=i32).pin_memory()
         b.host_out = torch.zeros(MB, dtype=i32).pin_memory()
         b.host_np, b.host_out_np = b.host_in.numpy(), b.host_out.numpy()
@@ -342,6 +387,43 @@ class B200Backend:
         self.kernel_launches += 1
         return (y.view(T, k, c.d_model) * wts.view(T, k, 1)).sum(1)
 
+    def _sk(self, ws, x: torch.Tensor, out: torch.Tensor, nb: int, norm_w=None, mode: int = SK.MODE_STORE) -> None:
+        """One streaming GEMV of the decode step: fp32 rows in (normalised with ``norm_w``), ``out`` stored / added to / gated."""
+        c, b = self.cfg, self.buf
+        k = ws[0].k
+        xin = x[:nb, :k]
+        if not SK.fits_fused_input(nb, k):      # wide or many rows: one CTA per row quantises, the GEMV reads int8 from global memory
+            xq, xd, xbs = b.sk_x          # flat buffers, used as dense [nb, k] rows
+            xin = SK.quant256(xin, norm_w, c.norm_eps, pdl=self.pdl,
+                              out=(xq[:nb * k].view(nb, k), xd[:nb * (k // 256)].view(nb, k // 256), xbs[:nb * (k // 32)].view(nb, k // 32)))
+            norm_w = None
+            self._n += 1
+        SK.gemv(ws, xin, norm_w=norm_w, eps=c.norm_eps, out=out, mode=mode, act=c.act, alpha=c.swiglu_alpha, limit=c.swiglu_limit, pdl=self.pdl)
+        self._n += 1
+
+    def _decode_layer_sk(self, i: int, L, nb: int) -> None:
+        """A layer on the streaming GEMV: both RMSNorms, both residual adds, the gated activation and every activation
+        quantisation happen inside the four matrix kernels; attention keeps its own kernels."""
+        c, b, lib, st = self.cfg, self.buf, K.lib(), K.stream
+        self._sk(L.sk.qkv, b.x, b.qkv, nb, norm_w=L.attn_norm)
+        local = L.swa and c.rope_base_local > 0
+        ra = K.RopeKvArgs(K.ptr(b.qkv), K.ptr(b.positions), K.ptr(b.slots), K.ptr(self.inv_freq_local if local else self.inv_freq),
+                          K.ptr(L.q_norm), K.ptr(L.k_norm), c.norm_eps, 1.0 if local else self.mscale, c.n_heads, c.n_kv_heads,
+                          c.head_dim, c.rope_dim, int(c.rope_style == "neox"), self.n_ctx, K.ptr(b.q), K.ptr(self.k_cache[i]),
+                          K.ptr(self.v_cache[i]), K.ptr(self.k_scale[i]), K.ptr(self.v_scale[i]))
+        K._check(lib.b2_rope_kv(C.byref(ra), nb, int(self.pdl), st()), "rope_kv")
+        aa = K.AttnDecodeArgs(K.ptr(b.q), K.ptr(self.k_cache[i]), K.ptr(self.v_cache[i]), K.ptr(b.positions), K.ptr(b.slots),
+                              c.n_heads, c.n_kv_heads, self.n_ctx, self.n_splits, self.attn_scale, c.attn_softcap,
+                              c.sliding_window if L.swa else 0, K.ptr(b.part_acc), K.ptr(b.part_ml), K.ptr(self.k_scale[i]),
+                              K.ptr(self.v_scale[i]))
+        ca = K.AttnCombineArgs(K.ptr(b.part_acc), K.ptr(b.part_ml), K.ptr(L.sinks), c.n_heads, self.n_splits, c.head_dim,
+                               K.ptr(b.ao), None, None)
+        K._check(lib.b2_attn_decode(C.byref(aa), C.byref(ca), nb, c.head_dim, int(self.pdl), st()), "attn_decode")
+        self._n += 3
+        self._sk([L.sk.o], b.ao, b.x, nb, mode=SK.MODE_ACCUM)
+        self._sk([L.sk.gu], b.x, b.hf, nb, norm_w=L.ffn_norm, mode=SK.MODE_GLU)
+        self._sk([L.sk.down], b.hf, b.x, nb, mode=SK.MODE_ACCUM)
+
     def _decode_kernels(self, nb: int, want_argmax: bool) -> None:
         """Enqueue one decode step for ``nb`` sequences on the current stream (inputs: buf.tokens/positions/slots)."""
         c, b, lib, st = self.cfg, self.buf, K.lib(), K.stream
@@ -351,6 +433,9 @@ class B200Backend:
             self._n += 1
         act = K._ACT[c.act]
         for i, L in enumerate(self.layers):
+            if L.sk is not None:
+                self._decode_layer_sk(i, L, nb)
+                continue
             self._norm_quant(b.x, L.attn_norm, nb, c.d_model)
             self._gemv([L.wq, L.wk, L.wv], nb, b.xq, b.xds, b.xf, b.qkv, b.qkv.stride(0))
             local = L.swa and c.rope_base_local > 0
@@ -396,8 +481,11 @@ class B200Backend:
         if not self.last:
             self.launches_per_step = self._n
             return
-        self._norm_quant(b.x, self.out_norm, nb, c.d_model)
-        self._gemv([self.head], nb, b.xq, b.xds, b.xf, b.logits, b.logits.stride(0))
+        if self.sk_head is not None:
+            self._sk([self.sk_head], b.x, b.logits, nb, norm_w=self.out_norm)
+        else:
+            self._norm_quant(b.x, self.out_norm, nb, c.d_model)
+            self._gemv([self.head], nb, b.xq, b.xds, b.xf, b.logits, b.logits.stride(0))
         if want_argmax:
             K.argmax(b.logits[:nb], out=b.sampled)
             self._n += 1
@@ -433,8 +521,8 @@ class B200Backend:
 
     def _stage(self, slots, tokens, positions) -> int:
         nb = len(slots)
-        if nb > MAX_DECODE_BATCH:
-            raise ValueError(f"decode batch {nb} exceeds {MAX_DECODE_BATCH}")
+        if nb > self.max_batch:
+            raise ValueError(f"decode batch {nb} exceeds {self.max_batch}")
         b = self.buf
         h = b.host_np
         h[0, :nb] = tokens
@@ -446,10 +534,10 @@ class B200Backend:
 
     @torch.no_grad()
     def decode_argmax(self, slots: Sequence[int], tokens: Sequence[int], positions: Sequence[int]) -> list[int]:
-        if len(slots) > MAX_DECODE_BATCH:      # more sequences than one step takes: consecutive steps of up to eight
+        if len(slots) > self.max_batch:      # more sequences than one step takes: consecutive steps
             out: list[int] = []
-            for i in range(0, len(slots), MAX_DECODE_BATCH):
-                j = i + MAX_DECODE_BATCH
+            for i in range(0, len(slots), self.max_batch):
+                j = i + self.max_batch
                 out += self.decode_argmax(slots[i:j], tokens[i:j], positions[i:j])
             return out
         nb = self._stage(slots, tokens, positions)
@@ -461,9 +549,9 @@ class B200Backend:
 
     @torch.no_grad()
     def decode(self, slots, tokens, positions) -> torch.Tensor:
-        if len(slots) > MAX_DECODE_BATCH:
-            return torch.cat([self.decode(slots[i:i + MAX_DECODE_BATCH], tokens[i:i + MAX_DECODE_BATCH], positions[i:i + MAX_DECODE_BATCH])
-                              for i in range(0, len(slots), MAX_DECODE_BATCH)])
+        if len(slots) > self.max_batch:
+            mb = self.max_batch
+            return torch.cat([self.decode(slots[i:i + mb], tokens[i:i + mb], positions[i:i + mb]) for i in range(0, len(slots), mb)])
         nb = self._stage(slots, tokens, positions)
         self._run_step(nb, False)
         return R.softcap(self.buf.logits[:nb].clone(), self.cfg.final_softcap)
@@ -476,10 +564,10 @@ class B200Backend:
         Returns the sampled ids as an int32 tensor [n_steps, nb] (still on the device).  Used by the
         benchmark's kernel-only measurement and by speculative prefixes where no stop condition can fire.
         """
-        if len(slots) > MAX_DECODE_BATCH:      # groups of up to eight sequences, one group after the other
+        if len(slots) > self.max_batch:      # one group of sequences after the other
             parts = []
-            for i in range(0, len(slots), MAX_DECODE_BATCH):
-                j = i + MAX_DECODE_BATCH
+            for i in range(0, len(slots), self.max_batch):
+                j = i + self.max_batch
                 parts.append(self.decode_loop(slots[i:j], tokens[i:j], positions[i:j], n_steps,
                                               None if first_tokens is None else first_tokens[i:j]))
             return torch.cat(parts, 1)

@@ -82,6 +82,7 @@ struct SkArgs {
 };
 
 constexpr int SK_MAX_PHASES = 4;
+constexpr int SK_MAX_DYN_SMEM = 224 * 1024;     // 227 KB per CTA less the kernel's static shared memory (the argument copy)
 
 // Several products in one launch, each reading what the one before it wrote (attention output -> FFN -> next layer's
 // Q/K/V, say).  All CTAs of the launch are resident at once; between two phases they meet at a barrier in global memory,
@@ -91,6 +92,7 @@ struct SkChain {
     SkArgs ph[SK_MAX_PHASES];
     int n;
     unsigned* bar;        // two counters (arrivals, exits), zero between launches; unused when n == 1
+    int tune;             // experiments: bits 0-1 = units per warp requested before the inputs are read (0: ring - 1), bit 2 = no requests across a phase end
     unsigned long long* trace;   // optional: [grid][16] nanosecond time stamps of thread 0 (launch, inputs ready, per phase: quantised, done)
 };
 
@@ -583,7 +585,7 @@ __device__ __forceinline__ void grid_barrier(unsigned* bar, unsigned target, int
 }
 
 template <int NT, bool ONE, bool XSMEM>
-__global__ void __launch_bounds__(SK_THREADS, ONE ? 3 : NT == 1 ? 2 : 1) gemv_sk_kernel(const __grid_constant__ SkChain c_param) {
+__global__ void __launch_bounds__(SK_THREADS, NT == 1 ? 2 : 1) gemv_sk_kernel(const __grid_constant__ SkChain c_param) {
     constexpr int FRAG = NT * 4 * 32;           // floats of one warp's accumulator fragment
     extern __shared__ __align__(128) uint8_t smem[];
     // The argument block is more than a kilobyte and is indexed at run time (phase, matrix): read from the constant bank
@@ -611,13 +613,31 @@ __global__ void __launch_bounds__(SK_THREADS, ONE ? 3 : NT == 1 ? 2 : 1) gemv_sk
     Walker wk;
     wk.ph = 0;
     walker_find(wk, c, warp, walker_enter(wk, c, warp));
-    int slot_in = 0, slot_out = 0;
-    for (int i = 0; i < R - 1; i++) {
+    // Requests in flight fill the SM's miss queues: an activation load issued behind R - 1 units per warp waits for the first of
+    // them to come back.  So only `pre` units per warp go out before the inputs are loaded; the ring is topped up right after
+    // the activation loads have been issued (`held` counts the slots still owed).
+    int slot_in = 0, slot_out = 0, held = 0;
+    const int pre = (c.tune & 3) == 0 ? R - 1 : min(c.tune & 3, R - 1);
+    const bool hold_phases = (c.tune & 4) != 0;
+    auto issue = [&](int ph_limit) {        // one ring slot: the walker's unit, unless it belongs to a phase that is held back
+        if (wk.valid && wk.ph > ph_limit) {
+            held++;
+            return;
+        }
         ring_issue(wk, ring + slot_in * slot_bytes, lane, policy);
         if (wk.valid) walker_next(wk, c, warp);
         slot_in = slot_in + 1 == R ? 0 : slot_in + 1;
+    };
+    auto top_up = [&](int ph_limit) {
+        while (held > 0 && !(wk.valid && wk.ph > ph_limit)) {
+            held--;
+            issue(ph_limit);
+        }
+    };
+    for (int i = 0; i < R - 1; i++) {
+        if (i < pre) issue(SK_MAX_PHASES);
+        else held++;
     }
-
     if (tr) tr[tr_n++] = global_ns();
     pdl_wait();
     if (tr) tr[tr_n++] = global_ns();
@@ -645,7 +665,8 @@ __global__ void __launch_bounds__(SK_THREADS, ONE ? 3 : NT == 1 ? 2 : 1) gemv_sk
             float* xd_s = reinterpret_cast<float*>(smem + a.off_xd);
             int16_t* xbs_s = reinterpret_cast<int16_t*>(smem + a.off_xbs);
             // token rows are 16 bytes apart from a multiple of 128, so the eight tokens of a B fragment hit different banks
-            quantise_rows<ONE ? 2 : 4>(a.x, a.ldx, a.norm_w, a.eps, a.k, a.nb, xq_s, a.k + 16, xd_s, ONE ? xbs_s : nullptr, ssq, ONE);
+            quantise_rows<2>(a.x, a.ldx, a.norm_w, a.eps, a.k, a.nb, xq_s, a.k + 16, xd_s, ONE ? xbs_s : nullptr, ssq, ONE);
+            top_up(SK_MAX_PHASES);
             __syncthreads();
             x.kw = (a.k + 16) >> 2;
             x.q = reinterpret_cast<const uint32_t*>(xq_s);
@@ -655,6 +676,7 @@ __global__ void __launch_bounds__(SK_THREADS, ONE ? 3 : NT == 1 ? 2 : 1) gemv_sk
             x.q = reinterpret_cast<const uint32_t*>(a.xq);
             x.d = a.xd;
             x.bs = reinterpret_cast<const uint32_t*>(a.xbs);
+            top_up(SK_MAX_PHASES);
         }
         if (tr) tr[tr_n++] = global_ns();
 
@@ -671,11 +693,11 @@ __global__ void __launch_bounds__(SK_THREADS, ONE ? 3 : NT == 1 ? 2 : 1) gemv_sk
     #pragma unroll
                 for (int i = 0; i < 4; i++) facc[n][i] = 0.f;
             for (int u = ua; u < ub; u++) {
-                // keep the ring full, then wait for the oldest unit (all but the R - 1 newest groups are complete)
-                ring_issue(wk, ring + slot_in * slot_bytes, lane, policy);
-                if (wk.valid) walker_next(wk, c, warp);
-                slot_in = slot_in + 1 == R ? 0 : slot_in + 1;
-                if (R == 3) cp_async_wait<2>(); else if (R == 2) cp_async_wait<1>(); else cp_async_wait<3>();
+                // keep the ring full, then wait for the oldest unit: every slot that was asked for has either closed a copy group
+                // or is still owed, so all but the R - 1 - held newest groups are complete when the oldest unit is
+                issue(hold_phases ? ph : SK_MAX_PHASES);
+                const int newer = R - 1 - held;
+                if (newer >= 3) cp_async_wait<3>(); else if (newer == 2) cp_async_wait<2>(); else if (newer == 1) cp_async_wait<1>(); else cp_async_wait<0>();
                 __syncwarp();
                 const uint8_t* sp = ring + slot_out * slot_bytes;
                 slot_out = slot_out + 1 == R ? 0 : slot_out + 1;
@@ -906,7 +928,7 @@ B2_API int b2_gemv_sk_chain(const SkChain* in, int max_ctas, int split, int ring
     const void* fn = one ? pick_x<1, true>(xsmem) : nt == 1 ? pick_x<1, false>(xsmem) : nt == 2 ? pick_x<2, false>(xsmem) : pick_x<4, false>(xsmem);
     const int which = (one ? 0 : nt == 1 ? 1 : nt == 2 ? 2 : 3) * 2 + (xsmem ? 1 : 0);
     if (g_attr[which].first()) {
-        const cudaError_t e = cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+        const cudaError_t e = cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, SK_MAX_DYN_SMEM);
         if (e != cudaSuccess) return (int)e;
     }
     // ring depth: the one that puts most units in flight per SM (CTAs per SM x slots in flight), more CTAs on a tie
@@ -914,7 +936,7 @@ B2_API int b2_gemv_sk_chain(const SkChain* in, int max_ctas, int split, int ring
     size_t smem = 0;
     for (int r = (ring_slots > 0 ? ring_slots : 4); r >= (ring_slots > 0 ? ring_slots : 2); r--) {
         const size_t need = (size_t)off + (size_t)SK_WARPS * r * slot;
-        if (need > 227 * 1024) continue;
+        if (need > (size_t)SK_MAX_DYN_SMEM) continue;
         int n = 0;
         const cudaError_t e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, fn, SK_THREADS, need);
         if (e != cudaSuccess) return (int)e;

@@ -24,7 +24,6 @@ from . import cuda as K
 UNIT_BYTES = {K.WT_Q4_K: 2368, K.WT_Q6_K: 3360}
 WS_FLOATS = 16 * 32
 MAX_TOKENS = 32
-XSMEM_BUDGET = 64 * 1024          # largest int8 activation block a GEMV quantises into its own shared memory
 
 
 class SkSeg(C.Structure):
@@ -42,10 +41,11 @@ class SkArgs(C.Structure):
 
 
 MAX_PHASES = 4
+TUNE = int(__import__('os').environ.get('B200_SK_TUNE', '0'))      # kernel experiments (see SkChain.tune in kernels/gemv_sk.cu)
 
 
 class SkChain(C.Structure):
-    _fields_ = [("ph", SkArgs * MAX_PHASES), ("n", C.c_int), ("bar", C.c_void_p), ("trace", C.c_void_p)]
+    _fields_ = [("ph", SkArgs * MAX_PHASES), ("n", C.c_int), ("bar", C.c_void_p), ("tune", C.c_int), ("trace", C.c_void_p)]
 
 
 class Quant256Args(C.Structure):
@@ -210,8 +210,9 @@ def workspace(device) -> Workspace:
 
 
 def fits_fused_input(nb: int, k: int) -> bool:
-    """True when the GEMV can quantise its nb x k input inside its own shared memory and still keep a useful ring."""
-    return nb * (k + 16 + k // 64 + k // 16) <= (XSMEM_BUDGET if nb > 8 else XSMEM_BUDGET // 2)
+    """True when the GEMV should normalise / quantise its nb x k fp32 input itself (every CTA repeats that work, so it only pays
+    for small inputs: at most two rounds of loads per warp, and room left in shared memory for the weight rings)."""
+    return nb * (k // 256) <= 32 and nb * (k + 16 + k // 64 + k // 16) <= 24 * 1024
 
 
 def quant256(x: torch.Tensor, norm_w: torch.Tensor | None = None, eps: float = 0.0, out: tuple | None = None, pdl: bool = False) -> tuple:
@@ -288,5 +289,6 @@ def gemv_chain(phases: list[SkArgs], device, max_ctas: int = 0, split: int = 0, 
     for i, a in enumerate(phases):
         c.ph[i] = a
     c.n, c.bar = len(phases), workspace(device).bar.data_ptr()
+    c.tune = TUNE
     c.trace = trace.data_ptr() if trace is not None else None      # int64 [grid, 16]: time stamps of thread 0 of every CTA
     K._check(K.lib().b2_gemv_sk_chain(C.byref(c), max_ctas, split, ring, int(pdl), K.stream()), "gemv_sk_chain")

@@ -153,3 +153,36 @@ def test_gemv_chain_runs_dependent_products_in_one_launch(nb):
         sk.workspace("cuda").check()
         assert _close(x.cpu(), x2, 5e-3), (x.cpu() - x2).abs().max()
         assert _close(out.cpu(), qkv, 1e-2), (out.cpu() - qkv).abs().max()
+
+
+def test_engine_decodes_up_to_32_sequences_in_one_step(tmp_path):
+    """A model whose matrices all have a unit layout takes 32 sequences per step; a batched step gives every sequence the
+    logits it gets when it is decoded alone, and both agree with the fp32 reference graph."""
+    from ollama_b200.engine.b200 import B200Backend, MAX_STREAM_BATCH
+    from ollama_b200.engine.backend import TorchBackend, open_model
+    from ollama_b200.models.synth import write_synthetic_gguf
+    p = str(tmp_path / "m.gguf")
+    write_synthetic_gguf(p, "tiny-qwen3", "Q4_K_M")
+    g = open_model(p)
+    eng = B200Backend(g, "cuda")
+    assert eng.max_batch == MAX_STREAM_BATCH and all(L.sk is not None for L in eng.layers) and eng.sk_head is not None
+    ref = TorchBackend(g, "cpu")
+    n = 32
+    eng.alloc(n, 64)
+    ref.alloc(n, 64)
+    gen = torch.Generator().manual_seed(5)
+    prompts = [torch.randint(259, 4096, (5 + s % 7,), generator=gen).tolist() for s in range(n)]
+    toks = []
+    for s, pr in enumerate(prompts):
+        lr = ref.prefill(s, pr, 0)
+        eng.prefill(s, pr, 0)
+        toks.append(int(lr.argmax()))
+    pos = [len(pr) for pr in prompts]
+    want = ref.decode(list(range(n)), toks, pos)
+    tol = 0.05 * want.abs().max().item()
+    for nb in (32, 13, 3, 1):
+        got = eng.decode(list(range(nb)), toks[:nb], pos[:nb]).cpu()
+        assert (got - want[:nb]).abs().max().item() < tol, nb
+        assert eng.decode_argmax(list(range(nb)), toks[:nb], pos[:nb]) == got.argmax(-1).tolist()
+    from ollama_b200.ops import sk
+    sk.workspace("cuda").check()
