@@ -65,7 +65,11 @@ def _follower(model_path: str, rank: int, world: int, device: str, conn, max_chu
     except Exception as e:      # the leader turns this into a load error
         conn.send(("error", f"rank {rank}: {e}"))
         return
-    follow(be, TPControl(rank, world, tr))
+    from .transport import TransportError
+    try:
+        follow(be, TPControl(rank, world, tr))
+    except TransportError:      # the leader closed the pipe or died: nothing left to follow
+        be.close()
 
 
 class TPGroup:
@@ -98,12 +102,7 @@ class TPGroup:
             tr = PipeTransport(0, world, conns)
             be = TPBackend(config_from_gguf(g), _source(g, adapters), device=dev0, rank=0, world=world, group=tr, max_chunk=max_chunk,
                            kv_type=kv_type)
-            for c in conns:
-                if not c.poll(float(os.environ.get("B200_TP_LOAD_TIMEOUT", "600"))):
-                    raise RuntimeError("a tensor-parallel follower did not finish loading in time")
-                kind, info = c.recv()
-                if kind != "ready":
-                    raise RuntimeError(f"tensor-parallel follower failed to load: {info}")
+            tr.wait_ready()
         except Exception:
             self.kill()
             raise

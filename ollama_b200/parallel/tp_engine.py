@@ -189,6 +189,13 @@ class TPBackend(B200Backend):
         self.check_exchanges()
         return out
 
+    def decode_loop(self, slots, tokens, positions, n_steps, first_tokens=None):
+        # after a wait has run out every later wait of that channel returns at once with zeros: without this check the rest
+        # of the loop would be fast garbage
+        out = super().decode_loop(slots, tokens, positions, n_steps, first_tokens)
+        self.check_exchanges()
+        return out
+
     # -- decode ---------------------------------------------------------------------------------------
     def _norm_quant_reduce(self, w, nb):
         """x += sum of the partial rows of the last exchange; then RMSNorm + int8 quantisation of x."""

@@ -44,20 +44,77 @@ class DistTransport:
         return buf.tolist()
 
 
-class PipeTransport:
-    """Leader: ``conns`` = one connection per follower (index rank - 1).  Follower: ``conns`` = [connection to the leader]."""
+class TransportError(RuntimeError):
+    pass
 
-    def __init__(self, rank: int, world: int, conns: list):
+
+class PipeTransport:
+    """Leader: ``conns`` = one connection per follower (index rank - 1).  Follower: ``conns`` = [connection to the leader].
+
+    Every message is a (tag, payload) pair: "gather" (one rank's share of an all-gather, and the combined list on the way
+    back), "ints" (a call record), "ready" / "error" (a follower's load result).  The leader never blocks without a limit:
+    a follower that hangs while loading, or dies, ends the wait with a :class:`TransportError` instead of holding the
+    scheduler's load lock for ever; a follower's "error" arriving in the middle of an all-gather is raised at once rather
+    than being taken for that rank's share.  A follower that finds the pipe closed knows that the leader is gone.
+    """
+
+    def __init__(self, rank: int, world: int, conns: list, timeout: float | None = None):
+        import os
         self.rank, self.world, self.conns = rank, world, conns
+        self.timeout = float(os.environ.get("B200_TP_LOAD_TIMEOUT", "600")) if timeout is None else timeout
+        self.ready: set[int] = set()          # leader: followers whose "ready" has been seen (index into conns)
+
+    def _recv(self, i: int, want: str) -> Any:
+        c = self.conns[i]
+        while True:
+            if self.rank == 0 and not c.poll(self.timeout):
+                raise TransportError(f"tensor-parallel rank {i + 1} did not answer within {self.timeout:.0f} s")
+            try:
+                msg = c.recv()
+            except (EOFError, OSError) as e:
+                raise TransportError("tensor-parallel peer closed the control pipe" if self.rank == 0 else "leader gone") from e
+            if not isinstance(msg, tuple) or len(msg) != 2:
+                raise TransportError("tensor-parallel control channel out of step")
+            tag, payload = msg
+            if tag == want:
+                return payload
+            if tag == "error":
+                raise TransportError(f"tensor-parallel follower failed: {payload}")
+            if tag == "ready" and self.rank == 0:
+                self.ready.add(i)
+                continue
+            raise TransportError(f"tensor-parallel control channel out of step: got {tag!r}, expected {want!r}")
+
+    def wait_ready(self) -> None:
+        """Leader: block (bounded) until every follower has reported that it finished loading."""
+        for i in range(len(self.conns)):
+            if i not in self.ready:
+                self._await_ready(i)
+
+    def _await_ready(self, i: int) -> None:
+        c = self.conns[i]
+        while i not in self.ready:
+            if not c.poll(self.timeout):
+                raise TransportError("a tensor-parallel follower did not finish loading in time")
+            try:
+                tag, payload = c.recv()
+            except (EOFError, OSError) as e:
+                raise TransportError("a tensor-parallel follower exited while loading") from e
+            if tag == "ready":
+                self.ready.add(i)
+            elif tag == "error":
+                raise TransportError(f"tensor-parallel follower failed to load: {payload}")
+            else:
+                raise TransportError(f"tensor-parallel control channel out of step: got {tag!r} while waiting for a load result")
 
     def all_gather(self, obj: Any) -> list[Any]:
         if self.rank == 0:
-            out = [obj] + [c.recv() for c in self.conns]
+            out = [obj] + [self._recv(i, "gather") for i in range(len(self.conns))]
             for c in self.conns:
-                c.send(out)
+                c.send(("gather", out))
             return out
-        self.conns[0].send(obj)
-        return self.conns[0].recv()
+        self.conns[0].send(("gather", obj))
+        return self._recv(0, "gather")
 
     def barrier(self) -> None:
         self.all_gather(None)
@@ -65,11 +122,11 @@ class PipeTransport:
     def bcast_ints(self, ints: list[int] | None, n: int) -> list[int]:
         if self.rank == 0:
             for c in self.conns:
-                c.send(ints)
+                c.send(("ints", ints))
             return list(ints)
-        got = self.conns[0].recv()
+        got = self._recv(0, "ints")
         if not isinstance(got, list) or len(got) != n:
-            raise RuntimeError("tensor-parallel control channel out of step")
+            raise TransportError("tensor-parallel control channel out of step")
         return got
 
 

@@ -181,3 +181,39 @@ def test_runner_ping_follows_the_follower_processes():
     assert not grp.alive() and not r.ping()
     r._tp_group = None
     assert r.ping()
+
+
+def test_pipe_transport_bounds_every_wait_and_tags_its_messages():
+    """A follower that fails, hangs or dies never leaves the leader blocked, and its error is not mistaken for data."""
+    import multiprocessing as mp
+    import pytest
+    from ollama_b200.parallel.transport import PipeTransport, TransportError
+    ctx = mp.get_context("spawn")
+
+    def leader(n=1, timeout=0.3):
+        pairs = [ctx.Pipe() for _ in range(n)]
+        return PipeTransport(0, n + 1, [p for p, _ in pairs], timeout=timeout), [c for _, c in pairs]
+
+    # an error that arrives in the middle of an all-gather is raised, not returned as that rank's share
+    tr, (child,) = leader()
+    child.send(("error", "rank 1: out of memory"))
+    with pytest.raises(TransportError, match="out of memory"):
+        tr.all_gather("handle-0")
+    # a follower that never answers
+    tr, _ = leader()
+    with pytest.raises(TransportError, match="did not answer"):
+        tr.all_gather("handle-0")
+    with pytest.raises(TransportError, match="in time"):
+        tr.wait_ready()
+    # "ready" may overtake the leader's next all-gather: it is remembered, the gather still completes
+    tr, (child,) = leader()
+    child.send(("ready", 1))
+    child.send(("gather", "handle-1"))
+    assert tr.all_gather("handle-0") == ["handle-0", "handle-1"] and child.recv() == ("gather", ["handle-0", "handle-1"])
+    tr.wait_ready()          # already seen
+    # a follower learns that the leader is gone from the closed pipe
+    parent, child = ctx.Pipe()
+    f = PipeTransport(1, 2, [child])
+    parent.close()
+    with pytest.raises(TransportError, match="leader gone"):
+        f.bcast_ints(None, 6)
