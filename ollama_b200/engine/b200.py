@@ -176,6 +176,14 @@ class B200Backend:
             L.swa = c.layer_is_swa(i)
             L.sk = self._load_sk_layer(p, L, get, vec) if self.use_sk and not L.moe else None
             self.layers.append(L)
+        # Expert matrices as 16-bit copies for the grouped prefill GEMM when they fit into a third of the free memory (EP shards
+        # of the large models do: 30 to 60 GB per GPU); otherwise every chunk expands the layer's experts into scratch.
+        moe_layers = [L for L in self.layers if L.moe]
+        if moe_layers and self.keep_bf16 is not False:
+            need = sum(2 * (L.gu.total_rows * L.gu.k + L.down.total_rows * L.down.k) for L in moe_layers)
+            if need < 0.33 * torch.cuda.mem_get_info(dev)[0]:
+                for L in moe_layers:
+                    L.gu.bf16, L.down.bf16 = K.dequant_to_bf16(L.gu), K.dequant_to_bf16(L.down)
         self.sk_head = None
         if self.use_sk and self.last and all(L.sk is not None for L in self.layers):
             hw = get("output.weight" if not tied else "token_embd.weight")
@@ -353,39 +361,36 @@ class B200Backend:
         self._n += 4
 
     def _moe_prefill(self, h: torch.Tensor, L) -> torch.Tensor:
-        """Expert FFN of a prefill chunk: tokens are grouped by expert and each resident expert runs one pair of GEMMs.
+        """Expert FFN of a prefill chunk without leaving the device: the (token, expert-slot) pairs are sorted by expert into
+        128-row tiles, one grouped tensor-core GEMM runs gate/up with the gated activation in its epilogue, a second one the
+        down projection, and the weighted rows are added back per token.
 
         ``h``: [T, d_model] bf16.  Returns this GPU's (partial, under expert parallelism) FFN output [T, d_model] fp32.
         """
-        c, dev = self.cfg, self.device
-        T, k, F = h.shape[0], c.n_experts_used, c.d_ff_expert
+        c = self.cfg
+        T, k = h.shape[0], c.n_experts_used
         logits = h.float() @ L.router_f32.t()                       # [T, E]: tiny; kept in fp32 so that near-ties select as the fp32 graph does
         if L.router.bias is not None:
             logits = logits + L.router.bias
-        ids = torch.empty(T * k, device=dev, dtype=torch.int32)
-        lids, wts = torch.empty_like(ids), torch.empty(T * k, device=dev, dtype=torch.float32)
+        ids = torch.empty(T * k, device=self.device, dtype=torch.int32)
+        lids, wts = torch.empty_like(ids), torch.empty(T * k, device=self.device, dtype=torch.float32)
         self._route(logits.contiguous(), T, ids, lids, wts, False)
-        order = torch.argsort(lids, stable=True)                     # pairs of experts that live elsewhere (-1) come first
-        counts = torch.bincount(lids[lids >= 0], minlength=self.e_cnt).tolist()
-        xs = h[(order // k).long()]                                  # activation row of every pair, grouped by expert
-        ys = torch.zeros(T * k, c.d_model, device=dev, dtype=torch.float32)
-        off = T * k - sum(counts)
-        for e, n in enumerate(counts):
-            if n == 0:
-                continue
-            wg = K.dequant_to_bf16(L.gu, e * 2 * F, 2 * F)
-            gb = L.gu.bias[e * 2 * F:(e + 1) * 2 * F] if L.gu.bias is not None else None
-            gu = K.gemm_bf16(xs[off:off + n], wg, gb)
-            f = R.glu(gu[:, 0::2], gu[:, 1::2], c.act, c.swiglu_alpha, c.swiglu_limit).to(torch.bfloat16)
-            wd = K.dequant_to_bf16(L.down, e * c.d_model, c.d_model)
-            db = L.down.bias[e * c.d_model:(e + 1) * c.d_model] if L.down.bias is not None else None
-            K.gemm_bf16(f, wd, db, out=ys[off:off + n])
-            self.kernel_launches += 4
-            off += n
-        y = torch.zeros_like(ys)
-        y[order] = ys
-        self.kernel_launches += 1
-        return (y.view(T, k, c.d_model) * wts.view(T, k, 1)).sum(1)
+        row, tile_expert, rows = K.moe_plan(lids, self.e_cnt)
+        xs = K.moe_gather(h, row, k, rows)
+        gu16 = getattr(L.gu, "bf16", None)
+        if gu16 is None:
+            gu16 = K.dequant_to_bf16(L.gu)                        # all resident experts at once: scratch until the call returns
+            self.kernel_launches += 1
+        f = K.gemm_bf16_grouped(xs, gu16, self.e_cnt, tile_expert, L.gu.bias, glu=c.act, alpha=c.swiglu_alpha, limit=c.swiglu_limit)
+        del gu16
+        dn16 = getattr(L.down, "bf16", None)
+        if dn16 is None:
+            dn16 = K.dequant_to_bf16(L.down)
+            self.kernel_launches += 1
+        ys = K.gemm_bf16_grouped(f, dn16, self.e_cnt, tile_expert, L.down.bias)
+        del dn16
+        self.kernel_launches += 6
+        return K.moe_scatter_combine(ys, row, wts, T, k)
 
     def _sk(self, ws, x: torch.Tensor, out: torch.Tensor, nb: int, norm_w=None, mode: int = SK.MODE_STORE) -> None:
         """One streaming GEMV of the decode step: fp32 rows in (normalised with ``norm_w``), ``out`` stored / added to / gated."""
@@ -603,6 +608,20 @@ class B200Backend:
             return K.gemm_bf16(x_bf16, wb, w.bias, out=out[:, out_off:out_off + w.n], accumulate=accumulate)
         return K.gemm_bf16(x_bf16, wb, w.bias)
 
+    def _mm_glu(self, x_bf16: torch.Tensor, w: K.DevWeight) -> torch.Tensor:
+        """act(gate) * up of the interleaved gate/up matrix for a prefill chunk, bf16 [T, d_ff]."""
+        c = self.cfg
+        if self.prefill_gemm == "fused" and K.gemm_q_supported(w):
+            self.kernel_launches += 2
+            gu = K.gemm_q(x_bf16, w).to(torch.bfloat16)                  # columns interleaved: even = gate, odd = up
+            return K.glu_rows(gu, c.act, c.swiglu_alpha, c.swiglu_limit)
+        wb = getattr(w, "bf16", None)
+        if wb is None:
+            wb = K.dequant_to_bf16(w)
+            self.kernel_launches += 1
+        self.kernel_launches += 1
+        return K.gemm_bf16_glu(x_bf16, wb, c.act, w.bias, c.swiglu_alpha, c.swiglu_limit)
+
     def _attn_prefill(self, q: torch.Tensor, i: int, L, slot: int, pos0: int, p_end: int) -> torch.Tensor:
         """Attention of a prefill chunk over cache positions [0, p_end): q [T, H, hd] fp32 -> bf16 [T, H * hd]."""
         c = self.cfg
@@ -658,8 +677,7 @@ class B200Backend:
             if L.moe:
                 x = x + self._moe_prefill(h, L)
                 continue
-            gu = self._mm(h, L.gu, out16=True)                            # columns interleaved: even = gate, odd = up
-            f = K.glu_rows(gu, c.act, c.swiglu_alpha, c.swiglu_limit)
+            f = self._mm_glu(h, L.gu)                                     # gate/up with the gated activation in the GEMM epilogue
             if c.sandwich_norm:
                 x = x + R.rmsnorm(self._mm(f, L.down), L.post_ffw_norm, c.norm_eps)
             else:

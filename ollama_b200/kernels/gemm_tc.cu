@@ -40,6 +40,12 @@ struct GemmParams {
     int out_bf16;
     CommSend cm;            // cm.n_dst > 0: row r goes to cm.dst[r / rows_per_rank] at row r % rows_per_rank (bf16)
     int rows_per_rank;
+    // grouped (mixture of experts): b holds E stacked [n][k] matrices and bias E x n values; the rows of a are sorted by expert
+    // and every 128-row tile belongs to one expert.  tile_expert[mt] = that expert, or -1: the tile holds no rows.
+    const int* tile_expert;
+    // gated activation in the epilogue: columns 2i / 2i + 1 are gate / up of output i; out is bf16 [m][ldo] with n / 2 columns
+    int glu;                // 0: off, 1 + act otherwise (0 silu, 1 gelu_tanh, 2 clamped swiglu)
+    float glu_alpha, glu_limit;
 };
 
 template <int BN>
@@ -115,13 +121,15 @@ __global__ void __launch_bounds__(192, 1) gemm_bf16_tc_kernel(const __grid_const
             for (int t = blockIdx.x; t < total && ok; t += gridDim.x) {
                 int mt, nt;
                 tile_coords(t, tiles_m, tiles_n, mt, nt);
+                const int e = p.tile_expert ? p.tile_expert[mt] : 0;
+                if (e < 0) continue;               // every role skips the same tiles
                 for (int kb = 0; kb < k_blocks; kb++, it++) {
                     const int s = it % STAGES;
                     if (it >= STAGES && !mbar_wait(&empty[s], ((it / STAGES) - 1) & 1)) { ok = false; break; }
                     uint8_t* a_dst = tiles + s * L::STAGE_BYTES;
                     mbar_expect_tx(&full[s], L::STAGE_BYTES);
                     tma_load_2d(a_dst, &map_a, kb * BK, mt * BM, &full[s]);
-                    tma_load_2d(a_dst + L::A_BYTES, &map_b, kb * BK, nt * BN, &full[s]);
+                    tma_load_2d(a_dst + L::A_BYTES, &map_b, kb * BK, e * p.n + nt * BN, &full[s]);
                 }
             }
             if (!ok) atomicExch(&s_failed, 1);
@@ -131,8 +139,14 @@ __global__ void __launch_bounds__(192, 1) gemm_bf16_tc_kernel(const __grid_const
             constexpr uint32_t idesc = umma_idesc(BM, BN);
             int it = 0, i = 0;
             bool ok = true;
-            for (int t = blockIdx.x; t < total && ok; t += gridDim.x, i++) {
+            for (int t = blockIdx.x; t < total && ok; t += gridDim.x) {
+                if (p.tile_expert) {
+                    int mt, nt;
+                    tile_coords(t, tiles_m, tiles_n, mt, nt);
+                    if (p.tile_expert[mt] < 0) continue;
+                }
                 const int buf = i & 1, use = i >> 1;
+                i++;
                 if (use >= 1 && !mbar_wait(&acc_empty[buf], (use - 1) & 1)) { ok = false; break; }
                 tc_fence_after();
                 const uint32_t acc = tmem_base + (uint32_t)(buf * L::ACC_STRIDE);
@@ -158,10 +172,13 @@ __global__ void __launch_bounds__(192, 1) gemm_bf16_tc_kernel(const __grid_const
         const int q = warp & 3;
         int i = 0;
         bool ok = true;
-        for (int t = blockIdx.x; t < total && ok; t += gridDim.x, i++) {
+        for (int t = blockIdx.x; t < total && ok; t += gridDim.x) {
             int mt, nt;
             tile_coords(t, tiles_m, tiles_n, mt, nt);
+            const int e = p.tile_expert ? p.tile_expert[mt] : 0;
+            if (e < 0) continue;
             const int buf = i & 1, use = i >> 1;
+            i++;
             if (!mbar_wait(&acc_full[buf], use & 1)) { ok = false; break; }
             tc_fence_after();
             // Each thread reads 32 columns of its own accumulator row; a 32 x 32 transpose through shared memory turns that into
@@ -181,7 +198,7 @@ __global__ void __launch_bounds__(192, 1) gemm_bf16_tc_kernel(const __grid_const
                 __syncwarp();
                 const int col = n0 + c0 + cq;
                 float4 bias = make_float4(0.f, 0.f, 0.f, 0.f);
-                if (p.bias && col < p.n) bias = *(const float4*)(p.bias + col);
+                if (p.bias && col < p.n) bias = *(const float4*)(p.bias + (size_t)e * p.n + col);
 #pragma unroll
                 for (int rr = 0; rr < 8; rr++) {
                     const int lr = rr * 4 + sub;
@@ -189,7 +206,10 @@ __global__ void __launch_bounds__(192, 1) gemm_bf16_tc_kernel(const __grid_const
                     if (row >= p.m || col >= p.n) continue;
                     float4 r = *(const float4*)(st + lr * L::EPI_LD + cq);
                     r.x += bias.x; r.y += bias.y; r.z += bias.z; r.w += bias.w;
-                    if (p.cm.n_dst > 0) {      // partial rows travel as bf16: half the NVLink bytes of fp32
+                    if (p.glu) {               // (gate, up, gate, up) -> two activated outputs
+                        const float h0 = glu_act(r.x, r.y, p.glu - 1, p.glu_alpha, p.glu_limit), h1 = glu_act(r.z, r.w, p.glu - 1, p.glu_alpha, p.glu_limit);
+                        *(uint32_t*)((__nv_bfloat16*)p.out + (size_t)row * p.ldo + (col >> 1)) = pack2_bf16(h0, h1);
+                    } else if (p.cm.n_dst > 0) {      // partial rows travel as bf16: half the NVLink bytes of fp32
                         const int owner = row / p.rows_per_rank;
                         __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(p.cm.dst[owner]) + (size_t)(row - owner * p.rows_per_rank) * p.ldo + col;
                         *(uint2*)dst = make_uint2(pack2_bf16(r.x, r.y), pack2_bf16(r.z, r.w));
@@ -234,9 +254,9 @@ int sm_count() {
 }
 
 template <int BN>
-int launch(const void* a, const void* b, const GemmParams& p, cudaStream_t st) {
+int launch(const void* a, const void* b, const GemmParams& p, cudaStream_t st, int b_rows = 0) {
     CUtensorMap ma, mb;
-    if (!make_map(&ma, a, p.m, p.k, BM) || !make_map(&mb, b, p.n, p.k, BN)) return (int)cudaErrorNotSupported;
+    if (!make_map(&ma, a, p.m, p.k, BM) || !make_map(&mb, b, b_rows ? b_rows : p.n, p.k, BN)) return (int)cudaErrorNotSupported;
     static PerDeviceOnce once;
     if (once.first()) cudaFuncSetAttribute(gemm_bf16_tc_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg<BN>::TOTAL);
     const int total = ((p.m + BM - 1) / BM) * ((p.n + BN - 1) / BN);
@@ -245,14 +265,14 @@ int launch(const void* a, const void* b, const GemmParams& p, cudaStream_t st) {
     return (int)cudaGetLastError();
 }
 
-int dispatch(const void* a, const void* b, const GemmParams& p, cudaStream_t st) {
+int dispatch(const void* a, const void* b, const GemmParams& p, cudaStream_t st, int b_rows = 0) {
     // wide tiles once they fill the machine; narrower ones keep more SMs busy on small problems
     const long tiles_m = (p.m + BM - 1) / BM;
-    if (p.n >= 256 && tiles_m * ((p.n + 255) / 256) >= sm_count()) return launch<256>(a, b, p, st);
+    if (p.n >= 256 && tiles_m * ((p.n + 255) / 256) >= sm_count()) return launch<256>(a, b, p, st, b_rows);
     // one round either way: the widest tile that still gives every SM at most one tile
-    if (p.n >= 192 && tiles_m * ((p.n + 191) / 192) <= sm_count() && tiles_m * ((p.n + 127) / 128) > sm_count()) return launch<192>(a, b, p, st);
-    if (p.n >= 128) return launch<128>(a, b, p, st);
-    return launch<64>(a, b, p, st);
+    if (p.n >= 192 && tiles_m * ((p.n + 191) / 192) <= sm_count() && tiles_m * ((p.n + 127) / 128) > sm_count()) return launch<192>(a, b, p, st, b_rows);
+    if (p.n >= 128) return launch<128>(a, b, p, st, b_rows);
+    return launch<64>(a, b, p, st, b_rows);
 }
 
 bool bad_operands(const void* a, const void* b, int m, int n, int k, int ldo) {
@@ -266,14 +286,14 @@ bool bad_operands(const void* a, const void* b, int m, int n, int k, int ldo) {
 B2_API int b2_gemm_bf16(const void* a, const void* b, int m, int n, int k, float* out, int ldo, const float* bias, int accumulate,
                         cudaStream_t st) {
     if (bad_operands(a, b, m, n, k, ldo) || ((uintptr_t)out & 15)) return (int)cudaErrorInvalidValue;
-    GemmParams p{m, n, k, out, ldo, bias, accumulate, 0, {}, 0};
+    GemmParams p{m, n, k, out, ldo, bias, accumulate, 0, {}, 0, nullptr, 0, 0.f, 0.f};
     return dispatch(a, b, p, st);
 }
 
 // Same product with a bf16 result (n % 8 == 0, ldo % 8 == 0); no accumulation.
 B2_API int b2_gemm_bf16_out16(const void* a, const void* b, int m, int n, int k, void* out, int ldo, const float* bias, cudaStream_t st) {
     if (bad_operands(a, b, m, n, k, ldo) || (n & 7) || (ldo & 7) || ((uintptr_t)out & 15)) return (int)cudaErrorInvalidValue;
-    GemmParams p{m, n, k, out, ldo, bias, 0, 1, {}, 0};
+    GemmParams p{m, n, k, out, ldo, bias, 0, 1, {}, 0, nullptr, 0, 0.f, 0.f};
     return dispatch(a, b, p, st);
 }
 
@@ -284,8 +304,29 @@ B2_API int b2_gemm_bf16_scatter(const void* a, const void* b, int m, int n, int 
     if (bad_operands(a, b, m, n, k, ldo) || !cm || rows_per_rank < 1 || cm->n_dst < 1 || cm->n_dst > COMM_MAX_RANKS ||
         (m + rows_per_rank - 1) / rows_per_rank > cm->n_dst)
         return (int)cudaErrorInvalidValue;
-    GemmParams p{m, n, k, nullptr, ldo, bias, 0, 0, *cm, rows_per_rank};
+    GemmParams p{m, n, k, nullptr, ldo, bias, 0, 0, *cm, rows_per_rank, nullptr, 0, 0.f, 0.f};
     return dispatch(a, b, p, st);
+}
+
+// Gate/up product with the gated activation in the epilogue: out[m][n / 2] (bf16) = act(gate, up) of the interleaved columns of
+// a . b^T + bias.  act: 0 silu, 1 gelu_tanh, 2 clamped swiglu (alpha, limit).
+B2_API int b2_gemm_bf16_glu(const void* a, const void* b, int m, int n, int k, void* out, int ldo, const float* bias, int act, float alpha,
+                            float limit, cudaStream_t st) {
+    if (bad_operands(a, b, m, n, k, ldo) || (n & 7) || (ldo & 1) || ((uintptr_t)out & 3) || act < 0 || act > 2) return (int)cudaErrorInvalidValue;
+    GemmParams p{m, n, k, out, ldo, bias, 0, 1, {}, 0, nullptr, 1 + act, alpha, limit};
+    return dispatch(a, b, p, st);
+}
+
+// Grouped product over the experts of a mixture-of-experts layer in one launch.  a: [m][k] rows sorted by expert, every 128-row
+// tile owned by one expert (tile_expert[m / 128] on the device: expert index, or -1 for a tile without rows); b: `experts`
+// stacked [n][k] matrices; bias: experts x n or null.  glu_act < 0: out fp32 [m][ldo] = a . b_e^T + bias_e; otherwise the gated
+// activation of interleaved gate/up columns, out bf16 [m][ldo] with n / 2 columns.
+B2_API int b2_gemm_bf16_grouped(const void* a, const void* b, int m, int n, int k, int experts, const int* tile_expert, void* out, int ldo,
+                                const float* bias, int glu_act_id, float alpha, float limit, cudaStream_t st) {
+    if (bad_operands(a, b, m, n, k, ldo) || !tile_expert || experts < 1 || glu_act_id > 2 || ((uintptr_t)out & 15)) return (int)cudaErrorInvalidValue;
+    if (glu_act_id >= 0 && ((n & 7) || (ldo & 1))) return (int)cudaErrorInvalidValue;
+    GemmParams p{m, n, k, out, ldo, bias, 0, glu_act_id >= 0 ? 1 : 0, {}, 0, tile_expert, glu_act_id >= 0 ? 1 + glu_act_id : 0, alpha, limit};
+    return dispatch(a, b, p, st, experts * n);
 }
 
 B2_API int b2_gemm_status() {

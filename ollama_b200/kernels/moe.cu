@@ -160,3 +160,113 @@ B2_API int b2_moe_combine(const MoeCombineArgs* a, int tokens, int pdl, cudaStre
     void* args[] = {&copy};
     return (int)cudaLaunchKernelExC(&cfg, (const void*)moe_combine_kernel, args);
 }
+
+// ---------------------------------------------------------------------------------------------
+// Grouped prefill.  The (token, expert-slot) pairs of a chunk are laid out in a buffer sorted by expert in which every
+// expert's rows start at a multiple of 128, so that one tensor-core GEMM launch with a tile -> expert table covers all
+// experts (kernels/gemm_tc.cu, b2_gemm_bf16_grouped).  Everything happens on the device: no count ever visits the host.
+// ---------------------------------------------------------------------------------------------
+struct MoePlanArgs {
+    const int* lids;       // [pairs] expert index on this GPU, or -1
+    int pairs;
+    int n_experts;         // experts on this GPU, <= 512
+    int* row_of_pair;      // [pairs] row of the pair in the sorted buffer, or -1
+    int* tile_expert;      // [max_tiles] expert of every 128-row tile, -1 for tiles without rows
+    int max_tiles;
+};
+
+// one CTA: count, scan the padded counts, hand out rows.  The order of the pairs inside an expert depends on the atomics, the
+// value computed for a pair does not.
+__global__ void __launch_bounds__(1024) moe_plan_kernel(const __grid_constant__ MoePlanArgs a) {
+    __shared__ int cnt[512], off[513], cur[512];
+    const int tid = threadIdx.x;
+    for (int e = tid; e < a.n_experts; e += 1024) cnt[e] = cur[e] = 0;
+    __syncthreads();
+    for (int p = tid; p < a.pairs; p += 1024) {
+        const int l = a.lids[p];
+        if (l >= 0 && l < a.n_experts) atomicAdd(&cnt[l], 1);
+    }
+    __syncthreads();
+    if (tid == 0) {
+        int o = 0;
+        for (int e = 0; e < a.n_experts; e++) {
+            off[e] = o;
+            o += (cnt[e] + 127) & ~127;
+        }
+        off[a.n_experts] = o;
+    }
+    __syncthreads();
+    for (int t = tid; t < a.max_tiles; t += 1024) {
+        // the expert whose padded range holds row 128 t (ranges are ascending: a short linear search per tile)
+        int e = -1;
+        const int row = t * 128;
+        if (row < off[a.n_experts]) {
+            int lo = 0, hi = a.n_experts - 1;
+            while (lo < hi) {
+                const int mid = (lo + hi + 1) >> 1;
+                if (off[mid] <= row) lo = mid; else hi = mid - 1;
+            }
+            e = lo;
+            // experts without rows share their offset with the next one: step to the one that owns the row
+            while (e < a.n_experts - 1 && off[e + 1] <= row) e++;
+            if (row >= off[e] + ((cnt[e] + 127) & ~127)) e = -1;
+        }
+        a.tile_expert[t] = e;
+    }
+    for (int p = tid; p < a.pairs; p += 1024) {
+        const int l = a.lids[p];
+        int r = -1;
+        if (l >= 0 && l < a.n_experts) r = off[l] + atomicAdd(&cur[l], 1);
+        a.row_of_pair[p] = r < a.max_tiles * 128 ? r : -1;
+    }
+}
+
+B2_API int b2_moe_plan(const MoePlanArgs* a, cudaStream_t st) {
+    if (a->pairs < 1 || a->n_experts < 1 || a->n_experts > 512 || a->max_tiles < 1) return (int)cudaErrorInvalidValue;
+    moe_plan_kernel<<<1, 1024, 0, st>>>(*a);
+    return (int)cudaGetLastError();
+}
+
+// xs[row_of_pair[p]] = h[p / k]   (bf16 rows of d elements, d % 8 == 0)
+__global__ void __launch_bounds__(128) moe_gather_kernel(const uint4* h, const int* row_of_pair, int k, int d8, uint4* xs) {
+    const int p = blockIdx.x, r = row_of_pair[p];
+    if (r < 0) return;
+    const uint4* src = h + (size_t)(p / k) * d8;
+    uint4* dst = xs + (size_t)r * d8;
+    for (int c = threadIdx.x; c < d8; c += 128) dst[c] = src[c];
+}
+
+B2_API int b2_moe_gather(const void* h, const int* row_of_pair, int pairs, int k, int d, void* xs, cudaStream_t st) {
+    if (pairs < 1 || k < 1 || (d & 7) || ((uintptr_t)h & 15) || ((uintptr_t)xs & 15)) return (int)cudaErrorInvalidValue;
+    moe_gather_kernel<<<pairs, 128, 0, st>>>((const uint4*)h, row_of_pair, k, d >> 3, (uint4*)xs);
+    return (int)cudaGetLastError();
+}
+
+// out[t] (+)= sum_s wts[t][s] * ys[row_of_pair[t k + s]]   (pairs whose expert lives elsewhere contribute nothing)
+__global__ void __launch_bounds__(256) moe_scatter_combine_kernel(const float* ys, const int* row_of_pair, const float* wts, int k, int d,
+                                                                  float* out, int accumulate) {
+    const int t = blockIdx.x;
+    for (int c = threadIdx.x; c < (d >> 2); c += 256) {
+        float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+        for (int s = 0; s < k; s++) {
+            const int r = row_of_pair[(size_t)t * k + s];
+            if (r < 0) continue;
+            const float w = wts[(size_t)t * k + s];
+            const float4 v = *(const float4*)(ys + (size_t)r * d + 4 * c);
+            acc.x += w * v.x; acc.y += w * v.y; acc.z += w * v.z; acc.w += w * v.w;
+        }
+        float4* o = (float4*)(out + (size_t)t * d + 4 * c);
+        if (accumulate) {
+            const float4 x = *o;
+            acc.x += x.x; acc.y += x.y; acc.z += x.z; acc.w += x.w;
+        }
+        *o = acc;
+    }
+}
+
+B2_API int b2_moe_scatter_combine(const float* ys, const int* row_of_pair, const float* wts, int tokens, int k, int d, float* out,
+                                  int accumulate, cudaStream_t st) {
+    if (tokens < 1 || k < 1 || (d & 3)) return (int)cudaErrorInvalidValue;
+    moe_scatter_combine_kernel<<<tokens, 256, 0, st>>>(ys, row_of_pair, wts, k, d, out, accumulate);
+    return (int)cudaGetLastError();
+}

@@ -540,3 +540,71 @@ def gemm_q(x: torch.Tensor, w: DevWeight, out: torch.Tensor | None = None, accum
     f.argtypes = [C.c_void_p, C.c_int, C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_void_p]
     _check(f(ptr(x), m, C.addressof(d), ptr(out), out.stride(0), int(accumulate), stream()), "gemm_q")
     return out
+
+
+# ---------------------------------------------------------------------------------------------------
+# grouped mixture-of-experts prefill
+# ---------------------------------------------------------------------------------------------------
+class MoePlanArgs(C.Structure):
+    _fields_ = [("lids", C.c_void_p), ("pairs", C.c_int), ("n_experts", C.c_int), ("row_of_pair", C.c_void_p), ("tile_expert", C.c_void_p),
+                ("max_tiles", C.c_int)]
+
+
+def moe_plan(lids: torch.Tensor, n_experts: int) -> tuple[torch.Tensor, torch.Tensor, int]:
+    """Rows of a buffer sorted by expert for the (token, expert-slot) pairs ``lids`` (local expert or -1): returns
+    (row_of_pair int32 [pairs], tile_expert int32 [tiles], padded row count).  Every expert's rows start at a multiple of 128."""
+    pairs = lids.numel()
+    max_tiles = (pairs + 127) // 128 + n_experts
+    row = torch.empty(pairs, dtype=torch.int32, device=lids.device)
+    te = torch.empty(max_tiles, dtype=torch.int32, device=lids.device)
+    a = MoePlanArgs(ptr(lids), pairs, n_experts, ptr(row), ptr(te), max_tiles)
+    _check(lib().b2_moe_plan(C.byref(a), stream()), "moe_plan")
+    return row, te, max_tiles * 128
+
+
+def moe_gather(h: torch.Tensor, row_of_pair: torch.Tensor, k: int, rows: int) -> torch.Tensor:
+    """bf16 activation rows [T, d] -> [rows, d] sorted by expert (rows nobody owns are left as they are)."""
+    xs = torch.empty(rows, h.shape[1], dtype=torch.bfloat16, device=h.device)
+    f = lib().b2_moe_gather
+    f.argtypes = [C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_void_p, C.c_void_p]
+    _check(f(ptr(h), ptr(row_of_pair), row_of_pair.numel(), k, h.shape[1], ptr(xs), stream()), "moe_gather")
+    return xs
+
+
+def moe_scatter_combine(ys: torch.Tensor, row_of_pair: torch.Tensor, wts: torch.Tensor, tokens: int, k: int, out: torch.Tensor | None = None,
+                        accumulate: bool = False) -> torch.Tensor:
+    d = ys.shape[1]
+    if out is None:
+        out = torch.empty(tokens, d, dtype=torch.float32, device=ys.device)
+    f = lib().b2_moe_scatter_combine
+    f.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_void_p, C.c_int, C.c_void_p]
+    _check(f(ptr(ys), ptr(row_of_pair), ptr(wts), tokens, k, d, ptr(out), int(accumulate), stream()), "moe_scatter_combine")
+    return out
+
+
+def gemm_bf16_grouped(a: torch.Tensor, b: torch.Tensor, experts: int, tile_expert: torch.Tensor, bias: torch.Tensor | None = None,
+                      glu: str | None = None, alpha: float = 1.702, limit: float = 7.0) -> torch.Tensor:
+    """One launch over all experts: a [m, k] bf16 sorted by expert in 128-row tiles, b [experts * n, k] bf16.  Returns fp32 [m, n], or
+    with ``glu`` (activation name) the gated activation of interleaved gate/up columns as bf16 [m, n / 2]."""
+    m, k = a.shape
+    n = b.shape[0] // experts
+    a, b = a.contiguous(), b.contiguous()
+    out = torch.empty(m, n // 2, device=a.device, dtype=torch.bfloat16) if glu else torch.empty(m, n, device=a.device, dtype=torch.float32)
+    f = lib().b2_gemm_bf16_grouped
+    f.argtypes = [C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_int, C.c_void_p, C.c_void_p, C.c_int, C.c_void_p, C.c_int, C.c_float,
+                  C.c_float, C.c_void_p]
+    _check(f(ptr(a), ptr(b), m, n, k, experts, ptr(tile_expert), ptr(out), out.stride(0), ptr(bias), _ACT[glu] if glu else -1, alpha, limit,
+             stream()), "gemm_bf16_grouped")
+    return out
+
+
+def gemm_bf16_glu(a: torch.Tensor, b: torch.Tensor, act: str, bias: torch.Tensor | None = None, alpha: float = 1.702, limit: float = 7.0) -> torch.Tensor:
+    """Gate/up product of a dense FFN with the gated activation in the GEMM epilogue: bf16 [m, n / 2]."""
+    m, k = a.shape
+    n = b.shape[0]
+    a, b = a.contiguous(), b.contiguous()
+    out = torch.empty(m, n // 2, device=a.device, dtype=torch.bfloat16)
+    f = lib().b2_gemm_bf16_glu
+    f.argtypes = [C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_void_p, C.c_int, C.c_void_p, C.c_int, C.c_float, C.c_float, C.c_void_p]
+    _check(f(ptr(a), ptr(b), m, n, k, ptr(out), out.stride(0), ptr(bias), _ACT[act], alpha, limit, stream()), "gemm_bf16_glu")
+    return out

@@ -339,9 +339,7 @@ class TPBackend(B200Backend):
                 K._check(f_sc(K.ptr(part), T, c.d_model, rpr, C.addressof(self.cm_rs), K.stream()), "tp_scatter_rows")
                 self.kernel_launches += 1
                 continue
-            gu = self._mm(h, L.gu, out16=True)
-            self._mm_scatter(K.glu_rows(gu, c.act, c.swiglu_alpha, c.swiglu_limit), L.down, rpr)
-            self.kernel_launches += 1
+            self._mm_scatter(self._mm_glu(h, L.gu), L.down, rpr)
         self._norm_gather(self.out_norm, rows, row0, reduce=True)
         return h
 
