@@ -95,7 +95,8 @@ class B200Backend:
         self.pdl = True
         # Decode matrices in unit order for the streaming GEMV (Q4_K / Q6_K layers without experts or sandwich norms); B200_SK=0
         # keeps every layer on the dp4a kernels.
-        self.use_sk = os.environ.get("B200_SK", "1") != "0" and not self.cfg.sandwich_norm
+        # Subclasses that enqueue their own decode kernels (tensor parallelism) keep the dp4a planes.
+        self.use_sk = os.environ.get("B200_SK", "1") != "0" and not self.cfg.sandwich_norm and type(self) is B200Backend
         self.max_batch = MAX_DECODE_BATCH
         self.fuse_attn_combine = False    # one launch (last CTA merges the splits) measured slower than two launches joined by PDL
         self.use_graphs = True

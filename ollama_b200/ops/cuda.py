@@ -145,6 +145,8 @@ class DevWeight:
 
     def desc(self, out_off: int = 0, row0: int = 0, rows: int | None = None) -> WDesc:
         """Descriptor of rows [row0, row0+rows) (used for expert slices of stacked tensors)."""
+        if not self.planes:      # a kernel given null planes would fault on the device: refuse on the host
+            raise CudaKernelError(f"{self.name or 'weight'}: the planes of this matrix were released (it runs on the streaming GEMV)")
         d = WDesc()
         ps = [0, 0, 0, 0]
         for i, p in enumerate(self.planes):
