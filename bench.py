@@ -252,7 +252,8 @@ def main() -> None:
     tp_selfcheck = None
     if world > 1 and not pp:
         from ollama_b200.parallel.selftest import run_selfcheck
-        sc = run_selfcheck(rank, world, dev, steps=3)
+        # 8-bit blocks of 32 divide the small model's 128 columns per rank at 4 and 8 ranks; 256-element K-quant blocks only at 2
+        sc = run_selfcheck(rank, world, dev, quant="Q4_K_M" if world == 2 else "Q8_0", steps=3)
         tp_selfcheck = "ok" if sc["ok"] else f"failed: {json.dumps(sc)}"
         if not sc["ok"]:
             if rank == 0:

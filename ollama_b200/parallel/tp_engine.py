@@ -59,7 +59,7 @@ def shard_plan(cfg: ModelConfig, world: int, types: dict[str, int] | None = None
         bs = max([block_size(t) for n, t in (types or {}).items() if n.endswith(name + ".weight")] or [256])
         if cols % bs:
             raise ValueError(f"{name}: {cols} columns per rank do not fall on {bs}-element quantisation blocks")
-    if fl % 32:
+    if fl % 32 and not cfg.is_moe:       # expert models have no dense FFN to split
         raise ValueError(f"FFN width per rank {fl} is not a multiple of 32")
     vl = (cfg.vocab_size + world - 1) // world
     vl = (vl + 7) // 8 * 8
