@@ -30,6 +30,27 @@ class CreateError(Exception):
         self.status = status
 
 
+def _detect_template(layers) -> tuple[str, tuple[str, ...]]:
+    """(Go template, stop strings) for the model layer's ``tokenizer.chat_template`` when it is a named layout, else ("", ())."""
+    from ..gguf.reader import open_gguf
+    from ..text import named
+    for l in layers:
+        if l.media_type != M.MT_MODEL:
+            continue
+        try:
+            g = open_gguf(l.path())
+        except Exception:
+            return "", ()
+        try:
+            jinja = g.kv.get("tokenizer.chat_template")
+        finally:
+            g.close()
+        layout = named.detect(jinja) if isinstance(jinja, str) else None
+        if layout is not None:
+            return named.gotemplate(layout), layout.stop
+    return "", ()
+
+
 def _param_size(n: int) -> str:
     from ..utils.format import human_number
     return human_number(n)
@@ -219,6 +240,11 @@ def create_model(req: dict[str, Any]) -> Iterator[dict[str, Any]]:
 
     template = req.get("template") or base_template
     system = req.get("system") if req.get("system") is not None else base_system
+    detected_stop: tuple[str, ...] = ()
+    if not template and not req.get("renderer"):
+        # a bare checkpoint: when its Jinja chat template is one of the well-known layouts the model gets the equivalent Go
+        # template and that layout's stop strings (server/create.go detectChatTemplate, template/template.go Named)
+        template, detected_stop = _detect_template(layers)
     if template:
         from ..text.template import Template
         from ..text.gotemplate import TemplateError
@@ -234,6 +260,8 @@ def create_model(req: dict[str, Any]) -> Iterator[dict[str, Any]]:
     for l in lic:
         layers.append(M.new_layer(l.encode(), M.MT_LICENSE))
     params = dict(base_opts)
+    if detected_stop and "stop" not in params:
+        params["stop"] = list(detected_stop)
     params.update(req.get("parameters") or {})
     if params:
         layers.append(M.new_layer(json.dumps(params, sort_keys=True).encode(), M.MT_PARAMS))
