@@ -5,23 +5,36 @@ The reference keeps one Go type per family (model/renderers/renderer.go:60-120, 
 Here all parsers are instances of one streaming state machine over literal tags (:class:`TagStreamParser`)
 that differ in their tags and in how the body of a tool call is decoded:
 
-===================  ==========================  ===================================================================
-name                 reasoning block             tool call
-===================  ==========================  ===================================================================
-``qwen3``            none                        ``<tool_call>{"name": .., "arguments": {..}}</tool_call>``
-``qwen3-thinking``   starts inside ``<think>``   same
-``qwen3-coder``      none                        ``<tool_call><function=f><parameter=k>\\nv\\n</parameter></function></tool_call>``
-``ministral``        ``[THINK]..[/THINK]``       ``[TOOL_CALLS]name[ARGS]{json}``
-``functiongemma``    none                        ``<start_function_call>call:name{k:<escape>v<escape>}<end_function_call>``
-``passthrough``      none                        none
-===================  ==========================  ===================================================================
+======================  ==========================  ================================================================
+name                    reasoning block             tool call
+======================  ==========================  ================================================================
+``qwen3``               none                        ``<tool_call>{"name": .., "arguments": {..}}</tool_call>``
+``qwen3-thinking``      starts inside ``<think>``   same
+``qwen3-vl-instruct``   none                        same
+``qwen3-vl-thinking``   starts inside ``<think>``   same; a call may cut the reasoning block short
+``qwen3-coder``         none                        ``<tool_call><function=f><parameter=k>\\nv\\n</parameter></function></tool_call>``
+``ministral``           ``[THINK]..[/THINK]``       ``[TOOL_CALLS]name[ARGS]{json}``
+``functiongemma``       none                        ``<start_function_call>call:name{k:<escape>v<escape>}<end_function_call>``
+``cogito``              on request, no open tag     ``function<sep>name`` + fenced JSON, between call marks inside a calls block
+``deepseek3``           on request, no open tag     ``name<sep>{json}`` between call marks inside a calls block
+``olmo3``               none                        ``<function_calls>name(k="v", n=1)`` one per line ``</function_calls>``
+``olmo3-think``         starts inside ``<think>``   none
+``glm-4.6``             ``<think>..</think>``       ``<tool_call>name<arg_key>k</arg_key><arg_value>v</arg_value></tool_call>``
+``glm-4.7``             starts inside ``<think>``   same
+``passthrough``         none                        none
+======================  ==========================  ================================================================
 
-``harmony`` is handled by :mod:`ollama_b200.text.harmony`.  Renderers: ``qwen3-coder``, ``functiongemma``.
+``harmony`` is handled by :mod:`ollama_b200.text.harmony`; the renderers by :mod:`ollama_b200.text.renderers`.
 """
 from __future__ import annotations
 
+import ast
+import io
 import json
+import keyword
 import re
+import tokenize
+from dataclasses import dataclass
 from typing import Any, Callable
 
 
@@ -36,99 +49,49 @@ def _overlap(s: str, tag: str) -> int:
     return 0
 
 
+@dataclass
+class Region:
+    """A stretch of output between two marks that is not prose: one tool call, a list of tool calls, or something to drop.
+
+    ``decode`` turns the body into one call, a list of calls, or None (not a call after all: the stretch is given back as
+    the text it was).  ``close`` None means the body has no closing mark and ends where ``body_end`` says.  With ``item``
+    the calls stand one by one between marks of their own inside the region and are handed out as each one closes.
+    ``drop`` regions are swallowed (a model echoing tool results); ``unwrap`` regions lose their marks only and the body
+    stays in the content, white space around it included."""
+    open: str
+    close: str | None = ""
+    decode: Callable[[str], Any] | None = None
+    body_end: Callable[[str], int] | None = None
+    item: tuple[str, str] | None = None
+    drop: bool = False
+    unwrap: bool = False
+
+
 class TagStreamParser:
     """Splits a streamed completion into content, reasoning and tool calls.
 
     ``add(text, done)`` returns ``(content, thinking, calls)`` for what became unambiguous with this chunk: text that
-    could still turn out to be the beginning of a tag (and the white space in front of it) is held back until the
+    could still turn out to be the beginning of a mark (and the white space in front of it) is held back until the
     next chunk decides, and everything held is released when ``done`` is true.
     """
 
-    def __init__(self, *, think_open: str = "", think_close: str = "", start_thinking: bool = False, tool_open: str = "",
-                 tool_close: str | None = "", decode_call: Callable[[str], dict[str, Any] | None] | None = None,
-                 body_end: Callable[[str], int] | None = None):
+    def __init__(self, *, think_open: str = "", think_close: str = "", start_thinking: bool = False, regions: list[Region] | None = None,
+                 call_ends_thinking: bool = False, keep_space: bool = False):
         self.think_open, self.think_close = think_open, think_close
-        self.tool_open, self.tool_close = tool_open, tool_close
-        self.decode_call, self.body_end = decode_call, body_end
-        self.state = "thinking" if start_thinking and think_close else "content"
-        self.may_open_think = bool(think_open)        # an explicit opening tag is accepted at the very start only
-        self.skip_ws = False                          # white space right after a closed block belongs to the markup
+        self.regions = [r for r in regions or [] if r.decode is not None or r.drop or r.unwrap]
+        self.call_ends_thinking = call_ends_thinking    # a call that opens inside the reasoning block ends the block
+        self.keep_space = keep_space                    # reasoning is handed on with the white space it ends in
+        self.state: Any = "thinking" if start_thinking and think_close else "content"
+        self.may_open_think = bool(think_open)          # an explicit opening tag is accepted at the very start only
+        self.skip_ws = False                            # white space right after a closed block belongs to the markup
         self.buf = ""
 
-    def add(self, text: str, done: bool = False) -> tuple[str, str, list[dict[str, Any]]]:
-        self.buf += text
-        content, thinking, calls = [], [], []
-        while True:
-            if self.state == "thinking":
-                if self.may_open_think:             # some checkpoints repeat the opening tag although the prompt ended with it
-                    t = self.buf.lstrip()
-                    if t.startswith(self.think_open):
-                        self.buf = t[len(self.think_open):]
-                        self.may_open_think = False
-                        continue
-                    if t and not self.think_open.startswith(t):
-                        self.may_open_think = False
-                    elif not done:
-                        break
-                i = self.buf.find(self.think_close)
-                if i >= 0:
-                    thinking.append(self.buf[:i].rstrip())
-                    self.buf = self.buf[i + len(self.think_close):]
-                    self.state, self.skip_ws = "content", True
-                    continue
-                keep = 0 if done else self._held(self.buf, [self.think_close])
-                thinking.append(self.buf[:len(self.buf) - keep])
-                self.buf = self.buf[len(self.buf) - keep:]
-                break
-            if self.state == "content":
-                if self.skip_ws:
-                    self.buf = self.buf.lstrip()
-                    if not self.buf:
-                        break
-                    self.skip_ws = False
-                tags = [t for t in (self.tool_open if self.decode_call else "", self.think_open if self.may_open_think else "") if t]
-                hit = min(((self.buf.find(t), t) for t in tags if t in self.buf), default=None)
-                if hit is not None:
-                    i, tag = hit
-                    before = self.buf[:i]
-                    if tag == self.think_open and before.strip():      # a reasoning block only opens the message
-                        self.may_open_think = False
-                        continue
-                    content.append(before.rstrip() if tag == self.tool_open else "")
-                    self.buf = self.buf[i + len(tag):]
-                    self.state = "tool" if tag == self.tool_open else "thinking"
-                    self.may_open_think = False
-                    continue
-                keep = 0 if done else self._held(self.buf, tags)
-                out = self.buf[:len(self.buf) - keep]
-                if out.strip():
-                    self.may_open_think = False
-                content.append(out)
-                self.buf = self.buf[len(self.buf) - keep:]
-                break
-            # state == "tool": wait for the whole body
-            end = -1
-            if self.tool_close:
-                i = self.buf.find(self.tool_close)
-                if i >= 0:
-                    body, end = self.buf[:i], i + len(self.tool_close)
-            elif self.body_end is not None:
-                n = self.body_end(self.buf)
-                if n >= 0:
-                    body, end = self.buf[:n], n
-            if end < 0:
-                if done:                             # an unterminated call is returned as text, the way it was produced
-                    content.append(self.tool_open + self.buf)
-                    self.buf = ""
-                break
-            call = self.decode_call(body) if self.decode_call else None
-            if call is not None:
-                calls.append(call)
-            else:
-                content.append(self.tool_open + self.buf[:end])
-            self.buf = self.buf[end:]
-            self.state, self.skip_ws = "content", True
-        return "".join(content), "".join(thinking), calls
+    # -- helpers ------------------------------------------------------------------------------------
+    def _first(self, marks: list[str]) -> tuple[int, str] | None:
+        return min(((self.buf.find(m), m) for m in marks if m and m in self.buf), default=None)
+
+    def _region(self, mark: str) -> Region | None:
+        return next((r for r in self.regions if r.open == mark), None)
 
     @staticmethod
     def _held(s: str, tags: list[str]) -> int:
@@ -137,6 +100,128 @@ class TagStreamParser:
         head = s[:len(s) - n]
         ws = len(head) - len(head.rstrip())
         return n + ws if (n or ws) and tags else 0
+
+    def _flush(self, sink: list[str], marks: list[str], done: bool) -> None:
+        keep = 0 if done else self._held(self.buf, marks)
+        sink.append(self.buf[:len(self.buf) - keep])
+        self.buf = self.buf[len(self.buf) - keep:]
+
+    @staticmethod
+    def _calls(decoded: Any) -> list[dict[str, Any]]:
+        return decoded if isinstance(decoded, list) else [decoded]
+
+    # -- the machine --------------------------------------------------------------------------------
+    def add(self, text: str, done: bool = False) -> tuple[str, str, list[dict[str, Any]]]:
+        self.buf += text
+        content: list[str] = []
+        thinking: list[str] = []
+        calls: list[dict[str, Any]] = []
+        while True:
+            step = self._in_thinking if self.state == "thinking" else self._in_content if self.state == "content" else self._in_region
+            if not step(content, thinking, calls, done):
+                break
+        return "".join(content), "".join(thinking), calls
+
+    def _in_thinking(self, content, thinking, calls, done) -> bool:
+        if self.may_open_think:                         # some checkpoints repeat the opening tag although the prompt ended with it
+            t = self.buf.lstrip()
+            if t.startswith(self.think_open):
+                self.buf, self.may_open_think = t[len(self.think_open):], False
+                return True
+            if t and not self.think_open.startswith(t):
+                self.may_open_think = False
+            elif not done:
+                return False
+        marks = [self.think_close] + ([r.open for r in self.regions] if self.call_ends_thinking else [])
+        hit = self._first(marks)
+        if hit is None:
+            self._flush(thinking, marks, done)
+            return False
+        i, mark = hit
+        thinking.append(self.buf[:i] if self.keep_space and mark == self.think_close else self.buf[:i].rstrip())
+        self.buf = self.buf[i + len(mark):]
+        if mark == self.think_close:
+            self.state, self.skip_ws = "content", True
+        else:
+            self.state = self._region(mark)
+        return True
+
+    def _in_content(self, content, thinking, calls, done) -> bool:
+        if self.skip_ws:
+            self.buf = self.buf.lstrip()
+            if not self.buf:
+                return False
+            self.skip_ws = False
+        marks = [r.open for r in self.regions] + ([self.think_open] if self.may_open_think else [])
+        hit = self._first(marks)
+        if hit is None:
+            before = len(content)
+            self._flush(content, marks, done)
+            if "".join(content[before:]).strip():
+                self.may_open_think = False
+            return False
+        i, mark = hit
+        before = self.buf[:i]
+        if mark == self.think_open and self.may_open_think and self._region(mark) is None:
+            if before.strip():                          # a reasoning block only opens the message
+                self.may_open_think = False
+                return True
+            self.buf, self.state, self.may_open_think = self.buf[i + len(mark):], "thinking", False
+            return True
+        region = self._region(mark)
+        content.append(before if region.unwrap else before.rstrip())
+        self.buf, self.state, self.may_open_think = self.buf[i + len(mark):], region, False
+        return True
+
+    def _in_region(self, content, thinking, calls, done) -> bool:
+        r: Region = self.state
+        if r.item is not None:
+            return self._in_item_region(r, content, calls, done)
+        end = -1
+        if r.close:
+            i = self.buf.find(r.close)
+            if i >= 0:
+                body, end = self.buf[:i], i + len(r.close)
+        elif r.body_end is not None:
+            n = r.body_end(self.buf)
+            if n >= 0:
+                body, end = self.buf[:n], n
+        if end < 0:
+            if done:                                    # an unterminated call is returned as text, the way it was produced
+                if not r.drop:
+                    content.append(("" if r.unwrap else r.open) + self.buf)
+                self.buf = ""
+            return False
+        if r.unwrap:
+            content.append(body)
+        elif not r.drop:
+            decoded = r.decode(body)
+            if decoded is not None:
+                calls.extend(self._calls(decoded))
+            else:
+                content.append(r.open + self.buf[:end])
+        self.buf = self.buf[end:]
+        self.state, self.skip_ws = "content", not r.unwrap
+        return True
+
+    def _in_item_region(self, r: Region, content, calls, done) -> bool:
+        opener, closer = r.item
+        i_end, i_item = self.buf.find(r.close), self.buf.find(closer)
+        if i_item >= 0 and (i_end < 0 or i_item < i_end):
+            start = self.buf.find(opener)
+            body = self.buf[start + len(opener):i_item] if 0 <= start < i_item else self.buf[:i_item]
+            decoded = r.decode(body)
+            if decoded is not None:
+                calls.extend(self._calls(decoded))
+            self.buf = self.buf[i_item + len(closer):]
+            return True
+        if i_end >= 0:
+            self.buf = self.buf[i_end + len(r.close):]
+            self.state, self.skip_ws = "content", True
+            return True
+        if done:
+            self.buf = ""
+        return False
 
 
 # ---------------------------------------------------------------------------------------------------
@@ -200,13 +285,16 @@ def typed_value(raw: str, types: list[str]) -> Any:
 
 
 def _schema_types(tools: list[dict[str, Any]] | None, fn: str, param: str) -> list[str]:
+    """Declared JSON-schema type(s) of one parameter; the members of an ``anyOf`` count together."""
+    def names(p: dict[str, Any]) -> list[str]:
+        ty = p.get("type", [])
+        return [ty] if isinstance(ty, str) else [x for x in ty if isinstance(x, str)]
     for t in tools or []:
         f = t.get("function", {})
         if f.get("name") == fn:
-            p = (f.get("parameters") or {}).get("properties", {}).get(param)
+            p = ((f.get("parameters") or {}).get("properties") or {}).get(param)
             if isinstance(p, dict):
-                ty = p.get("type", [])
-                return [ty] if isinstance(ty, str) else [x for x in ty if isinstance(x, str)]
+                return [n for alt in p["anyOf"] if isinstance(alt, dict) for n in names(alt)] if p.get("anyOf") else names(p)
     return []
 
 
@@ -335,7 +423,114 @@ def _functiongemma_call(body: str) -> dict[str, Any] | None:
     return {"function": {"name": m.group(1), "arguments": _fg_object(m.group(2))}}
 
 
-PARSERS = ("qwen3", "qwen3-thinking", "qwen3-coder", "ministral", "functiongemma", "passthrough")
+# -- DeepSeek marks: name and JSON arguments on either side of a separator mark -----------------------------------
+_DS_SEP = "<｜tool▁sep｜>"
+
+
+def _deepseek_call(body: str) -> dict[str, Any] | None:
+    """``name<sep>{json}``"""
+    name, sep, args = body.partition(_DS_SEP)
+    try:
+        obj = json.loads(args)
+    except ValueError:
+        return None
+    return {"function": {"name": name.strip(), "arguments": obj}} if sep and isinstance(obj, dict) else None
+
+
+def _cogito_call(body: str) -> dict[str, Any] | None:
+    """``function<sep>name`` followed by the arguments in a fenced ``json`` block"""
+    m = re.search(re.escape(_DS_SEP) + r"(.*?)\n```json\n(.*?)\n```", body, re.S)
+    if m is None:
+        return None
+    try:
+        obj = json.loads(m.group(2))
+    except ValueError:
+        return None
+    return {"function": {"name": m.group(1).strip(), "arguments": obj}} if isinstance(obj, dict) else None
+
+
+# -- Python-style calls: name(key="value", n=1), one per line ------------------------------------------------------
+_KW = "kw__"
+_WORDS = {"true": True, "True": True, "false": False, "False": False, "null": None, "None": None, "nil": None}
+
+
+def _py_value(node: ast.AST, src: str) -> Any:
+    """Value of an argument expression: literals, lists and maps as written; the JSON and Python spellings of
+    true / false / null; anything else (a bare word, an expression) is the text itself."""
+    if isinstance(node, ast.Constant) and not isinstance(node.value, (bytes, complex)) and node.value is not Ellipsis:
+        return node.value
+    if isinstance(node, ast.Name) and node.id in _WORDS:
+        return _WORDS[node.id]
+    if isinstance(node, ast.UnaryOp) and isinstance(node.op, (ast.USub, ast.UAdd)) and isinstance(node.operand, ast.Constant) \
+            and isinstance(node.operand.value, (int, float)) and not isinstance(node.operand.value, bool):
+        return -node.operand.value if isinstance(node.op, ast.USub) else node.operand.value
+    if isinstance(node, (ast.List, ast.Tuple)):
+        return [_py_value(e, src) for e in node.elts]
+    if isinstance(node, ast.Dict) and all(k is not None for k in node.keys):
+        return {str(_py_value(k, src)): _py_value(v, src) for k, v in zip(node.keys, node.values)}
+    return ast.get_source_segment(src, node) or ""
+
+
+def _free_keywords(line: str) -> str:
+    """Argument names that are Python keywords (``from=``, ``class=``) get a prefix, so that the line parses as Python."""
+    try:
+        toks = list(tokenize.generate_tokens(io.StringIO(line).readline))
+    except (tokenize.TokenError, IndentationError, SyntaxError):
+        return line
+    for i in range(len(toks) - 2, -1, -1):
+        t = toks[i]
+        if t.type == tokenize.NAME and keyword.iskeyword(t.string) and t.string not in _WORDS and toks[i + 1].string == "=" and t.start[0] == 1:
+            line = line[:t.start[1]] + _KW + line[t.start[1]:]
+    return line
+
+
+def _pythonic_calls(body: str) -> list[dict[str, Any]] | None:
+    calls = []
+    for line in filter(None, map(str.strip, body.splitlines())):
+        line = _free_keywords(line)
+        try:
+            tree = ast.parse(line, mode="eval").body
+        except (SyntaxError, ValueError):
+            return None
+        if not isinstance(tree, ast.Call) or not isinstance(tree.func, ast.Name) or tree.args or any(k.arg is None for k in tree.keywords):
+            return None
+        calls.append({"function": {"name": tree.func.id, "arguments": {k.arg.removeprefix(_KW): _py_value(k.value, line) for k in tree.keywords}}})
+    return calls
+
+
+# -- GLM: name, then <arg_key>/<arg_value> pairs; values typed by the tool's schema --------------------------------
+_GLM_MARKS = re.compile(r"(</?arg_(?:key|value)>)")
+
+
+def _glm_call(tools: list[dict[str, Any]] | None) -> Callable[[str], dict[str, Any] | None]:
+    def decode(body: str) -> dict[str, Any] | None:
+        head, *rest = _GLM_MARKS.split(body)
+        name = head.strip()
+        cols: dict[str, list[str]] = {"key": [], "value": []}
+        into: list[str] | None = None
+        loose = ""                                      # text outside any pair: a key or value whose opening mark the model left out
+        for tok in rest:
+            if _GLM_MARKS.fullmatch(tok) is None:
+                if into is not None:
+                    into[-1] += tok
+                else:
+                    loose = tok
+            elif tok.startswith("</"):
+                if into is None and loose.strip():
+                    cols["key" if "key" in tok else "value"].append(loose.strip("\n"))
+                into, loose = None, ""
+            else:
+                into, loose = cols["key" if "key" in tok else "value"], ""
+                into.append("")
+        if not name or len(cols["key"]) != len(cols["value"]):
+            return None
+        args = {k.strip(): typed_value(v, _schema_types(tools, name, k.strip())) for k, v in zip(cols["key"], cols["value"])}
+        return {"function": {"name": name, "arguments": args}}
+    return decode
+
+
+PARSERS = ("qwen3", "qwen3-thinking", "qwen3-coder", "qwen3-vl-instruct", "qwen3-vl-thinking", "ministral", "functiongemma", "cogito", "deepseek3",
+           "olmo3", "olmo3-think", "glm-4.6", "glm-4.7", "passthrough")
 
 
 def parser_for(name: str | None, tools: list[dict[str, Any]] | None = None, think: Any = None,
@@ -345,226 +540,53 @@ def parser_for(name: str | None, tools: list[dict[str, Any]] | None = None, thin
     ``think`` is the request's think value (None = unset); ``prefill`` the content of a trailing assistant message
     that the model continues (a reasoning model then continues the answer, not the reasoning block).
     """
-    want_tools = bool(tools)
+    asked = think is not None and bool(think)                     # reasoning explicitly requested
+    fresh = not prefill
+    json_call = Region("<tool_call>", "</tool_call>", _json_call)
     if name == "passthrough":
         return TagStreamParser()
     if name in ("qwen3", "qwen3-thinking"):
-        thinking = name == "qwen3-thinking" and think is not False and not prefill
-        return TagStreamParser(think_open="<think>", think_close="</think>", start_thinking=thinking, tool_open="<tool_call>",
-                               tool_close="</tool_call>", decode_call=_json_call if want_tools else None)
+        thinking = name == "qwen3-thinking" and think is not False and fresh
+        return TagStreamParser(think_open="<think>", think_close="</think>", start_thinking=thinking, regions=[json_call] if tools else [])
+    if name in ("qwen3-vl-instruct", "qwen3-vl-thinking"):        # model/parsers/qwen3vl.go:50-64: the variant decides, not the request
+        thinking = name == "qwen3-vl-thinking" and fresh
+        return TagStreamParser(think_close="</think>", start_thinking=thinking, regions=[json_call], call_ends_thinking=True)
     if name == "qwen3-coder":
-        return TagStreamParser(tool_open="<tool_call>", tool_close="</tool_call>", decode_call=_xml_call(tools))
+        return TagStreamParser(regions=[Region("<tool_call>", "</tool_call>", _xml_call(tools))])
     if name == "functiongemma":
-        return TagStreamParser(tool_open="<start_function_call>", tool_close="<end_function_call>", decode_call=_functiongemma_call)
+        return TagStreamParser(regions=[Region("<start_function_call>", "<end_function_call>", _functiongemma_call)])
     if name == "ministral":
-        return TagStreamParser(think_open="[THINK]", think_close="[/THINK]", tool_open="[TOOL_CALLS]", tool_close=None,
-                               decode_call=_ministral_call, body_end=_ministral_end)
+        return TagStreamParser(think_open="[THINK]", think_close="[/THINK]",
+                               regions=[Region("[TOOL_CALLS]", None, _ministral_call, body_end=_ministral_end)])
+    if name in ("cogito", "deepseek3"):
+        # model/parsers/cogito.go:64-87, deepseek3.go:61-78: reasoning only on request; cogito does not reason when tools are offered
+        thinking = asked and fresh and not (name == "cogito" and tools)
+        one = _cogito_call if name == "cogito" else _deepseek_call
+        calls = Region("<｜tool▁calls▁begin｜>", "<｜tool▁calls▁end｜>", one, item=("<｜tool▁call▁begin｜>", "<｜tool▁call▁end｜>"))
+        echo = (Region("<｜tool▁outputs▁begin｜>", "<｜tool▁outputs▁end｜>", drop=True) if name == "cogito"
+                else Region("<｜tool▁output▁begin｜>", "<｜tool▁output▁end｜>", unwrap=True))
+        return TagStreamParser(think_close="</think>", start_thinking=thinking, regions=[calls, echo])
+    if name == "olmo3":
+        return TagStreamParser(regions=[Region("<function_calls>", "</function_calls>", _pythonic_calls)])
+    if name == "olmo3-think":                                     # model/parsers/olmo3_think.go:43-55: the prompt always ends in <think>
+        return TagStreamParser(think_close="</think>", start_thinking=fresh)
+    if name in ("glm-4.6", "glm-4.7"):
+        # model/parsers/glm47.go:13-20: the 4.7 prompt ends inside the block unless reasoning was switched off
+        thinking = name == "glm-4.7" and (think is None or bool(think))
+        return TagStreamParser(think_open="<think>", think_close="</think>", start_thinking=thinking,
+                               regions=[Region("<tool_call>", "</tool_call>", _glm_call(tools))])
     return None
 
 
 # ---------------------------------------------------------------------------------------------------
-# renderers
+# renderers live in :mod:`ollama_b200.text.renderers`; the two oldest keep their function names here
 # ---------------------------------------------------------------------------------------------------
-_QWEN3_CODER_TOOL_HELP = (
-    "\n\nIf you choose to call a function ONLY reply in the following format with NO suffix:\n\n<tool_call>\n<function=example_function_name>\n"
-    "<parameter=example_parameter_1>\nvalue_1\n</parameter>\n<parameter=example_parameter_2>\nThis is the value for the second parameter\n"
-    "that can span\nmultiple lines\n</parameter>\n</function>\n</tool_call>\n\n<IMPORTANT>\nReminder:\n"
-    "- Function calls MUST follow the specified format: an inner <function=...></function> block must be nested within "
-    "<tool_call></tool_call> XML tags\n- Required parameters MUST be specified\n"
-    "- You may provide optional reasoning for your function call in natural language BEFORE the function call, but NOT after\n"
-    "- If there is no function call available, answer the question like normal with your current knowledge and do not tell the user "
-    "about function calls\n</IMPORTANT>")
-
-
-def _xml_extra(obj: dict[str, Any], handled: tuple[str, ...]) -> str:
-    out = []
-    for k, v in obj.items():
-        if k in handled or v is None:
-            continue
-        if isinstance(v, (dict, list)):
-            v = json.dumps(v, separators=(",", ":"), ensure_ascii=False)
-        elif isinstance(v, bool):
-            v = "true" if v else "false"
-        out.append(f"\n<{k}>{v}</{k}>")
-    return "".join(out)
-
-
-def _arg_text(v: Any) -> str:
-    if v is None:
-        return "null"
-    if isinstance(v, str):
-        return v
-    if isinstance(v, bool):
-        return "true" if v else "false"
-    if isinstance(v, (dict, list)):
-        return json.dumps(v, separators=(",", ":"), ensure_ascii=False)
-    return str(v)
+from .renderers import DIALECTS, renderer_for  # noqa: E402,F401
 
 
 def render_qwen3_coder(messages: list[dict[str, Any]], tools: list[dict[str, Any]] | None = None, think: Any = None) -> str:
-    """ChatML with XML tool definitions and XML tool calls (model/renderers/qwen3coder.go:63-198): the first system
-    message wins, consecutive tool results share one user turn, a trailing assistant message is left open."""
-    system = next((m.get("content", "") for m in messages if m.get("role") == "system"), "")
-    rest = [m for m in messages if m.get("role") != "system"]
-    sb: list[str] = []
-    if system or tools:
-        sb.append("<|im_start|>system\n")
-        sb.append(system or "You are Qwen, a helpful AI assistant that can interact with a computer to solve tasks.")
-        if tools:
-            sb.append("\n\n# Tools\n\nYou have access to the following functions:\n\n<tools>")
-            for t in tools:
-                f = t.get("function", {})
-                sb.append(f"\n<function>\n<name>{f.get('name', '')}</name>")
-                if f.get("description"):
-                    sb.append(f"\n<description>{f['description']}</description>")
-                sb.append("\n<parameters>")
-                params = f.get("parameters") or {}
-                for pname, prop in (params.get("properties") or {}).items():
-                    sb.append(f"\n<parameter>\n<name>{pname}</name>")
-                    ty = prop.get("type")
-                    if ty:
-                        sb.append(f"\n<type>{ty if isinstance(ty, str) else (ty[0] if len(ty) == 1 else json.dumps(ty, separators=(',', ':')))}</type>")
-                    if prop.get("description"):
-                        sb.append(f"\n<description>{prop['description']}</description>")
-                    sb.append(_xml_extra(prop, ("type", "description")))
-                    sb.append("\n</parameter>")
-                sb.append(_xml_extra(params, ("type", "properties")))
-                sb.append("\n</parameters>\n</function>")
-            sb.append("\n</tools>")
-            sb.append(_QWEN3_CODER_TOOL_HELP)
-        sb.append("<|im_end|>\n")
-    for i, m in enumerate(rest):
-        last = i == len(rest) - 1
-        role, content = m.get("role", "user"), m.get("content", "") or ""
-        prefill = last and role == "assistant"
-        if role == "assistant":
-            sb.append("<|im_start|>assistant\n")
-            if m.get("tool_calls"):
-                if content:
-                    sb.append(content + "\n")
-                for c in m["tool_calls"]:
-                    f = c.get("function", {})
-                    sb.append(f"\n<tool_call>\n<function={f.get('name', '')}>")
-                    for k, v in (f.get("arguments") or {}).items():
-                        sb.append(f"\n<parameter={k}>\n{_arg_text(v)}\n</parameter>")
-                    sb.append("\n</function>\n</tool_call>")
-                sb.append("<|im_end|>\n")
-                prefill = False
-            else:
-                sb.append(content)
-                if not prefill:
-                    sb.append("<|im_end|>\n")
-        elif role == "tool":
-            if i == 0 or rest[i - 1].get("role") != "tool":
-                sb.append("<|im_start|>user")
-            sb.append(f"\n<tool_response>\n{content}\n</tool_response>")
-            if last or rest[i + 1].get("role") != "tool":
-                sb.append("<|im_end|>\n")
-        else:
-            sb.append(f"<|im_start|>{role}\n{content}<|im_end|>\n")
-        if last and not prefill:
-            sb.append("<|im_start|>assistant\n")
-    return "".join(sb)
-
-
-def _fg_arg(v: Any) -> str:
-    if isinstance(v, str):
-        return _ESC + v + _ESC
-    if isinstance(v, bool):
-        return "true" if v else "false"
-    if isinstance(v, float) and v == int(v):
-        return str(int(v))
-    if isinstance(v, dict):
-        return "{" + ",".join(f"{k}:{_fg_arg(v[k])}" for k in sorted(v)) + "}"
-    if isinstance(v, list):
-        return "[" + ",".join(_fg_arg(x) for x in v) + "]"
-    return str(v)
+    return renderer_for("qwen3-coder").render(messages, tools, think)
 
 
 def render_functiongemma(messages: list[dict[str, Any]], tools: list[dict[str, Any]] | None = None, think: Any = None) -> str:
-    """Gemma turns with function declarations in a developer turn, calls as ``call:name{k:v}`` and tool results as
-    ``response:name{...}`` inside the model turn (model/renderers/functiongemma.go:20-125): strings travel between
-    ``<escape>`` marks, keys are sorted, types are upper-cased."""
-    default = "You can do function calling with the following functions:"
-    sb = ["<bos>"]
-    system, loop = "", list(messages)
-    if loop and loop[0].get("role") in ("system", "developer"):
-        system, loop = loop[0].get("content", "") or "", loop[1:]
-    if system or tools:
-        sb.append("<start_of_turn>developer\n")
-        if system:
-            sb.append(system.strip())
-        if tools:
-            if system:
-                sb.append("\n")
-            if system.strip() != default:
-                sb.append(default)
-        for t in tools or []:
-            f = t.get("function", {})
-            sb.append(f"<start_function_declaration>declaration:{f.get('name', '')}{{description:{_ESC}{f.get('description', '')}{_ESC}")
-            params = f.get("parameters") or {}
-            props, ptype = params.get("properties") or {}, params.get("type") or ""
-            if props or ptype or "properties" in params:
-                sb.append(",parameters:{")
-                items = []
-                if props:
-                    inner = []
-                    for name in sorted(props):
-                        pr = props[name] or {}
-                        ty = pr.get("type")
-                        ty = ty if isinstance(ty, str) else (ty[0] if ty else "")
-                        inner.append(f"{name}:{{description:{_ESC}{pr.get('description', '')}{_ESC}" + (f",type:{_ESC}{ty.upper()}{_ESC}" if ty else "") + "}")
-                    items.append("properties:{" + ",".join(inner) + "}")
-                if params.get("required"):
-                    items.append("required:[" + ",".join(_ESC + r + _ESC for r in params["required"]) + "]")
-                if ptype:
-                    items.append(f"type:{_ESC}{str(ptype).upper()}{_ESC}")
-                sb.append(",".join(items) + "}")
-            sb.append("}<end_function_declaration>")
-        sb.append("<end_of_turn>\n")
-    prev = ""
-    for i, m in enumerate(loop):
-        role, content = m.get("role", "user"), m.get("content", "") or ""
-        if role == "assistant":
-            if prev != "tool_response":
-                sb.append("<start_of_turn>model\n")
-            prev = ""
-            if content:
-                sb.append(content.strip())
-            calls = m.get("tool_calls") or []
-            for c in calls:
-                f = c.get("function", {})
-                args = f.get("arguments") or {}
-                sb.append("<start_function_call>call:" + f.get("name", "") + "{" + ",".join(f"{k}:{_fg_arg(args[k])}" for k in sorted(args)) + "}<end_function_call>")
-            if calls and i + 1 < len(loop) and loop[i + 1].get("role") == "tool":
-                sb.append("<start_function_response>")
-                prev = "tool_call"
-            else:
-                sb.append("<end_of_turn>\n")
-        elif role == "tool":
-            name = ""
-            for j in range(i - 1, -1, -1):          # the call this result answers: n-th result after the last assistant turn with calls
-                if loop[j].get("role") == "assistant" and loop[j].get("tool_calls"):
-                    n = sum(1 for k in range(j + 1, i) if loop[k].get("role") == "tool")
-                    if n < len(loop[j]["tool_calls"]):
-                        name = loop[j]["tool_calls"][n].get("function", {}).get("name", "")
-                    break
-            if prev != "tool_call":
-                sb.append("<start_function_response>")
-            sb.append("response:" + name + "{" + _fg_arg(content) + "}<end_function_response>")
-            prev = "tool_response"
-        else:
-            if role != "user" or prev != "tool_response":
-                sb.append(f"<start_of_turn>{role}\n")
-            prev = ""
-            sb.append(content.strip() + "<end_of_turn>\n")
-    if prev != "tool_response":
-        sb.append("<start_of_turn>model\n")
-    return "".join(sb)
-
-
-RENDERERS: dict[str, Callable[..., str]] = {"qwen3-coder": render_qwen3_coder, "functiongemma": render_functiongemma}
-
-
-def renderer_for(name: str | None) -> Callable[..., str] | None:
-    return RENDERERS.get(name or "")
+    return renderer_for("functiongemma").render(messages, tools, think)

