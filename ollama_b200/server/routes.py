@@ -164,7 +164,8 @@ class Server:
         except ValueError as e:
             raise APIError(400, str(e)) from None
         try:
-            ref = self.sched.get_runner(model, opts, ka)
+            batch_auto = "num_batch" not in (model.options or {}) and "num_batch" not in (req_opts or {})
+            ref = self.sched.get_runner(model, opts, ka, batch_auto=batch_auto)
         except SchedulerError as e:
             raise APIError(e.status, str(e)) from None
         return ref, opts
@@ -190,6 +191,9 @@ class Server:
         def guarded() -> Iterator[dict[str, Any]]:
             try:
                 yield from gen()
+            except RunnerError as e:
+                sched.expire_for_runtime_oom(e)       # a device that ran out of memory is emptied before the next request
+                raise
             finally:
                 if ref is not None:
                     sched.release(ref)

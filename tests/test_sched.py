@@ -7,7 +7,7 @@ import time
 import pytest
 
 from ollama_b200.discover.devices import DeviceInfo
-from ollama_b200.server.sched import ERR_MAX_QUEUE, Scheduler, SchedulerError, default_context, predict_memory
+from ollama_b200.server.sched import ERR_MAX_QUEUE, Scheduler, SchedulerError, auto_num_batch, default_context, is_out_of_memory, predict_memory
 
 GiB = 1 << 30
 
@@ -60,7 +60,8 @@ def make(n_gpus=1, free=80 * GiB, **kw):
         created.append(r)
         return r
 
-    s = Scheduler(new_runner_fn=kw.get("factory", factory), get_gpus_fn=lambda: gpus(n_gpus, free))
+    s = Scheduler(new_runner_fn=kw.get("factory", factory), get_gpus_fn=kw.get("get_gpus", lambda: gpus(n_gpus, free)),
+                  wait_for_recovery=kw.get("wait_for_recovery", 0.0))
     return s, created
 
 
@@ -210,3 +211,125 @@ def test_load_failure_and_oom_retry():
     with pytest.raises(SchedulerError) as e:
         s2.get_runner(FakeModel("a"), dict(OPTS), 60)
     assert e.value.status == 500 and "bad file" in str(e.value)
+
+
+def test_prompt_batch_nobody_chose_follows_context_and_memory():
+    """server/sched_test.go (automatic generation batch): 512 up to 4k of total context, 1024 up to 32k, 2048 above, stepping
+    down when the model leaves too little of the device; two automatic sizes never force a reload, an explicit one does."""
+    assert auto_num_batch(4096, 10 * GiB, 80 * GiB) == 512 and auto_num_batch(8192, 10 * GiB, 80 * GiB) == 1024
+    assert auto_num_batch(65536, 10 * GiB, 80 * GiB) == 2048
+    assert auto_num_batch(65536, 50 * GiB, 80 * GiB) == 1024            # over 60 % of the device: no room for the largest batch
+    assert auto_num_batch(65536, 62 * GiB, 80 * GiB) == 512             # over 75 %
+    assert auto_num_batch(65536, 63 * GiB + 512 * (1 << 20), 80 * GiB) == 512 and auto_num_batch(65536, 0, 0) == 2048
+    s, created = make()
+    m = FakeModel("a")
+    r = s.get_runner(m, {**OPTS, "num_ctx": 16384}, 60, batch_auto=True)
+    assert created[0].opts["num_batch"] == 1024 and r.batch_auto
+    s.release(r)
+    assert s.get_runner(m, {**OPTS, "num_ctx": 16384, "num_batch": 512}, 60, batch_auto=True) is r      # the default 512 is not a wish
+    s.release(r)
+    r2 = s.get_runner(m, {**OPTS, "num_ctx": 16384, "num_batch": 256}, 60)                               # an explicit size is
+    assert r2 is not r and created[1].opts["num_batch"] == 256 and created[0].closed
+    s.release(r2)
+
+
+def test_eviction_waits_for_the_memory_to_come_back():
+    """server/sched_test.go (VRAM recovery): after an unload the next load polls the devices until about three quarters of the
+    runner's memory shows up as free, and goes on after a bounded wait when it never does."""
+    state = {"free": 22 * GiB, "polls": 0, "closed_at": None}
+
+    def get_gpus():
+        state["polls"] += 1
+        if state["closed_at"] is not None and state["polls"] - state["closed_at"] >= 3:
+            return gpus(1, 70 * GiB)                                    # the driver catches up a few polls after the process is gone
+        return gpus(1, state["free"])
+
+    s, created = make(get_gpus=get_gpus, wait_for_recovery=5.0)
+    a = s.get_runner(FakeModel("a", 20 * GiB), dict(OPTS), 60)
+    s.release(a)
+    orig_close = created[0].close
+
+    def close():
+        orig_close()
+        state["closed_at"] = state["polls"]
+
+    created[0].close = close
+    t0 = time.monotonic()
+    b = s.get_runner(FakeModel("b", 25 * GiB), dict(OPTS), 60)           # 25 GiB do not fit into the 22 that are free: a has to go
+    assert created[0].closed and 0.2 < time.monotonic() - t0 < 4.0 and b.runner is created[1]
+    s.release(b)
+    # memory that never comes back: the wait gives up at its limit
+    s2, c2 = make(free=30 * GiB, wait_for_recovery=0.3)
+    x = s2.get_runner(FakeModel("x", 20 * GiB), dict(OPTS), 60)
+    s2.release(x)
+    t0 = time.monotonic()
+    y = s2.get_runner(FakeModel("y", 40 * GiB), dict(OPTS), 60)          # the load goes ahead on the estimate after the bounded wait
+    assert c2[0].closed and 0.25 < time.monotonic() - t0 < 3.0 and y.runner is c2[1]
+
+
+def test_running_out_of_memory_at_run_time_expires_every_runner():
+    """server/sched_test.go (runtime OOM): idle runners go at once, busy ones when their request ends; other errors change nothing."""
+    s, created = make(n_gpus=2)
+    a = s.get_runner(FakeModel("a"), dict(OPTS), 600)
+    b = s.get_runner(FakeModel("b"), dict(OPTS), 600)
+    s.release(a)
+    assert not s.expire_for_runtime_oom(RuntimeError("tokenizer mismatch")) and len(s.loaded) == 2
+    assert is_out_of_memory("CUDA out of memory. Tried to allocate 2 GiB") and is_out_of_memory(MemoryError()) and not is_out_of_memory("timeout")
+    assert s.expire_for_runtime_oom(RuntimeError("CUDA out of memory. Tried to allocate 2 GiB"))
+    assert created[0].closed and not created[1].closed and list(s.loaded) == ["/blobs/b"]
+    s.release(b)
+    assert created[1].closed and not s.loaded
+
+
+def test_a_slow_runner_does_not_hold_the_table_lock():
+    """A liveness probe or a shutdown that takes long runs with the lock released: requests for other models go through meanwhile."""
+    s, created = make(n_gpus=2)
+    a = s.get_runner(FakeModel("a"), dict(OPTS), 60)
+    s.release(a)
+    gate, entered = threading.Event(), threading.Event()
+
+    def slow_ping():
+        entered.set()
+        gate.wait(5)
+        return True
+
+    created[0].ping = slow_ping
+    got = []
+    t = threading.Thread(target=lambda: got.append(s.get_runner(FakeModel("a"), dict(OPTS), 60)))
+    t.start()
+    assert entered.wait(2)
+    t0 = time.monotonic()
+    b = s.get_runner(FakeModel("b"), dict(OPTS), 60)                     # loads while a's probe is still out
+    assert s.ps() and time.monotonic() - t0 < 1.0 and b.runner is created[1]
+    gate.set()
+    t.join(5)
+    assert got and got[0] is a and a.ref_count == 1
+    s.release(a); s.release(b)
+    # the same for close(): a zero keep-alive unload that blocks does not stop ps() or other requests
+    gate.clear(); entered.clear()
+
+    def slow_close():
+        entered.set()
+        gate.wait(5)
+
+    created[1].close = slow_close
+    b2 = s.get_runner(FakeModel("b"), dict(OPTS), 0)
+    t = threading.Thread(target=lambda: s.release(b2))
+    t.start()
+    assert entered.wait(2)
+    t0 = time.monotonic()
+    assert [r.model_key for r in s.ps()] == ["/blobs/a"] and time.monotonic() - t0 < 0.5
+    gate.set()
+    t.join(5)
+
+
+def test_predicted_memory_counts_the_prefill_copy_when_it_would_be_made():
+    m = FakeModel("a", 4 * GiB)
+    base = predict_memory(m, 2048, 1)
+    kv = dict(m.kv(), **{"llama.feed_forward_length": 1024, "llama.vocab_size": 32000})
+    m.kv = lambda: kv
+    copy = 2 * (2 * (256 * (2 * 4 * 64 + 2 * 2 * 64) + 3 * 256 * 1024) + 32000 * 256)
+    assert predict_memory(m, 2048, 1, free=80 * GiB) == base + copy
+    assert predict_memory(m, 2048, 1, free=2 * copy) == base             # would take more than 40 % of the free memory: not made
+    kv["llama.expert_count"] = 8
+    assert predict_memory(m, 2048, 1, free=80 * GiB) == base + copy - 2 * 2 * 3 * 256 * 1024   # expert matrices are not part of the dense copy
