@@ -32,7 +32,7 @@ from ..engine.runner import CompletionRequest, RunnerError
 from ..engine.sampler import SamplingParams
 from ..store import manifest as M
 from ..store.create import CreateError, create_model
-from ..store.model import CAP_COMPLETION, CAP_EMBEDDING, CAP_INSERT, CAP_THINKING, CAP_TOOLS, CapabilityError, Model, ModelNotFound, get_model
+from ..store.model import CAP_COMPLETION, CAP_EMBEDDING, CAP_INSERT, CAP_THINKING, CAP_TOOLS, CAP_VISION, CapabilityError, Model, ModelNotFound, get_model
 from ..store.names import parse_name
 from ..text import harmony
 from ..text.builtin import parser_for
@@ -170,6 +170,19 @@ class Server:
             raise APIError(e.status, str(e)) from None
         return ref, opts
 
+    @staticmethod
+    def _refuse_images(model: Model, has_images: bool):
+        """Image input: a model without a vision tower cannot take it (server/routes.go: images add the vision capability to the
+        request), and this engine runs the text path of vision checkpoints only.  Either way the request is refused, never
+        answered as if the images were not there."""
+        if not has_images:
+            return None
+        try:
+            model.check_capabilities(CAP_VISION)
+        except CapabilityError as e:
+            return _err(400, str(e))
+        return _err(400, f"{model.short_name or model.name}: image input is not available: this engine runs the text path of vision models only")
+
     def _renderer(self, model: Model, runner: Any) -> PromptRenderer:
         key = model.digest or model.name
         r = self.renderers.get(key)
@@ -262,6 +275,9 @@ class Server:
             caps.append(CAP_THINKING)
         if req.get("raw") and (req.get("template") or req.get("system") or req.get("context")):
             return _err(400, "raw mode does not support template, system, or context")
+        refusal = self._refuse_images(model, bool(req.get("images")))
+        if refusal is not None:
+            return refusal
         ref, opts = self._schedule(model, tuple(caps), req.get("options"), req.get("keep_alive"))
         runner = ref.runner
         t_loaded = time.time()
@@ -403,6 +419,9 @@ class Server:
             caps.append(CAP_TOOLS)
         if think is not None and think_enabled(think):
             caps.append(CAP_THINKING)
+        refusal = self._refuse_images(model, any(m.get("images") for m in messages if isinstance(m, dict)))
+        if refusal is not None:
+            return refusal
         ref, opts = self._schedule(model, tuple(caps), req.get("options"), req.get("keep_alive"))
         runner = ref.runner
         t_loaded = time.time()

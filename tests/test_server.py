@@ -359,3 +359,17 @@ def test_malformed_request_fields_are_client_errors(client):
     assert 400 in seen and 200 in seen
     assert client.post("/api/chat", json={"model": "tiny", "messages": "hi"}).json()["error"] == "invalid request: 'messages' must be an array of objects"
     assert client.post("/v1/chat/completions", json={"model": "tiny", "messages": [{"role": "user", "content": "x"}], "temperature": "hot"}).status_code == 400
+
+
+def test_image_input_is_refused_not_dropped(client):
+    """server/routes.go (images add the vision capability to a request): a text model answers 400; so does this engine for any
+    model, since it has no vision tower - the images are never silently left out of the prompt."""
+    r = client.post("/api/chat", json={"model": "tiny", "messages": [{"role": "user", "content": "what is this?", "images": ["aGk="]}], "stream": False})
+    assert r.status_code == 400 and "does not support vision" in r.json()["error"]
+    r = client.post("/api/generate", json={"model": "tiny", "prompt": "describe", "images": ["aGk="], "stream": False})
+    assert r.status_code == 400 and "does not support vision" in r.json()["error"]
+    r = client.post("/v1/chat/completions", json={"model": "tiny", "messages": [{"role": "user", "content": [
+        {"type": "text", "text": "hi"}, {"type": "image_url", "image_url": {"url": "data:image/png;base64,aGk="}}]}]})
+    assert r.status_code == 400
+    r = client.post("/api/chat", json={"model": "tiny", "messages": [{"role": "user", "content": "<t300>"}], "stream": False})
+    assert r.status_code == 200
