@@ -75,7 +75,8 @@ inline void st16(uint8_t* p, uint16_t v) {
     p[1] = (uint8_t)(v >> 8);
 }
 inline float rne(float x) { return nearbyintf(x); }
-inline float clampf(float x, float lo, float hi) { return x < lo ? lo : (x > hi ? hi : x); }
+// NaN (a block that holds non-finite values) clamps to the lower bound, so that the integer conversions that follow are defined
+inline float clampf(float x, float lo, float hi) { return x >= lo ? (x <= hi ? x : hi) : lo; }
 
 template <class F>
 void parallel_blocks(int64_t n, F f) {

@@ -236,3 +236,13 @@ def test_reader_survives_corrupted_files(tmp_path):
         except GGUFError:
             pass
     assert 0 < opened < 800
+
+
+def test_host_helpers_are_clean_under_sanitizers():
+    """The C++ codecs and the BPE merge loop, built with AddressSanitizer + UndefinedBehaviorSanitizer, on random blocks, on
+    floats that include NaN / infinities / denormals, and on random merge tables (exerciser: ollama_b200/native/selftest.cc)."""
+    import shutil
+    if shutil.which("g++") is None:
+        pytest.skip("no C++ compiler")
+    from ollama_b200.native.sanitize import run
+    assert run() == 0
