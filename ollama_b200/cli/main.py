@@ -224,6 +224,7 @@ class Repl:
     """Interactive chat session of ``run`` (cmd/interactive.go in the reference)."""
 
     HELP = ("Available Commands:\n  /set            Set session variables\n  /show           Show model information\n"
+            "  /load <model>   Load a session or model\n  /save <model>   Save your current session\n"
             "  /clear          Clear session context\n  /bye            Exit\n  /?, /help       Help for a command\n\n"
             'Use """ to begin a multi-line message.\n')
 
@@ -275,6 +276,34 @@ class Repl:
         elif parts[0] == "/clear":
             self.messages.clear()
             print("Cleared session context")
+        elif parts[0] == "/load":
+            if len(parts) != 2:
+                print("Usage:\n  /load <modelname>")
+                return True
+            try:                                    # a new model starts a new conversation (cmd/interactive.go:209-252)
+                self.c.show(parts[1])
+            except Exception as e:
+                print(f"Couldn't find model '{parts[1]}'" if "not found" in str(e) else f"error: {e}")
+                return True
+            print(f"Loading model '{parts[1]}'")
+            self.model, self.messages = parts[1], []
+            for _ in self.c.generate(model=self.model, prompt="", keep_alive=self.keep_alive):
+                pass
+        elif parts[0] == "/save":
+            if len(parts) != 2:
+                print("Usage:\n  /save <modelname>")
+                return True
+            req: dict[str, Any] = {"model": parts[1], "from": self.model, "messages": list(self.messages)}
+            if self.system:
+                req["system"] = self.system
+            if self.opts:
+                req["parameters"] = dict(self.opts)
+            try:                                    # the session becomes a model: system text, parameters and the conversation so far
+                for _ in self.c.create(**req):
+                    pass
+                print(f"Created new model '{parts[1]}'")
+            except Exception as e:
+                print(f"error: The model name '{parts[1]}' is invalid" if "invalid model name" in str(e) else f"error: {e}")
         elif parts[0] == "/show":
             info = self.c.show(self.model)
             what = parts[1] if len(parts) > 1 else "info"
@@ -293,6 +322,10 @@ class Repl:
                 print("Set system message.")
             elif parts[1] in ("verbose", "quiet"):
                 self.verbose = parts[1] == "verbose"
+            elif parts[1] in ("history", "nohistory"):
+                if getattr(self, "editor", None) is not None:
+                    self.editor.set_enabled(parts[1] == "history")
+                print("Enabled history." if parts[1] == "history" else "Disabled history.")
             elif parts[1] in ("think", "nothink"):
                 self.think = parts[1] == "think" if len(parts) < 3 else parts[2]
             elif parts[1] == "format" and len(parts) > 2:
@@ -306,10 +339,12 @@ class Repl:
         return True
 
     def loop(self) -> None:
+        from .lineedit import LineEditor
         buf: list[str] | None = None
+        self.editor = editor = LineEditor()
         while True:
             try:
-                line = input("... " if buf is not None else ">>> ")
+                line = editor.read("... " if buf is not None else ">>> ", record=buf is None)
             except EOFError:
                 print()
                 return

@@ -104,3 +104,38 @@ def test_repl_commands(server, monkeypatch):
     text = out.getvalue()
     assert r.opts == {"num_predict": 3} and r.system == "terse" and r.messages == []
     assert text.count("<t") == 3 and "Unknown command '/bogus'" in text and "Cleared session context" in text
+
+
+def test_repl_load_save_and_history(server, monkeypatch, tmp_path):
+    """cmd/interactive.go:209-278 (/load, /save) and readline/history.go:24-103 (100 entries, rewritten after every line,
+    OLLAMA_NOHISTORY)."""
+    from ollama_b200.api.client import Client
+    from ollama_b200.cli import lineedit
+    from ollama_b200.cli.main import Repl
+    run_cli("create", "tiny", "-f", str(server / "Modelfile"))
+    monkeypatch.setattr(lineedit, "history_path", lambda: str(tmp_path / "hist" / "history"))
+    lines = iter(["/set parameter num_predict 2", "/set system brief", "<t300>", "/save tiny-session", "/load nope", "/load tiny-session", "/save", "/set nohistory",
+                  "secret", "/bye"])
+    monkeypatch.setattr("builtins.input", lambda prompt="": next(lines))
+    out = io.StringIO()
+    r = Repl(Client(), "tiny", {}, "", None, None, False)
+    with redirect_stdout(out):
+        r.loop()
+    text = out.getvalue()
+    assert "Created new model 'tiny-session'" in text and "Couldn't find model 'nope'" in text and "Loading model 'tiny-session'" in text
+    assert "Usage:\n  /save <modelname>" in text and r.model == "tiny-session"
+    info = Client().show("tiny-session")
+    assert info["system"] == "brief" and "num_predict" in info["parameters"] and [m["role"] for m in info["messages"]] == ["user", "assistant"]
+    saved = open(tmp_path / "hist" / "history", encoding="utf-8").read().splitlines()
+    assert saved[:3] == ["/set parameter num_predict 2", "/set system brief", "<t300>"] and "secret" not in saved and "/bye" not in saved
+    # the file keeps the newest entries up to the limit, skips repeats, and is not touched when history is off
+    h = lineedit.History(str(tmp_path / "h2"), limit=3)
+    for x in ("a", "b", "b", "c", "d"):
+        h.add(x)
+    assert h.entries == ["b", "c", "d"] and lineedit.History(str(tmp_path / "h2"), limit=3).entries == ["b", "c", "d"]
+    monkeypatch.setenv("OLLAMA_NOHISTORY", "1")
+    off = lineedit.History(str(tmp_path / "h3"))
+    off.add("x")
+    assert off.entries == [] and not (tmp_path / "h3").exists()
+    assert lineedit.complete("/s", "/s") == ["/set ", "/show ", "/save "] and lineedit.complete("no", "/set no") == ["nohistory ", "nowordwrap ", "noformat ", "nothink "]
+    assert lineedit.complete("te", "/show te") == ["template"] and lineedit.complete("x", "hello x") == []
