@@ -2,8 +2,11 @@
 
 Older published blobs differ from today's key and tensor names; the reference fixes them while
 loading (llama/compat/llama-ollama-compat.cpp:3239-3286 dispatches per architecture; gpt-oss rules
-at :1510-1555, gemma3 at :237-275, llama3 tokenizer metadata at :1334-1355).  Here the same rules are
-a table applied to the opened :class:`GGUFFile` (nothing is written back to disk).  Set
+at :1510-1555, gemma3 at :237-275, llama3 tokenizer metadata at :1334-1355, qwen2.5-vl at :1776-1840, qwen3-vl at
+:1846-1868).  Here the same rules are a table applied to the opened :class:`GGUFFile` (nothing is written back to disk).
+Vision-language checkpoints of the Qwen family are read as their text model: the decoder has the tensor names and key
+names of qwen2 / qwen3 / qwen3moe under another prefix, and its multi-axis rotary embedding gives every axis the same
+position for text tokens, which is the ordinary rotary embedding; the ``v.*`` / ``mm.*`` tensors stay in the file unread.  Set
 ``OLLAMA_LLAMA_CPP_COMPAT=0`` to switch the normaliser off (llama/compat/README.md:64-66).
 """
 from __future__ import annotations
@@ -47,10 +50,22 @@ def _rename_tensors(g: GGUFFile, rules) -> None:
     g.tensors.update(out)
 
 
+# architecture of a vision-language checkpoint -> the text architecture its decoder is
+_TEXT_ARCH = {"qwen25vl": "qwen2", "qwen2vl": "qwen2", "qwen3vl": "qwen3", "qwen3vlmoe": "qwen3moe"}
+
+
 def normalise(g: GGUFFile) -> GGUFFile:
     if os.environ.get("OLLAMA_LLAMA_CPP_COMPAT", "1") == "0":
         return g
     arch = g.kv.get("general.architecture", "")
+    if arch in _TEXT_ARCH:
+        text = _TEXT_ARCH[arch]
+        g.kv["general.source_architecture"] = arch
+        g.kv["general.architecture"] = text
+        _rename_prefix(g, arch + ".", text + ".")
+        for name in [n for n in g.tensors if n.startswith(("v.", "mm."))]:
+            g.tensors.pop(name)                    # the vision tower and projector are not part of the text graph
+        arch = text
     if arch == "gptoss":
         g.kv["general.architecture"] = "gpt-oss"
         _rename_prefix(g, "gptoss.", "gpt-oss.")

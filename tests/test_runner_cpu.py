@@ -264,3 +264,37 @@ def test_concurrent_random_requests_neither_fail_nor_stall(tiny_llama_path):
         assert not errs and done[0] == 15 and not any(t.is_alive() for t in ths) and r.ping()
     finally:
         r.close()
+
+
+def test_vision_language_checkpoint_runs_as_its_text_model(tmp_path):
+    """llama/compat/llama-ollama-compat.cpp:1776-1868: a qwen3vl blob (keys under ``qwen3vl.``, vision tensors embedded) is loaded
+    as qwen3; text-only prompts give the tokens of the plain qwen3 file with the same weights, and the model still reports vision."""
+    import numpy as np
+
+    from ollama_b200.gguf.reader import open_gguf
+    from ollama_b200.gguf.writer import WriteTensor, write_gguf
+    from ollama_b200.models.synth import write_synthetic_gguf
+    plain, vl = str(tmp_path / "q3.gguf"), str(tmp_path / "q3vl.gguf")
+    write_synthetic_gguf(plain, "tiny-qwen3", "F32")
+    g = open_gguf(plain)
+    kv = {}
+    for k, v in g.kv.items():
+        kv["qwen3vl." + k[len("qwen3."):] if k.startswith("qwen3.") else k] = v
+    kv["general.architecture"] = "qwen3vl"
+    kv["qwen3vl.vision.block_count"] = 2
+    kv["qwen3vl.rope.dimension_sections"] = [24, 20, 20, 0]
+    tensors = [WriteTensor(n, tuple(t.shape), t.dtype, np.array(g.tensor_bytes(n))) for n, t in g.tensors.items()]
+    f32 = g.tensors["output_norm.weight"].dtype
+    tensors.append(WriteTensor("v.patch_embd.weight", (4, 4), f32, np.zeros(16, dtype=np.float32).view(np.uint8)))
+    tensors.append(WriteTensor("mm.0.weight", (4, 4), f32, np.zeros(16, dtype=np.float32).view(np.uint8)))
+    write_gguf(vl, kv, tensors)
+    out = []
+    for path in (plain, vl):
+        r = Runner(path, RunnerOptions(num_ctx=64, device="cpu"))
+        try:
+            out.append(_tokens(r, 6, prompt=list(range(300, 316)))[0])
+            if path == vl:
+                assert r.backend.cfg.arch == "qwen3"
+        finally:
+            r.close()
+    assert out[0] == out[1] and len(out[0]) == 6
