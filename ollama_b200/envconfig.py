@@ -275,6 +275,11 @@ def pp_degree() -> int:
     return _uint("B200_PP", 0)
 
 
+def replicas() -> int:
+    """B200_REPLICAS: whole copies of a model on different GPUs, requests spread over them; 0 or 1 = one runner."""
+    return _uint("B200_REPLICAS", 0)
+
+
 def attn_splits() -> int:
     """B200_ATTN_SPLITS: upper bound of the split-K width of decode attention (CTAs per sequence and KV head)."""
     return max(1, _uint("B200_ATTN_SPLITS", 32))
@@ -321,6 +326,7 @@ def as_map() -> dict[str, tuple[object, str]]:
         "CUDA_VISIBLE_DEVICES": (cuda_visible_devices(), "Set which NVIDIA devices are visible"),
         "B200_TP": (tp_degree(), "Tensor-parallel degree (0 = automatic)"),
         "B200_PP": (pp_degree(), "GPUs of a layer pipeline (0 = only as the fallback of B200_TP)"),
+        "B200_REPLICAS": (replicas(), "Data-parallel copies of a model, one per GPU (0 = one runner)"),
         "B200_ATTN_SPLITS": (attn_splits(), "Upper bound of the split-K width of decode attention"),
         "B200_ATTN_SPLIT_LEN": (attn_split_len(), "Positions of allocated context per split of decode attention"),
         "B200_ATTN_MMA": (var("B200_ATTN_MMA") or "auto", "Decode attention kernel: 1 tensor cores, 0 scalar, auto by model shape"),

@@ -407,15 +407,16 @@ class Scheduler:
             opts["num_ctx"] = ctx
             one_gpu = max((g.free_memory for g in gpus), default=0)
             need = predict_memory(model, ctx, num_parallel, free=one_gpu or None)
+            copies = max(1, min(envconfig.replicas(), len(gpus))) if gpus else 1
             if gpus:
-                while need > self.free_memory():
+                while need * copies > self.free_memory():
                     victim = self._find_runner_to_unload()
                     if victim is None:
                         break
                     self._evict(victim)
                 if need > self.free_memory() and attempt + 1 < len(ladder):
                     continue                      # automatic context shrinks 256k -> 32k -> 4k before giving up (sched.go:649-669)
-            use = self._place(gpus, need)
+            use = self._place(gpus, need) if copies == 1 else self._place_copies(gpus, need, copies)
             if batch_auto and "embedding" not in caps:
                 opts["num_batch"] = auto_num_batch(ctx * num_parallel, need, sum(g.free_memory for g in use))
             try:
@@ -439,6 +440,16 @@ class Scheduler:
                 raise SchedulerError(f"failed to load model: {e}", 500) from e
         raise SchedulerError(f"model requires more system memory than is available: {last_err}", 500)
 
+    @classmethod
+    def _place_copies(cls, gpus: list[DeviceInfo], need: int, copies: int) -> list[DeviceInfo]:
+        """GPUs for ``copies`` whole copies of a model: the group one copy needs, that many times over, on distinct devices
+        (most free memory first); fewer copies when the node does not have the devices."""
+        one = cls._place(gpus, need)
+        k = len(one)
+        by_free = sorted(gpus, key=lambda g: -g.free_memory)
+        n = max(1, min(copies, len(by_free) // k))
+        return by_free[:n * k]
+
     @staticmethod
     def _place(gpus: list[DeviceInfo], need: int) -> list[DeviceInfo]:
         """The smallest group of 1, 2, 4, ... GPUs (most free memory first) whose members can each hold their share within
@@ -458,6 +469,18 @@ class Scheduler:
 
 
 def _default_runner(model: Any, opts: dict[str, Any], num_parallel: int, gpus: list[DeviceInfo]):
+    from ..engine.runner import Runner, RunnerOptions
+    want = envconfig.replicas()
+    if want > 1 and len(gpus) >= 2:
+        # data-parallel copies: the placement's GPUs are dealt out in equal groups, one runner per group
+        n = min(want, len(gpus))
+        per = len(gpus) // n
+        from ..engine.replicas import ReplicaSet
+        return ReplicaSet(lambda i: _default_runner_on(model, opts, num_parallel, gpus[i * per:(i + 1) * per]), n)
+    return _default_runner_on(model, opts, num_parallel, gpus)
+
+
+def _default_runner_on(model: Any, opts: dict[str, Any], num_parallel: int, gpus: list[DeviceInfo]):
     from ..engine.runner import Runner, RunnerOptions
     device = envconfig.device()
     if len(gpus) == 1 and device in ("auto", "cuda"):

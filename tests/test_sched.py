@@ -333,3 +333,74 @@ def test_predicted_memory_counts_the_prefill_copy_when_it_would_be_made():
     assert predict_memory(m, 2048, 1, free=2 * copy) == base             # would take more than 40 % of the free memory: not made
     kv["llama.expert_count"] = 8
     assert predict_memory(m, 2048, 1, free=80 * GiB) == base + copy - 2 * 2 * 3 * 256 * 1024   # expert matrices are not part of the dense copy
+
+
+def test_replicas_spread_requests_over_whole_copies(monkeypatch):
+    """B200_REPLICAS: one runner per GPU behind one interface; a request goes to the copy with the fewest requests in flight,
+    a follow-up that shares its prompt prefix goes back to the copy that holds it, the set reports summed memory and closes whole."""
+    from ollama_b200.engine.replicas import ReplicaSet
+    from ollama_b200.server.sched import Scheduler as S
+
+    class R:
+        def __init__(self, i):
+            self.i, self.closed, self.n_ctx, self.seen = i, False, 64, []
+            self.stats = {"requests": 0}
+
+        def completion(self, req):
+            self.seen.append(req.prompt)
+            self.stats["requests"] += 1
+            yield self.i
+            yield "done"
+
+        def ping(self):
+            return not self.closed
+
+        def memory(self):
+            return {"total": 10, "vram": 10}
+
+        def close(self):
+            self.closed = True
+
+        def tokenize(self, text, **kw):
+            return [self.i]
+
+    class Req:
+        def __init__(self, prompt):
+            self.prompt = prompt
+
+    rs = ReplicaSet(R, 3)
+    a = rs.completion(Req([1, 2, 3]))
+    assert next(a) == 0                                     # first request: first copy, still in flight
+    b = rs.completion(Req([7, 8]))
+    assert next(b) == 1                                     # the idle copies come first
+    assert list(rs.completion(Req([9]))) == [2, "done"]
+    list(a), list(b)
+    assert list(rs.completion(Req([7, 8, 9, 10])))[0] == 1  # shares a prefix with what copy 1 served last
+    assert list(rs.completion(Req([1, 2, 3, 4])))[0] == 0
+    assert rs.inflight == [0, 0, 0] and rs.memory() == {"total": 30, "vram": 30} and rs.stats["requests"] == 5 and rs.stats["replicas"] == 3
+    assert rs.n_ctx == 64 and rs.tokenize("x") == [0] and rs.ping()
+    rs.replicas[1].closed = True
+    assert not rs.ping()
+    rs.close()
+    assert all(r.closed for r in rs.replicas)
+    # a copy that fails to start takes the ones before it down with it
+    made = []
+
+    def flaky(i):
+        if i == 2:
+            raise MemoryError("no room")
+        made.append(R(i))
+        return made[-1]
+
+    with pytest.raises(MemoryError):
+        ReplicaSet(flaky, 3)
+    assert len(made) == 2 and all(r.closed for r in made)
+    # placement: as many one-copy groups as asked for and as the node has, most free memory first
+    g = gpus(4)
+    assert len(S._place_copies(g, 10 * GiB, 2)) == 2 and len(S._place_copies(g, 10 * GiB, 8)) == 4
+    assert len(S._place_copies(g, 100 * GiB, 2)) == 4       # one copy already needs two GPUs
+    monkeypatch.setenv("B200_REPLICAS", "2")
+    s, created = make(n_gpus=4)
+    ref = s.get_runner(FakeModel("a", 10 * GiB), dict(OPTS), 60)
+    assert len(created[0].gpus) == 2                        # the factory is handed the GPUs of both copies
+    s.release(ref)
