@@ -39,7 +39,7 @@ from ..text.builtin import parser_for
 from ..text.gotemplate import TemplateError
 from ..text.thinking import ThinkingParser, infer_tags
 from ..text.tools import ToolParser, infer_tag, tool_call_id
-from .caches import ModelListCache, ModelShowCache
+from .caches import InferenceModelCache, ModelListCache, ModelShowCache, RecommendationsCache
 from .prompt import PromptRenderer, chat_prompt
 from .sched import Scheduler, SchedulerError
 
@@ -72,6 +72,7 @@ class Server:
         self.sched = sched or Scheduler(get_gpus_fn=gpu_devices)
         self.renderers: dict[str, PromptRenderer] = {}
         self.list_cache, self.show_cache = ModelListCache(), ModelShowCache()
+        self.model_cache, self.recommendations = InferenceModelCache(), RecommendationsCache()
         from .request_log import RequestLogger
         self.request_log = RequestLogger()
         self.app = self._build()
@@ -104,7 +105,7 @@ class Server:
             Route("/api/signout", self.cloud_stub, methods=["POST"]),
             Route("/api/experimental/web_search", self.cloud_stub, methods=["POST"]),
             Route("/api/experimental/web_fetch", self.cloud_stub, methods=["POST"]),
-            Route("/api/experimental/model-recommendations", self.cloud_stub, methods=["GET"]),
+            Route("/api/experimental/model-recommendations", self.model_recommendations, methods=["GET"]),
             Route("/api/user/keys/{key:path}", self.cloud_stub, methods=["DELETE"]),
         ]
         from .openai import openai_routes
@@ -121,6 +122,10 @@ class Server:
         app = Starlette(routes=r, middleware=mw, on_shutdown=[self.sched.unload_all])
         app.add_exception_handler(APIError, lambda req, e: _err(e.status, e.msg))
         return app
+
+    async def model_recommendations(self, request: Request):
+        """Cached list, refreshed behind the reader's back (server/routes.go:1931-1947)."""
+        return JSONResponse({"recommendations": self.recommendations.get_swr()})
 
     async def _json(self, request: Request) -> dict[str, Any]:
         body = await request.body()
@@ -140,7 +145,7 @@ class Server:
         if not name:
             raise APIError(400, "model is required")
         try:
-            return get_model(name)
+            return self.model_cache.get(name)
         except ModelNotFound:
             raise APIError(404, f"model '{name}' not found") from None
 

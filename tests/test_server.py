@@ -373,3 +373,71 @@ def test_image_input_is_refused_not_dropped(client):
     assert r.status_code == 400
     r = client.post("/api/chat", json={"model": "tiny", "messages": [{"role": "user", "content": "<t300>"}], "stream": False})
     assert r.status_code == 200
+
+
+def test_inference_model_cache_and_recommendations(client, tmp_path, monkeypatch):
+    """server/model_inference_cache_test.go: one load per manifest digest, a private copy per request, a new digest reloads;
+    server/model_recommendations_test.go: defaults, snapshot, stale-while-revalidate, back-off, nothing fetched with cloud off."""
+    from ollama_b200.server import caches as C
+    loads = []
+
+    def load(name):
+        from ollama_b200.store.model import get_model
+        loads.append(name)
+        return get_model(name)
+
+    c = C.InferenceModelCache(load)
+    a, b = c.get("tiny"), c.get("tiny:latest")
+    assert loads == ["tiny"] and a is not b and a.digest == b.digest and c.hits == 1
+    a.options["temperature"] = 9
+    a.adapter_paths.append("x")
+    assert "x" not in c.get("tiny").adapter_paths and c.get("tiny").options.get("temperature") != 9
+    assert a.capabilities() == b.capabilities() and a._kv is b._kv
+    r = client.post("/api/create", json={"model": "tiny", "from": "tiny", "system": "changed", "stream": False})
+    assert r.status_code == 200
+    assert c.get("tiny").system == "changed" and len(loads) == 2          # the manifest digest moved: loaded again
+    import pytest
+    from ollama_b200.store.model import ModelNotFound
+    with pytest.raises(ModelNotFound):
+        c.get("absent")
+    r = client.post("/api/create", json={"model": "tiny", "from": "tiny", "system": "", "stream": False})
+    assert r.status_code == 200
+
+    # recommendations
+    assert client.get("/api/experimental/model-recommendations").json()["recommendations"][0]["model"]
+    clock = [0.0]
+    answers = [[{"model": "m1", "description": "d", "vram_bytes": 5}], RuntimeError("down"), RuntimeError("down"), [{"model": "m2", "description": ""}]]
+
+    def fetch():
+        v = answers.pop(0)
+        if isinstance(v, Exception):
+            raise v
+        return v
+
+    monkeypatch.delenv("OLLAMA_NO_CLOUD", raising=False)
+    snap = str(tmp_path / "rec.json")
+    rc = C.RecommendationsCache(fetch, snap, now=lambda: clock[0])
+    assert rc.source == "default" and rc.get_swr(background=False)[0]["model"] == C.DEFAULT_RECOMMENDATIONS[0]["model"]   # stale first ...
+    assert rc.get()[0] == {"model": "m1", "description": "d", "vram_bytes": 5} and rc.source == "remote"              # ... fresh after
+    assert C.RecommendationsCache(fetch, snap).source == "snapshot"
+    rc.get_swr(background=False)
+    assert len(answers) == 3                                               # inside the 4 h refresh interval: no fetch
+    clock[0] += 4 * 3600 + 1
+    rc.get_swr(background=False)
+    assert rc.failures == 1 and rc.get()[0]["model"] == "m1"               # failure keeps the list
+    clock[0] += 299
+    rc.get_swr(background=False)
+    assert len(answers) == 2                                               # first back-off step: 5 minutes
+    clock[0] += 2
+    rc.get_swr(background=False)
+    assert rc.failures == 2
+    clock[0] += 901
+    rc.get_swr(background=False)
+    assert rc.failures == 0 and rc.get()[0]["model"] == "m2"
+    monkeypatch.setenv("OLLAMA_NO_CLOUD", "1")
+    quiet = C.RecommendationsCache(lambda: (_ for _ in ()).throw(AssertionError("fetched")), str(tmp_path / "none.json"))
+    quiet.get_swr(background=False)
+    assert quiet.source == "default" and quiet.failures == 0
+    for bad in (None, [], [{"description": "x"}], [{"model": "m", "vram_bytes": "big"}], [{"model": "m", "context_length": -1}]):
+        with pytest.raises(ValueError):
+            C.validate_recommendations(bad)
