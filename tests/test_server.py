@@ -441,3 +441,64 @@ def test_inference_model_cache_and_recommendations(client, tmp_path, monkeypatch
     for bad in (None, [], [{"description": "x"}], [{"model": "m", "vram_bytes": "big"}], [{"model": "m", "context_length": -1}]):
         with pytest.raises(ValueError):
             C.validate_recommendations(bad)
+
+
+def test_anthropic_web_search_server_tool_loop(client):
+    """middleware/anthropic_test.go (web search): calls of the built-in tool are answered by the server, results go back to the
+    model, at most three searches, every search shows up as a server_tool_use + web_search_tool_result pair."""
+    from ollama_b200.server import anthropic as A
+    tools, wants = A.split_server_tools([{"type": "web_search_20250305", "name": "web_search"}, {"name": "web_search", "input_schema": {}},
+                                         {"name": "calc", "description": "adds", "input_schema": {"type": "object"}}])
+    assert wants and [t["function"]["name"] for t in tools] == ["web_search", "calc"] and tools[0] is A.WEB_SEARCH_TOOL
+    assert A.split_server_tools([{"name": "web_search", "input_schema": {}}]) == ([{"type": "function", "function": {"name": "web_search", "description": "", "parameters": {}}}], False)
+
+    def call(q):
+        return {"message": {"role": "assistant", "content": "", "tool_calls": [{"id": "c1", "function": {"name": "web_search", "arguments": {"query": q}}}]},
+                "prompt_eval_count": 10, "eval_count": 5, "done_reason": "stop"}
+
+    answer = {"message": {"role": "assistant", "content": "It is sunny."}, "prompt_eval_count": 30, "eval_count": 7, "done_reason": "stop"}
+    native = {"model": "m", "messages": [{"role": "user", "content": "weather?"}], "tools": [A.WEB_SEARCH_TOOL], "options": {}}
+    seen = []
+
+    def chat_once(req):
+        seen.append(req["messages"])
+        return answer
+
+    found = [{"title": "Weather", "url": "https://w.example", "content": "sunny"}]
+    out = A.run_web_search_loop(chat_once, native, call("weather today"), lambda q, n: found, "msg_abc", "m")
+    assert [b["type"] for b in out["content"]] == ["server_tool_use", "web_search_tool_result", "text"]
+    assert out["content"][0] == {"type": "server_tool_use", "id": "srvtoolu_abc", "name": "web_search", "input": {"query": "weather today"}}
+    assert out["content"][1]["content"] == [{"type": "web_search_result", "url": "https://w.example", "title": "Weather"}]
+    assert out["usage"] == {"input_tokens": 40, "output_tokens": 12} and out["stop_reason"] == "end_turn"
+    assert seen[0][-1] == {"role": "tool", "content": "Title: Weather\nURL: https://w.example\nContent: sunny\n\n", "tool_call_id": "c1"}
+    assert seen[0][-2]["tool_calls"][0]["function"]["arguments"] == {"query": "weather today"} and len(native["messages"]) == 1
+    # a model that keeps searching is stopped after three searches
+    n = [0]
+
+    def chat_again(req):
+        n[0] += 1
+        return call(f"again {n[0]}")
+
+    out = A.run_web_search_loop(chat_again, native, call("q0"), lambda q, k: found, "msg_x", "m")
+    assert n[0] == 3 and [b["id"] for b in out["content"] if b["type"] == "server_tool_use"] == ["srvtoolu_x", "srvtoolu_x_2", "srvtoolu_x_3", "srvtoolu_x_4"]
+    assert out["content"][-1]["content"] == {"type": "web_search_tool_result_error", "error_code": "max_uses_exceeded"}
+    # failures of the search, of the follow-up turn and an empty query are results with an error code, not exceptions
+
+    def down(q, k):
+        raise OSError("no route")
+
+    assert A.run_web_search_loop(chat_once, native, call("q"), down, "msg_y", "m")["content"][1]["content"]["error_code"] == "unavailable"
+    assert A.run_web_search_loop(chat_once, native, call("  "), lambda q, k: found, "msg_y", "m")["content"][1]["content"]["error_code"] == "invalid_request"
+
+    def broken(req):
+        raise RuntimeError("runner died")
+
+    assert A.run_web_search_loop(broken, native, call("q"), lambda q, k: found, "msg_y", "m")["content"][-1]["content"]["error_code"] == "api_error"
+    # the finished message as a stream
+    names = [name for name, _ in A.message_events(A.run_web_search_loop(chat_once, native, call("q"), lambda q, k: found, "msg_z", "m"))]
+    assert names == ["message_start", "content_block_start", "content_block_delta", "content_block_stop", "content_block_start", "content_block_stop",
+                     "content_block_start", "content_block_delta", "content_block_stop", "message_delta", "message_stop"]
+    # through the route: a model without tool support refuses, as it does for client tools
+    r = client.post("/v1/messages", json={"model": "tiny", "max_tokens": 4, "messages": [{"role": "user", "content": "hi"}],
+                                         "tools": [{"type": "web_search_20250305", "name": "web_search"}]})
+    assert r.status_code == 400 and "does not support tools" in r.json()["error"]["message"]
