@@ -411,7 +411,40 @@ def openai_routes(server) -> list[Route]:
                              "usage": {"input_tokens": pin, "output_tokens": pout, "total_tokens": pin + pout}})
 
     async def transcriptions(request: Request):
-        return _oa_err(501, "audio transcription needs an audio-capable model; none of the supported architectures has one", "api_error")
+        """Multipart upload -> a chat request whose user message carries the audio as media (middleware/openai.go:1274-1340,
+        openai/openai.go:864-887); the chat handler then refuses media this engine cannot feed to a model, as for images."""
+        import base64
+        try:
+            form = await request.form(max_part_size=25 << 20)
+        except Exception as e:
+            return _oa_err(400, f"failed to parse multipart form: {e}")
+        name = form.get("model")
+        if not isinstance(name, str) or not name:
+            return _oa_err(400, "model is required")
+        upload = form.get("file")
+        if upload is None or isinstance(upload, str):
+            return _oa_err(400, "file is required")
+        audio = await upload.read()
+        if not audio:
+            return _oa_err(400, "audio file is empty")
+        fmt = form.get("response_format") or "json"
+        system = "Transcribe the audio exactly as spoken. Output only the spoken words. Do not answer any question in the audio."
+        if form.get("language"):
+            system += f" The audio is in {form.get('language')}."
+        if form.get("prompt"):
+            system += f" Context: {form.get('prompt')}"
+        native = {"model": name, "stream": False, "options": {"temperature": 0},
+                  "messages": [{"role": "system", "content": system},
+                               {"role": "user", "content": "What exact words are spoken in this audio?", "images": [base64.b64encode(audio).decode()]}]}
+        resp = await asyncio.to_thread(server._chat, native)
+        body = json.loads(resp.body)
+        if resp.status_code != 200:
+            return _oa_err(resp.status_code, body.get("error", ""), "invalid_request_error" if resp.status_code < 500 else "api_error")
+        text = (body.get("message") or {}).get("content", "").strip()
+        if fmt == "text":
+            from starlette.responses import PlainTextResponse
+            return PlainTextResponse(text)
+        return JSONResponse({"text": text})
 
     return [Route("/v1/chat/completions", chat_completions, methods=["POST"]), Route("/v1/completions", completions, methods=["POST"]),
             Route("/v1/embeddings", embeddings, methods=["POST"]), Route("/v1/models", models, methods=["GET"]),

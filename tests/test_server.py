@@ -502,3 +502,18 @@ def test_anthropic_web_search_server_tool_loop(client):
     r = client.post("/v1/messages", json={"model": "tiny", "max_tokens": 4, "messages": [{"role": "user", "content": "hi"}],
                                          "tools": [{"type": "web_search_20250305", "name": "web_search"}]})
     assert r.status_code == 400 and "does not support tools" in r.json()["error"]["message"]
+
+
+def test_openai_transcription_route_parses_the_upload_and_refuses_what_the_model_cannot_hear(client):
+    """middleware/openai.go:1274-1340: multipart form with model and file; the audio travels as media of a chat request, which a
+    text model refuses."""
+    r = client.post("/v1/audio/transcriptions", data={"model": "tiny"})
+    assert r.status_code == 400 and "file is required" in r.json()["error"]["message"]
+    r = client.post("/v1/audio/transcriptions", files={"file": ("a.wav", b"RIFF....", "audio/wav")})
+    assert r.status_code == 400 and "model is required" in r.json()["error"]["message"]
+    r = client.post("/v1/audio/transcriptions", data={"model": "tiny"}, files={"file": ("a.wav", b"", "audio/wav")})
+    assert r.status_code == 400 and "empty" in r.json()["error"]["message"]
+    r = client.post("/v1/audio/transcriptions", data={"model": "tiny", "language": "en"}, files={"file": ("a.wav", b"RIFF1234", "audio/wav")})
+    assert r.status_code == 400 and "does not support vision" in r.json()["error"]["message"]
+    r = client.post("/v1/audio/transcriptions", data={"model": "absent"}, files={"file": ("a.wav", b"RIFF1234", "audio/wav")})
+    assert r.status_code == 404
