@@ -12,6 +12,7 @@ name                    reasoning block             tool call
 ``qwen3-thinking``      starts inside ``<think>``   same
 ``qwen3-vl-instruct``   none                        same
 ``qwen3-vl-thinking``   starts inside ``<think>``   same; a call may cut the reasoning block short
+``qwen3.5``, ``ornith``  starts inside ``<think>``   the qwen3-coder form; a call may cut the reasoning block short
 ``qwen3-coder``         none                        ``<tool_call><function=f><parameter=k>\\nv\\n</parameter></function></tool_call>``
 ``ministral``           ``[THINK]..[/THINK]``       ``[TOOL_CALLS]name[ARGS]{json}``
 ``functiongemma``       none                        ``<start_function_call>call:name{k:<escape>v<escape>}<end_function_call>``
@@ -529,7 +530,7 @@ def _glm_call(tools: list[dict[str, Any]] | None) -> Callable[[str], dict[str, A
     return decode
 
 
-PARSERS = ("qwen3", "qwen3-thinking", "qwen3-coder", "qwen3-vl-instruct", "qwen3-vl-thinking", "ministral", "functiongemma", "cogito", "deepseek3",
+PARSERS = ("qwen3", "qwen3-thinking", "qwen3-coder", "qwen3.5", "ornith", "qwen3-vl-instruct", "qwen3-vl-thinking", "ministral", "functiongemma", "cogito", "deepseek3",
            "olmo3", "olmo3-think", "glm-4.6", "glm-4.7", "passthrough")
 
 
@@ -553,6 +554,9 @@ def parser_for(name: str | None, tools: list[dict[str, Any]] | None = None, thin
         return TagStreamParser(think_close="</think>", start_thinking=thinking, regions=[json_call], call_ends_thinking=True)
     if name == "qwen3-coder":
         return TagStreamParser(regions=[Region("<tool_call>", "</tool_call>", _xml_call(tools))])
+    if name in ("qwen3.5", "ornith"):             # model/parsers/qwen35.go:57-78: reasoning unless switched off, XML calls, a call ends the block
+        return TagStreamParser(think_open="<think>", think_close="</think>", start_thinking=think is not False and (think is None or bool(think)) and fresh,
+                               regions=[Region("<tool_call>", "</tool_call>", _xml_call(tools))], call_ends_thinking=True)
     if name == "functiongemma":
         return TagStreamParser(regions=[Region("<start_function_call>", "<end_function_call>", _functiongemma_call)])
     if name == "ministral":

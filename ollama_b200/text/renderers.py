@@ -14,6 +14,8 @@ name                 format
 qwen3-coder          ChatML, tools declared as XML, calls as ``<function=..><parameter=..>`` (qwen3coder.go:63-198)
 qwen3-vl-instruct    ChatML, tools declared as JSON lines, calls as JSON in ``<tool_call>`` (qwen3vl.go:40-148)
 qwen3-vl-thinking    the same with ``<think>`` blocks kept after the last question
+qwen3.5 / ornith     ChatML, JSON declarations with XML calls, trimmed content (qwen35.go:210-360)
+qwen3.8              the same with merged instructions and a reasoning-effort sentence (qwen35.go:117-208)
 cogito               DeepSeek marks, tools as fenced JSON in the system text (cogito.go:18-132)
 deepseek3.1          DeepSeek marks, ``</think>`` closes an absent reasoning block (deepseek3.go:26-160)
 olmo3 / olmo3.1      ChatML, ``<functions>`` in the system turn, Python-style calls (olmo3.go:27-158)
@@ -412,6 +414,107 @@ class Qwen3VL(ChatML):
         return f"{self.opener}assistant\n" + ("<think>\n" if x.memo["thinking"] else "<think>\n\n</think>\n\n" if self.empty_block_when_off else "")
 
 
+class RenderError(ValueError):
+    """The conversation cannot be rendered for this family (the request is at fault)."""
+
+
+_QWEN35_TOOLS_OUTRO = "\n</tools>" + _QWEN3_CODER_CALL_FORMAT
+_QWEN38_EFFORT = {
+    "high": ("Reasoning effort is set to xhigh. Please think carefully through the task, validate key assumptions, consider plausible alternatives, "
+             "and prioritize correctness, consistency, and clarity in the final answer."),
+    "low": "Reasoning effort is set to low. Keep your thinking brief and focused, moving directly to the conclusion without unnecessary elaboration.",
+    "medium": "",
+}
+_QWEN38_EFFORT["max"] = _QWEN38_EFFORT["high"]
+
+
+class Qwen35(Qwen3VL):
+    """ChatML with JSON tool declarations but XML calls; content is trimmed; the system text follows the tool section.
+
+    ``always_block``: every stored assistant turn is printed with a ``<think>`` block (empty if it has no reasoning), not only
+    the turns after the last question.  ``effort`` (the 3.8 spelling): system and developer messages are merged into one
+    leading system turn, a sentence about the reasoning effort opens it, reasoning is never dug out of stored content, and
+    a conversation without a real question is refused."""
+
+    def __init__(self, always_block: bool = False, effort: bool = False, image_tags: bool = True):
+        super().__init__(thinking=True, image_tags=image_tags, empty_block_when_off=True)
+        self.always_block, self.effort = always_block, effort
+
+    def render(self, messages, tools=None, think=None):
+        if self.effort:
+            messages = self._merged_instructions(messages)
+            if not messages:
+                raise RenderError("no messages provided")
+        return super().render(messages, tools, think)
+
+    @staticmethod
+    def _merged_instructions(messages: list[Message]) -> list[Message]:
+        lead = [m for m in messages if m.get("role") in ("system", "developer")]
+        if any(m.get("images") for m in lead):
+            raise RenderError("system message cannot contain images")
+        if not lead or (len(lead) == 1 and messages[0].get("role") == "system"):
+            return messages
+        text = "\n\n".join(t for t in ((m.get("content") or "").strip() for m in lead) if t)
+        return [{"role": "system", "content": text}] + [m for m in messages if m.get("role") not in ("system", "developer")]
+
+    def text(self, t: Turn) -> str:
+        return super().text(t).strip()
+
+    def prepare(self, x: Ctx) -> None:
+        super().prepare(x)
+        x.memo["thinking"] = self.thinking if x.think is None else think_on(x.think, True) and x.think is not False
+        x.memo["effort"] = ""
+        if self.effort:
+            if x.think is not None and not isinstance(x.think, bool) and x.think not in _QWEN38_EFFORT:
+                raise RenderError(f"unsupported reasoning effort {x.think!r}")
+            x.memo["effort"] = _QWEN38_EFFORT["high"] if x.think is None else "" if isinstance(x.think, bool) else _QWEN38_EFFORT[x.think]
+            if not any(t.role == "user" and not self._wrapped(self.text(t)) for t in x.conv.turns):
+                raise RenderError("no user query found in messages")
+
+    @staticmethod
+    def _wrapped(c: str) -> bool:
+        return c.startswith("<tool_response>") and c.endswith("</tool_response>")
+
+    def head(self, x: Ctx) -> str:
+        sys = None if x.conv.system_text is None else x.conv.system_text.strip()
+        effort = x.memo["effort"]
+        if x.tools:
+            body = (effort + "\n\n" if effort else "") + "# Tools\n\nYou have access to the following functions:\n\n<tools>"
+            body += "".join("\n" + go_json(tool_schema(t), spaced=True) for t in x.tools) + _QWEN35_TOOLS_OUTRO
+            return self.block("system", body + ("\n\n" + sys if sys else ""))
+        if sys is not None:
+            if self.effort and not sys and not effort:
+                return ""
+            return self.block("system", effort + ("\n\n" if effort and sys else "") + sys)
+        return self.block("system", effort) if effort else ""
+
+    def turn_other(self, t: Turn, x: Ctx) -> str:
+        if t.role in ("user", "system") or self.effort:
+            return self.block(t.role, self.text(t))
+        return ""
+
+    turn_user = turn_other
+
+    def turn_tool(self, t: Turn, x: Ctx) -> str:
+        return f"{self.opener}user" + "".join(f"\n<tool_response>\n{c.strip()}\n</tool_response>" for _, c in t.results) + self.closer
+
+    def turn_assistant(self, t: Turn, x: Ctx) -> str:
+        content = self.text(t)
+        block = self.always_block or (x.memo["thinking"] and t.pos > x.memo["question"])
+        reasoning = ""
+        if block and t.thinking:
+            reasoning = t.thinking.strip()
+        elif not self.effort and "</think>" in content:          # reasoning that an older client left inside the content
+            before, _, after = content.partition("</think>")
+            reasoning, content = before.rpartition("<think>")[2].strip(), after.lstrip("\n")
+        body = f"<think>\n{reasoning}\n</think>\n\n{content}" if block else content
+        for j, (name, args) in enumerate(t.calls):
+            body += ("\n\n" if content.strip() else "") if j == 0 else "\n"
+            body += f"<tool_call>\n<function={name}>\n" + "".join(f"<parameter={k}>\n{_xml_scalar(v)}\n</parameter>\n" for k, v in args.items())
+            body += "</function>\n</tool_call>"
+        return self.block("assistant", body, close=t is not x.conv.last)
+
+
 _OLMO3_WITH_FUNCTIONS = ("You are provided with function signatures within <functions></functions> XML tags. You may call one or more functions to assist "
                          "with the user query. Output any function calls within <function_calls></function_calls> XML tags. Do not make assumptions about "
                          "what values to plug into functions.")
@@ -739,6 +842,9 @@ DIALECTS: dict[str, Callable[[], Dialect]] = {
     "qwen3-coder": Qwen3Coder,
     "qwen3-vl-instruct": lambda: Qwen3VL(thinking=False),
     "qwen3-vl-thinking": lambda: Qwen3VL(thinking=True),
+    "qwen3.5": lambda: Qwen35(),
+    "qwen3.8": lambda: Qwen35(always_block=True, effort=True),
+    "ornith": lambda: Qwen35(always_block=True),
     "cogito": Cogito,
     "deepseek3.1": DeepSeek31,
     "olmo3": lambda: Olmo3(extended=False),

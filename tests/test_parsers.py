@@ -105,3 +105,27 @@ def test_registry_and_initial_state():
     # a call inside the reasoning block of qwen3-vl ends the block
     c, t, k = B.parser_for("qwen3-vl-thinking", TOOLS).add('hm <tool_call>{"name": "get_weather", "arguments": {}}</tool_call> ok', True)
     assert (c, t, k[0]["function"]["name"]) == ("ok", "hm", "get_weather")
+
+
+def test_qwen35_parser_cases():
+    """model/parsers/qwen35_test.go restated: reasoning unless switched off, an explicit opening tag is tolerated, a call inside the
+    block ends it, a false start of a call mark stays reasoning, a leading closing tag gives content, white space after the block goes."""
+    tools = [{"type": "function", "function": {"name": "get_weather", "parameters": {"type": "object", "properties": {"location": {"type": "string"}}}}}]
+    call = "<tool_call><function=get_weather><parameter=location>\nSF\n</parameter></function></tool_call>"
+
+    def run(chunks, think=True, prefill=""):
+        p = B.parser_for("qwen3.5", tools, think, prefill)
+        out = [p.add(c, i == len(chunks) - 1) for i, c in enumerate(chunks)]
+        return "".join(o[0] for o in out), "".join(o[1] for o in out), [k["function"] for o in out for k in o[2]], out
+
+    c, t, k, _ = run(["Need weather lookup" + call])
+    assert (c, t, k) == ("", "Need weather lookup", [{"name": "get_weather", "arguments": {"location": "SF"}}])
+    c, t, k, _ = run(["Need weather lookup<tool", "_call><function=get_weather><parameter=location>\nSF\n</parameter></function></tool_call>"])
+    assert (c, t, len(k)) == ("", "Need weather lookup", 1)
+    c, t, k, steps = run(["Need weather lookup<tool_c", "</thi", "nk>"])
+    assert (c, t, k) == ("", "Need weather lookup<tool_c", []) and steps[0][1] == "Need weather lookup" and steps[1][1] == "<tool_c"
+    assert run(["<think>Let me think</think>Answer."])[:2] == ("Answer.", "Let me think")
+    assert run(["I think</think>\n\nDone." + call])[:3] == ("Done.", "I think", [{"name": "get_weather", "arguments": {"location": "SF"}}])
+    assert run(["</think>The final answer."])[:2] == ("The final answer.", "")
+    assert run(["plain </think> text"], think=False)[:2] == ("plain </think> text", "") and run([" goes on"], prefill="It")[:2] == (" goes on", "")
+    assert run(["abc</th", "ink>", "\n\n  ", "def"])[:2] == ("def", "abc") and run(["never closed"])[:2] == ("", "never closed")

@@ -33,8 +33,8 @@ def test_renderer_reproduces_the_reference_prompts(name):
 
 def test_every_registered_renderer_has_cases_and_renders_an_empty_conversation():
     covered = {c["renderer"] for c in CASES}
-    assert covered >= set(R.DIALECTS) - {"olmo3.1"}
-    for name in R.DIALECTS:
+    assert covered >= set(R.DIALECTS) - {"olmo3.1", "qwen3.5", "qwen3.8", "ornith"}
+    for name in set(R.DIALECTS) - {"qwen3.8"}:
         assert isinstance(R.renderer_for(name).render([], None, None), str)
     assert R.renderer_for("olmo3.1").render([{"role": "user", "content": "hi"}]).startswith("<|im_start|>system\nYou are Olmo, a helpful AI assistant built by Ai2.")
     assert R.renderer_for("nope") is None and R.renderer_for(None) is None
@@ -64,3 +64,64 @@ def test_json_in_the_reference_encoders_spelling():
     assert R.go_json(R.tool_schema(tool)) == ('{"type":"function","function":{"name":"n","description":"D","parameters":{"type":"object","required":["p"],'
                                               '"properties":{"p":{"type":"string","description":"d","enum":["a"]}}}}}')
     assert R.image_tagged("look [img] and", 2, 3) == "[img-4] look [img-3] and" and R.image_tagged("x", 0, 0) == "x" and R.image_tagged("[img-0] x", 1, 5) == "[img-0] x"
+
+
+def test_qwen35_family():
+    """Cases of model/renderers/qwen35_test.go, qwen38_test.go and ornith_test.go restated: XML calls under JSON declarations, the
+    system text after the tool section, reasoning kept only after the last question (3.5) or on every stored turn (3.8, ornith),
+    merged instructions and the reasoning-effort sentence of 3.8, its refusals."""
+    tc = lambda n, **a: {"function": {"name": n, "arguments": a}}   # noqa: E731
+    XH, LOW = R._QWEN38_EFFORT["high"], R._QWEN38_EFFORT["low"]
+    U = lambda c: f"<|im_start|>user\n{c}<|im_end|>\n"              # noqa: E731
+    CUE = "<|im_start|>assistant\n<think>\n"
+    r35, r38 = R.Qwen35(image_tags=False), R.Qwen35(always_block=True, effort=True, image_tags=False)
+    tools = [{"type": "function", "function": {"name": n, "description": d, "parameters": {"type": "object", "required": ["city"], "properties": {"city": {"type": "string"}}}}}
+             for n, d in (("get_weather", "Get weather"), ("get_uv", "Get UV index"))]
+    msgs = [{"role": "system", "content": "You are a helpful assistant."}, {"role": "user", "content": "Run add and multiply."},
+            {"role": "assistant", "content": "I'll run both now.", "thinking": "Need to call add and multiply.", "tool_calls": [tc("add", a=2, b=3), tc("multiply", x=4, y=5)]},
+            {"role": "tool", "content": "5"}, {"role": "tool", "content": "20"}, {"role": "user", "content": "Summarize the results."}]
+    got = r35.render(msgs, tools)
+    assert "Need to call add" not in got and got.index("# Tools") < got.index("You are a helpful assistant.") and got.endswith(CUE)
+    assert ("<tool_call>\n<function=add>\n<parameter=a>\n2\n</parameter>\n<parameter=b>\n3\n</parameter>\n</function>\n</tool_call>\n<tool_call>\n<function=multiply>\n"
+            "<parameter=x>\n4\n</parameter>\n<parameter=y>\n5\n</parameter>\n</function>\n</tool_call>") in got
+    assert "<|im_start|>user\n<tool_response>\n5\n</tool_response>\n<tool_response>\n20\n</tool_response><|im_end|>" in got
+    msgs = [{"role": "user", "content": "Plan a picnic."}, {"role": "assistant", "content": "Checking weather first.", "thinking": "Need weather.", "tool_calls": [tc("get_weather", city="Paris")]},
+            {"role": "tool", "content": "22C"}]
+    assert ("<|im_start|>assistant\n<think>\nNeed weather.\n</think>\n\nChecking weather first.\n\n<tool_call>\n<function=get_weather>\n<parameter=city>\nParis\n</parameter>\n"
+            "</function>\n</tool_call><|im_end|>") in r35.render(msgs, tools)
+    assert r35.render([{"role": "user", "content": "Write two words."}, {"role": "assistant", "thinking": "Keep it short.", "content": "Hello world"}]) == \
+        U("Write two words.") + "<|im_start|>assistant\n<think>\nKeep it short.\n</think>\n\nHello world"
+    assert r35.render([{"role": "user", "content": "hello"}], None, False).endswith("<|im_start|>assistant\n<think>\n\n</think>\n\n")
+    # reasoning left inside stored content by an older client is moved into the block (3.5 only)
+    assert "<think>\nplan\n</think>\n\nAnswer" in r35.render([{"role": "user", "content": "q"}, {"role": "assistant", "content": "<think>plan</think>\nAnswer"}])
+    # 3.8
+    sys = lambda body: f"<|im_start|>system\n{body}<|im_end|>\n"    # noqa: E731
+    assert r38.render([{"role": "user", "content": "Hello"}]) == sys(XH) + U("Hello") + CUE
+    assert r38.render([{"role": "developer", "content": "Use Go."}, {"role": "user", "content": "Hello"}]) == sys(XH + "\n\nUse Go.") + U("Hello") + CUE
+    flow = [{"role": "system", "content": "Base policy."}, {"role": "user", "content": "Base question"}, {"role": "assistant", "content": "Base answer"},
+            {"role": "system", "content": "Request policy."}, {"role": "user", "content": "Current question"}]
+    assert r38.render(flow) == (sys(XH + "\n\nBase policy.\n\nRequest policy.") + U("Base question") + "<|im_start|>assistant\n<think>\n\n</think>\n\nBase answer<|im_end|>\n"
+                                + U("Current question") + CUE)
+    assert r38.render([{"role": "system", "content": " Be concise. \n"}, {"role": "user", "content": "Hello"}], None, True) == sys("Be concise.") + U("Hello") + CUE
+    assert r38.render([{"role": "user", "content": "Hello"}], None, "low") == sys(LOW) + U("Hello") + CUE
+    assert r38.render([{"role": "user", "content": "Hello"}], None, False) == U("Hello") + "<|im_start|>assistant\n<think>\n\n</think>\n\n"
+    kept = [{"role": "user", "content": "First"}, {"role": "assistant", "thinking": "Plan", "content": "<think>literal</think>\nAnswer"}, {"role": "user", "content": "Next"}]
+    assert r38.render(kept) == sys(XH) + U("First") + "<|im_start|>assistant\n<think>\nPlan\n</think>\n\n<think>literal</think>\nAnswer<|im_end|>\n" + U("Next") + CUE
+    got = r38.render([{"role": "developer", "content": "Use tools when requested."}, {"role": "user", "content": "Check the weather."}], tools, True)
+    assert got.startswith("<|im_start|>system\n# Tools\n\nYou have access to the following functions:\n\n<tools>\n" + R.go_json(R.tool_schema(tools[0]), spaced=True) + "\n")
+    assert got.endswith("</IMPORTANT>\n\nUse tools when requested.<|im_end|>\n" + U("Check the weather.") + CUE)
+    got = r38.render([{"role": "user", "content": "Weather?"}, {"role": "assistant", "thinking": "Need current data.", "content": "I'll check.", "tool_calls": [tc("get_weather", city="Montréal")]},
+                      {"role": "tool", "content": '{"temp": 18}'}], tools, True)
+    assert got.endswith(U("Weather?") + "<|im_start|>assistant\n<think>\nNeed current data.\n</think>\n\nI'll check.\n\n<tool_call>\n<function=get_weather>\n<parameter=city>\nMontréal\n"
+                        "</parameter>\n</function>\n</tool_call><|im_end|>\n<|im_start|>user\n<tool_response>\n{\"temp\": 18}\n</tool_response><|im_end|>\n" + CUE)
+    assert r38.render([{"role": "user", "content": "Describe this.", "images": ["x"]}], None, False).startswith(U("<|vision_start|><|image_pad|><|vision_end|>Describe this."))
+    for bad, why in (([], "no messages provided"), ([{"role": "system", "content": "Hello"}], "no user query"),
+                     ([{"role": "system", "images": ["x"]}, {"role": "user", "content": "Hello"}], "cannot contain images")):
+        with pytest.raises(R.RenderError, match=why):
+            r38.render(bad)
+    with pytest.raises(R.RenderError):
+        r38.render([{"role": "user", "content": "x"}], None, "extreme")
+    # ornith: every stored assistant turn carries a block, also with thinking switched off
+    orn = R.renderer_for("ornith")
+    got = orn.render([{"role": "user", "content": "a"}, {"role": "assistant", "content": "b"}, {"role": "user", "content": "c"}], None, False)
+    assert "<|im_start|>assistant\n<think>\n\n</think>\n\nb<|im_end|>" in got and got.endswith("<think>\n\n</think>\n\n")
