@@ -22,6 +22,7 @@ name                    reasoning block             tool call
 ``olmo3-think``         starts inside ``<think>``   none
 ``glm-4.6``             ``<think>..</think>``       ``<tool_call>name<arg_key>k</arg_key><arg_value>v</arg_value></tool_call>``
 ``glm-4.7``             starts inside ``<think>``   same
+``cohere``              starts inside the block     JSON list of ``{"tool_call_id", "tool_name", "parameters"}`` between action marks
 ``passthrough``         none                        none
 ======================  ==========================  ================================================================
 
@@ -77,11 +78,12 @@ class TagStreamParser:
     """
 
     def __init__(self, *, think_open: str = "", think_close: str = "", start_thinking: bool = False, regions: list[Region] | None = None,
-                 call_ends_thinking: bool = False, keep_space: bool = False):
+                 call_ends_thinking: bool = False, keep_space: bool = False, drop_marks: dict[str, bool] | None = None):
         self.think_open, self.think_close = think_open, think_close
         self.regions = [r for r in regions or [] if r.decode is not None or r.drop or r.unwrap]
         self.call_ends_thinking = call_ends_thinking    # a call that opens inside the reasoning block ends the block
         self.keep_space = keep_space                    # reasoning is handed on with the white space it ends in
+        self.drop_marks = dict(drop_marks or {})        # marks that only frame content: removed; True = white space after them goes too
         self.state: Any = "thinking" if start_thinking and think_close else "content"
         self.may_open_think = bool(think_open)          # an explicit opening tag is accepted at the very start only
         self.skip_ws = False                            # white space right after a closed block belongs to the markup
@@ -153,8 +155,13 @@ class TagStreamParser:
             if not self.buf:
                 return False
             self.skip_ws = False
-        marks = [r.open for r in self.regions] + ([self.think_open] if self.may_open_think else [])
+        marks = [r.open for r in self.regions] + list(self.drop_marks) + ([self.think_open] if self.may_open_think else [])
         hit = self._first(marks)
+        if hit is not None and hit[1] in self.drop_marks:
+            i, mark = hit
+            content.append(self.buf[:i])
+            self.buf, self.skip_ws = self.buf[i + len(mark):], self.drop_marks[mark]
+            return True
         if hit is None:
             before = len(content)
             self._flush(content, marks, done)
@@ -530,8 +537,35 @@ def _glm_call(tools: list[dict[str, Any]] | None) -> Callable[[str], dict[str, A
     return decode
 
 
+# -- Cohere: a JSON list of {"tool_call_id", "tool_name", "parameters"} between action marks ----------------------
+def _cohere_actions(body: str) -> list[dict[str, Any]]:
+    def call(o: Any) -> dict[str, Any] | None:
+        if not isinstance(o, dict) or not isinstance(o.get("tool_name"), str):
+            return None
+        args = o.get("parameters")
+        out: dict[str, Any] = {"function": {"name": o["tool_name"], "arguments": args if isinstance(args, dict) else {}}}
+        if o.get("tool_call_id") not in (None, ""):
+            out["id"] = str(o["tool_call_id"])
+        return out
+
+    body = body.strip()
+    try:
+        whole = json.loads(body) if body else []
+        items = whole if isinstance(whole, list) else [whole]
+    except ValueError:                          # a damaged list: take every object that still decodes on its own
+        items, dec, i = [], json.JSONDecoder(), body.find("{")
+        while i >= 0:
+            try:
+                obj, end = dec.raw_decode(body, i)
+                items.append(obj)
+                i = body.find("{", end)
+            except ValueError:
+                i = body.find("{", i + 1)
+    return [c for c in map(call, items) if c is not None]
+
+
 PARSERS = ("qwen3", "qwen3-thinking", "qwen3-coder", "qwen3.5", "ornith", "qwen3-vl-instruct", "qwen3-vl-thinking", "ministral", "functiongemma", "cogito", "deepseek3",
-           "olmo3", "olmo3-think", "glm-4.6", "glm-4.7", "passthrough")
+           "olmo3", "olmo3-think", "glm-4.6", "glm-4.7", "cohere", "passthrough")
 
 
 def parser_for(name: str | None, tools: list[dict[str, Any]] | None = None, think: Any = None,
@@ -570,6 +604,14 @@ def parser_for(name: str | None, tools: list[dict[str, Any]] | None = None, thin
         echo = (Region("<｜tool▁outputs▁begin｜>", "<｜tool▁outputs▁end｜>", drop=True) if name == "cogito"
                 else Region("<｜tool▁output▁begin｜>", "<｜tool▁output▁end｜>", unwrap=True))
         return TagStreamParser(think_close="</think>", start_thinking=thinking, regions=[calls, echo])
+    if name == "cohere":
+        # model/parsers/cohere.go:66-84: the prompt ends inside the reasoning block unless reasoning is off; the answer comes in
+        # text (or response) marks, calls in action marks; the marks themselves and the white space between blocks go
+        frames = {"<|START_TEXT|>": False, "<|START_RESPONSE|>": False, "<|END_TEXT|>": True, "<|END_RESPONSE|>": True, "<|END_OF_TURN_TOKEN|>": True}
+        p = TagStreamParser(think_close="<|END_THINKING|>", start_thinking=(think is None or bool(think)) and fresh, drop_marks=frames,
+                            regions=[Region("<|START_ACTION|>", "<|END_ACTION|>", _cohere_actions)])
+        p.skip_ws = fresh and p.state == "content"
+        return p
     if name == "olmo3":
         return TagStreamParser(regions=[Region("<function_calls>", "</function_calls>", _pythonic_calls)])
     if name == "olmo3-think":                                     # model/parsers/olmo3_think.go:43-55: the prompt always ends in <think>

@@ -21,6 +21,7 @@ deepseek3.1          DeepSeek marks, ``</think>`` closes an absent reasoning blo
 olmo3 / olmo3.1      ChatML, ``<functions>`` in the system turn, Python-style calls (olmo3.go:27-158)
 olmo3-think (+32b)   ChatML, no tools, cue ends in ``<think>`` (olmo3_think.go:32-87)
 glm-4.6 / glm-4.7    ``<|user|>`` marks, calls as ``<arg_key>/<arg_value>`` pairs (glm46.go:17-113, glm47.go:43-108)
+cohere               Command turn marks, tool section and action / result lists as JSON (cohere.go:77-226)
 functiongemma        Gemma turns, declarations and calls in the ``call:name{k:v}`` notation (functiongemma.go:20-125)
 ===================  ==============================================================================================
 """
@@ -138,6 +139,8 @@ class Turn:
     thinking: str = ""
     calls: list[tuple[str, dict[str, Any]]] = field(default_factory=list)     # assistant: (function name, arguments)
     results: list[tuple[str, str]] = field(default_factory=list)              # tool: (name of the answered call, content)
+    call_ids: list[str] = field(default_factory=list)                         # assistant: the id each call travelled with ("" if none)
+    result_ids: list[str] = field(default_factory=list)                       # tool: the call id each result names
     images: int = 0
     pos: int = 0                                # index among the turns
     first_image: int = 0                        # number of images in the turns before this one
@@ -171,12 +174,14 @@ class Conversation:
                 if not self.turns or self.turns[-1].role != "tool":
                     self.turns.append(Turn("tool", pos=len(self.turns), first_image=images))
                 self.turns[-1].results.append((name, m.get("content") or ""))
+                self.turns[-1].result_ids.append(m.get("tool_call_id") or "")
                 continue
             t = Turn(role, m.get("content") or "", m.get("thinking") or "", pos=len(self.turns), first_image=images,
                      images=len(m.get("images") or []))
             for c in m.get("tool_calls") or []:
                 f = c.get("function") or {}
                 t.calls.append((f.get("name", ""), f.get("arguments") or {}))
+                t.call_ids.append(c.get("id") or "")
             if role == "assistant" and t.calls:
                 pending = [n for n, _ in t.calls]
             images += t.images
@@ -684,6 +689,66 @@ class DeepSeek31(DeepSeekMarks):
 
 
 # ---------------------------------------------------------------------------------------------------
+# Cohere
+# ---------------------------------------------------------------------------------------------------
+class Cohere(Dialect):
+    """Command models: turns between ``<|START_OF_TURN_TOKEN|><|ROLE_TOKEN|>`` and ``<|END_OF_TURN_TOKEN|>``, text between text
+    marks, a tool section in the system turn even when it is empty, calls as a JSON action list whose ids are the running
+    number of the call in the conversation, results as a JSON list in a system turn."""
+
+    bos = "<BOS_TOKEN>"
+    T0, T1 = "<|START_OF_TURN_TOKEN|>", "<|END_OF_TURN_TOKEN|>"
+
+    def render(self, messages, tools=None, think=None):
+        alias = {"chatbot": "assistant"}
+        messages = [{**m, "role": alias.get(str(m.get("role", "")).lower(), str(m.get("role", "")).lower())} for m in messages]
+        return super().render(messages, tools, think)
+
+    def prepare(self, x: Ctx) -> None:
+        x.memo["numbers"], x.memo["next"] = {}, 0
+
+    def text_turn(self, who: str, text: str) -> str:
+        return f"{self.T0}<|{who}_TOKEN|><|START_TEXT|>{text}<|END_TEXT|>{self.T1}"
+
+    def head(self, x: Ctx) -> str:
+        entries = ['\n    {"name": ' + go_json(f.get("name", "")) + ', "description": ' + go_json(f.get("description", "")) + ', "parameters": '
+                   + go_json(parameters_schema(f.get("parameters")), spaced=True) + ', "responses": null}' for f in (t.get("function") or {} for t in x.tools)]
+        listing = ",\n\n".join(entries) + "\n\n" if entries else "\n\n"
+        sys = x.conv.system_text
+        return self.text_turn("SYSTEM", (sys + "\n\n\n\n" if sys else "") + "# Available Tools\n```json\n[\n" + listing + "\n]\n```")
+
+    def turn_system(self, t: Turn, x: Ctx) -> str:
+        return self.text_turn("SYSTEM", t.content)
+
+    def turn_user(self, t: Turn, x: Ctx) -> str:
+        return self.text_turn("USER", t.content)
+
+    def turn_assistant(self, t: Turn, x: Ctx) -> str:
+        out = f"{self.T0}<|CHATBOT_TOKEN|>"
+        thinking = f"<|START_THINKING|>{t.thinking}<|END_THINKING|>" if t.thinking else ""
+        if t.calls:
+            actions = []
+            for (name, args), cid in zip(t.calls, t.call_ids):
+                number = str(x.memo["next"])
+                x.memo["next"] += 1
+                if cid:
+                    x.memo["numbers"].setdefault(cid, number)
+                actions.append('\n\n    {"tool_call_id": "' + number + '", "tool_name": "' + name + '", "parameters": ' + args_json(args, spaced=True) + "}")
+            return out + "\n            \n                " + thinking + "<|START_ACTION|>[" + ",".join(actions) + "\n\n]<|END_ACTION|>" + self.T1
+        return out + thinking + "<|START_TEXT|>" + t.content + ("" if t is x.conv.last else "<|END_TEXT|>" + self.T1)
+
+    def turn_tool(self, t: Turn, x: Ctx) -> str:
+        items = ['\n    {\n        "tool_call_id": "' + x.memo["numbers"].get(rid, rid) + '",\n        "results": {\n\n            \n            "0": '
+                 + go_json({"content": c}, spaced=True) + '\n\n        },\n        "is_error": null\n    }' for (_, c), rid in zip(t.results, t.result_ids)]
+        return f"{self.T0}<|SYSTEM_TOKEN|><|START_TOOL_RESULT|>[" + ",".join(items) + "\n\n]<|END_TOOL_RESULT|>" + self.T1
+
+    def cue(self, x: Ctx) -> str:
+        if x.conv.continued is not None:
+            return ""
+        return f"{self.T0}<|CHATBOT_TOKEN|>" + ("<|START_THINKING|>" if think_on(x.think, True) else "<|START_THINKING|><|END_THINKING|>")
+
+
+# ---------------------------------------------------------------------------------------------------
 # GLM
 # ---------------------------------------------------------------------------------------------------
 def _glm_value(v: Any) -> str:
@@ -854,6 +919,7 @@ DIALECTS: dict[str, Callable[[], Dialect]] = {
     "glm-4.6": lambda: GLM(airy=True),
     "glm-4.7": lambda: GLM(airy=False),
     "functiongemma": FunctionGemma,
+    "cohere": Cohere,
 }
 
 

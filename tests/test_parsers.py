@@ -129,3 +129,36 @@ def test_qwen35_parser_cases():
     assert run(["</think>The final answer."])[:2] == ("The final answer.", "")
     assert run(["plain </think> text"], think=False)[:2] == ("plain </think> text", "") and run([" goes on"], prefill="It")[:2] == (" goes on", "")
     assert run(["abc</th", "ink>", "\n\n  ", "def"])[:2] == ("def", "abc") and run(["never closed"])[:2] == ("", "never closed")
+
+
+def test_cohere_parser_cases():
+    """model/parsers/cohere_test.go restated: reasoning up to the end mark, the answer inside text (or legacy response) marks or bare,
+    calls as a JSON action list that survives damaged entries, marks split over chunks, continuation of a prefilled answer."""
+    def run(chunks, think=None, prefill=""):
+        p = B.parser_for("cohere", None, think, prefill)
+        out = [p.add(c, i == len(chunks) - 1) for i, c in enumerate(chunks)]
+        return "".join(o[0] for o in out), "".join(o[1] for o in out), [k for o in out for k in o[2]]
+
+    assert run(["Let me think", " about this.<|END_THINKING|>", "<|START_TEXT|>Hello", " world!<|END_TEXT|>"]) == ("Hello world!", "Let me think about this.", [])
+    assert run(["think<|END_TH", "INKING|><|STAR", "T_TEXT|>ans", "wer<|END_", "TEXT|>"])[:2] == ("answer", "think")
+    c, t, k = run(["plan<|END_THINKING|><|START_ACTION|>[\n", '    {"tool_call_id": "0", "tool_name": "get_weather", "parameters": {"city": "Paris"}},',
+                   '    {"tool_call_id": "1", "tool_name": "get_time", "parameters": {}}', "\n]<|END_ACTION|>"])
+    assert (c, t) == ("", "plan") and [x["function"]["name"] for x in k] == ["get_weather", "get_time"] and k[0]["function"]["arguments"] == {"city": "Paris"} and k[1]["id"] == "1"
+    assert run(["<|START_TEXT|>direct answer<|END_TEXT|>"], think=False)[:2] == ("direct answer", "")
+    assert run(["thought<|END_THINKING|>", "Just plain text", " output"])[:2] == ("Just plain text output", "thought")
+    assert run(["t<|END_THINKING|><|START_TEXT|>answer<|END_OF_TURN_TOKEN|>"])[0] == "answer"
+    assert run([" continued<|END_TEXT|>"], prefill="partial")[:2] == (" continued", "")
+    k = run(["plan<|END_THINKING|><|START_ACTION|>[\n", '    {"tool_call_id": "0", "tool_name": "set_alarm", "parameters": {"time": 15:30}},',
+             '    {"tool_call_id": "1", "tool_name": "get_weather", "parameters": {"city": "Oslo"}}', "\n]<|END_ACTION|>"])[2]
+    assert [x["function"]["name"] for x in k] == ["get_weather"]
+    k = run(["<|END_THINKING|><|START_ACTION|>[", '{"tool_call_id": "0", "tool_name": "a", "parameters": {}}',
+             '{"tool_call_id": "1", "tool_name": "b", "parameters": {"x": "{not json}"}}', "]<|END_ACTION|>"])[2]
+    assert [x["function"]["name"] for x in k] == ["a", "b"] and k[1]["function"]["arguments"] == {"x": "{not json}"}
+    assert run(["x<|END_THINKING|><|START_ACTION|>[!!!]<|END_ACTION|>"])[2] == []
+    assert run(["plan<|END_THINKING|>", "<|START_RESPONSE|>Hello", " there<|END_RESPONSE|>"])[:2] == ("Hello there", "plan")
+    for chunk in ("<|START_RESPONSE|>The answer is 42.", "<|TOOL_PLAN|>I should call the tool.", "Just plain text."):
+        p = B.parser_for("cohere")
+        p.add("x<|END_THINKING|>", False)
+        assert p.add(chunk, False)[0] != ""                      # streams before the generation ends
+    assert run(["t<|END_THINKING|><|START_TEXT|>hi<|END_TEXT|><|END_OF_TURN_TOKEN|>"])[:2] == ("hi", "t")
+    assert run(["t<|END_THINKING|>plain answer<|END_OF_TURN_TOKEN|>"])[0] == "plain answer"

@@ -33,7 +33,7 @@ def test_renderer_reproduces_the_reference_prompts(name):
 
 def test_every_registered_renderer_has_cases_and_renders_an_empty_conversation():
     covered = {c["renderer"] for c in CASES}
-    assert covered >= set(R.DIALECTS) - {"olmo3.1", "qwen3.5", "qwen3.8", "ornith"}
+    assert covered >= set(R.DIALECTS) - {"olmo3.1", "qwen3.5", "qwen3.8", "ornith", "cohere", "lfm2", "lfm2-thinking", "nemotron-3-nano", "nemotron-3.5-nano"}   # these have tests of their own below
     for name in set(R.DIALECTS) - {"qwen3.8"}:
         assert isinstance(R.renderer_for(name).render([], None, None), str)
     assert R.renderer_for("olmo3.1").render([{"role": "user", "content": "hi"}]).startswith("<|im_start|>system\nYou are Olmo, a helpful AI assistant built by Ai2.")
@@ -125,3 +125,37 @@ def test_qwen35_family():
     orn = R.renderer_for("ornith")
     got = orn.render([{"role": "user", "content": "a"}, {"role": "assistant", "content": "b"}, {"role": "user", "content": "c"}], None, False)
     assert "<|im_start|>assistant\n<think>\n\n</think>\n\nb<|im_end|>" in got and got.endswith("<think>\n\n</think>\n\n")
+
+
+def test_cohere_renderer():
+    """model/renderers/cohere_test.go restated (expectations there come from the checkpoint's own Jinja template)."""
+    r = R.renderer_for("cohere")
+    T0, T1 = "<|START_OF_TURN_TOKEN|>", "<|END_OF_TURN_TOKEN|>"
+    no_tools = f"{T0}<|SYSTEM_TOKEN|><|START_TEXT|># Available Tools\n```json\n[\n\n\n\n]\n```<|END_TEXT|>{T1}"
+    user = lambda c: f"{T0}<|USER_TOKEN|><|START_TEXT|>{c}<|END_TEXT|>{T1}"      # noqa: E731
+    assert r.render([{"role": "user", "content": "USERMSG"}]) == no_tools + user("USERMSG") + f"{T0}<|CHATBOT_TOKEN|><|START_THINKING|>"
+    got = r.render([{"role": "system", "content": "DEVPREAMBLE"}, {"role": "user", "content": "Q1"}, {"role": "assistant", "content": "A1", "thinking": "THINK1"},
+                    {"role": "user", "content": "Q2"}])
+    assert got == (f"{T0}<|SYSTEM_TOKEN|><|START_TEXT|>DEVPREAMBLE\n\n\n\n# Available Tools\n```json\n[\n\n\n\n]\n```<|END_TEXT|>{T1}" + user("Q1")
+                   + f"{T0}<|CHATBOT_TOKEN|><|START_THINKING|>THINK1<|END_THINKING|><|START_TEXT|>A1<|END_TEXT|>{T1}" + user("Q2") + f"{T0}<|CHATBOT_TOKEN|><|START_THINKING|>")
+    assert r.render([{"role": "user", "content": "Q"}], None, False).endswith(f"{T0}<|CHATBOT_TOKEN|><|START_THINKING|><|END_THINKING|>")
+    tools = [{"type": "function", "function": {"name": "get_weather", "description": "Get weather",
+                                               "parameters": {"type": "object", "required": ["city"], "properties": {"city": {"type": "string"}}}}}]
+    got = r.render([{"role": "user", "content": "weather in Paris?"},
+                    {"role": "assistant", "thinking": "I should call the tool", "tool_calls": [{"id": "call_x", "function": {"name": "get_weather", "arguments": {"city": "Paris"}}}]},
+                    {"role": "tool", "tool_call_id": "call_x", "content": "15C sunny"}, {"role": "user", "content": "thanks"}], tools)
+    assert ('# Available Tools\n```json\n[\n\n    {"name": "get_weather", "description": "Get weather", "parameters": {"type": "object", "required": ["city"], '
+            '"properties": {"city": {"type": "string"}}}, "responses": null}\n\n\n]\n```') in got
+    assert (f'{T0}<|CHATBOT_TOKEN|>\n            \n                <|START_THINKING|>I should call the tool<|END_THINKING|><|START_ACTION|>[\n\n    '
+            f'{{"tool_call_id": "0", "tool_name": "get_weather", "parameters": {{"city": "Paris"}}}}\n\n]<|END_ACTION|>{T1}') in got
+    assert (f'{T0}<|SYSTEM_TOKEN|><|START_TOOL_RESULT|>[\n    {{\n        "tool_call_id": "0",\n        "results": {{\n\n            \n            "0": {{"content": "15C sunny"}}'
+            f'\n\n        }},\n        "is_error": null\n    }}\n\n]<|END_TOOL_RESULT|>{T1}') in got
+    got = r.render([{"role": "user", "content": "go"},
+                    {"role": "assistant", "tool_calls": [{"id": "a", "function": {"name": "t1", "arguments": {}}}, {"id": "b", "function": {"name": "t2", "arguments": {"x": 1}}}]},
+                    {"role": "tool", "tool_call_id": "a", "content": "r1"}, {"role": "tool", "tool_call_id": "b", "content": "r2"}])
+    assert ('<|START_ACTION|>[\n\n    {"tool_call_id": "0", "tool_name": "t1", "parameters": {}},\n\n    {"tool_call_id": "1", "tool_name": "t2", "parameters": {"x": 1}}\n\n]'
+            '<|END_ACTION|>') in got
+    assert ('<|START_TOOL_RESULT|>[\n    {\n        "tool_call_id": "0",\n        "results": {\n\n            \n            "0": {"content": "r1"}\n\n        },\n'
+            '        "is_error": null\n    },\n    {\n        "tool_call_id": "1",\n        "results": {\n\n            \n            "0": {"content": "r2"}\n\n        },\n'
+            '        "is_error": null\n    }\n\n]<|END_TOOL_RESULT|>') in got
+    assert r.render([{"role": "user", "content": "Q"}, {"role": "Chatbot", "content": "partial"}]).endswith(f"{T0}<|CHATBOT_TOKEN|><|START_TEXT|>partial")
