@@ -22,6 +22,7 @@ name                    reasoning block             tool call
 ``olmo3-think``         starts inside ``<think>``   none
 ``glm-4.6``             ``<think>..</think>``       ``<tool_call>name<arg_key>k</arg_key><arg_value>v</arg_value></tool_call>``
 ``glm-4.7``             starts inside ``<think>``   same
+``lfm2(-thinking)``     ``<think>..</think>``       ``<|tool_call_start|>[name(k='v'), ...]<|tool_call_end|>``
 ``cohere``              starts inside the block     JSON list of ``{"tool_call_id", "tool_name", "parameters"}`` between action marks
 ``passthrough``         none                        none
 ======================  ==========================  ================================================================
@@ -78,11 +79,12 @@ class TagStreamParser:
     """
 
     def __init__(self, *, think_open: str = "", think_close: str = "", start_thinking: bool = False, regions: list[Region] | None = None,
-                 call_ends_thinking: bool = False, keep_space: bool = False, drop_marks: dict[str, bool] | None = None):
+                 call_ends_thinking: bool = False, keep_space: bool = False, drop_marks: dict[str, bool] | None = None, trim_start: bool = False):
         self.think_open, self.think_close = think_open, think_close
         self.regions = [r for r in regions or [] if r.decode is not None or r.drop or r.unwrap]
         self.call_ends_thinking = call_ends_thinking    # a call that opens inside the reasoning block ends the block
         self.keep_space = keep_space                    # reasoning is handed on with the white space it ends in
+        self.trim_start = trim_start                    # white space that opens the reasoning block, or a message without one, goes
         self.drop_marks = dict(drop_marks or {})        # marks that only frame content: removed; True = white space after them goes too
         self.state: Any = "thinking" if start_thinking and think_close else "content"
         self.may_open_think = bool(think_open)          # an explicit opening tag is accepted at the very start only
@@ -135,6 +137,11 @@ class TagStreamParser:
                 self.may_open_think = False
             elif not done:
                 return False
+        if getattr(self, "lead_ws", False):
+            self.buf = self.buf.lstrip()
+            if not self.buf:
+                return False
+            self.lead_ws = False
         marks = [self.think_close] + ([r.open for r in self.regions] if self.call_ends_thinking else [])
         hit = self._first(marks)
         if hit is None:
@@ -163,6 +170,11 @@ class TagStreamParser:
             self.buf, self.skip_ws = self.buf[i + len(mark):], self.drop_marks[mark]
             return True
         if hit is None:
+            if self.trim_start and self.may_open_think:     # nothing but white space so far: it goes, whatever follows
+                t = self.buf.lstrip()
+                if not t or (self.think_open.startswith(t) and not done):
+                    return False
+                self.buf = t
             before = len(content)
             self._flush(content, marks, done)
             if "".join(content[before:]).strip():
@@ -175,6 +187,8 @@ class TagStreamParser:
                 self.may_open_think = False
                 return True
             self.buf, self.state, self.may_open_think = self.buf[i + len(mark):], "thinking", False
+            if self.trim_start:
+                self.lead_ws = True
             return True
         region = self._region(mark)
         content.append(before if region.unwrap else before.rstrip())
@@ -462,10 +476,14 @@ _KW = "kw__"
 _WORDS = {"true": True, "True": True, "false": False, "False": False, "null": None, "None": None, "nil": None}
 
 
-def _py_value(node: ast.AST, src: str) -> Any:
+def _py_value(node: ast.AST, src: str, raw: bool = False) -> Any:
     """Value of an argument expression: literals, lists and maps as written; the JSON and Python spellings of
     true / false / null; anything else (a bare word, an expression) is the text itself."""
     if isinstance(node, ast.Constant) and not isinstance(node.value, (bytes, complex)) and node.value is not Ellipsis:
+        if raw and isinstance(node.value, str):         # the text between the quotes as written, escapes untouched
+            seg = ast.get_source_segment(src, node) or ""
+            if len(seg) >= 2 and seg[0] in "'\"" and seg[-1] == seg[0] and not seg.startswith(seg[0] * 3):
+                return seg[1:-1]
         return node.value
     if isinstance(node, ast.Name) and node.id in _WORDS:
         return _WORDS[node.id]
@@ -473,9 +491,9 @@ def _py_value(node: ast.AST, src: str) -> Any:
             and isinstance(node.operand.value, (int, float)) and not isinstance(node.operand.value, bool):
         return -node.operand.value if isinstance(node.op, ast.USub) else node.operand.value
     if isinstance(node, (ast.List, ast.Tuple)):
-        return [_py_value(e, src) for e in node.elts]
+        return [_py_value(e, src, raw) for e in node.elts]
     if isinstance(node, ast.Dict) and all(k is not None for k in node.keys):
-        return {str(_py_value(k, src)): _py_value(v, src) for k, v in zip(node.keys, node.values)}
+        return {str(_py_value(k, src, raw)): _py_value(v, src, raw) for k, v in zip(node.keys, node.values)}
     return ast.get_source_segment(src, node) or ""
 
 
@@ -492,18 +510,43 @@ def _free_keywords(line: str) -> str:
     return line
 
 
+def _call_node(node: ast.AST, src: str, raw: bool = False) -> dict[str, Any] | None:
+    if not isinstance(node, ast.Call) or node.args or any(k.arg is None for k in node.keywords):
+        return None
+    name = node.func.id if isinstance(node.func, ast.Name) else (ast.get_source_segment(src, node.func) or "")
+    if not name:
+        return None
+    return {"function": {"name": name, "arguments": {k.arg.removeprefix(_KW): _py_value(k.value, src, raw) for k in node.keywords}}}
+
+
 def _pythonic_calls(body: str) -> list[dict[str, Any]] | None:
+    """One call per line."""
     calls = []
     for line in filter(None, map(str.strip, body.splitlines())):
         line = _free_keywords(line)
         try:
-            tree = ast.parse(line, mode="eval").body
+            call = _call_node(ast.parse(line, mode="eval").body, line)
         except (SyntaxError, ValueError):
             return None
-        if not isinstance(tree, ast.Call) or not isinstance(tree.func, ast.Name) or tree.args or any(k.arg is None for k in tree.keywords):
+        if call is None:
             return None
-        calls.append({"function": {"name": tree.func.id, "arguments": {k.arg.removeprefix(_KW): _py_value(k.value, line) for k in tree.keywords}}})
+        calls.append(call)
     return calls
+
+
+def _python_call_list(body: str) -> list[dict[str, Any]] | None:
+    """``[f(a='x'), g(n=1)]``, the same without brackets, or a single call; string values keep their escapes as written
+    (model/parsers/lfm2.go:377-470).  Call marks that the model repeated inside the body are ignored."""
+    for mark in ("<|tool_call_start|>", "<|tool_call_end|>"):
+        body = body.replace(mark, "")
+    src = _free_keywords(" ".join(body.strip().splitlines()))
+    try:
+        tree = ast.parse(src, mode="eval").body
+    except (SyntaxError, ValueError):
+        return None
+    nodes = tree.elts if isinstance(tree, (ast.List, ast.Tuple)) else [tree]
+    calls = [_call_node(n, src, raw=True) for n in nodes]
+    return None if not calls or any(c is None for c in calls) else calls
 
 
 # -- GLM: name, then <arg_key>/<arg_value> pairs; values typed by the tool's schema --------------------------------
@@ -565,7 +608,7 @@ def _cohere_actions(body: str) -> list[dict[str, Any]]:
 
 
 PARSERS = ("qwen3", "qwen3-thinking", "qwen3-coder", "qwen3.5", "ornith", "qwen3-vl-instruct", "qwen3-vl-thinking", "ministral", "functiongemma", "cogito", "deepseek3",
-           "olmo3", "olmo3-think", "glm-4.6", "glm-4.7", "cohere", "passthrough")
+           "olmo3", "olmo3-think", "glm-4.6", "glm-4.7", "cohere", "lfm2", "lfm2-thinking", "passthrough")
 
 
 def parser_for(name: str | None, tools: list[dict[str, Any]] | None = None, think: Any = None,
@@ -612,6 +655,11 @@ def parser_for(name: str | None, tools: list[dict[str, Any]] | None = None, thin
                             regions=[Region("<|START_ACTION|>", "<|END_ACTION|>", _cohere_actions)])
         p.skip_ws = fresh and p.state == "content"
         return p
+    if name in ("lfm2", "lfm2-thinking"):
+        # model/parsers/lfm2.go:62-82: a thinking variant that was asked to think may open a block with an explicit tag, or answer directly
+        may_think = name == "lfm2-thinking" and asked and fresh
+        return TagStreamParser(think_open="<think>" if may_think else "", think_close="</think>" if may_think else "", trim_start=may_think,
+                               regions=[Region("<|tool_call_start|>", "<|tool_call_end|>", _python_call_list)])
     if name == "olmo3":
         return TagStreamParser(regions=[Region("<function_calls>", "</function_calls>", _pythonic_calls)])
     if name == "olmo3-think":                                     # model/parsers/olmo3_think.go:43-55: the prompt always ends in <think>

@@ -21,6 +21,7 @@ deepseek3.1          DeepSeek marks, ``</think>`` closes an absent reasoning blo
 olmo3 / olmo3.1      ChatML, ``<functions>`` in the system turn, Python-style calls (olmo3.go:27-158)
 olmo3-think (+32b)   ChatML, no tools, cue ends in ``<think>`` (olmo3_think.go:32-87)
 glm-4.6 / glm-4.7    ``<|user|>`` marks, calls as ``<arg_key>/<arg_value>`` pairs (glm46.go:17-113, glm47.go:43-108)
+lfm2 / lfm2-thinking ChatML behind ``<|startoftext|>``, tool list in the system turn, Python-style call list (lfm2.go:222-335)
 cohere               Command turn marks, tool section and action / result lists as JSON (cohere.go:77-226)
 functiongemma        Gemma turns, declarations and calls in the ``call:name{k:v}`` notation (functiongemma.go:20-125)
 ===================  ==============================================================================================
@@ -50,11 +51,13 @@ def _plain(v: Any, sort: bool | None) -> Any:
     return v
 
 
-def go_json(v: Any, *, spaced: bool = False, indent: int | None = None, sort: bool | None = False) -> str:
+def go_json(v: Any, *, spaced: bool = False, indent: int | None = None, sort: bool | None = False, html: bool = True) -> str:
     """Compact JSON with ``<``, ``>``, ``&`` and the two Unicode line separators escaped, as Go's ``json.Marshal`` does;
     ``spaced`` puts one blank after every ``:`` and ``,`` outside strings, ``indent`` gives the multi-line form."""
     seps = None if indent is not None else ((", ", ": ") if spaced else (",", ":"))
     s = json.dumps(_plain(v, sort), ensure_ascii=False, separators=seps, indent=indent)
+    if not html:                                # an encoder with HTML escaping switched off
+        return s
     for ch, esc in (("<", "\\u003c"), (">", "\\u003e"), ("&", "\\u0026"), ("\u2028", "\\u2028"), ("\u2029", "\\u2029")):
         s = s.replace(ch, esc)
     return s
@@ -520,6 +523,63 @@ class Qwen35(Qwen3VL):
         return self.block("assistant", body, close=t is not x.conv.last)
 
 
+class LFM2(ChatML):
+    """ChatML behind ``<|startoftext|>``; tools as a JSON list in the system turn, calls as ``[name(k=json, ...)]`` between call
+    marks in front of the content, every tool result in a turn of its own between response marks.  Reasoning of stored turns
+    is cut away except in the last assistant turn, unless a thinking variant was asked to think."""
+
+    bos = "<|startoftext|>"
+
+    def __init__(self, thinking: bool, image_tags: bool = True):
+        self.thinking, self.image_tags = thinking, image_tags
+
+    def prepare(self, x: Ctx) -> None:
+        x.memo["keep"] = self.thinking and x.think is not None and think_on(x.think, False)
+        x.memo["last_assistant"] = max((t.pos for t in x.conv.turns if t.role == "assistant"), default=-1)
+
+    def text(self, t: Turn) -> str:
+        if not t.images:
+            return t.content
+        if self.image_tags:
+            return image_tagged(t.content, t.images, t.first_image)
+        return t.content if "<image>" in t.content else "<image>" * t.images + t.content
+
+    def head(self, x: Ctx) -> str:
+        sys = x.conv.system_text or ""
+        if x.tools:
+            listing = ", ".join(go_json(self.schema(t), spaced=True, html=False) for t in x.tools)
+            sys += ("\n" if sys else "") + "List of tools: <|tool_list_start|>[" + listing + "]<|tool_list_end|>"
+        return self.bos + (self.block("system", sys) if sys else "")
+
+    @staticmethod
+    def schema(tool: dict[str, Any]) -> dict[str, Any]:
+        full = tool_schema(tool)
+        return full["function"] if full["function"]["name"] else full
+
+    def turn_other(self, t: Turn, x: Ctx) -> str:
+        return self.block(t.role, self.text(t))
+
+    turn_user = turn_other
+
+    def turn_tool(self, t: Turn, x: Ctx) -> str:
+        return "".join(self.block("tool", c if "<|tool_response_start|>" in c else f"<|tool_response_start|>{c}<|tool_response_end|>") for _, c in t.results)
+
+    def turn_assistant(self, t: Turn, x: Ctx) -> str:
+        content = self.text(t)
+        if t.calls and "<|tool_call_start|>" not in content:
+            calls = ",".join(name + "(" + ",".join(f"{k}={go_json(args[k], spaced=True, html=False, sort=True)}" for k in sorted(args)) + ")" for name, args in t.calls)
+            content = "<|tool_call_start|>[" + calls + "]<|tool_call_end|>" + ("\n" + content if content.strip() else content)
+        if self.thinking and t.thinking and "</think>" not in content:
+            content = f"<think>{t.thinking}</think>{content}"
+        if not x.memo["keep"] and t.pos != x.memo["last_assistant"] and "</think>" in content:
+            content = content.rpartition("</think>")[2].strip()
+        return self.block("assistant", content, close=t is not x.conv.last)
+
+    def cue(self, x: Ctx) -> str:
+        last = x.conv.last
+        return "" if last is not None and last.role == "assistant" else f"{self.opener}assistant\n"
+
+
 _OLMO3_WITH_FUNCTIONS = ("You are provided with function signatures within <functions></functions> XML tags. You may call one or more functions to assist "
                          "with the user query. Output any function calls within <function_calls></function_calls> XML tags. Do not make assumptions about "
                          "what values to plug into functions.")
@@ -920,6 +980,8 @@ DIALECTS: dict[str, Callable[[], Dialect]] = {
     "glm-4.7": lambda: GLM(airy=False),
     "functiongemma": FunctionGemma,
     "cohere": Cohere,
+    "lfm2": lambda: LFM2(thinking=False),
+    "lfm2-thinking": lambda: LFM2(thinking=True),
 }
 
 

@@ -87,6 +87,12 @@ def test_single_call_bodies():
     for c in DATA["olmo3_values"]:
         got = B._pythonic_calls("f(x=" + c["text"] + ")")
         assert got is not None and _same(got[0]["function"]["arguments"]["x"], c["value"]), c["case"]
+    for c in DATA["lfm2_calls"]:
+        got = B._python_call_list(c["body"])
+        if c["error"]:
+            assert not got, c["case"]
+        else:
+            assert _same([{"name": k["function"]["name"], "arguments": k["function"]["arguments"]} for k in got or []], c["calls"]), c["case"]
     assert B._pythonic_calls('book(from="SFO", class="eco", to=None)')[0]["function"]["arguments"] == {"from": "SFO", "class": "eco", "to": None}
     assert B._pythonic_calls("not a call") is None and B._pythonic_calls("f(1, 2)") is None
     assert B._cogito_call("function<｜tool▁sep｜>w\n```json\n{\"a\": 1}\n```")["function"] == {"name": "w", "arguments": {"a": 1}}
