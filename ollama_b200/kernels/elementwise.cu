@@ -302,18 +302,23 @@ struct EmbedArgs {
     float* out;          // [nt][k]
 };
 
+// grid (tokens, slices): a slice is EMBED_SLICE consecutive elements of the row, so that one token's row is decoded by
+// several CTAs at once (a single CTA took 10-12 us for a 4096-wide Q4_K row)
+constexpr int EMBED_SLICE = 512;
+
 __global__ void __launch_bounds__(256) embed_kernel(const __grid_constant__ EmbedArgs a) {
     pdl_launch();
     pdl_wait();
     const int t = blockIdx.x;
     int row = a.ids[t];
     row = min(max(row, 0), a.table.n - 1);
-    for (int i = threadIdx.x; i < a.table.k; i += 256) a.out[(size_t)t * a.table.k + i] = a.scale * deq_elem(a.table, row, i);
+    const int lo = blockIdx.y * EMBED_SLICE, hi = min(a.table.k, lo + EMBED_SLICE);
+    for (int i = lo + threadIdx.x; i < hi; i += 256) a.out[(size_t)t * a.table.k + i] = a.scale * deq_elem(a.table, row, i);
 }
 
 B2_API int b2_embed(const EmbedArgs* a, int nt, cudaStream_t st) {
     EmbedArgs copy = *a;
-    embed_kernel<<<nt, 256, 0, st>>>(copy);
+    embed_kernel<<<dim3((unsigned)nt, (unsigned)((a->table.k + EMBED_SLICE - 1) / EMBED_SLICE)), 256, 0, st>>>(copy);
     return (int)cudaGetLastError();
 }
 
@@ -341,13 +346,27 @@ B2_API int b2_dequant_rows(const DequantArgs* a, cudaStream_t st) {
 // ---------------------------------------------------------------------------------------------
 // arg-max over the vocabulary, one CTA per row; optional soft-cap is monotonic so it is skipped
 // ---------------------------------------------------------------------------------------------
-__global__ void __launch_bounds__(1024) argmax_kernel(const float* logits, int n, int ld, int* out) {
+// One CTA per row.  The row is read as float4 with eight loads in flight per thread; ties go to the lowest index.  With
+// `tokens` the winner is also fed back as the next step's input token and the row's position advances (the decode loop's
+// bookkeeping, otherwise a launch of its own).
+__global__ void __launch_bounds__(1024) argmax_kernel(const float* logits, int n, int ld, int* out, int* tokens, int* positions) {
     pdl_launch();
     pdl_wait();
     const float* x = logits + (size_t)blockIdx.x * ld;
     float best = -INFINITY;
     int bi = 0x7fffffff;
-    for (int i = threadIdx.x; i < n; i += 1024) {
+    const int n4 = (((uintptr_t)x & 15) == 0) ? n >> 2 : 0;
+    const float4* x4 = reinterpret_cast<const float4*>(x);
+#pragma unroll 8
+    for (int i = threadIdx.x; i < n4; i += 1024) {
+        const float4 v = __ldcs(x4 + i);
+        const int e = 4 * i;
+        if (v.x > best) { best = v.x; bi = e; }
+        if (v.y > best) { best = v.y; bi = e + 1; }
+        if (v.z > best) { best = v.z; bi = e + 2; }
+        if (v.w > best) { best = v.w; bi = e + 3; }
+    }
+    for (int i = 4 * n4 + threadIdx.x; i < n; i += 1024) {
         const float v = x[i];
         if (v > best) { best = v; bi = i; }
     }
@@ -369,12 +388,25 @@ __global__ void __launch_bounds__(1024) argmax_kernel(const float* logits, int n
             const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
             if (ov > best || (ov == best && oi < bi)) { best = ov; bi = oi; }
         }
-        if (threadIdx.x == 0) out[blockIdx.x] = bi;
+        if (threadIdx.x == 0) {
+            out[blockIdx.x] = bi;
+            if (tokens) {
+                tokens[blockIdx.x] = bi;
+                positions[blockIdx.x] += 1;
+            }
+        }
     }
 }
 
 B2_API int b2_argmax(const float* logits, int rows, int n, int ld, int* out, cudaStream_t st) {
-    argmax_kernel<<<rows, 1024, 0, st>>>(logits, n, ld, out);
+    argmax_kernel<<<rows, 1024, 0, st>>>(logits, n, ld, out, nullptr, nullptr);
+    return (int)cudaGetLastError();
+}
+
+// arg-max of every row, and the row's token / position advanced for the next decode step, in one launch
+B2_API int b2_argmax_advance(const float* logits, int rows, int n, int ld, int* out, int* tokens, int* positions, cudaStream_t st) {
+    if (!tokens || !positions) return (int)cudaErrorInvalidValue;
+    argmax_kernel<<<rows, 1024, 0, st>>>(logits, n, ld, out, tokens, positions);
     return (int)cudaGetLastError();
 }
 

@@ -841,12 +841,26 @@ __global__ void __launch_bounds__(SK_THREADS, NT == 1 ? 2 : 1) gemv_sk_kernel(co
     }
 }
 
+// One CTA per token row when the row is normalised first (the row's sum of squares is needed before any element can be
+// scaled); without a norm the 256-blocks are independent and a row is spread over gridDim.y CTAs of up to eight blocks each,
+// one block per warp, so a 14336-wide row takes one trip to L2 instead of seven.
+constexpr int Q256_CHUNK = 8;      // 256-blocks per CTA in the spread form
+
 __global__ void __launch_bounds__(256) quant256_kernel(const __grid_constant__ Quant256Args a) {
     __shared__ float ssq[256];
     pdl_launch();
     pdl_wait();
-    quantise_rows<8>(a.x + (size_t)blockIdx.x * a.ldx, a.ldx, a.norm_w, a.eps, a.k, 1, a.xq + (size_t)blockIdx.x * a.k, a.k,
-                  a.xd + (size_t)blockIdx.x * (a.k >> 8), a.xbs ? a.xbs + (size_t)blockIdx.x * (a.k >> 5) : nullptr, ssq, a.perm != 0);
+    const size_t row = blockIdx.x;
+    const int blk0 = blockIdx.y * Q256_CHUNK, nkb = a.k >> 8;
+    if (gridDim.y == 1) {
+        quantise_rows<8>(a.x + row * a.ldx, a.ldx, a.norm_w, a.eps, a.k, 1, a.xq + row * a.k, a.k, a.xd + row * nkb,
+                      a.xbs ? a.xbs + row * (a.k >> 5) : nullptr, ssq, a.perm != 0);
+        return;
+    }
+    if (blk0 >= nkb) return;
+    const int kc = min(Q256_CHUNK, nkb - blk0) << 8;        // this CTA's slice of the row; norm_w is null here
+    quantise_rows<8>(a.x + row * a.ldx + (size_t)blk0 * 256, a.ldx, nullptr, a.eps, kc, 1, a.xq + row * a.k + (size_t)blk0 * 256, a.k,
+                  a.xd + row * nkb + blk0, a.xbs ? a.xbs + row * (a.k >> 5) + blk0 * 8 : nullptr, ssq, a.perm != 0);
 }
 
 int g_sm_count[64] = {};
@@ -999,5 +1013,7 @@ B2_API int b2_quant256(const Quant256Args* a, int nb, int pdl, cudaStream_t st) 
     if (nb < 1 || (a->k & 255) || (a->ldx & 3) || ((uintptr_t)a->x & 15)) return (int)cudaErrorInvalidValue;
     Quant256Args copy = *a;
     void* args[] = {&copy};
-    return (int)launch((const void*)quant256_kernel, dim3((unsigned)nb), dim3(256), 0, args, st, pdl);
+    const int nkb = a->k >> 8;
+    const unsigned chunks = a->norm_w ? 1u : (unsigned)((nkb + Q256_CHUNK - 1) / Q256_CHUNK);
+    return (int)launch((const void*)quant256_kernel, dim3((unsigned)nb, chunks), dim3(256), 0, args, st, pdl);
 }

@@ -323,10 +323,17 @@ def embed(table: DevWeight, ids: torch.Tensor, scale: float = 1.0, out: torch.Te
     return out
 
 
-def argmax(logits: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
+def argmax(logits: torch.Tensor, out: torch.Tensor | None = None, tokens: torch.Tensor | None = None,
+           positions: torch.Tensor | None = None) -> torch.Tensor:
+    """Arg-max of every row (ties: lowest index).  With ``tokens`` and ``positions`` (int32, one per row) the winner also
+    becomes the row's next input token and its position advances by one, in the same launch."""
     rows, n = logits.shape
     if out is None:
         out = torch.empty(rows, device=logits.device, dtype=torch.int32)
+    if tokens is not None:
+        lib().b2_argmax_advance.argtypes = [C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p]
+        _check(lib().b2_argmax_advance(ptr(logits), rows, n, logits.stride(0), ptr(out), ptr(tokens), ptr(positions), stream()), "argmax")
+        return out
     lib().b2_argmax.argtypes = [C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_void_p, C.c_void_p]
     _check(lib().b2_argmax(ptr(logits), rows, n, logits.stride(0), ptr(out), stream()), "argmax")
     return out

@@ -265,11 +265,8 @@ class TPBackend(B200Backend):
         self.region.wait(CH_LOGITS, self.pdl)
         self._n += 1
         if want_argmax:
-            K.argmax(b.logits[:nb], out=b.sampled)
-            self._n += 1
-        if want_argmax == "loop":
-            lib.b2_advance.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_void_p]
-            K._check(lib.b2_advance(K.ptr(b.tokens), K.ptr(b.positions), K.ptr(b.sampled), nb, st()), "advance")
+            loop = want_argmax == "loop"      # the winner is fed back on the device: no host round trip between steps
+            K.argmax(b.logits[:nb], out=b.sampled, tokens=b.tokens if loop else None, positions=b.positions if loop else None)
             self._n += 1
         self.launches_per_step = self._n
 
