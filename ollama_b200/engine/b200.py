@@ -96,6 +96,7 @@ class B200Backend:
         # Decode matrices in unit order for the streaming GEMV (Q4_K / Q6_K layers without experts or sandwich norms); B200_SK=0
         # keeps every layer on the dp4a kernels.
         # Subclasses that enqueue their own decode kernels (tensor parallelism) keep the dp4a planes.
+        self.fuse_rope = os.environ.get("B200_FUSE_ROPE", "1") != "0"      # decode attention rotates Q / K and appends K / V itself
         self.use_sk = os.environ.get("B200_SK", "1") != "0" and not self.cfg.sandwich_norm and type(self) is B200Backend
         self.max_batch = MAX_DECODE_BATCH
         self.fuse_attn_combine = False    # one launch (last CTA merges the splits) measured slower than two launches joined by PDL
@@ -413,19 +414,33 @@ class B200Backend:
         c, b, lib, st = self.cfg, self.buf, K.lib(), K.stream
         self._sk(L.sk.qkv, b.x, b.qkv, nb, norm_w=L.attn_norm)
         local = L.swa and c.rope_base_local > 0
-        ra = K.RopeKvArgs(K.ptr(b.qkv), K.ptr(b.positions), K.ptr(b.slots), K.ptr(self.inv_freq_local if local else self.inv_freq),
-                          K.ptr(L.q_norm), K.ptr(L.k_norm), c.norm_eps, 1.0 if local else self.mscale, c.n_heads, c.n_kv_heads,
-                          c.head_dim, c.rope_dim, int(c.rope_style == "neox"), self.n_ctx, K.ptr(b.q), K.ptr(self.k_cache[i]),
-                          K.ptr(self.v_cache[i]), K.ptr(self.k_scale[i]), K.ptr(self.v_scale[i]))
-        K._check(lib.b2_rope_kv(C.byref(ra), nb, int(self.pdl), st()), "rope_kv")
-        aa = K.AttnDecodeArgs(K.ptr(b.q), K.ptr(self.k_cache[i]), K.ptr(self.v_cache[i]), K.ptr(b.positions), K.ptr(b.slots),
+        inv_freq, mscale = (self.inv_freq_local, 1.0) if local else (self.inv_freq, self.mscale)
+        ca = K.AttnCombineArgs(K.ptr(b.part_acc), K.ptr(b.part_ml), K.ptr(L.sinks), c.n_heads, self.n_splits, c.head_dim,
+                               K.ptr(b.ao), None, None)
+        fused = self.fuse_rope and L.q_norm is None and L.k_norm is None and self.k_scale[i] is None
+        aa = K.AttnDecodeArgs(None if fused else K.ptr(b.q), K.ptr(self.k_cache[i]), K.ptr(self.v_cache[i]), K.ptr(b.positions), K.ptr(b.slots),
                               c.n_heads, c.n_kv_heads, self.n_ctx, self.n_splits, self.attn_scale, c.attn_softcap,
                               c.sliding_window if L.swa else 0, K.ptr(b.part_acc), K.ptr(b.part_ml), K.ptr(self.k_scale[i]),
                               K.ptr(self.v_scale[i]))
-        ca = K.AttnCombineArgs(K.ptr(b.part_acc), K.ptr(b.part_ml), K.ptr(L.sinks), c.n_heads, self.n_splits, c.head_dim,
-                               K.ptr(b.ao), None, None)
-        K._check(lib.b2_attn_decode(C.byref(aa), C.byref(ca), nb, c.head_dim, int(self.pdl), st()), "attn_decode")
-        self._n += 3
+        if fused:
+            # rotary embedding of the queries, rotation + cache append of the new key / value and the attention in one launch
+            rr = K.AttnRopeArgs(K.ptr(b.qkv), K.ptr(inv_freq), mscale, c.rope_dim, int(c.rope_style == "neox"))
+            lib.b2_attn_decode_rope.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_void_p]
+            rc = lib.b2_attn_decode_rope(C.byref(aa), C.byref(rr), C.byref(ca), nb, c.head_dim, int(self.pdl), st())
+            if rc == 801:               # cudaErrorNotSupported: nothing was launched; this model keeps the separate kernel
+                self.fuse_rope = fused = False
+                aa.q = K.ptr(b.q)
+            else:
+                K._check(rc, "attn_decode_rope")
+                self._n += 2
+        if not fused:
+            ra = K.RopeKvArgs(K.ptr(b.qkv), K.ptr(b.positions), K.ptr(b.slots), K.ptr(inv_freq),
+                              K.ptr(L.q_norm), K.ptr(L.k_norm), c.norm_eps, mscale, c.n_heads, c.n_kv_heads,
+                              c.head_dim, c.rope_dim, int(c.rope_style == "neox"), self.n_ctx, K.ptr(b.q), K.ptr(self.k_cache[i]),
+                              K.ptr(self.v_cache[i]), K.ptr(self.k_scale[i]), K.ptr(self.v_scale[i]))
+            K._check(lib.b2_rope_kv(C.byref(ra), nb, int(self.pdl), st()), "rope_kv")
+            K._check(lib.b2_attn_decode(C.byref(aa), C.byref(ca), nb, c.head_dim, int(self.pdl), st()), "attn_decode")
+            self._n += 3
         self._sk([L.sk.o], b.ao, b.x, nb, mode=SK.MODE_ACCUM)
         self._sk([L.sk.gu], b.x, b.hf, nb, norm_w=L.ffn_norm, mode=SK.MODE_GLU)
         self._sk([L.sk.down], b.hf, b.x, nb, mode=SK.MODE_ACCUM)

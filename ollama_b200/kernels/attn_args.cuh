@@ -17,6 +17,20 @@ struct AttnDecodeArgs {
     const __half* v_scale;
 };
 
+// Optional second argument of the tensor-core kernel: with `qkv` set the kernel takes the query rows straight from the
+// projection output and rotates them itself, and the CTA whose split holds the query's own position rotates the new key,
+// appends key and value to the cache (f16 caches only) and uses them from shared memory, so that no rotary-embedding launch
+// precedes the attention.
+struct AttnRopeArgs {
+    const float* qkv;        // [nb][(H + 2 Hkv) * HD] raw projections (q | k | v), or null: q comes rotated from a.q
+    const float* inv_freq;   // [n_rot / 2]
+    float mscale;
+    int n_rot, neox;
+};
+
 // Tensor-core variant (attn_decode_mma.cu): same partial outputs, so the same combine kernel follows.
 // Returns cudaErrorNotSupported for shapes it does not take (head size other than 64 / 128, more than 16 query heads per KV head).
 int attn_decode_mma_launch(const AttnDecodeArgs& a, int nb, int hd, int pdl, cudaStream_t st);
+// The same with the rotary embedding and the cache append inside; cudaErrorNotSupported also for quantised caches and more
+// than 256 rotated dimensions.
+int attn_decode_mma_rope_launch(const AttnDecodeArgs& a, const AttnRopeArgs& r, int nb, int hd, int pdl, cudaStream_t st);

@@ -318,6 +318,19 @@ B2_API int b2_attn_decode(const AttnDecodeArgs* a, const AttnCombineArgs* c, int
     return (int)launch1((const void*)attn_combine_kernel, dim3(a->n_heads, nb), dim3(hd), args2, st, pdl);
 }
 
+// Split-K attention on raw projections: rotary embedding of the queries, rotation + cache append of the new key / value and the
+// attention itself in one launch (tensor-core kernel only), then the merge of the splits.  Returns cudaErrorNotSupported
+// (nothing launched) for shapes, cache encodings or rotary settings that kernel does not take: the caller then runs
+// b2_rope_kv + b2_attn_decode.
+B2_API int b2_attn_decode_rope(const AttnDecodeArgs* a, const AttnRopeArgs* r, const AttnCombineArgs* c, int nb, int hd, int pdl, cudaStream_t st) {
+    if (!r || !r->qkv) return (int)cudaErrorInvalidValue;
+    const cudaError_t e = (cudaError_t)attn_decode_mma_rope_launch(*a, *r, nb, hd, pdl, st);
+    if (e != cudaSuccess) return (int)e;
+    AttnCombineArgs cc = *c;
+    void* args2[] = {&cc};
+    return (int)launch1((const void*)attn_combine_kernel, dim3(a->n_heads, nb), dim3(hd), args2, st, pdl);
+}
+
 // One launch: split-K attention with the merge of the splits done by the last CTA of every head group.
 // `tickets`: nb * n_kv_heads * (group / G) zero-initialised counters (at most nb * n_heads).
 B2_API int b2_attn_decode_fused(const AttnDecodeArgs* a, const AttnCombineArgs* c, unsigned* tickets, int nb, int hd, int pdl, cudaStream_t st) {

@@ -35,13 +35,15 @@ __device__ __forceinline__ uint32_t pack_half2(float a, float b) {
 }
 
 template <int D>
-__global__ void __launch_bounds__(128) attn_decode_mma_kernel(const __grid_constant__ AttnDecodeArgs a) {
+__global__ void __launch_bounds__(128) attn_decode_mma_kernel(const __grid_constant__ AttnDecodeArgs a, const __grid_constant__ AttnRopeArgs r) {
     constexpr int LD = D + PAD;
     extern __shared__ __align__(16) unsigned char smem_raw[];
     __half* sQ = reinterpret_cast<__half*>(smem_raw);            // [ROWS][LD]
     __half* sK = sQ + ROWS * LD;                                 // [2][BN][LD]
     __half* sV = sK + 2 * BN * LD;                               // [2][BN][LD]
     __shared__ float s_m[4][ROWS], s_l[4][ROWS];
+    __shared__ float s_cs[128], s_sn[128];                        // cos / sin of the query position per rotated pair (fused form)
+    __shared__ __half s_newk[D], s_newv[D];                       // the query token's own key and value rows (fused form, owning split)
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, tq = lane & 3;
     const int split = blockIdx.x, kvh = blockIdx.y, b = blockIdx.z;
     const int group = a.n_heads / a.n_kv_heads;                  // query heads per KV head (<= ROWS, checked by the launcher)
@@ -101,12 +103,67 @@ __global__ void __launch_bounds__(128) attn_decode_mma_kernel(const __grid_const
     };
 
     if (n_tiles > 0) load_kv(0, 0);
-    // Q rows: the heads of this KV head, fp32 -> f16, rows beyond the group are zero
-    for (int c = tid; c < ROWS * (D / 4); c += 128) {
-        const int r = c / (D / 4), col = (c % (D / 4)) * 4;
-        float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
-        if (r < group) v = *(const float4*)(a.q + ((size_t)b * a.n_heads + head0 + r) * D + col);
-        *reinterpret_cast<uint2*>(sQ + r * LD + col) = make_uint2(pack_half2(v.x, v.y), pack_half2(v.z, v.w));
+    const bool fresh = r.qkv != nullptr;
+    const bool owner = fresh && n_tiles > 0 && qpos >= p0 && qpos < p1;      // this split holds the query token's own position
+    // element i of a raw head row after the rotary embedding (pairs (2p, 2p+1), or (p, p + n_rot/2) in the neox order)
+    auto rotated = [&](const float* row, int i) -> float {
+        const float x = row[i];
+        if (i >= r.n_rot) return x;
+        const int half_rot = r.n_rot >> 1;
+        const bool first = r.neox ? i < half_rot : !(i & 1);
+        const int p = r.neox ? (first ? i : i - half_rot) : i >> 1;
+        const float y = row[r.neox ? (first ? i + half_rot : i - half_rot) : (i ^ 1)];
+        return first ? x * s_cs[p] - y * s_sn[p] : y * s_sn[p] + x * s_cs[p];
+    };
+    if (fresh) {
+        // the raw rows (query heads of this group, the key and the value) are staged in the second K stage, which stays unused
+        // until the tile loop requests tile 1; cos / sin of the position are computed once per CTA meanwhile
+        float* raw = reinterpret_cast<float*>(sK + BN * LD);                  // [group + 2][D]
+        const float* tok = r.qkv + (size_t)b * (a.n_heads + 2 * a.n_kv_heads) * D;
+        const int nrows = group + (owner ? 2 : 0);
+        for (int c = tid; c < nrows * (D / 4); c += 128) {
+            const int rr = c / (D / 4), col = (c % (D / 4)) * 4;
+            const float* src = rr < group ? tok + (size_t)(head0 + rr) * D
+                                          : tok + (size_t)(a.n_heads + (rr == group ? 0 : a.n_kv_heads) + kvh) * D;
+            *reinterpret_cast<float4*>(raw + rr * D + col) = __ldcg(reinterpret_cast<const float4*>(src + col));
+        }
+        for (int p = tid; p < (r.n_rot >> 1); p += 128) {
+            float sn, cs;
+            sincosf((float)qpos * r.inv_freq[p], &sn, &cs);
+            s_sn[p] = sn * r.mscale;
+            s_cs[p] = cs * r.mscale;
+        }
+        __syncthreads();
+        if (owner) {      // append the new key / value rows to the cache and keep them for the last tile
+            const float* krow = raw + group * D;
+            const float* vrow = raw + (group + 1) * D;
+            __half* kc = const_cast<__half*>(a.k_cache) + (row0 + qpos) * D;
+            __half* vc = const_cast<__half*>(a.v_cache) + (row0 + qpos) * D;
+            for (int i = tid; i < D; i += 128) {
+                const __half kh = __float2half_rn(rotated(krow, i)), vh = __float2half_rn(vrow[i]);
+                s_newk[i] = kh;
+                s_newv[i] = vh;
+                kc[i] = kh;
+                vc[i] = vh;
+            }
+        }
+        for (int c = tid; c < ROWS * (D / 4); c += 128) {
+            const int rr = c / (D / 4), col = (c % (D / 4)) * 4;
+            float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (rr < group) {
+                const float* qrow = raw + rr * D;
+                v = make_float4(rotated(qrow, col), rotated(qrow, col + 1), rotated(qrow, col + 2), rotated(qrow, col + 3));
+            }
+            *reinterpret_cast<uint2*>(sQ + rr * LD + col) = make_uint2(pack_half2(v.x, v.y), pack_half2(v.z, v.w));
+        }
+    } else {
+        // Q rows: the heads of this KV head, fp32 -> f16, rows beyond the group are zero
+        for (int c = tid; c < ROWS * (D / 4); c += 128) {
+            const int rr = c / (D / 4), col = (c % (D / 4)) * 4;
+            float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (rr < group) v = *(const float4*)(a.q + ((size_t)b * a.n_heads + head0 + rr) * D + col);
+            *reinterpret_cast<uint2*>(sQ + rr * LD + col) = make_uint2(pack_half2(v.x, v.y), pack_half2(v.z, v.w));
+        }
     }
     __syncthreads();
     uint32_t qf[D / 16][4];
@@ -128,6 +185,14 @@ __global__ void __launch_bounds__(128) attn_decode_mma_kernel(const __grid_const
             asm volatile("cp.async.wait_group 0;" ::: "memory");
         }
         __syncthreads();
+        if (owner && tile == n_tiles - 1) {      // the query's own row did not come from the cache: put it into the tile
+            const int rr = qpos - (p0 + tile * BN);
+            for (int i = tid; i < D; i += 128) {
+                sK[stage * BN * LD + rr * LD + i] = s_newk[i];
+                sV[stage * BN * LD + rr * LD + i] = s_newv[i];
+            }
+            __syncthreads();
+        }
         const __half* tk = sK + stage * BN * LD + 16 * warp * LD;       // this warp's 16 positions of the tile
         const __half* tv = sV + stage * BN * LD + 16 * warp * LD;
         const int n0 = p0 + tile * BN + 16 * warp;
@@ -234,7 +299,7 @@ __global__ void __launch_bounds__(128) attn_decode_mma_kernel(const __grid_const
 }
 
 template <int D>
-int launch(const AttnDecodeArgs& a, int nb, int pdl, cudaStream_t st) {
+int launch(const AttnDecodeArgs& a, const AttnRopeArgs& r, int nb, int pdl, cudaStream_t st) {
     constexpr int SMEM = (ROWS + 4 * BN) * (D + PAD) * 2;
     static PerDeviceOnce once;
     if (once.first()) cudaFuncSetAttribute(attn_decode_mma_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM);
@@ -249,15 +314,22 @@ int launch(const AttnDecodeArgs& a, int nb, int pdl, cudaStream_t st) {
     cfg.attrs = at;
     cfg.numAttrs = 1;
     AttnDecodeArgs copy = a;
-    void* args[] = {&copy};
+    AttnRopeArgs rcopy = r;
+    void* args[] = {&copy, &rcopy};
     return (int)cudaLaunchKernelExC(&cfg, (const void*)attn_decode_mma_kernel<D>, args);
 }
 
 }  // namespace
 
-int attn_decode_mma_launch(const AttnDecodeArgs& a, int nb, int hd, int pdl, cudaStream_t st) {
+int attn_decode_mma_rope_launch(const AttnDecodeArgs& a, const AttnRopeArgs& r, int nb, int hd, int pdl, cudaStream_t st) {
     if (a.n_kv_heads < 1 || a.n_heads % a.n_kv_heads || a.n_heads / a.n_kv_heads > ROWS) return (int)cudaErrorNotSupported;
-    if (hd == 128) return launch<128>(a, nb, pdl, st);
-    if (hd == 64) return launch<64>(a, nb, pdl, st);
+    if (r.qkv && (a.k_scale || a.v_scale || r.n_rot > 256 || r.n_rot > hd || (r.n_rot & 1) || !r.inv_freq)) return (int)cudaErrorNotSupported;
+    if (hd == 128) return launch<128>(a, r, nb, pdl, st);
+    if (hd == 64) return launch<64>(a, r, nb, pdl, st);
     return (int)cudaErrorNotSupported;
+}
+
+int attn_decode_mma_launch(const AttnDecodeArgs& a, int nb, int hd, int pdl, cudaStream_t st) {
+    const AttnRopeArgs none = {};
+    return attn_decode_mma_rope_launch(a, none, nb, hd, pdl, st);
 }

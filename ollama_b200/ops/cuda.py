@@ -123,6 +123,10 @@ class AttnDecodeArgs(C.Structure):
                 ("k_scale", C.c_void_p), ("v_scale", C.c_void_p)]
 
 
+class AttnRopeArgs(C.Structure):
+    _fields_ = [("qkv", C.c_void_p), ("inv_freq", C.c_void_p), ("mscale", C.c_float), ("n_rot", C.c_int), ("neox", C.c_int)]
+
+
 class AttnCombineArgs(C.Structure):
     _fields_ = [("part_acc", C.c_void_p), ("part_ml", C.c_void_p), ("sinks", C.c_void_p), ("n_heads", C.c_int),
                 ("n_splits", C.c_int), ("hd", C.c_int), ("out", C.c_void_p), ("out_q", C.c_void_p), ("out_ds", C.c_void_p)]
@@ -378,6 +382,31 @@ def attn_decode(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, p
     c = AttnCombineArgs(ptr(scratch[0]), ptr(scratch[1]), ptr(sinks), H, n_splits, hd, ptr(out), ptr(oq), ptr(ods))
     _check(lib().b2_attn_decode(C.byref(a), C.byref(c), nb, hd, int(pdl), stream()), "attn_decode")
     return out, (QAct(oq, ods, out) if quant_out else None)
+
+
+def attn_decode_rope(qkv: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, positions: torch.Tensor, slots: torch.Tensor,
+                     inv_freq: torch.Tensor, *, n_heads: int, n_rot: int, neox: bool, mscale: float, scale: float, n_splits: int,
+                     window: int = 0, softcap: float = 0.0, sinks: torch.Tensor | None = None, pdl: bool = False) -> torch.Tensor | None:
+    """Decode attention on raw projections ``qkv`` [nb, (H + 2 Hkv) * hd]: the kernel rotates the queries and the new key,
+    appends key and value to the f16 caches at ``positions`` and attends over positions 0..position.  Returns the output
+    [nb, H * hd], or None when the tensor-core kernel does not take the shape (nothing was launched)."""
+    nb = qkv.shape[0]
+    Hkv, n_ctx, hd = k_cache.shape[1], k_cache.shape[2], k_cache.shape[3]
+    dev = qkv.device
+    acc = torch.empty(nb * n_heads * n_splits * hd, device=dev, dtype=torch.float32)
+    ml = torch.empty(nb * n_heads * n_splits * 2, device=dev, dtype=torch.float32)
+    out = torch.empty(nb, n_heads * hd, device=dev, dtype=torch.float32)
+    a = AttnDecodeArgs(None, ptr(k_cache), ptr(v_cache), ptr(positions), ptr(slots), n_heads, Hkv, n_ctx, n_splits, scale, softcap,
+                       window, ptr(acc), ptr(ml), None, None)
+    r = AttnRopeArgs(ptr(qkv), ptr(inv_freq), mscale, n_rot, int(neox))
+    c = AttnCombineArgs(ptr(acc), ptr(ml), ptr(sinks), n_heads, n_splits, hd, ptr(out), None, None)
+    f = lib().b2_attn_decode_rope
+    f.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_void_p]
+    rc = f(C.byref(a), C.byref(r), C.byref(c), nb, hd, int(pdl), stream())
+    if rc == 801:
+        return None
+    _check(rc, "attn_decode_rope")
+    return out
 
 
 def gemm_bf16(a: torch.Tensor, b: torch.Tensor, bias: torch.Tensor | None = None, out: torch.Tensor | None = None,

@@ -182,6 +182,38 @@ def test_attn_decode(hd, H, Hkv, window, softcap, use_sinks, mma, attn_mode):
         assert (deq - out.cpu()).abs().max() <= out.abs().max().item() / 127 + 1e-6
 
 
+@pytest.mark.parametrize("hd,H,Hkv,n_rot", [(128, 32, 8, 128), (64, 8, 4, 64), (128, 8, 2, 64), (64, 6, 3, 32)])
+@pytest.mark.parametrize("neox", [False, True])
+@pytest.mark.parametrize("window,n_splits", [(0, 1), (0, 4), (48, 4)])
+def test_attn_decode_with_rotary_embedding_and_cache_append_inside(hd, H, Hkv, n_rot, neox, window, n_splits, attn_mode):
+    """One launch that rotates Q and the new K, appends K / V and attends, against the two-kernel path (rope_kv, then the
+    tensor-core attention): same cache rows bit for bit, same output; sequences at position 0, inside a tile, on a tile edge."""
+    K = _K()
+    attn_mode(1)
+    n_slots, n_ctx, nb = 4, 320, 4
+    kc = (torch.randn(n_slots, Hkv, n_ctx, hd) * 0.5).to(torch.float16).cuda()
+    vc = (torch.randn(n_slots, Hkv, n_ctx, hd) * 0.5).to(torch.float16).cuda()
+    qkv = torch.randn(nb, (H + 2 * Hkv) * hd).cuda()
+    pos = torch.tensor([0, 63, 64, 300], dtype=torch.int32).cuda()
+    slots = torch.tensor([2, 0, 3, 1], dtype=torch.int32).cuda()
+    inv = (1.0 / (10000.0 ** (torch.arange(0, n_rot, 2).float() / n_rot))).cuda()
+    scale = 1 / math.sqrt(hd)
+    kc2, vc2 = kc.clone(), vc.clone()
+    q = K.rope_kv(qkv, pos, slots, inv, n_heads=H, n_kv_heads=Hkv, hd=hd, n_rot=n_rot, neox=neox, mscale=1.3, k_cache=kc, v_cache=vc)
+    want, _ = K.attn_decode(q, kc, vc, pos, slots, scale=scale, n_splits=n_splits, window=window, quant_out=False)
+    for b in range(nb):                                 # the fused launch must not depend on what the cache row held before
+        kc2[int(slots[b]), :, int(pos[b])] = float("nan")
+        vc2[int(slots[b]), :, int(pos[b])] = float("nan")
+    got = K.attn_decode_rope(qkv, kc2, vc2, pos, slots, inv, n_heads=H, n_rot=n_rot, neox=neox, mscale=1.3, scale=scale, n_splits=n_splits, window=window)
+    assert got is not None
+    torch.cuda.synchronize()
+    assert torch.equal(kc2, kc) and torch.equal(vc2, vc)
+    assert torch.allclose(got, want, atol=2e-3, rtol=2e-3), (got - want).abs().max()
+    # quantised caches and head sizes without a tensor-core instantiation are refused before anything is launched
+    assert K.attn_decode_rope(torch.randn(1, 3 * 256).cuda(), torch.zeros(1, 1, 32, 256, dtype=torch.float16).cuda(), torch.zeros(1, 1, 32, 256, dtype=torch.float16).cuda(),
+                              pos[:1], slots[:1] * 0, inv, n_heads=1, n_rot=64, neox=neox, mscale=1.0, scale=1.0, n_splits=1) is None
+
+
 @pytest.mark.parametrize("hd,H,Hkv", [(128, 32, 8), (64, 16, 2), (128, 16, 1)])
 @pytest.mark.parametrize("q8", [False, True])
 def test_attn_decode_tensor_core_long_context(hd, H, Hkv, q8, attn_mode):
