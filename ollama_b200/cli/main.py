@@ -548,12 +548,49 @@ def build_parser() -> argparse.ArgumentParser:
     p.add_argument("--format", default="benchstat", choices=["benchstat", "csv", "json"])
     p.set_defaults(fn=cmd_bench)
     sub.add_parser("gpu-discover", help="Print the devices this process can see as JSON").set_defaults(fn=cmd_gpu_discover)
+    p = sub.add_parser("launch", help="Launch a coding tool connected to this server")
+    p.add_argument("integration", nargs="?", help="claude, opencode, codex, droid (omit to pick from a list)")
+    p.add_argument("--model", default=None, help="model to use (omit to reuse the last choice or pick from a list)")
+    p.add_argument("--config", action="store_true", help="choose and save the model without starting the tool")
+    p.add_argument("--dry-run", action="store_true", help="print the command line and environment instead of running them")
+    p.set_defaults(fn=cmd_launch, extra=[])          # arguments after "--" go to the tool (split off in main)
     return ap
+
+
+def cmd_launch(args) -> int:
+    from .launch import launch
+    extra = list(args.extra or [])
+    return launch(Client(), args.integration, args.model, extra, choose_only=args.config, dry_run=args.dry_run)
+
+
+def interactive_menu() -> int:
+    """No command on a terminal: pick what to do (cmd/tui: the reference opens its launcher the same way)."""
+    from . import tui
+    from .launch import INTEGRATIONS, launch
+    items = [tui.Item("run", "Chat with a model")] + [tui.Item(i.name, i.description) for i in INTEGRATIONS if not i.hidden]
+    try:
+        what = tui.select("What would you like to do?", items)
+        if what != "run":
+            return launch(Client(), what, None, [])
+        models = [tui.Item(m["name"]) for m in Client().list().get("models", [])]
+        if not models:
+            print("No models are installed; pull one first (ollama pull <model>).", file=sys.stderr)
+            return 1
+        return main(["run", tui.select("Select a model:", models)])
+    except tui.Cancelled:
+        return 130
 
 
 def main(argv: list[str] | None = None) -> int:
     ap = build_parser()
+    argv = list(sys.argv[1:] if argv is None else argv)
+    passthrough: list[str] = []
+    if "launch" in argv[:1] and "--" in argv:
+        cut = argv.index("--")
+        argv, passthrough = argv[:cut], argv[cut + 1:]
     args = ap.parse_args(argv)
+    if passthrough:
+        args.extra = passthrough
     if args.version and not args.cmd:
         try:
             print(f"ollama-b200 version is {Client(timeout=2).version()}")
@@ -561,6 +598,12 @@ def main(argv: list[str] | None = None) -> int:
             print(f"Warning: could not connect to a running server\nclient version is {VERSION}")
         return 0
     if not args.cmd:
+        if sys.stdin.isatty() and sys.stdout.isatty():
+            try:
+                return interactive_menu()
+            except (ConnectionError, ResponseError) as e:
+                print(f"Error: {e}", file=sys.stderr)
+                return 1
         ap.print_help()
         return 0
     try:

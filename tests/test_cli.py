@@ -139,3 +139,66 @@ def test_repl_load_save_and_history(server, monkeypatch, tmp_path):
     assert off.entries == [] and not (tmp_path / "h3").exists()
     assert lineedit.complete("/s", "/s") == ["/set ", "/show ", "/save "] and lineedit.complete("no", "/set no") == ["nohistory ", "nowordwrap ", "noformat ", "nothink "]
     assert lineedit.complete("te", "/show te") == ["template"] and lineedit.complete("x", "hello x") == []
+
+
+def test_launch_wires_tools_to_the_server(server, monkeypatch, tmp_path):
+    """cmd/launch: environment of Claude Code (claude.go:63-83), overrides of Codex (codex.go:35-49, 174-204), inline configuration of
+    OpenCode (opencode.go:289-386), settings edit of Droid (droid.go:67-150), the saved choice (cmd/config/config.go) and the pickers."""
+    from ollama_b200.api.client import Client
+    from ollama_b200.cli import launch as L
+    from ollama_b200.cli import tui
+    run_cli("create", "tiny", "-f", str(server / "Modelfile"))
+    monkeypatch.setenv("HOME", str(tmp_path))
+    monkeypatch.setenv("OLLAMA_HOST", os.environ.get("OLLAMA_HOST", "127.0.0.1:11434"))
+    host = L.host_url()
+    assert host.startswith("http://127.0.0.1:")
+    env = L.claude_env("m1", [])
+    assert env["ANTHROPIC_BASE_URL"] == host and env["ANTHROPIC_AUTH_TOKEN"] == "ollama" and env["ANTHROPIC_DEFAULT_SONNET_MODEL"] == "m1" and env["ANTHROPIC_API_KEY"] == ""
+    args = L.codex_args("m1", ["exec", "hi"])
+    assert args[:2] == ["-c", 'model_provider="ollama-launch"'] and f'model_providers.ollama-launch.base_url="{host}/v1/"' in args and args[-4:] == ["-m", "m1", "exec", "hi"]
+    with pytest.raises(L.LaunchError):
+        L.codex_args("m1", ["-c", "model_providers.x.base_url=evil"])
+    cfg = json.loads(L.opencode_env("m1", [L.LaunchModel("m1", ["thinking", "vision"], 8192, 4096), L.LaunchModel("m2")])["OPENCODE_CONFIG_CONTENT"])
+    prov = cfg["provider"]["ollama"]
+    assert cfg["model"] == "ollama/m1" and prov["options"]["baseURL"] == host + "/v1" and prov["models"]["m1"]["limit"] == {"context": 8192, "output": 4096}
+    assert prov["models"]["m1"]["reasoning"] is True and prov["models"]["m1"]["modalities"]["input"] == ["text", "image"] and prov["models"]["m2"] == {"name": "m2"}
+    # droid: our entries replace those of an earlier launch and go in front of the user's own
+    sp = tmp_path / ".factory" / "settings.json"
+    sp.parent.mkdir()
+    sp.write_text(json.dumps({"theme": "dark", "customModels": [{"model": "old", "apiKey": "ollama"}, {"model": "mine", "apiKey": "sk-1"}],
+                              "sessionDefaultSettings": {"reasoningEffort": "turbo"}}))
+    L.droid_configure("m1", [L.LaunchModel("m1", ["vision"]), L.LaunchModel("m2", max_output_tokens=100)])
+    st = json.loads(sp.read_text())
+    assert [m["model"] for m in st["customModels"]] == ["m1", "m2", "mine"] and st["theme"] == "dark" and (tmp_path / ".factory" / "settings.json.bak").exists()
+    assert st["customModels"][0] == {"model": "m1", "displayName": "m1", "baseUrl": host + "/v1", "apiKey": "ollama", "provider": "generic-chat-completion-api",
+                                     "maxOutputTokens": 64000, "supportsImages": True, "id": "custom:m1-0", "index": 0}
+    assert st["customModels"][1]["maxOutputTokens"] == 100 and st["sessionDefaultSettings"] == {"reasoningEffort": "none", "model": "custom:m1-0"}
+    # the command: pick from the list (piped input), remember the choice, dry run, missing tool, unknown names
+    out = io.StringIO()
+    assert L.launch(Client(), None, None, [], choose_only=True, inp=io.StringIO("claude\ntiny\n"), out=out) == 0
+    assert L.saved_models("claude") == ["tiny:latest"] and "will use tiny:latest" in out.getvalue()
+    out = io.StringIO()
+    assert L.launch(Client(), "claude", None, ["-p", "hi"], dry_run=True, out=out) == 0
+    line = out.getvalue().strip().splitlines()[-1]
+    assert "ANTHROPIC_BASE_URL=" + host in line and line.endswith("claude --model tiny:latest -p hi")
+    ran = []
+    monkeypatch.setattr(L.Integration, "find", lambda self: "/usr/bin/" + self.binary)
+    assert L.launch(Client(), "codex", "tiny", [], run=lambda cmd, env: ran.append((cmd, env.get("OPENAI_API_KEY"))) or 0, out=io.StringIO()) == 0
+    assert ran[0][0][0] == "/usr/bin/codex" and ran[0][0][-2:] == ["-m", "tiny"] and ran[0][1] == "ollama"
+    monkeypatch.setattr(L.Integration, "find", lambda self: None)
+    out = io.StringIO()
+    assert L.launch(Client(), "droid", "tiny", [], out=out) == 1 and "Droid is not installed" in out.getvalue() and "ollama launch droid" in out.getvalue()
+    assert L.launch(Client(), "nope", "tiny", [], out=io.StringIO()) == 1 and L.launch(Client(), "claude", "absent", [], out=io.StringIO()) == 1
+    # selector keys
+    st = tui.SelectorState([tui.Item("alpha", "first"), tui.Item("beta"), tui.Item("gamma", "has alpha in its text")], height=2)
+    assert st.key("down") is None and st.current.name == "beta" and st.key("down") is None and st.current.name == "gamma" and st.offset == 1
+    for ch in "alp":
+        st.key(ch)
+    assert [i.name for i in st.visible] == ["alpha", "gamma"] and st.current.name == "alpha" and st.key("\r") == "pick"
+    st.key("x")
+    assert st.visible == [] and st.key("\r") is None and st.key("\x7f") is None and len(st.visible) == 2 and st.key("\x1b") == "cancel"
+    assert tui.confirm("ok?", inp=io.StringIO("y\n"), out=io.StringIO()) and not tui.confirm("ok?", inp=io.StringIO("\n"), out=io.StringIO())
+    with pytest.raises(tui.Cancelled):
+        tui.select("pick", [tui.Item("a")], inp=io.StringIO("zzz\n"), out=io.StringIO())
+    rc, _, err_text = run_cli("launch", "claude", "--model", "tiny", "--dry-run", "--", "--print", "hello")
+    assert rc == 0 and err_text.strip().endswith("claude --model tiny --print hello")
