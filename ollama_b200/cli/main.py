@@ -548,6 +548,12 @@ def build_parser() -> argparse.ArgumentParser:
     p.add_argument("--format", default="benchstat", choices=["benchstat", "csv", "json"])
     p.set_defaults(fn=cmd_bench)
     sub.add_parser("gpu-discover", help="Print the devices this process can see as JSON").set_defaults(fn=cmd_gpu_discover)
+    p = sub.add_parser("agent", help="Let a model work through tools (shell, files, skills) in this directory")
+    p.add_argument("model")
+    p.add_argument("prompt", nargs="*", help="one task; without it an interactive session starts")
+    p.add_argument("--yes", action="store_true", help="allow every tool call without asking")
+    p.add_argument("--skill", default="", help="load this skill before the first request")
+    p.set_defaults(fn=cmd_agent)
     p = sub.add_parser("launch", help="Launch a coding tool connected to this server")
     p.add_argument("integration", nargs="?", help="claude, opencode, codex, droid (omit to pick from a list)")
     p.add_argument("--model", default=None, help="model to use (omit to reuse the last choice or pick from a list)")
@@ -555,6 +561,64 @@ def build_parser() -> argparse.ArgumentParser:
     p.add_argument("--dry-run", action="store_true", help="print the command line and environment instead of running them")
     p.set_defaults(fn=cmd_launch, extra=[])          # arguments after "--" go to the tool (split off in main)
     return ap
+
+
+def cmd_agent(args) -> int:
+    """A model working through tools in this directory: every change (shell command, file write) is asked about first
+    unless ``--yes`` was given; "a" at the prompt allows that tool or exact command for the rest of the session."""
+    from ..agent import Approval, Session, default_registry
+    from ..agent.skills import SkillCatalog
+    c = Client()
+    info = c.show(args.model)
+    if "tools" not in (info.get("capabilities") or []):
+        print(f"Error: {args.model} does not support tools", file=sys.stderr)
+        return 1
+    ctx = next((int(v) for k, v in (info.get("model_info") or {}).items() if k.endswith(".context_length")), 0)
+
+    def chat(**req):
+        return c.request("POST", "/api/chat", req)
+
+    def approver(calls, cwd):
+        if args.yes:
+            return Approval(True, allow_all=True)
+        for k in calls:
+            print(f"\n{k['name']} wants to run in {cwd}:\n  {json.dumps(k['args'], ensure_ascii=False)[:500]}", file=sys.stderr)
+        print("Allow? [y]es / [a]lways for this / [n]o: ", end="", file=sys.stderr, flush=True)
+        ans = sys.stdin.readline().strip().lower()
+        if ans in ("a", "always"):
+            return Approval(True, allow_scopes=[k["scope"] for k in calls])
+        return Approval(ans in ("y", "yes"), reason="" if ans in ("y", "yes") else "declined at the prompt")
+
+    def events(kind, data):
+        if kind == "tool_start":
+            print(f"\x1b[90m> {data['name']} {json.dumps(data['args'], ensure_ascii=False)[:200]}\x1b[0m", file=sys.stderr)
+        elif kind in ("compacted", "denied"):
+            print(f"\x1b[90m[{kind}]\x1b[0m", file=sys.stderr)
+
+    skills = SkillCatalog()
+    s = Session(chat, default_registry(skills), approver=approver, events=events, context_window=ctx, skills=skills)
+    system = ("You are a coding assistant working in the user's directory through tools. Inspect before you change, make the smallest change "
+              "that does the job, and say what you did." + ("\nSkills you can load with the skill tool:\n" + skills.describe() if skills.names() else ""))
+    messages: list[dict[str, Any]] = []
+    prompts = [" ".join(args.prompt)] if args.prompt else None
+    while True:
+        if prompts is not None:
+            if not prompts:
+                return 0
+            text = prompts.pop(0)
+        else:
+            try:
+                text = input(">>> ").strip()
+            except (EOFError, KeyboardInterrupt):
+                print()
+                return 0
+            if text in ("/bye", "/exit"):
+                return 0
+            if not text:
+                continue
+        r = s.run(args.model, messages + [{"role": "user", "content": text}], system=system, skill=args.skill or "")
+        messages = [m for m in r.messages if m.get("role") != "system"]
+        print(r.messages[-1].get("content", "") if r.stopped == "done" else f"[stopped: {r.stopped}]")
 
 
 def cmd_launch(args) -> int:
