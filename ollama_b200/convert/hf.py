@@ -14,6 +14,7 @@ quantisation is a separate pass (store/create.py quantize_gguf).
 from __future__ import annotations
 
 import json
+import math
 import os
 import re
 from typing import Any, Callable, Iterator
@@ -34,6 +35,7 @@ ARCHS = {
     "LlamaForCausalLM": "llama", "MistralForCausalLM": "llama", "MixtralForCausalLM": "llama", "Qwen2ForCausalLM": "qwen2",
     "Qwen3ForCausalLM": "qwen3", "Qwen3MoeForCausalLM": "qwen3moe", "GemmaForCausalLM": "gemma", "Gemma2ForCausalLM": "gemma2",
     "Gemma3ForCausalLM": "gemma3", "Gemma3ForConditionalGeneration": "gemma3", "GptOssForCausalLM": "gpt-oss",
+    "Phi3ForCausalLM": "phi3",
 }
 
 # (pattern on the checkpoint name, GGUF name); {n} = layer index, {e} = expert index
@@ -47,6 +49,9 @@ _RULES: list[tuple[str, str]] = [
     (_LAYER + r"self_attn\.k_proj\.(weight|bias)", "blk.{n}.attn_k.{1}"),
     (_LAYER + r"self_attn\.v_proj\.(weight|bias)", "blk.{n}.attn_v.{1}"),
     (_LAYER + r"self_attn\.o_proj\.(weight|bias)", "blk.{n}.attn_output.{1}"),
+    # phi3: Q, K and V in one matrix, gate and up in one matrix (convert/convert_phi3.go:103-117); split into views at load
+    (_LAYER + r"self_attn\.qkv_proj\.weight", "blk.{n}.attn_qkv.weight"),
+    (_LAYER + r"mlp\.gate_up_proj\.weight", "blk.{n}.ffn_up.weight"),
     (_LAYER + r"self_attn\.q_norm\.weight", "blk.{n}.attn_q_norm.weight"),
     (_LAYER + r"self_attn\.k_norm\.weight", "blk.{n}.attn_k_norm.weight"),
     (_LAYER + r"mlp\.gate_proj\.weight", "blk.{n}.ffn_gate.weight"),
@@ -121,6 +126,21 @@ def _kv(cfg: dict[str, Any], arch: str, name: str) -> dict[str, Any]:
         kv[f"{arch}.attention.value_length"] = hd
     if arch == "llama":
         kv["llama.rope.dimension_count"] = hd
+    if arch == "phi3":          # convert/convert_phi3.go:41-71
+        kv["phi3.rope.dimension_count"] = c["hidden_size"] // n_head
+        orig = c.get("original_max_position_embeddings") or (c.get("rope_parameters") or {}).get("original_max_position_embeddings") or c.get("max_position_embeddings", 4096)
+        kv["phi3.rope.scaling.original_context_length"] = orig
+        if c.get("sliding_window"):
+            kv["phi3.attention.sliding_window"] = c["sliding_window"]
+        rs3 = c.get("rope_scaling") or c.get("rope_parameters") or {}
+        kind = rs3.get("type") or rs3.get("rope_type") or ""
+        scale = c.get("max_position_embeddings", orig) / orig
+        if kind in ("su", "longrope"):
+            kv["phi3.rope.scaling.attn_factor"] = float(max(math.sqrt(1 + math.log(scale) / math.log(orig)), 1.0)) if scale > 1 else 1.0
+        elif kind == "yarn":
+            kv["phi3.rope.scaling.attn_factor"] = float(max(0.1 * math.log(scale) + 1.0, 1.0))
+        elif kind and kind != "default":
+            raise ConvertError(f"unknown rope scaling type {kind!r}")
     rs = c.get("rope_scaling") or c.get("rope_parameters") or {}      # newer configs keep theta and scaling in one `rope_parameters` table
     rtype = rs.get("rope_type") or rs.get("type")
     if rtype in ("linear", "yarn"):
@@ -435,6 +455,11 @@ def convert_tensors(src: ModelDir, cfg: dict[str, Any], arch: str, outtype: str 
         if sorted(idx) != list(range(len(idx))):
             raise ConvertError(f"{base}: expert indices are not contiguous")
         yield emit(base, torch.stack([src.tensor(idx[e]) for e in range(len(idx))]))
+    if arch == "phi3":          # per-frequency divisors for contexts beyond / within the original window (convert/convert_phi3.go:73-101)
+        rs3 = c.get("rope_scaling") or c.get("rope_parameters") or {}
+        for key, out_name in (("long_factor", "rope_factors_long.weight"), ("short_factor", "rope_factors_short.weight")):
+            if rs3.get(key):
+                yield emit(out_name, torch.tensor(rs3[key], dtype=torch.float32))
     ff = rope_freq_factors(c)
     if ff is not None:
         yield emit("rope_freqs.weight", ff)

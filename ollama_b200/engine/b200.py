@@ -198,6 +198,8 @@ class B200Backend:
         kw = dict(scaling=c.rope_scaling_type if c.rope_scaling_type != "llama3" else "none", factor=c.rope_scaling_factor,
                   orig_ctx=c.rope_orig_ctx, beta_fast=c.yarn_beta_fast, beta_slow=c.yarn_beta_slow, device=dev)
         self.inv_freq, self.mscale = R.rope_inv_freq(c.rope_dim, c.rope_base, freq_factors=ff, **kw)
+        if c.rope_attn_factor > 0:
+            self.mscale = c.rope_attn_factor
         self.inv_freq = self.inv_freq.contiguous()
         self.inv_freq_local = self.inv_freq
         if c.rope_base_local > 0:

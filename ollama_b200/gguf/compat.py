@@ -13,7 +13,8 @@ from __future__ import annotations
 
 import os
 
-from .reader import GGUFFile
+from .reader import GGUFFile, TensorInfo
+from .types import row_bytes
 
 _GEMMA3_TEMPLATE = (
     "{{ bos_token }}{% for message in messages %}{% if message['role'] == 'assistant' %}{% set role = 'model' %}"
@@ -54,10 +55,55 @@ def _rename_tensors(g: GGUFFile, rules) -> None:
 _TEXT_ARCH = {"qwen25vl": "qwen2", "qwen2vl": "qwen2", "qwen3vl": "qwen3", "qwen3vlmoe": "qwen3moe"}
 
 
+def _row_views(g: GGUFFile, fused: str, parts: list[tuple[str, int]]) -> None:
+    """Register ``parts`` (name, rows) as tensors that are consecutive row ranges of the stored tensor ``fused``: rows are the
+    quantisation axis, so a row range of any encoding is a contiguous byte range of the stored data."""
+    t = g.tensors.get(fused)
+    if t is None or sum(n for _, n in parts) != t.shape[-1] or len(t.shape) != 2:
+        return
+    per_row = row_bytes(t.dtype, t.shape[0])
+    at = 0
+    for name, n in parts:
+        if name not in g.tensors:
+            g.tensors[name] = TensorInfo(name, (t.shape[0], n), t.dtype, t.offset + at * per_row, n * per_row)
+        at += n
+
+
+def _phi3(g: GGUFFile) -> None:
+    """Phi-3 stores Q | K | V and gate | up as one matrix each (convert/convert_phi3.go:103-117); the decoder here reads the llama
+    names, which become views into the fused tensors.  The per-frequency rotary divisors are the long set when the checkpoint's
+    context is larger than the window it was trained on, else the short set."""
+    u = lambda k, d=0: int(g.kv.get("phi3." + k, d) or d)                    # noqa: E731
+    layers, d, heads = u("block_count"), u("embedding_length"), u("attention.head_count")
+    kvh, ff = u("attention.head_count_kv", heads), u("feed_forward_length")
+    if not (layers and d and heads):
+        return
+    hd = d // heads
+    for i in range(layers):
+        _row_views(g, f"blk.{i}.attn_qkv.weight", [(f"blk.{i}.attn_q.weight", heads * hd), (f"blk.{i}.attn_k.weight", kvh * hd), (f"blk.{i}.attn_v.weight", kvh * hd)])
+        if f"blk.{i}.ffn_gate.weight" not in g.tensors and f"blk.{i}.ffn_up.weight" in g.tensors and g.tensors[f"blk.{i}.ffn_up.weight"].shape[-1] == 2 * ff:
+            fused = g.tensors.pop(f"blk.{i}.ffn_up.weight")
+            g.tensors[f"blk.{i}.ffn_gate_up.weight"] = fused
+            _row_views(g, f"blk.{i}.ffn_gate_up.weight", [(f"blk.{i}.ffn_gate.weight", ff), (f"blk.{i}.ffn_up.weight", ff)])
+        g.tensors.pop(f"blk.{i}.attn_qkv.weight", None)
+        g.tensors.pop(f"blk.{i}.ffn_gate_up.weight", None)
+    long_ctx = u("context_length") > u("rope.scaling.original_context_length", u("context_length"))
+    pick = "rope_factors_long.weight" if long_ctx else "rope_factors_short.weight"
+    if pick in g.tensors and "rope_freqs.weight" not in g.tensors:
+        src = g.tensors[pick]
+        g.tensors["rope_freqs.weight"] = TensorInfo("rope_freqs.weight", src.shape, src.dtype, src.offset, src.nbytes)
+    if not long_ctx:
+        g.kv.pop("phi3.rope.scaling.attn_factor", None)
+    for name in ("rope_factors_long.weight", "rope_factors_short.weight"):
+        g.tensors.pop(name, None)
+
+
 def normalise(g: GGUFFile) -> GGUFFile:
     if os.environ.get("OLLAMA_LLAMA_CPP_COMPAT", "1") == "0":
         return g
     arch = g.kv.get("general.architecture", "")
+    if arch == "phi3":
+        _phi3(g)
     if arch in _TEXT_ARCH:
         text = _TEXT_ARCH[arch]
         g.kv["general.source_architecture"] = arch

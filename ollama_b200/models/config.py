@@ -14,7 +14,7 @@ from typing import Any
 
 import numpy as np
 
-SUPPORTED_ARCHS = ("llama", "mistral", "qwen2", "qwen3", "qwen3moe", "gemma", "gemma2", "gemma3", "gpt-oss",
+SUPPORTED_ARCHS = ("llama", "mistral", "qwen2", "qwen3", "qwen3moe", "gemma", "gemma2", "gemma3", "gpt-oss", "phi3",
                    "bert", "nomic-bert")
 
 
@@ -34,6 +34,7 @@ class ModelConfig:
     norm_eps: float = 1e-5
     # rotary embedding
     rope_dim: int = 0
+    rope_attn_factor: float = 0.0      # > 0: cos / sin are multiplied by this instead of the scale the rope scaling type implies
     rope_base: float = 10000.0
     rope_base_local: float = 0.0   # gemma3 sliding layers
     rope_style: str = "norm"       # "norm" = interleaved pairs (llama), "neox" = half-split
@@ -146,6 +147,14 @@ def config_from_gguf(g) -> ModelConfig:
             c.moe_router, c.moe_norm_topk = "softmax_topk", True
         if g.has("rope_freqs.weight"):
             c.rope_scaling_type = "llama3"
+    elif arch == "phi3":
+        # llama-shaped once the fused matrices are split into views (gguf/compat.py); rotary pairs in the half-split order,
+        # per-frequency divisors in rope_freqs.weight, cos / sin scaled by the attention factor of the long-context recipe
+        c.rope_style = "neox"
+        c.rope_attn_factor = f("rope.scaling.attn_factor", 0.0) if g.has("rope_freqs.weight") else 0.0
+        c.rope_scaling_type = "none"
+        if 0 < c.sliding_window < c.ctx_train:
+            c.swa_layers = [True] * c.n_layers          # every layer attends within the window
     elif arch == "qwen2":
         c.rope_style, c.attn_bias = "neox", True
     elif arch in ("qwen3", "qwen3moe"):

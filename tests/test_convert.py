@@ -48,7 +48,7 @@ def _tiny_tokenizer(path):
         json.dump({"bos_token": "<s>", "eos_token": "</s>", "add_bos_token": True, "chat_template": "{{ messages }}"}, f)
 
 
-@pytest.mark.parametrize("family", ["llama", "qwen3", "qwen3moe", "gpt-oss"])
+@pytest.mark.parametrize("family", ["llama", "qwen3", "qwen3moe", "gpt-oss", "phi3", "phi3-long"])
 def test_converted_checkpoint_matches_transformers(tmp_path, family):
     transformers = pytest.importorskip("transformers")
     torch.manual_seed(0)
@@ -64,6 +64,15 @@ def test_converted_checkpoint_matches_transformers(tmp_path, family):
         cfg = transformers.Qwen3MoeConfig(head_dim=16, num_experts=4, num_experts_per_tok=2, moe_intermediate_size=32, norm_topk_prob=True,
                                           decoder_sparse_step=1, mlp_only_layers=[], **common)
         model = transformers.Qwen3MoeForCausalLM(cfg)
+    elif family.startswith("phi3"):     # fused Q|K|V and gate|up matrices; "long": per-frequency divisors and the attention factor
+        extra = {}
+        if family == "phi3-long":
+            g = torch.Generator().manual_seed(3)
+            extra = dict(max_position_embeddings=256, original_max_position_embeddings=64,
+                         rope_scaling={"type": "longrope", "long_factor": (1 + 3 * torch.rand(8, generator=g)).tolist(),
+                                       "short_factor": (1 + 0.2 * torch.rand(8, generator=g)).tolist()})
+        cfg = transformers.Phi3Config(**{**common, **extra}, pad_token_id=0)
+        model = transformers.Phi3ForCausalLM(cfg)
     else:       # gpt-oss: YaRN beyond the original context, sinks, alternating 8-token window, biased router, clamped SwiGLU
         cfg = transformers.GptOssConfig(vocab_size=64, hidden_size=64, intermediate_size=32, num_hidden_layers=2, num_attention_heads=4,
                                         num_key_value_heads=2, head_dim=16, num_local_experts=4, num_experts_per_tok=2, sliding_window=8,
@@ -84,17 +93,24 @@ def test_converted_checkpoint_matches_transformers(tmp_path, family):
         pytest.skip("this transformers build did not write safetensors")
     out = str(tmp_path / "m.gguf")
     kv = convert_hf(str(src), out, outtype="f32")
-    assert kv["general.architecture"] == family and kv["tokenizer.ggml.model"] == "gpt2" and kv["tokenizer.ggml.bos_token_id"] == 27
+    assert kv["general.architecture"] == family.removesuffix("-long") and kv["tokenizer.ggml.model"] == "gpt2" and kv["tokenizer.ggml.bos_token_id"] == 27
     assert kv["tokenizer.chat_template"] == "{{ messages }}" and len(kv["tokenizer.ggml.tokens"]) == 64
 
     from ollama_b200.engine.backend import TorchBackend, open_model
     be = TorchBackend(open_model(out), "cpu")
     be.alloc(1, 128)
-    ids = torch.randint(0, 64, (90 if family == "gpt-oss" else 11,), generator=torch.Generator().manual_seed(1))
+    ids = torch.randint(0, 64, (90 if family in ("gpt-oss", "phi3-long") else 11,), generator=torch.Generator().manual_seed(1))
     with torch.no_grad():
         ref = model(ids[None]).logits[0, -1]
     got = be.prefill(0, ids.tolist(), 0)
     assert torch.allclose(got, ref, atol=2e-4, rtol=1e-3), (got - ref).abs().max()
+    if family == "phi3":        # the views into the fused matrices hold for a block-quantised encoding too
+        from ollama_b200.store.create import quantize_gguf
+        q = str(tmp_path / "q.gguf")
+        quantize_gguf(out, q, "q8_0")
+        bq = TorchBackend(open_model(q), "cpu")
+        bq.alloc(1, 128)
+        assert (bq.prefill(0, ids.tolist(), 0) - ref).abs().max() < 0.02
 
 
 def test_create_from_checkpoint_directory_through_the_api(tmp_path, monkeypatch):
