@@ -660,14 +660,30 @@ class B200Backend:
 
         ``x``: residual stream handed over by the previous pipeline stage (the token ids then only give the chunk length).
         """
+        return self._forward_rows([(slot, tokens, pos0)], x)
+
+    @torch.no_grad()
+    def _forward_rows(self, segs: Sequence[tuple[int, Sequence[int], int]], x: torch.Tensor | None = None) -> torch.Tensor:
+        """One pass over the rows of several chunks, each ``(slot, tokens, first position)`` of a different sequence: the
+        projections, the feed-forward block and the cache append see one matrix of all rows, attention runs per sequence
+        over its own cache rows.  Returns the hidden states of all rows in the order given."""
         c, dev = self.cfg, self.device
-        T = len(tokens)
-        ids = torch.tensor(list(tokens), device=dev, dtype=torch.int32)
-        pos = torch.arange(pos0, pos0 + T, device=dev, dtype=torch.int32)
-        slots = torch.full((T,), slot, device=dev, dtype=torch.int32)
+        flat = [t for _, toks, _ in segs for t in toks]
+        T = len(flat)
+        ids = torch.tensor(flat, device=dev, dtype=torch.int32)
+        if len(segs) == 1:
+            slot, toks, pos0 = segs[0]
+            pos = torch.arange(pos0, pos0 + T, device=dev, dtype=torch.int32)
+            slots = torch.full((T,), slot, device=dev, dtype=torch.int32)
+        else:
+            pos = torch.tensor([p0 + j for _, toks, p0 in segs for j in range(len(toks))], device=dev, dtype=torch.int32)
+            slots = torch.tensor([sl for sl, toks, _ in segs for _ in toks], device=dev, dtype=torch.int32)
+        bounds, at = [], 0
+        for sl, toks, p0 in segs:
+            bounds.append((at, at + len(toks), sl, p0))
+            at += len(toks)
         if x is None:
             x = K.embed(self.embd, ids, c.embed_scale)
-        p_end = pos0 + T
         for i, L in enumerate(self.layers):
             h = K.rmsnorm_bf16(x, L.attn_norm, c.norm_eps)
             qkv = torch.empty(T, (c.n_heads + 2 * c.n_kv_heads) * c.head_dim, device=dev, dtype=torch.float32)
@@ -683,7 +699,10 @@ class B200Backend:
                           hd=c.head_dim, n_rot=c.rope_dim, neox=c.rope_style == "neox", mscale=1.0 if local else self.mscale,
                           k_cache=self.k_cache[i], v_cache=self.v_cache[i], q_norm=L.q_norm, k_norm=L.k_norm, eps=c.norm_eps,
                           k_scale=self.k_scale[i], v_scale=self.v_scale[i])
-            o = self._attn_prefill(q, i, L, slot, pos0, p_end)
+            if len(bounds) == 1:
+                o = self._attn_prefill(q, i, L, bounds[0][2], bounds[0][3], bounds[0][3] + T)
+            else:
+                o = torch.cat([self._attn_prefill(q[r0:r1], i, L, sl, p0, p0 + r1 - r0) for r0, r1, sl, p0 in bounds])
             if c.sandwich_norm:
                 x = x + R.rmsnorm(self._mm(o, L.wo), L.post_attn_norm, c.norm_eps)
             else:
@@ -699,6 +718,51 @@ class B200Backend:
                 self._mm(f, L.down, x, 0, accumulate=True)
             self.kernel_launches += 3
         return x
+
+    @torch.no_grad()
+    def shift(self, slot: int, keep: int, discard: int, n: int) -> None:
+        """Context shift in place: cache rows [keep, keep + discard) of ``slot`` are dropped, the rows behind them (up to
+        ``n``) move down by ``discard`` and their keys, stored rotated, are turned back by ``discard`` positions
+        (kvcache/causal.go:640-700).  int8 caches are expanded, rotated and quantised again with fresh block scales.  Runs
+        once per ``n_ctx / 2`` generated tokens, so it is written with tensor ops rather than a kernel of its own."""
+        c = self.cfg
+        src, dst = slice(keep + discard, n), slice(keep, n - discard)
+        back = torch.full((n - keep - discard,), -discard, device=self.device)
+        for i, L in enumerate(self.layers):
+            inv = self.inv_freq_local if (L.swa and c.rope_base_local > 0) else self.inv_freq
+            kc, vc, ks, vs = self.k_cache[i], self.v_cache[i], self.k_scale[i], self.v_scale[i]
+            k = kc[slot, :, src].float()                                   # [Hkv, S, hd]
+            if ks is not None:
+                k = (k.view(*k.shape[:2], -1, 32) * ks[slot, :, src].float()[..., None]).view_as(k)
+            k = R.rope(k.transpose(0, 1), back, inv[: c.rope_dim // 2], c.rope_style, 1.0).transpose(0, 1)
+            if ks is not None:
+                blocks = k.reshape(*k.shape[:2], -1, 32)
+                d = blocks.abs().amax(-1) / 127.0
+                q = torch.where(d[..., None] > 0, blocks / d[..., None], torch.zeros_like(blocks)).round().clamp(-127, 127)
+                kc[slot, :, dst] = q.view_as(k).to(torch.int8)
+                ks[slot, :, dst] = d.to(torch.float16)
+                vs[slot, :, dst] = vs[slot, :, src].clone()
+            else:
+                kc[slot, :, dst] = k.to(kc.dtype)
+            vc[slot, :, dst] = vc[slot, :, src].clone()
+
+    @torch.no_grad()
+    def prefill_many(self, segs: Sequence[tuple[int, Sequence[int], int]], need_logits: Sequence[bool]) -> list:
+        """Prefill chunks of several sequences in one pass (one set of GEMMs over all their rows).  Returns, per chunk, the
+        logits after its last token where asked for, else None."""
+        x = self._forward_rows(segs)
+        ends, at = [], 0
+        for _, toks, _ in segs:
+            at += len(toks)
+            ends.append(at - 1)
+        want = [e for e, need in zip(ends, need_logits) if need]
+        out: list = [None] * len(segs)
+        if want:
+            h = R.rmsnorm(x[torch.tensor(want, device=x.device)], self.out_norm, self.cfg.norm_eps).to(torch.bfloat16)
+            logits = R.softcap(self._mm(h, self.head), self.cfg.final_softcap)
+            for j, i in enumerate([i for i, need in enumerate(need_logits) if need]):
+                out[i] = logits[j]
+        return out
 
     @torch.no_grad()
     def prefill(self, slot: int, tokens: Sequence[int], pos0: int, need_logits: bool = True):

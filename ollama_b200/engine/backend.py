@@ -65,6 +65,15 @@ class TorchBackend:
         out = self.model.forward(t, pos, self.cache, slot)
         return out[0] if need_logits else None
 
+    def shift(self, slot: int, keep: int, discard: int, n: int) -> None:
+        """Context shift without re-evaluating the prompt: cache rows [keep, keep + discard) of ``slot`` are dropped, the
+        ``n - keep - discard`` rows behind them move down and their keys are re-rotated to the new positions."""
+        self.model.shift_cache(self.cache, slot, keep, discard, n)
+
+    def prefill_many(self, segs, need_logits):
+        """Chunks of several sequences in one call; the reference graph runs them one after another."""
+        return [self.prefill(slot, toks, pos0, need) for (slot, toks, pos0), need in zip(segs, need_logits)]
+
     @torch.no_grad()
     def decode(self, slots, tokens, positions):
         rows = []

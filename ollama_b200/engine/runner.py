@@ -43,6 +43,7 @@ class RunnerOptions:
     adapter_paths: tuple = ()         # LoRA adapter files merged into the weights at load time (Modelfile ADAPTER)
     draft_path: str = ""              # a smaller model of the same vocabulary that drafts tokens (Modelfile DRAFT)
     draft_num_predict: int = 4        # tokens drafted per verification pass (api/types.go:1119)
+    shift_mode: str = "rotate"        # context shift: "rotate" re-rotates the cached keys in place, "recompute" evaluates the kept tokens again
 
 
 @dataclass
@@ -392,11 +393,14 @@ class Runner:
         for s in active:
             if s.cancelled and s.state != "done":
                 self._finish(s, "cancelled")
-        # one prefill chunk per iteration keeps decode latency of the other slots bounded
-        for s in active:
-            if s.state == "prefill":
-                self._prefill_chunk(s)
-                break
+        # one prefill pass per iteration keeps decode latency of the other slots bounded; the pass takes rows of every
+        # sequence that is waiting for its prompt, up to num_batch rows in all, when the backend can run them as one matrix
+        waiting = [s for s in active if s.state == "prefill"]
+        if len(waiting) > 1 and hasattr(self.backend, "prefill_many") and not any(s.req.embedding for s in waiting):
+            with self._range("prefill_batch"):
+                self._prefill_batch(waiting)
+        elif waiting:
+            self._prefill_chunk(waiting[0])
         dec = [s for s in self.slot_seq if s is not None and s.state == "decode"]
         if dec:
             self._decode(dec)
@@ -439,6 +443,41 @@ class Runner:
         else:
             _sync(None)
             s.t_prefill += time.perf_counter() - t0
+
+    def _prefill_batch(self, seqs: list[_Seq]) -> None:
+        """One pass over prompt rows of several sequences: the row budget (num_batch) is dealt out in equal shares, what a short
+        prompt leaves over goes to the longer ones, in arrival order."""
+        t0 = time.perf_counter()
+        budget = max(1, self.opts.num_batch)
+        seqs = seqs[:budget]
+        left = {id(s): len(s.prompt) - s.n_past for s in seqs}
+        take = {id(s): 0 for s in seqs}
+        while budget > 0 and any(left[id(s)] > take[id(s)] for s in seqs):
+            hungry = [s for s in seqs if left[id(s)] > take[id(s)]]
+            share = max(1, budget // len(hungry))
+            for s in hungry:
+                n = min(share, left[id(s)] - take[id(s)], budget)
+                take[id(s)] += n
+                budget -= n
+                if budget == 0:
+                    break
+        part = [s for s in seqs if take[id(s)] > 0]
+        segs = [(s.slot, s.prompt[s.n_past:s.n_past + take[id(s)]], s.n_past) for s in part]
+        last = [take[id(s)] == left[id(s)] for s in part]
+        outs = self.backend.prefill_many(segs, last)
+        if not any(last):
+            _sync(None)
+        dt = time.perf_counter() - t0
+        self.stats["prefill_batches"] = self.stats.get("prefill_batches", 0) + 1
+        for s, (_, chunk, _), done, logits in zip(part, segs, last, outs):
+            s.n_past += len(chunk)
+            s.n_prompt_eval += len(chunk)
+            self.slot_tokens[s.slot].extend(chunk)
+            s.t_prefill += dt
+            if done:
+                s.t_first = time.perf_counter() - s.t_submit
+                s.state = "decode"
+                self._sample_accept(s, logits)
 
     def _decode(self, seqs: list[_Seq]) -> None:
         with self._range("decode_step"):
@@ -566,13 +605,17 @@ class Runner:
         toks = self.slot_tokens[s.slot]
         discard = max(1, (len(toks) - keep) // 2)
         new = toks[:keep] + toks[keep + discard:]
-        self.slot_tokens[s.slot] = new[:keep]
-        tail = new[keep:]
-        pos = keep
-        while tail:
-            chunk, tail = tail[: self.opts.num_batch], tail[self.opts.num_batch:]
-            self.backend.prefill(s.slot, chunk, pos, need_logits=False)
-            pos += len(chunk)
+        if hasattr(self.backend, "shift") and self.opts.shift_mode != "recompute":
+            # the cache rows of the dropped tokens are removed and the keys behind them re-rotated to their new positions
+            self.backend.shift(s.slot, keep, discard, len(toks))
+        else:
+            self.slot_tokens[s.slot] = new[:keep]
+            tail = new[keep:]
+            pos = keep
+            while tail:
+                chunk, tail = tail[: self.opts.num_batch], tail[self.opts.num_batch:]
+                self.backend.prefill(s.slot, chunk, pos, need_logits=False)
+                pos += len(chunk)
         self.slot_tokens[s.slot] = new
         s.n_past = len(new)
         s.d_past = 0                     # positions moved: the draft cache is rebuilt at the next speculative step

@@ -77,6 +77,22 @@ class ReferenceModel:
         return RefKVCache(self.cfg, n_slots, n_ctx, self.device)
 
     # -- blocks ---------------------------------------------------------------------------------
+    def layer_rope(self, i: int) -> torch.Tensor:
+        """Rotary frequencies of layer ``i`` (sliding-window layers of gemma3 have their own)."""
+        return self.inv_freq_local if (self.cfg.layer_is_swa(i) and self.cfg.rope_base_local > 0) else self.inv_freq
+
+    @torch.no_grad()
+    def shift_cache(self, cache: RefKVCache, slot: int, keep: int, discard: int, n: int) -> None:
+        """Drop cache rows [keep, keep + discard) of ``slot``: rows [keep + discard, n) move down by ``discard`` and their
+        keys, stored rotated, are turned back by ``discard`` positions so that they carry their new positions
+        (kvcache/causal.go:640-700 does the same with a RoPE-shift graph).  Values only move."""
+        src, dst = slice(keep + discard, n), slice(keep, n - discard)
+        back = torch.full((n - keep - discard,), -discard, device=self.device)
+        for i in range(self.cfg.n_layers):
+            k = R.rope(cache.k[i][slot, src], back, self.layer_rope(i), self.cfg.rope_style, 1.0)
+            cache.k[i][slot, dst] = k.to(cache.k[i].dtype)
+            cache.v[i][slot, dst] = cache.v[i][slot, src].clone()
+
     def _mlp(self, h: torch.Tensor, p: str) -> torch.Tensor:
         c = self.cfg
         if not c.is_moe or not self._has(p + "ffn_gate_inp.weight"):

@@ -602,6 +602,68 @@ def test_bounded_waits_report_a_missing_rank():
         reg.close()
 
 
+@pytest.mark.parametrize("spec", ["tiny-qwen3", "tiny-gpt-oss"])
+def test_prefill_of_several_sequences_in_one_pass(tmp_path, spec):
+    """Chunks of three sequences (two of them continuing an earlier chunk) through one set of GEMMs: the logits after each
+    chunk and the next decode step equal those of the same chunks run one sequence at a time."""
+    from ollama_b200.engine.b200 import B200Backend
+    from ollama_b200.engine.backend import open_model
+    from ollama_b200.models.synth import write_synthetic_gguf
+    p = str(tmp_path / "m.gguf")
+    write_synthetic_gguf(p, spec, "Q8_0")
+    g = torch.Generator().manual_seed(11)
+    prompts = [torch.randint(259, 4096, (n,), generator=g).tolist() for n in (70, 33, 150)]
+    first = [30, 0, 100]                              # rows already in the cache before the shared pass
+    one, many = B200Backend(open_model(p), "cuda"), B200Backend(open_model(p), "cuda")
+    for e in (one, many):
+        e.alloc(3, 256)
+        for slot, (toks, n0) in enumerate(zip(prompts, first)):
+            if n0:
+                e.prefill(slot, toks[:n0], 0, need_logits=False)
+    want = [one.prefill(slot, toks[n0:], n0) for slot, (toks, n0) in enumerate(zip(prompts, first))]
+    got = many.prefill_many([(slot, toks[n0:], n0) for slot, (toks, n0) in enumerate(zip(prompts, first))], [True, False, True])
+    assert got[1] is None
+    for i in (0, 2):
+        assert (got[i] - want[i]).abs().max().item() < 5e-3 * want[i].abs().max().item() + 1e-4, i
+    step = lambda e: e.decode([0, 1, 2], [5, 6, 7], [len(t) for t in prompts])       # noqa: E731
+    a, b = step(one), step(many)
+    assert (a - b).abs().max().item() < 5e-3 * a.abs().max().item() + 1e-4
+    one.close()
+    many.close()
+
+
+@pytest.mark.parametrize("kv_type,spec", [("f16", "tiny-llama"), ("q8_0", "tiny-qwen3"), ("f16", "tiny-gpt-oss")])
+def test_context_shift_on_the_engine_cache(tmp_path, kv_type, spec):
+    """Rows [keep, keep + discard) leave a slot: afterwards the engine's cache holds what the fp32 graph's cache holds after
+    the same shift (keys re-rotated, values moved), and the next decode step agrees with the fp32 graph's."""
+    from ollama_b200.engine.b200 import B200Backend
+    from ollama_b200.engine.backend import TorchBackend, open_model
+    from ollama_b200.models.synth import write_synthetic_gguf
+    p = str(tmp_path / "m.gguf")
+    write_synthetic_gguf(p, spec, "F16")
+    ref, eng = TorchBackend(open_model(p), "cpu"), B200Backend(open_model(p), "cuda", kv_type=kv_type)
+    toks = torch.randint(259, 4096, (90,), generator=torch.Generator().manual_seed(3)).tolist()
+    keep, discard, n = 5, 40, 90
+    for e in (ref, eng):
+        e.alloc(1, 128)
+        e.prefill(0, toks, 0)
+        e.shift(0, keep, discard, n)
+    tol = 0.03 if kv_type == "q8_0" else 6e-3
+    for i in range(ref.cfg.n_layers):
+        k = eng.k_cache[i][0, :, :n - discard].float()
+        v = eng.v_cache[i][0, :, :n - discard].float()
+        if eng.k_scale[i] is not None:
+            k = (k.view(*k.shape[:2], -1, 32) * eng.k_scale[i][0, :, :n - discard].float()[..., None]).view_as(k)
+            v = (v.view(*v.shape[:2], -1, 32) * eng.v_scale[i][0, :, :n - discard].float()[..., None]).view_as(v)
+        rk, rv = ref.cache.k[i][0, :n - discard].transpose(0, 1), ref.cache.v[i][0, :n - discard].transpose(0, 1)
+        assert (k.cpu() - rk).abs().max().item() < tol * rk.abs().max().item(), i
+        assert (v.cpu() - rv).abs().max().item() < tol * rv.abs().max().item(), i
+    a = ref.decode([0], [toks[-1]], [n - discard])[0]
+    b = eng.decode([0], [toks[-1]], [n - discard])[0].float().cpu()
+    assert (a - b).abs().max().item() < 0.05 * a.abs().max().item()
+    eng.close()
+
+
 def test_verify_pass_and_speculative_decoding_on_the_engine(tmp_path):
     """The target pass of speculative decoding on the sm_100a engine: ``verify`` gives the logits of one-by-one decoding
     for every drafted position, and a runner with a draft model produces the tokens of the plain greedy run."""

@@ -54,6 +54,43 @@ def test_prefix_cache_and_parallel_slots(tiny_llama_path):
         r.close()
 
 
+def test_prompts_of_waiting_sequences_share_one_prefill_pass(tiny_llama_path):
+    """Three requests arrive together with prompts of 40, 9 and 23 tokens and a budget of 16 rows per pass: every pass takes rows
+    of all that still wait (short prompts leave their share to the others), and each request decodes what it decodes alone."""
+    g = torch.Generator().manual_seed(5)
+    prompts = [torch.randint(259, 32000, (n,), generator=g).tolist() for n in (40, 9, 23)]
+    req = lambda p: CompletionRequest(prompt=p, sampling=SamplingParams(temperature=0), num_predict=5, cache_prompt=False)
+    solo = Runner(tiny_llama_path, RunnerOptions(num_ctx=128, device="cpu"))
+    try:
+        want = [[t for c in solo.completion(req(p)) for t in c.tokens] for p in prompts]
+    finally:
+        solo.close()
+    r = Runner(tiny_llama_path, RunnerOptions(num_ctx=128, num_parallel=3, num_batch=16, device="cpu"))
+    try:
+        calls = []
+        inner = r.backend.prefill_many
+        r.backend.prefill_many = lambda segs, need: (calls.append([(len(t), p0) for _, t, p0 in segs]), inner(segs, need))[1]
+        with r.cv:                                  # all three are queued before the loop admits any
+            seqs = [r.submit(req(p)) for p in prompts]
+        got = []
+        for s in seqs:
+            toks = []
+            while True:
+                ch = s.out.get(timeout=60)
+                toks += ch.tokens
+                if ch.done:
+                    assert ch.prompt_eval_count == len(s.prompt) and not ch.error
+                    break
+            got.append(toks)
+        assert got == want
+        assert calls[0] == [(6, 0), (5, 0), (5, 0)]           # 16 rows: 5 each, the spare row to the first
+        assert all(sum(n for n, _ in c) <= 16 for c in calls)
+        assert calls[1] == [(6, 6), (4, 5), (6, 5)]           # the 9-token prompt ends and leaves rows to the others
+        assert r.stats["prefill_batches"] == len(calls) >= 3
+    finally:
+        r.close()
+
+
 def test_context_limit_and_shift(tiny_llama_path):
     r = Runner(tiny_llama_path, RunnerOptions(num_ctx=32, device="cpu"))
     try:
@@ -64,6 +101,32 @@ def test_context_limit_and_shift(tiny_llama_path):
         assert out[-1].eval_count == 40
     finally:
         r.close()
+
+
+def test_context_shift_turns_cached_keys_to_their_new_positions(tiny_llama_path):
+    """Dropping rows [keep, keep + discard) of a slot: the first layer's keys and values (functions of token and position only)
+    equal those of a fresh pass over the shortened sequence; deeper layers keep their content, turned back by the shift."""
+    from ollama_b200.engine.backend import TorchBackend, open_model
+    from ollama_b200.ops import reference as R
+    be = TorchBackend(open_model(tiny_llama_path), "cpu")
+    be.alloc(2, 64)
+    toks = torch.randint(259, 32000, (40,), generator=torch.Generator().manual_seed(2)).tolist()
+    keep, discard = 4, 10
+    be.prefill(0, toks, 0)
+    before = [k[0, :40].clone() for k in be.cache.k]
+    be.shift(0, keep, discard, 40)
+    new = toks[:keep] + toks[keep + discard:]
+    be.prefill(1, new, 0)
+    assert torch.allclose(be.cache.k[0][0, :30], be.cache.k[0][1, :30], atol=1e-4)
+    assert torch.allclose(be.cache.v[0][0, :30], be.cache.v[0][1, :30], atol=1e-6)
+    fwd = torch.full((26,), discard)
+    for i in range(be.cfg.n_layers):
+        again = R.rope(be.cache.k[i][0, keep:30], fwd, be.model.layer_rope(i), be.cfg.rope_style, 1.0)
+        assert torch.allclose(again, before[i][keep + discard:40], atol=1e-4)
+        assert torch.equal(be.cache.k[i][0, :keep], before[i][:keep])
+    # the next token's logits: attention sees 30 consecutive positions
+    a = be.decode([0], [toks[-1]], [30])[0]
+    assert torch.isfinite(a).all()
 
 
 def test_stop_strings_and_seeded_sampling(tiny_llama_path):
