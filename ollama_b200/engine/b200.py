@@ -39,7 +39,7 @@ MAX_STREAM_BATCH = 32            # sequences per step when every matrix runs on 
 def supports(cfg: ModelConfig) -> bool:
     if cfg.is_moe and (cfg.n_experts > 512 or cfg.n_experts_used > 16 or cfg.d_ff_expert % 32):
         return False
-    return cfg.arch in ("llama", "mistral", "qwen2", "qwen3", "qwen3moe", "gpt-oss", "gemma", "gemma2", "gemma3") \
+    return cfg.arch in ("llama", "mistral", "qwen2", "qwen3", "qwen3moe", "gpt-oss", "gemma", "gemma2", "gemma3", "phi3") \
         and cfg.head_dim in (32, 64, 128, 256) and cfg.head_dim == cfg.v_head_dim and cfg.d_model % 32 == 0 \
         and cfg.d_ff % 32 == 0
 
@@ -718,6 +718,15 @@ class B200Backend:
                 self._mm(f, L.down, x, 0, accumulate=True)
             self.kernel_launches += 3
         return x
+
+    @torch.no_grad()
+    def copy_rows(self, src: int, dst: int, n: int) -> None:
+        """Cache rows [0, n) of slot ``src`` become rows [0, n) of slot ``dst``: a prompt prefix that another request already
+        evaluated is copied on the device (a few MB per thousand tokens) instead of being evaluated again."""
+        for i in range(len(self.layers)):
+            for t in (self.k_cache[i], self.v_cache[i], self.k_scale[i], self.v_scale[i]):
+                if t is not None:
+                    t[dst, :, :n].copy_(t[src, :, :n])
 
     @torch.no_grad()
     def shift(self, slot: int, keep: int, discard: int, n: int) -> None:

@@ -65,6 +65,12 @@ class TorchBackend:
         out = self.model.forward(t, pos, self.cache, slot)
         return out[0] if need_logits else None
 
+    def copy_rows(self, src: int, dst: int, n: int) -> None:
+        """Cache rows [0, n) of slot ``src`` become rows [0, n) of slot ``dst`` (a prompt prefix evaluated for another request)."""
+        for k, v in zip(self.cache.k, self.cache.v):
+            k[dst, :n] = k[src, :n]
+            v[dst, :n] = v[src, :n]
+
     def shift(self, slot: int, keep: int, discard: int, n: int) -> None:
         """Context shift without re-evaluating the prompt: cache rows [keep, keep + discard) of ``slot`` are dropped, the
         ``n - keep - discard`` rows behind them move down and their keys are re-rotated to the new positions."""

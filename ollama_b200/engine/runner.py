@@ -119,6 +119,7 @@ class _Seq:
 
 
 class Runner:
+    PREFIX_COPY_MIN = 16              # a prefix held by another slot is copied when it is at least this much longer than the slot's own
     def __init__(self, model_path: str, opts: RunnerOptions | None = None, backend=None):
         self.opts = opts or RunnerOptions()
         self.path = model_path
@@ -369,6 +370,24 @@ class Runner:
             reuse = max(0, min(best_lcp, len(seq.prompt) - 1))   # always evaluate at least one token
             if seq.req.embedding or not self.cfg.causal:
                 reuse = 0
+            elif seq.req.cache_prompt and hasattr(self.backend, "copy_rows"):
+                # a longer prefix of this prompt may sit in another slot, busy or not: its cache rows are copied over
+                # (x/mlxrunner/prefix_cache.go:86-140 keeps such prefixes in a trie of snapshots; here the slots are the store)
+                donor, donor_lcp = -1, reuse + self.PREFIX_COPY_MIN - 1
+                for i in range(self.n_slots):
+                    if i == best:
+                        continue
+                    other = self.slot_seq[i]
+                    valid = self.slot_tokens[i] if other is None else self.slot_tokens[i][:other.n_past]
+                    lcp = min(_common_prefix(valid, seq.prompt), len(seq.prompt) - 1)
+                    if lcp > donor_lcp:
+                        donor, donor_lcp = i, lcp
+                if donor >= 0:
+                    self.backend.copy_rows(donor, best, donor_lcp)
+                    self.slot_tokens[best] = list(seq.prompt[:donor_lcp])
+                    reuse = donor_lcp
+                    self.stats["prefix_copies"] = self.stats.get("prefix_copies", 0) + 1
+                    self.stats["prefix_copied_tokens"] = self.stats.get("prefix_copied_tokens", 0) + donor_lcp
             seq.slot, seq.n_past, seq.cached = best, reuse, reuse
             seq.d_past = 0
             seq.t_queue = time.perf_counter() - seq.t_submit

@@ -632,6 +632,41 @@ def test_prefill_of_several_sequences_in_one_pass(tmp_path, spec):
     many.close()
 
 
+def test_phi3_checkpoint_with_fused_matrices_on_the_engine(tmp_path):
+    """A converted Phi-3 checkpoint (Q | K | V and gate | up stored fused, long-context rotary factors and attention factor)
+    runs on the sm_100a engine through row-range views of the fused tensors and agrees with the fp32 graph."""
+    transformers = pytest.importorskip("transformers")
+    from test_convert import _tiny_tokenizer
+    from ollama_b200.convert.hf import convert_hf
+    from ollama_b200.engine.b200 import B200Backend
+    from ollama_b200.engine.backend import TorchBackend, open_model
+    from ollama_b200.store.create import quantize_gguf
+    torch.manual_seed(0)
+    g = torch.Generator().manual_seed(3)
+    cfg = transformers.Phi3Config(vocab_size=64, hidden_size=256, intermediate_size=512, num_hidden_layers=2, num_attention_heads=4,
+                                  num_key_value_heads=2, rms_norm_eps=1e-5, rope_theta=10000.0, tie_word_embeddings=False, pad_token_id=0,
+                                  max_position_embeddings=512, original_max_position_embeddings=64,
+                                  rope_scaling={"type": "longrope", "long_factor": (1 + 3 * torch.rand(32, generator=g)).tolist(),
+                                                "short_factor": (1 + 0.2 * torch.rand(32, generator=g)).tolist()})
+    src = tmp_path / "hf"
+    transformers.Phi3ForCausalLM(cfg).float().save_pretrained(src, safe_serialization=True)
+    _tiny_tokenizer(str(src))
+    f16, q8 = str(tmp_path / "m.gguf"), str(tmp_path / "q.gguf")
+    convert_hf(str(src), f16, outtype="f16")
+    quantize_gguf(f16, q8, "q8_0")
+    ids = torch.randint(0, 64, (90,), generator=torch.Generator().manual_seed(1)).tolist()
+    for path in (f16, q8):
+        ref, eng = TorchBackend(open_model(path), "cpu"), B200Backend(open_model(path), "cuda")
+        assert eng.cfg.arch == "phi3" and eng.mscale > 1.0
+        for e in (ref, eng):
+            e.alloc(1, 128)
+        a, b = ref.prefill(0, ids, 0), eng.prefill(0, ids, 0).float().cpu()
+        assert (a - b).abs().max().item() < 0.05 * a.abs().max().item()
+        a, b = ref.decode([0], [7], [90])[0], eng.decode([0], [7], [90])[0].float().cpu()
+        assert (a - b).abs().max().item() < 0.05 * a.abs().max().item()
+        eng.close()
+
+
 @pytest.mark.parametrize("kv_type,spec", [("f16", "tiny-llama"), ("q8_0", "tiny-qwen3"), ("f16", "tiny-gpt-oss")])
 def test_context_shift_on_the_engine_cache(tmp_path, kv_type, spec):
     """Rows [keep, keep + discard) leave a slot: afterwards the engine's cache holds what the fp32 graph's cache holds after

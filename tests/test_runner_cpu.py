@@ -103,6 +103,36 @@ def test_context_limit_and_shift(tiny_llama_path):
         r.close()
 
 
+def test_prefix_held_by_a_busy_slot_is_copied_not_evaluated_again(tiny_llama_path):
+    """While one request is still generating, a second one with the same 48-token preamble arrives: it gets another slot, the
+    preamble's cache rows are copied from the busy slot, only the new tokens are evaluated, and the answer is what the
+    request produces on its own."""
+    g = torch.Generator().manual_seed(9)
+    shared = torch.randint(259, 32000, (48,), generator=g).tolist()
+    tail = torch.randint(259, 32000, (6,), generator=g).tolist()
+    req = lambda p, n: CompletionRequest(prompt=p, sampling=SamplingParams(temperature=0), num_predict=n, ignore_eos=True)
+    solo = Runner(tiny_llama_path, RunnerOptions(num_ctx=256, device="cpu"))
+    try:
+        want = [t for c in solo.completion(req(shared + tail, 6)) for t in c.tokens]
+    finally:
+        solo.close()
+    r = Runner(tiny_llama_path, RunnerOptions(num_ctx=256, num_parallel=2, device="cpu"))
+    try:
+        a = r.submit(req(shared + [300, 301], 150))
+        assert not a.out.get(timeout=60).done                      # its prompt is in the cache and it is generating
+        b = r.submit(req(shared + tail, 6))
+        got, last = [], None
+        while last is None or not last.done:
+            last = b.out.get(timeout=60)
+            got += last.tokens
+        assert got == want
+        assert last.cached_tokens == 48 and last.prompt_eval_count == 54
+        assert r.stats["prefix_copies"] == 1 and r.stats["prefix_copied_tokens"] == 48
+        a.cancelled = True
+    finally:
+        r.close()
+
+
 def test_context_shift_turns_cached_keys_to_their_new_positions(tiny_llama_path):
     """Dropping rows [keep, keep + discard) of a slot: the first layer's keys and values (functions of token and position only)
     equal those of a fresh pass over the shortened sequence; deeper layers keep their content, turned back by the shift."""
