@@ -536,19 +536,39 @@ class AttnPrefillArgs(C.Structure):
 
 
 ATTN_PREFILL_HEAD_DIMS = (32, 64, 128, 256)
+ATTN_PREFILL_DEFAULT = "mma"        # the kernel prefill attention runs on unless told otherwise (see attn_prefill)
 
 
 def attn_prefill(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, slot: int, pos0: int, kv_len: int, scale: float,
                  causal: bool = True, window: int = 0, softcap: float = 0.0, sinks: torch.Tensor | None = None,
-                 k_scale: torch.Tensor | None = None, v_scale: torch.Tensor | None = None) -> torch.Tensor:
-    """Flash attention of a prefill chunk (kernels/attn_prefill.cu): q [T, H, D] fp32 -> bf16 [T, H * D]."""
+                 k_scale: torch.Tensor | None = None, v_scale: torch.Tensor | None = None, mode: str | None = None) -> torch.Tensor:
+    """Flash attention of a prefill chunk: q [T, H, D] fp32 -> bf16 [T, H * D].  ``mode``: "tc" = the tcgen05 kernel
+    (kernels/attn_prefill_tc.cu: f16 caches, head size 64 / 128), "mma" = the mma.sync kernel (kernels/attn_prefill.cu), "auto" =
+    tcgen05 where it applies.  Default: B200_ATTN_PREFILL, else ATTN_PREFILL_DEFAULT."""
     T, H, D = q.shape
     n_slots, Hkv, n_ctx, _ = k_cache.shape
     out = torch.empty(T, H * D, device=q.device, dtype=torch.bfloat16)
     a = AttnPrefillArgs(ptr(q.contiguous()), ptr(k_cache), ptr(v_cache), ptr(out), ptr(sinks), T, H, Hkv, n_ctx, slot, pos0, kv_len,
                         int(causal), window, scale, softcap, ptr(k_scale), ptr(v_scale))
+    mode = mode or os.environ.get("B200_ATTN_PREFILL", ATTN_PREFILL_DEFAULT)
+    if mode in ("auto", "tc") and D in (64, 128) and k_scale is None and q.dtype == torch.float32:
+        rc = lib().b2_attn_prefill_tc(C.byref(a), D, n_slots, stream())
+        if rc == 0:
+            return out
+        if rc != 801 or mode == "tc":              # 801 = cudaErrorNotSupported: nothing was launched
+            _check(rc, "attn_prefill_tc")
+    elif mode == "tc":
+        raise RuntimeError("attn_prefill: the tcgen05 kernel takes f16 caches and head size 64 or 128")
     _check(lib().b2_attn_prefill(C.byref(a), D, stream()), "attn_prefill")
     return out
+
+
+def attn_prefill_tc_status(clear: bool = False) -> int:
+    """0 = ok; 1 = a bounded wait inside the tcgen05 attention kernel expired (the result of that launch is not valid)."""
+    v = int(lib().b2_attn_prefill_tc_status())
+    if clear and v:
+        lib().b2_attn_prefill_tc_clear_status()
+    return v
 
 
 def gemm_status() -> int:

@@ -282,6 +282,32 @@ def test_attn_prefill(hd, H, Hkv, T, pos0, window, softcap, use_sinks, causal):
     assert torch.allclose(out, ref, atol=1e-2, rtol=2e-2), (out - ref).abs().max()
 
 
+@pytest.mark.parametrize("hd,H,Hkv", [(128, 8, 2), (64, 4, 4), (128, 2, 1)])
+@pytest.mark.parametrize("T,pos0,window,softcap,use_sinks,causal", [(300, 517, 0, 0.0, False, True), (129, 0, 0, 0.0, True, True),
+                                                                    (260, 400, 200, 0.0, True, True), (128, 256, 0, 30.0, False, True),
+                                                                    (200, 0, 0, 0.0, False, False), (5, 0, 0, 0.0, False, True)])
+def test_attn_prefill_on_tcgen05(hd, H, Hkv, T, pos0, window, softcap, use_sinks, causal):
+    """The tcgen05 / TMEM / TMA flash-attention kernel (several query tiles, several key tiles, a chunk that continues a cached
+    prefix) against the fp32 statement of attention over the same f16 cache; no bounded wait inside it may run out."""
+    K = _K()
+    n_slots, n_ctx, slot = 3, 1024, 2
+    g = torch.Generator().manual_seed(hd + T)
+    kc = (torch.randn(n_slots, Hkv, n_ctx, hd, generator=g) * 0.7).to(torch.float16).cuda()
+    vc = (torch.randn(n_slots, Hkv, n_ctx, hd, generator=g) * 0.7).to(torch.float16).cuda()
+    q = torch.randn(T, H, hd, generator=g).cuda()
+    sinks = torch.randn(H, generator=g).cuda() if use_sinks else None
+    scale = 1 / math.sqrt(hd)
+    p_end = pos0 + T
+    out = K.attn_prefill(q, kc, vc, slot, pos0, p_end, scale, causal, window, softcap, sinks, mode="tc").float().cpu().view(T, H, hd)
+    torch.cuda.synchronize()
+    assert K.attn_prefill_tc_status(clear=True) == 0
+    qh = q.to(torch.float16).float().cpu()
+    ref = R.attention(qh, kc[slot, :, :p_end].transpose(0, 1).float().cpu(), vc[slot, :, :p_end].transpose(0, 1).float().cpu(),
+                      torch.arange(pos0, p_end), torch.arange(p_end), scale=scale, causal=causal, window=window, softcap=softcap,
+                      sinks=sinks.cpu() if use_sinks else None)
+    assert torch.allclose(out, ref, atol=1e-2, rtol=2e-2), (out - ref).abs().max()
+
+
 @pytest.fixture
 def attn_mode():
     """Selects the decode-attention kernel for one test and restores the automatic choice afterwards."""
@@ -667,7 +693,7 @@ def test_phi3_checkpoint_with_fused_matrices_on_the_engine(tmp_path):
         eng.close()
 
 
-@pytest.mark.parametrize("kv_type,spec", [("f16", "tiny-llama"), ("q8_0", "tiny-qwen3"), ("f16", "tiny-gpt-oss")])
+@pytest.mark.parametrize("kv_type,spec", [("f16", "tiny-tp"), ("q8_0", "tiny-qwen3"), ("f16", "tiny-gemma3")])
 def test_context_shift_on_the_engine_cache(tmp_path, kv_type, spec):
     """Rows [keep, keep + discard) leave a slot: afterwards the engine's cache holds what the fp32 graph's cache holds after
     the same shift (keys re-rotated, values moved), and the next decode step agrees with the fp32 graph's."""
@@ -683,7 +709,7 @@ def test_context_shift_on_the_engine_cache(tmp_path, kv_type, spec):
         e.alloc(1, 128)
         e.prefill(0, toks, 0)
         e.shift(0, keep, discard, n)
-    tol = 0.03 if kv_type == "q8_0" else 6e-3
+    tol = 0.03          # prefill runs bf16 GEMMs: a key of the second layer is a percent off; a wrong rotation is off by its own size
     for i in range(ref.cfg.n_layers):
         k = eng.k_cache[i][0, :, :n - discard].float()
         v = eng.v_cache[i][0, :, :n - discard].float()
