@@ -78,6 +78,26 @@ __device__ __forceinline__ void umma_f16(uint32_t tmem_d, uint64_t adesc, uint64
                  ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
 }
 
+// A operand from TMEM (lane = row, one 32-bit column = two consecutive K elements), B from shared memory
+__device__ __forceinline__ void umma_f16_ts(uint32_t tmem_d, uint32_t tmem_a, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+                 "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
+                 ::"r"(tmem_d), "r"(tmem_a), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
+}
+
+// 32 consecutive 32-bit columns of this thread's TMEM lane
+__device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t (&v)[32]) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+        "{%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31,%32};"
+        ::"r"(taddr), "r"(v[0]), "r"(v[1]), "r"(v[2]), "r"(v[3]), "r"(v[4]), "r"(v[5]), "r"(v[6]), "r"(v[7]), "r"(v[8]), "r"(v[9]),
+          "r"(v[10]), "r"(v[11]), "r"(v[12]), "r"(v[13]), "r"(v[14]), "r"(v[15]), "r"(v[16]), "r"(v[17]), "r"(v[18]), "r"(v[19]),
+          "r"(v[20]), "r"(v[21]), "r"(v[22]), "r"(v[23]), "r"(v[24]), "r"(v[25]), "r"(v[26]), "r"(v[27]), "r"(v[28]), "r"(v[29]),
+          "r"(v[30]), "r"(v[31])
+        : "memory");
+    asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+}
+
 __device__ __forceinline__ float ex2(float x) {
     float y;
     asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
@@ -103,7 +123,9 @@ bool make_kv_map(CUtensorMap* map, const void* base, size_t rows, int d) {
               CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
-template <int D>
+// PT: the probabilities stay in TMEM (written over the first 64 columns of S, two f16 per column) and are the A operand of
+// P V from there; otherwise they go through the swizzled shared-memory tile.
+template <int D, bool PT>
 __global__ void __launch_bounds__(THREADS, 1) attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v,
                                                                      const __grid_constant__ AttnPrefillArgs a) {
     using L = Lay<D>;
@@ -213,9 +235,13 @@ __global__ void __launch_bounds__(THREADS, 1) attn_prefill_tc_kernel(const __gri
                 const uint8_t* vt = sm + L::OFF_V + s * L::KV_BYTES;
 #pragma unroll
                 for (int kk = 0; kk < BKV / 16; kk++) {      // O_tile = P V, 16 keys per step
-                    const uint64_t pd = umma_desc(sP + (kk >> 2) * ATOM_BYTES) + 2 * (kk & 3);
                     const uint64_t vd = umma_desc_mn(vt + kk * 16 * 128, ATOM_BYTES);
-                    umma_f16(tmem + O_COL, pd, vd, id_o, kk != 0);
+                    if (PT) {
+                        umma_f16_ts(tmem + O_COL, tmem + 8 * kk, vd, id_o, kk != 0);
+                    } else {
+                        const uint64_t pd = umma_desc(sP + (kk >> 2) * ATOM_BYTES) + 2 * (kk & 3);
+                        umma_f16(tmem + O_COL, pd, vd, id_o, kk != 0);
+                    }
                 }
                 umma_commit(o_full);
                 umma_commit(&kv_empty[s]);
@@ -286,23 +312,37 @@ __global__ void __launch_bounds__(THREADS, 1) attn_prefill_tc_kernel(const __gri
             const float mref = m_new == -INFINITY ? 0.f : m_new;
             m_run = m_new;
             float ls = 0.f;
-            uint8_t* prow = sP + c * ATOM_BYTES + r * 128;
+            if (PT) {
+                uint32_t pw[32];
 #pragma unroll
-            for (int i = 0; i < 2; i++) {
+                for (int i = 0; i < 2; i++)
 #pragma unroll
-                for (int j = 0; j < 32; j += 8) {
-                    float p[8];
-#pragma unroll
-                    for (int e = 0; e < 8; e++) {
-                        p[e] = ex2(__uint_as_float(v[i][j + e]) - mref);
-                        ls += p[e];
+                    for (int j = 0; j < 32; j += 2) {
+                        const float p0 = ex2(__uint_as_float(v[i][j]) - mref), p1 = ex2(__uint_as_float(v[i][j + 1]) - mref);
+                        ls += p0 + p1;
+                        pw[16 * i + (j >> 1)] = pack_h2(p0, p1);
                     }
-                    const int chunk = 4 * i + (j >> 3);
-                    *(uint4*)(prow + ((chunk ^ (r & 7)) << 4)) = make_uint4(pack_h2(p[0], p[1]), pack_h2(p[2], p[3]), pack_h2(p[4], p[5]), pack_h2(p[6], p[7]));
+                // keys 64 c .. 64 c + 63 of this row = columns 32 c .. 32 c + 31; both warps of the quarter have read all of S by now
+                tmem_st32(tmem + lane_base + (uint32_t)(32 * c), pw);
+            } else {
+                uint8_t* prow = sP + c * ATOM_BYTES + r * 128;
+#pragma unroll
+                for (int i = 0; i < 2; i++) {
+#pragma unroll
+                    for (int j = 0; j < 32; j += 8) {
+                        float p[8];
+#pragma unroll
+                        for (int e = 0; e < 8; e++) {
+                            p[e] = ex2(__uint_as_float(v[i][j + e]) - mref);
+                            ls += p[e];
+                        }
+                        const int chunk = 4 * i + (j >> 3);
+                        *(uint4*)(prow + ((chunk ^ (r & 7)) << 4)) = make_uint4(pack_h2(p[0], p[1]), pack_h2(p[2], p[3]), pack_h2(p[4], p[5]), pack_h2(p[6], p[7]));
+                    }
                 }
+                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
             }
             l_run = l_run * corr + ls;
-            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(p_ready);
@@ -360,15 +400,44 @@ __global__ void __launch_bounds__(THREADS, 1) attn_prefill_tc_kernel(const __gri
     if (threadIdx.x == 0 && s_failed) atomicExch(&g_attn_tc_status, KS_TIMEOUT);
 }
 
-template <int D>
+// The tensor map of a cache tensor depends on its address and extent only, and a model asks for the same few dozen tensors
+// on every chunk: encoded maps are kept (per thread, so no lock) and found again by (address, rows, head size).
+struct MapKey {
+    const void* base;
+    size_t rows;
+    int d;
+};
+struct MapEntry {
+    MapKey key;
+    CUtensorMap map;
+};
+bool cached_kv_map(CUtensorMap* out, const void* base, size_t rows, int d) {
+    constexpr int CAP = 512;                      // K and V of up to 256 layers; beyond that the oldest entries are replaced
+    static thread_local MapEntry* table = nullptr;
+    static thread_local int used = 0, next = 0;
+    if (!table) table = new MapEntry[CAP];
+    for (int i = 0; i < used; i++)
+        if (table[i].key.base == base && table[i].key.rows == rows && table[i].key.d == d) {
+            *out = table[i].map;
+            return true;
+        }
+    if (!make_kv_map(out, base, rows, d)) return false;
+    const int at = used < CAP ? used++ : (next++ % CAP);
+    table[at] = MapEntry{{base, rows, d}, *out};
+    return true;
+}
+
+int g_variant = 0;      // 0: probabilities through shared memory, 1: probabilities in TMEM
+
+template <int D, bool PT>
 int launch(const AttnPrefillArgs& a, int n_slots, cudaStream_t st) {
     CUtensorMap mk, mv;
     const size_t rows = (size_t)n_slots * a.Hkv * a.n_ctx;
-    if (!make_kv_map(&mk, a.k_cache, rows, D) || !make_kv_map(&mv, a.v_cache, rows, D)) return (int)cudaErrorNotSupported;
+    if (!cached_kv_map(&mk, a.k_cache, rows, D) || !cached_kv_map(&mv, a.v_cache, rows, D)) return (int)cudaErrorNotSupported;
     static PerDeviceOnce once;
-    if (once.first()) cudaFuncSetAttribute(attn_prefill_tc_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, Lay<D>::TOTAL);
+    if (once.first()) cudaFuncSetAttribute(attn_prefill_tc_kernel<D, PT>, cudaFuncAttributeMaxDynamicSharedMemorySize, Lay<D>::TOTAL);
     dim3 grid((a.T + BQ - 1) / BQ, a.H);
-    attn_prefill_tc_kernel<D><<<grid, THREADS, Lay<D>::TOTAL, st>>>(mk, mv, a);
+    attn_prefill_tc_kernel<D, PT><<<grid, THREADS, Lay<D>::TOTAL, st>>>(mk, mv, a);
     return (int)cudaGetLastError();
 }
 
@@ -383,9 +452,16 @@ B2_API int b2_attn_prefill_tc(const AttnPrefillArgs* a, int head_dim, int n_slot
     if (a->k_scale || a->v_scale) return (int)cudaErrorNotSupported;
     if (((uintptr_t)a->k_cache & 15) || ((uintptr_t)a->v_cache & 15) || ((uintptr_t)a->q & 15) || ((uintptr_t)a->out & 15)) return (int)cudaErrorNotSupported;
     if ((size_t)n_slots * a->Hkv * a->n_ctx >= ((size_t)1 << 31)) return (int)cudaErrorNotSupported;
-    if (head_dim == 128) return launch<128>(*a, n_slots, st);
-    if (head_dim == 64) return launch<64>(*a, n_slots, st);
+    if (head_dim == 128) return g_variant ? launch<128, true>(*a, n_slots, st) : launch<128, false>(*a, n_slots, st);
+    if (head_dim == 64) return g_variant ? launch<64, true>(*a, n_slots, st) : launch<64, false>(*a, n_slots, st);
     return (int)cudaErrorNotSupported;
+}
+
+// 0: the probabilities go through shared memory (default); 1: they stay in TMEM.  Returns the previous setting.
+B2_API int b2_attn_prefill_tc_variant(int v) {
+    const int old = g_variant;
+    if (v == 0 || v == 1) g_variant = v;
+    return old;
 }
 
 B2_API int b2_attn_prefill_tc_status() {

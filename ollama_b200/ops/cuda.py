@@ -536,7 +536,7 @@ class AttnPrefillArgs(C.Structure):
 
 
 ATTN_PREFILL_HEAD_DIMS = (32, 64, 128, 256)
-ATTN_PREFILL_DEFAULT = "mma"        # the kernel prefill attention runs on unless told otherwise (see attn_prefill)
+ATTN_PREFILL_DEFAULT = "auto"       # the kernel prefill attention runs on unless told otherwise (see attn_prefill)
 
 
 def attn_prefill(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, slot: int, pos0: int, kv_len: int, scale: float,
@@ -563,6 +563,12 @@ def attn_prefill(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, 
     return out
 
 
+def attn_prefill_tc_variant(v: int) -> int:
+    """Where the tcgen05 attention kernel keeps the probabilities between its two products: 0 = a shared-memory tile,
+    1 = TMEM (they overwrite the scores and feed the second product from there).  Returns the previous setting."""
+    return int(lib().b2_attn_prefill_tc_variant(int(v)))
+
+
 def attn_prefill_tc_status(clear: bool = False) -> int:
     """0 = ok; 1 = a bounded wait inside the tcgen05 attention kernel expired (the result of that launch is not valid)."""
     v = int(lib().b2_attn_prefill_tc_status())
@@ -572,8 +578,8 @@ def attn_prefill_tc_status(clear: bool = False) -> int:
 
 
 def gemm_status() -> int:
-    """0 = ok; 1 = a bounded wait inside a tensor-core GEMM expired."""
-    return int(lib().b2_gemm_status()) | int(lib().b2_gemm_q_status())
+    """0 = ok; 1 = a bounded wait inside a tensor-core kernel (the GEMMs, the tcgen05 attention) expired."""
+    return int(lib().b2_gemm_status()) | int(lib().b2_gemm_q_status()) | int(lib().b2_attn_prefill_tc_status())
 
 
 GEMM_Q_TYPES = {WT_Q4_K, WT_Q6_K, WT_Q8_0, WT_BF16, WT_F16}
