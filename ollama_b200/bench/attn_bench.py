@@ -6,7 +6,7 @@ A chunk of ``--chunk`` query tokens that ends at position ``ctx`` attends causal
 timed launch uses another slot of the cache (the slots together are larger than the 126 MB L2 for the longer contexts).
 Launches are recorded in a CUDA graph and timed with CUDA events after warm-up; reported are microseconds and the FLOP rate counted on the causal
 part only (4 * head size FLOP per visible query-key pair), as a fraction of the measured cuBLAS bf16 peak in
-MEASURED_PEAKS.json (fallback 1590 TFLOP/s).  ``tc`` = tcgen05 kernel (``tc-ptmem``: its variant that keeps the probabilities in TMEM), ``mma`` = mma.sync kernel.
+MEASURED_PEAKS.json (fallback 1590 TFLOP/s).  ``tc`` = tcgen05 kernel (``tc-ptmem``: its variant that keeps the probabilities in TMEM, ``tc-pipe``: the pipelined kernel), ``mma`` = mma.sync kernel.
 """
 from __future__ import annotations
 
@@ -69,12 +69,12 @@ def main() -> None:
         q = torch.randn(chunk, H, args.hd, device="cuda", generator=g)
         flop = 4.0 * args.hd * H * visible_pairs(chunk, ctx)
         outs = {}
-        for name in ("mma", "tc", "tc-ptmem"):
+        for name in ("mma", "tc", "tc-ptmem", "tc-pipe"):
             mode = name.split("-")[0]
-            K.attn_prefill_tc_variant(1 if name == "tc-ptmem" else 0)
+            K.attn_prefill_tc_variant({"tc-ptmem": 1, "tc-pipe": 2}.get(name, 0))
             us = time_mode(mode, q, kc, vc, ctx - chunk, ctx, 1 / math.sqrt(args.hd), args.reps)
             outs[name] = K.attn_prefill(q, kc, vc, 0, ctx - chunk, ctx, 1 / math.sqrt(args.hd), True, mode=mode).float()
-            K.attn_prefill_tc_variant(0)
+            K.attn_prefill_tc_variant(2)
             rows.append({"kernel": name, "chunk": chunk, "ctx": ctx, "heads": args.heads, "hd": args.hd, "us": round(us, 1),
                          "tflops": round(flop / us / 1e6, 1), f"of_{src}_bf16_peak": round(flop / us / 1e6 / peak, 3)})
             if name != "mma":

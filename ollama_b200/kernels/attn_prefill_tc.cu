@@ -13,6 +13,9 @@
 // Roles: warps 0-7 softmax, warp 8 TMA producer, warp 9 MMA issue and TMEM allocation.  Every mbarrier wait is bounded; a
 // wait that runs out sets KS_TIMEOUT in the status word, and all roles leave their loops (TMEM is freed on the way out).
 //
+// The kernel that runs by default is the pipelined form further down (two score buffers, probabilities kept in TMEM, the
+// accumulation of a tile deferred behind the next tile's softmax); the single-buffered forms above it stay selectable.
+//
 // Attention sinks, logit soft-capping and sliding windows follow attn_prefill.cu, which stays the kernel for int8 caches
 // and head sizes other than 64 / 128.  In the reference stack this is ggml-cuda's fattn family (mma / tile / vec).
 #include "tc_common.cuh"
@@ -427,7 +430,281 @@ bool cached_kv_map(CUtensorMap* out, const void* base, size_t rows, int d) {
     return true;
 }
 
-int g_variant = 0;      // 0: probabilities through shared memory, 1: probabilities in TMEM
+// ---------------------------------------------------------------------------------------------------------------------
+// Pipelined form.  Two score buffers and two P V tiles in TMEM (all 512 columns), the probabilities in TMEM over the scores
+// they came from.  S of tile t + 2 is issued as soon as the softmax warps are done with S of tile t, so the scores of the next
+// tile are always waiting when a softmax pass ends; and the softmax warps add P V of tile t - 1 to their accumulators after
+// they have handed the probabilities of tile t to the tensor pipe, so that product runs under the accumulation instead of in
+// front of it.  Roles: warps 0-7 softmax, warp 8 K loads, warp 9 MMA issue and TMEM allocation, warp 10 V loads.
+// ---------------------------------------------------------------------------------------------------------------------
+constexpr int THREADS2 = (SOFTMAX_WARPS + 3) * 32;
+constexpr int TMEM_COLS2 = 512;
+
+template <int D>
+struct Lay2 {
+    static constexpr int ATOMS = D / 64;
+    static constexpr int Q_BYTES = ATOMS * ATOM_BYTES;
+    static constexpr int KV_BYTES = ATOMS * ATOM_BYTES;
+    static constexpr int OFF_K = Q_BYTES, OFF_V = OFF_K + 2 * KV_BYTES, OFF_BAR = OFF_V + 2 * KV_BYTES;
+    static constexpr int TOTAL = OFF_BAR + 256 + 2 * 2 * 128 * 4 + 1024;
+};
+
+template <int D>
+__global__ void __launch_bounds__(THREADS2, 1) attn_prefill_tc2_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v,
+                                                                       const __grid_constant__ AttnPrefillArgs a) {
+    using L = Lay2<D>;
+    constexpr int ATOMS = L::ATOMS;
+    constexpr int OH = D / 2;
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* sm = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    uint8_t* sQ = sm;
+    uint64_t* bars = reinterpret_cast<uint64_t*>(sm + L::OFF_BAR);
+    uint64_t* k_full = bars;             // every barrier below: one per buffer
+    uint64_t* k_empty = bars + 2;
+    uint64_t* v_full = bars + 4;
+    uint64_t* v_empty = bars + 6;
+    uint64_t* s_full = bars + 8;
+    uint64_t* p_ready = bars + 10;
+    uint64_t* o_full = bars + 12;
+    uint64_t* pair = bars + 14;          // [4]
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 18);
+    int* failed = reinterpret_cast<int*>(bars + 19);
+    float* x_max = reinterpret_cast<float*>(sm + L::OFF_BAR + 256);
+    float* x_sum = x_max + 256;
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int mt = gridDim.x - 1 - blockIdx.x;
+    const int m0 = mt * BQ, h = blockIdx.y, hkv = h / (a.H / a.Hkv);
+    const int q_lo = a.pos0 + m0, q_hi = a.pos0 + min(m0 + BQ, a.T) - 1;
+    const int k_end = a.causal ? min(a.kv_len, q_hi + 1) : a.kv_len;
+    const int k_begin = (a.window > 0 ? max(0, q_lo - a.window + 1) : 0) & ~(BKV - 1);
+    const int n_tiles = k_end > k_begin ? (k_end - k_begin + BKV - 1) / BKV : 0;
+
+    if (threadIdx.x == 0) {
+        *failed = 0;
+        for (int b = 0; b < 2; b++) {
+            mbar_init(&k_full[b], 1);
+            mbar_init(&k_empty[b], 1);
+            mbar_init(&v_full[b], 1);
+            mbar_init(&v_empty[b], 1);
+            mbar_init(&s_full[b], 1);
+            mbar_init(&p_ready[b], SOFTMAX_WARPS);
+            mbar_init(&o_full[b], 1);
+        }
+        for (int q = 0; q < 4; q++) mbar_init(&pair[q], 2);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 9) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(TMEM_COLS2) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    if (warp < SOFTMAX_WARPS) {
+        const int r = 32 * (warp & 3) + lane, c = warp >> 2;
+        const bool live = m0 + r < a.T;
+        const float* qp = a.q + ((size_t)(m0 + r) * a.H + h) * D + OH * c;
+#pragma unroll
+        for (int j = 0; j < OH / 8; j++) {
+            float4 v0 = make_float4(0.f, 0.f, 0.f, 0.f), v1 = v0;
+            if (live) {
+                v0 = *(const float4*)(qp + 8 * j);
+                v1 = *(const float4*)(qp + 8 * j + 4);
+            }
+            const int col = OH * c + 8 * j;
+            const int atom = col >> 6, chunk = (col & 63) >> 3;
+            *(uint4*)(sQ + atom * ATOM_BYTES + r * 128 + ((chunk ^ (r & 7)) << 4)) =
+                make_uint4(pack_h2(v0.x, v0.y), pack_h2(v0.z, v0.w), pack_h2(v1.x, v1.y), pack_h2(v1.z, v1.w));
+        }
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem = *tmem_slot;
+    const int row0 = (a.slot * a.Hkv + hkv) * a.n_ctx + k_begin;
+
+    if (warp == 8 || warp == 10) {
+        if (lane == 0) {                 // one thread streams the K tiles, another the V tiles: each waits only for its own buffers
+            const bool is_k = warp == 8;
+            const CUtensorMap* map = is_k ? &map_k : &map_v;
+            uint64_t* full = is_k ? k_full : v_full;
+            uint64_t* empty = is_k ? k_empty : v_empty;
+            uint8_t* base = sm + (is_k ? L::OFF_K : L::OFF_V);
+            for (int t = 0; t < n_tiles; t++) {
+                const int b = t & 1;
+                if (t >= 2 && !mbar_wait(&empty[b], ((t >> 1) - 1) & 1)) { atomicExch(failed, 1); break; }
+                mbar_expect_tx(&full[b], L::KV_BYTES);
+#pragma unroll
+                for (int at = 0; at < ATOMS; at++) tma_load_2d(base + b * L::KV_BYTES + at * ATOM_BYTES, map, 64 * at, row0 + t * BKV, &full[b]);
+            }
+        }
+    } else if (warp == 9) {
+        if (lane == 0 && n_tiles > 0) {
+            constexpr uint32_t id_s = idesc_f16(BQ, BKV, 0), id_o = idesc_f16(BQ, D, 1);
+            bool ok = true;
+            auto issue_s = [&](int t) {          // S(t) = Q K(t)^T into score buffer t & 1
+                const int b = t & 1;
+                if (!mbar_wait(&k_full[b], (t >> 1) & 1)) { ok = false; return; }
+                tc_fence_after();
+                const uint8_t* kt = sm + L::OFF_K + b * L::KV_BYTES;
+#pragma unroll
+                for (int at = 0; at < ATOMS; at++) {
+                    const uint64_t qd = umma_desc(sQ + at * ATOM_BYTES), kd = umma_desc(kt + at * ATOM_BYTES);
+#pragma unroll
+                    for (int k = 0; k < 4; k++) umma_f16(tmem + 128 * b, qd + 2 * k, kd + 2 * k, id_s, (at | k) != 0);
+                }
+                umma_commit(&s_full[b]);
+                umma_commit(&k_empty[b]);
+            };
+            issue_s(0);
+            if (ok && n_tiles > 1) issue_s(1);
+            for (int t = 0; t < n_tiles && ok; t++) {
+                const int b = t & 1, ph = (t >> 1) & 1;
+                if (!mbar_wait(&p_ready[b], ph) || !mbar_wait(&v_full[b], ph)) { ok = false; break; }
+                tc_fence_after();
+                const uint8_t* vt = sm + L::OFF_V + b * L::KV_BYTES;
+#pragma unroll
+                for (int kk = 0; kk < BKV / 16; kk++)      // O_tile(t) = P(t) V(t); P sits in the first 64 columns of its score buffer
+                    umma_f16_ts(tmem + 256 + 128 * b, tmem + 128 * b + 8 * kk, umma_desc_mn(vt + kk * 16 * 128, ATOM_BYTES), id_o, kk != 0);
+                umma_commit(&o_full[b]);
+                umma_commit(&v_empty[b]);
+                if (t + 2 < n_tiles) issue_s(t + 2);       // runs behind P V(t), which still reads the buffer it overwrites
+            }
+            if (!ok) atomicExch(failed, 1);
+        }
+    } else {
+        const int q = warp & 3, c = warp >> 2;
+        const int r = 32 * q + lane;
+        const int qp = a.pos0 + m0 + r;
+        const float LOG2E = 1.4426950408889634f;
+        const float sl2 = a.scale * LOG2E;
+        const uint32_t lane_base = (uint32_t)(32 * q) << 16;
+        float o[OH];
+#pragma unroll
+        for (int j = 0; j < OH; j++) o[j] = 0.f;
+        float m_run = -INFINITY, l_run = 0.f, corr_prev = 1.f;
+        bool ok = true;
+        auto accumulate = [&](int t, float corr) {      // o = o * corr + O_tile(t)
+            const int b = t & 1;
+            if (!mbar_wait(&o_full[b], (t >> 1) & 1)) { ok = false; return; }
+            tc_fence_after();
+#pragma unroll
+            for (int j0 = 0; j0 < OH; j0 += 32) {
+                uint32_t ov[32];
+                tmem_ld32(tmem + lane_base + (uint32_t)(256 + 128 * b + OH * c + j0), ov);
+#pragma unroll
+                for (int j = 0; j < 32; j++) o[j0 + j] = o[j0 + j] * corr + __uint_as_float(ov[j]);
+            }
+            tc_fence_before();
+        };
+        for (int t = 0; t < n_tiles && ok; t++) {
+            const int b = t & 1;
+            const int n0 = k_begin + t * BKV;
+            if (!mbar_wait(&s_full[b], (t >> 1) & 1)) { ok = false; break; }
+            tc_fence_after();
+            uint32_t v[2][32];
+            tmem_ld32(tmem + lane_base + (uint32_t)(128 * b + 64 * c), v[0]);
+            tmem_ld32(tmem + lane_base + (uint32_t)(128 * b + 64 * c + 32), v[1]);
+            const bool masked = (a.causal && n0 + BKV - 1 > q_lo) || n0 + BKV > a.kv_len || a.window > 0;
+            float mx = -INFINITY;
+            if (a.softcap > 0.f) {
+                const float cap2 = a.softcap * LOG2E, inv_cap = a.scale / a.softcap;
+#pragma unroll
+                for (int i = 0; i < 2; i++)
+#pragma unroll
+                    for (int j = 0; j < 32; j++) v[i][j] = __float_as_uint(cap2 * tanhf(__uint_as_float(v[i][j]) * inv_cap));
+            } else {
+#pragma unroll
+                for (int i = 0; i < 2; i++)
+#pragma unroll
+                    for (int j = 0; j < 32; j++) v[i][j] = __float_as_uint(__uint_as_float(v[i][j]) * sl2);
+            }
+            if (masked) {
+                const int kp0 = n0 + 64 * c;
+                const int hi = min(a.causal ? qp : a.kv_len - 1, a.kv_len - 1), lo = a.window > 0 ? qp - a.window + 1 : 0;
+#pragma unroll
+                for (int i = 0; i < 2; i++)
+#pragma unroll
+                    for (int j = 0; j < 32; j++) {
+                        const int kp = kp0 + 32 * i + j;
+                        if (kp > hi || kp < lo) v[i][j] = 0xff800000u;
+                    }
+            }
+#pragma unroll
+            for (int i = 0; i < 2; i++)
+#pragma unroll
+                for (int j = 0; j < 32; j++) mx = fmaxf(mx, __uint_as_float(v[i][j]));
+            x_max[c * 128 + r] = mx;
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&pair[q]);
+            if (!mbar_wait(&pair[q], t & 1)) { ok = false; break; }
+            mx = fmaxf(mx, x_max[(c ^ 1) * 128 + r]);
+            const float m_new = fmaxf(m_run, mx);
+            const float corr = m_new == -INFINITY ? 1.f : ex2(m_run - m_new);
+            const float mref = m_new == -INFINITY ? 0.f : m_new;
+            m_run = m_new;
+            float ls = 0.f;
+            uint32_t pw[32];
+#pragma unroll
+            for (int i = 0; i < 2; i++)
+#pragma unroll
+                for (int j = 0; j < 32; j += 2) {
+                    const float p0 = ex2(__uint_as_float(v[i][j]) - mref), p1 = ex2(__uint_as_float(v[i][j + 1]) - mref);
+                    ls += p0 + p1;
+                    pw[16 * i + (j >> 1)] = pack_h2(p0, p1);
+                }
+            tmem_st32(tmem + lane_base + (uint32_t)(128 * b + 32 * c), pw);      // both warps of the quarter have read all of S(t) by now
+            l_run = l_run * corr + ls;
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&p_ready[b]);
+            if (t >= 1) accumulate(t - 1, corr_prev);      // P V(t - 1) finished long ago; P V(t) runs under this
+            corr_prev = corr;
+        }
+        if (ok && n_tiles > 0) accumulate(n_tiles - 1, corr_prev);
+        if (!ok) atomicExch(failed, 1);
+        x_sum[c * 128 + r] = l_run;
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&pair[q]);
+        if (ok && !mbar_wait(&pair[q], n_tiles & 1)) {
+            ok = false;
+            atomicExch(failed, 1);
+        }
+        if (ok) {
+            float l = l_run + x_sum[(c ^ 1) * 128 + r];
+            float oc = 1.f;
+            if (a.sinks) {
+                const float sk = a.sinks[h] * LOG2E;
+                const float m_new = fmaxf(m_run, sk);
+                oc = m_run == -INFINITY ? 0.f : ex2(m_run - m_new);
+                l = l * oc + ex2(sk - m_new);
+            }
+            const float inv = l > 0.f ? oc / l : 0.f;
+            if (m0 + r < a.T) {
+                __nv_bfloat16* op = a.out + (size_t)(m0 + r) * a.H * D + (size_t)h * D + OH * c;
+#pragma unroll
+                for (int j = 0; j < OH; j += 8) {
+                    uint32_t w[4];
+#pragma unroll
+                    for (int e = 0; e < 4; e++) {
+                        const __nv_bfloat162 bb = __floats2bfloat162_rn(o[j + 2 * e] * inv, o[j + 2 * e + 1] * inv);
+                        w[e] = *reinterpret_cast<const uint32_t*>(&bb);
+                    }
+                    *(uint4*)(op + j) = make_uint4(w[0], w[1], w[2], w[3]);
+                }
+            }
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 9) {
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(TMEM_COLS2) : "memory");
+    }
+    if (threadIdx.x == 0 && *failed) atomicExch(&g_attn_tc_status, KS_TIMEOUT);
+}
+
+
+int g_variant = 2;      // 0: probabilities through shared memory, 1: probabilities in TMEM, 2: the pipelined kernel (default)
 
 template <int D, bool PT>
 int launch(const AttnPrefillArgs& a, int n_slots, cudaStream_t st) {
@@ -438,6 +715,18 @@ int launch(const AttnPrefillArgs& a, int n_slots, cudaStream_t st) {
     if (once.first()) cudaFuncSetAttribute(attn_prefill_tc_kernel<D, PT>, cudaFuncAttributeMaxDynamicSharedMemorySize, Lay<D>::TOTAL);
     dim3 grid((a.T + BQ - 1) / BQ, a.H);
     attn_prefill_tc_kernel<D, PT><<<grid, THREADS, Lay<D>::TOTAL, st>>>(mk, mv, a);
+    return (int)cudaGetLastError();
+}
+
+template <int D>
+int launch2(const AttnPrefillArgs& a, int n_slots, cudaStream_t st) {
+    CUtensorMap mk, mv;
+    const size_t rows = (size_t)n_slots * a.Hkv * a.n_ctx;
+    if (!cached_kv_map(&mk, a.k_cache, rows, D) || !cached_kv_map(&mv, a.v_cache, rows, D)) return (int)cudaErrorNotSupported;
+    static PerDeviceOnce once;
+    if (once.first()) cudaFuncSetAttribute(attn_prefill_tc2_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, Lay2<D>::TOTAL);
+    dim3 grid((a.T + BQ - 1) / BQ, a.H);
+    attn_prefill_tc2_kernel<D><<<grid, THREADS2, Lay2<D>::TOTAL, st>>>(mk, mv, a);
     return (int)cudaGetLastError();
 }
 
@@ -452,15 +741,17 @@ B2_API int b2_attn_prefill_tc(const AttnPrefillArgs* a, int head_dim, int n_slot
     if (a->k_scale || a->v_scale) return (int)cudaErrorNotSupported;
     if (((uintptr_t)a->k_cache & 15) || ((uintptr_t)a->v_cache & 15) || ((uintptr_t)a->q & 15) || ((uintptr_t)a->out & 15)) return (int)cudaErrorNotSupported;
     if ((size_t)n_slots * a->Hkv * a->n_ctx >= ((size_t)1 << 31)) return (int)cudaErrorNotSupported;
+    if (g_variant == 2 && head_dim == 128) return launch2<128>(*a, n_slots, st);
+    if (g_variant == 2 && head_dim == 64) return launch2<64>(*a, n_slots, st);
     if (head_dim == 128) return g_variant ? launch<128, true>(*a, n_slots, st) : launch<128, false>(*a, n_slots, st);
     if (head_dim == 64) return g_variant ? launch<64, true>(*a, n_slots, st) : launch<64, false>(*a, n_slots, st);
     return (int)cudaErrorNotSupported;
 }
 
-// 0: the probabilities go through shared memory (default); 1: they stay in TMEM.  Returns the previous setting.
+// 0: the probabilities go through shared memory; 1: they stay in TMEM; 2: the pipelined kernel (default).  Returns the previous setting.
 B2_API int b2_attn_prefill_tc_variant(int v) {
     const int old = g_variant;
-    if (v == 0 || v == 1) g_variant = v;
+    if (v >= 0 && v <= 2) g_variant = v;
     return old;
 }
 

@@ -565,7 +565,8 @@ def attn_prefill(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, 
 
 def attn_prefill_tc_variant(v: int) -> int:
     """Where the tcgen05 attention kernel keeps the probabilities between its two products: 0 = a shared-memory tile,
-    1 = TMEM (they overwrite the scores and feed the second product from there).  Returns the previous setting."""
+    1 = TMEM (they overwrite the scores and feed the second product from there), 2 = the pipelined kernel (two score buffers and
+    two output tiles in TMEM, the accumulation of a tile deferred behind the next tile's softmax).  Returns the previous setting."""
     return int(lib().b2_attn_prefill_tc_variant(int(v)))
 
 

@@ -286,7 +286,7 @@ def test_attn_prefill(hd, H, Hkv, T, pos0, window, softcap, use_sinks, causal):
 @pytest.mark.parametrize("T,pos0,window,softcap,use_sinks,causal", [(300, 517, 0, 0.0, False, True), (129, 0, 0, 0.0, True, True),
                                                                     (260, 400, 200, 0.0, True, True), (128, 256, 0, 30.0, False, True),
                                                                     (200, 0, 0, 0.0, False, False), (5, 0, 0, 0.0, False, True)])
-@pytest.mark.parametrize("variant", [0, 1])
+@pytest.mark.parametrize("variant", [0, 1, 2])
 def test_attn_prefill_on_tcgen05(hd, H, Hkv, T, pos0, window, softcap, use_sinks, causal, variant):
     """The tcgen05 / TMEM / TMA flash-attention kernel (several query tiles, several key tiles, a chunk that continues a cached
     prefix) against the fp32 statement of attention over the same f16 cache; no bounded wait inside it may run out."""
@@ -299,7 +299,7 @@ def test_attn_prefill_on_tcgen05(hd, H, Hkv, T, pos0, window, softcap, use_sinks
     sinks = torch.randn(H, generator=g).cuda() if use_sinks else None
     scale = 1 / math.sqrt(hd)
     p_end = pos0 + T
-    before = K.attn_prefill_tc_variant(variant)          # 1: probabilities stay in TMEM
+    before = K.attn_prefill_tc_variant(variant)          # 1: probabilities stay in TMEM, 2: the pipelined kernel
     try:
         out = K.attn_prefill(q, kc, vc, slot, pos0, p_end, scale, causal, window, softcap, sinks, mode="tc").float().cpu().view(T, H, hd)
         torch.cuda.synchronize()
