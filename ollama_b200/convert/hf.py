@@ -39,11 +39,11 @@ ARCHS = {
 }
 
 # (pattern on the checkpoint name, GGUF name); {n} = layer index, {e} = expert index
-_LAYER = r"(?:model\.|language_model\.model\.|model\.language_model\.)?layers\.(\d+)\."
+_LAYER = r"(?:model\.)?(?:language_model\.)?(?:model\.)?layers\.(\d+)\."
 _RULES: list[tuple[str, str]] = [
-    (r"(?:model\.|language_model\.model\.|model\.language_model\.)?embed_tokens\.weight", "token_embd.weight"),
-    (r"(?:model\.|language_model\.model\.|model\.language_model\.)?norm\.weight", "output_norm.weight"),
-    (r"(?:language_model\.)?lm_head\.weight", "output.weight"),
+    (r"(?:model\.)?(?:language_model\.)?(?:model\.)?embed_tokens\.weight", "token_embd.weight"),
+    (r"(?:model\.)?(?:language_model\.)?(?:model\.)?norm\.weight", "output_norm.weight"),
+    (r"(?:model\.)?(?:language_model\.)?lm_head\.weight", "output.weight"),
     (_LAYER + r"input_layernorm\.weight", "blk.{n}.attn_norm.weight"),
     (_LAYER + r"self_attn\.q_proj\.(weight|bias)", "blk.{n}.attn_q.{1}"),
     (_LAYER + r"self_attn\.k_proj\.(weight|bias)", "blk.{n}.attn_k.{1}"),
@@ -82,6 +82,37 @@ _RULES_SANDWICH = [(_LAYER + r"post_attention_layernorm\.weight", "blk.{n}.post_
                    (_LAYER + r"pre_feedforward_layernorm\.weight", "blk.{n}.ffn_norm.weight"),
                    (_LAYER + r"post_feedforward_layernorm\.weight", "blk.{n}.post_ffw_norm.weight")]
 _SKIP = re.compile(r".*(rotary_emb\.inv_freq|vision_tower|multi_modal_projector|vision_model|audio_tower).*")
+
+
+# SigLIP tower and projector of a multimodal gemma3 checkpoint (convert/convert_gemma3.go:155-188)
+_VISION_PREFIX = re.compile(r"(?:model\.)?(?:vision_tower|vision_model)\.vision_model\.(.*)")
+_VISION_RULES = [
+    (r"embeddings\.patch_embedding\.(weight|bias)", r"v.patch_embedding.\1"),
+    (r"embeddings\.position_embedding\.weight", "v.position_embedding.weight"),
+    (r"encoder\.layers\.(\d+)\.layer_norm([12])\.(weight|bias)", r"v.blk.\1.layer_norm\2.\3"),
+    (r"encoder\.layers\.(\d+)\.self_attn\.q_proj\.(weight|bias)", r"v.blk.\1.attn_q.\2"),
+    (r"encoder\.layers\.(\d+)\.self_attn\.k_proj\.(weight|bias)", r"v.blk.\1.attn_k.\2"),
+    (r"encoder\.layers\.(\d+)\.self_attn\.v_proj\.(weight|bias)", r"v.blk.\1.attn_v.\2"),
+    (r"encoder\.layers\.(\d+)\.self_attn\.out_proj\.(weight|bias)", r"v.blk.\1.attn_output.\2"),
+    (r"encoder\.layers\.(\d+)\.mlp\.fc([12])\.(weight|bias)", r"v.blk.\1.mlp.fc\2.\3"),
+    (r"post_layernorm\.(weight|bias)", r"v.post_layernorm.\1"),
+]
+
+
+def map_vision_name(name: str) -> str | None:
+    """GGUF name of a vision-tower / projector tensor of a multimodal gemma3 checkpoint, or None."""
+    m = re.fullmatch(r"(?:model\.)?multi_modal_projector\.mm_input_projection_weight", name)
+    if m:
+        return "mm.mm_input_projection.weight"
+    if re.fullmatch(r"(?:model\.)?multi_modal_projector\.mm_soft_emb_norm\.weight", name):
+        return "mm.mm_soft_emb_norm.weight"
+    m = _VISION_PREFIX.fullmatch(name)
+    if not m:
+        return None
+    for pat, repl in _VISION_RULES:
+        if re.fullmatch(pat, m.group(1)):
+            return re.sub(pat, repl, m.group(1))
+    return None
 
 
 def map_name(name: str, arch: str) -> str | None:
@@ -126,6 +157,17 @@ def _kv(cfg: dict[str, Any], arch: str, name: str) -> dict[str, Any]:
         kv[f"{arch}.attention.value_length"] = hd
     if arch == "llama":
         kv["llama.rope.dimension_count"] = hd
+    vc = cfg.get("vision_config") if arch == "gemma3" else None
+    if isinstance(vc, dict):     # convert/convert_gemma3.go:134-151
+        kv["gemma3.vision.block_count"] = vc.get("num_hidden_layers", 27)
+        kv["gemma3.vision.embedding_length"] = vc.get("hidden_size", 1152)
+        kv["gemma3.vision.feed_forward_length"] = vc.get("intermediate_size", 4304)
+        kv["gemma3.vision.image_size"] = vc.get("image_size", 896)
+        kv["gemma3.vision.patch_size"] = vc.get("patch_size", 14)
+        kv["gemma3.vision.num_channels"] = vc.get("num_channels", 3)
+        kv["gemma3.vision.attention.head_count"] = vc.get("num_attention_heads", 16)
+        kv["gemma3.vision.attention.layer_norm_epsilon"] = float(vc.get("layer_norm_eps", 1e-6))
+        kv["gemma3.mm.tokens_per_image"] = cfg.get("mm_tokens_per_image", 256)
     if arch == "phi3":          # convert/convert_phi3.go:41-71
         kv["phi3.rope.dimension_count"] = c["hidden_size"] // n_head
         orig = c.get("original_max_position_embeddings") or (c.get("rope_parameters") or {}).get("original_max_position_embeddings") or c.get("max_position_embeddings", 4096)
@@ -393,8 +435,13 @@ def convert_tensors(src: ModelDir, cfg: dict[str, Any], arch: str, outtype: str 
     n_head, n_kv = c["num_attention_heads"], c.get("num_key_value_heads", c["num_attention_heads"])
     experts: dict[str, dict[int, str]] = {}
     names: dict[str, str] = {}
+    vision: dict[str, str] = {}
+    keep_vision = arch == "gemma3" and isinstance(cfg.get("vision_config"), dict)
     for name in src.keys():
         if _SKIP.fullmatch(name):
+            v_out = map_vision_name(name) if keep_vision else None
+            if v_out is not None:
+                vision[v_out] = name
             continue
         out = map_name(name, arch)
         if out is None:
@@ -455,6 +502,17 @@ def convert_tensors(src: ModelDir, cfg: dict[str, Any], arch: str, outtype: str 
         if sorted(idx) != list(range(len(idx))):
             raise ConvertError(f"{base}: expert indices are not contiguous")
         yield emit(base, torch.stack([src.tensor(idx[e]) for e in range(len(idx))]))
+    for out in sorted(vision):       # the image tower rides along in the same file; matrices keep 16 bits, the rest fp32
+        t = src.tensor(vision[out])
+        if out == "v.patch_embedding.weight":
+            t = t.reshape(t.shape[0], -1)                       # [width, channels * patch * patch]
+        if out == "mm.mm_soft_emb_norm.weight":
+            t = t.float() + 1.0                                 # stored as w - 1 like the text model's norms
+        if progress:
+            progress(out)
+        small = t.dim() < 2 or out in ("v.position_embedding.weight", "v.patch_embedding.weight")
+        dt, raw = _encode(t.float() if small else t, out, "f32" if small else ("f16" if outtype == "auto" else outtype))
+        yield WriteTensor(out, tuple(reversed(t.shape)), dt, raw.cpu().numpy())
     if arch == "phi3":          # per-frequency divisors for contexts beyond / within the original window (convert/convert_phi3.go:73-101)
         rs3 = c.get("rope_scaling") or c.get("rope_parameters") or {}
         for key, out_name in (("long_factor", "rope_factors_long.weight"), ("short_factor", "rope_factors_short.weight")):

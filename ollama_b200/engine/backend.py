@@ -58,11 +58,15 @@ class TorchBackend:
         self.n_slots, self.n_ctx = n_slots, n_ctx
         self.cache = self.model.new_cache(n_slots, n_ctx)
 
+    supports_embeds = True
+
     @torch.no_grad()
-    def prefill(self, slot, tokens, pos0, need_logits=True):
+    def prefill(self, slot, tokens, pos0, need_logits=True, embeds=None, spans=()):
+        """``embeds`` = (rows of the chunk, [n, d_model] values) replaces the input embedding of those rows (image positions);
+        ``spans``: position ranges that attend to themselves in both directions (each must lie inside one chunk)."""
         t = torch.tensor(list(tokens), dtype=torch.long)
         pos = torch.arange(pos0, pos0 + len(tokens))
-        out = self.model.forward(t, pos, self.cache, slot)
+        out = self.model.forward(t, pos, self.cache, slot, embeds=embeds, spans=spans)
         return out[0] if need_logits else None
 
     def copy_rows(self, src: int, dst: int, n: int) -> None:

@@ -138,17 +138,21 @@ class ReferenceModel:
         return x * self.cfg.embed_scale
 
     def forward(self, tokens: torch.Tensor, positions: torch.Tensor, cache: RefKVCache, slot: int,
-                logit_rows: torch.Tensor | None = None, return_hidden: bool = False) -> torch.Tensor:
+                logit_rows: torch.Tensor | None = None, return_hidden: bool = False, embeds=None, spans=()) -> torch.Tensor:
         """Run ``tokens`` ([T]) at ``positions`` ([T]) for one slot; writes K/V at those positions.
 
         Returns logits for ``logit_rows`` (default: the last token) as [R, vocab], or the final normed
-        hidden states [T, d_model] when ``return_hidden``.
+        hidden states [T, d_model] when ``return_hidden``.  ``embeds`` = (rows, values): rows of the chunk whose input is the
+        given embedding (an image position; not scaled like a token embedding) instead of the token's; ``spans``: position
+        ranges [lo, hi) that attend to themselves in both directions.
         """
         c = self.cfg
         tokens = tokens.to(self.device)
         positions = positions.to(self.device)
         T = tokens.shape[0]
-        x = self.embed_tokens(tokens)
+        x = self.embed_tokens(tokens.clamp(min=0))
+        if embeds is not None and len(embeds[0]):
+            x[torch.as_tensor(embeds[0], device=self.device)] = embeds[1].to(self.device, x.dtype)
         p_end = int(positions.max().item()) + 1
         k_pos = torch.arange(p_end, device=self.device)
         for i in range(c.n_layers):
@@ -170,7 +174,7 @@ class ReferenceModel:
             sinks = self._f(p + "attn_sinks.weight") if c.attn_sinks and self._has(p + "attn_sinks.weight") else None
             o = R.attention(q, cache.k[i][slot, :p_end], cache.v[i][slot, :p_end], positions, k_pos,
                             scale=self.attn_scale, causal=c.causal, window=c.sliding_window if swa else 0,
-                            softcap=c.attn_softcap, sinks=sinks)
+                            softcap=c.attn_softcap, sinks=sinks, spans=spans)
             o = self._linear(o.reshape(T, -1), p + "attn_output")
             if c.sandwich_norm:
                 o = R.rmsnorm(o, self._f(p + "post_attention_norm.weight"), c.norm_eps)

@@ -71,12 +71,13 @@ def rope(x: torch.Tensor, pos: torch.Tensor, inv_freq: torch.Tensor, style: str,
 
 def attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, q_pos: torch.Tensor, k_pos: torch.Tensor, *,
               scale: float, causal: bool = True, window: int = 0, softcap: float = 0.0,
-              sinks: torch.Tensor | None = None) -> torch.Tensor:
+              sinks: torch.Tensor | None = None, spans=()) -> torch.Tensor:
     """q: [T,H,D]; k: [S,Hkv,D]; v: [S,Hkv,Dv]; returns [T,H,Dv].
 
     A key at position p_k is visible to a query at p_q when p_k <= p_q (causal) and, with a
     sliding window W, p_q - p_k < W.  ``sinks`` ([H]) adds one value-less logit per head to the
-    softmax denominator.
+    softmax denominator.  ``spans``: position ranges [lo, hi) inside which every query sees every key,
+    whatever the two rules above say (the positions of one image attend to each other in both directions).
     """
     T, H, D = q.shape
     S, Hkv, Dv = v.shape
@@ -91,6 +92,9 @@ def attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, q_pos: torch.Te
         mask |= dp < 0
     if window > 0:
         mask |= dp >= window
+    for lo, hi in spans:
+        inside_q, inside_k = (q_pos >= lo) & (q_pos < hi), (k_pos >= lo) & (k_pos < hi)
+        mask &= ~(inside_q[:, None] & inside_k[None, :])
     s = s.masked_fill(mask[None, None], float("-inf"))
     if sinks is not None:
         sk = sinks.float().view(Hkv, g, 1, 1).expand(Hkv, g, T, 1)

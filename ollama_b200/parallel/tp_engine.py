@@ -229,24 +229,38 @@ class TPBackend(B200Backend):
                 self._norm_quant_reduce(L.attn_norm, nb)            # completes the previous layer's FFN
             self._gemv([L.wq, L.wk, L.wv], nb, b.xq, b.xds, b.xf, b.qkv, b.qkv.stride(0))
             local = L.swa and c.rope_base_local > 0
-            ra = K.RopeKvArgs(K.ptr(b.qkv), K.ptr(b.positions), K.ptr(b.slots), K.ptr(self.inv_freq_local if local else self.inv_freq),
-                              K.ptr(L.q_norm), K.ptr(L.k_norm), c.norm_eps, 1.0 if local else self.mscale, c.n_heads, c.n_kv_heads,
-                              c.head_dim, c.rope_dim, int(c.rope_style == "neox"), self.n_ctx, K.ptr(b.q), K.ptr(self.k_cache[i]),
-                              K.ptr(self.v_cache[i]), K.ptr(self.k_scale[i]), K.ptr(self.v_scale[i]))
-            K._check(lib.b2_rope_kv(C.byref(ra), nb, int(self.pdl), st()), "rope_kv")
-            aa = K.AttnDecodeArgs(K.ptr(b.q), K.ptr(self.k_cache[i]), K.ptr(self.v_cache[i]), K.ptr(b.positions), K.ptr(b.slots),
+            inv_freq, mscale = (self.inv_freq_local, 1.0) if local else (self.inv_freq, self.mscale)
+            fused = self.fuse_rope and L.q_norm is None and L.k_norm is None and self.k_scale[i] is None and not self.fuse_attn_combine
+            aa = K.AttnDecodeArgs(None if fused else K.ptr(b.q), K.ptr(self.k_cache[i]), K.ptr(self.v_cache[i]), K.ptr(b.positions), K.ptr(b.slots),
                                   c.n_heads, c.n_kv_heads, self.n_ctx, self.n_splits, self.attn_scale, c.attn_softcap,
                                   c.sliding_window if L.swa else 0, K.ptr(b.part_acc), K.ptr(b.part_ml), K.ptr(self.k_scale[i]),
                                   K.ptr(self.v_scale[i]))
             ca = K.AttnCombineArgs(K.ptr(b.part_acc), K.ptr(b.part_ml), K.ptr(L.sinks), c.n_heads, self.n_splits, c.head_dim,
                                    K.ptr(b.ao), K.ptr(b.aq), K.ptr(b.ads))
-            if self.fuse_attn_combine:      # the last CTA of every head group merges the splits: one launch instead of two
-                K._check(lib.b2_attn_decode_fused(C.byref(aa), C.byref(ca), C.c_void_p(K.ptr(b.attn_tickets)), nb, c.head_dim, int(self.pdl), st()),
-                         "attn_decode_fused")
-                self._n += 2
-            else:
-                K._check(lib.b2_attn_decode(C.byref(aa), C.byref(ca), nb, c.head_dim, int(self.pdl), st()), "attn_decode")
-                self._n += 3
+            if fused:
+                # rotary embedding of the queries, rotation + cache append of the new key / value and the attention in one launch
+                rr = K.AttnRopeArgs(K.ptr(b.qkv), K.ptr(inv_freq), mscale, c.rope_dim, int(c.rope_style == "neox"))
+                lib.b2_attn_decode_rope.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_void_p]
+                rc = lib.b2_attn_decode_rope(C.byref(aa), C.byref(rr), C.byref(ca), nb, c.head_dim, int(self.pdl), st())
+                if rc == 801:           # cudaErrorNotSupported: nothing was launched; this model keeps the separate kernel
+                    self.fuse_rope = fused = False
+                    aa.q = K.ptr(b.q)
+                else:
+                    K._check(rc, "attn_decode_rope")
+                    self._n += 2
+            if not fused:
+                ra = K.RopeKvArgs(K.ptr(b.qkv), K.ptr(b.positions), K.ptr(b.slots), K.ptr(inv_freq),
+                                  K.ptr(L.q_norm), K.ptr(L.k_norm), c.norm_eps, mscale, c.n_heads, c.n_kv_heads,
+                                  c.head_dim, c.rope_dim, int(c.rope_style == "neox"), self.n_ctx, K.ptr(b.q), K.ptr(self.k_cache[i]),
+                                  K.ptr(self.v_cache[i]), K.ptr(self.k_scale[i]), K.ptr(self.v_scale[i]))
+                K._check(lib.b2_rope_kv(C.byref(ra), nb, int(self.pdl), st()), "rope_kv")
+                if self.fuse_attn_combine:      # the last CTA of every head group merges the splits: one launch instead of two
+                    K._check(lib.b2_attn_decode_fused(C.byref(aa), C.byref(ca), C.c_void_p(K.ptr(b.attn_tickets)), nb, c.head_dim, int(self.pdl), st()),
+                             "attn_decode_fused")
+                    self._n += 2
+                else:
+                    K._check(lib.b2_attn_decode(C.byref(aa), C.byref(ca), nb, c.head_dim, int(self.pdl), st()), "attn_decode")
+                    self._n += 3
             self._gemv_send(L.wo, nb, b.aq, b.ads, b.ao, self.cm_dec, c.d_model)
             self._norm_quant_reduce(L.ffn_norm, nb)
             if L.moe:      # expert parallel: local experts only; the weighted partial sum goes to every rank like a row-parallel GEMV
