@@ -637,38 +637,46 @@ class B200Backend:
         self.kernel_launches += 1
         return K.gemm_bf16_glu(x_bf16, wb, c.act, w.bias, c.swiglu_alpha, c.swiglu_limit)
 
-    def _attn_prefill(self, q: torch.Tensor, i: int, L, slot: int, pos0: int, p_end: int) -> torch.Tensor:
-        """Attention of a prefill chunk over cache positions [0, p_end): q [T, H, hd] fp32 -> bf16 [T, H * hd]."""
+    def _attn_prefill(self, q: torch.Tensor, i: int, L, slot: int, pos0: int, p_end: int, spans=()) -> torch.Tensor:
+        """Attention of a prefill chunk over cache positions [0, p_end): q [T, H, hd] fp32 -> bf16 [T, H * hd].  ``spans``
+        (position ranges that attend to themselves in both directions: the rows of an image) take the plain tensor-op path,
+        the kernels know the causal and windowed masks only; such chunks occur once per image."""
         c = self.cfg
         T = q.shape[0]
         window = c.sliding_window if L.swa else 0
-        if c.head_dim in K.ATTN_PREFILL_HEAD_DIMS:
+        spans = [(lo, hi) for lo, hi in spans if lo < p_end and hi > pos0]
+        if c.head_dim in K.ATTN_PREFILL_HEAD_DIMS and not spans:
             self.kernel_launches += 1
             return K.attn_prefill(q, self.k_cache[i], self.v_cache[i], slot, pos0, p_end, self.attn_scale, c.causal, window,
                                   c.attn_softcap, L.sinks, k_scale=self.k_scale[i], v_scale=self.v_scale[i])
         # head sizes without a flash-attention instantiation (32, 256): plain torch attention over the same cache rows
-        kk = self.k_cache[i][slot, :, :p_end].transpose(0, 1)        # [S, Hkv, hd] f16
-        vv = self.v_cache[i][slot, :, :p_end].transpose(0, 1)
+        kk = self.k_cache[i][slot, :, :p_end].transpose(0, 1).float()        # [S, Hkv, hd]
+        vv = self.v_cache[i][slot, :, :p_end].transpose(0, 1).float()
+        if self.k_scale[i] is not None:         # int8 cache: one f16 scale per 32 dims
+            kk = (kk.reshape(*kk.shape[:2], -1, 32) * self.k_scale[i][slot, :, :p_end].transpose(0, 1).float()[..., None]).reshape(kk.shape)
+            vv = (vv.reshape(*vv.shape[:2], -1, 32) * self.v_scale[i][slot, :, :p_end].transpose(0, 1).float()[..., None]).reshape(vv.shape)
         pos = torch.arange(pos0, p_end, device=q.device)
         o = R.attention(q, kk, vv, pos, torch.arange(p_end, device=q.device), scale=self.attn_scale, causal=c.causal, window=window,
-                        softcap=c.attn_softcap, sinks=L.sinks)
+                        softcap=c.attn_softcap, sinks=L.sinks, spans=spans)
         return o.reshape(T, -1).to(torch.bfloat16)
 
     @torch.no_grad()
-    def _forward_chunk(self, slot: int, tokens: Sequence[int], pos0: int, x: torch.Tensor | None = None) -> torch.Tensor:
+    def _forward_chunk(self, slot: int, tokens: Sequence[int], pos0: int, x: torch.Tensor | None = None, embeds=None, spans=()) -> torch.Tensor:
         """Chunked prefill: returns the final hidden states [T, d_model] (fp32, before the output norm).
 
         ``x``: residual stream handed over by the previous pipeline stage (the token ids then only give the chunk length).
+        ``embeds`` = (rows, [n, d_model] values): rows whose input embedding is given (image positions); ``spans``: position
+        ranges that attend to themselves in both directions.
         """
-        return self._forward_rows([(slot, tokens, pos0)], x)
+        return self._forward_rows([(slot, tokens, pos0)], x, embeds, spans)
 
     @torch.no_grad()
-    def _forward_rows(self, segs: Sequence[tuple[int, Sequence[int], int]], x: torch.Tensor | None = None) -> torch.Tensor:
+    def _forward_rows(self, segs: Sequence[tuple[int, Sequence[int], int]], x: torch.Tensor | None = None, embeds=None, spans=()) -> torch.Tensor:
         """One pass over the rows of several chunks, each ``(slot, tokens, first position)`` of a different sequence: the
         projections, the feed-forward block and the cache append see one matrix of all rows, attention runs per sequence
         over its own cache rows.  Returns the hidden states of all rows in the order given."""
         c, dev = self.cfg, self.device
-        flat = [t for _, toks, _ in segs for t in toks]
+        flat = [max(int(t), 0) for _, toks, _ in segs for t in toks]      # negative ids stand for rows whose input comes from ``embeds``
         T = len(flat)
         ids = torch.tensor(flat, device=dev, dtype=torch.int32)
         if len(segs) == 1:
@@ -684,6 +692,8 @@ class B200Backend:
             at += len(toks)
         if x is None:
             x = K.embed(self.embd, ids, c.embed_scale)
+            if embeds is not None and len(embeds[0]):      # image rows: projected features, not scaled like token embeddings
+                x[torch.as_tensor(list(embeds[0]), device=dev)] = embeds[1].to(dev, x.dtype)
         for i, L in enumerate(self.layers):
             h = K.rmsnorm_bf16(x, L.attn_norm, c.norm_eps)
             qkv = torch.empty(T, (c.n_heads + 2 * c.n_kv_heads) * c.head_dim, device=dev, dtype=torch.float32)
@@ -700,7 +710,7 @@ class B200Backend:
                           k_cache=self.k_cache[i], v_cache=self.v_cache[i], q_norm=L.q_norm, k_norm=L.k_norm, eps=c.norm_eps,
                           k_scale=self.k_scale[i], v_scale=self.v_scale[i])
             if len(bounds) == 1:
-                o = self._attn_prefill(q, i, L, bounds[0][2], bounds[0][3], bounds[0][3] + T)
+                o = self._attn_prefill(q, i, L, bounds[0][2], bounds[0][3], bounds[0][3] + T, spans)
             else:
                 o = torch.cat([self._attn_prefill(q[r0:r1], i, L, sl, p0, p0 + r1 - r0) for r0, r1, sl, p0 in bounds])
             if c.sandwich_norm:
@@ -773,9 +783,11 @@ class B200Backend:
                 out[i] = logits[j]
         return out
 
+    supports_embeds = True
+
     @torch.no_grad()
-    def prefill(self, slot: int, tokens: Sequence[int], pos0: int, need_logits: bool = True):
-        x = self._forward_chunk(slot, tokens, pos0)
+    def prefill(self, slot: int, tokens: Sequence[int], pos0: int, need_logits: bool = True, embeds=None, spans=()):
+        x = self._forward_chunk(slot, tokens, pos0, embeds=embeds, spans=spans)
         if not need_logits:
             return None
         h = R.rmsnorm(x[-1:], self.out_norm, self.cfg.norm_eps).to(torch.bfloat16)

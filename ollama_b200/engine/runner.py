@@ -62,6 +62,7 @@ class CompletionRequest:
     embedding: bool = False
     ignore_eos: bool = False
     preserved_tokens: bool = True     # render special tokens into the text stream (harmony needs them)
+    images: list = field(default_factory=list)   # encoded images (bytes); image N replaces the marker "[img-N]" of a text prompt
 
 
 @dataclass
@@ -116,6 +117,8 @@ class _Seq:
         self.repeat_run = 0
         self.logprobs: list[TokenLogprob] = []
         self.limit = 0
+        self.image_rows: dict[int, torch.Tensor] = {}      # prompt index -> embedding row (image positions)
+        self.spans: list[tuple[int, int]] = []              # prompt index ranges of the images: bidirectional attention inside
 
 
 class Runner:
@@ -181,6 +184,7 @@ class Runner:
             "decode_seconds", "ttft_seconds", "decode_steps", "decode_step_sequences", "context_shifts", "draft_tokens",
             "draft_accepted_tokens")}
         self.done_reasons: dict[str, int] = {}
+        self._vision = None           # the vision tower, loaded with the first image (False: the model has none)
         self._nvtx = bool(os.environ.get("B200_NVTX")) and str(getattr(self.backend, "device", "cpu")).startswith("cuda")
         self.thread = threading.Thread(target=self._loop, name="runner-loop", daemon=True)
         self.thread.start()
@@ -239,8 +243,13 @@ class Runner:
     def submit(self, req: CompletionRequest) -> _Seq:
         if self.closed:
             raise RunnerError("runner is closed")
+        image_rows: dict[int, torch.Tensor] = {}
+        spans: list[tuple[int, int]] = []
         if isinstance(req.prompt, str):
-            toks = self.tokenize(req.prompt, add_special=req.add_special)
+            if req.images:
+                toks, image_rows, spans = self._tokenize_with_images(req)
+            else:
+                toks = self.tokenize(req.prompt, add_special=req.add_special)
         else:
             toks = [int(t) for t in req.prompt]
         if req.embedding and self.tokenizer is not None and self.tokenizer.add_eos is False and self.cfg.pooling == "last":
@@ -253,13 +262,75 @@ class Runner:
             if not req.truncate or req.embedding:
                 raise RunnerError("the prompt is longer than the context length currently available to the model; shorten the "
                                   "prompt, adjust the context length in settings, or use a model with a longer context length", 400)
+            if image_rows:
+                raise RunnerError("the prompt and its images are longer than the context length currently available to the model", 400)
             keep = min(max(req.num_keep, 0), limit // 2)
             toks = toks[:keep] + toks[len(toks) - (limit - keep):]
         seq = _Seq(req, toks)
+        seq.image_rows, seq.spans = image_rows, spans
         with self.cv:
             self.pending.append(seq)
             self.cv.notify_all()
         return seq
+
+    # -- images ---------------------------------------------------------------------------------------
+    def vision(self):
+        """The model's vision tower (loaded on first use), or None for a text-only model or a back end that takes no embeddings."""
+        if self._vision is None and self.gguf is not None and getattr(self.backend, "supports_embeds", False):
+            from ..models.vision import load_tower
+            dev = self._cuda_device if self._cuda_device.startswith("cuda") else "cpu"
+            self._vision = load_tower(self.gguf, dev) or False
+        return self._vision or None
+
+    def _tokenize_with_images(self, req: CompletionRequest):
+        """Prompt text with ``[img-N]`` markers (server/prompt.go:96-133 writes them) -> token ids in which every image is a block
+        ``\n\n <start_of_image> soft tokens <end_of_image> \n\n``; the soft positions carry ids below zero that are derived from
+        the image's bytes (equal images share cached prefixes, different ones never do) and take their input from the vision
+        tower's projection.  Returns (ids, {prompt index: embedding row}, [(first, last + 1) of each image])."""
+        import hashlib
+        import re
+        tower = self.vision()
+        if tower is None:
+            raise RunnerError("this model does not take images", 400)
+        tk = self.tokenizer
+        boi, eoi = tk.vocab.get("<start_of_image>"), tk.vocab.get("<end_of_image>")
+        parts = re.split(r"\[img-(\d+)\]", req.prompt)
+        if len(parts) == 1:               # no marker at all: the images go in front, in order
+            parts = sum([["", str(i)] for i in range(len(req.images))], []) + parts
+        toks: list[int] = []
+        rows: dict[int, torch.Tensor] = {}
+        spans: list[tuple[int, int]] = []
+        first = True
+        for i, part in enumerate(parts):
+            if i % 2 == 0:
+                if part or first:
+                    toks += self.tokenize(part, add_special=req.add_special and first)
+                    first = False
+                continue
+            n = int(part)
+            if not 0 <= n < len(req.images):
+                raise RunnerError(f"the prompt names image {n} but the request has {len(req.images)}", 400)
+            data = req.images[n]
+            try:
+                emb = tower.encode(data)
+            except Exception as e:
+                raise RunnerError(f"image {n} could not be read: {e}", 400)
+            h = int.from_bytes(hashlib.sha256(data).digest()[:4], "little")
+            if first:
+                toks += self.tokenize("", add_special=req.add_special)
+                first = False
+            toks += self.tokenize("\n\n", add_special=False)
+            if boi is not None:
+                toks.append(boi)
+            lo = len(toks)
+            for j in range(emb.shape[0]):
+                rows[len(toks)] = emb[j]
+                toks.append(-(1 + ((h * 1000003 + j) & 0x3FFFFFFF)))
+            spans.append((lo, len(toks)))
+            if eoi is not None:
+                toks.append(eoi)
+            toks += self.tokenize("\n\n", add_special=False)
+        return toks, rows, spans
 
     def embedding(self, text: str | Sequence[int]) -> tuple[list[float], int]:
         seq = self.submit(CompletionRequest(prompt=text, embedding=True, truncate=False))
@@ -415,7 +486,7 @@ class Runner:
         # one prefill pass per iteration keeps decode latency of the other slots bounded; the pass takes rows of every
         # sequence that is waiting for its prompt, up to num_batch rows in all, when the backend can run them as one matrix
         waiting = [s for s in active if s.state == "prefill"]
-        if len(waiting) > 1 and hasattr(self.backend, "prefill_many") and not any(s.req.embedding for s in waiting):
+        if len(waiting) > 1 and hasattr(self.backend, "prefill_many") and not any(s.req.embedding or s.image_rows for s in waiting):
             with self._range("prefill_batch"):
                 self._prefill_batch(waiting)
         elif waiting:
@@ -438,6 +509,9 @@ class Runner:
         t0 = time.perf_counter()
         remaining = len(s.prompt) - s.n_past
         n = min(remaining, max(1, self.opts.num_batch))
+        for lo, hi in s.spans:            # the rows of an image attend to each other in both directions: one chunk holds them all
+            if lo < s.n_past + n < hi:
+                n = lo - s.n_past if lo > s.n_past else hi - s.n_past      # stop in front of the image, or take all of it
         chunk = s.prompt[s.n_past:s.n_past + n]
         last = n == remaining
         if s.req.embedding:
@@ -450,7 +524,12 @@ class Runner:
             self.slot_tokens[s.slot] = []
             self._release(s)
             return
-        logits = self.backend.prefill(s.slot, chunk, s.n_past, need_logits=last)
+        if s.image_rows:
+            rows = [i for i in range(n) if s.n_past + i in s.image_rows]
+            embeds = (rows, torch.stack([s.image_rows[s.n_past + i] for i in rows])) if rows else None
+            logits = self.backend.prefill(s.slot, chunk, s.n_past, need_logits=last, embeds=embeds, spans=s.spans)
+        else:
+            logits = self.backend.prefill(s.slot, chunk, s.n_past, need_logits=last)
         s.n_past += n
         s.n_prompt_eval += n
         self.slot_tokens[s.slot].extend(chunk)

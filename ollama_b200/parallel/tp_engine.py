@@ -111,6 +111,7 @@ class ShardedTensors:
 class TPBackend(B200Backend):
     name = "b200-tp"
     supports_verify = False      # the verification pass of speculative decoding is not part of the follower protocol
+    supports_embeds = False      # image rows are not part of the follower protocol either
 
     def __init__(self, cfg: ModelConfig, tensors, device: str = "cuda", rank: int = 0, world: int = 1, group=None,
                  max_chunk: int = 2048, keep_bf16: bool | None = None, kv_type: str | None = None):

@@ -176,17 +176,29 @@ class Server:
         return ref, opts
 
     @staticmethod
-    def _refuse_images(model: Model, has_images: bool):
+    def _refuse_images(model: Model, has_images: bool, runner: Any = None):
         """Image input: a model without a vision tower cannot take it (server/routes.go: images add the vision capability to the
-        request), and this engine runs the text path of vision checkpoints only.  Either way the request is refused, never
-        answered as if the images were not there."""
+        request); a vision checkpoint whose tower this engine does not run (anything but gemma3's, or a back end that takes no
+        embeddings) is refused as well, never answered as if the images were not there.  Called before scheduling with the
+        model only, and again with the loaded runner."""
         if not has_images:
             return None
         try:
             model.check_capabilities(CAP_VISION)
         except CapabilityError as e:
             return _err(400, str(e))
-        return _err(400, f"{model.short_name or model.name}: image input is not available: this engine runs the text path of vision models only")
+        if runner is not None and (not hasattr(runner, "vision") or runner.vision() is None):
+            return _err(400, f"{model.short_name or model.name}: image input is not available: this engine runs the text path of this model only")
+        return None
+
+    @staticmethod
+    def _image_bytes(images: list) -> list[bytes]:
+        """API images (base64 text, or bytes from an in-process caller) -> encoded image bytes."""
+        import base64
+        out = []
+        for im in images:
+            out.append(bytes(im) if isinstance(im, (bytes, bytearray)) else base64.b64decode(str(im), validate=False))
+        return out
 
     def _renderer(self, model: Model, runner: Any) -> PromptRenderer:
         key = model.digest or model.name
@@ -286,6 +298,19 @@ class Server:
         ref, opts = self._schedule(model, tuple(caps), req.get("options"), req.get("keep_alive"))
         runner = ref.runner
         t_loaded = time.time()
+        media: list[bytes] = []
+        if req.get("images"):
+            refusal = self._refuse_images(model, True, runner)
+            if refusal is not None:
+                self.sched.release(ref)
+                return refusal
+            try:
+                media = self._image_bytes(req["images"])
+            except Exception:
+                self.sched.release(ref)
+                return _err(400, "invalid image data")
+            if not req.get("raw") or "[img-" not in prompt:      # server/routes.go: every image gets its [img-N] marker in front of the prompt
+                prompt = "".join(f"[img-{i}]" for i in range(len(media))) + prompt
         if prompt == "" and not req.get("context"):
             self.sched.release(ref)
             return JSONResponse({"model": name, "created_at": _now(), "response": "", "done": True, "done_reason": "load"})
@@ -318,7 +343,7 @@ class Server:
                                  num_keep=opts["num_keep"], stop=list(opts.get("stop") or []), grammar=grammar,
                                  grammar_after="" if req.get("raw") else self._grammar_gate(rend, grammar, think, text),
                                  truncate=req.get("truncate", True) is not False, shift=req.get("shift", True) is not False,
-                                 preserved_tokens=rend.is_harmony)
+                                 preserved_tokens=rend.is_harmony, images=media if isinstance(tokens, str) else [])
         tp = self._thinking_parser(rend, think, text) if not req.get("raw") else None
         hp = harmony.HarmonyParser(rend.names) if rend.is_harmony and not req.get("raw") else None
         bp = parser_for(model.config.get("parser"), None, think) if hp is None and not req.get("raw") else None
@@ -441,6 +466,22 @@ class Server:
             return _err(400, str(e))
         rend = self._renderer(model, runner)
         msgs = list(model.messages) + [{**m, "role": str(m.get("role", "")).lower()} for m in messages]     # roles compare in lower case
+        media: list[bytes] = []
+        if any(m.get("images") for m in msgs):
+            refusal = self._refuse_images(model, True, runner)
+            if refusal is not None:
+                self.sched.release(ref)
+                return refusal
+            from ..text.renderers import image_tagged
+            try:
+                for i, m in enumerate(msgs):        # every image gets its [img-N] marker in the message it came with (server/prompt.go:96-133)
+                    imgs = m.get("images") or []
+                    if imgs:
+                        msgs[i] = {**m, "content": image_tagged(m.get("content", "") or "", len(imgs), len(media))}
+                        media += self._image_bytes(imgs)
+            except Exception:
+                self.sched.release(ref)
+                return _err(400, "invalid image data")
         if model.system and not any(m.get("role") == "system" for m in msgs):
             msgs.insert(0, {"role": "system", "content": model.system})
         if think == "max" and rend.is_harmony:
@@ -451,7 +492,9 @@ class Server:
                 if m.get("role") == "assistant" and "</think>" in m.get("content", ""):
                     m["content"] = m["content"].split("</think>", 1)[1].lstrip()
         try:
-            text, _ = chat_prompt(lambda ms: rend.render_chat(ms, tools, think), lambda s: len(runner.tokenize(s, add_special=True)),
+            # an image counts as 768 tokens when the conversation is cut to fit (server/prompt.go:29-33)
+            text, _ = chat_prompt(lambda ms: rend.render_chat(ms, tools, think),
+                                  lambda s: len(runner.tokenize(s, add_special=True)) + 768 * s.count("[img-"),
                                   msgs, runner.n_ctx, req.get("truncate", True) is not False)
         except TemplateError as e:
             self.sched.release(ref)
@@ -466,7 +509,7 @@ class Server:
         creq = CompletionRequest(prompt=text, sampling=self._sampling(opts, bool(req.get("logprobs")), top_lp), num_predict=opts["num_predict"],
                                  num_keep=opts["num_keep"], stop=list(opts.get("stop") or []), grammar=grammar, grammar_after=gate,
                                  truncate=req.get("truncate", True) is not False, shift=req.get("shift", True) is not False,
-                                 preserved_tokens=rend.is_harmony)
+                                 preserved_tokens=rend.is_harmony, images=media)
         hp = harmony.HarmonyParser(rend.names) if rend.is_harmony else None
         prefill = msgs[-1].get("content", "") if msgs and msgs[-1].get("role") == "assistant" else ""
         bp = parser_for(model.config.get("parser"), tools, think, prefill) if hp is None else None

@@ -335,3 +335,117 @@ def test_safetensors_reader_survives_corrupted_headers(tmp_path):
         except SafetensorsError:
             pass
     assert 0 < opened < 800
+
+
+def _tiny_gemma3_vision(path):
+    """A random multimodal gemma3 checkpoint (2-layer text model, 2-layer SigLIP tower on 56 x 56 images, 4 image tokens)."""
+    transformers = pytest.importorskip("transformers")
+    torch.manual_seed(0)
+    tc = dict(vocab_size=64, hidden_size=64, intermediate_size=96, num_hidden_layers=2, num_attention_heads=4, num_key_value_heads=2,
+              head_dim=16, max_position_embeddings=128, rms_norm_eps=1e-6, sliding_window=8, query_pre_attn_scalar=16)
+    vc = dict(hidden_size=32, intermediate_size=64, num_hidden_layers=2, num_attention_heads=4, image_size=56, patch_size=14, num_channels=3)
+    cfg = transformers.Gemma3Config(text_config=tc, vision_config=vc, mm_tokens_per_image=4, image_token_index=60, boi_token_index=61,
+                                    eoi_token_index=62)
+    model = transformers.Gemma3ForConditionalGeneration(cfg).float().eval()
+    with torch.no_grad():
+        for n, p in model.named_parameters():
+            if "norm" in n or "bias" in n:
+                p.normal_(0, 0.3)
+            if "mm_input_projection" in n:          # zero-initialised in the library: every image would project to nothing
+                p.normal_(0, 0.2)
+    model.save_pretrained(path, safe_serialization=True)
+    _tiny_tokenizer(str(path))
+    return model
+
+
+def _png(seed: int, w: int = 100, h: int = 80) -> bytes:
+    import io
+
+    import numpy as np
+    from PIL import Image
+    buf = io.BytesIO()
+    Image.fromarray((np.random.RandomState(seed).rand(h, w, 3) * 255).astype("uint8")).save(buf, format="PNG")
+    return buf.getvalue()
+
+
+def test_gemma3_image_input_matches_transformers(tmp_path):
+    """A multimodal gemma3 checkpoint keeps its vision tower through the conversion; the tower + projector give the image
+    features of the transformers model, and a prompt with the image in it (embedding rows in place of the soft tokens, the
+    image positions attending to each other in both directions) gives its logits."""
+    src = tmp_path / "hf"
+    model = _tiny_gemma3_vision(src)
+    out = str(tmp_path / "m.gguf")
+    kv = convert_hf(str(src), out, outtype="f32")
+    assert kv["gemma3.vision.block_count"] == 2 and kv["gemma3.vision.image_size"] == 56 and kv["gemma3.mm.tokens_per_image"] == 4
+    from ollama_b200.engine.backend import TorchBackend, open_model
+    from ollama_b200.models.vision import load_tower, preprocess
+    g = open_model(out)
+    assert g.has("v.patch_embedding.weight") and g.has("mm.mm_input_projection.weight") and g.has("v.blk.1.mlp.fc2.bias")
+    tower = load_tower(g)
+    data = _png(0)
+    px = preprocess(data, 56)
+    assert px.shape == (3, 56, 56) and -1.0 <= float(px.min()) and float(px.max()) <= 1.0
+    emb = tower.encode(data)
+    with torch.no_grad():
+        feats = model.get_image_features(pixel_values=px[None])
+    feats = feats if torch.is_tensor(feats) else getattr(feats, "pooler_output", feats[0])
+    assert emb.shape == (4, 64) and torch.allclose(emb, feats.reshape(4, 64), atol=1e-5) and float(emb.abs().mean()) > 0.05
+    ids = [5, 7, 61, 60, 60, 60, 60, 62, 9, 11, 13]
+    with torch.no_grad():
+        ref = model(input_ids=torch.tensor([ids]), pixel_values=px[None], token_type_ids=torch.tensor([[int(t == 60) for t in ids]])).logits[0, -1]
+    be = TorchBackend(g, "cpu")
+    be.alloc(1, 64)
+    rows = [i for i, t in enumerate(ids) if t == 60]
+    toks = [-(1 + i) if t == 60 else t for i, t in enumerate(ids)]
+    got = be.prefill(0, toks, 0, embeds=(rows, emb), spans=[(rows[0], rows[-1] + 1)])
+    assert torch.allclose(got, ref, atol=2e-5), (got - ref).abs().max()
+    causal_only = be.prefill(0, toks, 0, embeds=(rows, emb))
+    assert (causal_only - ref).abs().max() > 1e-4            # the two-way attention inside the image is part of the model
+
+
+def test_chat_with_images_through_the_api(tmp_path, monkeypatch):
+    """POST /api/chat with ``images``: the vision model answers, the prompt count includes the image's positions, another
+    image changes the first token's distribution, and a text-only model still refuses images with 400."""
+    import base64
+    import hashlib
+
+    from starlette.testclient import TestClient
+    monkeypatch.setenv("OLLAMA_MODELS", str(tmp_path / "store"))
+    monkeypatch.setenv("B200_DEVICE", "cpu")
+    monkeypatch.setenv("OLLAMA_CONTEXT_LENGTH", "128")
+    src = tmp_path / "hf"
+    _tiny_gemma3_vision(src)
+    from ollama_b200.server.routes import create_app
+    with TestClient(create_app()) as c:
+        files = {}
+        for n in sorted(os.listdir(src)):
+            data = open(src / n, "rb").read()
+            digest = "sha256:" + hashlib.sha256(data).hexdigest()
+            assert c.post(f"/api/blobs/{digest}", content=data).status_code in (200, 201)
+            files[n] = digest
+        r = c.post("/api/create", json={"model": "g3v", "files": files, "template": "{{ .Prompt }}", "stream": False})
+        assert r.status_code == 200 and r.json()["status"] == "success", r.text
+        info = c.post("/api/show", json={"model": "g3v"}).json()
+        assert "vision" in info["capabilities"] and info["model_info"]["gemma3.vision.block_count"] == 2
+        ask = lambda images, content="abab": c.post("/api/chat", json={                                  # noqa: E731
+            "model": "g3v", "messages": [{"role": "user", "content": content, "images": images}], "stream": False, "logprobs": True,
+            "top_logprobs": 3, "options": {"num_predict": 2, "temperature": 0}})
+        plain = c.post("/api/chat", json={"model": "g3v", "messages": [{"role": "user", "content": "abab"}], "stream": False,
+                                          "options": {"num_predict": 2, "temperature": 0}}).json()
+        one = ask([base64.b64encode(_png(1)).decode()])
+        assert one.status_code == 200, one.text
+        one = one.json()
+        assert one["done"] and one["eval_count"] == 2
+        assert one["prompt_eval_count"] >= plain["prompt_eval_count"] + 4         # four image positions (this toy vocabulary has no line break)
+        other = ask([base64.b64encode(_png(2)).decode()]).json()
+        lp = lambda r: [round(t["logprob"], 4) for t in r["logprobs"][0]["top_logprobs"]]                 # noqa: E731
+        assert lp(one) != lp(other)
+        again = ask([base64.b64encode(_png(1)).decode()]).json()
+        assert lp(again) == lp(one)
+        placed = ask([base64.b64encode(_png(1)).decode()], "ab [img] ab").json()
+        assert placed["done"] and lp(placed) != lp(one)
+        bad = ask(["bm90IGFuIGltYWdl"])
+        assert bad.status_code == 400 and "image" in bad.json()["error"]
+        gen = c.post("/api/generate", json={"model": "g3v", "prompt": "abab", "images": [base64.b64encode(_png(1)).decode()], "stream": False,
+                                            "options": {"num_predict": 2, "temperature": 0}})
+        assert gen.status_code == 200 and gen.json()["prompt_eval_count"] == one["prompt_eval_count"], gen.text

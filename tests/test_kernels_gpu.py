@@ -663,6 +663,39 @@ def test_prefill_of_several_sequences_in_one_pass(tmp_path, spec):
     many.close()
 
 
+@pytest.mark.parametrize("spec,kv_type", [("tiny-gemma3", "f16"), ("tiny-qwen3", "q8_0")])
+def test_prefill_with_image_rows_on_the_engine(tmp_path, spec, kv_type):
+    """Rows of a prompt whose input is a given embedding (an image's projected features) and whose positions attend to each
+    other in both directions: the engine's logits, and the decode step after them, follow the fp32 graph's; the same prompt
+    without the two-way span gives different logits."""
+    from ollama_b200.engine.b200 import B200Backend
+    from ollama_b200.engine.backend import TorchBackend, open_model
+    from ollama_b200.models.synth import write_synthetic_gguf
+    p = str(tmp_path / "m.gguf")
+    write_synthetic_gguf(p, spec, "F16")
+    ref, eng = TorchBackend(open_model(p), "cpu"), B200Backend(open_model(p), "cuda", kv_type=kv_type)
+    g = torch.Generator().manual_seed(4)
+    toks = torch.randint(259, 4096, (60,), generator=g).tolist()
+    rows = list(range(20, 36))
+    for r in rows:
+        toks[r] = -(1 + r)
+    emb = torch.randn(len(rows), ref.cfg.d_model, generator=g) * 0.5
+    spans = [(20, 36)]
+    for e in (ref, eng):
+        e.alloc(1, 128)
+    a = ref.prefill(0, toks, 0, embeds=(rows, emb), spans=spans)
+    b = eng.prefill(0, toks, 0, embeds=(rows, emb.cuda()), spans=spans).float().cpu()
+    tol = 0.05 * a.abs().max().item()
+    assert (a - b).abs().max().item() < tol
+    a1, b1 = ref.decode([0], [7], [60])[0], eng.decode([0], [7], [60])[0].float().cpu()
+    assert (a1 - b1).abs().max().item() < 0.05 * a1.abs().max().item()
+    # in two chunks, the second one starting inside the prompt but after the image: the cached image rows are used as they are
+    eng.prefill(0, toks[:40], 0, need_logits=False, embeds=(rows, emb.cuda()), spans=spans)
+    c = eng.prefill(0, toks[40:], 40, spans=spans).float().cpu()
+    assert (a - c).abs().max().item() < tol
+    eng.close()
+
+
 def test_phi3_checkpoint_with_fused_matrices_on_the_engine(tmp_path):
     """A converted Phi-3 checkpoint (Q | K | V and gate | up stored fused, long-context rotary factors and attention factor)
     runs on the sm_100a engine through row-range views of the fused tensors and agrees with the fp32 graph."""
