@@ -96,6 +96,7 @@ class B200Backend:
         # Decode matrices in unit order for the streaming GEMV (Q4_K / Q6_K layers without experts or sandwich norms); B200_SK=0
         # keeps every layer on the dp4a kernels.
         # Subclasses that enqueue their own decode kernels (tensor parallelism) keep the dp4a planes.
+        self.moe_stream_q = os.environ.get("B200_MOE_STREAM_Q", "1") != "0"    # MoE prefill reads MXFP4 experts as they are (no 16-bit expansion per chunk)
         self.fuse_rope = os.environ.get("B200_FUSE_ROPE", "1") != "0"      # decode attention rotates Q / K and appends K / V itself
         self.use_sk = os.environ.get("B200_SK", "1") != "0" and not self.cfg.sandwich_norm and type(self) is B200Backend
         self.max_batch = MAX_DECODE_BATCH
@@ -381,6 +382,13 @@ class B200Backend:
         self._route(logits.contiguous(), T, ids, lids, wts, False)
         row, tile_expert, rows = K.moe_plan(lids, self.e_cnt)
         xs = K.moe_gather(h, row, k, rows)
+        if self.moe_stream_q and getattr(L.gu, "bf16", None) is None and K.gemm_q_grouped_supported(L.gu) and K.gemm_q_grouped_supported(L.down):
+            # experts without a resident 16-bit copy: the grouped kernel streams their 4-bit blocks and expands them itself
+            f = K.gemm_q_grouped(xs, L.gu, tile_expert, glu=c.act, alpha=c.swiglu_alpha, limit=c.swiglu_limit)
+            ys = K.gemm_q_grouped(f, L.down, tile_expert) if f is not None else None
+            if ys is not None:
+                self.kernel_launches += 6
+                return K.moe_scatter_combine(ys, row, wts, T, k)
         gu16 = getattr(L.gu, "bf16", None)
         if gu16 is None:
             gu16 = K.dequant_to_bf16(L.gu)                        # all resident experts at once: scratch until the call returns

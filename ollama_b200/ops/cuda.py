@@ -580,7 +580,7 @@ def attn_prefill_tc_status(clear: bool = False) -> int:
 
 def gemm_status() -> int:
     """0 = ok; 1 = a bounded wait inside a tensor-core kernel (the GEMMs, the tcgen05 attention) expired."""
-    return int(lib().b2_gemm_status()) | int(lib().b2_gemm_q_status()) | int(lib().b2_attn_prefill_tc_status())
+    return int(lib().b2_gemm_status()) | int(lib().b2_gemm_q_status()) | int(lib().b2_attn_prefill_tc_status()) | int(lib().b2_gemm_q_grouped_status())
 
 
 GEMM_Q_TYPES = {WT_Q4_K, WT_Q6_K, WT_Q8_0, WT_BF16, WT_F16}
@@ -660,6 +660,33 @@ def gemm_bf16_grouped(a: torch.Tensor, b: torch.Tensor, experts: int, tile_exper
                   C.c_float, C.c_void_p]
     _check(f(ptr(a), ptr(b), m, n, k, experts, ptr(tile_expert), ptr(out), out.stride(0), ptr(bias), _ACT[glu] if glu else -1, alpha, limit,
              stream()), "gemm_bf16_grouped")
+    return out
+
+
+def gemm_q_grouped_supported(w: DevWeight) -> bool:
+    """True when the expert stack ``w`` can be streamed in its own encoding by :func:`gemm_q_grouped` (MXFP4, k % 64 == 0)."""
+    return w.wtype == WT_MXFP4 and w.k % 64 == 0 and w.n % 8 == 0
+
+
+def gemm_q_grouped(a: torch.Tensor, w: DevWeight, tile_expert: torch.Tensor, glu: str | None = None, alpha: float = 1.702,
+                   limit: float = 7.0) -> torch.Tensor | None:
+    """The grouped product of :func:`gemm_bf16_grouped` with the experts read as MXFP4 blocks and expanded inside the kernel
+    (kernels/gemm_q_grouped.cu).  ``w``: the stacked experts (``w.experts`` matrices of ``w.n`` rows, with their biases).
+    Returns fp32 [m, n], with ``glu`` bf16 [m, n / 2], or None when the kernel does not take the encoding or shape (nothing
+    was launched)."""
+    m, k = a.shape
+    n, experts = w.n, max(w.experts, 1)
+    if a.dtype != torch.bfloat16 or k != w.k or m % 128 or not gemm_q_grouped_supported(w):
+        return None
+    a = a.contiguous()
+    out = torch.empty(m, n // 2, device=a.device, dtype=torch.bfloat16) if glu else torch.empty(m, n, device=a.device, dtype=torch.float32)
+    d = w.desc()
+    f = lib().b2_gemm_q_grouped
+    f.argtypes = [C.c_void_p, C.c_int, C.c_void_p, C.c_int, C.c_void_p, C.c_void_p, C.c_int, C.c_void_p, C.c_int, C.c_float, C.c_float, C.c_void_p]
+    rc = f(ptr(a), m, C.addressof(d), experts, ptr(tile_expert), ptr(out), out.stride(0), d.bias, _ACT[glu] if glu else -1, alpha, limit, stream())
+    if rc == 801:
+        return None
+    _check(rc, "gemm_q_grouped")
     return out
 
 

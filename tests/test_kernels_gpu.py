@@ -552,6 +552,30 @@ def test_engine_prefill_gemm_modes(tmp_path, mode, keep):
     assert K_status_ok()
 
 
+@pytest.mark.parametrize("stream_q", ["1", "0"])
+def test_engine_moe_prefill_on_mxfp4_experts(tmp_path, monkeypatch, stream_q):
+    """gpt-oss prefill without a resident 16-bit copy of the experts: the grouped kernel that streams the MXFP4 blocks (and, with
+    the switch off, the expand-per-chunk path) agree with the fp32 graph."""
+    from ollama_b200.engine.b200 import B200Backend
+    from ollama_b200.engine.backend import TorchBackend, open_model
+    from ollama_b200.models.synth import write_synthetic_gguf
+    monkeypatch.setenv("B200_MOE_STREAM_Q", stream_q)
+    p = str(tmp_path / "m.gguf")
+    write_synthetic_gguf(p, "tiny-gpt-oss", "MXFP4")
+    g = open_model(p)
+    ref, eng = TorchBackend(g, "cpu"), B200Backend(g, "cuda", keep_bf16=False)
+    assert eng.moe_stream_q == (stream_q == "1")
+    ref.alloc(1, 256)
+    eng.alloc(1, 256)
+    prompt = torch.randint(259, 4096, (150,), generator=torch.Generator().manual_seed(5)).tolist()
+    lr = ref.prefill(0, prompt, 0)
+    n0 = eng.kernel_launches
+    le = eng.prefill(0, prompt, 0).cpu()
+    assert (le - lr).abs().max().item() < 0.05 * lr.abs().max().item()
+    assert K_status_ok() and eng.kernel_launches > n0
+    eng.close()
+
+
 def K_status_ok() -> bool:
     return _K().gemm_status() == 0
 
@@ -870,6 +894,39 @@ def test_grouped_gemm_and_moe_plan(glu):
                 ref[p // k] += wts[p] * out[int(row_c[p])]
         assert torch.allclose(comb, ref, atol=1e-4, rtol=1e-4)
     assert K.gemm_status() == 0
+
+
+@pytest.mark.parametrize("glu", [None, "swiglu_oai"])
+@pytest.mark.parametrize("E,n,k,T", [(8, 256, 320, 300), (32, 192, 2880, 500), (4, 2880 // 4 * 2, 512, 1100)])
+def test_grouped_gemm_over_mxfp4_experts(glu, E, n, k, T):
+    """The grouped kernel that streams MXFP4 expert blocks and expands them itself, against the product with the dequantised
+    experts: partial N tiles, experts with no row, experts with several tiles, bias, gated epilogue."""
+    K = _K()
+    g = torch.Generator().manual_seed(E + n)
+    topk = 2
+    lids = torch.randint(-1, E, (T * topk,), generator=g).to(torch.int32)
+    lids[lids == 1] = 0                                           # expert 1 gets no row, expert 0 twice the share
+    h = (torch.randn(T, k, generator=g) * 0.5).to(torch.bfloat16)
+    qw = QWeight.from_float("w", torch.randn(E, n, k, generator=g) * 0.05, GGMLType.MXFP4)
+    bias = torch.randn(E * n, generator=g) * 0.1
+    dw = K.repack(qw, "cuda", bias=bias)
+    assert dw.experts == E and K.gemm_q_grouped_supported(dw)
+    row, te, rows = K.moe_plan(lids.cuda(), E)
+    xs = K.moe_gather(h.cuda(), row, topk, rows)
+    out = K.gemm_q_grouped(xs, dw, te, glu=glu)
+    assert out is not None
+    torch.cuda.synchronize()
+    assert K.gemm_status() == 0
+    out, row_c = out.cpu().float(), row.cpu()
+    wf = qw.dequant().view(E, n, k)
+    for p in torch.randperm(T * topk, generator=g)[:150].tolist():
+        e = int(lids[p])
+        if e < 0:
+            continue
+        y = h[p // topk].float() @ wf[e].t() + bias[e * n:(e + 1) * n]
+        ref = R.glu(y[0::2], y[1::2], glu) if glu else y
+        got = out[int(row_c[p])]
+        assert torch.allclose(got, ref, atol=2e-2 * ref.abs().max().item() + 1e-3, rtol=2e-2), (p, e, (got - ref).abs().max())
 
 
 def test_dense_gemm_with_gated_epilogue():
