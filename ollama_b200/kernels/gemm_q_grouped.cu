@@ -5,10 +5,10 @@
 // tile -> expert table on the device).  A 16-bit copy of the experts would have to be streamed from HBM for every chunk
 // (3.8 x the bytes of the MXFP4 blocks, and it does not fit beside them for the large models), so this kernel reads the
 // blocks themselves.  One CTA = one 128-row tile x 128 weight rows of that tile's expert:
-//   * warp 0 brings the activation tile of every K block (64 columns) by TMA into a 4-stage ring;
+//   * warp 0 brings the activation tile of every K block (64 columns) by TMA into a 2-stage ring (two CTAs share an SM);
 //   * warps 2-9 stream the weight bytes: each thread owns 32 columns of one weight row per K block (16 bytes of nibbles and
-//     one E8M0 scale), keeps eight K blocks in flight with cp.async into a private shared-memory ring (enough bytes per SM to
-//     cover HBM latency), turns the codes into bf16 with shifts and two packed multiplies (the 3 magnitude bits dropped into
+//     one E8M0 scale), keeps six K blocks in flight with cp.async into a private shared-memory ring (enough bytes per SM to
+//     cover HBM latency), turns the codes into bf16 with one integer multiply, one mask and one packed multiply per pair (the 3 magnitude bits dropped into
 //     the exponent / mantissa of a bf16 are 2^-126 times the value, subnormals included) and writes them into the stage buffer
 //     in the 128-byte-swizzled K-major layout the tensor core reads;
 //   * warp 1 issues tcgen05.mma (M 128 x N 128 x K 16, bf16) into a TMEM accumulator;
@@ -25,8 +25,8 @@ namespace {
 
 using namespace tc;
 constexpr int BN = 128;
-constexpr int STAGES = 4;
-constexpr int DEPTH = 8;                       // K blocks of weight bytes in flight per thread
+constexpr int STAGES = 2;
+constexpr int DEPTH = 6;                       // K blocks of weight bytes in flight per thread
 constexpr int A_BYTES = BM * BK * 2, B_BYTES = BN * BK * 2;
 constexpr int DEQ_WARPS = 8;
 constexpr int THREADS = (2 + DEQ_WARPS) * 32;
@@ -57,17 +57,20 @@ __device__ __forceinline__ uint32_t pack2(float lo, float hi) {
     return *reinterpret_cast<const uint32_t*>(&v);
 }
 
-// Four E2M1 codes, one per byte of `codes` (sign in bit 3) -> two bf16x2 words of value * scale.
-// The magnitude bits EEM shifted to bits 8..6 of a bf16 read as 2^(E-127) (1 + M/2), or M 2^-127 for E = 0: the E2M1 value times
-// 2^-126 in every case.  `k126` = bf16x2 2^126 brings it back exactly; `scale2` = bf16x2 2^(e-127).
-__device__ __forceinline__ void expand_fp4x4(uint32_t codes, uint32_t k126, uint32_t scale2, uint32_t& w01, uint32_t& w23) {
-    const uint32_t c01 = __byte_perm(codes, 0u, 0x4140) << 6, c23 = __byte_perm(codes, 0u, 0x4342) << 6;      // {c0, 0, c1, 0} << 6
-    const uint32_t b01 = (c01 & 0x01C001C0u) | ((c01 & 0x02000200u) << 6), b23 = (c23 & 0x01C001C0u) | ((c23 & 0x02000200u) << 6);
-    w01 = mul_bf16x2(mul_bf16x2(b01, k126), scale2);
-    w23 = mul_bf16x2(mul_bf16x2(b23, k126), scale2);
+// Four E2M1 codes, one per byte of `codes` (sign in bit 3) -> two bf16x2 words of value * 2^(e-127).
+// A code c spread over a 16-bit lane and multiplied by 0x1040 is (c << 6) + (c << 12): the magnitude bits EEM land in bits 8..6
+// and the sign in bit 15 (mask 0x81C0 drops the rest).  Read as bf16 that is 2^(E-127) (1 + M/2), or M 2^-127 for E = 0: the E2M1
+// value times 2^-126 in every case, subnormal or not.  One packed multiply by `mult2` = bf16x2 2^(e-1) restores the value and
+// applies the block scale (exact: a power of two); blocks with e > 128 (scales above 2, which 2^(e-1) cannot hold next to the
+// 2^126) take two multiplies, by 2^126 and by 2^(e-127).
+__device__ __forceinline__ void expand_fp4x4(uint32_t codes, uint32_t mult2, uint32_t& w01, uint32_t& w23) {
+    const uint32_t b01 = (__byte_perm(codes, 0u, 0x4140) * 0x1040u) & 0x81C081C0u;      // {c0, 0, c1, 0}
+    const uint32_t b23 = (__byte_perm(codes, 0u, 0x4342) * 0x1040u) & 0x81C081C0u;
+    w01 = mul_bf16x2(b01, mult2);
+    w23 = mul_bf16x2(b23, mult2);
 }
 
-__global__ void __launch_bounds__(THREADS, 1) gemm_q_grouped_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ QGroupedParams p) {
+__global__ void __launch_bounds__(THREADS, 2) gemm_q_grouped_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ QGroupedParams p) {
     const int mt = blockIdx.y;
     const int e = p.tile_expert[mt];
     if (e < 0) return;                                   // padding of the tile table: the whole CTA leaves before it owns anything
@@ -149,7 +152,6 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_q_grouped_kernel(const __grid
         }
     } else {
         bool ok = true;
-        const uint32_t k126 = 0x7E807E80u;                   // bf16x2 2^126
         for (int kb = 0; kb < k_blocks && ok; kb++) {
             const int s = kb % STAGES;
             const int nxt = kb + DEPTH - 1;
@@ -157,15 +159,22 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_q_grouped_kernel(const __grid
             asm volatile("cp.async.commit_group;" ::: "memory");
             asm volatile("cp.async.wait_group %0;" ::"n"(DEPTH - 1) : "memory");
             const uint4 q = my_ring[(kb % DEPTH) * (DEQ_WARPS * 32)];
-            const uint32_t ebits = (uint32_t)scales[r * p.scale_pitch + 2 * kb + h] << 7;      // bf16 2^(e - 127); e = 0 reads as zero
-            const uint32_t scale2 = ebits | (ebits << 16);
+            const uint32_t eb = scales[r * p.scale_pitch + 2 * kb + h];                     // E8M0: the block scale is 2^(eb - 127)
+            const bool wide = eb > 128u;
+            const uint32_t m1 = wide ? 0x7E80u : (eb == 0u ? 0u : (eb + 126u) << 7);           // bf16 2^126, or 2^(eb - 1) (eb = 0 reads as zero)
+            const uint32_t mult2 = m1 | (m1 << 16);
             // byte j of the 16: low nibble = column j, high nibble = column 16 + j of this thread's 32
             const uint32_t qw[4] = {q.x, q.y, q.z, q.w};
             uint32_t vals[16];
 #pragma unroll
             for (int i = 0; i < 4; i++) {
-                expand_fp4x4(qw[i] & 0x0f0f0f0fu, k126, scale2, vals[2 * i], vals[2 * i + 1]);
-                expand_fp4x4((qw[i] >> 4) & 0x0f0f0f0fu, k126, scale2, vals[8 + 2 * i], vals[8 + 2 * i + 1]);
+                expand_fp4x4(qw[i] & 0x0f0f0f0fu, mult2, vals[2 * i], vals[2 * i + 1]);
+                expand_fp4x4((qw[i] >> 4) & 0x0f0f0f0fu, mult2, vals[8 + 2 * i], vals[8 + 2 * i + 1]);
+            }
+            if (wide) {                                   // rare: scales above 2
+                const uint32_t s1 = eb << 7, s2 = s1 | (s1 << 16);
+#pragma unroll
+                for (int i = 0; i < 16; i++) vals[i] = mul_bf16x2(vals[i], s2);
             }
             if (kb >= STAGES) ok = mbar_wait(&empty[s], ((kb / STAGES) - 1) & 1);
             if (ok) {

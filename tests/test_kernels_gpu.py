@@ -908,6 +908,10 @@ def test_grouped_gemm_over_mxfp4_experts(glu, E, n, k, T):
     lids[lids == 1] = 0                                           # expert 1 gets no row, expert 0 twice the share
     h = (torch.randn(T, k, generator=g) * 0.5).to(torch.bfloat16)
     qw = QWeight.from_float("w", torch.randn(E, n, k, generator=g) * 0.05, GGMLType.MXFP4)
+    if E == 8:          # block scales from 2^-9 to 2^7: both ways of applying them, and codes of every magnitude next to each other
+        blocks = qw.raw.view(-1, 17)
+        blocks[:, 0] = torch.randint(118, 135, (blocks.shape[0],), generator=g).to(torch.uint8)
+        h = h * 0.02
     bias = torch.randn(E * n, generator=g) * 0.1
     dw = K.repack(qw, "cuda", bias=bias)
     assert dw.experts == E and K.gemm_q_grouped_supported(dw)
