@@ -2,7 +2,7 @@
 
 Older published blobs differ from today's key and tensor names; the reference fixes them while
 loading (llama/compat/llama-ollama-compat.cpp:3239-3286 dispatches per architecture; gpt-oss rules
-at :1510-1555, gemma3 at :237-275, llama3 tokenizer metadata at :1334-1355, qwen2.5-vl at :1776-1840, qwen3-vl at
+at :1510-1555, gemma3 at :237-275, llama3 tokenizer metadata at :1334-1355, mistral3 at :1643-1665, qwen2.5-vl at :1776-1840, qwen3-vl at
 :1846-1868).  Here the same rules are a table applied to the opened :class:`GGUFFile` (nothing is written back to disk).
 Vision-language checkpoints of the Qwen family are read as their text model: the decoder has the tensor names and key
 names of qwen2 / qwen3 / qwen3moe under another prefix, and its multi-axis rotary embedding gives every axis the same
@@ -52,7 +52,7 @@ def _rename_tensors(g: GGUFFile, rules) -> None:
 
 
 # architecture of a vision-language checkpoint -> the text architecture its decoder is
-_TEXT_ARCH = {"qwen25vl": "qwen2", "qwen2vl": "qwen2", "qwen3vl": "qwen3", "qwen3vlmoe": "qwen3moe"}
+_TEXT_ARCH = {"qwen25vl": "qwen2", "qwen2vl": "qwen2", "qwen3vl": "qwen3", "qwen3vlmoe": "qwen3moe", "mistral3": "llama"}
 
 
 def _row_views(g: GGUFFile, fused: str, parts: list[tuple[str, int]]) -> None:
@@ -104,6 +104,15 @@ def normalise(g: GGUFFile) -> GGUFFile:
     arch = g.kv.get("general.architecture", "")
     if arch == "phi3":
         _phi3(g)
+    if arch == "mistral3":
+        # llama/compat/llama-ollama-compat.cpp:1643-1665: YaRN keys under their current names, the tekken pre-tokenizer as default.
+        # The decoder is llama's; its attention temperature (a factor on the queries that grows with log(position / trained
+        # context)) is 1 inside the trained context and is not applied beyond it.
+        for old, new in (("beta_fast", "yarn_beta_fast"), ("beta_slow", "yarn_beta_slow")):
+            if f"mistral3.rope.scaling.{old}" in g.kv:
+                g.kv.setdefault(f"mistral3.rope.scaling.{new}", g.kv[f"mistral3.rope.scaling.{old}"])
+        if g.kv.get("tokenizer.ggml.pre", "default") in ("", "default"):
+            g.kv["tokenizer.ggml.pre"] = "tekken"
     if arch in _TEXT_ARCH:
         text = _TEXT_ARCH[arch]
         g.kv["general.source_architecture"] = arch

@@ -391,3 +391,44 @@ def test_vision_language_checkpoint_runs_as_its_text_model(tmp_path):
         finally:
             r.close()
     assert out[0] == out[1] and len(out[0]) == 6
+
+
+def test_mistral3_blob_runs_on_the_llama_decoder(tmp_path):
+    """llama/compat/llama-ollama-compat.cpp:1643-1665: a mistral3 blob (keys under ``mistral3.``, YaRN betas under their older
+    names, no pre-tokenizer id, vision tensors embedded) is loaded as the llama decoder it is; the tokens equal those of the plain
+    llama file with the same weights, the pre-tokenizer defaults to tekken and the YaRN keys are found under their current names."""
+    import numpy as np
+
+    from ollama_b200.engine.backend import open_model
+    from ollama_b200.gguf.reader import open_gguf
+    from ollama_b200.gguf.writer import WriteTensor, write_gguf
+    from ollama_b200.models.synth import write_synthetic_gguf
+    from ollama_b200.text.tokenizer import PRETOKENIZERS
+    plain, m3 = str(tmp_path / "l.gguf"), str(tmp_path / "m3.gguf")
+    write_synthetic_gguf(plain, "tiny-llama", "F32")
+    g = open_gguf(plain)
+    kv = {}
+    for k, v in g.kv.items():
+        kv["mistral3." + k[len("llama."):] if k.startswith("llama.") else k] = v
+    kv["general.architecture"] = "mistral3"
+    kv["mistral3.rope.scaling.beta_fast"] = 32.0
+    kv["mistral3.rope.scaling.beta_slow"] = 1.0
+    kv.pop("tokenizer.ggml.pre", None)
+    tensors = [WriteTensor(n, tuple(t.shape), t.dtype, np.array(g.tensor_bytes(n))) for n, t in g.tensors.items()]
+    f32 = g.tensors["output_norm.weight"].dtype
+    tensors.append(WriteTensor("v.patch_conv.weight", (4, 4), f32, np.zeros(16, dtype=np.float32).view(np.uint8)))
+    write_gguf(m3, kv, tensors)
+    gm = open_model(m3)
+    assert gm.architecture == "llama" and gm.kv["tokenizer.ggml.pre"] == "tekken" and gm.kv["llama.rope.scaling.yarn_beta_fast"] == 32.0
+    assert not gm.has("v.patch_conv.weight")
+    import regex
+    pieces = [m.group(0) for m in regex.compile(PRETOKENIZERS["tekken"][0]).finditer("Hello WORLD don't 1234\n\n x")]
+    assert pieces == ["Hello", " WORLD", " don", "'t", " ", "1", "2", "3", "4", "\n\n", " x"]
+    out = []
+    for path in (plain, m3):
+        r = Runner(path, RunnerOptions(num_ctx=64, device="cpu"))
+        try:
+            out.append(_tokens(r, 6, prompt=list(range(300, 316)))[0])
+        finally:
+            r.close()
+    assert out[0] == out[1]
