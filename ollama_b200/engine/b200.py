@@ -41,7 +41,7 @@ def supports(cfg: ModelConfig) -> bool:
         return False
     return cfg.arch in ("llama", "mistral", "qwen2", "qwen3", "qwen3moe", "gpt-oss", "gemma", "gemma2", "gemma3", "phi3") \
         and cfg.head_dim in (32, 64, 128, 256) and cfg.head_dim == cfg.v_head_dim and cfg.d_model % 32 == 0 \
-        and cfg.d_ff % 32 == 0
+        and (cfg.d_ff % 32 == 0 or cfg.is_moe)       # expert models have no dense FFN: its width (per rank, under a split) plays no part
 
 
 class _Layer:
