@@ -217,3 +217,23 @@ def test_pipe_transport_bounds_every_wait_and_tags_its_messages():
     parent.close()
     with pytest.raises(TransportError, match="leader gone"):
         f.bcast_ints(None, 6)
+
+
+def test_every_split_of_an_expert_model_passes_the_engine_support_check():
+    """gpt-oss-120b under 2, 4 and 8 ranks: the per-rank configuration (heads, KV heads, experts and the unused dense-FFN width
+    divided by the rank count) is one the sm_100a engine takes; a dense model whose FFN width per rank is not a multiple of 32
+    is still refused."""
+    import dataclasses
+
+    from ollama_b200.engine.b200 import supports
+    from ollama_b200.models.config import config_from_gguf
+    from ollama_b200.models.synth import synthetic_header
+    from ollama_b200.parallel.tp_engine import shard_plan
+    cfg = config_from_gguf(synthetic_header("gpt-oss-120b", "MXFP4"))
+    for world in (2, 4, 8):
+        p = shard_plan(cfg, world)
+        local = dataclasses.replace(cfg, n_heads=p["heads"], n_kv_heads=p["kv_heads"], d_ff=p["d_ff"], n_experts=p["experts"])
+        assert p["d_ff"] % 32 != 0 or world == 2
+        assert supports(local), world
+    dense = config_from_gguf(synthetic_header("llama-3.1-8b", "Q4_K_M"))
+    assert supports(dense) and not supports(dataclasses.replace(dense, d_ff=14336 // 8 + 8))
