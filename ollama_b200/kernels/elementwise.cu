@@ -226,8 +226,80 @@ __global__ void __launch_bounds__(128) rope_kv_kernel(const __grid_constant__ Ro
     }
 }
 
+// Prefill form of the kernel above: one CTA per token, a warp per head (eight heads in flight, the rest in turns).  The
+// sines and cosines of the token's position are computed once per token, not once per head (a chunk of 2048 tokens of a
+// 48-head model otherwise evaluates 6 M full-range sincosf), and nothing but the warp has to synchronise.
+__global__ void __launch_bounds__(256) rope_kv_rows_kernel(const __grid_constant__ RopeKvArgs a) {
+    const int t = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int H = a.n_heads, Hkv = a.n_kv_heads, hd = a.hd;
+    const int half_rot = a.n_rot >> 1;
+    __shared__ float s_cs[256], s_sn[256];
+    __shared__ float sh_all[8][512];
+    const int pos = a.positions[t], slot = a.slots[t];
+    for (int p = threadIdx.x; p < half_rot; p += 256) {
+        float sn, cs;
+        sincosf((float)pos * a.inv_freq[p], &sn, &cs);
+        s_cs[p] = cs * a.mscale;
+        s_sn[p] = sn * a.mscale;
+    }
+    __syncthreads();
+    float* sh = sh_all[warp];
+    for (int head = warp; head < H + 2 * Hkv; head += 8) {
+        const float* src = a.qkv + (size_t)t * (H + 2 * Hkv) * hd + (size_t)head * hd;
+        const bool is_q = head < H, is_k = !is_q && head < H + Hkv;
+        for (int i = lane; i < hd; i += 32) sh[i] = src[i];
+        __syncwarp();
+        const float* nw = is_q ? a.q_norm : (is_k ? a.k_norm : nullptr);
+        if (nw) {
+            float ss = 0.f;
+            for (int i = lane; i < hd; i += 32) ss += sh[i] * sh[i];
+            ss = warp_sum(ss);
+            const float inv = rsqrtf(ss / (float)hd + a.eps);
+            for (int i = lane; i < hd; i += 32) sh[i] = sh[i] * inv * nw[i];
+            __syncwarp();
+        }
+        if (is_q || is_k) {
+            for (int p = lane; p < half_rot; p += 32) {
+                const int i0 = a.neox ? p : 2 * p, i1 = a.neox ? p + half_rot : 2 * p + 1;
+                const float cs = s_cs[p], sn = s_sn[p];
+                const float x0 = sh[i0], x1 = sh[i1];
+                sh[i0] = x0 * cs - x1 * sn;
+                sh[i1] = x0 * sn + x1 * cs;
+            }
+            __syncwarp();
+        }
+        if (is_q) {
+            float* dst = a.q_out + ((size_t)t * H + head) * hd;
+            for (int i = lane; i < hd; i += 32) dst[i] = sh[i];
+        } else {
+            const int kvh = is_k ? head - H : head - H - Hkv;
+            const size_t rowi = ((size_t)slot * Hkv + kvh) * a.n_ctx + pos;
+            __half* sc = is_k ? a.k_scale : a.v_scale;
+            if (sc) {      // q8_0: the warp covers one block of 32 dims per trip (hd is a multiple of 32)
+                int8_t* dst = reinterpret_cast<int8_t*>(is_k ? a.k_cache : a.v_cache) + rowi * hd;
+                for (int i0 = 0; i0 < hd; i0 += 32) {
+                    const float v = sh[i0 + lane];
+                    const __half dh = __float2half_rn(warp_max(fabsf(v)) / 127.f);
+                    const float d = __half2float(dh);
+                    dst[i0 + lane] = (int8_t)(d > 0.f ? max(-127, min(127, __float2int_rn(v / d))) : 0);
+                    if (lane == 0) sc[rowi * (hd >> 5) + (i0 >> 5)] = dh;
+                }
+            } else {
+                __half* dst = (is_k ? a.k_cache : a.v_cache) + rowi * hd;
+                for (int i = lane; i < hd; i += 32) dst[i] = __float2half_rn(sh[i]);
+            }
+        }
+        __syncwarp();
+    }
+}
+
 B2_API int b2_rope_kv(const RopeKvArgs* a, int nt, int pdl, cudaStream_t st) {
     if (a->hd > 512 || ((a->k_scale || a->v_scale) && ((a->hd & 31) || !a->k_scale || !a->v_scale))) return (int)cudaErrorInvalidValue;
+    if (nt >= 64 && a->n_rot <= 512) {          // prefill chunks: a CTA per token
+        RopeKvArgs copy = *a;
+        rope_kv_rows_kernel<<<nt, 256, 0, st>>>(copy);
+        return (int)cudaGetLastError();
+    }
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(nt, a->n_heads + 2 * a->n_kv_heads);
     cfg.blockDim = dim3(128);

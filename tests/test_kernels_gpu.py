@@ -152,6 +152,46 @@ def test_rope_kv(neox, qk_norm, hd, n_rot):
         assert torch.allclose(vc[slots[t], :, pos[t]].float().cpu(), vr[t], atol=5e-3, rtol=2e-3)
 
 
+@pytest.mark.parametrize("neox,qk_norm,hd,n_rot,H,Hkv,q8", [(False, False, 128, 128, 12, 2, False), (True, True, 64, 64, 9, 3, False),
+                                                          (True, False, 64, 32, 4, 2, True), (True, True, 256, 256, 3, 1, False)])
+def test_rope_kv_of_a_prefill_chunk(neox, qk_norm, hd, n_rot, H, Hkv, q8):
+    """Chunks of 64 tokens and more take the per-token form of the kernel (a warp per head, the sines and cosines once per token):
+    rotated queries, and keys / values in the f16 or int8 cache, against the fp32 statement; positions far into a long context."""
+    K = _K()
+    nt, n_ctx, n_slots, slot = 150, 200, 2, 1
+    g = torch.Generator().manual_seed(hd + H)
+    qkv = torch.randn(nt, (H + 2 * Hkv) * hd, generator=g).cuda()
+    pos0 = 40
+    pos = torch.arange(pos0, pos0 + nt, dtype=torch.int32).cuda()
+    slots = torch.full((nt,), slot, dtype=torch.int32).cuda()
+    inv, ms = R.rope_inv_freq(n_rot, 10000.0, device="cuda")
+    qn = (torch.rand(hd, generator=g) + 0.5).cuda() if qk_norm else None
+    kn = (torch.rand(hd, generator=g) + 0.5).cuda() if qk_norm else None
+    kc = torch.zeros(n_slots, Hkv, n_ctx, hd, device="cuda", dtype=torch.int8 if q8 else torch.float16)
+    vc = torch.zeros_like(kc)
+    ks = torch.zeros(n_slots, Hkv, n_ctx, hd // 32, device="cuda", dtype=torch.float16) if q8 else None
+    vs = torch.zeros_like(ks) if q8 else None
+    q = K.rope_kv(qkv, pos, slots, inv, n_heads=H, n_kv_heads=Hkv, hd=hd, n_rot=n_rot, neox=neox, mscale=1.3, k_cache=kc, v_cache=vc,
+                  q_norm=qn, k_norm=kn, eps=1e-6, k_scale=ks, v_scale=vs)
+    qr = qkv[:, :H * hd].view(nt, H, hd).cpu()
+    kr = qkv[:, H * hd:(H + Hkv) * hd].view(nt, Hkv, hd).cpu()
+    vr = qkv[:, (H + Hkv) * hd:].view(nt, Hkv, hd).cpu()
+    if qk_norm:
+        qr, kr = R.rmsnorm(qr, qn.cpu(), 1e-6), R.rmsnorm(kr, kn.cpu(), 1e-6)
+    style = "neox" if neox else "norm"
+    qr = R.rope(qr, pos.cpu(), inv.cpu(), style, 1.3)
+    kr = R.rope(kr, pos.cpu(), inv.cpu(), style, 1.3)
+    assert torch.allclose(q.cpu(), qr, atol=3e-4, rtol=1e-4)
+    kg, vg = kc[slot, :, pos0:pos0 + nt].float(), vc[slot, :, pos0:pos0 + nt].float()
+    if q8:
+        kg = (kg.view(Hkv, nt, -1, 32) * ks[slot, :, pos0:pos0 + nt].float()[..., None]).view(Hkv, nt, hd)
+        vg = (vg.view(Hkv, nt, -1, 32) * vs[slot, :, pos0:pos0 + nt].float()[..., None]).view(Hkv, nt, hd)
+    tol = 0.04 if q8 else 5e-3
+    assert torch.allclose(kg.cpu().transpose(0, 1), kr, atol=tol, rtol=tol)
+    assert torch.allclose(vg.cpu().transpose(0, 1), vr, atol=tol, rtol=tol)
+    assert float(kc[slot, :, :pos0].float().abs().max()) == 0.0 and float(kc[0].float().abs().max()) == 0.0      # nothing outside the chunk's rows
+
+
 @pytest.mark.parametrize("hd,H,Hkv", [(128, 8, 2), (64, 8, 8), (64, 6, 3), (256, 4, 1), (32, 8, 2)])
 @pytest.mark.parametrize("window,softcap,use_sinks", [(0, 0.0, False), (24, 0.0, True), (0, 30.0, False)])
 @pytest.mark.parametrize("mma", [0, 1])
