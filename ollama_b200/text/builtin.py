@@ -608,7 +608,7 @@ def _cohere_actions(body: str) -> list[dict[str, Any]]:
 
 
 PARSERS = ("qwen3", "qwen3-thinking", "qwen3-coder", "qwen3.5", "ornith", "qwen3-vl-instruct", "qwen3-vl-thinking", "ministral", "functiongemma", "cogito", "deepseek3",
-           "olmo3", "olmo3-think", "glm-4.6", "glm-4.7", "cohere", "lfm2", "lfm2-thinking", "passthrough")
+           "olmo3", "olmo3-think", "glm-4.6", "glm-4.7", "glm-ocr", "cohere", "lfm2", "lfm2-thinking", "passthrough")
 
 
 def parser_for(name: str | None, tools: list[dict[str, Any]] | None = None, think: Any = None,
@@ -664,6 +664,8 @@ def parser_for(name: str | None, tools: list[dict[str, Any]] | None = None, thin
         return TagStreamParser(regions=[Region("<function_calls>", "</function_calls>", _pythonic_calls)])
     if name == "olmo3-think":                                     # model/parsers/olmo3_think.go:43-55: the prompt always ends in <think>
         return TagStreamParser(think_close="</think>", start_thinking=fresh)
+    if name == "glm-ocr":                                         # model/parsers/glmocr.go:5-17: the 4.6 parser with reasoning off
+        return TagStreamParser(regions=[Region("<tool_call>", "</tool_call>", _glm_call(tools))])
     if name in ("glm-4.6", "glm-4.7"):
         # model/parsers/glm47.go:13-20: the 4.7 prompt ends inside the block unless reasoning was switched off
         thinking = name == "glm-4.7" and (think is None or bool(think))

@@ -872,6 +872,41 @@ class GLM(Dialect):
         return "<|assistant|>" + ("</think>" if x.memo["off"] else "<think>")
 
 
+class GLMOcr(GLM):
+    """The OCR checkpoints' spelling (model/renderers/glmocr.go:27-107): the 4.7 tool preamble, a line break after every role mark
+    and after every stored assistant turn, a ``<think>`` block on every assistant turn (empty when it carries no reasoning),
+    ``/nothink`` on questions and an empty block in the cue when reasoning was switched off explicitly, ``[img-N]`` marks in
+    front of the text of messages that carry images."""
+
+    def __init__(self, image_tags: bool = True):
+        super().__init__(airy=False)
+        self.image_tags = image_tags
+
+    def text(self, t: Turn) -> str:
+        return image_tagged(t.content, t.images, t.first_image) if self.image_tags else t.content
+
+    def turn_system(self, t: Turn, x: Ctx) -> str:
+        return "<|system|>\n" + t.content + "\n"
+
+    def turn_user(self, t: Turn, x: Ctx) -> str:
+        nudge = "/nothink" if x.memo["off"] and not t.content.endswith("/nothink") else ""
+        return "<|user|>\n" + self.text(t) + nudge
+
+    def turn_assistant(self, t: Turn, x: Ctx) -> str:
+        out = "<|assistant|>\n<think>" + t.thinking.strip() + "</think>"
+        if t.content:
+            out += "\n" + t.content.strip()
+        for name, args in t.calls:
+            out += f"\n<tool_call>{name}" + "".join(f"<arg_key>{k}</arg_key><arg_value>{_glm_value(v)}</arg_value>" for k, v in args.items()) + "</tool_call>"
+        return out + "\n"
+
+    def turn_tool(self, t: Turn, x: Ctx) -> str:
+        return "<|observation|>" + "".join(f"\n<tool_response>\n{c}\n</tool_response>\n" for _, c in t.results)
+
+    def cue(self, x: Ctx) -> str:
+        return "<|assistant|>\n" + ("<think></think>\n" if x.memo["off"] else "")
+
+
 # ---------------------------------------------------------------------------------------------------
 # FunctionGemma
 # ---------------------------------------------------------------------------------------------------
@@ -978,6 +1013,7 @@ DIALECTS: dict[str, Callable[[], Dialect]] = {
     "olmo3-32b-think": lambda: Olmo3Think("You are a helpful AI assistant."),
     "glm-4.6": lambda: GLM(airy=True),
     "glm-4.7": lambda: GLM(airy=False),
+    "glm-ocr": lambda: GLMOcr(),
     "functiongemma": FunctionGemma,
     "cohere": Cohere,
     "lfm2": lambda: LFM2(thinking=False),

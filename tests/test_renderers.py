@@ -40,6 +40,29 @@ def test_every_registered_renderer_has_cases_and_renders_an_empty_conversation()
     assert R.renderer_for("nope") is None and R.renderer_for(None) is None
 
 
+def test_glm_ocr_turns_reasoning_switch_and_tools():
+    """model/renderers/glmocr.go:27-107 beyond the image cases of its own test table: the stored reasoning of an assistant turn, calls
+    and their results, a system message in place, the ``/nothink`` nudge and the empty block when reasoning is switched off."""
+    r = R.renderer_for("glm-ocr")
+    msgs = [{"role": "system", "content": "Be brief."}, {"role": "user", "content": "read it"},
+            {"role": "assistant", "content": " ok ", "thinking": " plan ", "tool_calls": [{"function": {"name": "ocr", "arguments": {"page": 2, "lang": "en"}}}]},
+            {"role": "tool", "content": "text A"}, {"role": "tool", "content": "text B"}, {"role": "user", "content": "and now?"}]
+    got = r.render(msgs, None, False)
+    assert got == ("[gMASK]<sop><|system|>\nBe brief.\n<|user|>\nread it/nothink<|assistant|>\n<think>plan</think>\nok\n<tool_call>ocr"
+                   "<arg_key>page</arg_key><arg_value>2</arg_value><arg_key>lang</arg_key><arg_value>en</arg_value></tool_call>\n"
+                   "<|observation|>\n<tool_response>\ntext A\n</tool_response>\n\n<tool_response>\ntext B\n</tool_response>\n"
+                   "<|user|>\nand now?/nothink<|assistant|>\n<think></think>\n")
+    assert r.render(msgs[1:2], None, None) == "[gMASK]<sop><|user|>\nread it<|assistant|>\n"
+    tools = [{"type": "function", "function": {"name": "ocr", "description": "read a page", "parameters": {"type": "object", "properties": {"page": {"type": "integer"}}}}}]
+    head = r.render(msgs[1:2], tools, True)
+    assert head.startswith("[gMASK]<sop><|system|>\n# Tools\n\nYou may call one or more functions") and '"name": "ocr"' in head
+    assert head.endswith("<arg_value>{arg-value-2}</arg_value>...</tool_call><|user|>\nread it<|assistant|>\n")
+    from ollama_b200.text.builtin import parser_for
+    p = parser_for("glm-ocr", tools, None)
+    content, thinking, calls = p.add("done <tool_call>ocr<arg_key>page</arg_key><arg_value>3</arg_value></tool_call>", True)
+    assert content.strip() == "done" and thinking == "" and calls[0]["function"] == {"name": "ocr", "arguments": {"page": 3}}
+
+
 def test_conversation_normal_form():
     msgs = [{"role": "system", "content": "S"}, {"role": "user", "content": "q", "images": ["a", "b"]},
             {"role": "assistant", "content": "", "tool_calls": [{"function": {"name": "f", "arguments": {"x": 1}}}, {"function": {"name": "g", "arguments": {}}}]},
