@@ -5,7 +5,8 @@
 // query heads that share a KV head are the rows of an m16n8k16 MMA tile (grouped-query attention gives
 // 4..16 such heads; missing rows are zero), so one tile of 64 cached positions costs each warp 32 MMAs
 // instead of some 1800 scalar instructions per 16 positions.  grid = (splits, kv heads, sequences), 4 warps.
-// Cache rows arrive in shared memory through cp.async (two stages); warp w owns positions 16w..16w+15 of
+// Cache rows arrive in shared memory through cp.async (two stages, or four when the launch has so few CTAs that each SM
+// holds one: the bytes in flight per SM, not the math, bound this kernel at long contexts); warp w owns positions 16w..16w+15 of
 // every tile and keeps its own running soft-max statistics and output accumulator, the four warps are merged
 // through shared memory at the end.  The scalar kernel stays the choice for short contexts and for head
 // sizes without an instantiation here.
@@ -34,13 +35,13 @@ __device__ __forceinline__ uint32_t pack_half2(float a, float b) {
     return *reinterpret_cast<const uint32_t*>(&h);
 }
 
-template <int D>
+template <int D, int NS>
 __global__ void __launch_bounds__(128) attn_decode_mma_kernel(const __grid_constant__ AttnDecodeArgs a, const __grid_constant__ AttnRopeArgs r) {
     constexpr int LD = D + PAD;
     extern __shared__ __align__(16) unsigned char smem_raw[];
     __half* sQ = reinterpret_cast<__half*>(smem_raw);            // [ROWS][LD]
-    __half* sK = sQ + ROWS * LD;                                 // [2][BN][LD]
-    __half* sV = sK + 2 * BN * LD;                               // [2][BN][LD]
+    __half* sK = sQ + ROWS * LD;                                 // [NS][BN][LD]
+    __half* sV = sK + NS * BN * LD;                              // [NS][BN][LD]
     __shared__ float s_m[4][ROWS], s_l[4][ROWS];
     __shared__ float s_cs[128], s_sn[128];                        // cos / sin of the query position per rotated pair (fused form)
     __shared__ __half s_newk[D], s_newv[D];                       // the query token's own key and value rows (fused form, owning split)
@@ -102,7 +103,12 @@ __global__ void __launch_bounds__(128) attn_decode_mma_kernel(const __grid_const
         asm volatile("cp.async.commit_group;" ::: "memory");
     };
 
-    if (n_tiles > 0) load_kv(0, 0);
+    // the first NS - 1 tiles are requested at once (one commit group each, empty past the end, so that the counting stays uniform)
+#pragma unroll
+    for (int t = 0; t < NS - 1; t++) {
+        if (t < n_tiles) load_kv(t, t);
+        else asm volatile("cp.async.commit_group;" ::: "memory");
+    }
     const bool fresh = r.qkv != nullptr;
     const bool owner = fresh && n_tiles > 0 && qpos >= p0 && qpos < p1;      // this split holds the query token's own position
     // element i of a raw head row after the rotary embedding (pairs (2p, 2p+1), or (p, p + n_rot/2) in the neox order)
@@ -116,9 +122,9 @@ __global__ void __launch_bounds__(128) attn_decode_mma_kernel(const __grid_const
         return first ? x * s_cs[p] - y * s_sn[p] : y * s_sn[p] + x * s_cs[p];
     };
     if (fresh) {
-        // the raw rows (query heads of this group, the key and the value) are staged in the second K stage, which stays unused
-        // until the tile loop requests tile 1; cos / sin of the position are computed once per CTA meanwhile
-        float* raw = reinterpret_cast<float*>(sK + BN * LD);                  // [group + 2][D]
+        // the raw rows (query heads of this group, the key and the value) are staged in the last K stage, which stays unused
+        // until the tile loop requests tile NS - 1; cos / sin of the position are computed once per CTA meanwhile
+        float* raw = reinterpret_cast<float*>(sK + (NS - 1) * BN * LD);       // [group + 2][D]
         const float* tok = r.qkv + (size_t)b * (a.n_heads + 2 * a.n_kv_heads) * D;
         const int nrows = group + (owner ? 2 : 0);
         for (int c = tid; c < nrows * (D / 4); c += 128) {
@@ -177,13 +183,10 @@ __global__ void __launch_bounds__(128) attn_decode_mma_kernel(const __grid_const
     float m_run[2] = {-1e30f, -1e30f}, l_run[2] = {0.f, 0.f};
 
     for (int tile = 0; tile < n_tiles; tile++) {
-        const int stage = tile & 1;
-        if (tile + 1 < n_tiles) {
-            load_kv(tile + 1, stage ^ 1);
-            asm volatile("cp.async.wait_group 1;" ::: "memory");
-        } else {
-            asm volatile("cp.async.wait_group 0;" ::: "memory");
-        }
+        const int stage = tile % NS;
+        if (tile + NS - 1 < n_tiles) load_kv(tile + NS - 1, (tile + NS - 1) % NS);      // into the stage that tile - 1 has just left
+        else asm volatile("cp.async.commit_group;" ::: "memory");
+        asm volatile("cp.async.wait_group %0;" ::"n"(NS - 1) : "memory");               // tile's own group is complete
         __syncthreads();
         if (owner && tile == n_tiles - 1) {      // the query's own row did not come from the cache: put it into the tile
             const int rr = qpos - (p0 + tile * BN);
@@ -258,8 +261,9 @@ __global__ void __launch_bounds__(128) attn_decode_mma_kernel(const __grid_const
             mma_f16(o[j], pa, vb[0], vb[1]);
             mma_f16(o[j + 1], pa, vb[2], vb[3]);
         }
-        __syncthreads();        // everyone is done with this stage before it is overwritten two iterations later
+        __syncthreads();        // everyone is done with this stage before the next iteration's request overwrites it
     }
+    asm volatile("cp.async.wait_group 0;" ::: "memory");
 
     // merge the four warps: (max, sum, acc) of every query head through shared memory (the staging area is free now)
 #pragma unroll
@@ -298,11 +302,11 @@ __global__ void __launch_bounds__(128) attn_decode_mma_kernel(const __grid_const
     }
 }
 
-template <int D>
+template <int D, int NS>
 int launch(const AttnDecodeArgs& a, const AttnRopeArgs& r, int nb, int pdl, cudaStream_t st) {
-    constexpr int SMEM = (ROWS + 4 * BN) * (D + PAD) * 2;
+    constexpr int SMEM = (ROWS + 2 * NS * BN) * (D + PAD) * 2;
     static PerDeviceOnce once;
-    if (once.first()) cudaFuncSetAttribute(attn_decode_mma_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM);
+    if (once.first()) cudaFuncSetAttribute(attn_decode_mma_kernel<D, NS>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM);
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(a.n_splits, a.n_kv_heads, nb);
     cfg.blockDim = dim3(128);
@@ -316,7 +320,23 @@ int launch(const AttnDecodeArgs& a, const AttnRopeArgs& r, int nb, int pdl, cuda
     AttnDecodeArgs copy = a;
     AttnRopeArgs rcopy = r;
     void* args[] = {&copy, &rcopy};
-    return (int)cudaLaunchKernelExC(&cfg, (const void*)attn_decode_mma_kernel<D>, args);
+    return (int)cudaLaunchKernelExC(&cfg, (const void*)attn_decode_mma_kernel<D, NS>, args);
+}
+
+int g_stages = 0;      // 0: by the size of the launch; 2 or 4: forced (tests)
+
+// Four stages take 140 KB of shared memory (one CTA per SM): right when the launch has about one CTA per SM anyway and every
+// split is several tiles long; launches with many more CTAs keep two stages and three CTAs per SM.
+bool deep(const AttnDecodeArgs& a, int nb) {
+    if (g_stages) return g_stages == 4;
+    static int sms = 0;
+    if (!sms) {
+        int dev = 0;
+        cudaGetDevice(&dev);
+        cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+        if (sms <= 0) sms = 148;
+    }
+    return (long)a.n_splits * a.n_kv_heads * nb <= 2L * sms && a.n_ctx / a.n_splits >= 2 * BN;
 }
 
 }  // namespace
@@ -324,9 +344,17 @@ int launch(const AttnDecodeArgs& a, const AttnRopeArgs& r, int nb, int pdl, cuda
 int attn_decode_mma_rope_launch(const AttnDecodeArgs& a, const AttnRopeArgs& r, int nb, int hd, int pdl, cudaStream_t st) {
     if (a.n_kv_heads < 1 || a.n_heads % a.n_kv_heads || a.n_heads / a.n_kv_heads > ROWS) return (int)cudaErrorNotSupported;
     if (r.qkv && (a.k_scale || a.v_scale || r.n_rot > 256 || r.n_rot > hd || (r.n_rot & 1) || !r.inv_freq)) return (int)cudaErrorNotSupported;
-    if (hd == 128) return launch<128>(a, r, nb, pdl, st);
-    if (hd == 64) return launch<64>(a, r, nb, pdl, st);
+    const bool four = deep(a, nb);
+    if (hd == 128) return four ? launch<128, 4>(a, r, nb, pdl, st) : launch<128, 2>(a, r, nb, pdl, st);
+    if (hd == 64) return four ? launch<64, 4>(a, r, nb, pdl, st) : launch<64, 2>(a, r, nb, pdl, st);
     return (int)cudaErrorNotSupported;
+}
+
+// Pipeline depth of the tensor-core decode kernel: 0 = chosen per launch (default), 2 or 4 = forced.  Returns the previous setting.
+B2_API int b2_attn_decode_stages(int n) {
+    const int old = g_stages;
+    if (n == 0 || n == 2 || n == 4) g_stages = n;
+    return old;
 }
 
 int attn_decode_mma_launch(const AttnDecodeArgs& a, int nb, int hd, int pdl, cudaStream_t st) {

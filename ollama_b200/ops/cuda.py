@@ -363,6 +363,12 @@ def attn_decode_mode(mode: int) -> None:
     lib().b2_attn_decode_mode(int(mode))
 
 
+def attn_decode_stages(n: int) -> int:
+    """Pipeline depth of the tensor-core decode-attention kernel: 0 = chosen per launch (four stages when the launch has about one
+    CTA per SM, else two), 2 or 4 = forced.  Returns the previous setting."""
+    return int(lib().b2_attn_decode_stages(int(n)))
+
+
 def attn_decode(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, positions: torch.Tensor, slots: torch.Tensor, *,
                 scale: float, n_splits: int, window: int = 0, softcap: float = 0.0, sinks: torch.Tensor | None = None,
                 scratch: tuple[torch.Tensor, torch.Tensor] | None = None, quant_out: bool = True, pdl: bool = False,
