@@ -13,6 +13,7 @@ import hashlib
 import json
 import os
 import statistics
+import re
 import sys
 import time
 from typing import Any
@@ -220,6 +221,51 @@ def cmd_create(args) -> int:
     return 0
 
 
+_MEDIA_PATH = re.compile(r"(?:[a-zA-Z]:)?(?:\./|/|\\)[\S\\ ]+?\.(?i:jpg|jpeg|png|webp|wav)\b")
+_MEDIA_MAGIC = ((b"\xff\xd8\xff", "image/jpeg"), (b"\x89PNG\r\n\x1a\n", "image/png"), (b"RIFF", "riff"))
+_UNESCAPE = {"\\ ": " ", "\\(": "(", "\\)": ")", "\\[": "[", "\\]": "]", "\\{": "{", "\\}": "}", "\\$": "$", "\\&": "&", "\\;": ";",
+             "\\'": "'", "\\\\": "\\", "\\*": "*", "\\?": "?", "\\~": "~", "%20": " "}
+
+
+def _media_type(head: bytes) -> str:
+    for magic, kind in _MEDIA_MAGIC:
+        if head.startswith(magic):
+            if kind == "riff":
+                return {b"WEBP": "image/webp", b"WAVE": "audio/wave"}.get(head[8:12], "")
+            return kind
+    return ""
+
+
+def extract_media(text: str) -> tuple[str, list[str]]:
+    """File paths of images (or audio) inside a prompt -> (prompt without them, their contents as base64), as the reference's
+    prompt line does (cmd/interactive.go:605-644, :700-740): a path starts with ``/``, ``./``, a backslash or a drive letter,
+    may contain escaped spaces, and ends in jpg / jpeg / png / webp / wav; strings that name no existing file stay in the text;
+    a file that exists must really be one of those types and at most 100 MB."""
+    import base64
+    images: list[str] = []
+    for found in _MEDIA_PATH.findall(text):
+        path = found
+        for a, b in _UNESCAPE.items():
+            path = path.replace(a, b)
+        try:
+            with open(path, "rb") as f:
+                data = f.read(100 * 1024 * 1024 + 1)
+        except FileNotFoundError:
+            continue
+        except OSError as e:
+            raise ValueError(f"couldn't process file: {e}")
+        if len(data) > 100 * 1024 * 1024:
+            raise ValueError("file size exceeds maximum limit (100MB)")
+        kind = _media_type(data[:512])
+        if not kind:
+            raise ValueError(f"invalid file type: {path}")
+        print(f"Added {'audio' if kind.startswith('audio') else 'image'} '{path}'", file=sys.stderr)
+        for quoted in ("'" + path + "'", "'" + found + "'", found):
+            text = text.replace(quoted, "")
+        images.append(base64.b64encode(data).decode())
+    return text.strip(), images
+
+
 class Repl:
     """Interactive chat session of ``run`` (cmd/interactive.go in the reference)."""
 
@@ -234,7 +280,12 @@ class Repl:
         self.system = ""
 
     def turn(self, text: str) -> None:
-        self.messages.append({"role": "user", "content": text})
+        try:
+            text, images = extract_media(text)
+        except ValueError as e:
+            print(f"Error: {e}", file=sys.stderr)
+            return
+        self.messages.append({"role": "user", "content": text, **({"images": images} if images else {})})
         req: dict[str, Any] = {"model": self.model, "messages": ([{"role": "system", "content": self.system}] if self.system else []) + self.messages,
                                "options": self.opts}
         if self.fmt:
@@ -411,7 +462,14 @@ def cmd_run(args) -> int:
         piped = sys.stdin.read()
         prompt = (prompt + "\n" + piped).strip() if prompt else piped
     if prompt:
+        try:
+            prompt, images = extract_media(prompt)
+        except ValueError as e:
+            print(f"Error: {e}", file=sys.stderr)
+            return 1
         req: dict[str, Any] = {"model": args.model, "prompt": prompt, "options": opts}
+        if images:
+            req["images"] = images
         if args.format:
             req["format"] = args.format
         if think is not None:

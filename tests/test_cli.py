@@ -202,3 +202,28 @@ def test_launch_wires_tools_to_the_server(server, monkeypatch, tmp_path):
         tui.select("pick", [tui.Item("a")], inp=io.StringIO("zzz\n"), out=io.StringIO())
     rc, _, err_text = run_cli("launch", "claude", "--model", "tiny", "--dry-run", "--", "--print", "hello")
     assert rc == 0 and err_text.strip().endswith("claude --model tiny --print hello")
+
+
+def test_prompt_lines_carry_image_files(tmp_path, capsys):
+    """cmd/interactive.go:605-644: paths of image files inside a prompt leave the text and travel as images; names of files that do
+    not exist stay; a file of another kind behind an image extension is refused."""
+    import base64
+
+    from ollama_b200.cli.main import extract_media
+    png = tmp_path / "a pic.png"
+    png.write_bytes(b"\x89PNG\r\n\x1a\n" + b"\0" * 32)
+    jpg = tmp_path / "b.JPG"
+    jpg.write_bytes(b"\xff\xd8\xff\xe0" + b"\0" * 32)
+    esc = str(png).replace(" ", "\\ ")
+    text, images = extract_media(f"compare {esc} with '{jpg}' and /no/such/file.png please")
+    assert text == "compare  with  and /no/such/file.png please"
+    assert [base64.b64decode(i)[:4] for i in images] == [b"\x89PNG", b"\xff\xd8\xff\xe0"]
+    assert "Added image" in capsys.readouterr().err
+    assert extract_media("no files here") == ("no files here", [])
+    fake = tmp_path / "notes.png"
+    fake.write_text("just text")
+    with pytest.raises(ValueError, match="invalid file type"):
+        extract_media(f"look at {fake}")
+    wav = tmp_path / "s.wav"
+    wav.write_bytes(b"RIFF\0\0\0\0WAVEfmt " + b"\0" * 16)
+    assert len(extract_media(f"{wav} transcribe")[1]) == 1
