@@ -446,6 +446,14 @@ def test_chat_with_images_through_the_api(tmp_path, monkeypatch):
         assert placed["done"] and lp(placed) != lp(one)
         bad = ask(["bm90IGFuIGltYWdl"])
         assert bad.status_code == 400 and "image" in bad.json()["error"]
+        url = "data:image/png;base64," + base64.b64encode(_png(1)).decode()
+        oa = c.post("/v1/chat/completions", json={"model": "g3v", "max_tokens": 2, "temperature": 0, "messages": [
+            {"role": "user", "content": [{"type": "text", "text": "abab"}, {"type": "image_url", "image_url": {"url": url}}]}]})
+        assert oa.status_code == 200 and oa.json()["usage"]["prompt_tokens"] == one["prompt_eval_count"], oa.text
+        an = c.post("/v1/messages", json={"model": "g3v", "max_tokens": 2, "messages": [{"role": "user", "content": [
+            {"type": "image", "source": {"type": "base64", "media_type": "image/png", "data": base64.b64encode(_png(1)).decode()}},
+            {"type": "text", "text": "abab"}]}]})
+        assert an.status_code == 200 and an.json()["usage"]["input_tokens"] == one["prompt_eval_count"], an.text
         gen = c.post("/api/generate", json={"model": "g3v", "prompt": "abab", "images": [base64.b64encode(_png(1)).decode()], "stream": False,
                                             "options": {"num_predict": 2, "temperature": 0}})
         assert gen.status_code == 200 and gen.json()["prompt_eval_count"] == one["prompt_eval_count"], gen.text
