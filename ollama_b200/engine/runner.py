@@ -534,10 +534,11 @@ class Runner:
         s.n_prompt_eval += n
         self.slot_tokens[s.slot].extend(chunk)
         if last:
-            s.t_prefill += time.perf_counter() - t0
-            s.t_first = time.perf_counter() - s.t_submit
             s.state = "decode"
-            self._sample_accept(s, logits)
+            self._sample_accept(s, logits)       # reads the logits: the chunk has finished on the device when this returns
+            now = time.perf_counter()
+            s.t_prefill += now - t0              # prompt-eval time includes the device's work, not only the host's enqueueing
+            s.t_first = now - s.t_submit
         else:
             _sync(None)
             s.t_prefill += time.perf_counter() - t0
@@ -565,17 +566,16 @@ class Runner:
         outs = self.backend.prefill_many(segs, last)
         if not any(last):
             _sync(None)
-        dt = time.perf_counter() - t0
         self.stats["prefill_batches"] = self.stats.get("prefill_batches", 0) + 1
         for s, (_, chunk, _), done, logits in zip(part, segs, last, outs):
             s.n_past += len(chunk)
             s.n_prompt_eval += len(chunk)
             self.slot_tokens[s.slot].extend(chunk)
-            s.t_prefill += dt
             if done:
-                s.t_first = time.perf_counter() - s.t_submit
                 s.state = "decode"
-                self._sample_accept(s, logits)
+                self._sample_accept(s, logits)   # reads the logits: the pass has finished on the device
+                s.t_first = time.perf_counter() - s.t_submit
+            s.t_prefill += time.perf_counter() - t0
 
     def _decode(self, seqs: list[_Seq]) -> None:
         with self._range("decode_step"):
