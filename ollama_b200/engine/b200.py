@@ -82,6 +82,10 @@ class B200Backend:
         # quantised blocks cover 32 dims; head sizes outside the flash-attention kernel read the cache through torch
         self.kv_q8 = kv_type != "f16" and self.cfg.head_dim % 32 == 0 and self.cfg.head_dim in K.ATTN_PREFILL_HEAD_DIMS
         self.kv_type = "q8_0" if self.kv_q8 else "f16"
+        if kv_type != self.kv_type:       # say so: the cache costs what the stored encoding costs, not what was asked for
+            import logging
+            logging.getLogger("ollama_b200.engine").warning("K/V cache type %s is stored as %s (%s)", kv_type, self.kv_type,
+                                                            "there is no 4-bit cache encoding" if self.kv_q8 else "this head size has no quantised cache")
         if keep_bf16 is None:
             c = self.cfg
             est = 2 * (c.n_layers * (c.d_model * (2 * c.q_dim + 2 * c.kv_dim) + 3 * c.d_model * c.d_ff) + c.vocab_size * c.d_model)
