@@ -544,22 +544,18 @@ class Runner:
             s.t_prefill += time.perf_counter() - t0
 
     def _prefill_batch(self, seqs: list[_Seq]) -> None:
-        """One pass over prompt rows of several sequences: the row budget (num_batch) is dealt out in equal shares, what a short
-        prompt leaves over goes to the longer ones, in arrival order."""
+        """One pass over prompt rows of several sequences: the row budget (num_batch) is filled in arrival order, so the request that
+        came first reaches its first token first and short prompts ride along in what a longer one leaves over (the order in which
+        the reference's runner packs the prompts of its slots into a batch)."""
         t0 = time.perf_counter()
         budget = max(1, self.opts.num_batch)
-        seqs = seqs[:budget]
         left = {id(s): len(s.prompt) - s.n_past for s in seqs}
         take = {id(s): 0 for s in seqs}
-        while budget > 0 and any(left[id(s)] > take[id(s)] for s in seqs):
-            hungry = [s for s in seqs if left[id(s)] > take[id(s)]]
-            share = max(1, budget // len(hungry))
-            for s in hungry:
-                n = min(share, left[id(s)] - take[id(s)], budget)
-                take[id(s)] += n
-                budget -= n
-                if budget == 0:
-                    break
+        for s in seqs:
+            if budget == 0:
+                break
+            take[id(s)] = min(left[id(s)], budget)
+            budget -= take[id(s)]
         part = [s for s in seqs if take[id(s)] > 0]
         segs = [(s.slot, s.prompt[s.n_past:s.n_past + take[id(s)]], s.n_past) for s in part]
         last = [take[id(s)] == left[id(s)] for s in part]

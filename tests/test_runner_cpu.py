@@ -55,8 +55,8 @@ def test_prefix_cache_and_parallel_slots(tiny_llama_path):
 
 
 def test_prompts_of_waiting_sequences_share_one_prefill_pass(tiny_llama_path):
-    """Three requests arrive together with prompts of 40, 9 and 23 tokens and a budget of 16 rows per pass: every pass takes rows
-    of all that still wait (short prompts leave their share to the others), and each request decodes what it decodes alone."""
+    """Three requests arrive together with prompts of 40, 9 and 23 tokens and a budget of 16 rows per pass: a pass is filled in
+    arrival order (what the first prompt leaves over goes to the next), and each request decodes what it decodes alone."""
     g = torch.Generator().manual_seed(5)
     prompts = [torch.randint(259, 32000, (n,), generator=g).tolist() for n in (40, 9, 23)]
     req = lambda p: CompletionRequest(prompt=p, sampling=SamplingParams(temperature=0), num_predict=5, cache_prompt=False)
@@ -83,10 +83,11 @@ def test_prompts_of_waiting_sequences_share_one_prefill_pass(tiny_llama_path):
                     break
             got.append(toks)
         assert got == want
-        assert calls[0] == [(6, 0), (5, 0), (5, 0)]           # 16 rows: 5 each, the spare row to the first
         assert all(sum(n for n, _ in c) <= 16 for c in calls)
-        assert calls[1] == [(6, 6), (4, 5), (6, 5)]           # the 9-token prompt ends and leaves rows to the others
-        assert r.stats["prefill_batches"] == len(calls) >= 3
+        assert calls[0] == [(16, 0)] and calls[1] == [(16, 16)]          # the first prompt fills the pass while it can
+        assert calls[2] == [(8, 32), (8, 0)]                             # its last rows, and the second prompt rides along
+        assert calls[3] == [(1, 8), (15, 0)]                             # the second ends, the third starts in the same pass
+        assert r.stats["prefill_batches"] == len(calls) >= 4
     finally:
         r.close()
 
