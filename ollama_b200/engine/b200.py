@@ -100,7 +100,7 @@ class B200Backend:
         # Decode matrices in unit order for the streaming GEMV (Q4_K / Q6_K layers without experts or sandwich norms); B200_SK=0
         # keeps every layer on the dp4a kernels.
         # Subclasses that enqueue their own decode kernels (tensor parallelism) keep the dp4a planes.
-        if os.environ.get("B200_ATTN_DECODE_STAGES", "") in ("2", "4"):      # pipeline depth of the tensor-core decode attention (default: per launch)
+        if os.environ.get("B200_ATTN_DECODE_STAGES", "") in ("2", "3", "4"):      # pipeline depth of the tensor-core decode attention (default: per launch)
             K.attn_decode_stages(int(os.environ["B200_ATTN_DECODE_STAGES"]))
         self.moe_stream_q = os.environ.get("B200_MOE_STREAM_Q", "1") != "0"    # MoE prefill reads MXFP4 experts as they are (no 16-bit expansion per chunk)
         self.fuse_rope = os.environ.get("B200_FUSE_ROPE", "1") != "0"      # decode attention rotates Q / K and appends K / V itself

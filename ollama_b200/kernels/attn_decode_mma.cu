@@ -5,8 +5,8 @@
 // query heads that share a KV head are the rows of an m16n8k16 MMA tile (grouped-query attention gives
 // 4..16 such heads; missing rows are zero), so one tile of 64 cached positions costs each warp 32 MMAs
 // instead of some 1800 scalar instructions per 16 positions.  grid = (splits, kv heads, sequences), 4 warps.
-// Cache rows arrive in shared memory through cp.async (two stages, or four when the launch has so few CTAs that each SM
-// holds one: the bytes in flight per SM, not the math, bound this kernel at long contexts); warp w owns positions 16w..16w+15 of
+// Cache rows arrive in shared memory through cp.async (two stages, or three / four when the launch has so few CTAs that each SM
+// holds two / one: the bytes in flight per SM, not the math, bound this kernel at long contexts); warp w owns positions 16w..16w+15 of
 // every tile and keeps its own running soft-max statistics and output accumulator, the four warps are merged
 // through shared memory at the end.  The scalar kernel stays the choice for short contexts and for head
 // sizes without an instantiation here.
@@ -323,12 +323,13 @@ int launch(const AttnDecodeArgs& a, const AttnRopeArgs& r, int nb, int pdl, cuda
     return (int)cudaLaunchKernelExC(&cfg, (const void*)attn_decode_mma_kernel<D, NS>, args);
 }
 
-int g_stages = 0;      // 0: by the size of the launch; 2 or 4: forced (tests)
+int g_stages = 0;      // 0: by the size of the launch; 2, 3 or 4: forced (tests)
 
-// Four stages take 140 KB of shared memory (one CTA per SM): right when the launch has about one CTA per SM anyway and every
-// split is several tiles long; launches with many more CTAs keep two stages and three CTAs per SM.
-bool deep(const AttnDecodeArgs& a, int nb) {
-    if (g_stages) return g_stages == 4;
+// Four stages take 140 KB of shared memory (one CTA per SM), three 109 KB (two per SM), two 74 KB (three per SM).  A launch that
+// gives every SM at most one CTA runs four stages, one that gives it at most two runs three, larger ones keep two: the bytes in
+// flight per SM stay about the same and no launch needs a second round because of its shared memory.
+int stages_for(const AttnDecodeArgs& a, int nb) {
+    if (g_stages) return g_stages;
     static int sms = 0;
     if (!sms) {
         int dev = 0;
@@ -336,7 +337,18 @@ bool deep(const AttnDecodeArgs& a, int nb) {
         cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
         if (sms <= 0) sms = 148;
     }
-    return (long)a.n_splits * a.n_kv_heads * nb <= 2L * sms && a.n_ctx / a.n_splits >= 2 * BN;
+    const long ctas = (long)a.n_splits * a.n_kv_heads * nb;
+    if (a.n_ctx / a.n_splits < 2 * BN) return 2;
+    return ctas <= sms ? 4 : (ctas <= 2L * sms ? 3 : 2);
+}
+
+template <int D>
+int launch_d(const AttnDecodeArgs& a, const AttnRopeArgs& r, int nb, int pdl, cudaStream_t st) {
+    switch (stages_for(a, nb)) {
+        case 4: return launch<D, 4>(a, r, nb, pdl, st);
+        case 3: return launch<D, 3>(a, r, nb, pdl, st);
+        default: return launch<D, 2>(a, r, nb, pdl, st);
+    }
 }
 
 }  // namespace
@@ -344,16 +356,15 @@ bool deep(const AttnDecodeArgs& a, int nb) {
 int attn_decode_mma_rope_launch(const AttnDecodeArgs& a, const AttnRopeArgs& r, int nb, int hd, int pdl, cudaStream_t st) {
     if (a.n_kv_heads < 1 || a.n_heads % a.n_kv_heads || a.n_heads / a.n_kv_heads > ROWS) return (int)cudaErrorNotSupported;
     if (r.qkv && (a.k_scale || a.v_scale || r.n_rot > 256 || r.n_rot > hd || (r.n_rot & 1) || !r.inv_freq)) return (int)cudaErrorNotSupported;
-    const bool four = deep(a, nb);
-    if (hd == 128) return four ? launch<128, 4>(a, r, nb, pdl, st) : launch<128, 2>(a, r, nb, pdl, st);
-    if (hd == 64) return four ? launch<64, 4>(a, r, nb, pdl, st) : launch<64, 2>(a, r, nb, pdl, st);
+    if (hd == 128) return launch_d<128>(a, r, nb, pdl, st);
+    if (hd == 64) return launch_d<64>(a, r, nb, pdl, st);
     return (int)cudaErrorNotSupported;
 }
 
-// Pipeline depth of the tensor-core decode kernel: 0 = chosen per launch (default), 2 or 4 = forced.  Returns the previous setting.
+// Pipeline depth of the tensor-core decode kernel: 0 = chosen per launch (default), 2, 3 or 4 = forced.  Returns the previous setting.
 B2_API int b2_attn_decode_stages(int n) {
     const int old = g_stages;
-    if (n == 0 || n == 2 || n == 4) g_stages = n;
+    if (n == 0 || (n >= 2 && n <= 4)) g_stages = n;
     return old;
 }
 

@@ -364,8 +364,8 @@ def attn_decode_mode(mode: int) -> None:
 
 
 def attn_decode_stages(n: int) -> int:
-    """Pipeline depth of the tensor-core decode-attention kernel: 0 = chosen per launch (four stages when the launch has about one
-    CTA per SM, else two), 2 or 4 = forced.  Returns the previous setting."""
+    """Pipeline depth of the tensor-core decode-attention kernel: 0 = chosen per launch (four stages when every SM gets at most one
+    CTA, three when at most two, else two), 2, 3 or 4 = forced.  Returns the previous setting."""
     return int(lib().b2_attn_decode_stages(int(n)))
 
 
