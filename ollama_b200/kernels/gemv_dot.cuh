@@ -271,18 +271,24 @@ __device__ __forceinline__ void dot_q4_0(const Planes& w, int row0, int rmax, co
     }
 }
 
-// e2m1 code -> 2 * value as int8, four codes at a time
-__device__ __forceinline__ uint32_t fp4x4_to_i8(uint32_t idx) {
-    const uint32_t sel = (idx & 0x7u) | ((idx >> 4) & 0x70u) | ((idx >> 8) & 0x700u) | ((idx >> 12) & 0x7000u);
-    const uint32_t mag = __byte_perm(0x03020100u, 0x0c080604u, sel);
-    const uint32_t neg = ((idx >> 3) & 0x01010101u) * 0xffu;
-    return __vsub4(mag ^ neg, neg);
+// MXFP4: p0 = nibbles, p1 = e8m0 per 32.
+// A 32-bit word of the nibble plane holds eight E2M1 codes, and a code is already a byte-permute selector: its three magnitude
+// bits index a table of the eight magnitudes (times two, as int8), and its sign bit is the selector's "replicate the top bit"
+// flag, which turns the looked-up byte into 0x00 because no magnitude has its top bit set.  So prmt(table, word) gives the
+// magnitudes of the positive codes of four nibbles and zero for the negative ones, prmt(table, word ^ 0x8888) the reverse; the dot
+// product is dp4a(positive part) - dp4a(negative part).  No selector is assembled and no byte is negated.  The four nibbles of a
+// half word are the codes of columns (j, 16 + j, j + 1, 17 + j): the activation bytes are brought into that order once per block
+// and token and shared by the rows a thread works on.
+__device__ __forceinline__ int prmt_b32(uint32_t a, uint32_t b, uint32_t sel) {      // PTX prmt, default mode: selector bit 3 = replicate the byte's top bit
+    uint32_t d;
+    asm("prmt.b32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(sel));
+    return (int)d;
 }
 
-// MXFP4: p0 = nibbles, p1 = e8m0 per 32
 template <int R, int NB>
 __device__ __forceinline__ void dot_mxfp4(const Planes& w, int row0, int rmax, const XRef<NB>& x, float (&acc)[R][NB], int it0, int step) {
     const int K = x.k, items = K >> 5;
+    constexpr uint32_t MAG_LO = 0x03020100u, MAG_HI = 0x0c080604u;      // 2 x {0, 0.5, 1, 1.5} and 2 x {2, 3, 4, 6}
     const uint8_t* qp[R];
     const uint8_t* ep[R];
 #pragma unroll
@@ -301,17 +307,30 @@ __device__ __forceinline__ void dot_mxfp4(const Planes& w, int row0, int rmax, c
             d[r] = 0.5f * e8m0_to_float(__ldg(ep[r] + it));
         }
 #pragma unroll
-        for (int r = 0; r < R; r++) {
-            uint4 lo, hi;
-            lo.x = fp4x4_to_i8(q[r].x & 0x0f0f0f0fu); lo.y = fp4x4_to_i8(q[r].y & 0x0f0f0f0fu);
-            lo.z = fp4x4_to_i8(q[r].z & 0x0f0f0f0fu); lo.w = fp4x4_to_i8(q[r].w & 0x0f0f0f0fu);
-            hi.x = fp4x4_to_i8((q[r].x >> 4) & 0x0f0f0f0fu); hi.y = fp4x4_to_i8((q[r].y >> 4) & 0x0f0f0f0fu);
-            hi.z = fp4x4_to_i8((q[r].z >> 4) & 0x0f0f0f0fu); hi.w = fp4x4_to_i8((q[r].w >> 4) & 0x0f0f0f0fu);
+        for (int b = 0; b < NB; b++) {
+            const int4* xp = (const int4*)(x.q + x.tok(b) * K + it * 32);
+            const int4 xl = xp[0], xh = xp[1];
+            const int xlo[4] = {xl.x, xl.y, xl.z, xl.w}, xhi[4] = {xh.x, xh.y, xh.z, xh.w};
+            int xa[4], xb[4];
 #pragma unroll
-            for (int b = 0; b < NB; b++) {
-                const int4* xp = (const int4*)(x.q + x.tok(b) * K + it * 32);
-                const float dx = x.ds[x.tok(b) * items + it].x;
-                acc[r][b] += d[r] * dx * (float)(dot16(lo, xp[0]) + dot16(hi, xp[1]));
+            for (int i = 0; i < 4; i++) {
+                xa[i] = (int)__byte_perm((uint32_t)xlo[i], (uint32_t)xhi[i], 0x5140);      // columns 4i, 16 + 4i, 4i + 1, 17 + 4i
+                xb[i] = (int)__byte_perm((uint32_t)xlo[i], (uint32_t)xhi[i], 0x7362);      // columns 4i + 2, 18 + 4i, 4i + 3, 19 + 4i
+            }
+            const float dx = x.ds[x.tok(b) * items + it].x;
+#pragma unroll
+            for (int r = 0; r < R; r++) {
+                const uint32_t qw[4] = {q[r].x, q[r].y, q[r].z, q[r].w};
+                int sp = 0, sn = 0;
+#pragma unroll
+                for (int i = 0; i < 4; i++) {
+                    const uint32_t lo = qw[i], hi = qw[i] >> 16;
+                    sp = __dp4a(prmt_b32(MAG_LO, MAG_HI, lo), xa[i], sp);
+                    sn = __dp4a(prmt_b32(MAG_LO, MAG_HI, lo ^ 0x8888u), xa[i], sn);
+                    sp = __dp4a(prmt_b32(MAG_LO, MAG_HI, hi), xb[i], sp);
+                    sn = __dp4a(prmt_b32(MAG_LO, MAG_HI, hi ^ 0x8888u), xb[i], sn);
+                }
+                acc[r][b] += d[r] * dx * (float)(sp - sn);
             }
         }
     }
