@@ -117,6 +117,7 @@ class _Seq:
         self.repeat_run = 0
         self.logprobs: list[TokenLogprob] = []
         self.limit = 0
+        self.pixels: list[tuple[int, torch.Tensor]] = []    # (first prompt index, preprocessed image) until the tower has run
         self.image_rows: dict[int, torch.Tensor] = {}      # prompt index -> embedding row (image positions)
         self.spans: list[tuple[int, int]] = []              # prompt index ranges of the images: bidirectional attention inside
 
@@ -184,7 +185,8 @@ class Runner:
             "decode_seconds", "ttft_seconds", "decode_steps", "decode_step_sequences", "context_shifts", "draft_tokens",
             "draft_accepted_tokens")}
         self.done_reasons: dict[str, int] = {}
-        self._vision = None           # the vision tower, loaded with the first image (False: the model has none)
+        self._vision = None           # the vision tower, loaded with the first image
+        self._vision_cfg = None       # its hyper-parameters (False: the model takes no images)
         self._nvtx = bool(os.environ.get("B200_NVTX")) and str(getattr(self.backend, "device", "cpu")).startswith("cuda")
         self.thread = threading.Thread(target=self._loop, name="runner-loop", daemon=True)
         self.thread.start()
@@ -243,11 +245,11 @@ class Runner:
     def submit(self, req: CompletionRequest) -> _Seq:
         if self.closed:
             raise RunnerError("runner is closed")
-        image_rows: dict[int, torch.Tensor] = {}
+        pixels: list[tuple[int, torch.Tensor]] = []
         spans: list[tuple[int, int]] = []
         if isinstance(req.prompt, str):
             if req.images:
-                toks, image_rows, spans = self._tokenize_with_images(req)
+                toks, pixels, spans = self._tokenize_with_images(req)
             else:
                 toks = self.tokenize(req.prompt, add_special=req.add_special)
         else:
@@ -262,12 +264,12 @@ class Runner:
             if not req.truncate or req.embedding:
                 raise RunnerError("the prompt is longer than the context length currently available to the model; shorten the "
                                   "prompt, adjust the context length in settings, or use a model with a longer context length", 400)
-            if image_rows:
+            if pixels:
                 raise RunnerError("the prompt and its images are longer than the context length currently available to the model", 400)
             keep = min(max(req.num_keep, 0), limit // 2)
             toks = toks[:keep] + toks[len(toks) - (limit - keep):]
         seq = _Seq(req, toks)
-        seq.image_rows, seq.spans = image_rows, spans
+        seq.pixels, seq.spans = pixels, spans
         with self.cv:
             self.pending.append(seq)
             self.cv.notify_all()
@@ -275,12 +277,30 @@ class Runner:
 
     # -- images ---------------------------------------------------------------------------------------
     def vision(self):
-        """The model's vision tower (loaded on first use), or None for a text-only model or a back end that takes no embeddings."""
-        if self._vision is None and self.gguf is not None and getattr(self.backend, "supports_embeds", False):
+        """The vision hyper-parameters of the model when this runner takes images (the file carries a tower and the back end takes
+        embedding rows), else None.  Reads metadata only: safe from any thread."""
+        if self._vision_cfg is None and self.gguf is not None and getattr(self.backend, "supports_embeds", False):
+            from ..models.vision import vision_config_from_gguf
+            self._vision_cfg = vision_config_from_gguf(self.gguf) or False
+        return self._vision_cfg or None
+
+    def _tower(self):
+        """The vision tower on the model's device, loaded with the first image.  Runner thread only: loading and encoding
+        allocate device memory, which must not happen on another thread while this one may be capturing a CUDA graph."""
+        if self._vision is None:
             from ..models.vision import load_tower
             dev = self._cuda_device if self._cuda_device.startswith("cuda") else "cpu"
-            self._vision = load_tower(self.gguf, dev) or False
-        return self._vision or None
+            self._vision = load_tower(self.gguf, dev)
+        return self._vision
+
+    def _encode_images(self, s: "_Seq") -> None:
+        """Turn the pixels of a sequence's images into embedding rows (once, before its first prefill chunk)."""
+        tower = self._tower()
+        for lo, px in s.pixels:
+            emb = tower.project(tower.patches(px))
+            for j in range(emb.shape[0]):
+                s.image_rows[lo + j] = emb[j]
+        s.pixels = []
 
     def _tokenize_with_images(self, req: CompletionRequest):
         """Prompt text with ``[img-N]`` markers (server/prompt.go:96-133 writes them) -> token ids in which every image is a block
@@ -289,16 +309,17 @@ class Runner:
         tower's projection.  Returns (ids, {prompt index: embedding row}, [(first, last + 1) of each image])."""
         import hashlib
         import re
-        tower = self.vision()
-        if tower is None:
+        vc = self.vision()
+        if vc is None:
             raise RunnerError("this model does not take images", 400)
+        from ..models.vision import preprocess
         tk = self.tokenizer
         boi, eoi = tk.vocab.get("<start_of_image>"), tk.vocab.get("<end_of_image>")
         parts = re.split(r"\[img-(\d+)\]", req.prompt)
         if len(parts) == 1:               # no marker at all: the images go in front, in order
             parts = sum([["", str(i)] for i in range(len(req.images))], []) + parts
         toks: list[int] = []
-        rows: dict[int, torch.Tensor] = {}
+        pixels: list[tuple[int, torch.Tensor]] = []
         spans: list[tuple[int, int]] = []
         first = True
         for i, part in enumerate(parts):
@@ -312,7 +333,7 @@ class Runner:
                 raise RunnerError(f"the prompt names image {n} but the request has {len(req.images)}", 400)
             data = req.images[n]
             try:
-                emb = tower.encode(data)
+                px = preprocess(data, vc.image_size)
             except Exception as e:
                 raise RunnerError(f"image {n} could not be read: {e}", 400)
             h = int.from_bytes(hashlib.sha256(data).digest()[:4], "little")
@@ -323,14 +344,13 @@ class Runner:
             if boi is not None:
                 toks.append(boi)
             lo = len(toks)
-            for j in range(emb.shape[0]):
-                rows[len(toks)] = emb[j]
-                toks.append(-(1 + ((h * 1000003 + j) & 0x3FFFFFFF)))
+            pixels.append((lo, px))
+            toks += [-(1 + ((h * 1000003 + j) & 0x3FFFFFFF)) for j in range(vc.tokens_per_image)]
             spans.append((lo, len(toks)))
             if eoi is not None:
                 toks.append(eoi)
             toks += self.tokenize("\n\n", add_special=False)
-        return toks, rows, spans
+        return toks, pixels, spans
 
     def embedding(self, text: str | Sequence[int]) -> tuple[list[float], int]:
         seq = self.submit(CompletionRequest(prompt=text, embedding=True, truncate=False))
@@ -486,7 +506,7 @@ class Runner:
         # one prefill pass per iteration keeps decode latency of the other slots bounded; the pass takes rows of every
         # sequence that is waiting for its prompt, up to num_batch rows in all, when the backend can run them as one matrix
         waiting = [s for s in active if s.state == "prefill"]
-        if len(waiting) > 1 and hasattr(self.backend, "prefill_many") and not any(s.req.embedding or s.image_rows for s in waiting):
+        if len(waiting) > 1 and hasattr(self.backend, "prefill_many") and not any(s.req.embedding or s.image_rows or s.pixels for s in waiting):
             with self._range("prefill_batch"):
                 self._prefill_batch(waiting)
         elif waiting:
@@ -524,6 +544,8 @@ class Runner:
             self.slot_tokens[s.slot] = []
             self._release(s)
             return
+        if s.pixels:
+            self._encode_images(s)
         if s.image_rows:
             rows = [i for i in range(n) if s.n_past + i in s.image_rows]
             embeds = (rows, torch.stack([s.image_rows[s.n_past + i] for i in rows])) if rows else None
