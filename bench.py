@@ -372,7 +372,8 @@ def main() -> None:
             "metric": "decode_tok_s", "value": round(decode_tok_s, 2), "unit": "tok/s", "n_gpus": n_gpus, "steps": args.steps,
             "warmup": warmup, "ms_per_step": round(main_r["tot_ms"] / args.steps, 3), "higher_is_better": True,
             "scaling": "strong", "vs_baseline": None,
-            "dtype": "int8 activations x Q4_K/Q6_K weights (decode), bf16 (prefill)", "data": "synthetic",
+            "dtype": ("int8 activations x MXFP4 experts and 8 / 16-bit dense weights (decode), bf16 (prefill)" if wl["ft"] == "MXFP4"
+                      else "int8 activations x Q4_K/Q6_K weights (decode), bf16 (prefill)"), "data": "synthetic",
             "prompt_eval_tok_s": round(prefill_tok_s, 1), "ttft_ms_p50": round(ttft_p50, 3),
             "config": {"model": model, "quant": wl["ft"], "global_batch": slots, "seq_len": P + G, "prompt_tokens": P,
                        "generated_tokens": G, "num_ctx": wl["ctx"], "slots": slots, "kv_cache": args.kv_type,
