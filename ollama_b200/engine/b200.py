@@ -102,6 +102,11 @@ class B200Backend:
         # Subclasses that enqueue their own decode kernels (tensor parallelism) keep the dp4a planes.
         if os.environ.get("B200_ATTN_DECODE_STAGES", "") in ("2", "3", "4"):      # pipeline depth of the tensor-core decode attention (default: per launch)
             K.attn_decode_stages(int(os.environ["B200_ATTN_DECODE_STAGES"]))
+        # decode steps of at least this many sequences run their 16-bit matrices (bf16 weights, or resident bf16 copies of matrices
+        # that have no streaming-GEMV form) on the tcgen05 GEMM instead of the plane GEMV; 0 = never
+        # (tensor-parallel ranks keep the GEMV unless the variable asks otherwise)
+        env = os.environ.get("B200_TC_DECODE_MIN", "")
+        self.tc_decode_min = int(env) if env else (4 if type(self) is B200Backend else 0)
         self.moe_stream_q = os.environ.get("B200_MOE_STREAM_Q", "1") != "0"    # MoE prefill reads MXFP4 experts as they are (no 16-bit expansion per chunk)
         self.fuse_rope = os.environ.get("B200_FUSE_ROPE", "1") != "0"      # decode attention rotates Q / K and appends K / V itself
         self.use_sk = os.environ.get("B200_SK", "1") != "0" and not self.cfg.sandwich_norm and type(self) is B200Backend
@@ -324,7 +329,34 @@ class B200Backend:
         K._check(K.lib().b2_rmsnorm_quant(C.byref(a), nb, int(self.pdl), K.stream()), "rmsnorm_quant")
         self._n += 1
 
-    def _gemv(self, ws, nb, xq, xds, xf, out, ldo, accumulate=False):
+    @staticmethod
+    def _bf16_of(w):
+        """The 16-bit form of a matrix when one is resident: its bf16 copy, or the planes of a bf16 matrix."""
+        if w.experts or w.wtype not in (K.WT_BF16, K.WT_F16):      # quantised matrices stream fewer bytes through the GEMV
+            return None
+        b16 = getattr(w, "bf16", None)
+        if b16 is None and w.wtype == K.WT_BF16 and w.planes:
+            b16 = w.planes[0]
+        return b16 if b16 is not None and w.k % 8 == 0 and w.n % 4 == 0 else None
+
+    def _gemm_step(self, ws, b16s, nb, xf, out, accumulate=False, bias=None) -> None:
+        """A projection of a decode step on the tcgen05 GEMM: fp32 activation rows -> bf16, one product per matrix (the rows
+        beyond ``nb`` of the 128-row tile are the tensor map's zero fill).  Steps of several sequences on 16-bit matrices:
+        a dp4a / FMA GEMV over a 16-bit matrix costs one multiply-add per weight and token, the tensor core does not care."""
+        k = b16s[0].shape[1]
+        a16 = xf.view(-1)[:nb * k].view(nb, k).to(torch.bfloat16)      # activation rows are packed at the matrix's row length
+        off = 0
+        for w, b16 in zip(ws, b16s):
+            K.gemm_bf16(a16, b16, w.bias if bias is None else bias, out=out[:nb, off:off + b16.shape[0]], accumulate=accumulate)
+            off += b16.shape[0]
+        self._n += 1 + len(ws)
+
+    def _gemv(self, ws, nb, xq, xds, xf, out, ldo, accumulate=False, tc=True):
+        if tc and self.tc_decode_min and nb >= self.tc_decode_min and xf is not None and out.dim() == 2:
+            b16s = [self._bf16_of(w) for w in ws]
+            if all(b is not None for b in b16s):
+                self._gemm_step(ws, b16s, nb, xf, out, accumulate)
+                return
         a = K.GemvArgs()
         off = 0
         for i, w in enumerate(ws):
@@ -350,7 +382,8 @@ class B200Backend:
         c, b, lib, st = self.cfg, self.buf, K.lib(), K.stream
         k = c.n_experts_used
         pairs = nb * k
-        self._gemv([L.router], nb, b.xq, b.xds, b.xf, b.rlogits, b.rlogits.stride(0))
+        # the router stays on fp32 activations: its matrix is small and the choice of experts is sensitive to rounding
+        self._gemv([L.router], nb, b.xq, b.xds, b.xf, b.rlogits, b.rlogits.stride(0), tc=False)
         self._route(b.rlogits, nb, b.moe_ids, b.moe_lids, b.moe_w, self.pdl)
         ga = K.GluArgs()
         ga.gu = L.gu.desc()
@@ -474,7 +507,11 @@ class B200Backend:
                 self._decode_layer_sk(i, L, nb)
                 continue
             self._norm_quant(b.x, L.attn_norm, nb, c.d_model)
-            self._gemv([L.wq, L.wk, L.wv], nb, b.xq, b.xds, b.xf, b.qkv, b.qkv.stride(0))
+            if (self.tc_decode_min and nb >= self.tc_decode_min and L.wqkv16 is not None
+                    and all(w.wtype in (K.WT_BF16, K.WT_F16) for w in (L.wq, L.wk, L.wv))):
+                self._gemm_step([L.wq], [L.wqkv16], nb, b.xf, b.qkv, bias=L.bqkv)      # Q, K and V in one product
+            else:
+                self._gemv([L.wq, L.wk, L.wv], nb, b.xq, b.xds, b.xf, b.qkv, b.qkv.stride(0))
             local = L.swa and c.rope_base_local > 0
             ra = K.RopeKvArgs(K.ptr(b.qkv), K.ptr(b.positions), K.ptr(b.slots), K.ptr(self.inv_freq_local if local else self.inv_freq),
                               K.ptr(L.q_norm), K.ptr(L.k_norm), c.norm_eps, 1.0 if local else self.mscale, c.n_heads, c.n_kv_heads,

@@ -268,6 +268,10 @@ int launch(const void* a, const void* b, const GemmParams& p, cudaStream_t st, i
 int dispatch(const void* a, const void* b, const GemmParams& p, cudaStream_t st, int b_rows = 0) {
     // wide tiles once they fill the machine; narrower ones keep more SMs busy on small problems
     const long tiles_m = (p.m + BM - 1) / BM;
+    // a handful of rows (a decode step of several sequences): the product streams b once, so the narrowest tile that spreads
+    // b over the most SMs wins
+    if (p.m <= 32 && !p.out_bf16 && !p.glu && p.cm.n_dst == 0 && !b_rows && p.n >= 64 && (p.n + 127) / 128 < sm_count())
+        return launch<64>(a, b, p, st, b_rows);
     if (p.n >= 256 && tiles_m * ((p.n + 255) / 256) >= sm_count()) return launch<256>(a, b, p, st, b_rows);
     // one round either way: the widest tile that still gives every SM at most one tile
     if (p.n >= 192 && tiles_m * ((p.n + 191) / 192) <= sm_count() && tiles_m * ((p.n + 127) / 128) > sm_count()) return launch<192>(a, b, p, st, b_rows);

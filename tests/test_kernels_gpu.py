@@ -581,6 +581,64 @@ def test_gemm_bf16_tensor_core(m, n, k):
     assert torch.allclose(acc, ref - bias + 1, atol=1e-2 + 1e-3 * ref.abs().max().item(), rtol=1e-3)
 
 
+@pytest.mark.parametrize("m,n,k", [(4, 5120, 2880), (8, 2880, 4096), (16, 20480, 512), (32, 192, 64)])
+def test_gemm_bf16_of_a_decode_step(m, n, k):
+    """A handful of rows against a wide 16-bit matrix (narrow tiles over many SMs), written into a strided slice of a wider buffer."""
+    K = _K()
+    g = torch.Generator().manual_seed(m + n + k)
+    a = (torch.randn(m, k, generator=g) * 0.5).to(torch.bfloat16).cuda()
+    b = (torch.randn(n, k, generator=g) * 0.5).to(torch.bfloat16).cuda()
+    bias = torch.randn(n, generator=g).cuda()
+    ref = a.float() @ b.float().t() + bias
+    wide = torch.full((m + 3, n + 64), 7.0, device="cuda")
+    K.gemm_bf16(a, b, bias, out=wide[:m, 32:32 + n])
+    torch.cuda.synchronize()
+    assert K.gemm_status() == 0
+    assert torch.allclose(wide[:m, 32:32 + n], ref, atol=1e-2 + 1e-3 * ref.abs().max().item(), rtol=1e-3)
+    assert (wide[m:] == 7).all() and (wide[:, :32] == 7).all() and (wide[:, 32 + n:] == 7).all()
+
+
+@pytest.mark.parametrize("spec,ft", [("tiny-gpt-oss", "MXFP4"), ("tiny-qwen2", "BF16"), ("tiny-gemma3", "F16")])
+def test_engine_decode_steps_of_several_sequences_on_the_gemm(tmp_path, spec, ft):
+    """Six sequences per step: the 16-bit matrices of the step (attention projections, LM head) on the tcgen05 GEMM give the
+    logits of the GEMV route and of the fp32 graph, eagerly and from the recorded graph."""
+    from ollama_b200.engine.b200 import B200Backend
+    from ollama_b200.engine.backend import TorchBackend, open_model
+    from ollama_b200.models.synth import write_synthetic_gguf
+    p = str(tmp_path / "m.gguf")
+    write_synthetic_gguf(p, spec, ft)
+    g = open_model(p)
+    ref, eng = TorchBackend(g, "cpu"), B200Backend(g, "cuda")
+    assert eng.tc_decode_min == 4
+    nb = 6
+    ref.alloc(nb, 64)
+    eng.alloc(nb, 64)
+    gen = torch.Generator().manual_seed(11)
+    prompts = [torch.randint(259, 4096, (5 + 2 * i,), generator=gen).tolist() for i in range(nb)]
+    toks = []
+    for i, pr in enumerate(prompts):
+        lr = ref.prefill(i, pr, 0)
+        eng.prefill(i, pr, 0)
+        toks.append(int(lr.argmax()))
+    slots, pos = list(range(nb)), [len(pr) for pr in prompts]
+    lr = ref.decode(slots, toks, pos)
+    tol = 0.05 * lr.abs().max().item()
+    n0 = eng.kernel_launches
+    eng.use_graphs = False
+    le = eng.decode(slots, toks, pos).cpu()                 # GEMM route, eager (same positions again: the cache rows are rewritten)
+    assert (le - lr).abs().max().item() < tol and K_status_ok()
+    eng.tc_decode_min = 0
+    lv = eng.decode(slots, toks, pos).cpu()                 # GEMV route
+    assert (lv - lr).abs().max().item() < tol
+    assert (le - lv).abs().max().item() < 0.02 * lr.abs().max().item()
+    eng.tc_decode_min, eng.use_graphs = 4, True
+    for _ in range(3):                                      # warm-up, capture, replay
+        lg = eng.decode(slots, toks, pos).cpu()
+    assert torch.allclose(lg, le, atol=1e-3 * lr.abs().max().item())
+    assert K_status_ok() and eng.kernel_launches > n0
+    eng.close()
+
+
 @pytest.mark.parametrize("mode,keep", [("fused", False), ("bf16", False), ("bf16", True)])
 def test_engine_prefill_gemm_modes(tmp_path, mode, keep):
     """Prefill logits agree with the fp32 graph whichever way the weights reach the tensor cores."""
