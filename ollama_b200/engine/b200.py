@@ -206,6 +206,13 @@ class B200Backend:
         # a step takes up to 32 sequences only when no layer falls back to the dp4a kernels (eight per launch)
         if all(L.sk is not None for L in self.layers) and (self.sk_head is not None or not self.last) and type(self) is B200Backend:
             self.max_batch = MAX_STREAM_BATCH
+        # ... and up to 32 when every layer is a mixture of experts (its kernels run one grid row per token-expert pair) whose dense
+        # matrices are 16-bit and multiply on the tensor-core GEMM; the router's GEMV then runs eight rows per launch
+        if (type(self) is B200Backend and 0 < self.tc_decode_min <= MAX_DECODE_BATCH and self.layers and all(L.moe for L in self.layers)
+                and all(self._bf16_of(w) is not None for L in self.layers for w in ((L.wo,) if L.wqkv16 is not None else (L.wq, L.wk, L.wv, L.wo)))
+                and all(w.wtype in (K.WT_BF16, K.WT_F16) for L in self.layers for w in (L.wq, L.wk, L.wv))
+                and (not self.last or self._bf16_of(self.head) is not None)):
+            self.max_batch = MAX_STREAM_BATCH
         ff = vec("rope_freqs.weight")
         kw = dict(scaling=c.rope_scaling_type if c.rope_scaling_type != "llama3" else "none", factor=c.rope_scaling_factor,
                   orig_ctx=c.rope_orig_ctx, beta_fast=c.yarn_beta_fast, beta_slow=c.yarn_beta_slow, device=dev)
@@ -362,10 +369,14 @@ class B200Backend:
         for i, w in enumerate(ws):
             a.seg[i] = w.desc(out_off=off)
             off += w.n
-        a.nseg, a.nb = len(ws), nb
-        a.xq, a.xds, a.xf, a.out, a.ldo, a.accumulate = K.ptr(xq), K.ptr(xds), K.ptr(xf), K.ptr(out), ldo, int(accumulate)
-        K._check(K.lib().b2_gemv(C.byref(a), int(self.pdl), K.stream()), "gemv")
-        self._n += 1
+        k = ws[0].k
+        for r0 in range(0, nb, MAX_DECODE_BATCH):      # the kernel takes eight rows; rows are packed at the matrix's row length
+            a.nseg, a.nb = len(ws), min(MAX_DECODE_BATCH, nb - r0)
+            a.xq, a.xds = K.ptr(xq) + r0 * k, K.ptr(xds) + r0 * (k // 32) * 8
+            a.xf = K.ptr(xf) + r0 * k * 4 if xf is not None else None
+            a.out, a.ldo, a.accumulate = K.ptr(out) + r0 * ldo * 4, ldo, int(accumulate)
+            K._check(K.lib().b2_gemv(C.byref(a), int(self.pdl), K.stream()), "gemv")
+            self._n += 1
 
     def _route(self, logits: torch.Tensor, tokens: int, ids, lids, wts, pdl: bool) -> None:
         c = self.cfg

@@ -598,10 +598,11 @@ def test_gemm_bf16_of_a_decode_step(m, n, k):
     assert (wide[m:] == 7).all() and (wide[:, :32] == 7).all() and (wide[:, 32 + n:] == 7).all()
 
 
-@pytest.mark.parametrize("spec,ft", [("tiny-gpt-oss", "MXFP4"), ("tiny-qwen2", "BF16"), ("tiny-gemma3", "F16")])
-def test_engine_decode_steps_of_several_sequences_on_the_gemm(tmp_path, spec, ft):
-    """Six sequences per step: the 16-bit matrices of the step (attention projections, LM head) on the tcgen05 GEMM give the
-    logits of the GEMV route and of the fp32 graph, eagerly and from the recorded graph."""
+@pytest.mark.parametrize("spec,ft,nb", [("tiny-gpt-oss", "MXFP4", 6), ("tiny-gpt-oss", "MXFP4", 12), ("tiny-qwen2", "BF16", 6), ("tiny-gemma3", "F16", 6)])
+def test_engine_decode_steps_of_several_sequences_on_the_gemm(tmp_path, spec, ft, nb):
+    """Several sequences per step: the 16-bit matrices of the step (attention projections, LM head) on the tcgen05 GEMM give the
+    logits of the GEMV route and of the fp32 graph, eagerly and from the recorded graph.  A model of expert layers only, with
+    16-bit dense matrices, takes more than eight sequences in one step (the GEMV route then runs eight rows per launch)."""
     from ollama_b200.engine.b200 import B200Backend
     from ollama_b200.engine.backend import TorchBackend, open_model
     from ollama_b200.models.synth import write_synthetic_gguf
@@ -610,7 +611,7 @@ def test_engine_decode_steps_of_several_sequences_on_the_gemm(tmp_path, spec, ft
     g = open_model(p)
     ref, eng = TorchBackend(g, "cpu"), B200Backend(g, "cuda")
     assert eng.tc_decode_min == 4
-    nb = 6
+    assert eng.max_batch == (32 if spec == "tiny-gpt-oss" else 8)
     ref.alloc(nb, 64)
     eng.alloc(nb, 64)
     gen = torch.Generator().manual_seed(11)
