@@ -132,6 +132,8 @@ class TagStreamParser:
             t = self.buf.lstrip()
             if t.startswith(self.think_open):
                 self.buf, self.may_open_think = t[len(self.think_open):], False
+                if self.trim_start:
+                    self.lead_ws = True
                 return True
             if t and not self.think_open.startswith(t):
                 self.may_open_think = False
@@ -633,6 +635,12 @@ def parser_for(name: str | None, tools: list[dict[str, Any]] | None = None, thin
         return TagStreamParser(regions=[Region("<tool_call>", "</tool_call>", _xml_call(tools))])
     if name in ("qwen3.5", "ornith"):             # model/parsers/qwen35.go:57-78: reasoning unless switched off, XML calls, a call ends the block
         return TagStreamParser(think_open="<think>", think_close="</think>", start_thinking=think is not False and (think is None or bool(think)) and fresh,
+                               regions=[Region("<tool_call>", "</tool_call>", _xml_call(tools))], call_ends_thinking=True)
+    if name in ("nemotron-3-nano", "nemotron-3.5-nano"):
+        # model/parsers/nemotron3nano.go:46-66: the prompt ends inside the reasoning block unless reasoning is off or an answer is
+        # being continued; a repeated opening tag and the white space behind it go; a call without a closing tag ends the block
+        thinking = (think is None or bool(think)) and fresh
+        return TagStreamParser(think_open="<think>" if thinking else "", think_close="</think>", start_thinking=thinking, trim_start=thinking,
                                regions=[Region("<tool_call>", "</tool_call>", _xml_call(tools))], call_ends_thinking=True)
     if name == "functiongemma":
         return TagStreamParser(regions=[Region("<start_function_call>", "<end_function_call>", _functiongemma_call)])

@@ -996,9 +996,178 @@ class FunctionGemma(Dialect):
 
 
 # ---------------------------------------------------------------------------------------------------
+# Nemotron 3 nano
+# ---------------------------------------------------------------------------------------------------
+def _py_json(v: Any, shape: str = "any") -> str:
+    """A schema value the way the checkpoints' template prints it (``tojson`` of a Python object: ``", "`` and ``": "``
+    separators).  ``shape`` says what the wire type of the value is (model/renderers/nemotron3nano.go:382-476): "prop" is one
+    parameter's schema, printed with its known keys in a fixed order and a one-element type list as a plain string; "props" a
+    map of those in the order sent; anything else prints every key, sorted."""
+    if shape == "prop" and isinstance(v, dict):
+        parts = []
+        ty = _types(v)
+        for key in ("anyOf", "type", "items", "description", "enum", "properties", "required"):
+            val = v.get(key)
+            if key == "type":
+                if ty:
+                    parts.append('"type": ' + _py_json(ty[0] if len(ty) == 1 else ty))
+            elif val not in (None, "", [], {}) or (key == "items" and val is not None):
+                parts.append(f'"{key}": ' + _py_json(val, {"anyOf": "proplist", "properties": "props"}.get(key, "any")))
+        return "{" + ", ".join(parts) + "}"
+    if shape == "props" and isinstance(v, dict):
+        return "{" + ", ".join(json.dumps(k, ensure_ascii=False) + ": " + _py_json(p, "prop") for k, p in v.items()) + "}"
+    if shape == "proplist" and isinstance(v, list):
+        return "[" + ", ".join(_py_json(p, "prop") for p in v) + "]"
+    if isinstance(v, dict):
+        return "{" + ", ".join(json.dumps(k, ensure_ascii=False) + ": " + _py_json(v[k]) for k in sorted(v)) + "}"
+    if isinstance(v, (list, tuple)):
+        return "[" + ", ".join(_py_json(i) for i in v) + "]"
+    if isinstance(v, float) and v.is_integer() and abs(v) < 1e21:
+        return str(int(v))
+    return json.dumps(v, ensure_ascii=False)
+
+
+def _py_str(v: Any) -> str:
+    """A call argument or schema scalar as the template's ``str()`` prints it: ``True`` / ``False`` / ``None``, containers as JSON."""
+    if v is None:
+        return "None"
+    if isinstance(v, bool):
+        return "True" if v else "False"
+    if isinstance(v, (dict, list, tuple)):
+        return _py_json(v)
+    if isinstance(v, float) and v.is_integer() and abs(v) < 1e21:
+        return str(int(v))
+    return str(v)
+
+
+def _strip_think_toggles(s: str) -> str:
+    """``/think`` and ``/no_think`` switches go once they have been read; a real ``</think>`` tag stays."""
+    return s.replace("</think>", "\0").replace("/think", "").replace("/no_think", "").replace("\0", "</think>")
+
+
+class Nemotron3Nano(ChatML):
+    """ChatML with a system block on every prompt, XML tool declarations and calls in the Qwen3-Coder shape, and a ``<think>``
+    block on every assistant turn: the stored reasoning for turns after the last question, an empty pair for earlier ones and
+    for answers without reasoning (model/renderers/nemotron3nano.go:23-131).  The 3 checkpoints read ``/think`` and
+    ``/no_think`` switches out of system and user text (the last one wins over the request) and delete them; the 3.5
+    checkpoints leave text alone, close the reasoning block without line breaks, and ask for short reasoning with a note
+    behind the last question when the request's think value is "medium"."""
+
+    def __init__(self, v35: bool = False, image_tags: bool = True):
+        self.v35, self.image_tags = v35, image_tags
+
+    def prepare(self, x: Ctx) -> None:
+        on = x.think is None or bool(x.think)
+        if not self.v35:
+            texts = ([x.conv.system_text] if x.conv.system_text is not None else []) + [t.content for t in x.conv.turns if t.role in ("user", "system")]
+            for c in texts:
+                if "/think" in c.replace("</think>", ""):
+                    on = True
+                elif "/no_think" in c:
+                    on = False
+        x.memo["thinking"] = on
+        x.memo["question"] = x.conv.last_user()
+        x.memo["brief"] = self.v35 and x.think == "medium"
+
+    def head(self, x: Ctx) -> str:
+        body = x.conv.system_text or ""
+        if not self.v35:
+            body = _strip_think_toggles(body)
+        if x.tools:
+            body += ("\n\n" if body else "") + "# Tools\n\nYou have access to the following functions:\n\n<tools>"
+            body += "".join(map(self.declare, x.tools)) + "\n</tools>" + _QWEN3_CODER_CALL_FORMAT
+        return self.block("system", body)
+
+    @staticmethod
+    def declare(tool: dict[str, Any]) -> str:
+        f = tool.get("function") or {}
+        params = f.get("parameters") or {}
+        out = f"\n<function>\n<name>{f.get('name', '')}</name>"
+        if f.get("description"):
+            out += f"\n<description>{f['description'].strip()}</description>"
+        out += "\n<parameters>"
+        for name, prop in (params.get("properties") or {}).items():
+            prop = prop if isinstance(prop, dict) else {}
+            ty = _types(prop)
+            out += f"\n<parameter>\n<name>{name}</name>"
+            if ty:
+                out += "\n<type>" + (ty[0] if len(ty) == 1 else "[" + ", ".join(f"'{t}'" for t in ty) + "]") + "</type>"
+            if prop.get("description"):
+                out += f"\n<description>{prop['description'].strip()}</description>"
+            if prop.get("enum"):
+                out += f"\n<enum>{_py_json(prop['enum'])}</enum>"
+            if prop.get("anyOf"):
+                out += f"\n<anyOf>{_py_json(prop['anyOf'], 'proplist')}</anyOf>"
+            if prop.get("items") is not None:
+                out += f"\n<items>{_py_json(prop['items'])}</items>"
+            if prop.get("properties") is not None:
+                out += f"\n<properties>{_py_json(prop['properties'], 'props')}</properties>"
+            if prop.get("required"):
+                out += f"\n<required>{_py_json(prop['required'])}</required>"
+            out += "\n</parameter>"
+        if params.get("$defs") is not None:
+            out += f"\n<$defs>{_py_str(params['$defs'])}</$defs>"
+        if params.get("items") is not None:
+            out += f"\n<items>{_py_str(params['items'])}</items>"
+        if params.get("required"):
+            out += f"\n<required>{_py_json(params['required'])}</required>"
+        return out + "\n</parameters>\n</function>"
+
+    def text(self, t: Turn) -> str:
+        return image_tagged(t.content, t.images, t.first_image) if self.image_tags else t.content
+
+    def turn_other(self, t: Turn, x: Ctx) -> str:
+        if t.role not in ("user", "system"):
+            return self.block(t.role, t.content)
+        body = self.text(t)
+        if not self.v35:
+            body = _strip_think_toggles(body).strip()
+        elif t.role == "user" and t.pos == x.memo["question"] and x.memo["brief"]:
+            body += "\n\n{reasoning effort: efficient}"
+        return self.block(t.role, body)
+
+    turn_user = turn_other
+
+    def turn_tool(self, t: Turn, x: Ctx) -> str:
+        # a result with nothing in front of it opens no user block
+        return (f"{self.opener}user\n" if t.pos > 0 else "") + "".join(f"<tool_response>\n{c}\n</tool_response>\n" for _, c in t.results) + self.closer
+
+    def turn_assistant(self, t: Turn, x: Ctx) -> str:
+        body = t.content
+        if t.thinking:
+            body = "<think>\n" + t.thinking + ("</think>" if self.v35 else "\n</think>\n") + body
+        elif "<think>" not in body and "</think>" not in body:
+            body = "<think></think>" + body
+        earlier = t.pos < x.memo["question"]
+        if not t.calls:
+            if earlier and "<think>" in body and "</think>" in body:
+                body = "<think></think>" + body.rsplit("</think>", 1)[1]
+            return self.block("assistant", body.strip())
+        if not body.strip():
+            body = "<think></think>"
+        elif not earlier:
+            body = body.strip() + "\n"
+        else:
+            if "</think>" in body:
+                body = body.rsplit("</think>", 1)[1]
+            elif "<think>" in body:
+                body = body.split("<think>", 1)[0]
+            body = ("<think></think>" + body.strip()).strip() + "\n"
+        for name, args in t.calls:
+            body += f"<tool_call>\n<function={name}>\n" + "".join(f"<parameter={k}>\n{_py_str(v)}\n</parameter>\n" for k, v in args.items())
+            body += "</function>\n</tool_call>\n"
+        return self.block("assistant", body)
+
+    def cue(self, x: Ctx) -> str:
+        return f"{self.opener}assistant\n" + ("<think>\n" if x.memo["thinking"] else "<think></think>")
+
+
+# ---------------------------------------------------------------------------------------------------
 # registry
 # ---------------------------------------------------------------------------------------------------
 DIALECTS: dict[str, Callable[[], Dialect]] = {
+    "nemotron-3-nano": lambda: Nemotron3Nano(v35=False),
+    "nemotron-3.5-nano": lambda: Nemotron3Nano(v35=True),
     "qwen3-coder": Qwen3Coder,
     "qwen3-vl-instruct": lambda: Qwen3VL(thinking=False),
     "qwen3-vl-thinking": lambda: Qwen3VL(thinking=True),

@@ -33,7 +33,7 @@ def test_renderer_reproduces_the_reference_prompts(name):
 
 def test_every_registered_renderer_has_cases_and_renders_an_empty_conversation():
     covered = {c["renderer"] for c in CASES}
-    assert covered >= set(R.DIALECTS) - {"olmo3.1", "qwen3.5", "qwen3.8", "ornith", "cohere", "nemotron-3-nano", "nemotron-3.5-nano"}   # these have tests of their own below
+    assert covered >= set(R.DIALECTS) - {"olmo3.1", "qwen3.5", "qwen3.8", "ornith", "cohere"}   # these have tests of their own below
     for name in set(R.DIALECTS) - {"qwen3.8"}:
         assert isinstance(R.renderer_for(name).render([], None, None), str)
     assert R.renderer_for("olmo3.1").render([{"role": "user", "content": "hi"}]).startswith("<|im_start|>system\nYou are Olmo, a helpful AI assistant built by Ai2.")
