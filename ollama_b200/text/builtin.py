@@ -79,12 +79,14 @@ class TagStreamParser:
     """
 
     def __init__(self, *, think_open: str = "", think_close: str = "", start_thinking: bool = False, regions: list[Region] | None = None,
-                 call_ends_thinking: bool = False, keep_space: bool = False, drop_marks: dict[str, bool] | None = None, trim_start: bool = False):
+                 call_ends_thinking: bool = False, keep_space: bool = False, drop_marks: dict[str, bool] | None = None, trim_start: bool = False,
+                 trim_end: bool = False):
         self.think_open, self.think_close = think_open, think_close
         self.regions = [r for r in regions or [] if r.decode is not None or r.drop or r.unwrap]
         self.call_ends_thinking = call_ends_thinking    # a call that opens inside the reasoning block ends the block
         self.keep_space = keep_space                    # reasoning is handed on with the white space it ends in
         self.trim_start = trim_start                    # white space that opens the reasoning block, or a message without one, goes
+        self.trim_end = trim_end                        # white space the answer ends in goes when the stream ends
         self.drop_marks = dict(drop_marks or {})        # marks that only frame content: removed; True = white space after them goes too
         self.state: Any = "thinking" if start_thinking and think_close else "content"
         self.may_open_think = bool(think_open)          # an explicit opening tag is accepted at the very start only
@@ -178,6 +180,8 @@ class TagStreamParser:
                     return False
                 self.buf = t
             before = len(content)
+            if done and self.trim_end:
+                self.buf = self.buf.rstrip()
             self._flush(content, marks, done)
             if "".join(content[before:]).strip():
                 self.may_open_think = False
@@ -582,6 +586,45 @@ def _glm_call(tools: list[dict[str, Any]] | None) -> Callable[[str], dict[str, A
     return decode
 
 
+# -- Laguna: GLM-style pairs, a JSON object behind the name line, or a whole JSON call ------------------------------
+_LAGUNA_ALIASES = {"read_file": "read", "write_file": "write", "edit_file": "edit", "web_fetch": "webfetch"}
+
+
+def _laguna_call(tools: list[dict[str, Any]] | None) -> Callable[[str], dict[str, Any] | None]:
+    """``name`` + ``<arg_key>`` / ``<arg_value>`` pairs; ``name`` + a JSON object of arguments; or ``{"name", "arguments"}``
+    (model/parsers/laguna.go:424-569).  A name the request did not offer is mapped to the offered tool it commonly stands for
+    (``read_file`` -> ``read`` ...); a call repeated inside its own body counts once."""
+    declared = {(t.get("function") or {}).get("name") for t in tools or []}
+    pairs = _glm_call(tools)
+
+    def resolve(name: str) -> str:
+        alias = _LAGUNA_ALIASES.get(name)
+        return alias if name not in declared and alias in declared else name
+
+    def decode(body: str) -> dict[str, Any] | None:
+        body = body.strip()
+        while body.startswith("<tool_call>"):
+            body = body[len("<tool_call>"):].strip()
+        if body.startswith("{"):
+            call = _json_call(body)
+            if call is None:
+                return None
+            call["function"]["name"] = resolve(call["function"]["name"])
+            return call
+        name, _, rest = body.partition("\n")
+        if rest.strip().startswith("{"):
+            try:
+                args = json.loads(rest.strip())
+            except ValueError:
+                return None
+            return {"function": {"name": resolve(name.strip()), "arguments": args}} if isinstance(args, dict) and name.strip() else None
+        call = pairs(body)
+        if call is not None:
+            call["function"]["name"] = resolve(call["function"]["name"])
+        return call
+    return decode
+
+
 # -- Cohere: a JSON list of {"tool_call_id", "tool_name", "parameters"} between action marks ----------------------
 def _cohere_actions(body: str) -> list[dict[str, Any]]:
     def call(o: Any) -> dict[str, Any] | None:
@@ -636,6 +679,14 @@ def parser_for(name: str | None, tools: list[dict[str, Any]] | None = None, thin
     if name in ("qwen3.5", "ornith"):             # model/parsers/qwen35.go:57-78: reasoning unless switched off, XML calls, a call ends the block
         return TagStreamParser(think_open="<think>", think_close="</think>", start_thinking=think is not False and (think is None or bool(think)) and fresh,
                                regions=[Region("<tool_call>", "</tool_call>", _xml_call(tools))], call_ends_thinking=True)
+    if name in ("laguna", "poolside-v1"):
+        # model/parsers/laguna.go:68-95: reasoning only on request; the later checkpoints close a continued turn in the prompt, so
+        # they always start fresh.  A closing tag the model repeats (the prompt ends with one when reasoning is off) goes.
+        thinking = asked and (fresh or name == "poolside-v1")
+        p = TagStreamParser(think_open="<think>", think_close="</think>", start_thinking=thinking, trim_start=True, trim_end=True, call_ends_thinking=True,
+                            drop_marks={"</think>": True}, regions=[Region("<tool_call>", "</tool_call>", _laguna_call(tools))])
+        p.skip_ws = p.state == "content"
+        return p
     if name in ("nemotron-3-nano", "nemotron-3.5-nano"):
         # model/parsers/nemotron3nano.go:46-66: the prompt ends inside the reasoning block unless reasoning is off or an answer is
         # being continued; a repeated opening tag and the white space behind it go; a call without a closing tag ends the block

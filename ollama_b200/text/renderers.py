@@ -1163,9 +1163,102 @@ class Nemotron3Nano(ChatML):
 
 
 # ---------------------------------------------------------------------------------------------------
+# Laguna (Poolside)
+# ---------------------------------------------------------------------------------------------------
+_LAGUNA_IDENTITY = ("You are a helpful, conversationally-fluent assistant made by Poolside. You are here to be helpful to users through "
+                    "natural language conversations.")
+_LAGUNA_CALL_SHAPE = ("For each function call, return an unescaped XML-like object with function name and arguments within '<tool_call>' and "
+                      "'</tool_call>' tags, like here:\n")
+
+
+def _laguna_value(v: Any) -> str:
+    return v if isinstance(v, str) else go_json(v, spaced=True)
+
+
+class Laguna(Dialect):
+    """``<role>`` ... ``</role>`` blocks behind the end-of-sequence mark; a default identity when the conversation brings no system
+    message; tools as JSON lines inside ``<available_tools>``; every assistant turn opens with its reasoning block or a bare
+    closing tag; calls as ``<tool_call>name`` with ``<arg_key>`` / ``<arg_value>`` pairs (model/renderers/laguna.go:24-147).
+    ``compact`` is the later checkpoints' spelling (model/renderers/laguna.go:171-262): no line breaks inside blocks, no call
+    instructions, stored reasoning printed only when the request reasons, and the trailing assistant turn is closed too."""
+
+    bos = "〈|EOS|〉"
+
+    def __init__(self, compact: bool = False):
+        self.compact = compact
+
+    def prepare(self, x: Ctx) -> None:
+        x.memo["thinking"] = x.think is not None and bool(x.think)
+
+    def head(self, x: Ctx) -> str:
+        system = _LAGUNA_IDENTITY if x.conv.system_text is None else x.conv.system_text
+        on, nl = x.memo["thinking"], "" if self.compact else "\n"
+        out = self.bos
+        if not (system.strip() or x.tools or (self.compact and on)):
+            return out
+        out += "<system>" + nl
+        if system.strip():
+            out += nl + system.rstrip()
+        if x.tools:
+            if not self.compact or system.strip():
+                out += "\n\n"
+            out += ("### Tools\n\nYou may call functions to assist with the user query.\nAll available function signatures are listed below:\n"
+                    "<available_tools>\n" + "".join(go_json(tool_schema(t), spaced=True) + "\n" for t in x.tools) + "</available_tools>")
+            if not self.compact:
+                out += "\n\n"
+                if on:
+                    out += "Wrap your thinking in '<think>', '</think>' tags, followed by a function call. " + _LAGUNA_CALL_SHAPE + "<think> your thoughts here </think>\n"
+                else:
+                    out += _LAGUNA_CALL_SHAPE
+                out += "<tool_call>function-name\n<arg_key>argument-key</arg_key>\n<arg_value>value-of-argument-key</arg_value>\n</tool_call>"
+        return out + nl + "</system>\n"
+
+    def wrap(self, role: str, body: str) -> str:
+        nl = "" if self.compact else "\n"
+        return f"<{role}>{nl}{body}{nl}</{role}>\n"
+
+    def turn_user(self, t: Turn, x: Ctx) -> str:
+        return self.wrap("user", t.content)
+
+    def turn_system(self, t: Turn, x: Ctx) -> str:
+        return self.wrap("system", t.content)
+
+    def turn_tool(self, t: Turn, x: Ctx) -> str:
+        return "".join(self.wrap("tool_response", c) for _, c in t.results)
+
+    def turn_assistant(self, t: Turn, x: Ctx) -> str:
+        nl = "" if self.compact else "\n"
+        calls = "".join(f"<tool_call>{name}{nl}" + "".join(f"<arg_key>{k}</arg_key>{nl}<arg_value>{_laguna_value(v)}</arg_value>{nl}" for k, v in args.items())
+                        + f"</tool_call>{nl}" for name, args in t.calls)
+        if self.compact:
+            return "<assistant>" + (f"<think>{t.thinking}</think>" if x.memo["thinking"] else "</think>") + t.content + calls + "</assistant>\n"
+        content, reasoning = t.content, t.thinking
+        parts = content.split("</think>")
+        if len(parts) > 1:                              # reasoning stored inside the content
+            if not reasoning:
+                before = parts[0].rstrip("\n")
+                reasoning = before[before.rfind("<think>") + len("<think>"):].lstrip("\n") if "<think>" in before else before.lstrip("\n")
+            content = parts[-1].lstrip("\n")
+        out = "<assistant>\n" + (f"<think>\n{reasoning.strip()}\n</think>\n" if reasoning.strip() else "</think>\n")
+        if content.strip():
+            out += content.strip() + "\n"
+        out += calls
+        open_end = t is x.conv.last and bool(content.strip() or reasoning.strip() or t.calls)     # the model continues this turn
+        return out + ("" if open_end else "</assistant>\n")
+
+    def cue(self, x: Ctx) -> str:
+        last = x.conv.last
+        if not self.compact and last is not None and last.role == "assistant":
+            return ""
+        return "<assistant>" + ("" if self.compact else "\n") + ("<think>" if x.memo["thinking"] else "</think>")
+
+
+# ---------------------------------------------------------------------------------------------------
 # registry
 # ---------------------------------------------------------------------------------------------------
 DIALECTS: dict[str, Callable[[], Dialect]] = {
+    "laguna": lambda: Laguna(compact=False),
+    "poolside-v1": lambda: Laguna(compact=True),
     "nemotron-3-nano": lambda: Nemotron3Nano(v35=False),
     "nemotron-3.5-nano": lambda: Nemotron3Nano(v35=True),
     "qwen3-coder": Qwen3Coder,

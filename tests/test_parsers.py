@@ -168,3 +168,39 @@ def test_cohere_parser_cases():
         assert p.add(chunk, False)[0] != ""                      # streams before the generation ends
     assert run(["t<|END_THINKING|><|START_TEXT|>hi<|END_TEXT|><|END_OF_TURN_TOKEN|>"])[:2] == ("hi", "t")
     assert run(["t<|END_THINKING|>plain answer<|END_OF_TURN_TOKEN|>"])[0] == "plain answer"
+
+
+def test_laguna_parser_cases():
+    """model/parsers/laguna_test.go, restated: the three spellings of a call body, names mapped to the offered tool, reasoning only
+    on request and ended by a call, a repeated closing tag dropped, a continued answer, white space around the answer."""
+    tools = [{"type": "function", "function": {"name": "get_weather", "parameters": {"type": "object", "properties": {"location": {"type": "string"}, "days": {"type": "integer"}}}}}]
+    reader = [{"type": "function", "function": {"name": "read", "parameters": {"type": "object", "properties": {"path": {"type": "string"}}}}}]
+
+    def run(name, text, tools=tools, think=None, prefill=""):
+        outs = []
+        for chunks in ([text], _cut(text, 1), _cut(text, 7)):
+            p = B.parser_for(name, tools, think, prefill)
+            content = thinking = ""
+            calls = []
+            for i, ch in enumerate(chunks):
+                c, t, k = p.add(ch, i == len(chunks) - 1)
+                content, thinking, calls = content + c, thinking + t, calls + k
+            outs.append((content, thinking, [(k["function"]["name"], k["function"]["arguments"]) for k in calls]))
+        assert outs[0] == outs[1] == outs[2], text
+        return outs[0]
+
+    pairs = "<tool_call>get_weather\n<arg_key>location</arg_key>\n<arg_value>Paris</arg_value>\n<arg_key>days</arg_key>\n<arg_value>3</arg_value>\n</tool_call>"
+    assert run("laguna", pairs) == ("", "", [("get_weather", {"location": "Paris", "days": 3})])
+    assert run("laguna", '<tool_call>get_weather\n{"location":"San Francisco"}</tool_call>') == ("", "", [("get_weather", {"location": "San Francisco"})])
+    assert run("laguna", '<tool_call>\n{"name":"read_file","arguments":{"path":"./go.mod"}}\n</tool_call>', tools=reader) == ("", "", [("read", {"path": "./go.mod"})])
+    assert run("laguna", '<tool_call>\n{"name":"read_file","arguments":{"path":"x"}}\n</tool_call>')[2] == [("read_file", {"path": "x"})]      # no such tool offered: as written
+    assert run("laguna", "I should check.</think>\n\n" + pairs, think=True) == ("", "I should check.", [("get_weather", {"location": "Paris", "days": 3})])
+    assert run("laguna", "Let me look." + pairs, think=True)[1:] == ("Let me look.", [("get_weather", {"location": "Paris", "days": 3})])
+    assert run("laguna", "<think>\nhm\n</think>\nfine", think=True) == ("fine", "hm", [])
+    assert run("laguna", "Just an answer", think=True) == ("", "Just an answer", [])             # the prompt ended inside the block
+    for think in (None, False):
+        assert run("laguna", "</think>\n\n  Hello there  \n", think=think) == ("Hello there", "", [])
+        assert run("laguna", "Plain answer", think=think, tools=None) == ("Plain answer", "", [])
+    assert run("laguna", " continues here", think=True, prefill="It") == ("continues here", "", [])
+    assert run("poolside-v1", "thinking</think>answer", think=True, prefill="It") == ("answer", "thinking", [])
+    assert run("laguna", "ok <tool_call>never closed", think=None) == ("ok<tool_call>never closed", "", [])
