@@ -356,7 +356,10 @@ class Server:
                 if hp is not None:
                     thinking, content, _ = hp.add(content)
                 elif bp is not None:        # the model names a built-in parser (Modelfile PARSER)
-                    content, thinking, _ = bp.add(content, ch.done)
+                    try:
+                        content, thinking, _ = bp.add(content, ch.done)
+                    except ValueError as e:     # a call block the parser cannot read fails the request (server/routes.go:686-690, :2810-2814)
+                        raise APIError(500, str(e)) from e
                 elif tp is not None:
                     thinking, content = tp.add(content)
                 if think is not None and not think_enabled(think):
@@ -526,7 +529,10 @@ class Server:
                 if hp is not None:
                     thinking, content, calls = hp.add(content)
                 elif bp is not None:
-                    content, thinking, calls = bp.add(content, ch.done)
+                    try:
+                        content, thinking, calls = bp.add(content, ch.done)
+                    except ValueError as e:     # a call block the parser cannot read fails the request (server/routes.go:686-690, :2810-2814)
+                        raise APIError(500, str(e)) from e
                     for c in calls:         # calls of the built-in parsers get their id and running index here
                         c.setdefault("id", tool_call_id())
                         c["function"].setdefault("index", n_calls)

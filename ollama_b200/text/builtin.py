@@ -653,11 +653,129 @@ def _cohere_actions(body: str) -> list[dict[str, Any]]:
 
 
 PARSERS = ("qwen3", "qwen3-thinking", "qwen3-coder", "qwen3.5", "ornith", "qwen3-vl-instruct", "qwen3-vl-thinking", "ministral", "functiongemma", "cogito", "deepseek3",
-           "olmo3", "olmo3-think", "glm-4.6", "glm-4.7", "glm-ocr", "cohere", "lfm2", "lfm2-thinking", "passthrough")
+           "olmo3", "olmo3-think", "glm-4.6", "glm-4.7", "glm-ocr", "cohere", "lfm2", "lfm2-thinking", "nemotron-3-nano", "nemotron-3.5-nano",
+           "laguna", "poolside-v1", "glimmer", "passthrough")
+
+
+# ---------------------------------------------------------------------------------------------------
+# Glimmer: addressed messages instead of marks inside one message
+# ---------------------------------------------------------------------------------------------------
+_ATEM_OPEN, _ATEM_CLOSE = "<atem:function_calls>", "</atem:function_calls>"
+_ATEM_PARAM = re.compile(r'<atem:parameter name="([^"]*)">(.*?)</atem:parameter>\n?', re.S)
+
+
+class GlimmerStreamParser:
+    """A completion is a run of messages ``[<|start|>assistant] to=<recipient><|message|>body<|eom|>`` (the last one ends in
+    ``<|eot|>``; the prompt already holds the first ``<|start|>assistant``).  ``to=self`` is reasoning, ``to=<declared tool>``
+    a call written as an ``<atem:function_calls>`` block, anything else the answer (model/parsers/glimmer.go:55-141).  A tool may
+    be addressed with its name space repeated (``ns.ns.fn`` for ``ns.fn``); an answer that is nothing but a call block for
+    a declared tool counts as the call (the model forgot the address); a call block that does not parse raises ``ValueError``.
+    Same ``add(text, done)`` interface as :class:`TagStreamParser`."""
+
+    HEAD, MSG, ENDS = "<|start|>assistant", "<|message|>", ("<|eom|>", "<|eot|>")
+
+    def __init__(self, tools: list[dict[str, Any]] | None = None, think: Any = None):
+        self.tools = {((t.get("function") or {}).get("name") or "").strip(): t for t in tools or []}
+        self.tools.pop("", None)
+        self.emit_thinking = think is None or bool(think)
+        self.state, self.recipient, self.buf, self.streamed = "header", "", "", False
+
+    def _resolve(self, name: str) -> str | None:
+        if name in self.tools:
+            return name
+        ns, dot, fn = name.partition(".")
+        return fn if dot and fn in self.tools and fn.partition(".")[0] == ns else None
+
+    def _atem(self, body: str, want: str | None) -> dict[str, Any]:
+        body = body.strip()
+        if not (body.startswith(_ATEM_OPEN) and body.endswith(_ATEM_CLOSE)):
+            raise ValueError("missing ATEM function_calls wrapper")
+        inv = body[len(_ATEM_OPEN):-len(_ATEM_CLOSE)].strip()
+        if not (inv.startswith('<atem:invoke name="') and inv.endswith("</atem:invoke>") and '">' in inv):
+            raise ValueError("missing ATEM invoke wrapper")
+        name, _, rest = inv[len('<atem:invoke name="'):-len("</atem:invoke>")].partition('">')
+        name = name.replace(self.MSG, "")               # a stray message mark inside the name is dropped
+        fn = self._resolve(name)
+        if fn is None or (want is not None and fn != want):
+            raise ValueError(f"Glimmer recipient {want!r} does not match ATEM invoke {name!r}")
+        params, args, pos = rest.strip("\n"), {}, 0
+        while pos < len(params):
+            m = _ATEM_PARAM.match(params, pos)
+            if m is None:
+                raise ValueError("malformed ATEM parameter")
+            args[m.group(1)] = typed_value(m.group(2), _schema_types(list(self.tools.values()), fn, m.group(1)))
+            pos = m.end()
+        return {"function": {"name": fn, "arguments": args}}
+
+    def _may_be_call(self) -> bool:
+        t = self.buf.lstrip(" \t\r\n")
+        return bool(self.tools) and not self.streamed and (_ATEM_OPEN.startswith(t) or t.startswith(_ATEM_OPEN))
+
+    def add(self, text: str, done: bool = False) -> tuple[str, str, list[dict[str, Any]]]:
+        self.buf += text
+        content, thinking, calls = [], [], []
+        while True:
+            if self.state == "header":
+                if self.buf.startswith(self.HEAD):
+                    self.buf = self.buf[len(self.HEAD):]
+                elif self.buf.startswith("<") and self.HEAD.startswith(self.buf) and not done:
+                    break
+                i = self.buf.find(self.MSG)
+                if i < 0:
+                    if done:                             # no message follows: what is left is text
+                        content.append(self.buf)
+                        self.buf = ""
+                    break
+                self.recipient = self.buf[:i].strip().removeprefix("to=").strip()
+                self.buf = self.buf[i + len(self.MSG):]
+                self.state = "thinking" if self.recipient == "self" else "tool" if self._resolve(self.recipient) else "content"
+                self.streamed = False
+                continue
+            hold = self.state == "tool" or (self.state == "content" and self._may_be_call())
+            skip = 0                                    # a call block may hold the text of a mark inside a value
+            if hold:
+                j = self.buf.find(_ATEM_CLOSE)
+                skip = j + len(_ATEM_CLOSE) if j >= 0 else len(self.buf)
+            ends = [(k, len(m)) for m in self.ENDS if (k := self.buf.find(m, skip)) >= 0]
+            nxt = self.buf.find(self.HEAD, skip)        # the next message begins without an end mark
+            if nxt >= 0:
+                ends.append((nxt, 0))
+            if ends or done:
+                k, n = min(ends) if ends else (len(self.buf), 0)
+                body, self.buf = self.buf[:k], self.buf[k + n:]
+                if self.state == "tool":
+                    calls.append(self._atem(body, self._resolve(self.recipient)))
+                elif self.state == "thinking":
+                    if self.emit_thinking:
+                        thinking.append(body)
+                elif hold and body.strip().startswith(_ATEM_OPEN) and body.strip().endswith(_ATEM_CLOSE):
+                    try:
+                        calls.append(self._atem(body, None))
+                    except ValueError:
+                        content.append(body)
+                else:
+                    content.append(body)
+                self.state, self.recipient = "header", ""
+                if not ends:
+                    break
+                continue
+            if hold:
+                break
+            keep = max(_overlap(self.buf, m) for m in self.ENDS + (self.HEAD,))
+            out, self.buf = self.buf[:len(self.buf) - keep], self.buf[len(self.buf) - keep:]
+            if out:
+                if self.state == "thinking":
+                    if self.emit_thinking:
+                        thinking.append(out)
+                else:
+                    content.append(out)
+                    self.streamed = True
+            break
+        return "".join(content), "".join(thinking), calls
 
 
 def parser_for(name: str | None, tools: list[dict[str, Any]] | None = None, think: Any = None,
-               prefill: str = "") -> TagStreamParser | None:
+               prefill: str = "") -> "TagStreamParser | GlimmerStreamParser | None":
     """Parser named by a model's configuration, or None when the name is not a built-in of this module.
 
     ``think`` is the request's think value (None = unset); ``prefill`` the content of a trailing assistant message
@@ -679,6 +797,8 @@ def parser_for(name: str | None, tools: list[dict[str, Any]] | None = None, thin
     if name in ("qwen3.5", "ornith"):             # model/parsers/qwen35.go:57-78: reasoning unless switched off, XML calls, a call ends the block
         return TagStreamParser(think_open="<think>", think_close="</think>", start_thinking=think is not False and (think is None or bool(think)) and fresh,
                                regions=[Region("<tool_call>", "</tool_call>", _xml_call(tools))], call_ends_thinking=True)
+    if name == "glimmer":
+        return GlimmerStreamParser(tools, think)
     if name in ("laguna", "poolside-v1"):
         # model/parsers/laguna.go:68-95: reasoning only on request; the later checkpoints close a continued turn in the prompt, so
         # they always start fresh.  A closing tag the model repeats (the prompt ends with one when reasoning is off) goes.

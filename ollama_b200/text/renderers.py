@@ -28,6 +28,7 @@ functiongemma        Gemma turns, declarations and calls in the ``call:name{k:v}
 """
 from __future__ import annotations
 
+import datetime
 import json
 from dataclasses import dataclass, field
 from typing import Any, Callable
@@ -1254,9 +1255,133 @@ class Laguna(Dialect):
 
 
 # ---------------------------------------------------------------------------------------------------
+# Glimmer
+# ---------------------------------------------------------------------------------------------------
+_GLIMMER_TOOLS_INTRO = """In this environment you have access to a set of tools you can use to answer the user's question.
+
+You can invoke a function by writing a "<atem:function_calls>" block like the following:
+<atem:function_calls>
+<atem:invoke name="$FUNCTION_NAME">
+<atem:parameter name="$PARAMETER_NAME">$PARAMETER_VALUE</atem:parameter>
+...
+</atem:invoke>
+</atem:function_calls>
+
+String and scalar parameters should be specified as is, while lists and objects should use JSON format. Note that spaces for string values are not stripped. The output is not expected to be valid XML and is parsed with regular expressions.
+Here are the functions available in JSONSchema format:
+// Tool metadata
+"""
+_GLIMMER_TOOLS_OUTRO = """
+
+Here's an example of how to call a function in the tool set:
+(If the tool namespace is not specified, invoke the function directly as `example_function_name` rather than `example_tool_name.example_function_name`)
+
+to=example_tool_name.example_function_name
+
+<atem:function_calls>
+<atem:invoke name="example_tool_name.example_function_name">
+<atem:parameter name="example_parameter_1">value_1</atem:parameter>
+<atem:parameter name="example_parameter_2">This is the value for the second parameter
+that can span
+"multiple" lines
+</atem:parameter>
+</atem:invoke>
+</atem:function_calls>"""
+
+
+class Glimmer(Dialect):
+    """``<|start|>header<|message|>body`` messages closed by an end-of-turn or (when the same speaker goes on) end-of-message
+    mark; the assistant addresses every message: ``to=self`` for reasoning, ``to=<function>`` for a call written as an
+    ``<atem:function_calls>`` block, ``to=user`` for the answer (model/renderers/glimmer.go:289-368).  Every system message
+    carries the reasoning strength (from the request, unless its text names one), the tool declarations with their name
+    spaces, and the list of valid recipients; without a system message a default one with the knowledge cut-off and the
+    current date stands in front.  Works on the messages as sent: a tool result is named by its ``tool_name``, else by the
+    call its ``tool_call_id`` points to."""
+
+    bos = "<|begin_of_text|>"
+    knowledge_cutoff = "2026-01-04"
+
+    def __init__(self, image_tags: bool = True, current_date: str = ""):
+        self.image_tags, self.current_date = image_tags, current_date
+
+    @staticmethod
+    def _json(v: Any) -> str:
+        return go_json(v, spaced=True, html=False)
+
+    @staticmethod
+    def _msg(header: str, body: str, end: str) -> str:
+        return f"<|start|>{header}<|message|>{body}{end}"
+
+    def _system(self, text: str, tools: list[dict[str, Any]], strength: str, default: bool) -> str:
+        if default:
+            today = self.current_date or datetime.date.today().isoformat()
+            text += f"\nKnowledge cutoff: {self.knowledge_cutoff}.\nCurrent date: {today}."
+        else:
+            for a, b in (("Reasoning effort", "Reasoning strength"), ("Reasoning Effort", "Reasoning Strength"),
+                         ("reasoning effort", "reasoning strength"), ("REASONING EFFORT", "REASONING STRENGTH")):
+                text = text.replace(a, b)
+        if default or "reasoning strength" not in text.lower():
+            text += f"\n\nReasoning strength: {strength}."
+        spaces = list(dict.fromkeys(((t.get("function") or {}).get("name") or "").split(".", 1)[0] for t in tools))
+        if tools:
+            text += "\n\n" + _GLIMMER_TOOLS_INTRO + "".join('{"name": ' + self._json(n) + ', "description": ""}\n' for n in spaces) + "// Function schemas"
+            for t in tools:
+                f = t.get("function") or {}
+                text += ('\n{"name": ' + self._json(f.get("name") or "") + ', "description": ' + self._json(f.get("description") or "")
+                         + ', "parameters": ' + self._json(parameters_schema(f.get("parameters"))) + "}")
+            text += _GLIMMER_TOOLS_OUTRO
+        text += '\n\n# Valid recipients: "self"' + "".join(f', "{n}.*"' for n in spaces) + ', "user".'
+        return self._msg("system", text, "<|eot|>")
+
+    @staticmethod
+    def _atem(name: str, args: dict[str, Any]) -> str:
+        out = f'<atem:function_calls>\n<atem:invoke name="{name}">\n'
+        for k, v in args.items():
+            out += f'<atem:parameter name="{k}">' + (Glimmer._json(v) if isinstance(v, (dict, list)) else _xml_scalar(_plain(v, None))) + "</atem:parameter>\n"
+        return out + "</atem:invoke>\n</atem:function_calls>"
+
+    def render(self, messages: list[Message], tools: list[dict[str, Any]] | None = None, think: Any = None) -> str:
+        tools = list(tools or [])
+        strength = "high" if think is None or think is True else "none" if not think else str(think)
+        out = self.bos
+        if not any(m.get("role") == "system" for m in messages):
+            out += self._system("You are a helpful AI assistant.", tools, strength, True)
+        names = {c.get("id"): (c.get("function") or {}).get("name", "") for m in messages for c in m.get("tool_calls") or [] if c.get("id")}
+        seen = 0
+        for i, m in enumerate(messages):
+            role, n = m.get("role"), len(m.get("images") or [])
+            body = m.get("content") or ""
+            body = image_tagged(body, n, seen) if self.image_tags else "<|patch|>" * n + body
+            seen += n
+            if role == "system":
+                out += self._system(body, tools, strength, False)
+            elif role == "user":
+                out += self._msg("user", body, "<|eot|>")
+            elif role == "tool":
+                cid = m.get("tool_call_id") or ""
+                name = m.get("tool_name") or names.get(cid, cid)
+                out += self._msg("tool " + name, f'<tool_output name="{name}">\n{body}\n</tool_output>', "<|eot|>")
+            elif role == "assistant":
+                reasoning, calls = m.get("thinking") or "", m.get("tool_calls") or []
+                if reasoning:
+                    out += self._msg("assistant to=self", reasoning, "<|eom|>")
+                goes_on = i + 1 < len(messages) and messages[i + 1].get("role") == "assistant"
+                for j, c in enumerate(calls):
+                    f = c.get("function") or {}
+                    end = "<|eom|>" if j + 1 < len(calls) or goes_on else "<|eot|>"
+                    out += self._msg("assistant to=" + f.get("name", ""), self._atem(f.get("name", ""), f.get("arguments") or {}), end)
+                if not calls and (body or not reasoning):
+                    out += self._msg("assistant to=user", body, "<|eot|>")
+        return out + "<|start|>assistant"
+
+    __call__ = render
+
+
+# ---------------------------------------------------------------------------------------------------
 # registry
 # ---------------------------------------------------------------------------------------------------
 DIALECTS: dict[str, Callable[[], Dialect]] = {
+    "glimmer": lambda: Glimmer(),
     "laguna": lambda: Laguna(compact=False),
     "poolside-v1": lambda: Laguna(compact=True),
     "nemotron-3-nano": lambda: Nemotron3Nano(v35=False),

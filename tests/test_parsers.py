@@ -204,3 +204,62 @@ def test_laguna_parser_cases():
     assert run("laguna", " continues here", think=True, prefill="It") == ("continues here", "", [])
     assert run("poolside-v1", "thinking</think>answer", think=True, prefill="It") == ("answer", "thinking", [])
     assert run("laguna", "ok <tool_call>never closed", think=None) == ("ok<tool_call>never closed", "", [])
+
+
+def _glimmer_tool(name, props=None):
+    return {"type": "function", "function": {"name": name, "parameters": {"type": "object", "properties": props or {}}}}
+
+
+def _atem(name, params=""):
+    return f'<atem:function_calls>\n<atem:invoke name="{name}">\n{params}</atem:invoke>\n</atem:function_calls>'
+
+
+def _glimmer_run(text, tools=None, think=None, cuts=None):
+    """Every two-chunk split of ``text`` (or the given cut points) gives the same result; returns it."""
+    outs = set()
+    for split in (range(len(text) + 1) if cuts is None else cuts):
+        p = B.parser_for("glimmer", tools, think)
+        content = thinking = ""
+        calls = []
+        for i, ch in enumerate((text[:split], text[split:])):
+            c, t, k = p.add(ch, i == 1)
+            content, thinking, calls = content + c, thinking + t, calls + k
+        outs.add((content, thinking, json.dumps([(k["function"]["name"], k["function"]["arguments"]) for k in calls])))
+    assert len(outs) == 1, outs
+    c, t, k = outs.pop()
+    return c, t, [tuple(x) for x in json.loads(k)]
+
+
+def test_glimmer_parser_cases():
+    """model/parsers/glimmer_test.go, restated: addressed messages, reasoning on and off, typed call values, mark text inside a
+    value, several messages at every split point, the repeated name space, a call without an address, text that only looks like one."""
+    assert _glimmer_run(" to=user<|message|>Hello") == ("Hello", "", [])
+    assert _glimmer_run(" to=self<|message|>Check the facts.") == ("", "Check the facts.", [])
+    both = " to=self<|message|>Check the facts.<|eom|><|start|>assistant to=user<|message|>Answer<|eot|>"
+    assert _glimmer_run(both, think=False) == ("Answer", "", [])
+    assert _glimmer_run(both) == ("Answer", "Check the facts.", [])
+    assert _glimmer_run(" to=self<|message|>Think<|start|>assistant to=user<|message|>Answer") == ("Answer", "Think", [])      # no end mark
+    tool = _glimmer_tool("tools.run", {"text": {"type": "string"}, "count": {"type": "integer"}, "enabled": {"type": "boolean"}, "items": {"type": "array"},
+                                       "config": {"type": "object"}, "choice": {"anyOf": [{"type": "null"}, {"type": "string"}]}})
+    params = ('<atem:parameter name="text"> keep  spaces </atem:parameter>\n<atem:parameter name="count">3</atem:parameter>\n'
+              '<atem:parameter name="enabled">true</atem:parameter>\n<atem:parameter name="items">["one", "two"]</atem:parameter>\n'
+              '<atem:parameter name="config">{"mode":"fast"}</atem:parameter>\n<atem:parameter name="choice">null</atem:parameter>\n')
+    want = {"text": " keep  spaces ", "count": 3, "enabled": True, "items": ["one", "two"], "config": {"mode": "fast"}, "choice": None}
+    assert _glimmer_run(" to=tools.run<|message|>" + _atem("tools.run", params), [tool], cuts=(0, 40, 200)) == ("", "", [("tools.run", want)])
+    assert _glimmer_run(" to=tools.tools.run<|message|>" + _atem("tools.run", params), [tool], cuts=(0,))[2] == [("tools.run", want)]     # name space said twice
+    echo = _glimmer_tool("echo", {"text": {"type": "string"}})
+    value = "literal <|eot|> and <|start|>assistant to=user<|message|> text"
+    got = _glimmer_run(" to=echo<|message|>" + _atem("echo", f'<atem:parameter name="text">{value}</atem:parameter>\n') + "<|eot|>", [echo])
+    assert got == ("", "", [("echo", {"text": value})])
+    first, second = _glimmer_tool("first", {"x": {"type": "integer"}}), _glimmer_tool("second")
+    run = (" to=self<|message|>Think<|eom|><|start|>assistant to=first<|message|>" + _atem("first", '<atem:parameter name="x">1</atem:parameter>\n')
+           + "<|eom|><|start|>assistant to=second<|message|>" + _atem("second") + "<|eot|>")
+    assert _glimmer_run(run, [first, second]) == ("", "Think", [("first", {"x": 1}), ("second", {})])
+    assert _glimmer_run(" to=user<|message|>" + _atem("echo", '<atem:parameter name="text">hi</atem:parameter>\n') + "<|eot|>", [echo]) == ("", "", [("echo", {"text": "hi"})])
+    looks = " to=user<|message|>Use " + _atem("echo") + " like this.<|eot|>"
+    assert _glimmer_run(looks, [echo]) == ("Use " + _atem("echo") + " like this.", "", [])
+    assert _glimmer_run(" to=nobody<|message|>Hi<|eot|>", [echo]) == ("Hi", "", [])                 # an undeclared recipient reads as the answer
+    with pytest.raises(ValueError):
+        B.parser_for("glimmer", [first, second]).add(" to=first<|message|>" + _atem("second") + "<|eot|>", True)
+    with pytest.raises(ValueError):
+        B.parser_for("glimmer", [first]).add(" to=first<|message|><atem:function_calls>oops<|eot|>", True)

@@ -19,6 +19,8 @@ def _renderer(case):
     r = R.renderer_for(case["renderer"])
     if "image_tags" in case:
         r.image_tags = case["image_tags"]
+    if "current_date" in case:
+        r.current_date = case["current_date"]
     return r
 
 
@@ -182,3 +184,28 @@ def test_cohere_renderer():
             '        "is_error": null\n    },\n    {\n        "tool_call_id": "1",\n        "results": {\n\n            \n            "0": {"content": "r2"}\n\n        },\n'
             '        "is_error": null\n    }\n\n]<|END_TOOL_RESULT|>') in got
     assert r.render([{"role": "user", "content": "Q"}, {"role": "Chatbot", "content": "partial"}]).endswith(f"{T0}<|CHATBOT_TOKEN|><|START_TEXT|>partial")
+
+
+def test_glimmer_images_call_values_strength_and_result_names():
+    """model/renderers/glimmer_test.go, restated."""
+    g = R.renderer_for("glimmer")
+    g.image_tags = False
+    assert "<|start|>user<|message|><|patch|>Describe.<|eot|>" in g.render([{"role": "user", "content": "Describe.", "images": ["aQ=="]}])
+    tagged = R.renderer_for("glimmer").render([{"role": "user", "content": "First.", "images": ["aQ=="]}, {"role": "assistant", "content": "Done."},
+                                               {"role": "user", "content": "Compare.", "images": ["ag==", "aw=="]}])
+    assert ("<|start|>user<|message|>[img-0] First.<|eot|><|start|>assistant to=user<|message|>Done.<|eot|>"
+            "<|start|>user<|message|>[img-1][img-2] Compare.<|eot|>") in tagged
+    args = {"text": "keep  spaces", "count": 3, "enabled": True, "fallback": None, "items": ["one", "two"], "config": {"mode": "fast"}}
+    got = g.render([{"role": "user", "content": "Run it."}, {"role": "assistant", "tool_calls": [{"function": {"name": "tools.run", "arguments": args}}]}])
+    assert ('<atem:function_calls>\n<atem:invoke name="tools.run">\n<atem:parameter name="text">keep  spaces</atem:parameter>\n'
+            '<atem:parameter name="count">3</atem:parameter>\n<atem:parameter name="enabled">true</atem:parameter>\n'
+            '<atem:parameter name="fallback">null</atem:parameter>\n<atem:parameter name="items">["one", "two"]</atem:parameter>\n'
+            '<atem:parameter name="config">{"mode": "fast"}</atem:parameter>\n</atem:invoke>\n</atem:function_calls>') in got
+    for think, want in ((None, "high"), (True, "high"), (False, "none"), ("medium", "medium")):
+        assert f"Reasoning strength: {want}." in g.render([{"role": "user", "content": "Hello"}], None, think)
+    got = g.render([{"role": "assistant", "tool_calls": [{"id": "call_1", "function": {"name": "get_weather", "arguments": {}}}]},
+                    {"role": "tool", "tool_call_id": "call_1", "content": '{"temp":65}'}, {"role": "tool", "tool_call_id": "missing", "content": "not found"}])
+    assert '<|start|>tool get_weather<|message|><tool_output name="get_weather">\n{"temp":65}\n</tool_output><|eot|>' in got
+    assert '<|start|>tool missing<|message|><tool_output name="missing">\nnot found\n</tool_output><|eot|>' in got
+    import datetime
+    assert f"Current date: {datetime.date.today().isoformat()}." in g.render([{"role": "user", "content": "x"}])
