@@ -30,6 +30,7 @@ from __future__ import annotations
 
 import datetime
 import json
+import re
 from dataclasses import dataclass, field
 from typing import Any, Callable
 
@@ -1378,9 +1379,252 @@ class Glimmer(Dialect):
 
 
 # ---------------------------------------------------------------------------------------------------
+# Gemma 4
+# ---------------------------------------------------------------------------------------------------
+_G4Q = '<|"|>'                                      # the string delimiter of the format
+_G4_STANDARD = ("description", "type", "properties", "required", "nullable")
+
+
+def _g4_upper(v: Any) -> list[str]:
+    return [v.upper()] if isinstance(v, str) else [t.upper() for t in v if isinstance(t, str)] if isinstance(v, (list, tuple)) else []
+
+
+def _g4_strs(v: Any) -> list[str]:
+    return [x for x in v if isinstance(x, str)] if isinstance(v, (list, tuple)) else []
+
+
+def _g4_num(v: Any) -> str:
+    return str(int(v)) if isinstance(v, float) and v.is_integer() else str(v)
+
+
+def _g4_value(v: Any, schema: bool = False) -> str:
+    """A call argument (keys bare) or a schema value (keys quoted): strings between the format's delimiters, maps sorted."""
+    if v is None:
+        return "null"
+    if isinstance(v, str):
+        return _G4Q + v + _G4Q
+    if isinstance(v, bool):
+        return "true" if v else "false"
+    if isinstance(v, (int, float)):
+        return _g4_num(v)
+    if isinstance(v, dict):
+        return "{" + ",".join(((_G4Q + k + _G4Q) if schema else k) + ":" + _g4_value(v[k], schema) for k in sorted(v)) + "}"
+    if isinstance(v, (list, tuple)):
+        return "[" + ",".join(_g4_value(i, schema) for i in v) + "]"
+    return str(v)
+
+
+def _g4_typed(prop: dict[str, Any]) -> dict[str, Any]:
+    """One declared parameter as the wire type keeps it (type, description, enum, items, properties, required; a union of bare
+    types written as ``anyOf`` counts as a type list), with a type list folded into one string the way the checkpoints'
+    template prints it (model/renderers/gemma4.go:473-513)."""
+    out: dict[str, Any] = {}
+    ty = _types(prop) if prop.get("type") else []
+    if not ty and prop.get("anyOf"):
+        bare = all(isinstance(b, dict) and b.get("type") and not any(b.get(k) for k in ("anyOf", "items", "description", "enum", "properties", "required"))
+                   for b in prop["anyOf"])
+        if bare:
+            ty = list(dict.fromkeys(t for b in prop["anyOf"] for t in _types(b)))
+    if ty:
+        out["type"] = ty[0] if len(ty) == 1 else "[" + ", ".join(f"'{t.upper()}'" for t in ty) + "]"
+    if prop.get("description"):
+        out["description"] = prop["description"]
+    if prop.get("enum"):
+        out["enum"] = prop["enum"]
+    if prop.get("items") is not None:
+        out["items"] = prop["items"]
+    if prop.get("properties") is not None:
+        out["properties"] = {k: _g4_typed(v if isinstance(v, dict) else {}) for k, v in prop["properties"].items()}
+    if prop.get("required"):
+        out["required"] = prop["required"]
+    return out
+
+
+def _g4_type_spec(names: list[str]) -> str:
+    return "type:" + (_G4Q + names[0] + _G4Q if len(names) == 1 else "[" + ",".join(_G4Q + n + _G4Q for n in names) + "]")
+
+
+def _g4_required(v: Any) -> str:
+    return "required:[" + ",".join(_G4Q + r + _G4Q for r in _g4_strs(v)) + "]"
+
+
+def _g4_items(items: dict[str, Any]) -> str:
+    parts = []
+    for key in sorted(items):
+        v = items[key]
+        if v is None:
+            continue
+        if key == "properties":
+            parts.append("properties:{" + (_g4_props(v) if isinstance(v, dict) else "") + "}")
+        elif key == "required":
+            parts.append(_g4_required(v))
+        elif key == "type":
+            names = _g4_upper(v)
+            parts.append(_g4_type_spec(names) if names else "")
+        else:
+            parts.append(key + ":" + _g4_value(v, schema=True))
+    return ",".join(parts)
+
+
+def _g4_props(props: dict[str, Any]) -> str:
+    """Parameters by name, sorted: description, then what the first type calls for (enum of a string, items of an array, nested
+    properties and required of an object), nullable, and the type last (model/renderers/gemma4.go:329-450)."""
+    out = []
+    for name in sorted(props):
+        prop = props[name]
+        if name in _G4_STANDARD or not isinstance(prop, dict):
+            continue
+        parts = []
+        if isinstance(prop.get("description"), str) and prop["description"]:
+            parts.append("description:" + _G4Q + prop["description"] + _G4Q)
+        names = _g4_upper(prop.get("type"))
+        first = names[0] if names else ""
+        if first == "STRING" and isinstance(prop.get("enum"), (list, tuple)) and prop["enum"]:
+            parts.append("enum:[" + ",".join(_G4Q + (_g4_num(e) if isinstance(e, (int, float)) and not isinstance(e, bool) else
+                                                     ("true" if e else "false") if isinstance(e, bool) else str(e)) + _G4Q for e in prop["enum"]) + "]")
+        if first == "ARRAY" and isinstance(prop.get("items"), dict) and prop["items"]:
+            parts.append("items:{" + _g4_items(prop["items"]) + "}")
+        if prop.get("nullable") is True:
+            parts.append("nullable:true")
+        if first == "OBJECT":
+            nested = prop.get("properties")
+            parts.append("properties:{" + _g4_props(nested if isinstance(nested, dict) else prop) + "}")
+            if _g4_strs(prop.get("required")):
+                parts.append(_g4_required(prop["required"]))
+        if names:
+            parts.append(_g4_type_spec(names))
+        out.append(name + ":{" + ",".join(parts) + "}")
+    return ",".join(out)
+
+
+def _g4_without_channels(text: str) -> str:
+    """Stored answers lose their ``<|channel>`` ... ``<channel|>`` stretches; one that never closes takes the rest with it."""
+    out = ""
+    while True:
+        a = text.find("<|channel>")
+        if a < 0:
+            return (out + text).strip()
+        out += text[:a]
+        b = text.find("<channel|>", a)
+        if b < 0:
+            return out.strip()
+        text = text[b + len("<channel|>"):]
+
+
+class Gemma4(Dialect):
+    """``<|turn>role`` ... ``<turn|>`` turns behind ``<bos>``; a system turn when there is a system (or developer) message, a
+    tool or a request to reason (``<|think|>``); tools as ``<|tool>declaration:name{...}<tool|>`` in a key:value notation with
+    its own string delimiter; an assistant turn holds its reasoning (after the last question only) as a ``thought`` channel,
+    its calls, and the results that answer them, and a run of assistant messages is one model turn; after results the prompt
+    goes on inside that turn instead of opening a new one (model/renderers/gemma4.go:24-147).  ``empty_block``: the large
+    checkpoints get an empty thought channel in the cue when reasoning is off."""
+
+    bos = "<bos>"
+
+    def __init__(self, image_tags: bool = True, empty_block: bool = False):
+        self.image_tags, self.empty_block = image_tags, empty_block
+
+    @staticmethod
+    def declare(tool: dict[str, Any]) -> str:
+        f = tool.get("function") or {}
+        params = f.get("parameters") or {}
+        out = "<|tool>declaration:" + (f.get("name") or "") + "{description:" + _G4Q + (f.get("description") or "") + _G4Q
+        props = params.get("properties")
+        if props is not None or params.get("type"):
+            parts = []
+            if props:
+                parts.append("properties:{" + _g4_props({k: _g4_typed(v if isinstance(v, dict) else {}) for k, v in props.items()}) + "}")
+            if params.get("required"):
+                parts.append(_g4_required(params["required"]))
+            if params.get("type"):
+                parts.append("type:" + _G4Q + str(params["type"]).upper() + _G4Q)
+            out += ",parameters:{" + ",".join(parts) + "}"
+        return out + "}<tool|>"
+
+    def render(self, messages: list[Message], tools: list[dict[str, Any]] | None = None, think: Any = None) -> str:
+        tools = list(tools or [])
+        on = think is not None and bool(think)
+        lead = bool(messages) and messages[0].get("role") in ("system", "developer")
+        msgs = messages[1:] if lead else messages
+        out = self.bos
+        if lead or tools or on:
+            out += "<|turn>system\n" + ("<|think|>\n" if on else "") + (messages[0].get("content") or "").strip() * lead
+            out += "".join(map(self.declare, tools)) + "<turn|>\n"
+        question = max((i for i, m in enumerate(msgs) if m.get("role") == "user"), default=-1)
+        seen = 0
+
+        def text(m: Message, trim: bool) -> str:
+            nonlocal seen
+            body, n = m.get("content") or "", len(m.get("images") or [])
+            if trim:
+                body = body.strip()
+            if n and self.image_tags:
+                body = image_tagged(body, n, seen)
+                seen += n
+            return body
+
+        def next_speaker(i: int) -> str:
+            return next((m.get("role") or "" for m in msgs[i + 1:] if m.get("role") != "tool"), "")
+
+        last_kind, before = "", ""
+        for i, m in enumerate(msgs):
+            role = m.get("role") or ""
+            if role == "tool":
+                continue
+            last_kind = ""
+            shown = "model" if role == "assistant" else role
+            if not (shown == "model" and before == "assistant"):
+                out += f"<|turn>{shown}\n"
+            if role == "assistant" and m.get("thinking") and i > question:
+                out += "<|channel>thought\n" + m["thinking"] + "\n<channel|>"
+            calls = m.get("tool_calls") or []
+            for c in calls:
+                f = c.get("function") or {}
+                args = f.get("arguments") or {}
+                out += "<|tool_call>call:" + f.get("name", "") + "{" + ",".join(k + ":" + _g4_value(args[k]) for k in sorted(args)) + "}<tool_call|>"
+                last_kind = "tool_call"
+            answered = False
+            if calls:
+                for r in msgs[i + 1:]:
+                    if r.get("role") != "tool":
+                        break
+                    name = r.get("tool_name") or "unknown"
+                    if r.get("tool_call_id"):
+                        name = next(((c.get("function") or {}).get("name", "") for c in calls if c.get("id") == r["tool_call_id"]), name)
+                    out += "<|tool_response>response:" + name + "{value:" + _g4_value(text(r, False)) + "}<tool_response|>"
+                    answered, last_kind = True, "tool_response"
+            has_body = False
+            if shown == "model":
+                if m.get("content") or m.get("images"):
+                    m = dict(m, content=_g4_without_channels(m.get("content") or ""))
+                    out += text(m, False)
+                    has_body = bool(m["content"].strip() or m.get("images"))
+            else:
+                out += text(m, True)
+                has_body = bool((m.get("content") or "").strip() or m.get("images"))
+            nxt = next_speaker(i)
+            goes_on = shown == "model" and nxt == "assistant" and (not calls or answered)
+            if last_kind == "tool_call" and not answered:
+                out += "<|tool_response>"
+            elif not goes_on and not (answered and not has_body and nxt == ""):
+                out += "<turn|>\n"
+            before = role
+        if last_kind not in ("tool_response", "tool_call"):
+            out += "<|turn>model\n" + ("<|channel>thought\n<channel|>" if self.empty_block and not on else "")
+        elif last_kind == "tool_response" and on:
+            out += "<|channel>thought\n"
+        return out
+
+    __call__ = render
+
+
+# ---------------------------------------------------------------------------------------------------
 # registry
 # ---------------------------------------------------------------------------------------------------
 DIALECTS: dict[str, Callable[[], Dialect]] = {
+    "gemma4": lambda: Gemma4(),
+    "gemma4-small": lambda: Gemma4(),
+    "gemma4-large": lambda: Gemma4(empty_block=True),
     "glimmer": lambda: Glimmer(),
     "laguna": lambda: Laguna(compact=False),
     "poolside-v1": lambda: Laguna(compact=True),

@@ -35,7 +35,7 @@ def test_renderer_reproduces_the_reference_prompts(name):
 
 def test_every_registered_renderer_has_cases_and_renders_an_empty_conversation():
     covered = {c["renderer"] for c in CASES}
-    assert covered >= set(R.DIALECTS) - {"olmo3.1", "qwen3.5", "qwen3.8", "ornith", "cohere"}   # these have tests of their own below
+    assert covered >= set(R.DIALECTS) - {"olmo3.1", "qwen3.5", "qwen3.8", "ornith", "cohere", "gemma4-small", "gemma4-large"}   # these have tests of their own below
     for name in set(R.DIALECTS) - {"qwen3.8"}:
         assert isinstance(R.renderer_for(name).render([], None, None), str)
     assert R.renderer_for("olmo3.1").render([{"role": "user", "content": "hi"}]).startswith("<|im_start|>system\nYou are Olmo, a helpful AI assistant built by Ai2.")
@@ -209,3 +209,28 @@ def test_glimmer_images_call_values_strength_and_result_names():
     assert '<|start|>tool missing<|message|><tool_output name="missing">\nnot found\n</tool_output><|eot|>' in got
     import datetime
     assert f"Current date: {datetime.date.today().isoformat()}." in g.render([{"role": "user", "content": "x"}])
+
+
+def test_gemma4_variants_and_turns_that_continue():
+    """model/renderers/gemma4_reference_test.go, the tables besides the main one: the large checkpoints' empty thought channel in the
+    cue (not when the request reasons), and a run of assistant messages with a call and its result rendered as one model turn."""
+    hello = [{"role": "user", "content": "Hello"}]
+    base = "<bos><|turn>user\nHello<turn|>\n<|turn>model\n"
+    assert R.renderer_for("gemma4").render(hello) == R.renderer_for("gemma4-small").render(hello) == base
+    assert R.renderer_for("gemma4-large").render(hello) == base + "<|channel>thought\n<channel|>"
+    assert R.renderer_for("gemma4-large").render(hello, None, True) == "<bos><|turn>system\n<|think|>\n<turn|>\n<|turn>user\nHello<turn|>\n<|turn>model\n"
+    msgs = [{"role": "user", "content": "Use the tool"}, {"role": "assistant", "content": "First."},
+            {"role": "assistant", "content": "Checking.", "tool_calls": [{"function": {"name": "bash", "arguments": {"command": None}}}]},
+            {"role": "tool", "tool_name": "bash", "content": "done"}, {"role": "assistant", "content": "Done."}, {"role": "user", "content": "Next"}]
+    tool = [{"type": "function", "function": {"name": "bash", "description": "Run", "parameters": {"type": "object", "required": ["command"],
+                                                                                                    "properties": {"command": {"type": "string", "description": "Cmd"}}}}}]
+    q = '<|"|>'
+    decl = (f"<|tool>declaration:bash{{description:{q}Run{q},parameters:{{properties:{{command:{{description:{q}Cmd{q},type:{q}STRING{q}}}}},"
+            f"required:[{q}command{q}],type:{q}OBJECT{q}}}}}<tool|>")
+    want = ("<bos><|turn>system\n" + decl + "<turn|>\n<|turn>user\nUse the tool<turn|>\n<|turn>model\nFirst.<|tool_call>call:bash{command:null}<tool_call|>"
+            f"<|tool_response>response:bash{{value:{q}done{q}}}<tool_response|>Checking.Done.<turn|>\n<|turn>user\nNext<turn|>\n<|turn>model\n")
+    assert R.renderer_for("gemma4").render(msgs, tool) == want
+    assert R.renderer_for("gemma4-large").render(msgs, tool) == want + "<|channel>thought\n<channel|>"
+    # a union of bare types written as anyOf reads as a type list
+    union = [{"type": "function", "function": {"name": "f", "description": "d", "parameters": {"type": "object", "properties": {"v": {"anyOf": [{"type": "string"}, {"type": "null"}]}}}}}]
+    assert f"v:{{type:{q}['STRING', 'NULL']{q}}}" in R.renderer_for("gemma4").render(hello, union)
