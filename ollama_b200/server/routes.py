@@ -515,7 +515,8 @@ class Server:
                                  preserved_tokens=rend.is_harmony, images=media)
         hp = harmony.HarmonyParser(rend.names) if rend.is_harmony else None
         prefill = msgs[-1].get("content", "") if msgs and msgs[-1].get("role") == "assistant" else ""
-        bp = parser_for(model.config.get("parser"), tools, think, prefill) if hp is None else None
+        after_tool = bool(msgs) and msgs[-1].get("role") == "tool"
+        bp = parser_for(model.config.get("parser"), tools, think, prefill, after_tool) if hp is None else None
         tp = self._thinking_parser(rend, think, text) if bp is None else None
         tool_parser = ToolParser(tools, infer_tag(rend.template_source)) if tools and hp is None and bp is None else None
         show_thinking = think is None or think_enabled(think)

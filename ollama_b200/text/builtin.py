@@ -68,6 +68,7 @@ class Region:
     item: tuple[str, str] | None = None
     drop: bool = False
     unwrap: bool = False
+    lenient_end: bool = False                       # the stream may end inside the body: decode what is there
 
 
 class TagStreamParser:
@@ -87,6 +88,9 @@ class TagStreamParser:
         self.keep_space = keep_space                    # reasoning is handed on with the white space it ends in
         self.trim_start = trim_start                    # white space that opens the reasoning block, or a message without one, goes
         self.trim_end = trim_end                        # white space the answer ends in goes when the stream ends
+        self.channel = ""                               # text that names the block right after its opening mark ("thought\n"): dropped
+        self.reopen = False                             # a reasoning block may open anywhere in the answer, not only in front of it
+        self.mute_thinking = False                      # reasoning is parsed but not handed on
         self.drop_marks = dict(drop_marks or {})        # marks that only frame content: removed; True = white space after them goes too
         self.state: Any = "thinking" if start_thinking and think_close else "content"
         self.may_open_think = bool(think_open)          # an explicit opening tag is accepted at the very start only
@@ -130,7 +134,7 @@ class TagStreamParser:
         return "".join(content), "".join(thinking), calls
 
     def _in_thinking(self, content, thinking, calls, done) -> bool:
-        if self.may_open_think:                         # some checkpoints repeat the opening tag although the prompt ended with it
+        if self.may_open_think and not self.reopen:     # some checkpoints repeat the opening tag although the prompt ended with it
             t = self.buf.lstrip()
             if t.startswith(self.think_open):
                 self.buf, self.may_open_think = t[len(self.think_open):], False
@@ -146,6 +150,14 @@ class TagStreamParser:
             if not self.buf:
                 return False
             self.lead_ws = False
+        if getattr(self, "name_due", False):
+            if self.buf.startswith(self.channel):
+                self.buf = self.buf[len(self.channel):]
+            elif self.channel.startswith(self.buf) and not done:
+                return False
+            self.name_due = False
+        if self.mute_thinking:
+            thinking = []                               # a sink nobody reads
         marks = [self.think_close] + ([r.open for r in self.regions] if self.call_ends_thinking else [])
         hit = self._first(marks)
         if hit is None:
@@ -183,18 +195,21 @@ class TagStreamParser:
             if done and self.trim_end:
                 self.buf = self.buf.rstrip()
             self._flush(content, marks, done)
-            if "".join(content[before:]).strip():
+            if "".join(content[before:]).strip() and not self.reopen:
                 self.may_open_think = False
             return False
         i, mark = hit
         before = self.buf[:i]
         if mark == self.think_open and self.may_open_think and self._region(mark) is None:
-            if before.strip():                          # a reasoning block only opens the message
+            if before.strip() and not self.reopen:      # a reasoning block only opens the message
                 self.may_open_think = False
                 return True
-            self.buf, self.state, self.may_open_think = self.buf[i + len(mark):], "thinking", False
+            self.buf, self.state, self.may_open_think = self.buf[i + len(mark):], "thinking", self.reopen
+            if self.reopen:
+                content.append(before.rstrip())
             if self.trim_start:
                 self.lead_ws = True
+            self.name_due = bool(self.channel)
             return True
         region = self._region(mark)
         content.append(before if region.unwrap else before.rstrip())
@@ -215,6 +230,10 @@ class TagStreamParser:
             if n >= 0:
                 body, end = self.buf[:n], n
         if end < 0:
+            if done and r.lenient_end and self.buf and (decoded := r.decode(self.buf)) is not None:
+                calls.extend(self._calls(decoded))
+                self.buf, self.state = "", "content"
+                return False
             if done:                                    # an unterminated call is returned as text, the way it was produced
                 if not r.drop:
                     content.append(("" if r.unwrap else r.open) + self.buf)
@@ -586,6 +605,36 @@ def _glm_call(tools: list[dict[str, Any]] | None) -> Callable[[str], dict[str, A
     return decode
 
 
+# -- Gemma 4: call:name{key:value,...} with strings between <|"|> marks ------------------------------------------------
+_G4_STRING = re.compile(r'<\|"\|>(.*?)<\|"\|>', re.S)
+_G4_JSON_STRING = re.compile(r'"(?:\\.|[^"\\])*"')
+_G4_KEY = re.compile(r'([{,]\s*)([^\W]+)\s*:', re.UNICODE)
+
+
+def gemma4_args_to_json(text: str) -> str:
+    """The format's argument notation as JSON text: delimited strings become JSON strings (whatever they hold), bare keys are
+    quoted; numbers, booleans, null, lists and nested maps are JSON already (model/parsers/gemma4.go:394-447)."""
+    held: list[str] = []
+
+    def hold(m: re.Match) -> str:
+        held.append(json.dumps(m.group(1), ensure_ascii=False) if m.re is _G4_STRING else m.group(0))
+        return f"\x00{len(held) - 1}\x00"
+    text = _G4_JSON_STRING.sub(hold, _G4_STRING.sub(hold, text))         # strings a model wrote the JSON way stay as they are
+    text = _G4_KEY.sub(lambda m: f'{m.group(1)}"{m.group(2)}":', text)
+    return re.sub(r"\x00(\d+)\x00", lambda m: held[int(m.group(1))], text)
+
+
+def _gemma4_call(body: str) -> dict[str, Any] | None:
+    if not body.startswith("call:") or "{" not in body:
+        return None
+    name, _, rest = body[len("call:"):].partition("{")
+    try:
+        args = json.loads(gemma4_args_to_json("{" + rest))
+    except ValueError:
+        return None
+    return {"function": {"name": name.strip(), "arguments": args}} if isinstance(args, dict) else None
+
+
 # -- Laguna: GLM-style pairs, a JSON object behind the name line, or a whole JSON call ------------------------------
 _LAGUNA_ALIASES = {"read_file": "read", "write_file": "write", "edit_file": "edit", "web_fetch": "webfetch"}
 
@@ -654,7 +703,7 @@ def _cohere_actions(body: str) -> list[dict[str, Any]]:
 
 PARSERS = ("qwen3", "qwen3-thinking", "qwen3-coder", "qwen3.5", "ornith", "qwen3-vl-instruct", "qwen3-vl-thinking", "ministral", "functiongemma", "cogito", "deepseek3",
            "olmo3", "olmo3-think", "glm-4.6", "glm-4.7", "glm-ocr", "cohere", "lfm2", "lfm2-thinking", "nemotron-3-nano", "nemotron-3.5-nano",
-           "laguna", "poolside-v1", "glimmer", "passthrough")
+           "laguna", "poolside-v1", "glimmer", "gemma4", "passthrough")
 
 
 # ---------------------------------------------------------------------------------------------------
@@ -775,7 +824,7 @@ class GlimmerStreamParser:
 
 
 def parser_for(name: str | None, tools: list[dict[str, Any]] | None = None, think: Any = None,
-               prefill: str = "") -> "TagStreamParser | GlimmerStreamParser | None":
+               prefill: str = "", after_tool: bool = False) -> "TagStreamParser | GlimmerStreamParser | None":
     """Parser named by a model's configuration, or None when the name is not a built-in of this module.
 
     ``think`` is the request's think value (None = unset); ``prefill`` the content of a trailing assistant message
@@ -797,6 +846,17 @@ def parser_for(name: str | None, tools: list[dict[str, Any]] | None = None, thin
     if name in ("qwen3.5", "ornith"):             # model/parsers/qwen35.go:57-78: reasoning unless switched off, XML calls, a call ends the block
         return TagStreamParser(think_open="<think>", think_close="</think>", start_thinking=think is not False and (think is None or bool(think)) and fresh,
                                regions=[Region("<tool_call>", "</tool_call>", _xml_call(tools))], call_ends_thinking=True)
+    if name == "gemma4":
+        # model/parsers/gemma4.go:66-92, :167-365: a thought channel may open anywhere in the answer and is handed on only when the
+        # request reasons; after tool results the prompt goes on inside the model's turn, so a reasoning request starts in the
+        # channel; what the model adds behind a call (a second closing mark, the mark that opens a result) goes
+        asked_now = think is not None and bool(think)
+        p = TagStreamParser(think_open="<|channel>", think_close="<channel|>", start_thinking=asked_now and after_tool,
+                            drop_marks={"<tool_call|>": True, "<|tool_response>": True},
+                            regions=[Region("<|tool_call>", "<tool_call|>", _gemma4_call, lenient_end=True)])
+        p.channel, p.reopen, p.mute_thinking = "thought\n", True, not asked_now
+        p.may_open_think = True
+        return p
     if name == "glimmer":
         return GlimmerStreamParser(tools, think)
     if name in ("laguna", "poolside-v1"):

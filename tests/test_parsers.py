@@ -41,7 +41,7 @@ def _same(a, b):
 
 
 def _run(case, chunks):
-    p = B.parser_for(case["parser"], case.get("tools") or TOOLS if case["parser"] != "cogito" else case.get("tools"), case.get("think"), case.get("prefill", ""))
+    p = B.parser_for(case["parser"], case.get("tools") or TOOLS if case["parser"] != "cogito" else case.get("tools"), case.get("think"), case.get("prefill", ""), case.get("after_tool", False))
     content = thinking = ""
     calls = []
     for i, ch in enumerate(chunks):
@@ -263,3 +263,16 @@ def test_glimmer_parser_cases():
         B.parser_for("glimmer", [first, second]).add(" to=first<|message|>" + _atem("second") + "<|eot|>", True)
     with pytest.raises(ValueError):
         B.parser_for("glimmer", [first]).add(" to=first<|message|><atem:function_calls>oops<|eot|>", True)
+
+
+def test_gemma4_argument_notation_as_json():
+    """model/parsers/gemma4_test.go (TestGemma4ArgsToJSON), as data: delimited strings, bare keys, nesting, strings that look like keys."""
+    rows = DATA["gemma4_args"]
+    assert len(rows) >= 25
+    for c in rows:
+        assert json.loads(B.gemma4_args_to_json(c["input"])) == json.loads(c["expected"]), c["case"]
+    # the stream may end inside a call; what a model adds behind a call goes; reasoning is parsed but withheld unless asked for
+    p = B.parser_for("gemma4", None, None)
+    assert p.add('<|channel>thought\nhm<channel|>ok <|tool_call>call:f{a:<|"|>x<|"|>,n:2}', True) == ("ok", "", [{"function": {"name": "f", "arguments": {"a": "x", "n": 2}}}])
+    p = B.parser_for("gemma4", None, True, "", True)                # after tool results a reasoning request goes on inside the channel
+    assert p.add("more thought<channel|>done<tool_call|><|tool_response>", True) == ("done", "more thought", [])
