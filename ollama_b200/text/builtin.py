@@ -703,7 +703,7 @@ def _cohere_actions(body: str) -> list[dict[str, Any]]:
 
 PARSERS = ("qwen3", "qwen3-thinking", "qwen3-coder", "qwen3.5", "ornith", "qwen3-vl-instruct", "qwen3-vl-thinking", "ministral", "functiongemma", "cogito", "deepseek3",
            "olmo3", "olmo3-think", "glm-4.6", "glm-4.7", "glm-ocr", "cohere", "lfm2", "lfm2-thinking", "nemotron-3-nano", "nemotron-3.5-nano",
-           "laguna", "poolside-v1", "glimmer", "gemma4", "passthrough")
+           "laguna", "poolside-v1", "glimmer", "gemma4", "gemma4-no-thinking", "passthrough")
 
 
 # ---------------------------------------------------------------------------------------------------
@@ -846,11 +846,11 @@ def parser_for(name: str | None, tools: list[dict[str, Any]] | None = None, thin
     if name in ("qwen3.5", "ornith"):             # model/parsers/qwen35.go:57-78: reasoning unless switched off, XML calls, a call ends the block
         return TagStreamParser(think_open="<think>", think_close="</think>", start_thinking=think is not False and (think is None or bool(think)) and fresh,
                                regions=[Region("<tool_call>", "</tool_call>", _xml_call(tools))], call_ends_thinking=True)
-    if name == "gemma4":
+    if name in ("gemma4", "gemma4-no-thinking"):
         # model/parsers/gemma4.go:66-92, :167-365: a thought channel may open anywhere in the answer and is handed on only when the
         # request reasons; after tool results the prompt goes on inside the model's turn, so a reasoning request starts in the
         # channel; what the model adds behind a call (a second closing mark, the mark that opens a result) goes
-        asked_now = think is not None and bool(think)
+        asked_now = think is not None and bool(think) and name == "gemma4"      # the other name: checkpoints that never reason
         p = TagStreamParser(think_open="<|channel>", think_close="<channel|>", start_thinking=asked_now and after_tool,
                             drop_marks={"<tool_call|>": True, "<|tool_response>": True},
                             regions=[Region("<|tool_call>", "<tool_call|>", _gemma4_call, lenient_end=True)])

@@ -276,3 +276,5 @@ def test_gemma4_argument_notation_as_json():
     assert p.add('<|channel>thought\nhm<channel|>ok <|tool_call>call:f{a:<|"|>x<|"|>,n:2}', True) == ("ok", "", [{"function": {"name": "f", "arguments": {"a": "x", "n": 2}}}])
     p = B.parser_for("gemma4", None, True, "", True)                # after tool results a reasoning request goes on inside the channel
     assert p.add("more thought<channel|>done<tool_call|><|tool_response>", True) == ("done", "more thought", [])
+    p = B.parser_for("gemma4-no-thinking", None, True)
+    assert p.add("<|channel>thought\nhm<channel|>ok", True) == ("ok", "", [])
