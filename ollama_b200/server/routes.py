@@ -345,7 +345,9 @@ class Server:
                                  truncate=req.get("truncate", True) is not False, shift=req.get("shift", True) is not False,
                                  preserved_tokens=rend.is_harmony, images=media if isinstance(tokens, str) else [])
         tp = self._thinking_parser(rend, think, text) if not req.get("raw") else None
-        hp = harmony.HarmonyParser(rend.names) if rend.is_harmony and not req.get("raw") else None
+        # a model may name the harmony parser although it brings a template of its own (model/parsers/parsers.go:69-70)
+        use_harmony = rend.is_harmony or model.config.get("parser") == "harmony"
+        hp = harmony.HarmonyParser(rend.names) if use_harmony and not req.get("raw") else None
         bp = parser_for(model.config.get("parser"), None, think) if hp is None and not req.get("raw") else None
 
         def gen() -> Iterator[dict[str, Any]]:
@@ -513,7 +515,7 @@ class Server:
                                  num_keep=opts["num_keep"], stop=list(opts.get("stop") or []), grammar=grammar, grammar_after=gate,
                                  truncate=req.get("truncate", True) is not False, shift=req.get("shift", True) is not False,
                                  preserved_tokens=rend.is_harmony, images=media)
-        hp = harmony.HarmonyParser(rend.names) if rend.is_harmony else None
+        hp = harmony.HarmonyParser(rend.names) if rend.is_harmony or model.config.get("parser") == "harmony" else None
         prefill = msgs[-1].get("content", "") if msgs and msgs[-1].get("role") == "assistant" else ""
         after_tool = bool(msgs) and msgs[-1].get("role") == "tool"
         bp = parser_for(model.config.get("parser"), tools, think, prefill, after_tool) if hp is None else None
