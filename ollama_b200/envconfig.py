@@ -330,6 +330,11 @@ def as_map() -> dict[str, tuple[object, str]]:
         "B200_ATTN_SPLITS": (attn_splits(), "Upper bound of the split-K width of decode attention"),
         "B200_ATTN_SPLIT_LEN": (attn_split_len(), "Positions of allocated context per split of decode attention"),
         "B200_ATTN_MMA": (var("B200_ATTN_MMA") or "auto", "Decode attention kernel: 1 tensor cores, 0 scalar, auto by model shape"),
+        "B200_ATTN_PREFILL": (var("B200_ATTN_PREFILL") or "auto", "Prefill attention kernel: auto (tcgen05 where the shape allows), tc, mma"),
+        "B200_ATTN_DECODE_STAGES": (var("B200_ATTN_DECODE_STAGES") or "auto", "Pipeline depth of the tensor-core decode attention: 2, 3, 4 or by launch size"),
+        "B200_TC_DECODE_MIN": (var("B200_TC_DECODE_MIN") or "4", "Decode steps of at least this many sequences multiply 16-bit matrices on the tcgen05 GEMM (0 = never)"),
+        "B200_MOE_STREAM_Q": (var("B200_MOE_STREAM_Q") or "1", "MoE prefill streams MXFP4 experts as they are when no 16-bit copy is resident (0 = expand per chunk)"),
+        "B200_SK": (var("B200_SK") or "1", "Streaming decode GEMV for Q4_K / Q6_K / Q8_0 layers (0 = plane kernels)"),
         "B200_NVTX": (_bool("B200_NVTX"), "NVTX ranges around prefill chunks and decode steps"),
         "B200_NO_NATIVE": (_bool("B200_NO_NATIVE"), "Do not load the C++ host helpers (codecs, BPE merges)"),
         "B200_COMM": (comm_mode(), "Collective implementation: p2p (fused kernels) or nccl"),
